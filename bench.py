@@ -1,0 +1,364 @@
+#!/usr/bin/env python3
+"""Decode-throughput benchmark of the CUDA backend.
+
+    python bench.py --gpus 1 --steps 32 --warmup 4
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...        # the CPU restatement of the reference path
+
+A step is one greedy decode step (one token per sequence) of the workload through the
+whole layer stack. Default workload: Qwen2.5-32B-shaped dense model, Q8_0 weights
+(synthetic N(0, 0.02), seed 3), batch 1, context 8192 filled by feeding random prompt
+tokens one at a time, fp32 KV cache; with N > 1 GPUs the attention heads and MLP
+columns/rows are sharded tensor-parallel (strong scaling: the job is the same at every N).
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TYPE_BPW = {8: 34.0 / 32.0, 2: 18.0 / 32.0}          # Q8_0, Q4_0 bytes per weight
+WORKLOAD_DEFAULTS = {
+    # arch: (ggml type, seed, batch, context)
+    "qwen2.5-32b": (8, 3, 1, 8192),
+    "qwen2.5-0.5b": (8, 0, 1, 256),
+    "tinyllama-1.1b": (2, 1, 16, 768),
+    "olmoe-1b-7b": (8, 2, 64, 2048),
+}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()           # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons = [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    clocks.append(float(parts[0]))
+                    out["sm_max_mhz"] = float(parts[1])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            out["sm_mhz"] = float(np.median(clocks))
+            out["samples"] = len(clocks)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# --------------------------------------------------------------------------------------
+# CPU baseline: the C (AVX2 + OpenMP) restatement of the reference path, bounded sample
+# --------------------------------------------------------------------------------------
+def _random_blocks(ggml_type, rows, cols, rng, pool):
+    """GGUF rows of random codes with sane fp16 scales, tiled from a random pool (values do not
+    affect timing; scales are kept finite and small)."""
+    nblk = rows * cols // 32
+    bb = 34 if ggml_type == 8 else 18
+    reps = (nblk * bb + pool.size - 1) // pool.size
+    raw = np.tile(pool, reps)[:nblk * bb].reshape(nblk, bb).copy()
+    raw[:, 0] = rng.integers(0, 256, 1, dtype=np.uint8)[0]
+    raw[:, 1] = 0x10                                  # fp16 exponent ~2^-11: scale ~ 5e-4
+    return raw.reshape(-1)
+
+
+class CpuSample:
+    """A few layers + LM head of the workload on the host cores; one step = one token."""
+
+    def __init__(self, arch_kw, ggml_type, ctx):
+        from oracle import c_oracle
+        self.c = c_oracle
+        kw = arch_kw
+        if kw.get("n_experts", 0):
+            raise RuntimeError("the C restatement covers dense models")
+        from neural_api_b200.configs import step_weight_bytes
+        full_bytes = step_weight_bytes(kw, TYPE_BPW[ggml_type])
+        self.full_layers = kw["layers"]
+        self.layers = kw["layers"] if full_bytes < (2 << 30) else 2
+        rng = np.random.default_rng(0)
+        pool = rng.integers(0, 256, 8 << 20, dtype=np.uint8)
+        H, I = kw["hidden"], kw["inter"]
+        qw, kvw = kw["heads"] * kw["head_dim"], kw["kv_heads"] * kw["head_dim"]
+        m = c_oracle.CModel(H, I, self.layers, kw["heads"], kw["kv_heads"], kw["head_dim"], kw["vocab"],
+                            kw.get("rms_eps", 1e-5), kw.get("rope_theta", 1e4), tie_embeddings=True,
+                            qkv_bias=kw.get("qkv_bias", False))
+        ones = np.ones(H, dtype=np.float32)
+        m.set_tensor("embed", 0, ggml_type, _random_blocks(ggml_type, kw["vocab"], H, rng, pool))
+        m.set_tensor("final_norm", 0, 0, ones)
+        for l in range(self.layers):
+            m.set_tensor("attn_norm", l, 0, ones)
+            m.set_tensor("ffn_norm", l, 0, ones)
+            for kind, rows, cols in (("q", qw, H), ("k", kvw, H), ("v", kvw, H), ("o", H, qw), ("up", I, H),
+                                     ("gate", I, H), ("down", H, I)):
+                m.set_tensor(kind, l, ggml_type, _random_blocks(ggml_type, rows, cols, rng, pool))
+            if kw.get("qkv_bias", False):
+                m.set_tensor("bq", l, 0, np.zeros(qw, dtype=np.float32))
+                m.set_tensor("bk", l, 0, np.zeros(kvw, dtype=np.float32))
+                m.set_tensor("bv", l, 0, np.zeros(kvw, dtype=np.float32))
+        self.model = m
+        self.ctx = ctx
+        self.sess = c_oracle.CSession(m, ctx + 4)
+        self.sess.assume_len(ctx)
+        self.cores = c_oracle.num_threads()
+        self.desc = ("%d of %d layers + LM head at context %d, AVX2+OpenMP C restatement of the reference CPU path, "
+                     "layer time scaled x%g" % (self.layers, self.full_layers, ctx, self.full_layers / self.layers))
+
+    def step_seconds(self):
+        """Seconds one full decode step would take: sampled layers scaled to the full depth + head."""
+        s = self.sess
+        s.assume_len(self.ctx)
+        t0 = time.perf_counter()
+        s.step(1, self.ctx, want_logits=False)
+        t1 = time.perf_counter()
+        s.assume_len(self.ctx)
+        s.step(1, self.ctx, want_logits=True)
+        t2 = time.perf_counter()
+        layers_t = t1 - t0
+        head_t = max((t2 - t1) - layers_t, 0.0)
+        return layers_t * (self.full_layers / self.layers) + head_t
+
+    def close(self):
+        self.sess.close()
+        self.model.close()
+
+
+def run_reference(args, arch_kw, ggml_type, batch, ctx):
+    """--impl reference: the reference's CPU algorithm on the host cores, all threads."""
+    sample = CpuSample(arch_kw, ggml_type, ctx)
+    for _ in range(args.warmup):
+        sample.step_seconds()
+    times = [sample.step_seconds() for _ in range(args.steps)]
+    sample.close()
+    sec = float(np.mean(times)) * batch               # sequences run one after another on the CPU path
+    value = batch / sec
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, arch_kw, ggml_type, batch, ctx, 1),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": sample.cores, "kind": "port", "sample": sample.desc},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, arch_kw, ggml_type, batch, ctx, world):
+    return {"workload": "%s-architecture %s decode, batch %d, context %d, fp32 KV, fp32 activations"
+                        % (args.workload, {8: "Q8_0", 2: "Q4_0"}[ggml_type], batch, ctx),
+            "batch": batch, "context": ctx, "weights": {8: "Q8_0", 2: "Q4_0"}[ggml_type],
+            "parallelism": "tp%d" % world if world > 1 else "single",
+            "l2": "inputs larger than L2 (weights streamed once per step)"}
+
+
+def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, steps, warmup, do_e2e=True, do_profile=True):
+    """Builds the synthetic model, fills the context, and measures. Returns a dict of raw numbers."""
+    from neural_api_b200.backend import LlamaModel, StreamingDecoder
+    from neural_api_b200.configs import ARCHS, arch_config, step_weight_bytes
+    from neural_api_b200 import parallel
+    kw = ARCHS[arch]
+    model = LlamaModel(backend, arch_config(arch), tp_rank=rank if world > 1 else 0, tp_size=world)
+    model.init_synthetic(ggml_type, seed=seed, std=0.02)
+    model.finalize()
+    prof_steps = 2 if do_profile else 0
+    max_ctx = ctx + warmup + steps * (2 if do_e2e else 1) + prof_steps + 8
+    sess = StreamingDecoder(model, max_ctx, batch=batch)
+    rng = np.random.default_rng(seed)
+    prompt = rng.integers(0, kw["vocab"], (batch, ctx)).astype(np.int32)
+    t0 = time.perf_counter()
+    if ctx > 1:
+        sess.prefill(prompt[:, :-1])
+    prefill_s = time.perf_counter() - t0
+    tok = prompt[:, -1].copy()
+
+    def barrier():
+        backend.sync()
+        if dist is not None:
+            parallel.max_over_ranks(dist, 0.0)
+
+    out = sess.decode_greedy(tok, max(warmup, 1))
+    tok = out[-1].copy()
+    launches0 = backend.launch_count()
+    sampler = ClockSampler(backend.device)
+    sampler.start()
+    barrier()
+    backend.timer_begin()
+    out = sess.decode_greedy(tok, steps)
+    ms = backend.timer_end()
+    barrier()
+    clocks = sampler.stop()
+    launches = backend.launch_count() - launches0
+    ms = parallel.max_over_ranks(dist, ms)
+    tok = out[-1].copy()
+    res = {"ms_total": ms, "ms_per_step": ms / steps, "tokens_per_s": steps * batch / (ms * 1e-3), "launches": launches,
+           "clocks": clocks, "prefill_s": prefill_s, "kv_bytes_step": sess.last_kv_bytes(),
+           "weight_bytes_rank": model.step_weight_bytes(),
+           "weight_bytes_job": step_weight_bytes(kw, TYPE_BPW[ggml_type], tokens_per_step=batch)}
+    if do_e2e:
+        # the reference-facing call: token ids from host memory in, logits row + argmax back out, every step
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            _, amax = sess.step_forward(tok, want_logits=True)
+            tok = amax.copy()
+        backend.sync()
+        e2e_s = parallel.max_over_ranks(dist, time.perf_counter() - t0)
+        res["e2e_tokens_per_s"] = steps * batch / e2e_s
+        res["h2d"] = 8 * batch
+        res["d2h"] = batch * kw["vocab"] * 4 + 4 * batch
+    if do_profile:
+        res["profile"] = sess.profile(tok, prof_steps)
+        res["profile_steps"] = prof_steps
+    sess.close()
+    model.close()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qwen2.5-32b", choices=sorted(WORKLOAD_DEFAULTS))
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--ctx", type=int, default=None)
+    ap.add_argument("--no-extra", action="store_true", help="skip the Qwen2.5-0.5B side measurement and the CPU baseline")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    from neural_api_b200.configs import ARCHS
+    from neural_api_b200 import parallel
+    ggml_type, seed, batch, ctx = WORKLOAD_DEFAULTS[args.workload]
+    batch = args.batch or batch
+    ctx = args.ctx or ctx
+    arch_kw = ARCHS[args.workload]
+    rank, world, local_rank = parallel.env_rank_world()
+
+    if args.impl == "reference":
+        if rank == 0:
+            run_reference(args, arch_kw, ggml_type, batch, ctx)
+        return 0
+
+    dist = None
+    if world > 1:
+        import torch  # noqa: F401  (first, so that its NCCL is the one the process loads)
+        rank, world, local_rank, dist = parallel.init_process_group("cpu:gloo,cuda:nccl")
+    from neural_api_b200.backend import CudaBackend
+    backend = CudaBackend(local_rank)
+    if world > 1:
+        uid = backend.comm_unique_id() if rank == 0 else bytes(128)
+        uid = parallel.broadcast_bytes(dist, uid, src=0, length=128)
+        backend.comm_init(rank, world, uid)
+
+    res = run_workload(backend, dist, rank, world, args.workload, ggml_type, seed, batch, ctx, args.steps, args.warmup)
+    peak, peak_kind = measured_peak_gbs()
+    prof = res["profile"]
+    lin_ms, lin_n = prof["linear"]
+    lin_ms_step = lin_ms / res["profile_steps"]
+    achieved = res["weight_bytes_rank"] / (lin_ms_step * 1e-3) / 1e9 if lin_ms_step > 0 else 0.0
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tpath):
+        try:
+            traffic = json.load(open(tpath)).get(args.workload)
+        except Exception:
+            traffic = None
+    step_bytes = res["weight_bytes_rank"] + res["kv_bytes_step"]
+    line = {
+        "metric": "decode_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, arch_kw, ggml_type, batch, ctx, world),
+        "clocks": {"sm_mhz": res["clocks"]["sm_mhz"], "sm_max_mhz": res["clocks"]["sm_max_mhz"], "reasons": res["clocks"]["reasons"]},
+        "e2e": {"value": res["e2e_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},
+        "gpu_launches": res["launches"],
+        "roofline": {"bound": "hbm", "kernel": "gemv_quant_kernel (Q8_0 dequant-fused GEMV)", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
+                     "bytes_per_step": res["weight_bytes_rank"], "launches_per_step": lin_n / res["profile_steps"],
+                     "ms_per_step_in_kernel": lin_ms_step},
+        "step_roofline": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (res["ms_per_step"] * 1e-3) / 1e9,
+                          "frac": step_bytes / (res["ms_per_step"] * 1e-3) / 1e9 / peak, "frac_of_8tbs": step_bytes / (res["ms_per_step"] * 1e-3) / 8e12},
+        "profile_ms_per_step": {k: v[0] / res["profile_steps"] for k, v in prof.items()},
+        "prefill_s": res["prefill_s"],
+    }
+    if rank == 0 and world == 1 and not args.no_extra:
+        try:
+            sample = CpuSample(arch_kw, ggml_type, ctx)
+            sample.step_seconds()
+            ts = [sample.step_seconds() for _ in range(3)]
+            sec = float(np.median(ts)) * batch
+            line["cpu_baseline"] = {"value": batch / sec, "unit": "tokens/s", "cores": sample.cores, "kind": "port", "sample": sample.desc}
+            sample.close()
+        except Exception as e:                               # the baseline is reported, never required
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": "failed: %s" % e}
+        if args.workload != "qwen2.5-0.5b":
+            t, sd, b2, c2 = WORKLOAD_DEFAULTS["qwen2.5-0.5b"]
+            r2 = run_workload(backend, None, 0, 1, "qwen2.5-0.5b", t, sd, b2, c2, 128, 8, do_e2e=True, do_profile=False)
+            sb = r2["weight_bytes_rank"] + r2["kv_bytes_step"]
+            line["also"] = {"qwen2.5-0.5b Q8_0 batch 1 context 256": {
+                "tokens_per_s": r2["tokens_per_s"], "ms_per_step": r2["ms_per_step"], "e2e_tokens_per_s": r2["e2e_tokens_per_s"],
+                "step_hbm_frac": sb / (r2["ms_per_step"] * 1e-3) / 1e9 / peak, "launches_per_step": r2["launches"] / 128}}
+    if rank == 0:
+        print(json.dumps(line))
+    backend.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

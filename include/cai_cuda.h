@@ -1,0 +1,259 @@
+/*
+ * cai_cuda.h - C ABI of the B200 (sm_100a) decode backend for CAI Neural API.
+ *
+ * A cdecl shared library (libcai_cuda.so) that a Free Pascal unit placed beside
+ * neural/neuralopencl.pas binds with `external 'cai_cuda'` declarations. Plain
+ * C types only: no C++ types, no PyTorch types. Every entry point returns an
+ * int status (CAI_OK == 0) and never throws; the message of the last failure is
+ * read with cai_cuda_last_error, the way the OpenCL backend reports cl_int
+ * results through ErrorProc callbacks (neural/neuralopencl.pas:740-753,
+ * 1051-1055).
+ *
+ * Threading: one caller thread per context, like the reference's shared
+ * in-order queue that funnels every device layer through scheduler worker 0
+ * (examples/ChatTerminal/README.md:174-180). Work is enqueued on one CUDA
+ * stream owned by the context.
+ *
+ * Pointers named *_host are host memory owned by the caller; pointers named
+ * *_dev are device memory on the context's GPU (from cai_dev_alloc or another
+ * entry point of this library).
+ */
+#ifndef CAI_CUDA_H
+#define CAI_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cai_ctx cai_ctx;
+typedef struct cai_linear cai_linear;
+typedef struct cai_sdpa cai_sdpa;
+typedef struct cai_model cai_model;
+typedef struct cai_session cai_session;
+
+/* status codes */
+enum {
+  CAI_OK = 0,
+  CAI_ERR_INVALID = 1,      /* bad argument, shape or handle */
+  CAI_ERR_CUDA = 2,         /* a CUDA runtime call failed */
+  CAI_ERR_OOM = 3,          /* device allocation failed or request too large */
+  CAI_ERR_STATE = 4,        /* call out of order (e.g. step before finalize, context full) */
+  CAI_ERR_UNSUPPORTED = 5,  /* tensor type or shape outside what the kernels cover */
+  CAI_ERR_COMM = 6          /* multi-GPU communicator failure */
+};
+
+/* Tensor storage types: the ggml type ids a GGUF file carries
+ * (neural/neuralgguf.pas:100-131). */
+enum {
+  CAI_TYPE_F32 = 0,
+  CAI_TYPE_F16 = 1,
+  CAI_TYPE_Q4_0 = 2,  /* 18-byte blocks of 32: fp16 d, 16 nibble bytes; x = d*(nib-8)  (neuralgguf.pas:822-845) */
+  CAI_TYPE_Q8_0 = 8   /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
+};
+
+/* Activation opcodes of the fused linear epilogue; the numbering of
+ * cai_dot_product_int8 (neural/neural.cl:161-291): 0 none, 1 ReLU, 2 sigmoid, 3 tanh. */
+enum { CAI_ACT_NONE = 0, CAI_ACT_RELU = 1, CAI_ACT_SIGMOID = 2, CAI_ACT_TANH = 3 };
+
+/* ------------------------------------------------------------------------- */
+/* Context. Replaces TEasyOpenCL platform/device/queue setup                  */
+/* (neural/neuralopencl.pas:72-164) and the TNNet.EnableOpenCL hook           */
+/* (neural/neuralchatengine.pas:1156-1157).                                   */
+/* ------------------------------------------------------------------------- */
+int cai_cuda_init(int device_id, cai_ctx** out_ctx);
+int cai_cuda_shutdown(cai_ctx* ctx);
+/* Copies the last error message of this context (NUL terminated) into buf. */
+int cai_cuda_last_error(cai_ctx* ctx, char* buf, int buf_len);
+/* sm_count, total device bytes; either pointer may be NULL. */
+int cai_cuda_device_info(cai_ctx* ctx, int* sm_count, int64_t* total_bytes);
+/* Number of kernels this library has launched on the context since init. */
+int cai_cuda_launch_count(cai_ctx* ctx, int64_t* out_count);
+
+/* Device buffers: the cl_mem create/write/read calls of TEasyOpenCLV
+ * (neural/neuralopencl.pas:167-202). */
+int cai_dev_alloc(cai_ctx* ctx, int64_t bytes, void** out_dev);
+int cai_dev_free(cai_ctx* ctx, void* dev);
+int cai_memcpy_h2d(cai_ctx* ctx, void* dst_dev, const void* src_host, int64_t bytes);
+int cai_memcpy_d2h(cai_ctx* ctx, void* dst_host, const void* src_dev, int64_t bytes);
+int cai_dev_sync(cai_ctx* ctx);
+/* Device-time bracket on the context's stream (CUDA events):
+ * begin records, end records, synchronizes and returns the milliseconds. */
+int cai_timer_begin(cai_ctx* ctx);
+int cai_timer_end(cai_ctx* ctx, float* out_ms);
+/* Overwrites a private device buffer larger than the L2 cache (cold-cache timing). */
+int cai_flush_l2(cai_ctx* ctx);
+
+/* ------------------------------------------------------------------------- */
+/* Block codec check hook: dequantizes on the GPU through the same resident   */
+/* layout the linear kernels read, so the result must be bit-identical to     */
+/* DecodeGGMLSpan (neural/neuralgguf.pas:1471-1523).                          */
+/* ------------------------------------------------------------------------- */
+int cai_dequantize(cai_ctx* ctx, int type, const void* blocks_host, int64_t rows, int64_t cols,
+                   float* out_host);
+
+/* ------------------------------------------------------------------------- */
+/* Quantized linear layer. Replaces TDotProductSharedKernel                   */
+/* (neural/neuralopencl.pas:245-388):                                         */
+/*   cai_linear_create       <- PrepareForComputeInt8 (:844-891): weights are */
+/*                              uploaded ONCE and stay resident and immutable */
+/*   cai_linear_forward      <- ComputeInt8 + FinishAndLoadResult (:946-1104) */
+/*                              with host operands (NewVBs = true)            */
+/*   cai_linear_forward_dev  <- ComputeInt8 with pExternalVBs / ResultBuffer  */
+/*                              (:352-356, 382-387): operands stay on device  */
+/* Weights are [N rows, K cols] row-major in `type` blocks (K % 32 == 0 for   */
+/* Q8_0/Q4_0), output layout y[b*N + a] (neural/neuralvolume.pas:12736).      */
+/* ------------------------------------------------------------------------- */
+int cai_linear_create(cai_ctx* ctx, int type, const void* blocks_host, int64_t n_rows, int64_t k_cols,
+                      const float* bias_host /* nullable, N floats */, cai_linear** out);
+int cai_linear_destroy(cai_linear* lin);
+int cai_linear_forward(cai_linear* lin, const float* x_host, int batch, float* y_host, int act);
+int cai_linear_forward_dev(cai_linear* lin, const float* x_dev, int batch, float* y_dev, int act);
+/* Resident weight bytes (codes + scales), the algorithmic bytes one forward streams. */
+int cai_linear_weight_bytes(cai_linear* lin, int64_t* out_bytes);
+/* Dequantizes the RESIDENT (repacked) weights to fp32 [N*K] on the host. */
+int cai_linear_dequantize(cai_linear* lin, float* out_host);
+/* Forces one kernel family for cai_linear_forward*: 0 auto, 1 CUDA-core GEMV, 2 tcgen05 GEMM. */
+int cai_linear_set_path(cai_linear* lin, int path);
+
+/* ------------------------------------------------------------------------- */
+/* Layer-granular shims on device buffers (a TNNetLayer.ComputeCUDA override  */
+/* delegates one layer at a time, like ComputeOpenCL). Token rows are         */
+/* depth-contiguous: x[t*depth + c] (neural/neuralvolume.pas:8951-8954).      */
+/* ------------------------------------------------------------------------- */
+/* cai_token_norm with FUseMean = 0 (neural/neural.cl:1047-1085). y may alias x. */
+int cai_rmsnorm_dev(cai_ctx* ctx, const float* x_dev, const float* gain_dev, float* y_dev,
+                    int tokens, int depth, float eps);
+/* cai_rope (neural/neural.cl:1517-1542): pairs (2k,2k+1), head-tiled theta_k =
+ * base^(-2k/head_dim), token t rotates by (t + position_offset). In place. */
+int cai_rope_dev(cai_ctx* ctx, float* x_dev, int tokens, int depth, int head_dim,
+                 int position_offset, float theta_base);
+/* cai_glu_gate with FActFlag = 1 (neural/neural.cl:1213-1263):
+ * y[t*half + d] = x[t*2half + d] * swish(x[t*2half + half + d]). */
+int cai_swiglu_dev(cai_ctx* ctx, const float* x_dev, float* y_dev, int tokens, int half_depth);
+/* softmax -> top-k -> optional renormalisation of one router row per token
+ * (TNNetPointwiseSoftMax + TNNetTopKGate, neural/neuralpretrained.pas:15347-15366).
+ * Writes k expert ids and k gate values per token; ties: lowest index wins. */
+int cai_topk_gate_dev(cai_ctx* ctx, const float* router_logits_dev, int tokens, int n_experts,
+                      int top_k, int renorm, int32_t* expert_ids_dev, float* gates_dev);
+
+/* Fused GQA attention with a KV cache: TNNetFusedSDPA in incremental-decode mode
+ * (BeginIncrementalDecode / ResetCache / TruncateCache / CacheLength,
+ * tests/TestNeuralFusedSDPA.pas:226-236, 329-420; kernels neural/neural.cl:2354-2379,
+ * 2406-2499). Input row packing [allQ | allK | allV]; cache head-major. */
+int cai_sdpa_create(cai_ctx* ctx, int q_heads, int kv_heads, int head_dim, int max_ctx, cai_sdpa** out);
+int cai_sdpa_destroy(cai_sdpa* s);
+int cai_sdpa_reset(cai_sdpa* s);
+int cai_sdpa_truncate(cai_sdpa* s, int committed_len);
+int cai_sdpa_cache_len(cai_sdpa* s, int* out_len);
+/* Appends the row's K,V at slot CacheLength, then attends the row's Q over the
+ * whole cache. out_dev: q_heads*head_dim floats. */
+int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev);
+
+/* ------------------------------------------------------------------------- */
+/* Whole-model fast path: the graph BuildLlamaFromTensorReaderWithConfig      */
+/* wires (neural/neuralpretrained.pas:16196-17473), resident on the GPU.      */
+/* ------------------------------------------------------------------------- */
+/* Subset of TLlamaConfig (neural/neuralpretrained.pas:677-952). */
+typedef struct cai_llama_config {
+  int32_t hidden;
+  int32_t inter;          /* dense MLP intermediate size (ignored when n_experts > 0) */
+  int32_t layers;
+  int32_t heads;
+  int32_t kv_heads;
+  int32_t head_dim;
+  int32_t vocab;
+  float rms_eps;
+  float rope_theta;
+  int32_t tie_embeddings; /* LM head = embedding rows (neuralpretrained.pas:15655-15671) */
+  int32_t qkv_bias;       /* Qwen2 q/k/v biases (:16960-16965) */
+  int32_t qk_norm;        /* OLMoE full-width q/k RMSNorm before RoPE (:16520-16530) */
+  int32_t n_experts;      /* 0 = dense */
+  int32_t top_k;
+  int32_t norm_topk;      /* renormalise the kept router probabilities (:15347-15366) */
+  int32_t moe_inter;      /* expert intermediate size */
+} cai_llama_config;
+
+/* tp_size > 1 shards attention heads and MLP columns/rows over tp_size processes
+ * (one GPU each); ep_size > 1 shards MoE experts. Neither exists in the reference. */
+int cai_model_create(cai_ctx* ctx, const cai_llama_config* cfg, int tp_rank, int tp_size, cai_model** out);
+int cai_model_destroy(cai_model* m);
+/* One tensor under its HF name ("model.layers.3.self_attn.q_proj.weight", ...) in
+ * HF layout: rows = out features, cols = in features, `type` blocks along cols
+ * (LoadLlamaLinearWeights, neural/neuralpretrained.pas:14770-14989). 1-D tensors
+ * (norm gains, biases) are F32 with rows = 1. interleave_head_dim > 0 applies the
+ * importer's q/k row permutation target(h*hd+2k) <- row(h*hd+k),
+ * target(h*hd+2k+1) <- row(h*hd+k+hd/2) (:14792-14812); pass 0 for rows already
+ * in GGUF order. The host buffer is not retained. With tp_size > 1 the caller
+ * passes the FULL tensor and the library keeps this rank's slice. */
+int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const void* data_host,
+                            int64_t rows, int64_t cols, int interleave_head_dim);
+/* Fills every tensor on the device: weights N(0, std) from a counter-based
+ * generator keyed by (seed, tensor, global element index), quantized to `type`
+ * with the GGUF writer's Q8_0 rule (neural/neuralgguf.pas:1950-1993) or ggml's Q4_0
+ * rule; norm gains 1; biases N(0, std). Shards generate their own slices. */
+int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std);
+/* Reads one tensor (this rank's slice) back as GGUF blocks of its storage type.
+ * out_bytes_cap guards the host buffer; rows/cols/type of the slice are returned. */
+int cai_model_read_tensor(cai_model* m, const char* hf_name, void* out_host, int64_t out_bytes_cap,
+                          int* out_type, int64_t* out_rows, int64_t* out_cols);
+/* Verifies every tensor the configuration needs is present; required before sessions. */
+int cai_model_finalize(cai_model* m);
+/* Bytes of matrix weights one decode step streams on this rank (codes + scales). */
+int cai_model_step_weight_bytes(cai_model* m, int64_t* out_bytes);
+
+/* Decode session: TNNetStreamingDecoder (neural/neuraldecode.pas:5614-5663 Create,
+ * :5686-5694 Reset, :5696-5712 StepForward, :5714-5720 TruncateTo, :5759-5843
+ * Snapshot/RestoreSnapshot). `batch` independent sequences step together; the
+ * reference has one sequence per session, so per-sequence results must equal the
+ * single-sequence path. kv_type: CAI_TYPE_F32 (the --kv-fp32 cache). */
+int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_session** out);
+int cai_session_destroy(cai_session* s);
+int cai_session_reset(cai_session* s, int seq /* -1 = all */);
+int cai_session_truncate(cai_session* s, int seq, int committed_len);
+int cai_session_cache_len(cai_session* s, int seq, int* out_len);
+/* One width-1 forward per sequence. tokens_host[batch]; abs_pos_host[batch] may be
+ * NULL (= cache length, the position StepForward writes into every RoPE layer).
+ * logits_out_host (batch*vocab floats) and argmax_out_host (batch ints, first
+ * index of the maximum: ArgMaxRow, neural/neuralchatengine.pas:683-697) are
+ * nullable. Blocks until the results are on the host. */
+int cai_session_step(cai_session* s, const int32_t* tokens_host, const int32_t* abs_pos_host,
+                     float* logits_out_host, int32_t* argmax_out_host);
+/* Greedy loop kept on the device: feeds tokens_host[batch] then n_steps-1 times
+ * the previous argmax (GenerateFromIds decode loop, neural/neuralchatengine.pas:1485-1561,
+ * greedy fast path). out_tokens_host[n_steps*batch] (step-major) nullable.
+ * No host round trip between steps. */
+int cai_session_decode_greedy(cai_session* s, const int32_t* tokens_host, int n_steps,
+                              int32_t* out_tokens_host);
+/* Feeds n_tokens per sequence (tokens_host[seq*n_tokens + i]) one position at a
+ * time without reading anything back: the prefill loop of GenerateFromIds
+ * (neural/neuralchatengine.pas:1466-1470). */
+int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens);
+/* Per-launch device timing of n_steps eager (non-graph) steps fed like cai_session_decode_greedy:
+ * one CUDA event after every launch on the context's stream, times summed per kernel family.
+ * out_ms[4] / out_launches[4]: 0 linear layers, 1 attention, 2 other operators, 3 collectives.
+ * The per-layer-class report of TNNet.LayerClassTimingReport (neural/neuralchatengine.pas:1613-1623).
+ * Advances the session by n_steps. */
+int cai_session_profile(cai_session* s, const int32_t* tokens_host, int n_steps, float* out_ms, int64_t* out_launches);
+/* Deep copy of the KV caches and lengths / restore (TNNetDecoderSessionSnapshot). */
+int cai_session_snapshot(cai_session* s);
+int cai_session_restore(cai_session* s);
+/* Device logits of the last step, [batch*vocab] (this rank's shard when tp_size > 1). */
+int cai_session_logits_dev(cai_session* s, const float** out_dev);
+/* Bytes of KV cache the last step read (for the roofline arithmetic). */
+int cai_session_last_kv_bytes(cai_session* s, int64_t* out_bytes);
+
+/* ------------------------------------------------------------------------- */
+/* Multi-GPU plumbing (no reference counterpart): one process per GPU. The    */
+/* 128-byte id is created on rank 0 and handed to the others by the host      */
+/* program (torch.distributed, MPI, a file ...).                              */
+/* ------------------------------------------------------------------------- */
+int cai_comm_unique_id(unsigned char out_id[128]);
+int cai_comm_init(cai_ctx* ctx, int rank, int world, const unsigned char id[128]);
+int cai_comm_allreduce_dev(cai_ctx* ctx, float* buf_dev, int64_t count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAI_CUDA_H */

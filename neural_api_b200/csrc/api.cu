@@ -1,0 +1,418 @@
+// C-ABI entry points: context, device buffers, timing, codec hook, the resident
+// linear layer and the layer-granular shims. The model / session entry points
+// live in model.cu.
+#include "cai_common.cuh"
+#include <new>
+#include <stdlib.h>
+
+int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...) {
+  if (ctx) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+int cai_prof_mark(cai_ctx* ctx, int family) {
+  if (ctx->prof_n >= ctx->prof_cap) {
+    const int ncap = ctx->prof_cap ? ctx->prof_cap * 2 : 4096;
+    cudaEvent_t* ne = (cudaEvent_t*)realloc(ctx->prof_events, sizeof(cudaEvent_t) * (size_t)ncap);
+    int* nf = (int*)realloc(ctx->prof_family, sizeof(int) * (size_t)ncap);
+    if (!ne || !nf) return CAI_ERR_OOM;
+    ctx->prof_events = ne; ctx->prof_family = nf;
+    for (int i = ctx->prof_cap; i < ncap; ++i) cudaEventCreate(&ctx->prof_events[i]);
+    ctx->prof_cap = ncap;
+  }
+  cudaEventRecord(ctx->prof_events[ctx->prof_n], ctx->stream);
+  ctx->prof_family[ctx->prof_n] = family;
+  ctx->prof_n++;
+  return CAI_OK;
+}
+
+extern "C" {
+
+int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
+  if (!out_ctx) return CAI_ERR_INVALID;
+  *out_ctx = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device_id < 0 || device_id >= count) { cudaGetLastError(); return CAI_ERR_CUDA; }
+  if (cudaSetDevice(device_id) != cudaSuccess) { cudaGetLastError(); return CAI_ERR_CUDA; }
+  cai_ctx* ctx = new (std::nothrow) cai_ctx();
+  if (!ctx) return CAI_ERR_OOM;
+  memset(ctx, 0, sizeof(*ctx));
+  ctx->device = device_id;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device_id) != cudaSuccess) { delete ctx; return CAI_ERR_CUDA; }
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->total_mem = prop.totalGlobalMem;
+  if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreate(&ctx->ev_begin) != cudaSuccess || cudaEventCreate(&ctx->ev_end) != cudaSuccess) {
+    delete ctx;
+    return CAI_ERR_CUDA;
+  }
+  *out_ctx = ctx;
+  return CAI_OK;
+}
+
+int cai_cuda_shutdown(cai_ctx* ctx) {
+  if (!ctx) return CAI_ERR_INVALID;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  comm_destroy(ctx);
+  for (int i = 0; i < ctx->prof_cap; ++i) cudaEventDestroy(ctx->prof_events[i]);
+  free(ctx->prof_events);
+  free(ctx->prof_family);
+  if (ctx->l2_flush_buf) cudaFree(ctx->l2_flush_buf);
+  if (ctx->staging_dev) cudaFree(ctx->staging_dev);
+  if (ctx->staging_pinned) cudaFreeHost(ctx->staging_pinned);
+  cudaEventDestroy(ctx->ev_begin);
+  cudaEventDestroy(ctx->ev_end);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return CAI_OK;
+}
+
+int cai_cuda_last_error(cai_ctx* ctx, char* buf, int buf_len) {
+  if (!ctx || !buf || buf_len < 1) return CAI_ERR_INVALID;
+  strncpy(buf, ctx->err, (size_t)buf_len - 1);
+  buf[buf_len - 1] = 0;
+  return CAI_OK;
+}
+
+int cai_cuda_device_info(cai_ctx* ctx, int* sm_count, int64_t* total_bytes) {
+  if (!ctx) return CAI_ERR_INVALID;
+  if (sm_count) *sm_count = ctx->sm_count;
+  if (total_bytes) *total_bytes = (int64_t)ctx->total_mem;
+  return CAI_OK;
+}
+
+int cai_cuda_launch_count(cai_ctx* ctx, int64_t* out_count) {
+  if (!ctx || !out_count) return CAI_ERR_INVALID;
+  *out_count = ctx->launches;
+  return CAI_OK;
+}
+
+int cai_dev_alloc(cai_ctx* ctx, int64_t bytes, void** out_dev) {
+  CAI_TRY(cai_bind(ctx));
+  if (!out_dev || bytes <= 0) return cai_fail(ctx, CAI_ERR_INVALID, "cai_dev_alloc: %lld bytes", (long long)bytes);
+  size_t free_b = 0, total_b = 0;
+  CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
+  if ((size_t)bytes > free_b) return cai_fail(ctx, CAI_ERR_OOM, "request of %lld bytes exceeds %zu free device bytes", (long long)bytes, free_b);
+  if (cudaMalloc(out_dev, (size_t)bytes) != cudaSuccess) { cudaGetLastError(); return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%lld) failed", (long long)bytes); }
+  return CAI_OK;
+}
+int cai_dev_free(cai_ctx* ctx, void* dev) {
+  CAI_TRY(cai_bind(ctx));
+  if (dev) CAI_CUDA(ctx, cudaFree(dev));
+  return CAI_OK;
+}
+int cai_memcpy_h2d(cai_ctx* ctx, void* dst_dev, const void* src_host, int64_t bytes) {
+  CAI_TRY(cai_bind(ctx));
+  if (!dst_dev || !src_host || bytes < 0) return cai_fail(ctx, CAI_ERR_INVALID, "cai_memcpy_h2d: bad argument");
+  CAI_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+int cai_memcpy_d2h(cai_ctx* ctx, void* dst_host, const void* src_dev, int64_t bytes) {
+  CAI_TRY(cai_bind(ctx));
+  if (!dst_host || !src_dev || bytes < 0) return cai_fail(ctx, CAI_ERR_INVALID, "cai_memcpy_d2h: bad argument");
+  CAI_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, (size_t)bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+int cai_dev_sync(cai_ctx* ctx) {
+  CAI_TRY(cai_bind(ctx));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+int cai_timer_begin(cai_ctx* ctx) {
+  CAI_TRY(cai_bind(ctx));
+  CAI_CUDA(ctx, cudaEventRecord(ctx->ev_begin, ctx->stream));
+  return CAI_OK;
+}
+int cai_timer_end(cai_ctx* ctx, float* out_ms) {
+  CAI_TRY(cai_bind(ctx));
+  if (!out_ms) return cai_fail(ctx, CAI_ERR_INVALID, "cai_timer_end: null output");
+  CAI_CUDA(ctx, cudaEventRecord(ctx->ev_end, ctx->stream));
+  CAI_CUDA(ctx, cudaEventSynchronize(ctx->ev_end));
+  CAI_CUDA(ctx, cudaEventElapsedTime(out_ms, ctx->ev_begin, ctx->ev_end));
+  return CAI_OK;
+}
+int cai_flush_l2(cai_ctx* ctx) {
+  CAI_TRY(cai_bind(ctx));
+  if (!ctx->l2_flush_buf) {
+    ctx->l2_flush_bytes = (size_t)256 << 20;   // twice the 126 MB L2
+    CAI_CUDA(ctx, cudaMalloc(&ctx->l2_flush_buf, ctx->l2_flush_bytes));
+  }
+  CAI_CUDA(ctx, cudaMemsetAsync(ctx->l2_flush_buf, 0, ctx->l2_flush_bytes, ctx->stream));
+  return CAI_OK;
+}
+
+int cai_dequantize(cai_ctx* ctx, int type, const void* blocks_host, int64_t rows, int64_t cols, float* out_host) {
+  CAI_TRY(cai_bind(ctx));
+  if (!blocks_host || !out_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_dequantize: null buffer");
+  QWeight w;
+  int st = qweight_alloc(ctx, &w, type, rows, cols);
+  if (st != CAI_OK) return st;
+  float* out_dev = nullptr;
+  st = qweight_upload(ctx, &w, blocks_host, rows, cols, 0, 0, 0);
+  if (st == CAI_OK && cudaMalloc((void**)&out_dev, (size_t)rows * cols * 4) != cudaSuccess) { cudaGetLastError(); st = cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc failed"); }
+  if (st == CAI_OK) st = qweight_dequantize_to_dev(ctx, &w, out_dev);
+  if (st == CAI_OK) {
+    cudaError_t e = cudaMemcpyAsync(out_host, out_dev, (size_t)rows * cols * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) st = cai_fail(ctx, CAI_ERR_CUDA, "readback -> %s", cudaGetErrorString(e));
+  }
+  if (out_dev) cudaFree(out_dev);
+  qweight_free(&w);
+  return st;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// resident linear layer
+// ---------------------------------------------------------------------------
+struct cai_linear {
+  cai_ctx* ctx;
+  QWeight w;
+  float* x_dev = nullptr;
+  float* y_dev = nullptr;
+  int cap_batch = 0;
+  int path = 0;
+};
+
+static int linear_ensure_io(cai_linear* lin, int batch) {
+  if (batch <= lin->cap_batch) return CAI_OK;
+  cai_ctx* ctx = lin->ctx;
+  if (lin->x_dev) cudaFree(lin->x_dev);
+  if (lin->y_dev) cudaFree(lin->y_dev);
+  lin->x_dev = lin->y_dev = nullptr; lin->cap_batch = 0;
+  CAI_CUDA(ctx, cudaMalloc((void**)&lin->x_dev, (size_t)batch * lin->w.k * 4));
+  CAI_CUDA(ctx, cudaMalloc((void**)&lin->y_dev, (size_t)batch * lin->w.n * 4));
+  lin->cap_batch = batch;
+  return CAI_OK;
+}
+
+extern "C" {
+
+int cai_linear_create(cai_ctx* ctx, int type, const void* blocks_host, int64_t n_rows, int64_t k_cols,
+                      const float* bias_host, cai_linear** out) {
+  CAI_TRY(cai_bind(ctx));
+  if (!out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_create: null output");
+  *out = nullptr;
+  cai_linear* lin = new (std::nothrow) cai_linear();
+  if (!lin) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
+  lin->ctx = ctx;
+  int st = qweight_alloc(ctx, &lin->w, type, n_rows, k_cols);
+  if (st == CAI_OK) st = qweight_upload(ctx, &lin->w, blocks_host, n_rows, k_cols, 0, 0, 0);
+  if (st == CAI_OK && bias_host) {
+    if (cudaMalloc((void**)&lin->w.bias, (size_t)n_rows * 4) != cudaSuccess) { cudaGetLastError(); st = cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc failed"); }
+    else {
+      cudaError_t e = cudaMemcpyAsync(lin->w.bias, bias_host, (size_t)n_rows * 4, cudaMemcpyHostToDevice, ctx->stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+      if (e != cudaSuccess) st = cai_fail(ctx, CAI_ERR_CUDA, "bias upload -> %s", cudaGetErrorString(e));
+    }
+  }
+  if (st != CAI_OK) { qweight_free(&lin->w); delete lin; return st; }
+  *out = lin;
+  return CAI_OK;
+}
+
+int cai_linear_destroy(cai_linear* lin) {
+  if (!lin) return CAI_ERR_INVALID;
+  cudaSetDevice(lin->ctx->device);
+  cudaStreamSynchronize(lin->ctx->stream);
+  if (lin->x_dev) cudaFree(lin->x_dev);
+  if (lin->y_dev) cudaFree(lin->y_dev);
+  qweight_free(&lin->w);
+  delete lin;
+  return CAI_OK;
+}
+
+int cai_linear_forward_dev(cai_linear* lin, const float* x_dev, int batch, float* y_dev, int act) {
+  if (!lin) return CAI_ERR_INVALID;
+  cai_ctx* ctx = lin->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (act < 0 || act > 3) return cai_fail(ctx, CAI_ERR_INVALID, "activation opcode %d", act);
+  LinearArgs a;
+  a.w = &lin->w; a.x = x_dev; a.ldx = lin->w.k; a.y = y_dev; a.ldy = lin->w.n; a.batch = batch; a.act = act;
+  return linear_launch(ctx, a);
+}
+
+int cai_linear_forward(cai_linear* lin, const float* x_host, int batch, float* y_host, int act) {
+  if (!lin) return CAI_ERR_INVALID;
+  cai_ctx* ctx = lin->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!x_host || !y_host || batch < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_forward: bad argument");
+  CAI_TRY(linear_ensure_io(lin, batch));
+  CAI_CUDA(ctx, cudaMemcpyAsync(lin->x_dev, x_host, (size_t)batch * lin->w.k * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_TRY(cai_linear_forward_dev(lin, lin->x_dev, batch, lin->y_dev, act));
+  CAI_CUDA(ctx, cudaMemcpyAsync(y_host, lin->y_dev, (size_t)batch * lin->w.n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+int cai_linear_weight_bytes(cai_linear* lin, int64_t* out_bytes) {
+  if (!lin || !out_bytes) return CAI_ERR_INVALID;
+  *out_bytes = (int64_t)lin->w.bytes();
+  return CAI_OK;
+}
+
+int cai_linear_dequantize(cai_linear* lin, float* out_host) {
+  if (!lin) return CAI_ERR_INVALID;
+  cai_ctx* ctx = lin->ctx;
+  CAI_TRY(cai_bind(ctx));
+  float* out_dev = nullptr;
+  const size_t bytes = (size_t)lin->w.n * lin->w.k * 4;
+  if (cudaMalloc((void**)&out_dev, bytes) != cudaSuccess) { cudaGetLastError(); return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%zu) failed", bytes); }
+  int st = qweight_dequantize_to_dev(ctx, &lin->w, out_dev);
+  if (st == CAI_OK) {
+    cudaError_t e = cudaMemcpyAsync(out_host, out_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) st = cai_fail(ctx, CAI_ERR_CUDA, "readback -> %s", cudaGetErrorString(e));
+  }
+  cudaFree(out_dev);
+  return st;
+}
+
+int cai_linear_set_path(cai_linear* lin, int path) {
+  if (!lin) return CAI_ERR_INVALID;
+  if (path < 0 || path > 2) return cai_fail(lin->ctx, CAI_ERR_INVALID, "path %d", path);
+  if (path == 2) return cai_fail(lin->ctx, CAI_ERR_UNSUPPORTED, "the tcgen05 GEMM path is not built into this library");
+  lin->path = path;
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// layer shims
+// ---------------------------------------------------------------------------
+int cai_rmsnorm_dev(cai_ctx* ctx, const float* x_dev, const float* gain_dev, float* y_dev, int tokens, int depth, float eps) {
+  CAI_TRY(cai_bind(ctx));
+  if (!x_dev || !gain_dev || !y_dev || tokens < 1 || depth < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_rmsnorm_dev: bad argument");
+  return op_rmsnorm(ctx, x_dev, depth, gain_dev, y_dev, depth, tokens, depth, eps);
+}
+
+int cai_rope_dev(cai_ctx* ctx, float* x_dev, int tokens, int depth, int head_dim, int position_offset, float theta_base) {
+  CAI_TRY(cai_bind(ctx));
+  if (!x_dev || tokens < 1 || depth < 2 || head_dim < 2 || (head_dim % 2) || (depth % head_dim))
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_rope_dev: depth %d head_dim %d", depth, head_dim);
+  float* theta = nullptr;
+  CAI_CUDA(ctx, cudaMalloc((void**)&theta, (size_t)(head_dim / 2) * 4));
+  int st = op_rope_theta_table(ctx, theta, head_dim, theta_base);
+  if (st == CAI_OK) st = op_rope(ctx, x_dev, depth, tokens, depth, head_dim, theta, nullptr, 0, position_offset);
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(theta);
+  return st;
+}
+
+int cai_swiglu_dev(cai_ctx* ctx, const float* x_dev, float* y_dev, int tokens, int half_depth) {
+  CAI_TRY(cai_bind(ctx));
+  if (!x_dev || !y_dev || tokens < 1 || half_depth < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_swiglu_dev: bad argument");
+  return op_swiglu(ctx, x_dev, 2 * (int64_t)half_depth, y_dev, half_depth, tokens, half_depth);
+}
+
+int cai_topk_gate_dev(cai_ctx* ctx, const float* router_logits_dev, int tokens, int n_experts, int top_k, int renorm,
+                      int32_t* expert_ids_dev, float* gates_dev) {
+  CAI_TRY(cai_bind(ctx));
+  if (!router_logits_dev || !expert_ids_dev || !gates_dev || tokens < 1 || n_experts < 1)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_topk_gate_dev: bad argument");
+  return op_topk_gate(ctx, router_logits_dev, tokens, n_experts, top_k, renorm, expert_ids_dev, gates_dev);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// fused attention layer with its cache
+// ---------------------------------------------------------------------------
+struct cai_sdpa {
+  cai_ctx* ctx;
+  int q_heads, kv_heads, head_dim, max_ctx;
+  float* k_cache = nullptr;
+  float* v_cache = nullptr;
+  int32_t* len_dev = nullptr;
+  float* row_dev = nullptr;      // private copy of the input row
+  float* partial = nullptr;
+  int nsplit = 1;
+  int len = 0;
+};
+
+extern "C" {
+
+int cai_sdpa_create(cai_ctx* ctx, int q_heads, int kv_heads, int head_dim, int max_ctx, cai_sdpa** out) {
+  CAI_TRY(cai_bind(ctx));
+  if (!out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_sdpa_create: null output");
+  *out = nullptr;
+  if (q_heads < 1 || kv_heads < 1 || (q_heads % kv_heads) || head_dim < 2 || (head_dim % 2) || head_dim > 256 || max_ctx < 1)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_sdpa_create: heads %d/%d head_dim %d ctx %d", q_heads, kv_heads, head_dim, max_ctx);
+  cai_sdpa* s = new (std::nothrow) cai_sdpa();
+  if (!s) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
+  s->ctx = ctx; s->q_heads = q_heads; s->kv_heads = kv_heads; s->head_dim = head_dim; s->max_ctx = max_ctx;
+  const size_t cache = (size_t)kv_heads * max_ctx * head_dim * 4;
+  s->nsplit = attn_nsplit(ctx, 1, kv_heads, max_ctx);
+  const size_t rowf = (size_t)(q_heads + 2 * kv_heads) * head_dim;
+  bool ok = cudaMalloc((void**)&s->k_cache, cache) == cudaSuccess && cudaMalloc((void**)&s->v_cache, cache) == cudaSuccess &&
+            cudaMalloc((void**)&s->len_dev, 4) == cudaSuccess && cudaMalloc((void**)&s->row_dev, rowf * 4) == cudaSuccess &&
+            cudaMalloc((void**)&s->partial, attn_partial_floats(1, q_heads, s->nsplit, head_dim) * 4) == cudaSuccess;
+  if (!ok) { cudaGetLastError(); cai_sdpa_destroy(s); return cai_fail(ctx, CAI_ERR_OOM, "attention cache of %zu bytes does not fit", 2 * cache); }
+  cudaMemsetAsync(s->len_dev, 0, 4, ctx->stream);
+  *out = s;
+  return CAI_OK;
+}
+
+int cai_sdpa_destroy(cai_sdpa* s) {
+  if (!s) return CAI_ERR_INVALID;
+  cudaSetDevice(s->ctx->device);
+  cudaStreamSynchronize(s->ctx->stream);
+  if (s->k_cache) cudaFree(s->k_cache);
+  if (s->v_cache) cudaFree(s->v_cache);
+  if (s->len_dev) cudaFree(s->len_dev);
+  if (s->row_dev) cudaFree(s->row_dev);
+  if (s->partial) cudaFree(s->partial);
+  delete s;
+  return CAI_OK;
+}
+
+static int sdpa_set_len(cai_sdpa* s, int len) {
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  s->len = len;
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->len_dev, &s->len, 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+int cai_sdpa_reset(cai_sdpa* s) { return s ? sdpa_set_len(s, 0) : CAI_ERR_INVALID; }
+int cai_sdpa_truncate(cai_sdpa* s, int committed_len) {
+  if (!s) return CAI_ERR_INVALID;
+  if (committed_len < 0 || committed_len > s->len) return cai_fail(s->ctx, CAI_ERR_INVALID, "truncate to %d outside the committed prefix of %d", committed_len, s->len);
+  return sdpa_set_len(s, committed_len);
+}
+int cai_sdpa_cache_len(cai_sdpa* s, int* out_len) {
+  if (!s || !out_len) return CAI_ERR_INVALID;
+  *out_len = s->len;
+  return CAI_OK;
+}
+
+int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!qkv_row_dev || !out_dev) return cai_fail(ctx, CAI_ERR_INVALID, "cai_sdpa_step_dev: null buffer");
+  if (s->len >= s->max_ctx) return cai_fail(ctx, CAI_ERR_STATE, "attention cache is full (%d rows)", s->max_ctx);
+  const size_t rowf = (size_t)(s->q_heads + 2 * s->kv_heads) * s->head_dim;
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->row_dev, qkv_row_dev, rowf * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  AttnArgs a;
+  a.qkv = s->row_dev; a.ld = (int64_t)rowf; a.k_cache = s->k_cache; a.v_cache = s->v_cache; a.cache_len_dev = s->len_dev;
+  a.batch = 1; a.q_heads = s->q_heads; a.kv_heads = s->kv_heads; a.head_dim = s->head_dim; a.max_ctx = s->max_ctx;
+  a.out = out_dev; a.ldo = (int64_t)s->q_heads * s->head_dim; a.partial = s->partial; a.nsplit = s->nsplit;
+  CAI_TRY(attn_rope_append(ctx, a));
+  CAI_TRY(attn_decode(ctx, a));
+  s->len += 1;
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->len_dev, &s->len, 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+}  // extern "C"

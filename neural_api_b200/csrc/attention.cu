@@ -1,0 +1,337 @@
+// KV-cache GQA decode attention with a split over the context.
+//
+//   rope_append : optional full-width q/k RMSNorm, RoPE on Q (in place) and K,
+//                 K,V of the token written at slot cache_len[b] of the head-major
+//                 cache [b][kv_head][pos][d].
+//   decode      : one CTA per (kv head, context split, sequence). The CTA serves
+//                 every query head of the GQA group, so each K/V row is read from
+//                 HBM once per group rather than once per query head. Lanes are
+//                 grouped LPK = ceil(hd/8) per key (8 channels per lane, two
+//                 16-byte loads); every lane group keeps an online-softmax state
+//                 (m, l, acc) that is merged lanes -> warps -> splits in a fixed
+//                 order. Scores are scaled by 1/sqrt(hd) after the dot product and
+//                 the sum is divided once at the end, as in the reference kernel.
+//   combine     : merges the per-split partial states.
+#include "cai_common.cuh"
+#include <math.h>
+
+struct AttnParams {
+  float* qkv; int64_t ld;
+  float* k_cache; float* v_cache;
+  const int32_t* cache_len;
+  int q_heads, kv_heads, head_dim, max_ctx;
+  const float* theta; const int32_t* pos;
+  const float* q_norm; const float* k_norm; float eps;
+  float* out; int64_t ldo;
+  float* partial; int nsplit;
+  float inv_sqrt_d;
+};
+
+__global__ void rope_append_kernel(const AttnParams p) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const int hd = p.head_dim;
+  const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
+  float* row = p.qkv + (int64_t)b * p.ld;
+  const int slot = p.cache_len[b];
+  if (slot >= p.max_ctx) return;
+  float inv_q = 1.f, inv_k = 1.f;
+  if (p.q_norm) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < qw; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+    ss = block_sum(ss, red);
+    inv_q = 1.0f / sqrtf(ss / (float)qw + p.eps);
+    ss = 0.f;
+    for (int c = threadIdx.x; c < kw; c += blockDim.x) ss = fmaf(row[qw + c], row[qw + c], ss);
+    ss = block_sum(ss, red);
+    inv_k = 1.0f / sqrtf(ss / (float)kw + p.eps);
+  }
+  const int pos = p.pos ? p.pos[b] : slot;
+  const int half_hd = hd >> 1;
+  // Q pairs, in place
+  for (int pr = threadIdx.x; pr < (qw >> 1); pr += blockDim.x) {
+    float x0 = row[2 * pr], x1 = row[2 * pr + 1];
+    if (p.q_norm) { x0 = p.q_norm[2 * pr] * (x0 * inv_q); x1 = p.q_norm[2 * pr + 1] * (x1 * inv_q); }
+    if (p.theta) {
+      float s, c;
+      sincosf((float)pos * p.theta[pr % half_hd], &s, &c);
+      const float y0 = c * x0 - s * x1, y1 = s * x0 + c * x1;
+      x0 = y0; x1 = y1;
+    }
+    row[2 * pr] = x0; row[2 * pr + 1] = x1;
+  }
+  // K pairs -> cache; V -> cache
+  for (int pr = threadIdx.x; pr < (kw >> 1); pr += blockDim.x) {
+    float x0 = row[qw + 2 * pr], x1 = row[qw + 2 * pr + 1];
+    if (p.k_norm) { x0 = p.k_norm[2 * pr] * (x0 * inv_k); x1 = p.k_norm[2 * pr + 1] * (x1 * inv_k); }
+    if (p.theta) {
+      float s, c;
+      sincosf((float)pos * p.theta[pr % half_hd], &s, &c);
+      const float y0 = c * x0 - s * x1, y1 = s * x0 + c * x1;
+      x0 = y0; x1 = y1;
+    }
+    const int g = (2 * pr) / hd, d = (2 * pr) % hd;
+    float* dst = p.k_cache + (((int64_t)b * p.kv_heads + g) * p.max_ctx + slot) * hd + d;
+    dst[0] = x0; dst[1] = x1;
+  }
+  for (int c = threadIdx.x; c < kw; c += blockDim.x) {
+    const int g = c / hd, d = c % hd;
+    p.v_cache[(((int64_t)b * p.kv_heads + g) * p.max_ctx + slot) * hd + d] = row[qw + kw + c];
+  }
+}
+
+__device__ __forceinline__ void load8(const float* __restrict__ ptr, int nd, bool vec, float (&v)[8]) {
+  if (vec) {
+    const float4 a = *(const float4*)ptr, b = *(const float4*)(ptr + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (i < nd) ? ptr[i] : 0.f;
+  }
+}
+
+constexpr int ATTN_WARPS = 4;
+constexpr int ATTN_KEYS = 4;   // keys in flight per lane group
+
+template <int GT>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const AttnParams p, int lpk) {
+  extern __shared__ float smem[];
+  const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int hd = p.head_dim;
+  const int G = p.q_heads / p.kv_heads;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % lpk, kslot = lane / lpk;
+  const int kpw = 32 / lpk;
+  const int d0 = sub * 8;
+  int nd = hd - d0; nd = nd > 8 ? 8 : (nd < 0 ? 0 : nd);
+  const bool vec = (nd == 8) && ((hd & 3) == 0);
+
+  const int n = p.cache_len[b] + 1;                  // keys after the append
+  const int chunk = (n + p.nsplit - 1) / p.nsplit;
+  const int j_begin = split * chunk;
+  int j_end = j_begin + chunk; if (j_end > n) j_end = n;
+
+  float* q_s = smem;                                  // [G][hd]
+  float* merge_s = smem + (size_t)G * hd;             // [ATTN_WARPS][GT][hd + 2]
+  const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * hd;
+  for (int i = threadIdx.x; i < G * hd; i += blockDim.x) q_s[i] = qrow[i];
+  __syncthreads();
+
+  const float* kbase = p.k_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * hd;
+  const float* vbase = p.v_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * hd;
+  const int key_stride = ATTN_WARPS * kpw;
+
+  for (int h0 = 0; h0 < G; h0 += GT) {
+    float m[GT], l[GT], acc[GT][8];
+#pragma unroll
+    for (int t = 0; t < GT; ++t) {
+      m[t] = -INFINITY; l[t] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[t][i] = 0.f;
+    }
+    for (int j0 = j_begin + warp * kpw + kslot; j0 < j_end; j0 += key_stride * ATTN_KEYS) {
+      float kv[ATTN_KEYS][8];
+      bool valid[ATTN_KEYS];
+#pragma unroll
+      for (int t = 0; t < ATTN_KEYS; ++t) {
+        const int j = j0 + t * key_stride;
+        valid[t] = (j < j_end) && (nd > 0);
+        if (valid[t]) load8(kbase + (int64_t)j * hd + d0, nd, vec, kv[t]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) kv[t][i] = 0.f;
+        }
+      }
+      float s[GT][ATTN_KEYS];
+#pragma unroll
+      for (int hh = 0; hh < GT; ++hh) {
+        const int h = (h0 + hh < G) ? (h0 + hh) : (G - 1);
+        float qv[8];
+        load8(q_s + h * hd + d0, nd, vec, qv);
+#pragma unroll
+        for (int t = 0; t < ATTN_KEYS; ++t) {
+          float dsum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dsum = fmaf(qv[i], kv[t][i], dsum);
+          s[hh][t] = dsum;
+        }
+      }
+      // reduce the partial dots across the lanes of a key group
+      for (int o = 1; o < lpk; o <<= 1) {
+#pragma unroll
+        for (int hh = 0; hh < GT; ++hh)
+#pragma unroll
+          for (int t = 0; t < ATTN_KEYS; ++t) s[hh][t] += __shfl_xor_sync(0xffffffffu, s[hh][t], o);
+      }
+      // V rows reuse the K registers
+#pragma unroll
+      for (int t = 0; t < ATTN_KEYS; ++t) {
+        const int j = j0 + t * key_stride;
+        if (valid[t]) load8(vbase + (int64_t)j * hd + d0, nd, vec, kv[t]);
+      }
+#pragma unroll
+      for (int hh = 0; hh < GT; ++hh) {
+        float mx = m[hh];
+#pragma unroll
+        for (int t = 0; t < ATTN_KEYS; ++t) {
+          const int j = j0 + t * key_stride;
+          s[hh][t] = (j < j_end) ? s[hh][t] * p.inv_sqrt_d : -INFINITY;
+          mx = fmaxf(mx, s[hh][t]);
+        }
+        if (mx == -INFINITY) continue;
+        const float scale = expf(m[hh] - mx);
+        float pt[ATTN_KEYS];
+        float lsum = 0.f;
+#pragma unroll
+        for (int t = 0; t < ATTN_KEYS; ++t) { pt[t] = expf(s[hh][t] - mx); lsum += pt[t]; }
+        l[hh] = l[hh] * scale + lsum;
+        m[hh] = mx;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float a = acc[hh][i] * scale;
+#pragma unroll
+          for (int t = 0; t < ATTN_KEYS; ++t) a = fmaf(pt[t], kv[t][i], a);
+          acc[hh][i] = a;
+        }
+      }
+    }
+    // merge the key groups of a warp (lanes with the same `sub`)
+    for (int o = lpk; o < 32; o <<= 1) {
+#pragma unroll
+      for (int hh = 0; hh < GT; ++hh) {
+        const float om = __shfl_xor_sync(0xffffffffu, m[hh], o);
+        const float ol = __shfl_xor_sync(0xffffffffu, l[hh], o);
+        const float mx = fmaxf(m[hh], om);
+        const float sa = (mx == -INFINITY) ? 0.f : expf(m[hh] - mx);
+        const float sb = (mx == -INFINITY) ? 0.f : expf(om - mx);
+        l[hh] = l[hh] * sa + ol * sb;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float oa = __shfl_xor_sync(0xffffffffu, acc[hh][i], o);
+          acc[hh][i] = acc[hh][i] * sa + oa * sb;
+        }
+        m[hh] = mx;
+      }
+    }
+    // warps -> shared memory
+    __syncthreads();   // merge_s free (previous head tile consumed)
+    if (kslot == 0) {
+#pragma unroll
+      for (int hh = 0; hh < GT; ++hh) {
+        float* dst = merge_s + ((size_t)warp * GT + hh) * (hd + 2);
+        if (sub == 0) { dst[0] = m[hh]; dst[1] = l[hh]; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (i < nd) dst[2 + d0 + i] = acc[hh][i];
+      }
+    }
+    __syncthreads();
+    // all threads: merge the warps for (head, d) pairs and write
+    for (int idx = threadIdx.x; idx < GT * hd; idx += blockDim.x) {
+      const int hh = idx / hd, d = idx % hd;
+      if (h0 + hh >= G) continue;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * GT + hh) * (hd + 2)]);
+      float lt = 0.f, at = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATTN_WARPS; ++w) {
+        const float* src = merge_s + ((size_t)w * GT + hh) * (hd + 2);
+        const float sc = (mx == -INFINITY) ? 0.f : expf(src[0] - mx);
+        lt += src[1] * sc;
+        at += src[2 + d] * sc;
+      }
+      const int h = g * G + h0 + hh;
+      if (p.nsplit == 1) {
+        p.out[(int64_t)b * p.ldo + (int64_t)h * hd + d] = (lt > 0.f) ? at / lt : 0.f;
+      } else {
+        float* dst = p.partial + (((int64_t)b * p.q_heads + h) * p.nsplit + split) * (hd + 2);
+        if (d == 0) { dst[0] = mx; dst[1] = lt; }
+        dst[2 + d] = at;
+      }
+    }
+  }
+}
+
+__global__ void attn_combine_kernel(const AttnParams p) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int hd = p.head_dim;
+  const float* src = p.partial + ((int64_t)b * p.q_heads + h) * (int64_t)p.nsplit * (hd + 2);
+  float mx = -INFINITY;
+  for (int s = 0; s < p.nsplit; ++s) mx = fmaxf(mx, src[(size_t)s * (hd + 2)]);
+  float lt = 0.f;
+  for (int s = 0; s < p.nsplit; ++s) {
+    const float ms = src[(size_t)s * (hd + 2)];
+    lt += src[(size_t)s * (hd + 2) + 1] * ((ms == -INFINITY) ? 0.f : expf(ms - mx));
+  }
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float at = 0.f;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const float ms = src[(size_t)s * (hd + 2)];
+      at += src[(size_t)s * (hd + 2) + 2 + d] * ((ms == -INFINITY) ? 0.f : expf(ms - mx));
+    }
+    p.out[(int64_t)b * p.ldo + (int64_t)h * hd + d] = (lt > 0.f) ? at / lt : 0.f;
+  }
+}
+
+int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx) {
+  int64_t ctas = (int64_t)batch * kv_heads;
+  int ns = (int)((2 * (int64_t)ctx->sm_count + ctas - 1) / ctas);
+  const int cap = (max_ctx + 127) / 128;
+  if (ns > cap) ns = cap;
+  if (ns > 64) ns = 64;
+  if (ns < 1) ns = 1;
+  return ns;
+}
+size_t attn_partial_floats(int batch, int q_heads, int nsplit, int head_dim) {
+  return (size_t)batch * q_heads * nsplit * (head_dim + 2);
+}
+
+static AttnParams to_params(const AttnArgs& a) {
+  AttnParams p;
+  p.qkv = a.qkv; p.ld = a.ld; p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.cache_len = a.cache_len_dev;
+  p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.head_dim = a.head_dim; p.max_ctx = a.max_ctx;
+  p.theta = a.theta; p.pos = a.pos_dev; p.q_norm = a.q_norm; p.k_norm = a.k_norm; p.eps = a.eps;
+  p.out = a.out; p.ldo = a.ldo; p.partial = a.partial; p.nsplit = a.nsplit;
+  p.inv_sqrt_d = (float)(1.0 / sqrt((double)a.head_dim));
+  return p;
+}
+
+int attn_rope_append(cai_ctx* ctx, const AttnArgs& a) {
+  ctx->cur_family = FAM_ATTN;
+  if (a.head_dim % 2) return cai_fail(ctx, CAI_ERR_INVALID, "head_dim must be even");
+  rope_append_kernel<<<a.batch, 256, 0, ctx->stream>>>(to_params(a));
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
+  ctx->cur_family = FAM_ATTN;
+  if (a.q_heads % a.kv_heads) return cai_fail(ctx, CAI_ERR_INVALID, "q_heads %d not a multiple of kv_heads %d", a.q_heads, a.kv_heads);
+  if (a.head_dim > 256 || a.head_dim < 2) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "head_dim %d outside 2..256", a.head_dim);
+  if (a.nsplit > 1 && !a.partial) return cai_fail(ctx, CAI_ERR_INVALID, "split attention without scratch");
+  const int G = a.q_heads / a.kv_heads;
+  int lpk = 1;
+  while (lpk * 8 < a.head_dim) lpk <<= 1;
+  const AttnParams p = to_params(a);
+  dim3 grid(a.kv_heads, a.nsplit, a.batch);
+  const int gt = G >= 8 ? 8 : G;
+  const size_t smem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * gt * (a.head_dim + 2)) * sizeof(float);
+  if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "attention group of %d heads x %d dims exceeds shared memory", G, a.head_dim);
+  switch (gt) {
+    case 1: attn_decode_kernel<1><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 2: attn_decode_kernel<2><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 3: attn_decode_kernel<3><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 4: attn_decode_kernel<4><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 5: attn_decode_kernel<5><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 6: attn_decode_kernel<6><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 7: attn_decode_kernel<7><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    default: attn_decode_kernel<8><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+  }
+  CAI_LAUNCHED(ctx);
+  if (a.nsplit > 1) {
+    dim3 cgrid(a.q_heads, a.batch);
+    attn_combine_kernel<<<cgrid, 128, 0, ctx->stream>>>(p);
+    CAI_LAUNCHED(ctx);
+  }
+  return CAI_OK;
+}

@@ -1,0 +1,228 @@
+// Internal declarations shared by the translation units of libcai_cuda.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <string.h>
+#include <vector>
+#include <string>
+#include "../../include/cai_cuda.h"
+
+#define CAI_QK 32
+#define CAI_Q8_0_BLOCK_BYTES 34
+#define CAI_Q4_0_BLOCK_BYTES 18
+
+struct cai_comm_state;  // comm.cu
+
+struct cai_ctx {
+  int device;
+  int sm_count;
+  size_t total_mem;
+  cudaStream_t stream;
+  cudaEvent_t ev_begin, ev_end;
+  char err[1024];
+  int64_t launches;          // kernels launched by this library on this context
+  void* l2_flush_buf;        // lazily allocated, > L2 size
+  size_t l2_flush_bytes;
+  void* staging_dev;         // upload staging (device)
+  size_t staging_bytes;
+  void* staging_pinned;      // upload staging (pinned host)
+  cai_comm_state* comm;      // NULL until cai_comm_init
+  // per-launch profiling (cai_session_profile): one event after every launch
+  int prof_on;
+  int cur_family;            // FAM_* of the launches being enqueued
+  cudaEvent_t* prof_events;
+  int* prof_family;
+  int prof_n, prof_cap;
+};
+enum { FAM_LINEAR = 0, FAM_ATTN = 1, FAM_OTHER = 2, FAM_COMM = 3, FAM_COUNT = 4 };
+int cai_prof_mark(cai_ctx* ctx, int family);
+
+int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...);
+
+#define CAI_CUDA(ctx, call)                                                              \
+  do {                                                                                   \
+    cudaError_t e__ = (call);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return cai_fail((ctx), CAI_ERR_CUDA, "%s -> %s (%s:%d)", #call,                    \
+                      cudaGetErrorString(e__), __FILE__, __LINE__);                      \
+  } while (0)
+
+#define CAI_TRY(call)                  \
+  do {                                 \
+    int s__ = (call);                  \
+    if (s__ != CAI_OK) return s__;     \
+  } while (0)
+
+// Checks the launch of the kernel just enqueued and counts it.
+#define CAI_LAUNCHED(ctx)                                                                \
+  do {                                                                                   \
+    cudaError_t e__ = cudaGetLastError();                                                \
+    if (e__ != cudaSuccess)                                                              \
+      return cai_fail((ctx), CAI_ERR_CUDA, "kernel launch -> %s (%s:%d)",                \
+                      cudaGetErrorString(e__), __FILE__, __LINE__);                      \
+    (ctx)->launches++;                                                                   \
+    if ((ctx)->prof_on) cai_prof_mark((ctx), (ctx)->cur_family);                         \
+  } while (0)
+
+static inline int cai_bind(cai_ctx* ctx) {
+  if (!ctx) return CAI_ERR_INVALID;
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "cudaSetDevice(%d) -> %s", ctx->device, cudaGetErrorString(e));
+  return CAI_OK;
+}
+
+int cai_ensure_staging(cai_ctx* ctx, size_t bytes);
+
+// ---------------------------------------------------------------------------
+// Resident weight matrix. GGUF blocks are split into planes when uploaded so
+// that rows of codes start on 16-byte boundaries (a 34-byte Q8_0 block does
+// not): values stay bit-identical, d * q is formed in fp32 exactly as
+// DecodeGGMLSpan does.
+//   Q8_0: codes int8  [N][K],      scales fp16 [N][K/32]
+//   Q4_0: codes uint8 [N][K/2] (the 16 nibble bytes of each block kept together),
+//         scales fp16 [N][K/32]
+//   F16 : codes fp16  [N][K];  F32: codes float [N][K]
+// ---------------------------------------------------------------------------
+struct QWeight {
+  int type = -1;
+  int64_t n = 0, k = 0;
+  void* codes = nullptr;
+  __half* scales = nullptr;
+  float* bias = nullptr;       // optional, N floats
+  bool owns = true;            // false for row-range views (tied LM head shard)
+  bool present = false;
+  size_t code_bytes() const;
+  size_t scale_bytes() const;
+  size_t bytes() const { return code_bytes() + scale_bytes(); }
+  size_t row_code_bytes() const;
+};
+
+size_t cai_type_row_bytes(int type, int64_t k);   // bytes of one GGUF row of k elements
+bool cai_type_supported(int type);
+
+int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k);
+void qweight_free(QWeight* w);
+QWeight qweight_rows_view(const QWeight& w, int64_t row0, int64_t nrows);
+// Uploads host GGUF rows [row0,row0+nrows) x cols [col0,col0+ncols) of a [src_rows, src_cols]
+// tensor into w (already allocated as nrows x ncols), optionally gathering source rows through
+// the q/k interleave permutation.
+int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows, int64_t src_cols,
+                   int64_t row0, int64_t col0, int interleave_head_dim);
+int qweight_download_blocks(cai_ctx* ctx, const QWeight* w, void* out_host, size_t cap);
+int qweight_dequantize_to_dev(cai_ctx* ctx, const QWeight* w, float* out_dev);
+int qweight_init_synthetic(cai_ctx* ctx, QWeight* w, uint64_t seed, uint64_t tensor_id, float std,
+                           int64_t global_row0, int64_t global_col0, int64_t global_cols);
+int vec_init_synthetic(cai_ctx* ctx, float* v, int64_t n, uint64_t seed, uint64_t tensor_id, float std,
+                       int64_t global0, float constant /* used when std == 0 */);
+
+// ---------------------------------------------------------------------------
+// GEMV / GEMM launchers (gemv.cu, gemm_tc.cu)
+// ---------------------------------------------------------------------------
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+
+struct LinearArgs {
+  const QWeight* w = nullptr;
+  const float* x = nullptr;      // [B][K] (ldx floats between rows)
+  int64_t ldx = 0;
+  float* y = nullptr;            // [B][ldy]
+  int64_t ldy = 0;
+  int batch = 1;
+  int epilogue = EPI_STORE;
+  const float* resid = nullptr;  // EPI_RESID: y = resid + W x (+bias); ld = ldy
+  int act = CAI_ACT_NONE;
+  // Indexed (MoE) mode: per pair p, the weight matrix is banks[expert_ids[p]] and the
+  // activation row is x + x_row[p]*ldx (x_row NULL -> p).
+  const QWeight* const* bank = nullptr;  // unused (device arrays below are what kernels read)
+  const void* const* bank_codes_dev = nullptr;
+  const __half* const* bank_scales_dev = nullptr;
+  const int32_t* expert_ids_dev = nullptr;
+  int x_row_div = 1;             // activation row of pair p = p / x_row_div
+  const float* row_scale_dev = nullptr;  // optional per-pair output scale (router gate)
+};
+
+int linear_launch(cai_ctx* ctx, const LinearArgs& a);
+
+// ops.cu
+int op_embed(cai_ctx* ctx, const QWeight* table, const int32_t* tokens_dev, int batch, float* out, int64_t ld);
+int op_rmsnorm(cai_ctx* ctx, const float* x, int64_t ldx, const float* gain, float* y, int64_t ldy, int tokens, int depth, float eps);
+int op_rope(cai_ctx* ctx, float* x, int64_t ldx, int tokens, int depth, int head_dim, const float* theta_dev,
+            const int32_t* pos_dev, int pos_stride, int pos_offset);
+int op_swiglu(cai_ctx* ctx, const float* x, int64_t ldx, float* y, int64_t ldy, int tokens, int half);
+int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, int top_k, int renorm,
+                 int32_t* ids, float* gates);
+int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val);
+int op_moe_combine(cai_ctx* ctx, float* x, int64_t ldx, const float* pair_out, int64_t ldp, const float* gates,
+                   int tokens, int top_k, int depth);
+int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n);
+int op_rope_theta_table(cai_ctx* ctx, float* theta_dev, int head_dim, float base);
+
+// attention.cu
+struct AttnArgs {
+  float* qkv = nullptr;         // [B][ld]: [allQ | allK | allV] rows; Q and K are normed/rotated in place
+  int64_t ld = 0;
+  float* k_cache = nullptr;     // [B][kv_heads][max_ctx][hd], head-major per sequence
+  float* v_cache = nullptr;
+  const int32_t* cache_len_dev = nullptr;  // [B] length BEFORE this step (slot to append at)
+  int batch = 1, q_heads = 0, kv_heads = 0, head_dim = 0, max_ctx = 0;
+  const float* theta = nullptr;            // [hd/2] RoPE frequencies; NULL = rows are already rotated
+  const int32_t* pos_dev = nullptr;        // [B] absolute positions (NULL = cache length)
+  const float* q_norm = nullptr;           // optional full-width RMSNorm gains applied before RoPE
+  const float* k_norm = nullptr;
+  float eps = 0.f;
+  float* out = nullptr;         // [B][ldo]
+  int64_t ldo = 0;
+  float* partial = nullptr;     // scratch: [B][q_heads][nsplit][hd + 2]
+  int nsplit = 1;
+};
+int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx);
+size_t attn_partial_floats(int batch, int q_heads, int nsplit, int head_dim);
+int attn_rope_append(cai_ctx* ctx, const AttnArgs& a);
+int attn_decode(cai_ctx* ctx, const AttnArgs& a);
+
+// comm.cu
+int comm_allreduce(cai_ctx* ctx, float* buf, int64_t count);
+int comm_allgather(cai_ctx* ctx, const float* send, float* recv, int64_t count_per_rank);
+int comm_world(cai_ctx* ctx);
+void comm_destroy(cai_ctx* ctx);
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum; every thread gets the result. `red` needs 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+// int8 code in byte `i` of a word whose bytes were XOR-ed with 0x80 -> float, exactly.
+// (0x4B000000 | u) is the float 8388608 + u; subtracting 8388736 leaves u - 128.
+__device__ __forceinline__ float biased_byte_to_float(uint32_t w, int i) {
+  uint32_t bits = __byte_perm(w, 0x4B000000u, 0x7650u + (uint32_t)i);
+  return __uint_as_float(bits) - 8388736.0f;
+}
+// unsigned byte `i` of w minus `bias` -> float, exactly.
+__device__ __forceinline__ float ubyte_to_float(uint32_t w, int i, float magic_plus_bias) {
+  uint32_t bits = __byte_perm(w, 0x4B000000u, 0x7650u + (uint32_t)i);
+  return __uint_as_float(bits) - magic_plus_bias;
+}
+#endif

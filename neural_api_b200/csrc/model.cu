@@ -1,0 +1,1000 @@
+// Whole-model fast path: the Llama-family graph resident on the GPU and the
+// decode session that steps it one token per sequence over a KV cache.
+//
+// Weight conventions follow the reference importer: nn.Linear rows = output
+// channels, q/k rows interleaved per head for the pairwise RoPE, fused gate|up
+// matrix with the up rows first and the gate rows second, experts laid out the
+// same way per expert.
+#include "cai_common.cuh"
+#include <new>
+#include <math.h>
+#include <stdlib.h>
+
+enum TKind {
+  T_EMBED, T_LM_HEAD, T_FINAL_NORM, T_ATTN_NORM, T_FFN_NORM, T_Q, T_K, T_V, T_QB, T_KB, T_VB, T_O,
+  T_GATE, T_UP, T_DOWN, T_QNORM, T_KNORM, T_ROUTER, T_EXP_GATE, T_EXP_UP, T_EXP_DOWN, T_IGNORE, T_UNKNOWN
+};
+struct TName { TKind kind; int layer; int expert; };
+
+static TName parse_name(const char* name) {
+  TName t{T_UNKNOWN, -1, -1};
+  if (!strcmp(name, "model.embed_tokens.weight")) { t.kind = T_EMBED; return t; }
+  if (!strcmp(name, "lm_head.weight")) { t.kind = T_LM_HEAD; return t; }
+  if (!strcmp(name, "model.norm.weight")) { t.kind = T_FINAL_NORM; return t; }
+  int layer = -1, consumed = 0;
+  if (sscanf(name, "model.layers.%d.%n", &layer, &consumed) < 1 || consumed == 0) return t;
+  t.layer = layer;
+  const char* rest = name + consumed;
+  struct { const char* s; TKind k; } simple[] = {
+      {"input_layernorm.weight", T_ATTN_NORM}, {"post_attention_layernorm.weight", T_FFN_NORM},
+      {"self_attn.q_proj.weight", T_Q}, {"self_attn.k_proj.weight", T_K}, {"self_attn.v_proj.weight", T_V},
+      {"self_attn.q_proj.bias", T_QB}, {"self_attn.k_proj.bias", T_KB}, {"self_attn.v_proj.bias", T_VB},
+      {"self_attn.o_proj.weight", T_O}, {"mlp.gate_proj.weight", T_GATE}, {"mlp.up_proj.weight", T_UP},
+      {"mlp.down_proj.weight", T_DOWN}, {"self_attn.q_norm.weight", T_QNORM}, {"self_attn.k_norm.weight", T_KNORM},
+      {"mlp.gate.weight", T_ROUTER}, {"block_sparse_moe.gate.weight", T_ROUTER},
+      {"self_attn.rotary_emb.inv_freq", T_IGNORE}};
+  for (auto& e : simple) if (!strcmp(rest, e.s)) { t.kind = e.k; return t; }
+  int ex = -1; consumed = 0;
+  const char* er = nullptr;
+  if (sscanf(rest, "mlp.experts.%d.%n", &ex, &consumed) >= 1 && consumed) er = rest + consumed;
+  else { consumed = 0; if (sscanf(rest, "block_sparse_moe.experts.%d.%n", &ex, &consumed) >= 1 && consumed) er = rest + consumed; }
+  if (er) {
+    t.expert = ex;
+    if (!strcmp(er, "gate_proj.weight") || !strcmp(er, "w1.weight")) t.kind = T_EXP_GATE;
+    else if (!strcmp(er, "up_proj.weight") || !strcmp(er, "w3.weight")) t.kind = T_EXP_UP;
+    else if (!strcmp(er, "down_proj.weight") || !strcmp(er, "w2.weight")) t.kind = T_EXP_DOWN;
+  }
+  return t;
+}
+
+enum {
+  HAVE_ATTN_NORM = 1, HAVE_FFN_NORM = 2, HAVE_Q = 4, HAVE_K = 8, HAVE_V = 16, HAVE_QB = 32, HAVE_KB = 64, HAVE_VB = 128,
+  HAVE_O = 256, HAVE_GATE = 512, HAVE_UP = 1024, HAVE_DOWN = 2048, HAVE_QNORM = 4096, HAVE_KNORM = 8192, HAVE_ROUTER = 16384
+};
+
+struct LayerW {
+  float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+  QWeight wqkv, wo, wgu, wdown, router;
+  std::vector<QWeight> exp_gu, exp_down;
+  std::vector<uint8_t> exp_have;              // bit 1 gate, 2 up, 4 down
+  const void** d_gu_codes = nullptr; const __half** d_gu_scales = nullptr;
+  const void** d_down_codes = nullptr; const __half** d_down_scales = nullptr;
+  uint32_t have = 0;
+};
+
+struct cai_model {
+  cai_ctx* ctx;
+  cai_llama_config cfg;
+  int tp_rank, tp_size;
+  // local (this rank's) dimensions
+  int heads_l, kv_heads_l, qw_l, kw_l, inter_l, vocab_l;
+  QWeight embed, lm_head;
+  bool have_embed = false, have_head = false;
+  float* final_norm = nullptr;
+  float* theta = nullptr;
+  std::vector<LayerW> layers;
+  bool finalized = false;
+  int sessions = 0;
+};
+
+static int ensure_weight(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
+  if (w->codes) {
+    if (w->type != type || w->n != n || w->k != k)
+      return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "tensors fused into one matrix must share one storage type (have %d, got %d)", w->type, type);
+    return CAI_OK;
+  }
+  return qweight_alloc(ctx, w, type, n, k);
+}
+static int ensure_vec(cai_ctx* ctx, float** p, int64_t n, bool zero) {
+  if (*p) return CAI_OK;
+  CAI_CUDA(ctx, cudaMalloc((void**)p, (size_t)n * 4));
+  if (zero) CAI_CUDA(ctx, cudaMemsetAsync(*p, 0, (size_t)n * 4, ctx->stream));
+  return CAI_OK;
+}
+// host vector slice [g0, g0+n) of a length-`total` fp32 vector, optional per-head interleave, to device
+static int upload_vec(cai_ctx* ctx, float* dst, const float* host, int64_t total, int64_t g0, int64_t n, int interleave_hd) {
+  std::vector<float> tmp((size_t)n);
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t g = g0 + i;
+    if (interleave_hd > 0) {
+      const int64_t h = g / interleave_hd, r = g % interleave_hd;
+      g = h * interleave_hd + ((r % 2 == 0) ? r / 2 : r / 2 + interleave_hd / 2);
+    }
+    if (g >= total) return cai_fail(ctx, CAI_ERR_INVALID, "vector index out of range");
+    tmp[(size_t)i] = host[g];
+  }
+  CAI_CUDA(ctx, cudaMemcpyAsync(dst, tmp.data(), (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+static void layer_free(LayerW& L) {
+  if (L.attn_norm) cudaFree(L.attn_norm);
+  if (L.ffn_norm) cudaFree(L.ffn_norm);
+  if (L.q_norm) cudaFree(L.q_norm);
+  if (L.k_norm) cudaFree(L.k_norm);
+  qweight_free(&L.wqkv); qweight_free(&L.wo); qweight_free(&L.wgu); qweight_free(&L.wdown); qweight_free(&L.router);
+  for (auto& w : L.exp_gu) qweight_free(&w);
+  for (auto& w : L.exp_down) qweight_free(&w);
+  if (L.d_gu_codes) cudaFree((void*)L.d_gu_codes);
+  if (L.d_gu_scales) cudaFree((void*)L.d_gu_scales);
+  if (L.d_down_codes) cudaFree((void*)L.d_down_codes);
+  if (L.d_down_scales) cudaFree((void*)L.d_down_scales);
+}
+
+extern "C" {
+
+int cai_model_create(cai_ctx* ctx, const cai_llama_config* cfg, int tp_rank, int tp_size, cai_model** out) {
+  CAI_TRY(cai_bind(ctx));
+  if (!cfg || !out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_create: null argument");
+  *out = nullptr;
+  const cai_llama_config& c = *cfg;
+  if (c.hidden < 1 || c.layers < 1 || c.heads < 1 || c.kv_heads < 1 || c.head_dim < 2 || (c.head_dim % 2) || c.vocab < 1 ||
+      (c.heads % c.kv_heads) || (c.n_experts == 0 && c.inter < 1) || c.head_dim > 256)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_create: inconsistent configuration");
+  if (c.n_experts > 0 && (c.top_k < 1 || c.top_k > c.n_experts || c.moe_inter < 1))
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_create: inconsistent MoE configuration");
+  if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return cai_fail(ctx, CAI_ERR_INVALID, "tp rank %d of %d", tp_rank, tp_size);
+  if (tp_size > 1) {
+    if (c.n_experts > 0 || c.qk_norm) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "tensor parallelism covers dense models without full-width q/k norm");
+    if ((c.heads % tp_size) || (c.kv_heads % tp_size) || (c.inter % tp_size) || (c.vocab % tp_size) || ((c.inter / tp_size) % 32) ||
+        ((c.heads / tp_size * c.head_dim) % 32))
+      return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "heads/kv_heads/inter/vocab must divide by tp_size with 32-aligned shards");
+    if (comm_world(ctx) != tp_size) return cai_fail(ctx, CAI_ERR_STATE, "call cai_comm_init with world == tp_size first");
+  }
+  cai_model* m = new (std::nothrow) cai_model();
+  if (!m) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
+  m->ctx = ctx; m->cfg = c; m->tp_rank = tp_rank; m->tp_size = tp_size;
+  m->heads_l = c.heads / tp_size; m->kv_heads_l = c.kv_heads / tp_size;
+  m->qw_l = m->heads_l * c.head_dim; m->kw_l = m->kv_heads_l * c.head_dim;
+  m->inter_l = c.n_experts ? 0 : c.inter / tp_size;
+  m->vocab_l = c.vocab / tp_size;
+  m->layers.resize((size_t)c.layers);
+  if (c.n_experts)
+    for (auto& L : m->layers) { L.exp_gu.resize((size_t)c.n_experts); L.exp_down.resize((size_t)c.n_experts); L.exp_have.assign((size_t)c.n_experts, 0); }
+  *out = m;
+  return CAI_OK;
+}
+
+int cai_model_destroy(cai_model* m) {
+  if (!m) return CAI_ERR_INVALID;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  for (auto& L : m->layers) layer_free(L);
+  qweight_free(&m->embed);
+  qweight_free(&m->lm_head);
+  if (m->final_norm) cudaFree(m->final_norm);
+  if (m->theta) cudaFree(m->theta);
+  delete m;
+  return CAI_OK;
+}
+
+int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const void* data_host, int64_t rows, int64_t cols,
+                            int interleave_head_dim) {
+  if (!m) return CAI_ERR_INVALID;
+  cai_ctx* ctx = m->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!hf_name || !data_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_upload_tensor: null argument");
+  if (m->sessions > 0) return cai_fail(ctx, CAI_ERR_STATE, "weights are immutable while sessions exist");
+  const cai_llama_config& c = m->cfg;
+  const TName t = parse_name(hf_name);
+  if (t.kind == T_IGNORE) return CAI_OK;
+  if (t.kind == T_UNKNOWN) return cai_fail(ctx, CAI_ERR_INVALID, "unknown tensor name '%s'", hf_name);
+  if (t.layer >= c.layers) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': layer %d of %d", hf_name, t.layer, c.layers);
+  const int H = c.hidden, QW = c.heads * c.head_dim, KW = c.kv_heads * c.head_dim;
+  const int r = m->tp_rank;
+  auto shape_is = [&](int64_t er, int64_t ec) -> bool { return rows == er && cols == ec; };
+  auto vec_len = [&]() -> int64_t { return rows * cols; };
+#define NEED_SHAPE(er, ec)                                                                                      \
+  if (!shape_is((er), (ec)))                                                                                    \
+    return cai_fail(ctx, CAI_ERR_INVALID, "'%s': shape %lld x %lld, expected %lld x %lld", hf_name,              \
+                    (long long)rows, (long long)cols, (long long)(er), (long long)(ec))
+#define NEED_VEC(n)                                                                                             \
+  if (type != CAI_TYPE_F32 || vec_len() != (n))                                                                 \
+    return cai_fail(ctx, CAI_ERR_INVALID, "'%s': expected an F32 vector of %lld", hf_name, (long long)(n))
+  m->finalized = false;
+  switch (t.kind) {
+    case T_EMBED: {
+      NEED_SHAPE(c.vocab, H);
+      CAI_TRY(ensure_weight(ctx, &m->embed, type, c.vocab, H));
+      CAI_TRY(qweight_upload(ctx, &m->embed, data_host, rows, cols, 0, 0, 0));
+      m->have_embed = true;
+      return CAI_OK;
+    }
+    case T_LM_HEAD: {
+      NEED_SHAPE(c.vocab, H);
+      CAI_TRY(ensure_weight(ctx, &m->lm_head, type, m->vocab_l, H));
+      CAI_TRY(qweight_upload(ctx, &m->lm_head, data_host, rows, cols, (int64_t)r * m->vocab_l, 0, 0));
+      m->have_head = true;
+      return CAI_OK;
+    }
+    case T_FINAL_NORM: {
+      NEED_VEC(H);
+      CAI_TRY(ensure_vec(ctx, &m->final_norm, H, false));
+      return upload_vec(ctx, m->final_norm, (const float*)data_host, H, 0, H, 0);
+    }
+    default: break;
+  }
+  LayerW& L = m->layers[(size_t)t.layer];
+  const int qkv_rows = m->qw_l + 2 * m->kw_l;
+  switch (t.kind) {
+    case T_ATTN_NORM: NEED_VEC(H); CAI_TRY(ensure_vec(ctx, &L.attn_norm, H, false)); L.have |= HAVE_ATTN_NORM;
+      return upload_vec(ctx, L.attn_norm, (const float*)data_host, H, 0, H, 0);
+    case T_FFN_NORM: NEED_VEC(H); CAI_TRY(ensure_vec(ctx, &L.ffn_norm, H, false)); L.have |= HAVE_FFN_NORM;
+      return upload_vec(ctx, L.ffn_norm, (const float*)data_host, H, 0, H, 0);
+    case T_QNORM: NEED_VEC(QW); CAI_TRY(ensure_vec(ctx, &L.q_norm, QW, false)); L.have |= HAVE_QNORM;
+      return upload_vec(ctx, L.q_norm, (const float*)data_host, QW, 0, QW, interleave_head_dim);
+    case T_KNORM: NEED_VEC(KW); CAI_TRY(ensure_vec(ctx, &L.k_norm, KW, false)); L.have |= HAVE_KNORM;
+      return upload_vec(ctx, L.k_norm, (const float*)data_host, KW, 0, KW, interleave_head_dim);
+    case T_Q: case T_K: case T_V: {
+      const bool isq = t.kind == T_Q;
+      NEED_SHAPE(isq ? QW : KW, H);
+      CAI_TRY(ensure_weight(ctx, &L.wqkv, type, qkv_rows, H));
+      const int64_t nloc = isq ? m->qw_l : m->kw_l;
+      const int64_t dst0 = isq ? 0 : (t.kind == T_K ? m->qw_l : m->qw_l + m->kw_l);
+      QWeight view = qweight_rows_view(L.wqkv, dst0, nloc);
+      CAI_TRY(qweight_upload(ctx, &view, data_host, rows, cols, (int64_t)r * nloc, 0, t.kind == T_V ? 0 : interleave_head_dim));
+      L.have |= isq ? HAVE_Q : (t.kind == T_K ? HAVE_K : HAVE_V);
+      return CAI_OK;
+    }
+    case T_QB: case T_KB: case T_VB: {
+      const bool isq = t.kind == T_QB;
+      NEED_VEC(isq ? QW : KW);
+      if (!L.wqkv.codes) return cai_fail(ctx, CAI_ERR_STATE, "'%s': upload the projection weight before its bias", hf_name);
+      CAI_TRY(ensure_vec(ctx, &L.wqkv.bias, qkv_rows, true));
+      const int64_t nloc = isq ? m->qw_l : m->kw_l;
+      const int64_t dst0 = isq ? 0 : (t.kind == T_KB ? m->qw_l : m->qw_l + m->kw_l);
+      L.have |= isq ? HAVE_QB : (t.kind == T_KB ? HAVE_KB : HAVE_VB);
+      return upload_vec(ctx, L.wqkv.bias + dst0, (const float*)data_host, isq ? QW : KW, (int64_t)r * nloc, nloc,
+                        t.kind == T_VB ? 0 : interleave_head_dim);
+    }
+    case T_O: {
+      NEED_SHAPE(H, QW);
+      CAI_TRY(ensure_weight(ctx, &L.wo, type, H, m->qw_l));
+      CAI_TRY(qweight_upload(ctx, &L.wo, data_host, rows, cols, 0, (int64_t)r * m->qw_l, 0));
+      L.have |= HAVE_O;
+      return CAI_OK;
+    }
+    case T_GATE: case T_UP: {
+      if (c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': dense MLP tensor in an MoE configuration", hf_name);
+      NEED_SHAPE(c.inter, H);
+      CAI_TRY(ensure_weight(ctx, &L.wgu, type, 2 * (int64_t)m->inter_l, H));
+      // up rows first, gate rows second
+      QWeight view = qweight_rows_view(L.wgu, t.kind == T_UP ? 0 : m->inter_l, m->inter_l);
+      CAI_TRY(qweight_upload(ctx, &view, data_host, rows, cols, (int64_t)r * m->inter_l, 0, 0));
+      L.have |= (t.kind == T_UP) ? HAVE_UP : HAVE_GATE;
+      return CAI_OK;
+    }
+    case T_DOWN: {
+      if (c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': dense MLP tensor in an MoE configuration", hf_name);
+      NEED_SHAPE(H, c.inter);
+      CAI_TRY(ensure_weight(ctx, &L.wdown, type, H, m->inter_l));
+      CAI_TRY(qweight_upload(ctx, &L.wdown, data_host, rows, cols, 0, (int64_t)r * m->inter_l, 0));
+      L.have |= HAVE_DOWN;
+      return CAI_OK;
+    }
+    case T_ROUTER: {
+      if (!c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': router in a dense configuration", hf_name);
+      NEED_SHAPE(c.n_experts, H);
+      CAI_TRY(ensure_weight(ctx, &L.router, type, c.n_experts, H));
+      CAI_TRY(qweight_upload(ctx, &L.router, data_host, rows, cols, 0, 0, 0));
+      L.have |= HAVE_ROUTER;
+      return CAI_OK;
+    }
+    case T_EXP_GATE: case T_EXP_UP: case T_EXP_DOWN: {
+      if (!c.n_experts || t.expert < 0 || t.expert >= c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': expert index", hf_name);
+      const int Im = c.moe_inter;
+      if (t.kind == T_EXP_DOWN) {
+        NEED_SHAPE(H, Im);
+        QWeight* w = &L.exp_down[(size_t)t.expert];
+        CAI_TRY(ensure_weight(ctx, w, type, H, Im));
+        CAI_TRY(qweight_upload(ctx, w, data_host, rows, cols, 0, 0, 0));
+        L.exp_have[(size_t)t.expert] |= 4;
+      } else {
+        NEED_SHAPE(Im, H);
+        QWeight* w = &L.exp_gu[(size_t)t.expert];
+        CAI_TRY(ensure_weight(ctx, w, type, 2 * (int64_t)Im, H));
+        QWeight view = qweight_rows_view(*w, t.kind == T_EXP_UP ? 0 : Im, Im);
+        CAI_TRY(qweight_upload(ctx, &view, data_host, rows, cols, 0, 0, 0));
+        w->present = true;
+        L.exp_have[(size_t)t.expert] |= (t.kind == T_EXP_UP) ? 2 : 1;
+      }
+      return CAI_OK;
+    }
+    default: break;
+  }
+#undef NEED_SHAPE
+#undef NEED_VEC
+  return cai_fail(ctx, CAI_ERR_INVALID, "'%s': unhandled tensor", hf_name);
+}
+
+int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std) {
+  if (!m) return CAI_ERR_INVALID;
+  cai_ctx* ctx = m->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (m->sessions > 0) return cai_fail(ctx, CAI_ERR_STATE, "weights are immutable while sessions exist");
+  const cai_llama_config& c = m->cfg;
+  const int H = c.hidden, QW = c.heads * c.head_dim, KW = c.kv_heads * c.head_dim, r = m->tp_rank;
+  if ((H % 32) || (QW % 32) || (c.n_experts ? (c.moe_inter % 32) : (c.inter % 32)))
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "synthetic init needs 32-aligned widths");
+  m->finalized = false;
+  CAI_TRY(ensure_weight(ctx, &m->embed, type, c.vocab, H));
+  CAI_TRY(qweight_init_synthetic(ctx, &m->embed, seed, 9000, std, 0, 0, H));
+  m->have_embed = true;
+  if (!c.tie_embeddings) {
+    CAI_TRY(ensure_weight(ctx, &m->lm_head, type, m->vocab_l, H));
+    CAI_TRY(qweight_init_synthetic(ctx, &m->lm_head, seed, 9001, std, (int64_t)r * m->vocab_l, 0, H));
+    m->have_head = true;
+  }
+  CAI_TRY(ensure_vec(ctx, &m->final_norm, H, false));
+  CAI_TRY(vec_init_synthetic(ctx, m->final_norm, H, seed, 0, 0.f, 0, 1.0f));
+  for (int l = 0; l < c.layers; ++l) {
+    LayerW& L = m->layers[(size_t)l];
+    const uint64_t tid = 100 + (uint64_t)l * 32;
+    CAI_TRY(ensure_vec(ctx, &L.attn_norm, H, false));
+    CAI_TRY(vec_init_synthetic(ctx, L.attn_norm, H, seed, 0, 0.f, 0, 1.0f));
+    CAI_TRY(ensure_vec(ctx, &L.ffn_norm, H, false));
+    CAI_TRY(vec_init_synthetic(ctx, L.ffn_norm, H, seed, 0, 0.f, 0, 1.0f));
+    L.have |= HAVE_ATTN_NORM | HAVE_FFN_NORM;
+    CAI_TRY(ensure_weight(ctx, &L.wqkv, type, m->qw_l + 2 * m->kw_l, H));
+    {
+      QWeight vq = qweight_rows_view(L.wqkv, 0, m->qw_l);
+      QWeight vk = qweight_rows_view(L.wqkv, m->qw_l, m->kw_l);
+      QWeight vv = qweight_rows_view(L.wqkv, m->qw_l + m->kw_l, m->kw_l);
+      CAI_TRY(qweight_init_synthetic(ctx, &vq, seed, tid + 0, std, (int64_t)r * m->qw_l, 0, H));
+      CAI_TRY(qweight_init_synthetic(ctx, &vk, seed, tid + 1, std, (int64_t)r * m->kw_l, 0, H));
+      CAI_TRY(qweight_init_synthetic(ctx, &vv, seed, tid + 2, std, (int64_t)r * m->kw_l, 0, H));
+      L.wqkv.present = true;
+      L.have |= HAVE_Q | HAVE_K | HAVE_V;
+    }
+    if (c.qkv_bias) {
+      CAI_TRY(ensure_vec(ctx, &L.wqkv.bias, m->qw_l + 2 * m->kw_l, true));
+      CAI_TRY(vec_init_synthetic(ctx, L.wqkv.bias, m->qw_l, seed, tid + 3, std, (int64_t)r * m->qw_l, 0.f));
+      CAI_TRY(vec_init_synthetic(ctx, L.wqkv.bias + m->qw_l, m->kw_l, seed, tid + 4, std, (int64_t)r * m->kw_l, 0.f));
+      CAI_TRY(vec_init_synthetic(ctx, L.wqkv.bias + m->qw_l + m->kw_l, m->kw_l, seed, tid + 5, std, (int64_t)r * m->kw_l, 0.f));
+      L.have |= HAVE_QB | HAVE_KB | HAVE_VB;
+    }
+    if (c.qk_norm) {
+      CAI_TRY(ensure_vec(ctx, &L.q_norm, QW, false));
+      CAI_TRY(vec_init_synthetic(ctx, L.q_norm, QW, seed, 0, 0.f, 0, 1.0f));
+      CAI_TRY(ensure_vec(ctx, &L.k_norm, KW, false));
+      CAI_TRY(vec_init_synthetic(ctx, L.k_norm, KW, seed, 0, 0.f, 0, 1.0f));
+      L.have |= HAVE_QNORM | HAVE_KNORM;
+    }
+    CAI_TRY(ensure_weight(ctx, &L.wo, type, H, m->qw_l));
+    CAI_TRY(qweight_init_synthetic(ctx, &L.wo, seed, tid + 6, std, 0, (int64_t)r * m->qw_l, QW));
+    L.have |= HAVE_O;
+    if (!c.n_experts) {
+      CAI_TRY(ensure_weight(ctx, &L.wgu, type, 2 * (int64_t)m->inter_l, H));
+      QWeight vu = qweight_rows_view(L.wgu, 0, m->inter_l);
+      QWeight vg = qweight_rows_view(L.wgu, m->inter_l, m->inter_l);
+      CAI_TRY(qweight_init_synthetic(ctx, &vu, seed, tid + 7, std, (int64_t)r * m->inter_l, 0, H));
+      CAI_TRY(qweight_init_synthetic(ctx, &vg, seed, tid + 8, std, (int64_t)r * m->inter_l, 0, H));
+      L.wgu.present = true;
+      CAI_TRY(ensure_weight(ctx, &L.wdown, type, H, m->inter_l));
+      CAI_TRY(qweight_init_synthetic(ctx, &L.wdown, seed, tid + 9, std, 0, (int64_t)r * m->inter_l, c.inter));
+      L.have |= HAVE_GATE | HAVE_UP | HAVE_DOWN;
+    } else {
+      const int Im = c.moe_inter;
+      CAI_TRY(ensure_weight(ctx, &L.router, type, c.n_experts, H));
+      CAI_TRY(qweight_init_synthetic(ctx, &L.router, seed, tid + 10, std, 0, 0, H));
+      L.have |= HAVE_ROUTER;
+      for (int e = 0; e < c.n_experts; ++e) {
+        const uint64_t etid = 100000 + ((uint64_t)l * (uint64_t)c.n_experts + (uint64_t)e) * 4;
+        QWeight* gu = &L.exp_gu[(size_t)e];
+        CAI_TRY(ensure_weight(ctx, gu, type, 2 * (int64_t)Im, H));
+        QWeight vu = qweight_rows_view(*gu, 0, Im);
+        QWeight vg = qweight_rows_view(*gu, Im, Im);
+        CAI_TRY(qweight_init_synthetic(ctx, &vu, seed, etid + 0, std, 0, 0, H));
+        CAI_TRY(qweight_init_synthetic(ctx, &vg, seed, etid + 1, std, 0, 0, H));
+        gu->present = true;
+        QWeight* dn = &L.exp_down[(size_t)e];
+        CAI_TRY(ensure_weight(ctx, dn, type, H, Im));
+        CAI_TRY(qweight_init_synthetic(ctx, dn, seed, etid + 2, std, 0, 0, Im));
+        L.exp_have[(size_t)e] = 7;
+      }
+    }
+  }
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+// Resolves a tensor name to the resident storage (view) it was placed in.
+static int locate_tensor(cai_model* m, const char* hf_name, QWeight* out_view, const float** out_vec, int64_t* out_vec_len) {
+  cai_ctx* ctx = m->ctx;
+  const TName t = parse_name(hf_name);
+  *out_vec = nullptr; *out_vec_len = 0;
+  if (t.kind == T_UNKNOWN || t.kind == T_IGNORE || t.layer >= m->cfg.layers) return cai_fail(ctx, CAI_ERR_INVALID, "unknown tensor name '%s'", hf_name);
+  const cai_llama_config& c = m->cfg;
+  if (t.kind == T_EMBED) { *out_view = qweight_rows_view(m->embed, 0, m->embed.n); return CAI_OK; }
+  if (t.kind == T_LM_HEAD) { *out_view = qweight_rows_view(m->lm_head, 0, m->lm_head.n); return CAI_OK; }
+  if (t.kind == T_FINAL_NORM) { *out_vec = m->final_norm; *out_vec_len = c.hidden; return CAI_OK; }
+  LayerW& L = m->layers[(size_t)t.layer];
+  switch (t.kind) {
+    case T_ATTN_NORM: *out_vec = L.attn_norm; *out_vec_len = c.hidden; return CAI_OK;
+    case T_FFN_NORM: *out_vec = L.ffn_norm; *out_vec_len = c.hidden; return CAI_OK;
+    case T_QNORM: *out_vec = L.q_norm; *out_vec_len = c.heads * c.head_dim; return CAI_OK;
+    case T_KNORM: *out_vec = L.k_norm; *out_vec_len = c.kv_heads * c.head_dim; return CAI_OK;
+    case T_Q: *out_view = qweight_rows_view(L.wqkv, 0, m->qw_l); return CAI_OK;
+    case T_K: *out_view = qweight_rows_view(L.wqkv, m->qw_l, m->kw_l); return CAI_OK;
+    case T_V: *out_view = qweight_rows_view(L.wqkv, m->qw_l + m->kw_l, m->kw_l); return CAI_OK;
+    case T_QB: *out_vec = L.wqkv.bias; *out_vec_len = m->qw_l; return CAI_OK;
+    case T_KB: *out_vec = L.wqkv.bias ? L.wqkv.bias + m->qw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
+    case T_VB: *out_vec = L.wqkv.bias ? L.wqkv.bias + m->qw_l + m->kw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
+    case T_O: *out_view = qweight_rows_view(L.wo, 0, L.wo.n); return CAI_OK;
+    case T_UP: *out_view = qweight_rows_view(L.wgu, 0, m->inter_l); return CAI_OK;
+    case T_GATE: *out_view = qweight_rows_view(L.wgu, m->inter_l, m->inter_l); return CAI_OK;
+    case T_DOWN: *out_view = qweight_rows_view(L.wdown, 0, L.wdown.n); return CAI_OK;
+    case T_ROUTER: *out_view = qweight_rows_view(L.router, 0, L.router.n); return CAI_OK;
+    case T_EXP_UP: case T_EXP_GATE: case T_EXP_DOWN: {
+      if (t.expert < 0 || t.expert >= c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': expert index", hf_name);
+      if (t.kind == T_EXP_DOWN) *out_view = qweight_rows_view(L.exp_down[(size_t)t.expert], 0, c.hidden);
+      else *out_view = qweight_rows_view(L.exp_gu[(size_t)t.expert], t.kind == T_EXP_UP ? 0 : c.moe_inter, c.moe_inter);
+      return CAI_OK;
+    }
+    default: break;
+  }
+  return cai_fail(ctx, CAI_ERR_INVALID, "'%s': unhandled tensor", hf_name);
+}
+
+int cai_model_read_tensor(cai_model* m, const char* hf_name, void* out_host, int64_t out_bytes_cap, int* out_type,
+                          int64_t* out_rows, int64_t* out_cols) {
+  if (!m) return CAI_ERR_INVALID;
+  cai_ctx* ctx = m->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!hf_name || !out_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_read_tensor: null argument");
+  QWeight view; const float* vec = nullptr; int64_t vlen = 0;
+  CAI_TRY(locate_tensor(m, hf_name, &view, &vec, &vlen));
+  if (vlen > 0) {
+    if (!vec) return cai_fail(ctx, CAI_ERR_STATE, "'%s' has not been uploaded", hf_name);
+    if (vlen * 4 > out_bytes_cap) return cai_fail(ctx, CAI_ERR_INVALID, "host buffer too small");
+    CAI_CUDA(ctx, cudaMemcpyAsync(out_host, vec, (size_t)vlen * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (out_type) *out_type = CAI_TYPE_F32;
+    if (out_rows) *out_rows = 1;
+    if (out_cols) *out_cols = vlen;
+    return CAI_OK;
+  }
+  if (!view.codes) return cai_fail(ctx, CAI_ERR_STATE, "'%s' has not been uploaded", hf_name);
+  CAI_TRY(qweight_download_blocks(ctx, &view, out_host, (size_t)out_bytes_cap));
+  if (out_type) *out_type = view.type;
+  if (out_rows) *out_rows = view.n;
+  if (out_cols) *out_cols = view.k;
+  return CAI_OK;
+}
+
+static int upload_ptr_array(cai_ctx* ctx, const void*** dst, const std::vector<const void*>& src) {
+  if (*dst) cudaFree((void*)*dst);
+  *dst = nullptr;
+  CAI_CUDA(ctx, cudaMalloc((void**)dst, src.size() * sizeof(void*)));
+  CAI_CUDA(ctx, cudaMemcpyAsync((void*)*dst, src.data(), src.size() * sizeof(void*), cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+int cai_model_finalize(cai_model* m) {
+  if (!m) return CAI_ERR_INVALID;
+  cai_ctx* ctx = m->ctx;
+  CAI_TRY(cai_bind(ctx));
+  const cai_llama_config& c = m->cfg;
+  if (!m->have_embed) return cai_fail(ctx, CAI_ERR_STATE, "missing tensor model.embed_tokens.weight");
+  if (!m->final_norm) return cai_fail(ctx, CAI_ERR_STATE, "missing tensor model.norm.weight");
+  if (!m->have_head) {
+    // tied head = the embedding rows (this rank's vocabulary shard)
+    if (!c.tie_embeddings) return cai_fail(ctx, CAI_ERR_STATE, "missing tensor lm_head.weight (and tie_embeddings is off)");
+    m->lm_head = qweight_rows_view(m->embed, (int64_t)m->tp_rank * m->vocab_l, m->vocab_l);
+    m->have_head = true;
+  }
+  for (int l = 0; l < c.layers; ++l) {
+    LayerW& L = m->layers[(size_t)l];
+    uint32_t need = HAVE_ATTN_NORM | HAVE_FFN_NORM | HAVE_Q | HAVE_K | HAVE_V | HAVE_O;
+    if (c.qkv_bias) need |= HAVE_QB | HAVE_KB | HAVE_VB;
+    if (c.qk_norm) need |= HAVE_QNORM | HAVE_KNORM;
+    if (c.n_experts) need |= HAVE_ROUTER; else need |= HAVE_GATE | HAVE_UP | HAVE_DOWN;
+    if ((L.have & need) != need) return cai_fail(ctx, CAI_ERR_STATE, "layer %d is missing tensors (have mask 0x%x, need 0x%x)", l, L.have, need);
+    if (c.n_experts) {
+      std::vector<const void*> gc, gs, dc, ds;
+      for (int e = 0; e < c.n_experts; ++e) {
+        if (L.exp_have[(size_t)e] != 7) return cai_fail(ctx, CAI_ERR_STATE, "layer %d expert %d is missing tensors", l, e);
+        if (L.exp_gu[(size_t)e].type != L.exp_gu[0].type || L.exp_down[(size_t)e].type != L.exp_down[0].type)
+          return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "experts of one layer must share a storage type");
+        gc.push_back(L.exp_gu[(size_t)e].codes); gs.push_back(L.exp_gu[(size_t)e].scales);
+        dc.push_back(L.exp_down[(size_t)e].codes); ds.push_back(L.exp_down[(size_t)e].scales);
+      }
+      CAI_TRY(upload_ptr_array(ctx, &L.d_gu_codes, gc));
+      CAI_TRY(upload_ptr_array(ctx, (const void***)&L.d_gu_scales, gs));
+      CAI_TRY(upload_ptr_array(ctx, &L.d_down_codes, dc));
+      CAI_TRY(upload_ptr_array(ctx, (const void***)&L.d_down_scales, ds));
+    }
+  }
+  if (!m->theta) CAI_CUDA(ctx, cudaMalloc((void**)&m->theta, (size_t)(c.head_dim / 2) * 4));
+  CAI_TRY(op_rope_theta_table(ctx, m->theta, c.head_dim, c.rope_theta));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  m->finalized = true;
+  return CAI_OK;
+}
+
+int cai_model_step_weight_bytes(cai_model* m, int64_t* out_bytes) {
+  if (!m || !out_bytes) return CAI_ERR_INVALID;
+  if (!m->finalized) return cai_fail(m->ctx, CAI_ERR_STATE, "model is not finalized");
+  int64_t b = (int64_t)m->lm_head.bytes();
+  for (auto& L : m->layers) {
+    b += (int64_t)(L.wqkv.bytes() + L.wo.bytes());
+    if (m->cfg.n_experts) {
+      b += (int64_t)L.router.bytes();
+      // one token touches top_k experts
+      b += (int64_t)m->cfg.top_k * (int64_t)(L.exp_gu[0].bytes() + L.exp_down[0].bytes());
+    } else {
+      b += (int64_t)(L.wgu.bytes() + L.wdown.bytes());
+    }
+  }
+  *out_bytes = b;
+  return CAI_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// session
+// ---------------------------------------------------------------------------
+struct cai_session {
+  cai_model* m;
+  cai_ctx* ctx;
+  int max_ctx, batch;
+  float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][max_ctx][hd]
+  float *k_snap = nullptr, *v_snap = nullptr;
+  size_t layer_stride = 0;                            // floats per layer
+  int32_t *tokens_dev = nullptr, *pos_dev = nullptr, *len_dev = nullptr;
+  int32_t* io_pinned = nullptr;                       // [3][B] tokens, pos, len
+  std::vector<int32_t> len_host, len_snap;
+  bool have_snap = false;
+  float *x = nullptr, *x_alt = nullptr, *h = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
+  float *router_logits = nullptr, *gates = nullptr, *moe_hidden = nullptr, *pair_out = nullptr;
+  int32_t* expert_ids = nullptr;
+  float* partial = nullptr;
+  int nsplit = 1;
+  int32_t* amax_idx = nullptr; float* amax_val = nullptr;
+  float *amax_pack = nullptr, *amax_gather = nullptr, *logits_gather = nullptr;
+  int32_t* trace = nullptr; int32_t* trace_count = nullptr; int64_t trace_cap = 0;
+  int32_t* prefill_buf = nullptr; int64_t prefill_cap = 0;
+  cudaGraphExec_t graph_exec = nullptr;
+  int64_t graph_kernels = 0;
+  bool use_graph = true;
+  std::vector<float> host_gather;
+};
+
+__global__ void pack_argmax_kernel(const int32_t* idx, const float* val, int batch, int offset, float* pack) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < batch) { pack[2 * b] = val[b]; pack[2 * b + 1] = __int_as_float(idx[b] + offset); }
+}
+__global__ void pick_argmax_kernel(const float* gathered, int batch, int world, int32_t* idx) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  float best = -INFINITY; int besti = 0x7fffffff;
+  for (int r = 0; r < world; ++r) {
+    const float v = gathered[((size_t)r * batch + b) * 2];
+    const int i = __float_as_int(gathered[((size_t)r * batch + b) * 2 + 1]);
+    if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+  }
+  idx[b] = (besti == 0x7fffffff) ? 0 : besti;
+}
+// end of step: next token = argmax, position and cache length advance, argmax appended to the trace
+__global__ void advance_kernel(int32_t* tokens, int32_t* pos, int32_t* len, const int32_t* amax, int batch,
+                               int32_t* trace, int32_t* trace_count, int64_t trace_cap) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  const int cnt = *trace_count;
+  if (b < batch) {
+    tokens[b] = amax[b];
+    pos[b] += 1;
+    len[b] += 1;
+    if ((int64_t)(cnt + 1) * batch <= trace_cap) trace[(int64_t)cnt * batch + b] = amax[b];
+  }
+  __syncthreads();
+  if (b == 0) *trace_count = cnt + 1;
+}
+
+static int enqueue_step(cai_session* s) {
+  cai_model* m = s->m;
+  cai_ctx* ctx = s->ctx;
+  const cai_llama_config& c = m->cfg;
+  const int B = s->batch, H = c.hidden;
+  const int QKVW = m->qw_l + 2 * m->kw_l;
+  float* x = s->x;
+  float* xalt = s->x_alt;
+  CAI_TRY(op_embed(ctx, &m->embed, s->tokens_dev, B, x, H));
+  for (int l = 0; l < c.layers; ++l) {
+    LayerW& L = m->layers[(size_t)l];
+    CAI_TRY(op_rmsnorm(ctx, x, H, L.attn_norm, s->h, H, B, H, c.rms_eps));
+    {
+      LinearArgs a; a.w = &L.wqkv; a.x = s->h; a.ldx = H; a.y = s->qkv; a.ldy = QKVW; a.batch = B;
+      CAI_TRY(linear_launch(ctx, a));
+    }
+    {
+      AttnArgs a;
+      a.qkv = s->qkv; a.ld = QKVW;
+      a.k_cache = s->k_cache + (size_t)l * s->layer_stride; a.v_cache = s->v_cache + (size_t)l * s->layer_stride;
+      a.cache_len_dev = s->len_dev; a.batch = B; a.q_heads = m->heads_l; a.kv_heads = m->kv_heads_l;
+      a.head_dim = c.head_dim; a.max_ctx = s->max_ctx; a.theta = m->theta; a.pos_dev = s->pos_dev;
+      a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
+      a.out = s->att; a.ldo = m->qw_l; a.partial = s->partial; a.nsplit = s->nsplit;
+      CAI_TRY(attn_rope_append(ctx, a));
+      CAI_TRY(attn_decode(ctx, a));
+    }
+    // attention output projection + residual
+    if (m->tp_size == 1) {
+      LinearArgs a; a.w = &L.wo; a.x = s->att; a.ldx = m->qw_l; a.y = x; a.ldy = H; a.batch = B; a.epilogue = EPI_RESID; a.resid = x;
+      CAI_TRY(linear_launch(ctx, a));
+    } else {
+      LinearArgs a; a.w = &L.wo; a.x = s->att; a.ldx = m->qw_l; a.y = xalt; a.ldy = H; a.batch = B;
+      if (m->tp_rank == 0) { a.epilogue = EPI_RESID; a.resid = x; }
+      CAI_TRY(linear_launch(ctx, a));
+      CAI_TRY(comm_allreduce(ctx, xalt, (int64_t)B * H));
+      float* t = x; x = xalt; xalt = t;
+    }
+    CAI_TRY(op_rmsnorm(ctx, x, H, L.ffn_norm, s->h, H, B, H, c.rms_eps));
+    if (!c.n_experts) {
+      {
+        LinearArgs a; a.w = &L.wgu; a.x = s->h; a.ldx = H; a.y = s->act; a.ldy = m->inter_l; a.batch = B; a.epilogue = EPI_SWIGLU;
+        CAI_TRY(linear_launch(ctx, a));
+      }
+      if (m->tp_size == 1) {
+        LinearArgs a; a.w = &L.wdown; a.x = s->act; a.ldx = m->inter_l; a.y = x; a.ldy = H; a.batch = B; a.epilogue = EPI_RESID; a.resid = x;
+        CAI_TRY(linear_launch(ctx, a));
+      } else {
+        LinearArgs a; a.w = &L.wdown; a.x = s->act; a.ldx = m->inter_l; a.y = xalt; a.ldy = H; a.batch = B;
+        if (m->tp_rank == 0) { a.epilogue = EPI_RESID; a.resid = x; }
+        CAI_TRY(linear_launch(ctx, a));
+        CAI_TRY(comm_allreduce(ctx, xalt, (int64_t)B * H));
+        float* t = x; x = xalt; xalt = t;
+      }
+    } else {
+      const int E = c.n_experts, K = c.top_k, Im = c.moe_inter;
+      {
+        LinearArgs a; a.w = &L.router; a.x = s->h; a.ldx = H; a.y = s->router_logits; a.ldy = E; a.batch = B;
+        CAI_TRY(linear_launch(ctx, a));
+      }
+      CAI_TRY(op_topk_gate(ctx, s->router_logits, B, E, K, c.norm_topk, s->expert_ids, s->gates));
+      {
+        LinearArgs a; a.w = &L.exp_gu[0]; a.x = s->h; a.ldx = H; a.y = s->moe_hidden; a.ldy = Im; a.batch = B * K;
+        a.epilogue = EPI_SWIGLU; a.bank_codes_dev = L.d_gu_codes; a.bank_scales_dev = L.d_gu_scales;
+        a.expert_ids_dev = s->expert_ids; a.x_row_div = K;
+        CAI_TRY(linear_launch(ctx, a));
+      }
+      {
+        LinearArgs a; a.w = &L.exp_down[0]; a.x = s->moe_hidden; a.ldx = Im; a.y = s->pair_out; a.ldy = H; a.batch = B * K;
+        a.bank_codes_dev = L.d_down_codes; a.bank_scales_dev = L.d_down_scales; a.expert_ids_dev = s->expert_ids; a.x_row_div = 1;
+        CAI_TRY(linear_launch(ctx, a));
+      }
+      CAI_TRY(op_moe_combine(ctx, x, H, s->pair_out, H, s->gates, B, K, H));
+    }
+  }
+  CAI_TRY(op_rmsnorm(ctx, x, H, m->final_norm, s->h, H, B, H, c.rms_eps));
+  {
+    LinearArgs a; a.w = &m->lm_head; a.x = s->h; a.ldx = H; a.y = s->logits; a.ldy = m->vocab_l; a.batch = B;
+    CAI_TRY(linear_launch(ctx, a));
+  }
+  CAI_TRY(op_argmax(ctx, s->logits, m->vocab_l, B, m->vocab_l, s->amax_idx, s->amax_val));
+  if (m->tp_size > 1) {
+    pack_argmax_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(s->amax_idx, s->amax_val, B, m->tp_rank * m->vocab_l, s->amax_pack);
+    CAI_LAUNCHED(ctx);
+    CAI_TRY(comm_allgather(ctx, s->amax_pack, s->amax_gather, (int64_t)B * 2));
+    pick_argmax_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(s->amax_gather, B, m->tp_size, s->amax_idx);
+    CAI_LAUNCHED(ctx);
+  }
+  if (B > 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "batch above 1024");
+  advance_kernel<<<1, ((B + 31) / 32) * 32, 0, ctx->stream>>>(s->tokens_dev, s->pos_dev, s->len_dev, s->amax_idx, B, s->trace,
+                                                              s->trace_count, s->trace_cap);
+  CAI_LAUNCHED(ctx);
+  if (x != s->x) return cai_fail(ctx, CAI_ERR_STATE, "internal: residual buffer parity");
+  return CAI_OK;
+}
+
+// Runs one step: through the captured CUDA graph when enabled, else eagerly.
+static int run_step(cai_session* s) {
+  cai_ctx* ctx = s->ctx;
+  if (!s->use_graph) return enqueue_step(s);
+  if (!s->graph_exec) {
+    const int64_t before = ctx->launches;
+    cudaGraph_t graph = nullptr;
+    CAI_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    const int st = enqueue_step(s);
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (st != CAI_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "cudaStreamEndCapture -> %s", cudaGetErrorString(e));
+    s->graph_kernels = ctx->launches - before;
+    ctx->launches = before;
+    e = cudaGraphInstantiate(&s->graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { s->graph_exec = nullptr; return cai_fail(ctx, CAI_ERR_CUDA, "cudaGraphInstantiate -> %s", cudaGetErrorString(e)); }
+  }
+  CAI_CUDA(ctx, cudaGraphLaunch(s->graph_exec, ctx->stream));
+  ctx->launches += s->graph_kernels;
+  return CAI_OK;
+}
+
+static int push_len(cai_session* s) {
+  cai_ctx* ctx = s->ctx;
+  int32_t* pin = s->io_pinned + 2 * s->batch;
+  for (int b = 0; b < s->batch; ++b) pin[b] = s->len_host[(size_t)b];
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->len_dev, pin, (size_t)s->batch * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+static int check_room(cai_session* s, int steps) {
+  for (int b = 0; b < s->batch; ++b)
+    if (s->len_host[(size_t)b] + steps > s->max_ctx)
+      return cai_fail(s->ctx, CAI_ERR_STATE, "context full: sequence %d holds %d of %d positions, %d more requested", b,
+                      s->len_host[(size_t)b], s->max_ctx, steps);
+  return CAI_OK;
+}
+
+extern "C" {
+
+int cai_session_destroy(cai_session* s) {
+  if (!s) return CAI_ERR_INVALID;
+  cudaSetDevice(s->ctx->device);
+  cudaStreamSynchronize(s->ctx->stream);
+  if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
+  void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
+                  s->att, s->act, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
+                  s->amax_idx, s->amax_val, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf};
+  for (void* p : bufs) if (p) cudaFree(p);
+  if (s->io_pinned) cudaFreeHost(s->io_pinned);
+  s->m->sessions -= 1;
+  delete s;
+  return CAI_OK;
+}
+
+int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_session** out) {
+  if (!m) return CAI_ERR_INVALID;
+  cai_ctx* ctx = m->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_create: null output");
+  *out = nullptr;
+  if (!m->finalized) return cai_fail(ctx, CAI_ERR_STATE, "call cai_model_finalize before creating sessions");
+  if (max_ctx < 1 || batch < 1 || batch > 1024) return cai_fail(ctx, CAI_ERR_INVALID, "max_ctx %d batch %d", max_ctx, batch);
+  if (kv_type != CAI_TYPE_F32) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "only the fp32 KV cache is built");
+  const cai_llama_config& c = m->cfg;
+  const size_t layer_stride = (size_t)batch * m->kv_heads_l * max_ctx * c.head_dim;
+  const size_t cache_bytes = layer_stride * (size_t)c.layers * 4;
+  size_t free_b = 0, total_b = 0;
+  CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
+  if (2 * cache_bytes + ((size_t)256 << 20) > free_b)
+    return cai_fail(ctx, CAI_ERR_OOM, "KV cache of %zu bytes does not fit in %zu free device bytes", 2 * cache_bytes, free_b);
+  cai_session* s = new (std::nothrow) cai_session();
+  if (!s) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
+  s->m = m; s->ctx = ctx; s->max_ctx = max_ctx; s->batch = batch; s->layer_stride = layer_stride;
+  s->len_host.assign((size_t)batch, 0);
+  m->sessions += 1;
+  const char* ng = getenv("CAI_NO_GRAPH");
+  s->use_graph = !(ng && *ng && *ng != '0');
+  const int B = batch, H = c.hidden, QKVW = m->qw_l + 2 * m->kw_l;
+  s->nsplit = attn_nsplit(ctx, B, m->kv_heads_l, max_ctx);
+  s->trace_cap = (int64_t)max_ctx * B;
+  bool ok = true;
+  auto A = [&](void** p, size_t bytes) { if (ok && cudaMalloc(p, bytes ? bytes : 4) != cudaSuccess) { cudaGetLastError(); ok = false; } };
+  A((void**)&s->k_cache, cache_bytes); A((void**)&s->v_cache, cache_bytes);
+  A((void**)&s->tokens_dev, (size_t)B * 4); A((void**)&s->pos_dev, (size_t)B * 4); A((void**)&s->len_dev, (size_t)B * 4);
+  A((void**)&s->x, (size_t)B * H * 4); A((void**)&s->x_alt, (size_t)B * H * 4); A((void**)&s->h, (size_t)B * H * 4);
+  A((void**)&s->qkv, (size_t)B * QKVW * 4); A((void**)&s->att, (size_t)B * m->qw_l * 4);
+  A((void**)&s->act, (size_t)B * (m->inter_l ? m->inter_l : 1) * 4);
+  A((void**)&s->logits, (size_t)B * m->vocab_l * 4);
+  A((void**)&s->partial, attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim) * 4);
+  A((void**)&s->amax_idx, (size_t)B * 4); A((void**)&s->amax_val, (size_t)B * 4);
+  A((void**)&s->trace, (size_t)s->trace_cap * 4); A((void**)&s->trace_count, 4);
+  if (c.n_experts) {
+    A((void**)&s->router_logits, (size_t)B * c.n_experts * 4); A((void**)&s->gates, (size_t)B * c.top_k * 4);
+    A((void**)&s->expert_ids, (size_t)B * c.top_k * 4);
+    A((void**)&s->moe_hidden, (size_t)B * c.top_k * c.moe_inter * 4); A((void**)&s->pair_out, (size_t)B * c.top_k * H * 4);
+  }
+  if (m->tp_size > 1) {
+    A((void**)&s->amax_pack, (size_t)B * 2 * 4); A((void**)&s->amax_gather, (size_t)m->tp_size * B * 2 * 4);
+    A((void**)&s->logits_gather, (size_t)m->tp_size * B * m->vocab_l * 4);
+  }
+  if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)3 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
+  if (!ok) { cai_session_destroy(s); return cai_fail(ctx, CAI_ERR_OOM, "session buffers do not fit on the device"); }
+  CAI_CUDA(ctx, cudaMemsetAsync(s->len_dev, 0, (size_t)B * 4, ctx->stream));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->pos_dev, 0, (size_t)B * 4, ctx->stream));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->tokens_dev, 0, (size_t)B * 4, ctx->stream));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->trace_count, 0, 4, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  *out = s;
+  return CAI_OK;
+}
+
+int cai_session_reset(cai_session* s, int seq) {
+  if (!s) return CAI_ERR_INVALID;
+  CAI_TRY(cai_bind(s->ctx));
+  if (seq < -1 || seq >= s->batch) return cai_fail(s->ctx, CAI_ERR_INVALID, "sequence %d of %d", seq, s->batch);
+  for (int b = 0; b < s->batch; ++b) if (seq < 0 || seq == b) s->len_host[(size_t)b] = 0;
+  return push_len(s);
+}
+
+int cai_session_truncate(cai_session* s, int seq, int committed_len) {
+  if (!s) return CAI_ERR_INVALID;
+  CAI_TRY(cai_bind(s->ctx));
+  if (seq < 0 || seq >= s->batch) return cai_fail(s->ctx, CAI_ERR_INVALID, "sequence %d of %d", seq, s->batch);
+  if (committed_len < 0 || committed_len > s->len_host[(size_t)seq])
+    return cai_fail(s->ctx, CAI_ERR_INVALID, "truncate to %d outside the committed prefix of %d", committed_len, s->len_host[(size_t)seq]);
+  s->len_host[(size_t)seq] = committed_len;
+  return push_len(s);
+}
+
+int cai_session_cache_len(cai_session* s, int seq, int* out_len) {
+  if (!s || !out_len) return CAI_ERR_INVALID;
+  if (seq < 0 || seq >= s->batch) return cai_fail(s->ctx, CAI_ERR_INVALID, "sequence %d of %d", seq, s->batch);
+  *out_len = s->len_host[(size_t)seq];
+  return CAI_OK;
+}
+
+static int stage_inputs(cai_session* s, const int32_t* tokens_host, const int32_t* abs_pos_host) {
+  cai_ctx* ctx = s->ctx;
+  const int B = s->batch;
+  const int vocab = s->m->cfg.vocab;
+  for (int b = 0; b < B; ++b) {
+    if (tokens_host[b] < 0 || tokens_host[b] >= vocab) return cai_fail(ctx, CAI_ERR_INVALID, "token id %d outside the vocabulary of %d", tokens_host[b], vocab);
+    s->io_pinned[b] = tokens_host[b];
+    s->io_pinned[B + b] = abs_pos_host ? abs_pos_host[b] : s->len_host[(size_t)b];
+  }
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->tokens_dev, s->io_pinned, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->pos_dev, s->io_pinned + B, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+  return CAI_OK;
+}
+
+int cai_session_step(cai_session* s, const int32_t* tokens_host, const int32_t* abs_pos_host, float* logits_out_host,
+                     int32_t* argmax_out_host) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  cai_model* m = s->m;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_step: null tokens");
+  CAI_TRY(check_room(s, 1));
+  CAI_TRY(stage_inputs(s, tokens_host, abs_pos_host));
+  CAI_TRY(run_step(s));
+  for (auto& l : s->len_host) l += 1;
+  const int B = s->batch, Vl = m->vocab_l, V = m->cfg.vocab;
+  if (logits_out_host) {
+    if (m->tp_size == 1) {
+      CAI_CUDA(ctx, cudaMemcpyAsync(logits_out_host, s->logits, (size_t)B * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    } else {
+      CAI_TRY(comm_allgather(ctx, s->logits, s->logits_gather, (int64_t)B * Vl));
+      s->host_gather.resize((size_t)m->tp_size * B * Vl);
+      CAI_CUDA(ctx, cudaMemcpyAsync(s->host_gather.data(), s->logits_gather, s->host_gather.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+  }
+  if (argmax_out_host) CAI_CUDA(ctx, cudaMemcpyAsync(argmax_out_host, s->amax_idx, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (logits_out_host && m->tp_size > 1) {
+    for (int r = 0; r < m->tp_size; ++r)
+      for (int b = 0; b < B; ++b)
+        memcpy(logits_out_host + (size_t)b * V + (size_t)r * Vl, s->host_gather.data() + ((size_t)r * B + b) * Vl, (size_t)Vl * 4);
+  }
+  return CAI_OK;
+}
+
+int cai_session_decode_greedy(cai_session* s, const int32_t* tokens_host, int n_steps, int32_t* out_tokens_host) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host || n_steps < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_decode_greedy: bad argument");
+  CAI_TRY(check_room(s, n_steps));
+  CAI_TRY(stage_inputs(s, tokens_host, nullptr));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->trace_count, 0, 4, ctx->stream));
+  for (int i = 0; i < n_steps; ++i) CAI_TRY(run_step(s));
+  for (auto& l : s->len_host) l += n_steps;
+  if (out_tokens_host)
+    CAI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, s->trace, (size_t)n_steps * s->batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host || n_tokens < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_prefill: bad argument");
+  CAI_TRY(check_room(s, n_tokens));
+  const int B = s->batch, vocab = s->m->cfg.vocab;
+  const int64_t need = (int64_t)n_tokens * B;
+  if (s->prefill_cap < need) {
+    if (s->prefill_buf) cudaFree(s->prefill_buf);
+    s->prefill_buf = nullptr; s->prefill_cap = 0;
+    CAI_CUDA(ctx, cudaMalloc((void**)&s->prefill_buf, (size_t)need * 4));
+    s->prefill_cap = need;
+  }
+  // step-major copy: row i holds the i-th token of every sequence
+  std::vector<int32_t> stepmajor((size_t)need);
+  for (int b = 0; b < B; ++b)
+    for (int i = 0; i < n_tokens; ++i) {
+      const int32_t t = tokens_host[(size_t)b * n_tokens + i];
+      if (t < 0 || t >= vocab) return cai_fail(ctx, CAI_ERR_INVALID, "token id %d outside the vocabulary of %d", t, vocab);
+      stepmajor[(size_t)i * B + b] = t;
+    }
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->prefill_buf, stepmajor.data(), (size_t)need * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  std::vector<int32_t> first(stepmajor.begin(), stepmajor.begin() + B);
+  CAI_TRY(stage_inputs(s, first.data(), nullptr));
+  for (int i = 0; i < n_tokens; ++i) {
+    CAI_CUDA(ctx, cudaMemcpyAsync(s->tokens_dev, s->prefill_buf + (size_t)i * B, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    CAI_TRY(run_step(s));
+  }
+  for (auto& l : s->len_host) l += n_tokens;
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+int cai_session_profile(cai_session* s, const int32_t* tokens_host, int n_steps, float* out_ms, int64_t* out_launches) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host || n_steps < 1 || !out_ms || !out_launches) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_profile: bad argument");
+  CAI_TRY(check_room(s, n_steps));
+  CAI_TRY(stage_inputs(s, tokens_host, nullptr));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int f = 0; f < FAM_COUNT; ++f) { out_ms[f] = 0.f; out_launches[f] = 0; }
+  ctx->prof_n = 0;
+  ctx->prof_on = 1;
+  int st = cai_prof_mark(ctx, FAM_OTHER);     // origin event
+  for (int i = 0; i < n_steps && st == CAI_OK; ++i) st = enqueue_step(s);   // eager launches, one event after each
+  ctx->prof_on = 0;
+  if (st != CAI_OK) return st;
+  for (auto& l : s->len_host) l += n_steps;
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int i = 1; i < ctx->prof_n; ++i) {
+    float ms = 0.f;
+    CAI_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->prof_events[i - 1], ctx->prof_events[i]));
+    const int f = ctx->prof_family[i];
+    out_ms[f] += ms;
+    out_launches[f] += 1;
+  }
+  return CAI_OK;
+}
+
+int cai_session_snapshot(cai_session* s) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  const size_t bytes = s->layer_stride * (size_t)s->m->cfg.layers * 4;
+  if (!s->k_snap) {
+    size_t free_b = 0, total_b = 0;
+    CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
+    if (2 * bytes + ((size_t)64 << 20) > free_b) return cai_fail(ctx, CAI_ERR_OOM, "snapshot of %zu bytes does not fit", 2 * bytes);
+    CAI_CUDA(ctx, cudaMalloc((void**)&s->k_snap, bytes));
+    CAI_CUDA(ctx, cudaMalloc((void**)&s->v_snap, bytes));
+  }
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->k_snap, s->k_cache, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->v_snap, s->v_cache, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  s->len_snap = s->len_host;
+  s->have_snap = true;
+  return CAI_OK;
+}
+
+int cai_session_restore(cai_session* s) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!s->have_snap) return cai_fail(ctx, CAI_ERR_STATE, "no snapshot to restore");
+  const size_t bytes = s->layer_stride * (size_t)s->m->cfg.layers * 4;
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->k_cache, s->k_snap, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->v_cache, s->v_snap, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  s->len_host = s->len_snap;
+  return push_len(s);
+}
+
+int cai_session_logits_dev(cai_session* s, const float** out_dev) {
+  if (!s || !out_dev) return CAI_ERR_INVALID;
+  *out_dev = s->logits;
+  return CAI_OK;
+}
+
+int cai_session_last_kv_bytes(cai_session* s, int64_t* out_bytes) {
+  if (!s || !out_bytes) return CAI_ERR_INVALID;
+  int64_t rows = 0;
+  for (int l : s->len_host) rows += l;
+  *out_bytes = rows * 2 * (int64_t)s->m->kw_l * 4 * (int64_t)s->m->cfg.layers;
+  return CAI_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,260 @@
+// Small per-token operators of the decode step: embedding gather, RMSNorm, RoPE,
+// SwiGLU, router softmax/top-k, argmax, MoE combine.
+#include "cai_common.cuh"
+#include <math.h>
+
+// ---------------------------------------------------------------------------
+// embedding gather: out[b][c] = dequant(table[token_b][c])   (EncodeZero = 1:
+// token 0 is a real row)
+// ---------------------------------------------------------------------------
+__global__ void embed_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
+                             int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld) {
+  const int b = blockIdx.x;
+  int64_t tok = tokens[b];
+  if (tok < 0) tok = 0;
+  if (tok >= n_rows) tok = n_rows - 1;
+  for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
+    float v;
+    const int64_t i = tok * k + c;
+    if (type == CAI_TYPE_Q8_0) v = __half2float(scales[i / CAI_QK]) * (float)((const int8_t*)codes)[i];
+    else if (type == CAI_TYPE_Q4_0) {
+      const int64_t blk = i / CAI_QK;
+      const int e = (int)(i % CAI_QK);
+      const uint8_t byte = ((const uint8_t*)codes)[blk * 16 + (e & 15)];
+      const int nib = (e < 16) ? (byte & 0x0F) : (byte >> 4);
+      v = __half2float(scales[blk]) * (float)(nib - 8);
+    } else if (type == CAI_TYPE_F16) v = __half2float(((const __half*)codes)[i]);
+    else v = ((const float*)codes)[i];
+    out[(int64_t)b * ld + c] = v;
+  }
+}
+
+int op_embed(cai_ctx* ctx, const QWeight* t, const int32_t* tokens_dev, int batch, float* out, int64_t ld) {
+  ctx->cur_family = FAM_OTHER;
+  embed_kernel<<<batch, 256, 0, ctx->stream>>>(t->type, t->codes, t->scales, t->k, t->n, tokens_dev, out, ld);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm per token: inv = 1/sqrt(mean(x^2) + eps); y = gain * (x * inv)
+// ---------------------------------------------------------------------------
+__global__ void rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ gain,
+                               float* __restrict__ y, int64_t ldy, int depth, float eps) {
+  __shared__ float red[32];
+  const float* xr = x + (int64_t)blockIdx.x * ldx;
+  float* yr = y + (int64_t)blockIdx.x * ldy;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < depth; c += blockDim.x) { const float v = xr[c]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)depth + eps);
+  for (int c = threadIdx.x; c < depth; c += blockDim.x) yr[c] = gain[c] * (xr[c] * inv);
+}
+
+int op_rmsnorm(cai_ctx* ctx, const float* x, int64_t ldx, const float* gain, float* y, int64_t ldy, int tokens, int depth, float eps) {
+  ctx->cur_family = FAM_OTHER;
+  int threads = depth >= 2048 ? 512 : (depth >= 512 ? 256 : 128);
+  rmsnorm_kernel<<<tokens, threads, 0, ctx->stream>>>(x, ldx, gain, y, ldy, depth, eps);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// RoPE on interleaved pairs (2k, 2k+1); angle = (float)pos * theta[k] in fp32,
+// full-range sincosf.
+// ---------------------------------------------------------------------------
+__global__ void rope_theta_kernel(float* theta, int half, int head_dim, double log_base) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < half) theta[k] = (float)exp(-2.0 * (double)k / (double)head_dim * log_base);
+}
+int op_rope_theta_table(cai_ctx* ctx, float* theta_dev, int head_dim, float base) {
+  ctx->cur_family = FAM_OTHER;
+  const int half = head_dim / 2;
+  rope_theta_kernel<<<(half + 127) / 128, 128, 0, ctx->stream>>>(theta_dev, half, head_dim, log((double)base));
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+__global__ void rope_kernel(float* __restrict__ x, int64_t ldx, int depth, int head_dim, const float* __restrict__ theta,
+                            const int32_t* __restrict__ pos_dev, int pos_stride, int pos_offset) {
+  const int t = blockIdx.x;
+  const int pos = (pos_dev ? pos_dev[t * pos_stride] : t) + pos_offset;
+  const int half_hd = head_dim >> 1;
+  float* xr = x + (int64_t)t * ldx;
+  for (int pr = threadIdx.x; pr < (depth >> 1); pr += blockDim.x) {
+    const int k = pr % half_hd;
+    const float angle = (float)pos * theta[k];
+    float s, c;
+    sincosf(angle, &s, &c);
+    const float x0 = xr[2 * pr], x1 = xr[2 * pr + 1];
+    xr[2 * pr] = c * x0 - s * x1;
+    xr[2 * pr + 1] = s * x0 + c * x1;
+  }
+}
+
+int op_rope(cai_ctx* ctx, float* x, int64_t ldx, int tokens, int depth, int head_dim, const float* theta_dev,
+            const int32_t* pos_dev, int pos_stride, int pos_offset) {
+  ctx->cur_family = FAM_OTHER;
+  rope_kernel<<<tokens, 128, 0, ctx->stream>>>(x, ldx, depth, head_dim, theta_dev, pos_dev, pos_stride, pos_offset);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU: y[d] = x[d] * swish(x[half + d])   (first half = up, second = gate)
+// ---------------------------------------------------------------------------
+__global__ void swiglu_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ y, int64_t ldy, int half) {
+  const float* xr = x + (int64_t)blockIdx.y * ldx;
+  float* yr = y + (int64_t)blockIdx.y * ldy;
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= half) return;
+  const float a = xr[d], b = xr[half + d];
+  float sig;
+  if (b > 0.f) sig = 1.0f / (1.0f + expf(-b));
+  else { const float s = expf(b); sig = s / (1.0f + s); }
+  yr[d] = a * (b * sig);
+}
+int op_swiglu(cai_ctx* ctx, const float* x, int64_t ldx, float* y, int64_t ldy, int tokens, int half) {
+  ctx->cur_family = FAM_OTHER;
+  dim3 grid((half + 255) / 256, tokens);
+  swiglu_kernel<<<grid, 256, 0, ctx->stream>>>(x, ldx, y, ldy, half);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Router: softmax over all experts, keep top-k (ties: lowest index), optional
+// renormalisation of the survivors. One warp per token.
+// ---------------------------------------------------------------------------
+__global__ void topk_gate_kernel(const float* __restrict__ logits, int tokens, int n_experts, int top_k, int renorm,
+                                 int32_t* __restrict__ ids, float* __restrict__ gates) {
+  extern __shared__ float probs_all[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= tokens) return;
+  float* probs = probs_all + (size_t)warp * n_experts;
+  const float* row = logits + (int64_t)t * n_experts;
+  float m = -INFINITY;
+  for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, row[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < n_experts; e += 32) { const float v = expf(row[e] - m); probs[e] = v; sum += v; }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < n_experts; e += 32) probs[e] = probs[e] / sum;
+  __syncwarp();
+  float kept_sum = 0.f;
+  for (int s = 0; s < top_k; ++s) {
+    float best = -INFINITY; int besti = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = probs[e];
+      if (v >= 0.f && (v > best || (v == best && e < besti))) { best = v; besti = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0) {
+      ids[(int64_t)t * top_k + s] = besti;
+      gates[(int64_t)t * top_k + s] = best;
+      probs[besti] = -1.0f;   // taken
+    }
+    kept_sum += best;
+    __syncwarp();
+  }
+  if (renorm && lane == 0)
+    for (int s = 0; s < top_k; ++s) gates[(int64_t)t * top_k + s] = gates[(int64_t)t * top_k + s] / kept_sum;
+}
+
+int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, int top_k, int renorm,
+                 int32_t* ids, float* gates) {
+  ctx->cur_family = FAM_OTHER;
+  if (top_k < 1 || top_k > n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "top_k %d of %d experts", top_k, n_experts);
+  const int warps = 4;
+  const size_t smem = (size_t)warps * n_experts * sizeof(float);
+  if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "router with %d experts exceeds the kernel's shared memory", n_experts);
+  topk_gate_kernel<<<(tokens + warps - 1) / warps, warps * 32, smem, ctx->stream>>>(logits, tokens, n_experts, top_k, renorm, ids, gates);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// argmax: first index of the maximum of each row.
+// ---------------------------------------------------------------------------
+__global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int n, int32_t* __restrict__ out_idx,
+                              float* __restrict__ out_val) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const float* row = logits + (int64_t)blockIdx.x * ld;
+  float best = -INFINITY; int besti = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) { best = v; besti = i; }      // strided scan keeps the first index per thread
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+    if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+  }
+  if (lane == 0) { sv[warp] = best; si[warp] = besti; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = (lane < nw) ? sv[lane] : -INFINITY;
+    besti = (lane < nw) ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0) {
+      if (besti == 0x7fffffff) besti = 0;        // every entry NaN or -inf: index 0, like a scan that never updates
+      out_idx[blockIdx.x] = besti;
+      if (out_val) out_val[blockIdx.x] = best;
+    }
+  }
+}
+int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val) {
+  ctx->cur_family = FAM_OTHER;
+  argmax_kernel<<<batch, 1024, 0, ctx->stream>>>(logits, ld, n, out_idx, out_val);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// MoE combine: x[t] += sum_s gate[t][s] * pair_out[t*k + s]   (slot order)
+// ---------------------------------------------------------------------------
+__global__ void moe_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ pair_out, int64_t ldp,
+                                   const float* __restrict__ gates, int top_k, int depth) {
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= depth) return;
+  float y = 0.f;
+  for (int s = 0; s < top_k; ++s)
+    y = y + gates[(int64_t)t * top_k + s] * pair_out[((int64_t)t * top_k + s) * ldp + c];
+  x[(int64_t)t * ldx + c] += y;
+}
+int op_moe_combine(cai_ctx* ctx, float* x, int64_t ldx, const float* pair_out, int64_t ldp, const float* gates,
+                   int tokens, int top_k, int depth) {
+  ctx->cur_family = FAM_OTHER;
+  dim3 grid((depth + 255) / 256, tokens);
+  moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(x, ldx, pair_out, ldp, gates, top_k, depth);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += y[i];
+}
+int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n) {
+  ctx->cur_family = FAM_OTHER;
+  add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, y, n);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}

@@ -1,0 +1,249 @@
+"""Whole-model decode on the GPU against (a) the reference's golden logits of its pico
+checkpoints, (b) the oracle on GGUF Q8_0 weights, (c) the Qwen2.5-0.5B-shaped Q8_0
+workload: bit-exact dequantization, logits within 1e-3 of the logit RMS, identical
+greedy tokens."""
+import json
+
+import numpy as np
+import pytest
+
+from conftest import golden_hf_case, load_golden
+from oracle import codecs
+from oracle.forward import LlamaConfig, OracleModel, OracleSession, argmax_first
+from neural_api_b200.backend import (CaiError, LlamaModel, StreamingDecoder, generate_tokens_streamed, make_config,
+                                     TYPE_F32, TYPE_Q4_0, TYPE_Q8_0)
+from neural_api_b200.configs import ARCHS
+
+pytestmark = pytest.mark.gpu
+
+
+def cfg_to_c(cfg):
+    return make_config(hidden=cfg.hidden, inter=cfg.inter, layers=cfg.layers, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                       head_dim=cfg.head_dim, vocab=cfg.vocab, rms_eps=cfg.rms_eps, rope_theta=cfg.rope_theta,
+                       tie_embeddings=cfg.tie_embeddings, qkv_bias=cfg.qkv_bias, qk_norm=cfg.qk_norm,
+                       n_experts=cfg.n_experts, top_k=cfg.top_k, norm_topk=cfg.norm_topk, moe_inter=cfg.moe_inter)
+
+
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen2", "tiny_olmoe", "tiny_mixtral"])
+def test_golden_logits_of_the_reference_pico_checkpoints(backend, name):
+    """The reference's own end-to-end gate: max |logit diff| < 1e-4 against the float64 oracle
+    logits (tests/TestNeuralPretrained.pas:5684-5751)."""
+    cfg_json, tensors, seqs, gold = golden_hf_case(name)
+    cfg = LlamaConfig.from_hf(cfg_json)
+    model = LlamaModel(backend, cfg_to_c(cfg))
+    model.upload_hf_tensors(tensors)
+    model.finalize()
+    sess = StreamingDecoder(model, 16)
+    try:
+        worst = 0.0
+        for s, g in zip(seqs, gold):
+            sess.reset()
+            for i, t in enumerate(s):
+                logits, amax = sess.step_forward([int(t)], [i])
+                worst = max(worst, float(np.max(np.abs(logits[0] - g[i]))))
+                assert int(amax[0]) == argmax_first(logits[0])
+        assert worst < 1e-4, worst
+    finally:
+        sess.close()
+        model.close()
+
+
+def test_batched_sequences_equal_single_sequence_results(backend):
+    """`batch` is new surface: each row must reproduce the one-sequence session."""
+    cfg_json, tensors, seqs, gold = golden_hf_case("tiny_olmoe")
+    cfg = LlamaConfig.from_hf(cfg_json)
+    model = LlamaModel(backend, cfg_to_c(cfg))
+    model.upload_hf_tensors(tensors)
+    model.finalize()
+    sess = StreamingDecoder(model, 16, batch=3)
+    try:
+        for i in range(16):
+            logits, _ = sess.step_forward(seqs[:, i])
+            for b in range(3):
+                assert np.max(np.abs(logits[b] - gold[b][i])) < 1e-4
+    finally:
+        sess.close()
+        model.close()
+
+
+def _upload_gguf(model, z):
+    for k in z.files:
+        if k.startswith("raw::"):
+            name = k[5:]
+            ty, rows, cols = (int(v) for v in z["meta::" + name])
+            model.upload_tensor(name, ty, z[k], rows, cols, 0)      # GGUF row order is the in-net order
+
+
+def _oracle_from_gguf(z, cfg):
+    tensors = {}
+    for k in z.files:
+        if k.startswith("raw::"):
+            name = k[5:]
+            ty, rows, cols = (int(v) for v in z["meta::" + name])
+            w = codecs.dequantize(ty, z[k])
+            tensors[name] = w.reshape(rows, cols) if rows > 1 else w
+    return OracleModel.from_hf_tensors(cfg, tensors, interleave=False)
+
+
+@pytest.mark.parametrize("fixture", ["tiny_llama_q8_gguf", "tiny_llama_f16_gguf"])
+def test_reference_gguf_checkpoints(backend, fixture):
+    z = load_golden(fixture)
+    cfg = LlamaConfig.from_hf(json.loads(bytes(z["config_json"]).decode()))
+    model = LlamaModel(backend, cfg_to_c(cfg))
+    _upload_gguf(model, z)
+    model.finalize()
+    oracle = _oracle_from_gguf(z, cfg)
+    ctx = 12
+    sess = StreamingDecoder(model, ctx)
+    osess = OracleSession(oracle, ctx)
+    try:
+        seq = [1, 5, 2, 7, 0, 3, 6, 4, 2, 1]
+        for i, t in enumerate(seq):
+            logits, _ = sess.step_forward([t])
+            ref = osess.step(t)
+            rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+            assert np.max(np.abs(logits[0] - ref)) < 1e-4 * max(rms, 1.0)
+        if "q8" in fixture:
+            # drift against the F32 twin stays in the reference's band (1e-3, 1.5e-1) of max |logit|
+            twin = OracleModel.from_hf_tensors(cfg, {k[6:]: z[k] for k in z.files if k.startswith("twin::")})
+            ts = OracleSession(twin, ctx)
+            sess.reset()
+            drift, mx = 0.0, 0.0
+            for i, t in enumerate(seq):
+                logits, _ = sess.step_forward([t])
+                lt = ts.step(t)
+                drift = max(drift, float(np.max(np.abs(logits[0] - lt))))
+                mx = max(mx, float(np.max(np.abs(lt))))
+            assert 1e-3 < drift / mx < 1.5e-1
+    finally:
+        sess.close()
+        model.close()
+
+
+def test_session_services(backend):
+    """Reset, TruncateTo, Snapshot/RestoreSnapshot, context-full, bad tokens
+    (neural/neuraldecode.pas:5686-5720, 5759-5843)."""
+    cfg_json, tensors, seqs, gold = golden_hf_case("tiny_qwen2")
+    cfg = LlamaConfig.from_hf(cfg_json)
+    model = LlamaModel(backend, cfg_to_c(cfg))
+    model.upload_hf_tensors(tensors)
+    with pytest.raises(CaiError, match="finalize"):
+        StreamingDecoder(model, 16)
+    model.finalize()
+    sess = StreamingDecoder(model, 16)
+    try:
+        s = [int(t) for t in seqs[0]]
+        rows = []
+        for i, t in enumerate(s[:8]):
+            rows.append(sess.step_forward([t])[0][0].copy())
+        assert sess.cache_length() == 8
+        sess.snapshot()
+        for t in s[8:12]:
+            sess.step_forward([t])
+        sess.restore_snapshot()
+        assert sess.cache_length() == 8
+        again = sess.step_forward([s[8]])[0][0]
+        assert np.max(np.abs(again - gold[0][8])) < 1e-4
+        sess.truncate_to(5)
+        redo = sess.step_forward([s[5]])[0][0]
+        assert np.array_equal(redo, rows[5])            # same kernels, same inputs: bit-identical
+        with pytest.raises(CaiError):
+            sess.truncate_to(9)
+        with pytest.raises(CaiError, match="vocabulary"):
+            sess.step_forward([cfg.vocab])
+        sess.reset()
+        for i in range(16):
+            sess.step_forward([s[i]])
+        with pytest.raises(CaiError, match="context full"):
+            sess.step_forward([0])
+        # prefill + greedy loop == stepping by hand
+        sess.reset()
+        toks, _ = generate_tokens_streamed(sess, [s[:6]], 5)
+        sess.reset()
+        sess.prefill([s[:5]])
+        dev = sess.decode_greedy([s[5]], 5)
+        assert np.array_equal(toks, dev)
+    finally:
+        sess.close()
+        model.close()
+    with pytest.raises(CaiError, match="unknown tensor"):
+        m2 = LlamaModel(backend, cfg_to_c(cfg))
+        try:
+            m2.upload_tensor("model.layers.0.nope.weight", TYPE_F32, np.zeros(8, dtype=np.float32), 1, 8)
+        finally:
+            m2.close()
+
+
+def _read_model_into_oracle(model, cfg, arch):
+    """Reads every resident tensor back as GGUF blocks and builds the oracle from them, checking
+    on the way that the device dequantization of those blocks is bit-exact."""
+    H = cfg.hidden
+    names = ["model.embed_tokens.weight", "model.norm.weight"]
+    if not cfg.tie_embeddings:
+        names.append("lm_head.weight")
+    for l in range(cfg.layers):
+        p = "model.layers.%d." % l
+        names += [p + s for s in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_proj.weight",
+                                  "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+                                  "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")]
+        if cfg.qkv_bias:
+            names += [p + s for s in ("self_attn.q_proj.bias", "self_attn.k_proj.bias", "self_attn.v_proj.bias")]
+    tensors = {}
+    cap = cfg.vocab * (H // 32) * 34 + 64
+    for n in names:
+        buf, ty, rows, cols = model.read_tensor(n, cap)
+        nbytes = rows * codecs.block_bytes_per_row(ty, cols)
+        w = codecs.dequantize(ty, buf[:nbytes])
+        tensors[n] = w.reshape(rows, cols) if rows > 1 else w
+    return OracleModel.from_hf_tensors(cfg, tensors, interleave=False)
+
+
+@pytest.mark.parametrize("arch,ggml_type,layers,prompt_len,n_new", [
+    ("qwen2.5-0.5b", TYPE_Q8_0, 24, 128, 32),       # the CPU-runnable decode workload at full size
+    ("tinyllama-1.1b", TYPE_Q4_0, 4, 24, 8),        # Q4_0 path, depth cut for test time
+])
+def test_synthetic_architectures_match_the_oracle(backend, arch, ggml_type, layers, prompt_len, n_new):
+    kw = dict(ARCHS[arch])
+    kw["layers"] = layers
+    cfgc = make_config(**kw)
+    cfg = LlamaConfig(hidden=kw["hidden"], inter=kw["inter"], layers=layers, heads=kw["heads"], kv_heads=kw["kv_heads"],
+                      head_dim=kw["head_dim"], vocab=kw["vocab"], rms_eps=kw["rms_eps"], rope_theta=kw["rope_theta"],
+                      tie_embeddings=kw.get("tie_embeddings", False), qkv_bias=kw.get("qkv_bias", False))
+    model = LlamaModel(backend, cfgc)
+    model.init_synthetic(ggml_type, seed=0, std=0.02)
+    model.finalize()
+    # dequantized weights bit-exact: device dequant of one matrix == oracle dequant of its blocks
+    buf, ty, rows, cols = model.read_tensor("model.layers.0.mlp.down_proj.weight", kw["hidden"] * kw["inter"] * 2)
+    nbytes = rows * codecs.block_bytes_per_row(ty, cols)
+    dev = backend.dequantize(ty, buf[:nbytes], rows, cols)
+    assert np.array_equal(dev.view(np.uint32), codecs.dequantize(ty, buf[:nbytes]).view(np.uint32))
+    std = float(np.std(dev))
+    assert 0.015 < std < 0.025                       # N(0, 0.02) survives quantization
+    oracle = _read_model_into_oracle(model, cfg, arch)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, prompt_len)
+    ctx = prompt_len + n_new
+    sess = StreamingDecoder(model, ctx)
+    osess = OracleSession(oracle, ctx)
+    try:
+        sess.prefill([prompt[:-1]])
+        for i, t in enumerate(prompt[:-1]):
+            osess.step(int(t), i)
+        tok = int(prompt[-1])
+        worst = 0.0
+        gpu_tokens, ref_tokens = [], []
+        otok = tok
+        for _ in range(n_new):
+            logits, amax = sess.step_forward([tok])
+            ref = osess.step(otok)
+            rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+            if tok == otok:
+                worst = max(worst, float(np.max(np.abs(logits[0] - ref))) / rms)
+            tok, otok = int(amax[0]), argmax_first(ref)
+            gpu_tokens.append(tok)
+            ref_tokens.append(otok)
+        assert gpu_tokens == ref_tokens, (gpu_tokens, ref_tokens)
+        assert worst < 1e-3, worst
+    finally:
+        sess.close()
+        model.close()
