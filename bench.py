@@ -267,19 +267,73 @@ def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, 
     return res
 
 
+def run_linear(args):
+    """Isolated quantized linear: one resident [N, K] matrix per copy, enough distinct copies to exceed
+    the L2 cache, activations and outputs resident on the device. One step = one pass over every copy."""
+    from neural_api_b200.backend import CudaBackend, DotProductSharedKernel
+    k, n = (int(v) for v in args.kn.lower().split("x"))
+    ggml_type = {"q8_0": 8, "q4_0": 2}[args.type]
+    batch = args.batch or 1
+    backend = CudaBackend(0)
+    rng = np.random.default_rng(0)
+    nblk = n * k // 32
+    bb = 34 if ggml_type == 8 else 18
+    wbytes = nblk * bb
+    copies = max(2, int((300 << 20) // wbytes) + 1)
+    lins = []
+    for c in range(copies):
+        blk = rng.integers(0, 256, (nblk, bb), dtype=np.uint8)
+        blk[:, :2] = np.asarray(rng.uniform(0.001, 0.05, nblk), dtype=np.float16).view(np.uint8).reshape(-1, 2)
+        lin = DotProductSharedKernel(backend)
+        lin.prepare_for_compute_quant(ggml_type, blk.reshape(-1), n, k)
+        lins.append(lin)
+    x = backend.to_device(rng.standard_normal((batch, k)).astype(np.float32))
+    for _ in range(args.warmup):
+        for lin in lins:
+            lin.compute_quant(x, batch=batch)
+    backend.sync()
+    launches0 = backend.launch_count()
+    backend.timer_begin()
+    for _ in range(args.steps):
+        for lin in lins:
+            lin.compute_quant(x, batch=batch)
+    ms = backend.timer_end()
+    launches = backend.launch_count() - launches0
+    per_launch_ms = ms / (args.steps * copies)
+    alg_bytes = wbytes + 4 * batch * (k + n)
+    gbs = alg_bytes / (per_launch_ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    line = {"metric": "qgemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "isolated %s linear K=%d N=%d batch %d, %d weight copies (> L2)" % (args.type, k, n, batch, copies)},
+            "gpu_launches": launches, "us_per_launch": per_launch_ms * 1e3,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_kind": peak_kind,
+                         "traffic": None, "bytes_per_launch": alg_bytes}}
+    print(json.dumps(line))
+    for lin in lins:
+        lin.unprepare_for_compute()
+    backend.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kn", default="5120x27648", help="linear workload: KxN")
+    ap.add_argument("--type", default="q8_0", choices=["q8_0", "q4_0"], help="linear workload: block type")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="qwen2.5-32b", choices=sorted(WORKLOAD_DEFAULTS))
+    ap.add_argument("--workload", default="qwen2.5-32b", choices=sorted(WORKLOAD_DEFAULTS) + ["linear"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--no-extra", action="store_true", help="skip the Qwen2.5-0.5B side measurement and the CPU baseline")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "linear":
+        return run_linear(args)
     from neural_api_b200.configs import ARCHS
     from neural_api_b200 import parallel
     ggml_type, seed, batch, ctx = WORKLOAD_DEFAULTS[args.workload]

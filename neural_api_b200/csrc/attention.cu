@@ -129,7 +129,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[t][i] = 0.f;
     }
-    for (int j0 = j_begin + warp * kpw + kslot; j0 < j_end; j0 += key_stride * ATTN_KEYS) {
+    // The trip count depends on the warp only (not on the lane's key slot): every lane of a
+    // warp runs the same iterations, so the full-mask shuffles below are always converged.
+    for (int jb = j_begin + warp * kpw; jb < j_end; jb += key_stride * ATTN_KEYS) {
+      const int j0 = jb + kslot;
       float kv[ATTN_KEYS][8];
       bool valid[ATTN_KEYS];
 #pragma unroll

@@ -54,6 +54,7 @@ enum {
 
 struct LayerW {
   float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+  float* qkv_bias = nullptr;                  // [q | k | v] biases, owned here; wqkv.bias aliases it after finalize
   QWeight wqkv, wo, wgu, wdown, router;
   std::vector<QWeight> exp_gu, exp_down;
   std::vector<uint8_t> exp_have;              // bit 1 gate, 2 up, 4 down
@@ -113,6 +114,8 @@ static void layer_free(LayerW& L) {
   if (L.ffn_norm) cudaFree(L.ffn_norm);
   if (L.q_norm) cudaFree(L.q_norm);
   if (L.k_norm) cudaFree(L.k_norm);
+  if (L.qkv_bias) cudaFree(L.qkv_bias);
+  L.wqkv.bias = nullptr;
   qweight_free(&L.wqkv); qweight_free(&L.wo); qweight_free(&L.wgu); qweight_free(&L.wdown); qweight_free(&L.router);
   for (auto& w : L.exp_gu) qweight_free(&w);
   for (auto& w : L.exp_down) qweight_free(&w);
@@ -240,12 +243,11 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
     case T_QB: case T_KB: case T_VB: {
       const bool isq = t.kind == T_QB;
       NEED_VEC(isq ? QW : KW);
-      if (!L.wqkv.codes) return cai_fail(ctx, CAI_ERR_STATE, "'%s': upload the projection weight before its bias", hf_name);
-      CAI_TRY(ensure_vec(ctx, &L.wqkv.bias, qkv_rows, true));
+      CAI_TRY(ensure_vec(ctx, &L.qkv_bias, qkv_rows, true));
       const int64_t nloc = isq ? m->qw_l : m->kw_l;
       const int64_t dst0 = isq ? 0 : (t.kind == T_KB ? m->qw_l : m->qw_l + m->kw_l);
       L.have |= isq ? HAVE_QB : (t.kind == T_KB ? HAVE_KB : HAVE_VB);
-      return upload_vec(ctx, L.wqkv.bias + dst0, (const float*)data_host, isq ? QW : KW, (int64_t)r * nloc, nloc,
+      return upload_vec(ctx, L.qkv_bias + dst0, (const float*)data_host, isq ? QW : KW, (int64_t)r * nloc, nloc,
                         t.kind == T_VB ? 0 : interleave_head_dim);
     }
     case T_O: {
@@ -348,10 +350,10 @@ int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std) {
       L.have |= HAVE_Q | HAVE_K | HAVE_V;
     }
     if (c.qkv_bias) {
-      CAI_TRY(ensure_vec(ctx, &L.wqkv.bias, m->qw_l + 2 * m->kw_l, true));
-      CAI_TRY(vec_init_synthetic(ctx, L.wqkv.bias, m->qw_l, seed, tid + 3, std, (int64_t)r * m->qw_l, 0.f));
-      CAI_TRY(vec_init_synthetic(ctx, L.wqkv.bias + m->qw_l, m->kw_l, seed, tid + 4, std, (int64_t)r * m->kw_l, 0.f));
-      CAI_TRY(vec_init_synthetic(ctx, L.wqkv.bias + m->qw_l + m->kw_l, m->kw_l, seed, tid + 5, std, (int64_t)r * m->kw_l, 0.f));
+      CAI_TRY(ensure_vec(ctx, &L.qkv_bias, m->qw_l + 2 * m->kw_l, true));
+      CAI_TRY(vec_init_synthetic(ctx, L.qkv_bias, m->qw_l, seed, tid + 3, std, (int64_t)r * m->qw_l, 0.f));
+      CAI_TRY(vec_init_synthetic(ctx, L.qkv_bias + m->qw_l, m->kw_l, seed, tid + 4, std, (int64_t)r * m->kw_l, 0.f));
+      CAI_TRY(vec_init_synthetic(ctx, L.qkv_bias + m->qw_l + m->kw_l, m->kw_l, seed, tid + 5, std, (int64_t)r * m->kw_l, 0.f));
       L.have |= HAVE_QB | HAVE_KB | HAVE_VB;
     }
     if (c.qk_norm) {
@@ -418,9 +420,9 @@ static int locate_tensor(cai_model* m, const char* hf_name, QWeight* out_view, c
     case T_Q: *out_view = qweight_rows_view(L.wqkv, 0, m->qw_l); return CAI_OK;
     case T_K: *out_view = qweight_rows_view(L.wqkv, m->qw_l, m->kw_l); return CAI_OK;
     case T_V: *out_view = qweight_rows_view(L.wqkv, m->qw_l + m->kw_l, m->kw_l); return CAI_OK;
-    case T_QB: *out_vec = L.wqkv.bias; *out_vec_len = m->qw_l; return CAI_OK;
-    case T_KB: *out_vec = L.wqkv.bias ? L.wqkv.bias + m->qw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
-    case T_VB: *out_vec = L.wqkv.bias ? L.wqkv.bias + m->qw_l + m->kw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
+    case T_QB: *out_vec = L.qkv_bias; *out_vec_len = m->qw_l; return CAI_OK;
+    case T_KB: *out_vec = L.qkv_bias ? L.qkv_bias + m->qw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
+    case T_VB: *out_vec = L.qkv_bias ? L.qkv_bias + m->qw_l + m->kw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
     case T_O: *out_view = qweight_rows_view(L.wo, 0, L.wo.n); return CAI_OK;
     case T_UP: *out_view = qweight_rows_view(L.wgu, 0, m->inter_l); return CAI_OK;
     case T_GATE: *out_view = qweight_rows_view(L.wgu, m->inter_l, m->inter_l); return CAI_OK;
@@ -492,6 +494,7 @@ int cai_model_finalize(cai_model* m) {
     if (c.qk_norm) need |= HAVE_QNORM | HAVE_KNORM;
     if (c.n_experts) need |= HAVE_ROUTER; else need |= HAVE_GATE | HAVE_UP | HAVE_DOWN;
     if ((L.have & need) != need) return cai_fail(ctx, CAI_ERR_STATE, "layer %d is missing tensors (have mask 0x%x, need 0x%x)", l, L.have, need);
+    L.wqkv.bias = L.qkv_bias;     // alias; freed through qkv_bias
     if (c.n_experts) {
       std::vector<const void*> gc, gs, dc, ds;
       for (int e = 0; e < c.n_experts; ++e) {
