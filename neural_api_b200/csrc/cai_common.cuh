@@ -81,7 +81,7 @@ int cai_ensure_staging(cai_ctx* ctx, size_t bytes);
 // that rows of codes start on 16-byte boundaries (a 34-byte Q8_0 block does
 // not): values stay bit-identical, d * q is formed in fp32 exactly as
 // DecodeGGMLSpan does.
-//   Q8_0: codes int8  [N][K],      scales fp16 [N][K/32]
+//   Q8_0: codes int8  [N][K],      scales fp16 [N][sstride], sstride = K/32 rounded up to 8
 //   Q4_0: codes uint8 [N][K/2] (the 16 nibble bytes of each block kept together),
 //         scales fp16 [N][K/32]
 //   F16 : codes fp16  [N][K];  F32: codes float [N][K]
@@ -89,13 +89,15 @@ int cai_ensure_staging(cai_ctx* ctx, size_t bytes);
 struct QWeight {
   int type = -1;
   int64_t n = 0, k = 0;
+  int64_t sstride = 0;         // halves between scale rows: K/32 rounded up to 8
   void* codes = nullptr;
   __half* scales = nullptr;
   float* bias = nullptr;       // optional, N floats
   bool owns = true;            // false for row-range views (tied LM head shard)
   bool present = false;
   size_t code_bytes() const;
-  size_t scale_bytes() const;
+  size_t scale_bytes() const;         // algorithmic (unpadded) bytes
+  size_t scale_alloc_bytes() const;   // resident bytes, rows padded to sstride
   size_t bytes() const { return code_bytes() + scale_bytes(); }
   size_t row_code_bytes() const;
 };

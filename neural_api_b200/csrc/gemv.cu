@@ -5,101 +5,22 @@
 //
 // The sum is formed per 32-block as d * (sum code*x) in fp32: one multiply by the
 // block scale per 16 codes instead of one per code. Codes become floats exactly
-// (integer -> float through the 2^23 magic constant), accumulation is fp32, the
-// reduction order is fixed (no atomics), so results are reproducible run to run.
+// (integer -> float through the 2^23 constant), accumulation is fp32 in packed
+// fp32x2 instructions, the reduction order is fixed (no atomics), so results are
+// reproducible run to run.
 //
 // Work split: a warp owns RPW output rows and walks K in 512-code (Q8_0) or
-// 1024-code (Q4_0) strides, one 16-byte vector load per lane per row; KSPLIT warps
-// of a CTA may share the same rows (small-N / large-K shapes) and are combined in
-// shared memory in a fixed order.
-#include "cai_common.cuh"
+// 1024-code (Q4_0) strides, one 16-byte streaming load per lane per row, the next
+// stride's loads issued before the current one is consumed; KSPLIT warps of a CTA
+// may share the same rows (small-N / large-K shapes) and are combined in shared
+// memory in a fixed order. Activations are staged once per CTA in shared memory
+// when they fit.
+#include "gemv_common.cuh"
 #include <stdlib.h>
-
-struct GemvParams {
-  const void* codes;
-  const __half* scales;
-  const float* bias;
-  const float* x;
-  int64_t ldx;
-  float* y;
-  int64_t ldy;
-  const float* resid;
-  int64_t n;        // weight rows
-  int64_t k;
-  int batch;
-  int act;
-  int epi;
-  int ksplit;       // warps cooperating on one row group
-  // indexed (expert bank) mode
-  const void* const* bank_codes;
-  const __half* const* bank_scales;
-  const int32_t* expert_ids;
-  int x_row_div;
-  const float* row_scale;
-};
-
-__device__ __forceinline__ float apply_act(float v, int act) {
-  if (act == CAI_ACT_RELU) return v > 0.f ? v : 0.f;
-  if (act == CAI_ACT_SIGMOID) {
-    if (v > 0.f) return 1.0f / (1.0f + expf(-v));
-    const float s = expf(v);
-    return s / (1.0f + s);
-  }
-  if (act == CAI_ACT_TANH) return tanhf(v);
-  return v;
-}
-// swish(b) = b * sigmoid(b), two-branch form: exp never overflows.
-__device__ __forceinline__ float swish(float b) {
-  float sig;
-  if (b > 0.f) sig = 1.0f / (1.0f + expf(-b));
-  else { const float s = expf(b); sig = s / (1.0f + s); }
-  return b * sig;
-}
-
-// Writes the outputs of one row group. acc[r][b] are complete sums held by every
-// lane; lane `r*NB + b` (mod 32) does the store.
-template <int NB, int RPW>
-__device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const float (&acc)[RPW][NB], int64_t unit0,
-                                              int b0, int pair, const float* bias) {
-  const int lane = threadIdx.x & 31;
-  if (p.epi == EPI_SWIGLU) {
-    const int64_t half = p.n >> 1;
-#pragma unroll
-    for (int r = 0; r < RPW; r += 2) {
-      const int64_t j = unit0 + (r >> 1);
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        if (lane == ((r * NB + b) & 31) && j < half && (b0 + b) < p.batch) {
-          float up = acc[r][b], gate = acc[r + 1][b];
-          if (bias) { up += bias[j]; gate += bias[half + j]; }
-          const int64_t yrow = p.expert_ids ? pair : (b0 + b);
-          p.y[yrow * p.ldy + j] = up * swish(gate);
-        }
-      }
-    }
-    return;
-  }
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    const int64_t row = unit0 + r;
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      if (lane == ((r * NB + b) & 31) && row < p.n && (b0 + b) < p.batch) {
-        float v = acc[r][b];
-        if (bias) v += bias[row];
-        v = apply_act(v, p.act);
-        const int64_t yrow = p.expert_ids ? pair : (b0 + b);
-        if (p.row_scale) v *= p.row_scale[yrow];
-        if (p.epi == EPI_RESID) v += p.resid[yrow * p.ldy + row];
-        p.y[yrow * p.ldy + row] = v;
-      }
-    }
-  }
-}
 
 template <int TYPE, int NB, int RPW>
 __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
-  extern __shared__ float smem_red[];
+  extern __shared__ __align__(16) float smem_f[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps_per_cta = blockDim.x >> 5;
@@ -125,6 +46,25 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
   } else {
     x = p.x + (int64_t)b0 * p.ldx;
   }
+  const int64_t K = p.k;
+
+  // activations -> shared memory (rows beyond the batch repeat row 0 and are never stored)
+  const float* xr[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) xr[b] = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
+  float* red = smem_f;
+  if (p.x_in_smem) {
+    for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
+      const int b = (int)(i / K);
+      const int64_t c = i - (int64_t)b * K;
+      const int bb = (b0 + b < p.batch) ? b : 0;
+      *(float4*)(smem_f + i) = __ldg((const float4*)(x + (int64_t)bb * p.ldx + c));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int b = 0; b < NB; ++b) xr[b] = smem_f + (int64_t)b * K;
+    red = smem_f + (int64_t)NB * K;
+  }
 
   // rows of this warp
   const int64_t gidx = (int64_t)blockIdx.x * groups_per_cta + group;
@@ -149,122 +89,92 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
     }
   }
 
-  float acc[RPW][NB];
+  f32x2_t acc2[RPW][NB];
 #pragma unroll
   for (int r = 0; r < RPW; ++r)
 #pragma unroll
-    for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
+    for (int b = 0; b < NB; ++b) acc2[r][b] = 0ull;
 
-  const int64_t K = p.k;
-  const int64_t bpr = K / CAI_QK;
+  // codes per lane chunk (one 16-byte load) and per warp stride
+  constexpr int CHUNK = (TYPE == CAI_TYPE_Q8_0) ? 16 : 32;
+  constexpr int CODE_SHIFT = (TYPE == CAI_TYPE_Q8_0) ? 0 : 1;     // bytes = codes >> shift
+  const int64_t row_bytes = K >> CODE_SHIFT;
+  const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
+  int64_t k0 = ((int64_t)kpart * 32 + lane) * CHUNK;
 
-  if (TYPE == CAI_TYPE_Q8_0) {
-    // lane chunk: 16 codes = one 16-byte load; two lanes share a block scale
-    const int64_t stride = (int64_t)p.ksplit * 512;
-#pragma unroll 2
-    for (int64_t k0 = ((int64_t)kpart * 32 + lane) * 16; k0 < K; k0 += stride) {
-      int4 wv[RPW];
-      float d[RPW];
+  int4 wv[RPW], wn[RPW];
+  uint32_t sv[RPW], sn[RPW];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) { wn[r] = make_int4(0, 0, 0, 0); sn[r] = 0; }
+  if (k0 < K) {
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      wn[r] = ldg_stream16(codes + rows[r] * row_bytes + (k0 >> CODE_SHIFT));
+      sn[r] = __ldg((const unsigned short*)scales + rows[r] * p.sstride + (k0 >> 5));
+    }
+  }
+  for (; k0 < K; k0 += stride) {
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) { wv[r] = wn[r]; sv[r] = sn[r]; }
+    const int64_t k1 = k0 + stride;
+    if (k1 < K) {
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        wv[r] = __ldg((const int4*)(codes + rows[r] * K + k0));
-        d[r] = __half2float(scales[rows[r] * bpr + (k0 >> 5)]);
+        wn[r] = ldg_stream16(codes + rows[r] * row_bytes + (k1 >> CODE_SHIFT));
+        sn[r] = __ldg((const unsigned short*)scales + rows[r] * p.sstride + (k1 >> 5));
       }
-      float part[RPW][NB];
+    }
+    f32x2_t part[RPW][NB];
 #pragma unroll
-      for (int r = 0; r < RPW; ++r)
+    for (int r = 0; r < RPW; ++r)
 #pragma unroll
-        for (int b = 0; b < NB; ++b) part[r][b] = 0.f;
+      for (int b = 0; b < NB; ++b) part[r][b] = 0ull;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 4; ++i) {
+      if (TYPE == CAI_TYPE_Q8_0) {
         float4 xv[NB];
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          const int bb = (b0 + b < p.batch) ? b : 0;
-          xv[b] = __ldg((const float4*)(x + (int64_t)bb * p.ldx + k0 + 4 * i));
-        }
+        for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + k0 + 4 * i);
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
-          const uint32_t w = ((const uint32_t*)&wv[r])[i] ^ 0x80808080u;
-          const float f0 = biased_byte_to_float(w, 0), f1 = biased_byte_to_float(w, 1);
-          const float f2 = biased_byte_to_float(w, 2), f3 = biased_byte_to_float(w, 3);
+          const uint32_t w = ((const uint32_t*)&wv[r])[i];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            float s = part[r][b];
-            s = fmaf(f0, xv[b].x, s); s = fmaf(f1, xv[b].y, s);
-            s = fmaf(f2, xv[b].z, s); s = fmaf(f3, xv[b].w, s);
-            part[r][b] = s;
-          }
+          for (int b = 0; b < NB; ++b) part[r][b] = q8_word_fma(w, xv[b], part[r][b]);
         }
-      }
-#pragma unroll
-      for (int r = 0; r < RPW; ++r)
-#pragma unroll
-        for (int b = 0; b < NB; ++b) acc[r][b] = fmaf(d[r], part[r][b], acc[r][b]);
-    }
-  } else {
-    // Q4_0: lane chunk = one whole block (16 bytes = 32 nibbles). Byte e carries
-    // element e (low nibble) and element e+16 (high nibble).
-    const int64_t stride = (int64_t)p.ksplit * 1024;
-    const int64_t row_bytes = K >> 1;
-#pragma unroll 2
-    for (int64_t k0 = ((int64_t)kpart * 32 + lane) * 32; k0 < K; k0 += stride) {
-      int4 wv[RPW];
-      float d[RPW];
-#pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        wv[r] = __ldg((const int4*)(codes + rows[r] * row_bytes + (k0 >> 1)));
-        d[r] = __half2float(scales[rows[r] * bpr + (k0 >> 5)]);
-      }
-      float part[RPW][NB];
-#pragma unroll
-      for (int r = 0; r < RPW; ++r)
-#pragma unroll
-        for (int b = 0; b < NB; ++b) part[r][b] = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      } else {
         float4 xlo[NB], xhi[NB];
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          const int bb = (b0 + b < p.batch) ? b : 0;
-          xlo[b] = __ldg((const float4*)(x + (int64_t)bb * p.ldx + k0 + 4 * i));
-          xhi[b] = __ldg((const float4*)(x + (int64_t)bb * p.ldx + k0 + 16 + 4 * i));
+          xlo[b] = *(const float4*)(xr[b] + k0 + 4 * i);
+          xhi[b] = *(const float4*)(xr[b] + k0 + 16 + 4 * i);
         }
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
           const uint32_t w = ((const uint32_t*)&wv[r])[i];
-          const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-          const float l0 = ubyte_to_float(lo, 0, 8388616.0f), l1 = ubyte_to_float(lo, 1, 8388616.0f);
-          const float l2 = ubyte_to_float(lo, 2, 8388616.0f), l3 = ubyte_to_float(lo, 3, 8388616.0f);
-          const float h0 = ubyte_to_float(hi, 0, 8388616.0f), h1 = ubyte_to_float(hi, 1, 8388616.0f);
-          const float h2 = ubyte_to_float(hi, 2, 8388616.0f), h3 = ubyte_to_float(hi, 3, 8388616.0f);
 #pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            float s = part[r][b];
-            s = fmaf(l0, xlo[b].x, s); s = fmaf(l1, xlo[b].y, s);
-            s = fmaf(l2, xlo[b].z, s); s = fmaf(l3, xlo[b].w, s);
-            s = fmaf(h0, xhi[b].x, s); s = fmaf(h1, xhi[b].y, s);
-            s = fmaf(h2, xhi[b].z, s); s = fmaf(h3, xhi[b].w, s);
-            part[r][b] = s;
-          }
+          for (int b = 0; b < NB; ++b) part[r][b] = q4_word_fma(w, xlo[b], xhi[b], part[r][b]);
         }
       }
+    }
 #pragma unroll
-      for (int r = 0; r < RPW; ++r)
+    for (int r = 0; r < RPW; ++r) {
+      const float d = half_bits_to_float(sv[r]);
+      const f32x2_t d2 = pack2(d, d);
 #pragma unroll
-        for (int b = 0; b < NB; ++b) acc[r][b] = fmaf(d[r], part[r][b], acc[r][b]);
+      for (int b = 0; b < NB; ++b) acc2[r][b] = fma2(d2, part[r][b], acc2[r][b]);
     }
   }
 
   // lanes -> one value per (row, batch)
+  float acc[RPW][NB];
 #pragma unroll
   for (int r = 0; r < RPW; ++r)
 #pragma unroll
-    for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(acc[r][b]);
+    for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(sum2(acc2[r][b]));
 
   if (p.ksplit > 1) {
     // fixed-order combine of the KSPLIT warps of a group through shared memory
-    float* slot = smem_red + (size_t)warp * (RPW * NB);
+    float* slot = red + (size_t)warp * (RPW * NB);
     if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < RPW; ++r)
@@ -278,7 +188,7 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         float s = 0.f;
-        for (int q = 0; q < p.ksplit; ++q) s += smem_red[(size_t)(group * p.ksplit + q) * (RPW * NB) + r * NB + b];
+        for (int q = 0; q < p.ksplit; ++q) s += red[(size_t)(group * p.ksplit + q) * (RPW * NB) + r * NB + b];
         acc[r][b] = s;
       }
   }
@@ -347,18 +257,27 @@ static int env_int(const char* name, int dflt) {
   return (s && *s) ? atoi(s) : dflt;
 }
 
+template <int TYPE, int NB, int RPW>
+static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  gemv_quant_kernel<TYPE, NB, RPW><<<grid, threads, smem, ctx->stream>>>(p);
+  return cudaSuccess;
+}
 template <int TYPE, int NB>
-static void launch_quant(cai_ctx* ctx, const GemvParams& p, int rpw, dim3 grid, int threads, size_t smem) {
-  if (rpw == 4) gemv_quant_kernel<TYPE, NB, 4><<<grid, threads, smem, ctx->stream>>>(p);
-  else if (rpw == 2) gemv_quant_kernel<TYPE, NB, 2><<<grid, threads, smem, ctx->stream>>>(p);
-  else gemv_quant_kernel<TYPE, NB, 1><<<grid, threads, smem, ctx->stream>>>(p);
+static cudaError_t launch_quant(cai_ctx* ctx, const GemvParams& p, int rpw, dim3 grid, int threads, size_t smem) {
+  if (rpw == 4) return launch_one<TYPE, NB, 4>(ctx, p, grid, threads, smem);
+  if (rpw == 2) return launch_one<TYPE, NB, 2>(ctx, p, grid, threads, smem);
+  return launch_one<TYPE, NB, 1>(ctx, p, grid, threads, smem);
 }
 template <int TYPE>
-static void launch_quant_nb(cai_ctx* ctx, const GemvParams& p, int nb, int rpw, dim3 grid, int threads, size_t smem) {
-  if (nb == 1) launch_quant<TYPE, 1>(ctx, p, rpw, grid, threads, smem);
-  else if (nb == 2) launch_quant<TYPE, 2>(ctx, p, rpw, grid, threads, smem);
-  else if (nb == 4) launch_quant<TYPE, 4>(ctx, p, rpw, grid, threads, smem);
-  else launch_quant<TYPE, 8>(ctx, p, rpw, grid, threads, smem);
+static cudaError_t launch_quant_nb(cai_ctx* ctx, const GemvParams& p, int nb, int rpw, dim3 grid, int threads, size_t smem) {
+  if (nb == 1) return launch_quant<TYPE, 1>(ctx, p, rpw, grid, threads, smem);
+  if (nb == 2) return launch_quant<TYPE, 2>(ctx, p, rpw, grid, threads, smem);
+  if (nb == 4) return launch_quant<TYPE, 4>(ctx, p, rpw, grid, threads, smem);
+  return launch_quant<TYPE, 8>(ctx, p, rpw, grid, threads, smem);
 }
 
 int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
@@ -370,9 +289,10 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   if (a.epilogue == EPI_RESID && !a.resid) return cai_fail(ctx, CAI_ERR_INVALID, "residual epilogue without residual");
   const bool indexed = a.expert_ids_dev != nullptr;
   GemvParams p;
+  memset(&p, 0, sizeof(p));
   p.codes = w->codes; p.scales = w->scales; p.bias = w->bias;
   p.x = a.x; p.ldx = a.ldx; p.y = a.y; p.ldy = a.ldy; p.resid = a.resid;
-  p.n = w->n; p.k = w->k; p.batch = a.batch; p.act = a.act; p.epi = a.epilogue;
+  p.n = w->n; p.k = w->k; p.sstride = w->sstride; p.batch = a.batch; p.act = a.act; p.epi = a.epilogue;
   p.bank_codes = a.bank_codes_dev; p.bank_scales = a.bank_scales_dev; p.expert_ids = a.expert_ids_dev;
   p.x_row_div = a.x_row_div < 1 ? 1 : a.x_row_div; p.row_scale = a.row_scale_dev;
   p.ksplit = 1;
@@ -393,18 +313,19 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   // batch tile
   int nb = 1;
   if (!indexed) nb = a.batch >= 5 ? 8 : (a.batch >= 3 ? 4 : (a.batch == 2 ? 2 : 1));
-  // rows per warp / warps per row group: enough 16-byte loads in flight per SM without
-  // leaving SMs idle on small matrices
+  // Rows per warp / warps per row group: every CTA of the launch should be resident at once (one wave)
+  // with as many 16-byte loads in flight as possible; small-N / large-K shapes split K over the warps of a CTA.
   const int64_t lane_chunk = (w->type == CAI_TYPE_Q8_0) ? 16 : 32;
-  const int64_t k_iters_1 = (w->k + lane_chunk * 32 - 1) / (lane_chunk * 32);   // iterations of one warp alone
+  const int64_t k_iters_1 = (w->k + lane_chunk * 32 - 1) / (lane_chunk * 32);   // strides of one warp alone
   int rpw, ksplit;
   const int64_t target_groups = (int64_t)ctx->sm_count * 16;   // warps' worth of row groups for a full machine
   if (units >= target_groups * 4) rpw = 4;
-  else if (units >= target_groups * 2) rpw = 2;
+  else if (units >= target_groups) rpw = 2;
   else rpw = (a.epilogue == EPI_SWIGLU) ? 2 : 1;
-  if (nb == 8 && rpw == 4) rpw = 2;
+  if (nb >= 4 && rpw == 4) rpw = 2;
   {
-    const int64_t groups = (units + ((a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw) - 1) / ((a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw);
+    const int upg = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;
+    const int64_t groups = (units + upg - 1) / upg;
     ksplit = 1;
     while (ksplit < 8 && groups * ksplit < target_groups && k_iters_1 >= 2 * ksplit) ksplit *= 2;
   }
@@ -412,6 +333,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   ksplit = env_int("CAI_GEMV_KSPLIT", ksplit);
   if (rpw != 1 && rpw != 2 && rpw != 4) rpw = 2;
   if (a.epilogue == EPI_SWIGLU && rpw == 1) rpw = 2;
+  if (nb == 8 && rpw == 4) rpw = 2;
   if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) ksplit = 1;
   p.ksplit = ksplit;
   const int threads = 256;
@@ -420,9 +342,14 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   const int units_per_group = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;
   const int64_t groups = (units + units_per_group - 1) / units_per_group;
   dim3 grid((unsigned)((groups + groups_per_cta - 1) / groups_per_cta), indexed ? a.batch : (unsigned)((a.batch + nb - 1) / nb));
-  const size_t smem = (ksplit > 1) ? (size_t)wpc * rpw * nb * sizeof(float) : 0;
-  if (w->type == CAI_TYPE_Q8_0) launch_quant_nb<CAI_TYPE_Q8_0>(ctx, p, nb, rpw, grid, threads, smem);
-  else launch_quant_nb<CAI_TYPE_Q4_0>(ctx, p, nb, rpw, grid, threads, smem);
+  // activations in shared memory when they fit beside a healthy number of resident CTAs
+  const size_t x_bytes = (size_t)nb * (size_t)w->k * 4;
+  p.x_in_smem = (x_bytes <= (size_t)env_int("CAI_GEMV_XSMEM", 64 * 1024)) ? 1 : 0;
+  const size_t smem = (p.x_in_smem ? x_bytes : 0) + ((ksplit > 1) ? (size_t)wpc * rpw * nb * sizeof(float) : 0);
+  cudaError_t e;
+  if (w->type == CAI_TYPE_Q8_0) e = launch_quant_nb<CAI_TYPE_Q8_0>(ctx, p, nb, rpw, grid, threads, smem);
+  else e = launch_quant_nb<CAI_TYPE_Q4_0>(ctx, p, nb, rpw, grid, threads, smem);
+  if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "gemv launch setup -> %s", cudaGetErrorString(e));
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

@@ -1,0 +1,158 @@
+// Pieces shared by the quantized GEMV kernels: launch parameters, the exact
+// code -> float conversion with packed fp32x2 arithmetic, and the epilogue.
+#pragma once
+#include "cai_common.cuh"
+
+struct GemvParams {
+  const void* codes;
+  const __half* scales;
+  const float* bias;
+  const float* x;
+  int64_t ldx;
+  float* y;
+  int64_t ldy;
+  const float* resid;
+  int64_t n;        // weight rows
+  int64_t k;
+  int64_t sstride;  // halves between scale rows
+  int batch;
+  int act;
+  int epi;
+  int ksplit;       // warps cooperating on one row group
+  int x_in_smem;    // activations staged in shared memory by the CTA
+  // indexed (expert bank) mode
+  const void* const* bank_codes;
+  const __half* const* bank_scales;
+  const int32_t* expert_ids;
+  int x_row_div;
+  const float* row_scale;
+  int* err_flag;    // set by a kernel whose bounded wait ran out
+};
+
+typedef unsigned long long f32x2_t;   // two packed floats in one 64-bit register
+
+__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
+  f32x2_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ float sum2(f32x2_t v) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return lo + hi;
+}
+// Blackwell packed fp32: two IEEE fp32 operations per instruction (round to nearest even,
+// identical results to two scalar operations).
+__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b) {
+  f32x2_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// fp16 bit pattern -> float, exact for zero, subnormal and normal halves: the exponent/mantissa
+// bits are placed in an fp32 pattern that is 2^-112 times the value, then scaled back by an exact
+// power of two. Inf/NaN patterns take the conversion instruction.
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) {
+  if ((h & 0x7C00u) == 0x7C00u) return __half2float(__ushort_as_half((unsigned short)h));
+  const uint32_t bits = ((h & 0x8000u) << 16) | ((h & 0x7FFFu) << 13);
+  return __uint_as_float(bits) * __uint_as_float(0x77800000u);   // * 2^112
+}
+
+// Streaming 16-byte load of weight codes: read-only path, no L1 allocation (each byte is used once).
+__device__ __forceinline__ int4 ldg_stream16(const void* ptr) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+
+// 4 int8 codes of one 32-bit word times 4 activations, accumulated into a packed pair.
+// (0x4B000000 | (code ^ 0x80)) is the float 2^23 + code + 128; adding -(2^23 + 128) leaves the code exactly.
+__device__ __forceinline__ f32x2_t q8_word_fma(uint32_t w, const float4& x, f32x2_t acc) {
+  w ^= 0x80808080u;
+  const f32x2_t negc = pack2(-8388736.0f, -8388736.0f);
+  const f32x2_t f01 = pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7651u)));
+  const f32x2_t f23 = pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7653u)));
+  acc = fma2(add2(f01, negc), pack2(x.x, x.y), acc);
+  acc = fma2(add2(f23, negc), pack2(x.z, x.w), acc);
+  return acc;
+}
+// 8 nibbles of one 32-bit word of a Q4_0 block: byte e of the block holds element e (low nibble)
+// and element e+16 (high nibble); xlo/xhi are the activations of the two element groups.
+__device__ __forceinline__ f32x2_t q4_word_fma(uint32_t w, const float4& xlo, const float4& xhi, f32x2_t acc) {
+  const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+  const f32x2_t negc = pack2(-8388616.0f, -8388616.0f);   // -(2^23 + 8)
+  const f32x2_t l01 = pack2(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7651u)));
+  const f32x2_t l23 = pack2(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7653u)));
+  const f32x2_t h01 = pack2(__uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7651u)));
+  const f32x2_t h23 = pack2(__uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7653u)));
+  acc = fma2(add2(l01, negc), pack2(xlo.x, xlo.y), acc);
+  acc = fma2(add2(l23, negc), pack2(xlo.z, xlo.w), acc);
+  acc = fma2(add2(h01, negc), pack2(xhi.x, xhi.y), acc);
+  acc = fma2(add2(h23, negc), pack2(xhi.z, xhi.w), acc);
+  return acc;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == CAI_ACT_RELU) return v > 0.f ? v : 0.f;
+  if (act == CAI_ACT_SIGMOID) {
+    if (v > 0.f) return 1.0f / (1.0f + expf(-v));
+    const float s = expf(v);
+    return s / (1.0f + s);
+  }
+  if (act == CAI_ACT_TANH) return tanhf(v);
+  return v;
+}
+// swish(b) = b * sigmoid(b), two-branch form: exp never overflows.
+__device__ __forceinline__ float swish(float b) {
+  float sig;
+  if (b > 0.f) sig = 1.0f / (1.0f + expf(-b));
+  else { const float s = expf(b); sig = s / (1.0f + s); }
+  return b * sig;
+}
+
+// Writes the outputs of one row group. acc[r][b] are complete sums held by every
+// lane; lane `r*NB + b` (mod 32) does the store.
+template <int NB, int RPW>
+__device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const float (&acc)[RPW][NB], int64_t unit0,
+                                              int b0, int pair, const float* bias) {
+  const int lane = threadIdx.x & 31;
+  if (p.epi == EPI_SWIGLU) {
+    const int64_t half = p.n >> 1;
+#pragma unroll
+    for (int r = 0; r + 1 < RPW; r += 2) {
+      const int64_t j = unit0 + (r >> 1);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        if (lane == ((r * NB + b) & 31) && j < half && (b0 + b) < p.batch) {
+          float up = acc[r][b], gate = acc[r + 1][b];
+          if (bias) { up += bias[j]; gate += bias[half + j]; }
+          const int64_t yrow = p.expert_ids ? pair : (b0 + b);
+          p.y[yrow * p.ldy + j] = up * swish(gate);
+        }
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    const int64_t row = unit0 + r;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      if (lane == ((r * NB + b) & 31) && row < p.n && (b0 + b) < p.batch) {
+        float v = acc[r][b];
+        if (bias) v += bias[row];
+        v = apply_act(v, p.act);
+        const int64_t yrow = p.expert_ids ? pair : (b0 + b);
+        if (p.row_scale) v *= p.row_scale[yrow];
+        if (p.epi == EPI_RESID) v += p.resid[yrow * p.ldy + row];
+        p.y[yrow * p.ldy + row] = v;
+      }
+    }
+  }
+}

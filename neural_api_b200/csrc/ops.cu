@@ -8,7 +8,7 @@
 // token 0 is a real row)
 // ---------------------------------------------------------------------------
 __global__ void embed_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
-                             int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld) {
+                             int64_t sstride, int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld) {
   const int b = blockIdx.x;
   int64_t tok = tokens[b];
   if (tok < 0) tok = 0;
@@ -16,13 +16,13 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
   for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
     float v;
     const int64_t i = tok * k + c;
-    if (type == CAI_TYPE_Q8_0) v = __half2float(scales[i / CAI_QK]) * (float)((const int8_t*)codes)[i];
+    if (type == CAI_TYPE_Q8_0) v = __half2float(scales[tok * sstride + c / CAI_QK]) * (float)((const int8_t*)codes)[i];
     else if (type == CAI_TYPE_Q4_0) {
       const int64_t blk = i / CAI_QK;
       const int e = (int)(i % CAI_QK);
       const uint8_t byte = ((const uint8_t*)codes)[blk * 16 + (e & 15)];
       const int nib = (e < 16) ? (byte & 0x0F) : (byte >> 4);
-      v = __half2float(scales[blk]) * (float)(nib - 8);
+      v = __half2float(scales[tok * sstride + c / CAI_QK]) * (float)(nib - 8);
     } else if (type == CAI_TYPE_F16) v = __half2float(((const __half*)codes)[i]);
     else v = ((const float*)codes)[i];
     out[(int64_t)b * ld + c] = v;
@@ -31,7 +31,7 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
 
 int op_embed(cai_ctx* ctx, const QWeight* t, const int32_t* tokens_dev, int batch, float* out, int64_t ld) {
   ctx->cur_family = FAM_OTHER;
-  embed_kernel<<<batch, 256, 0, ctx->stream>>>(t->type, t->codes, t->scales, t->k, t->n, tokens_dev, out, ld);
+  embed_kernel<<<batch, 256, 0, ctx->stream>>>(t->type, t->codes, t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

@@ -29,6 +29,10 @@ size_t QWeight::scale_bytes() const {
   if (type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0) return (size_t)n * (size_t)(k / CAI_QK) * 2;
   return 0;
 }
+size_t QWeight::scale_alloc_bytes() const {
+  if (type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0) return (size_t)n * (size_t)sstride * 2;
+  return 0;
+}
 
 int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
   if (!cai_type_supported(type)) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "tensor type %d is not supported (F32, F16, Q4_0, Q8_0)", type);
@@ -37,15 +41,18 @@ int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
     return cai_fail(ctx, CAI_ERR_INVALID, "quantized rows need a multiple of 32 columns, got %lld", (long long)k);
   qweight_free(w);
   w->type = type; w->n = n; w->k = k; w->owns = true; w->present = false;
-  size_t cb = w->code_bytes(), sb = w->scale_bytes();
+  // scale rows padded to 8 halves so that every row (and every 256-column tile of it) starts on a
+  // 16-byte boundary, which the bulk-copy (TMA) loads of the GEMV need
+  w->sstride = ((k / CAI_QK) + 7) / 8 * 8;
+  size_t cb = w->code_bytes(), sb = w->scale_alloc_bytes();
   size_t free_b = 0, total_b = 0;
   cudaMemGetInfo(&free_b, &total_b);
   if (cb + sb + (64u << 20) > free_b)
     return cai_fail(ctx, CAI_ERR_OOM, "weight of %zu bytes does not fit in %zu free device bytes", cb + sb, free_b);
   // +16 bytes of slack so that 16-byte vector loads of a row tail never leave the allocation
-  if (cudaMalloc(&w->codes, cb + 16) != cudaSuccess) { cudaGetLastError(); return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%zu) failed", cb); }
+  if (cudaMalloc(&w->codes, cb + 64) != cudaSuccess) { cudaGetLastError(); return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%zu) failed", cb); }
   if (sb) {
-    if (cudaMalloc((void**)&w->scales, sb + 16) != cudaSuccess) { cudaGetLastError(); cudaFree(w->codes); w->codes = nullptr; return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%zu) failed", sb); }
+    if (cudaMalloc((void**)&w->scales, sb + 64) != cudaSuccess) { cudaGetLastError(); cudaFree(w->codes); w->codes = nullptr; return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%zu) failed", sb); }
   }
   return CAI_OK;
 }
@@ -64,7 +71,7 @@ QWeight qweight_rows_view(const QWeight& w, int64_t row0, int64_t nrows) {
   v.owns = false;
   v.n = nrows;
   v.codes = (char*)w.codes + (size_t)row0 * w.row_code_bytes();
-  v.scales = w.scales ? w.scales + (size_t)row0 * (size_t)(w.k / CAI_QK) : nullptr;
+  v.scales = w.scales ? w.scales + (size_t)row0 * (size_t)w.sstride : nullptr;
   v.bias = w.bias ? w.bias + row0 : nullptr;
   return v;
 }
@@ -86,24 +93,24 @@ int cai_ensure_staging(cai_ctx* ctx, size_t bytes) {
 // ---------------------------------------------------------------------------
 template <int HALFWORDS /* 17 for Q8_0, 9 for Q4_0 */>
 __global__ void repack_blocks_kernel(const uint16_t* __restrict__ src, int64_t nrows, int64_t blocks_per_row,
-                                     uint16_t* __restrict__ codes, uint16_t* __restrict__ scales) {
+                                     uint16_t* __restrict__ codes, uint16_t* __restrict__ scales, int64_t sstride) {
   const int64_t total = nrows * blocks_per_row * HALFWORDS;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t blk = i / HALFWORDS;
     const int j = (int)(i - blk * HALFWORDS);
     const uint16_t v = src[i];
-    if (j == 0) scales[blk] = v;
+    if (j == 0) scales[(blk / blocks_per_row) * sstride + (blk % blocks_per_row)] = v;
     else codes[blk * (HALFWORDS - 1) + (j - 1)] = v;
   }
 }
 template <int HALFWORDS>
 __global__ void unpack_blocks_kernel(uint16_t* __restrict__ dst, int64_t nrows, int64_t blocks_per_row,
-                                     const uint16_t* __restrict__ codes, const uint16_t* __restrict__ scales) {
+                                     const uint16_t* __restrict__ codes, const uint16_t* __restrict__ scales, int64_t sstride) {
   const int64_t total = nrows * blocks_per_row * HALFWORDS;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t blk = i / HALFWORDS;
     const int j = (int)(i - blk * HALFWORDS);
-    dst[i] = (j == 0) ? scales[blk] : codes[blk * (HALFWORDS - 1) + (j - 1)];
+    dst[i] = (j == 0) ? scales[(blk / blocks_per_row) * sstride + (blk % blocks_per_row)] : codes[blk * (HALFWORDS - 1) + (j - 1)];
   }
 }
 
@@ -147,10 +154,10 @@ int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows,
       const int blocks = (int)(want > 65535 ? 65535 : (want < 1 ? 1 : want));
       if (w->type == CAI_TYPE_Q8_0)
         repack_blocks_kernel<17><<<blocks, threads, 0, ctx->stream>>>((const uint16_t*)ctx->staging_dev, nr, bpr,
-            (uint16_t*)((char*)w->codes + (size_t)r * w->row_code_bytes()), (uint16_t*)(w->scales + (size_t)r * bpr));
+            (uint16_t*)((char*)w->codes + (size_t)r * w->row_code_bytes()), (uint16_t*)(w->scales + (size_t)r * w->sstride), w->sstride);
       else
         repack_blocks_kernel<9><<<blocks, threads, 0, ctx->stream>>>((const uint16_t*)ctx->staging_dev, nr, bpr,
-            (uint16_t*)((char*)w->codes + (size_t)r * w->row_code_bytes()), (uint16_t*)(w->scales + (size_t)r * bpr));
+            (uint16_t*)((char*)w->codes + (size_t)r * w->row_code_bytes()), (uint16_t*)(w->scales + (size_t)r * w->sstride), w->sstride);
       CAI_LAUNCHED(ctx);
     }
     CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the pinned buffer is reused by the next chunk
@@ -180,10 +187,10 @@ int qweight_download_blocks(cai_ctx* ctx, const QWeight* w, void* out_host, size
     const int blocks = (int)(want > 65535 ? 65535 : (want < 1 ? 1 : want));
     if (w->type == CAI_TYPE_Q8_0)
       unpack_blocks_kernel<17><<<blocks, threads, 0, ctx->stream>>>((uint16_t*)ctx->staging_dev, nr, bpr,
-          (const uint16_t*)((const char*)w->codes + (size_t)r * w->row_code_bytes()), (const uint16_t*)(w->scales + (size_t)r * bpr));
+          (const uint16_t*)((const char*)w->codes + (size_t)r * w->row_code_bytes()), (const uint16_t*)(w->scales + (size_t)r * w->sstride), w->sstride);
     else
       unpack_blocks_kernel<9><<<blocks, threads, 0, ctx->stream>>>((uint16_t*)ctx->staging_dev, nr, bpr,
-          (const uint16_t*)((const char*)w->codes + (size_t)r * w->row_code_bytes()), (const uint16_t*)(w->scales + (size_t)r * bpr));
+          (const uint16_t*)((const char*)w->codes + (size_t)r * w->row_code_bytes()), (const uint16_t*)(w->scales + (size_t)r * w->sstride), w->sstride);
     CAI_LAUNCHED(ctx);
     CAI_CUDA(ctx, cudaMemcpyAsync((char*)out_host + (size_t)r * row_bytes, ctx->staging_dev, (size_t)nr * row_bytes, cudaMemcpyDeviceToHost, ctx->stream));
     CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -197,18 +204,18 @@ int qweight_download_blocks(cai_ctx* ctx, const QWeight* w, void* out_host, size
 // __half2float is exact for every half, subnormals included.
 // ---------------------------------------------------------------------------
 __global__ void dequant_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
-                               int64_t n_elems, float* __restrict__ out) {
+                               int64_t n_elems, int64_t k, int64_t sstride, float* __restrict__ out) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += (int64_t)gridDim.x * blockDim.x) {
     float v;
     if (type == CAI_TYPE_Q8_0) {
-      const float d = __half2float(scales[i / CAI_QK]);
+      const float d = __half2float(scales[(i / k) * sstride + (i % k) / CAI_QK]);
       v = d * (float)((const int8_t*)codes)[i];
     } else if (type == CAI_TYPE_Q4_0) {
       const int64_t blk = i / CAI_QK;
       const int e = (int)(i % CAI_QK);
       const uint8_t byte = ((const uint8_t*)codes)[blk * 16 + (e & 15)];
       const int nib = (e < 16) ? (byte & 0x0F) : (byte >> 4);
-      const float d = __half2float(scales[blk]);
+      const float d = __half2float(scales[(i / k) * sstride + (i % k) / CAI_QK]);
       v = d * (float)(nib - 8);
     } else if (type == CAI_TYPE_F16) {
       v = __half2float(((const __half*)codes)[i]);
@@ -224,7 +231,7 @@ int qweight_dequantize_to_dev(cai_ctx* ctx, const QWeight* w, float* out_dev) {
   const int threads = 256;
   int64_t want = (n_elems + threads - 1) / threads;
   const int blocks = (int)(want > 148 * 32 ? 148 * 32 : want);
-  dequant_kernel<<<blocks, threads, 0, ctx->stream>>>(w->type, w->codes, w->scales, n_elems, out_dev);
+  dequant_kernel<<<blocks, threads, 0, ctx->stream>>>(w->type, w->codes, w->scales, n_elems, w->k, w->sstride, out_dev);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -248,7 +255,7 @@ __device__ __forceinline__ float keyed_normal(uint64_t seed, uint64_t tensor_id,
 
 // One warp per 32-element block; lane = element.
 __global__ void synth_weight_kernel(int type, void* __restrict__ codes, __half* __restrict__ scales,
-                                    int64_t n, int64_t k, uint64_t seed, uint64_t tensor_id, float std,
+                                    int64_t n, int64_t k, int64_t sstride, uint64_t seed, uint64_t tensor_id, float std,
                                     int64_t grow0, int64_t gcol0, int64_t gcols) {
   const int lane = threadIdx.x & 31;
   const int64_t bpr = k / CAI_QK;
@@ -273,7 +280,7 @@ __global__ void synth_weight_kernel(int type, void* __restrict__ codes, __half* 
       int e = (q >= 0.f) ? (int)truncf(q + 0.5f) : (int)truncf(q - 0.5f);
       e = e > 127 ? 127 : (e < -127 ? -127 : e);
       ((int8_t*)codes)[row * k + col] = (int8_t)e;
-      if (lane == 0) scales[b] = __float2half_rn(scale);
+      if (lane == 0) scales[row * sstride + kb] = __float2half_rn(scale);
     } else {  // Q4_0, ggml rule: signed value of largest magnitude (first on ties), d = max/-8
       float best = fabsf(v);
       float bestv = v;
@@ -291,7 +298,7 @@ __global__ void synth_weight_kernel(int type, void* __restrict__ codes, __half* 
       c = c > 15 ? 15 : (c < 0 ? 0 : c);
       const int hi = __shfl_down_sync(0xffffffffu, c, 16);
       if (lane < 16) ((uint8_t*)codes)[b * 16 + lane] = (uint8_t)(c | (hi << 4));
-      if (lane == 0) scales[b] = __float2half_rn(d);
+      if (lane == 0) scales[row * sstride + kb] = __float2half_rn(d);
     }
   }
 }
@@ -309,7 +316,7 @@ int qweight_init_synthetic(cai_ctx* ctx, QWeight* w, uint64_t seed, uint64_t ten
   const int threads = 256;
   int64_t want = (nblk * 32 + threads - 1) / threads;
   const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
-  synth_weight_kernel<<<blocks, threads, 0, ctx->stream>>>(w->type, w->codes, w->scales, w->n, w->k, seed, tensor_id, std,
+  synth_weight_kernel<<<blocks, threads, 0, ctx->stream>>>(w->type, w->codes, w->scales, w->n, w->k, w->sstride, seed, tensor_id, std,
                                                            global_row0, global_col0, global_cols);
   CAI_LAUNCHED(ctx);
   w->present = true;
