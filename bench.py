@@ -287,16 +287,15 @@ def run_linear(args):
         lin = DotProductSharedKernel(backend)
         lin.prepare_for_compute_quant(ggml_type, blk.reshape(-1), n, k)
         lins.append(lin)
+    import ctypes as C
     x = backend.to_device(rng.standard_normal((batch, k)).astype(np.float32))
-    for _ in range(args.warmup):
-        for lin in lins:
-            lin.compute_quant(x, batch=batch)
+    y = backend.alloc(batch * n * 4)
+    handles = (C.c_void_p * copies)(*[lin.handle for lin in lins])
+    backend._check(backend.lib.cai_linear_forward_many(handles, copies, x.ptr, batch, y.ptr, args.warmup))
     backend.sync()
     launches0 = backend.launch_count()
     backend.timer_begin()
-    for _ in range(args.steps):
-        for lin in lins:
-            lin.compute_quant(x, batch=batch)
+    backend._check(backend.lib.cai_linear_forward_many(handles, copies, x.ptr, batch, y.ptr, args.steps))
     ms = backend.timer_end()
     launches = backend.launch_count() - launches0
     per_launch_ms = ms / (args.steps * copies)

@@ -110,6 +110,9 @@ int cai_linear_create(cai_ctx* ctx, int type, const void* blocks_host, int64_t n
 int cai_linear_destroy(cai_linear* lin);
 int cai_linear_forward(cai_linear* lin, const float* x_host, int batch, float* y_host, int act);
 int cai_linear_forward_dev(cai_linear* lin, const float* x_dev, int batch, float* y_dev, int act);
+/* Enqueues iters passes over `count` resident layers of identical shape (same x, same y), without
+ * returning to the caller between launches: the measurement loop for kernels shorter than a host call. */
+int cai_linear_forward_many(cai_linear* const* lins, int count, const float* x_dev, int batch, float* y_dev, int iters);
 /* Resident weight bytes (codes + scales), the algorithmic bytes one forward streams. */
 int cai_linear_weight_bytes(cai_linear* lin, int64_t* out_bytes);
 /* Dequantizes the RESIDENT (repacked) weights to fp32 [N*K] on the host. */

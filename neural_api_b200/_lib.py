@@ -56,6 +56,7 @@ SIGNATURES = {
     "cai_linear_destroy": [_P],
     "cai_linear_forward": [_P, _P, _I, _P, _I],
     "cai_linear_forward_dev": [_P, _P, _I, _P, _I],
+    "cai_linear_forward_many": [C.POINTER(_P), _I, _P, _I, _P, _I],
     "cai_linear_weight_bytes": [_P, C.POINTER(_I64)],
     "cai_linear_dequantize": [_P, _P],
     "cai_linear_set_path": [_P, _I],

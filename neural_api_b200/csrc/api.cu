@@ -15,6 +15,14 @@ int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...) {
   return code;
 }
 
+int cai_check_device_error(cai_ctx* ctx) {
+  if (ctx->err_flag && *(volatile int*)ctx->err_flag) {
+    *ctx->err_flag = 0;
+    return cai_fail(ctx, CAI_ERR_CUDA, "a kernel gave up a bounded wait (device error word raised)");
+  }
+  return CAI_OK;
+}
+
 int cai_prof_mark(cai_ctx* ctx, int family) {
   if (ctx->prof_n >= ctx->prof_cap) {
     const int ncap = ctx->prof_cap ? ctx->prof_cap * 2 : 4096;
@@ -32,6 +40,8 @@ int cai_prof_mark(cai_ctx* ctx, int family) {
 }
 
 extern "C" {
+
+int cai_cuda_shutdown(cai_ctx* ctx);
 
 int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
   if (!out_ctx) return CAI_ERR_INVALID;
@@ -52,6 +62,17 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
     delete ctx;
     return CAI_ERR_CUDA;
   }
+  ctx->gemv_scratch_ctas = 2 * ctx->sm_count;
+  ctx->gemv_ticket_cap = 65536;
+  if (cudaMalloc((void**)&ctx->gemv_scratch, (size_t)ctx->gemv_scratch_ctas * 2 * 32 * 4 * sizeof(float)) != cudaSuccess ||
+      cudaMalloc((void**)&ctx->gemv_tickets, (size_t)ctx->gemv_ticket_cap * sizeof(int)) != cudaSuccess ||
+      cudaMemset(ctx->gemv_tickets, 0, (size_t)ctx->gemv_ticket_cap * sizeof(int)) != cudaSuccess ||
+      cudaHostAlloc((void**)&ctx->err_flag, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+    cudaGetLastError();
+    cai_cuda_shutdown(ctx);
+    return CAI_ERR_CUDA;
+  }
+  *ctx->err_flag = 0;
   *out_ctx = ctx;
   return CAI_OK;
 }
@@ -65,6 +86,9 @@ int cai_cuda_shutdown(cai_ctx* ctx) {
   free(ctx->prof_events);
   free(ctx->prof_family);
   if (ctx->l2_flush_buf) cudaFree(ctx->l2_flush_buf);
+  if (ctx->gemv_scratch) cudaFree(ctx->gemv_scratch);
+  if (ctx->gemv_tickets) cudaFree(ctx->gemv_tickets);
+  if (ctx->err_flag) cudaFreeHost(ctx->err_flag);
   if (ctx->staging_dev) cudaFree(ctx->staging_dev);
   if (ctx->staging_pinned) cudaFreeHost(ctx->staging_pinned);
   cudaEventDestroy(ctx->ev_begin);
@@ -125,7 +149,7 @@ int cai_memcpy_d2h(cai_ctx* ctx, void* dst_host, const void* src_dev, int64_t by
 int cai_dev_sync(cai_ctx* ctx) {
   CAI_TRY(cai_bind(ctx));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return CAI_OK;
+  return cai_check_device_error(ctx);
 }
 int cai_timer_begin(cai_ctx* ctx) {
   CAI_TRY(cai_bind(ctx));
@@ -252,6 +276,21 @@ int cai_linear_forward(cai_linear* lin, const float* x_host, int batch, float* y
   CAI_TRY(cai_linear_forward_dev(lin, lin->x_dev, batch, lin->y_dev, act));
   CAI_CUDA(ctx, cudaMemcpyAsync(y_host, lin->y_dev, (size_t)batch * lin->w.n * 4, cudaMemcpyDeviceToHost, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return cai_check_device_error(ctx);
+}
+
+int cai_linear_forward_many(cai_linear* const* lins, int count, const float* x_dev, int batch, float* y_dev, int iters) {
+  if (!lins || count < 1 || !lins[0]) return CAI_ERR_INVALID;
+  cai_ctx* ctx = lins[0]->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!x_dev || !y_dev || batch < 1 || iters < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_forward_many: bad argument");
+  for (int it = 0; it < iters; ++it)
+    for (int c = 0; c < count; ++c) {
+      if (!lins[c] || lins[c]->ctx != ctx) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_forward_many: handle %d", c);
+      LinearArgs a;
+      a.w = &lins[c]->w; a.x = x_dev; a.ldx = lins[c]->w.k; a.y = y_dev; a.ldy = lins[c]->w.n; a.batch = batch;
+      CAI_TRY(linear_launch(ctx, a));
+    }
   return CAI_OK;
 }
 

@@ -30,6 +30,12 @@ struct cai_ctx {
   size_t staging_bytes;
   void* staging_pinned;      // upload staging (pinned host)
   cai_comm_state* comm;      // NULL until cai_comm_init
+  // stream-K GEMV: partial sums of row groups shared by several CTAs, arrival tickets, error word
+  float* gemv_scratch;
+  int* gemv_tickets;
+  int gemv_ticket_cap;
+  int gemv_scratch_ctas;
+  int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out
   // per-launch profiling (cai_session_profile): one event after every launch
   int prof_on;
   int cur_family;            // FAM_* of the launches being enqueued
@@ -81,7 +87,7 @@ int cai_ensure_staging(cai_ctx* ctx, size_t bytes);
 // that rows of codes start on 16-byte boundaries (a 34-byte Q8_0 block does
 // not): values stay bit-identical, d * q is formed in fp32 exactly as
 // DecodeGGMLSpan does.
-//   Q8_0: codes int8  [N][K],      scales fp16 [N][sstride], sstride = K/32 rounded up to 8
+//   Q8_0: codes uint8 [N][K] holding q + 128 (the bias saves one logic op per word in the GEMV),      scales fp16 [N][sstride], sstride = K/32 rounded up to 8
 //   Q4_0: codes uint8 [N][K/2] (the 16 nibble bytes of each block kept together),
 //         scales fp16 [N][K/32]
 //   F16 : codes fp16  [N][K];  F32: codes float [N][K]
@@ -146,6 +152,7 @@ struct LinearArgs {
 };
 
 int linear_launch(cai_ctx* ctx, const LinearArgs& a);
+int cai_check_device_error(cai_ctx* ctx);   // CAI_ERR_CUDA if a kernel raised the error word
 
 // ops.cu
 int op_embed(cai_ctx* ctx, const QWeight* table, const int32_t* tokens_dev, int batch, float* out, int64_t ld);

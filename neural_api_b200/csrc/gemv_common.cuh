@@ -54,13 +54,9 @@ __device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) {
   return r;
 }
 
-// fp16 bit pattern -> float, exact for zero, subnormal and normal halves: the exponent/mantissa
-// bits are placed in an fp32 pattern that is 2^-112 times the value, then scaled back by an exact
-// power of two. Inf/NaN patterns take the conversion instruction.
+// fp16 bit pattern -> float.
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) {
-  if ((h & 0x7C00u) == 0x7C00u) return __half2float(__ushort_as_half((unsigned short)h));
-  const uint32_t bits = ((h & 0x8000u) << 16) | ((h & 0x7FFFu) << 13);
-  return __uint_as_float(bits) * __uint_as_float(0x77800000u);   // * 2^112
+  return __half2float(__ushort_as_half((unsigned short)h));      // exact for every half; runs on the conversion pipe
 }
 
 // Streaming 16-byte load of weight codes: read-only path, no L1 allocation (each byte is used once).
@@ -71,10 +67,9 @@ __device__ __forceinline__ int4 ldg_stream16(const void* ptr) {
   return v;
 }
 
-// 4 int8 codes of one 32-bit word times 4 activations, accumulated into a packed pair.
-// (0x4B000000 | (code ^ 0x80)) is the float 2^23 + code + 128; adding -(2^23 + 128) leaves the code exactly.
+// 4 biased Q8_0 codes (q + 128, one per byte) times 4 activations, accumulated into a packed pair.
+// (0x4B000000 | byte) is the float 2^23 + q + 128; adding -(2^23 + 128) leaves q exactly.
 __device__ __forceinline__ f32x2_t q8_word_fma(uint32_t w, const float4& x, f32x2_t acc) {
-  w ^= 0x80808080u;
   const f32x2_t negc = pack2(-8388736.0f, -8388736.0f);
   const f32x2_t f01 = pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7651u)));
   const f32x2_t f23 = pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7653u)));

@@ -868,6 +868,7 @@ int cai_session_step(cai_session* s, const int32_t* tokens_host, const int32_t* 
   }
   if (argmax_out_host) CAI_CUDA(ctx, cudaMemcpyAsync(argmax_out_host, s->amax_idx, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  CAI_TRY(cai_check_device_error(ctx));
   if (logits_out_host && m->tp_size > 1) {
     for (int r = 0; r < m->tp_size; ++r)
       for (int b = 0; b < B; ++b)

@@ -16,7 +16,7 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
   for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
     float v;
     const int64_t i = tok * k + c;
-    if (type == CAI_TYPE_Q8_0) v = __half2float(scales[tok * sstride + c / CAI_QK]) * (float)((const int8_t*)codes)[i];
+    if (type == CAI_TYPE_Q8_0) v = __half2float(scales[tok * sstride + c / CAI_QK]) * (float)((int)((const uint8_t*)codes)[i] - 128);
     else if (type == CAI_TYPE_Q4_0) {
       const int64_t blk = i / CAI_QK;
       const int e = (int)(i % CAI_QK);

@@ -100,7 +100,7 @@ __global__ void repack_blocks_kernel(const uint16_t* __restrict__ src, int64_t n
     const int j = (int)(i - blk * HALFWORDS);
     const uint16_t v = src[i];
     if (j == 0) scales[(blk / blocks_per_row) * sstride + (blk % blocks_per_row)] = v;
-    else codes[blk * (HALFWORDS - 1) + (j - 1)] = v;
+    else codes[blk * (HALFWORDS - 1) + (j - 1)] = (HALFWORDS == 17) ? (uint16_t)(v ^ 0x8080u) : v;   // Q8_0 codes are kept biased: q + 128
   }
 }
 template <int HALFWORDS>
@@ -110,7 +110,8 @@ __global__ void unpack_blocks_kernel(uint16_t* __restrict__ dst, int64_t nrows, 
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t blk = i / HALFWORDS;
     const int j = (int)(i - blk * HALFWORDS);
-    dst[i] = (j == 0) ? scales[(blk / blocks_per_row) * sstride + (blk % blocks_per_row)] : codes[blk * (HALFWORDS - 1) + (j - 1)];
+    const uint16_t c = (j == 0) ? (uint16_t)0 : codes[blk * (HALFWORDS - 1) + (j - 1)];
+    dst[i] = (j == 0) ? scales[(blk / blocks_per_row) * sstride + (blk % blocks_per_row)] : ((HALFWORDS == 17) ? (uint16_t)(c ^ 0x8080u) : c);
   }
 }
 
@@ -209,7 +210,7 @@ __global__ void dequant_kernel(int type, const void* __restrict__ codes, const _
     float v;
     if (type == CAI_TYPE_Q8_0) {
       const float d = __half2float(scales[(i / k) * sstride + (i % k) / CAI_QK]);
-      v = d * (float)((const int8_t*)codes)[i];
+      v = d * (float)((int)((const uint8_t*)codes)[i] - 128);   // resident Q8_0 codes are biased by 128
     } else if (type == CAI_TYPE_Q4_0) {
       const int64_t blk = i / CAI_QK;
       const int e = (int)(i % CAI_QK);
@@ -279,7 +280,7 @@ __global__ void synth_weight_kernel(int type, void* __restrict__ codes, __half* 
       const float q = v * inv;
       int e = (q >= 0.f) ? (int)truncf(q + 0.5f) : (int)truncf(q - 0.5f);
       e = e > 127 ? 127 : (e < -127 ? -127 : e);
-      ((int8_t*)codes)[row * k + col] = (int8_t)e;
+      ((uint8_t*)codes)[row * k + col] = (uint8_t)(e + 128);    // biased resident form
       if (lane == 0) scales[row * sstride + kb] = __float2half_rn(scale);
     } else {  // Q4_0, ggml rule: signed value of largest magnitude (first on ties), d = max/-8
       float best = fabsf(v);
