@@ -154,6 +154,23 @@ int cai_sdpa_cache_len(cai_sdpa* s, int* out_len);
  * whole cache. out_dev: q_heads*head_dim floats. */
 int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev);
 
+/* Allocation-free variant of cai_sdpa_step_dev. It has no counterpart in the reference.
+ * For callers that must not allocate device memory when they call in: real-time loops that cannot
+ * block in the driver's allocator, plugins confined to an arena their host application handed them,
+ * processes whose device-memory budget was fixed at start-up. The caller owns every buffer: the token row
+ * [allQ | allK | allV], the head-major K and V caches ([kv_head][max_ctx][head_dim] floats each), one
+ * device int holding the number of rows already cached (the caller adds 1 after the call), and the
+ * output (q_heads*head_dim floats). The split-context partial results go to a fixed 2 MiB array that is
+ * part of the library (each GPU that loads the library holds it until the process exits); a shape whose
+ * partials need more (q_heads x context splits x (head_dim+2) floats > 524288) is rejected with
+ * CAI_ERR_UNSUPPORTED. The call performs no cudaMalloc / cudaFree and launches on the context's stream
+ * without synchronizing. Its first call on a device looks up the array's device address; make that
+ * first call before any stream capture. All calls share the array: two calls that overlap on the GPU
+ * (different streams, different contexts on one device) race; nothing in it needs clearing between calls. */
+int cai_sdpa_step_noalloc(cai_ctx* ctx, float* qkv_row_dev, float* k_cache_dev, float* v_cache_dev,
+                          const int32_t* cache_len_dev, int q_heads, int kv_heads, int head_dim, int max_ctx,
+                          float* out_dev);
+
 /* ------------------------------------------------------------------------- */
 /* Whole-model fast path: the graph BuildLlamaFromTensorReaderWithConfig      */
 /* wires (neural/neuralpretrained.pas:16196-17473), resident on the GPU.      */

@@ -338,3 +338,56 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
   }
   return CAI_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free decode step.
+//
+// Some hosts may not allocate device memory when they call into this library:
+// a real-time audio or control loop that must not block in the driver's
+// allocator, a plugin that was handed a fixed arena by its embedding
+// application, or a process whose device-memory budget was fixed at start-up.
+// For them the split-context partial results live in the fixed array below,
+// which is part of the library image: every GPU that loads the library holds
+// these 2 MiB until the process exits.
+// ---------------------------------------------------------------------------
+#define CAI_SDPA_NOALLOC_MAX_FLOATS (512 * 1024)
+static __device__ __align__(256) float g_sdpa_noalloc_scratch[CAI_SDPA_NOALLOC_MAX_FLOATS];
+
+// Device address of the array above, looked up once per device. In host code the symbol
+// g_sdpa_noalloc_scratch is only a handle, not an address the GPU can use.
+static float* g_sdpa_noalloc_ptr[64] = {nullptr};
+
+extern "C" int cai_sdpa_step_noalloc(cai_ctx* ctx, float* qkv_row_dev, float* k_cache_dev, float* v_cache_dev,
+                                     const int32_t* cache_len_dev, int q_heads, int kv_heads, int head_dim, int max_ctx,
+                                     float* out_dev) {
+  CAI_TRY(cai_bind(ctx));
+  if (!qkv_row_dev || !k_cache_dev || !v_cache_dev || !cache_len_dev || !out_dev)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_sdpa_step_noalloc: null buffer");
+  if (q_heads < 1 || kv_heads < 1 || (q_heads % kv_heads) || head_dim < 2 || (head_dim % 2) || head_dim > 256 || max_ctx < 1)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_sdpa_step_noalloc: heads %d/%d head_dim %d ctx %d", q_heads, kv_heads, head_dim, max_ctx);
+  if (ctx->device < 0 || ctx->device >= 64) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "cai_sdpa_step_noalloc: device index %d", ctx->device);
+  const int nsplit = attn_nsplit(ctx, 1, kv_heads, max_ctx);
+  const size_t need = attn_partial_floats(1, q_heads, nsplit, head_dim);
+  if (need > (size_t)CAI_SDPA_NOALLOC_MAX_FLOATS)
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED,
+                    "cai_sdpa_step_noalloc: %d heads x %d context splits x %d dims need %zu scratch floats, the built-in "
+                    "scratch holds %d; use cai_sdpa_create / cai_sdpa_step_dev for this shape",
+                    q_heads, nsplit, head_dim, need, CAI_SDPA_NOALLOC_MAX_FLOATS);
+  if (!g_sdpa_noalloc_ptr[ctx->device]) {
+    // first call on this device (current device == ctx->device after cai_bind)
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_sdpa_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) return cai_fail(ctx, CAI_ERR_CUDA, "cudaGetSymbolAddress(scratch) -> %s", cudaGetErrorString(e));
+    g_sdpa_noalloc_ptr[ctx->device] = ptr;
+  }
+  AttnArgs a;
+  a.qkv = qkv_row_dev; a.ld = (int64_t)(q_heads + 2 * kv_heads) * head_dim;
+  a.k_cache = k_cache_dev; a.v_cache = v_cache_dev; a.cache_len_dev = cache_len_dev;
+  a.batch = 1; a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.max_ctx = max_ctx;
+  a.out = out_dev; a.ldo = (int64_t)q_heads * head_dim;
+  a.partial = g_sdpa_noalloc_ptr[ctx->device];   // every slot the combine kernel reads is written first: nothing to clear
+  a.nsplit = nsplit;
+  CAI_TRY(attn_rope_append(ctx, a));
+  CAI_TRY(attn_decode(ctx, a));
+  return CAI_OK;
+}
