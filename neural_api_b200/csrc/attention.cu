@@ -29,6 +29,8 @@ struct AttnParams {
 
 __global__ void rope_append_kernel(const AttnParams p) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const int hd = p.head_dim;
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
@@ -90,12 +92,15 @@ __device__ __forceinline__ void load8(const float* __restrict__ ptr, int nd, boo
   }
 }
 
+constexpr int ATTN_MIN_CHUNK = 64;
 constexpr int ATTN_WARPS = 4;
-constexpr int ATTN_KEYS = 4;   // keys in flight per lane group
+constexpr int ATTN_KEYS = 2;   // keys in flight per lane group (K and V rows of both are loaded together)
 
 template <int GT>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const AttnParams p, int lpk) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int hd = p.head_dim;
   const int G = p.q_heads / p.kv_heads;
@@ -107,7 +112,11 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
   const bool vec = (nd == 8) && ((hd & 3) == 0);
 
   const int n = p.cache_len[b] + 1;                  // keys after the append
-  const int chunk = (n + p.nsplit - 1) / p.nsplit;
+  // a split covers at least ATTN_MIN_CHUNK rows: short contexts use few splits, the other CTAs leave at once
+  int chunk = (n + p.nsplit - 1) / p.nsplit;
+  if (chunk < ATTN_MIN_CHUNK) chunk = ATTN_MIN_CHUNK;
+  const int used = (n + chunk - 1) / chunk;
+  if (split >= used) return;
   const int j_begin = split * chunk;
   int j_end = j_begin + chunk; if (j_end > n) j_end = n;
 
@@ -133,16 +142,19 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
     // warp runs the same iterations, so the full-mask shuffles below are always converged.
     for (int jb = j_begin + warp * kpw; jb < j_end; jb += key_stride * ATTN_KEYS) {
       const int j0 = jb + kslot;
-      float kv[ATTN_KEYS][8];
+      float kv[ATTN_KEYS][8], vv[ATTN_KEYS][8];
       bool valid[ATTN_KEYS];
+      // K and V rows of the keys of this iteration are requested together, before any arithmetic
 #pragma unroll
       for (int t = 0; t < ATTN_KEYS; ++t) {
         const int j = j0 + t * key_stride;
         valid[t] = (j < j_end) && (nd > 0);
-        if (valid[t]) load8(kbase + (int64_t)j * hd + d0, nd, vec, kv[t]);
-        else {
+        if (valid[t]) {
+          load8(kbase + (int64_t)j * hd + d0, nd, vec, kv[t]);
+          load8(vbase + (int64_t)j * hd + d0, nd, vec, vv[t]);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) kv[t][i] = 0.f;
+          for (int i = 0; i < 8; ++i) { kv[t][i] = 0.f; vv[t][i] = 0.f; }
         }
       }
       float s[GT][ATTN_KEYS];
@@ -166,12 +178,6 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
 #pragma unroll
           for (int t = 0; t < ATTN_KEYS; ++t) s[hh][t] += __shfl_xor_sync(0xffffffffu, s[hh][t], o);
       }
-      // V rows reuse the K registers
-#pragma unroll
-      for (int t = 0; t < ATTN_KEYS; ++t) {
-        const int j = j0 + t * key_stride;
-        if (valid[t]) load8(vbase + (int64_t)j * hd + d0, nd, vec, kv[t]);
-      }
 #pragma unroll
       for (int hh = 0; hh < GT; ++hh) {
         float mx = m[hh];
@@ -193,7 +199,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
         for (int i = 0; i < 8; ++i) {
           float a = acc[hh][i] * scale;
 #pragma unroll
-          for (int t = 0; t < ATTN_KEYS; ++t) a = fmaf(pt[t], kv[t][i], a);
+          for (int t = 0; t < ATTN_KEYS; ++t) a = fmaf(pt[t], vv[t][i], a);
           acc[hh][i] = a;
         }
       }
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
         at += src[2 + d] * sc;
       }
       const int h = g * G + h0 + hh;
-      if (p.nsplit == 1) {
+      if (used == 1) {
         p.out[(int64_t)b * p.ldo + (int64_t)h * hd + d] = (lt > 0.f) ? at / lt : 0.f;
       } else {
         float* dst = p.partial + (((int64_t)b * p.q_heads + h) * p.nsplit + split) * (hd + 2);
@@ -256,19 +262,26 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
 }
 
 __global__ void attn_combine_kernel(const AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
   const int hd = p.head_dim;
   const float* src = p.partial + ((int64_t)b * p.q_heads + h) * (int64_t)p.nsplit * (hd + 2);
+  const int n = p.cache_len[b] + 1;
+  int chunk = (n + p.nsplit - 1) / p.nsplit;
+  if (chunk < ATTN_MIN_CHUNK) chunk = ATTN_MIN_CHUNK;
+  const int used = (n + chunk - 1) / chunk;
+  if (used == 1) return;                              // the single split wrote the output itself
   float mx = -INFINITY;
-  for (int s = 0; s < p.nsplit; ++s) mx = fmaxf(mx, src[(size_t)s * (hd + 2)]);
+  for (int s = 0; s < used; ++s) mx = fmaxf(mx, src[(size_t)s * (hd + 2)]);
   float lt = 0.f;
-  for (int s = 0; s < p.nsplit; ++s) {
+  for (int s = 0; s < used; ++s) {
     const float ms = src[(size_t)s * (hd + 2)];
     lt += src[(size_t)s * (hd + 2) + 1] * ((ms == -INFINITY) ? 0.f : expf(ms - mx));
   }
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float at = 0.f;
-    for (int s = 0; s < p.nsplit; ++s) {
+    for (int s = 0; s < used; ++s) {
       const float ms = src[(size_t)s * (hd + 2)];
       at += src[(size_t)s * (hd + 2) + 2 + d] * ((ms == -INFINITY) ? 0.f : expf(ms - mx));
     }
@@ -278,10 +291,10 @@ __global__ void attn_combine_kernel(const AttnParams p) {
 
 int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx) {
   int64_t ctas = (int64_t)batch * kv_heads;
-  int ns = (int)((2 * (int64_t)ctx->sm_count + ctas - 1) / ctas);
-  const int cap = (max_ctx + 127) / 128;
+  int ns = (int)((6 * (int64_t)ctx->sm_count + ctas - 1) / ctas);   // about 6 CTAs of 4 warps per SM
+  const int cap = (max_ctx + 63) / 64;                              // at least 64 rows per split at full context
   if (ns > cap) ns = cap;
-  if (ns > 64) ns = 64;
+  if (ns > 128) ns = 128;
   if (ns < 1) ns = 1;
   return ns;
 }
@@ -302,7 +315,7 @@ static AttnParams to_params(const AttnArgs& a) {
 int attn_rope_append(cai_ctx* ctx, const AttnArgs& a) {
   ctx->cur_family = FAM_ATTN;
   if (a.head_dim % 2) return cai_fail(ctx, CAI_ERR_INVALID, "head_dim must be even");
-  rope_append_kernel<<<a.batch, 256, 0, ctx->stream>>>(to_params(a));
+  pdl_launch(ctx, rope_append_kernel, dim3(a.batch), dim3(256), 0, to_params(a));
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -321,19 +334,19 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
   const size_t smem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * gt * (a.head_dim + 2)) * sizeof(float);
   if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "attention group of %d heads x %d dims exceeds shared memory", G, a.head_dim);
   switch (gt) {
-    case 1: attn_decode_kernel<1><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    case 2: attn_decode_kernel<2><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    case 3: attn_decode_kernel<3><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    case 4: attn_decode_kernel<4><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    case 5: attn_decode_kernel<5><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    case 6: attn_decode_kernel<6><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    case 7: attn_decode_kernel<7><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
-    default: attn_decode_kernel<8><<<grid, ATTN_WARPS * 32, smem, ctx->stream>>>(p, lpk); break;
+    case 1: pdl_launch(ctx, attn_decode_kernel<1>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    case 2: pdl_launch(ctx, attn_decode_kernel<2>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    case 3: pdl_launch(ctx, attn_decode_kernel<3>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    case 4: pdl_launch(ctx, attn_decode_kernel<4>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    case 5: pdl_launch(ctx, attn_decode_kernel<5>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    case 6: pdl_launch(ctx, attn_decode_kernel<6>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    case 7: pdl_launch(ctx, attn_decode_kernel<7>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
+    default: pdl_launch(ctx, attn_decode_kernel<8>, grid, dim3(ATTN_WARPS * 32), smem, p, lpk); break;
   }
   CAI_LAUNCHED(ctx);
   if (a.nsplit > 1) {
     dim3 cgrid(a.q_heads, a.batch);
-    attn_combine_kernel<<<cgrid, 128, 0, ctx->stream>>>(p);
+    pdl_launch(ctx, attn_combine_kernel, cgrid, dim3(128), 0, p);
     CAI_LAUNCHED(ctx);
   }
   return CAI_OK;

@@ -36,6 +36,7 @@ struct cai_ctx {
   int gemv_ticket_cap;
   int gemv_scratch_ctas;
   int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out
+  int use_pdl;               // launch step kernels with programmatic dependent launch
   // per-launch profiling (cai_session_profile): one event after every launch
   int prof_on;
   int cur_family;            // FAM_* of the launches being enqueued
@@ -129,7 +130,7 @@ int vec_init_synthetic(cai_ctx* ctx, float* v, int64_t n, uint64_t seed, uint64_
 // ---------------------------------------------------------------------------
 // GEMV / GEMM launchers (gemv.cu, gemm_tc.cu)
 // ---------------------------------------------------------------------------
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_QKV_ROPE = 3 };
 
 struct LinearArgs {
   const QWeight* w = nullptr;
@@ -149,7 +150,18 @@ struct LinearArgs {
   const int32_t* expert_ids_dev = nullptr;
   int x_row_div = 1;             // activation row of pair p = p / x_row_div
   const float* row_scale_dev = nullptr;  // optional per-pair output scale (router gate)
+  // EPI_QKV_ROPE: rows are [allQ | allK | allV]; Q pairs are rotated and stored to y, K pairs are rotated and
+  // stored straight into the cache at slot cache_len[b], V rows go to the cache unrotated (RoPE + KV append fused)
+  const float* rope_cs = nullptr;        // [B][head_dim/2][2] cos, sin of this step
+  int rope_q_width = 0, rope_kv_width = 0, rope_head_dim = 0, rope_kv_heads = 0, rope_max_ctx = 0;
+  float* k_cache = nullptr;
+  float* v_cache = nullptr;
+  const int32_t* cache_len_dev = nullptr;
+  const float* norm_gain = nullptr;      // fuse y = W (gain * x * inv_rms(x)): the preceding TNNetTokenRMSNorm
+  float norm_eps = 0.f;
 };
+// true when linear_launch can apply the RMSNorm itself for this weight and batch
+bool linear_can_fuse_norm(const QWeight* w, int batch);
 
 int linear_launch(cai_ctx* ctx, const LinearArgs& a);
 int cai_check_device_error(cai_ctx* ctx);   // CAI_ERR_CUDA if a kernel raised the error word
@@ -162,7 +174,10 @@ int op_rope(cai_ctx* ctx, float* x, int64_t ldx, int tokens, int depth, int head
 int op_swiglu(cai_ctx* ctx, const float* x, int64_t ldx, float* y, int64_t ldy, int tokens, int half);
 int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, int top_k, int renorm,
                  int32_t* ids, float* gates);
-int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val);
+#define CAI_ARGMAX_CHUNKS 128
+int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val,
+              float* part_val, int* part_idx, int* tickets);   // scratch: [batch][CAI_ARGMAX_CHUNKS] x2, tickets [batch] zeroed once
+int op_rope_table(cai_ctx* ctx, const float* theta_dev, const int32_t* pos_dev, int batch, int half, float* cs_dev);
 int op_moe_combine(cai_ctx* ctx, float* x, int64_t ldx, const float* pair_out, int64_t ldp, const float* gates,
                    int tokens, int top_k, int depth);
 int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n);
@@ -201,6 +216,25 @@ void comm_destroy(cai_ctx* ctx);
 // device helpers
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
+// Programmatic dependent launch. A kernel launched through pdl_launch may start while the kernel
+// before it in the stream is still running; it must call pdl_wait() before it touches anything that
+// kernel wrote (pdl_wait returns once the previous kernel has completed and its writes are visible),
+// and may do independent work (barrier set-up, weight prefetch) before that. pdl_trigger() lets the
+// NEXT kernel start early in the same way. Both are no-ops for ordinarily launched kernels.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t pdl_launch(cai_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -28,6 +28,9 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
   const int group = warp / p.ksplit;
   const int kpart = warp - group * p.ksplit;
 
+  pdl_trigger();
+  if (p.expert_ids) pdl_wait();      // the expert choice itself comes from the previous kernel
+
   // operand selection
   const char* codes = (const char*)p.codes;
   const __half* scales = p.scales;
@@ -47,24 +50,6 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
     x = p.x + (int64_t)b0 * p.ldx;
   }
   const int64_t K = p.k;
-
-  // activations -> shared memory (rows beyond the batch repeat row 0 and are never stored)
-  const float* xr[NB];
-#pragma unroll
-  for (int b = 0; b < NB; ++b) xr[b] = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
-  float* red = smem_f;
-  if (p.x_in_smem) {
-    for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
-      const int b = (int)(i / K);
-      const int64_t c = i - (int64_t)b * K;
-      const int bb = (b0 + b < p.batch) ? b : 0;
-      *(float4*)(smem_f + i) = __ldg((const float4*)(x + (int64_t)bb * p.ldx + c));
-    }
-    __syncthreads();
-#pragma unroll
-    for (int b = 0; b < NB; ++b) xr[b] = smem_f + (int64_t)b * K;
-    red = smem_f + (int64_t)NB * K;
-  }
 
   // rows of this warp
   const int64_t gidx = (int64_t)blockIdx.x * groups_per_cta + group;
@@ -102,26 +87,75 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
   const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
   int64_t k0 = ((int64_t)kpart * 32 + lane) * CHUNK;
 
+  // Per-row pointers advance by a fixed stride: no address multiplications inside the loop.
+  const int64_t stride_b = stride >> CODE_SHIFT;                  // bytes of codes per stride
+  const int64_t stride_s = stride >> 5;                           // scales per stride
+  const int iters = (k0 < K) ? (int)((K - k0 + stride - 1) / stride) : 0;
+  const char* wp[RPW];
+  const unsigned short* sp[RPW];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    wp[r] = codes + rows[r] * row_bytes + (k0 >> CODE_SHIFT);
+    sp[r] = (const unsigned short*)scales + rows[r] * p.sstride + (k0 >> 5);
+  }
+  // The first weight loads do not depend on the previous kernel: they are in flight while it finishes.
   int4 wv[RPW], wn[RPW];
   uint32_t sv[RPW], sn[RPW];
 #pragma unroll
   for (int r = 0; r < RPW; ++r) { wn[r] = make_int4(0, 0, 0, 0); sn[r] = 0; }
-  if (k0 < K) {
+  if (iters > 0) {
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
-      wn[r] = ldg_stream16(codes + rows[r] * row_bytes + (k0 >> CODE_SHIFT));
-      sn[r] = __ldg((const unsigned short*)scales + rows[r] * p.sstride + (k0 >> 5));
+      wn[r] = ldg_stream16(wp[r]);
+      sn[r] = __ldg(sp[r]);
     }
   }
-  for (; k0 < K; k0 += stride) {
+  if (!p.expert_ids) pdl_wait();     // from here on the activations of the previous kernel are read
+
+  // activations -> shared memory (rows beyond the batch repeat row 0 and are never stored), with the
+  // per-token RMSNorm of the reference applied on the way when asked: y = gain * (x * inv)
+  const float* xr[NB];
+#pragma unroll
+  for (int b = 0; b < NB; ++b) xr[b] = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
+  float* red = smem_f;
+  if (p.x_in_smem) {
+    for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
+      const int b = (int)(i / K);
+      const int64_t c = i - (int64_t)b * K;
+      const int bb = (b0 + b < p.batch) ? b : 0;
+      *(float4*)(smem_f + i) = *(const float4*)(x + (int64_t)bb * p.ldx + c);
+    }
+    red = smem_f + (int64_t)NB * K;
+    float* nred = red + (size_t)(blockDim.x >> 5) * (RPW * NB);
+    __syncthreads();
+    if (p.norm_gain) {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float* xb = smem_f + (int64_t)b * K;
+        float ss = 0.f;
+        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) ss = fmaf(xb[c], xb[c], ss);
+        ss = block_sum(ss, nred);
+        const float inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
+        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) xb[c] = p.norm_gain[c] * (xb[c] * inv);
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int b = 0; b < NB; ++b) xr[b] = smem_f + (int64_t)b * K;
+  }
+
+#pragma unroll
+  for (int b = 0; b < NB; ++b) xr[b] += k0;
+  for (int it = 0; it < iters; ++it) {
 #pragma unroll
     for (int r = 0; r < RPW; ++r) { wv[r] = wn[r]; sv[r] = sn[r]; }
-    const int64_t k1 = k0 + stride;
-    if (k1 < K) {
+    if (it + 1 < iters) {
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        wn[r] = ldg_stream16(codes + rows[r] * row_bytes + (k1 >> CODE_SHIFT));
-        sn[r] = __ldg((const unsigned short*)scales + rows[r] * p.sstride + (k1 >> 5));
+        wp[r] += stride_b;
+        sp[r] += stride_s;
+        wn[r] = ldg_stream16(wp[r]);
+        sn[r] = __ldg(sp[r]);
       }
     }
     f32x2_t part[RPW][NB];
@@ -134,7 +168,7 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
       if (TYPE == CAI_TYPE_Q8_0) {
         float4 xv[NB];
 #pragma unroll
-        for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + k0 + 4 * i);
+        for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + 4 * i);
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
           const uint32_t w = ((const uint32_t*)&wv[r])[i];
@@ -145,8 +179,8 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
         float4 xlo[NB], xhi[NB];
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          xlo[b] = *(const float4*)(xr[b] + k0 + 4 * i);
-          xhi[b] = *(const float4*)(xr[b] + k0 + 16 + 4 * i);
+          xlo[b] = *(const float4*)(xr[b] + 4 * i);
+          xhi[b] = *(const float4*)(xr[b] + 16 + 4 * i);
         }
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
@@ -163,6 +197,8 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
 #pragma unroll
       for (int b = 0; b < NB; ++b) acc2[r][b] = fma2(d2, part[r][b], acc2[r][b]);
     }
+#pragma unroll
+    for (int b = 0; b < NB; ++b) xr[b] += stride;
   }
 
   // lanes -> one value per (row, batch)
@@ -199,6 +235,8 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
 // Generic path: F32 / F16 weights, any K (scalar loads), warp per row (pair of rows for SwiGLU).
 template <int NB>
 __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, int type) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps_per_cta = blockDim.x >> 5;
@@ -265,8 +303,7 @@ static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int 
     cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  gemv_quant_kernel<TYPE, NB, RPW><<<grid, threads, smem, ctx->stream>>>(p);
-  return cudaSuccess;
+  return pdl_launch(ctx, gemv_quant_kernel<TYPE, NB, RPW>, grid, dim3(threads), smem, p);
 }
 template <int TYPE, int NB>
 static cudaError_t launch_quant(cai_ctx* ctx, const GemvParams& p, int rpw, dim3 grid, int threads, size_t smem) {
@@ -280,6 +317,14 @@ static cudaError_t launch_quant_nb(cai_ctx* ctx, const GemvParams& p, int nb, in
   if (nb == 2) return launch_quant<TYPE, 2>(ctx, p, rpw, grid, threads, smem);
   if (nb == 4) return launch_quant<TYPE, 4>(ctx, p, rpw, grid, threads, smem);
   return launch_quant<TYPE, 8>(ctx, p, rpw, grid, threads, smem);
+}
+
+bool linear_can_fuse_norm(const QWeight* w, int batch) {
+  if (!w || (w->type != CAI_TYPE_Q8_0 && w->type != CAI_TYPE_Q4_0)) return false;
+  if (env_int("CAI_FUSE_NORM", 1) == 0) return false;
+  const int nb = batch >= 5 ? 8 : (batch >= 3 ? 4 : (batch == 2 ? 2 : 1));
+  if (batch > 8) return false;       // several batch tiles would each redo the norm; keep the separate kernel
+  return (size_t)nb * (size_t)w->k * 4 <= (size_t)env_int("CAI_GEMV_XSMEM", 64 * 1024);
 }
 
 int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
@@ -298,6 +343,14 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   p.bank_codes = a.bank_codes_dev; p.bank_scales = a.bank_scales_dev; p.expert_ids = a.expert_ids_dev;
   p.x_row_div = a.x_row_div < 1 ? 1 : a.x_row_div; p.row_scale = a.row_scale_dev;
   p.ksplit = 1;
+  if (a.epilogue == EPI_QKV_ROPE) {
+    if (!a.rope_cs || !a.k_cache || !a.v_cache || !a.cache_len_dev || a.rope_head_dim < 2 || (a.rope_head_dim % 2) || indexed ||
+        a.rope_q_width + 2 * a.rope_kv_width != w->n || (a.rope_q_width % a.rope_head_dim) || (a.rope_kv_width % a.rope_head_dim))
+      return cai_fail(ctx, CAI_ERR_INVALID, "linear: inconsistent fused RoPE / KV-append arguments");
+    p.rope_cs = a.rope_cs; p.rope_q_width = a.rope_q_width; p.rope_kv_width = a.rope_kv_width; p.rope_head_dim = a.rope_head_dim;
+    p.rope_kv_heads = a.rope_kv_heads; p.rope_max_ctx = a.rope_max_ctx; p.k_cache = a.k_cache; p.v_cache = a.v_cache;
+    p.cache_len = a.cache_len_dev;
+  }
   const int64_t units = (a.epilogue == EPI_SWIGLU) ? w->n / 2 : w->n;
   const bool quant = (w->type == CAI_TYPE_Q8_0 || w->type == CAI_TYPE_Q4_0);
   if (!quant) {
@@ -306,8 +359,9 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     const int64_t groups = (a.epilogue == EPI_SWIGLU) ? units : (units + 1) / 2;
     const int nb = indexed ? 1 : (a.batch >= 4 ? 4 : 1);
     dim3 grid((unsigned)((groups + wpc - 1) / wpc), indexed ? a.batch : (unsigned)((a.batch + nb - 1) / nb));
-    if (nb == 4) gemv_generic_kernel<4><<<grid, threads, 0, ctx->stream>>>(p, w->type);
-    else gemv_generic_kernel<1><<<grid, threads, 0, ctx->stream>>>(p, w->type);
+    if (a.norm_gain) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: fused RMSNorm needs quantized weights");
+    if (nb == 4) pdl_launch(ctx, gemv_generic_kernel<4>, grid, dim3(threads), 0, p, w->type);
+    else pdl_launch(ctx, gemv_generic_kernel<1>, grid, dim3(threads), 0, p, w->type);
     CAI_LAUNCHED(ctx);
     return CAI_OK;
   }
@@ -315,7 +369,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   // stream-K kernel with bulk-copy (TMA) staging, opt-in with CAI_GEMV_PATH=2: on B200 it measured
   // 3.0 TB/s against 4.0 TB/s for the register-staged kernel below on the 5120 x 55296 Q8_0 matrix
   // (its per-row bulk copies are small; both kernels are bound by the integer pipe that unpacks codes).
-  if (!indexed && a.batch <= 4 && env_int("CAI_GEMV_PATH", 0) == 2) {
+  if (!indexed && a.batch <= 4 && !a.norm_gain && a.epilogue != EPI_QKV_ROPE && env_int("CAI_GEMV_PATH", 0) == 2) {
     const int st = gemv_tma_launch(ctx, p, w->type, a.batch >= 3 ? 4 : a.batch);
     if (st != CAI_ERR_UNSUPPORTED) return st;
   }
@@ -332,7 +386,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   // load between 4 rows); K is split over the warps of a CTA until the launch has a machine's worth of warps
   if (units >= 2048) rpw = 4;
   else if (units >= 512) rpw = 2;
-  else rpw = (a.epilogue == EPI_SWIGLU) ? 2 : 1;
+  else rpw = (a.epilogue == EPI_SWIGLU || a.epilogue == EPI_QKV_ROPE) ? 2 : 1;
   if (nb >= 4 && rpw == 4) rpw = 2;
   {
     const int upg = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;
@@ -343,7 +397,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   rpw = env_int("CAI_GEMV_RPW", rpw);
   ksplit = env_int("CAI_GEMV_KSPLIT", ksplit);
   if (rpw != 1 && rpw != 2 && rpw != 4) rpw = 2;
-  if (a.epilogue == EPI_SWIGLU && rpw == 1) rpw = 2;
+  if ((a.epilogue == EPI_SWIGLU || a.epilogue == EPI_QKV_ROPE) && rpw == 1) rpw = 2;
   if (nb == 8 && rpw == 4) rpw = 2;
   if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) ksplit = 1;
   p.ksplit = ksplit;
@@ -356,7 +410,11 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   // activations in shared memory when they fit beside a healthy number of resident CTAs
   const size_t x_bytes = (size_t)nb * (size_t)w->k * 4;
   p.x_in_smem = (x_bytes <= (size_t)env_int("CAI_GEMV_XSMEM", 64 * 1024)) ? 1 : 0;
-  const size_t smem = (p.x_in_smem ? x_bytes : 0) + ((ksplit > 1) ? (size_t)wpc * rpw * nb * sizeof(float) : 0);
+  if (a.norm_gain) {
+    if (!p.x_in_smem) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: fused RMSNorm needs the activations to fit in shared memory");
+    p.norm_gain = a.norm_gain; p.norm_eps = a.norm_eps;
+  }
+  const size_t smem = (p.x_in_smem ? x_bytes + 32 * sizeof(float) : 0) + (size_t)wpc * rpw * nb * sizeof(float);
   cudaError_t e;
   if (w->type == CAI_TYPE_Q8_0) e = launch_quant_nb<CAI_TYPE_Q8_0>(ctx, p, nb, rpw, grid, threads, smem);
   else e = launch_quant_nb<CAI_TYPE_Q4_0>(ctx, p, nb, rpw, grid, threads, smem);

@@ -27,6 +27,14 @@ struct GemvParams {
   int x_row_div;
   const float* row_scale;
   int* err_flag;    // set by a kernel whose bounded wait ran out
+  const float* norm_gain;   // fused per-token RMSNorm of the input (needs x_in_smem), NULL = none
+  float norm_eps;
+  // EPI_QKV_ROPE
+  const float* rope_cs;
+  int rope_q_width, rope_kv_width, rope_head_dim, rope_kv_heads, rope_max_ctx;
+  float* k_cache;
+  float* v_cache;
+  const int32_t* cache_len;
 };
 
 typedef unsigned long long f32x2_t;   // two packed floats in one 64-bit register
@@ -117,6 +125,41 @@ template <int NB, int RPW>
 __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const float (&acc)[RPW][NB], int64_t unit0,
                                               int b0, int pair, const float* bias) {
   const int lane = threadIdx.x & 31;
+  if (p.epi == EPI_QKV_ROPE) {
+    // rows come in (even, odd) pairs = the interleaved RoPE pairs (2k, 2k+1) of a head
+    const int hd = p.rope_head_dim, half_hd = hd >> 1;
+#pragma unroll
+    for (int r = 0; r + 1 < RPW; r += 2) {
+      const int64_t row = unit0 + r;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        if (lane == ((r * NB + b) & 31) && row + 1 < p.n && (b0 + b) < p.batch) {
+          const int bi = b0 + b;
+          float v0 = acc[r][b], v1 = acc[r + 1][b];
+          if (bias) { v0 += bias[row]; v1 += bias[row + 1]; }
+          if (row < p.rope_q_width + p.rope_kv_width) {
+            const int64_t rr = (row < p.rope_q_width) ? row : row - p.rope_q_width;
+            const float* cs = p.rope_cs + ((size_t)bi * half_hd + (size_t)((rr % hd) >> 1)) * 2;
+            const float c = cs[0], s = cs[1];
+            const float y0 = c * v0 - s * v1, y1 = s * v0 + c * v1;
+            v0 = y0; v1 = y1;
+          }
+          if (row < p.rope_q_width) {
+            p.y[(int64_t)bi * p.ldy + row] = v0;
+            p.y[(int64_t)bi * p.ldy + row + 1] = v1;
+          } else {
+            const bool is_k = row < p.rope_q_width + p.rope_kv_width;
+            const int64_t rr = row - p.rope_q_width - (is_k ? 0 : p.rope_kv_width);
+            const int64_t g = rr / hd, d = rr % hd;
+            float* dst = (is_k ? p.k_cache : p.v_cache) +
+                         (((int64_t)bi * p.rope_kv_heads + g) * p.rope_max_ctx + p.cache_len[bi]) * hd + d;
+            dst[0] = v0; dst[1] = v1;
+          }
+        }
+      }
+    }
+    return;
+  }
   if (p.epi == EPI_SWIGLU) {
     const int64_t half = p.n >> 1;
 #pragma unroll

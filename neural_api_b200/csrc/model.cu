@@ -557,6 +557,8 @@ struct cai_session {
   float* partial = nullptr;
   int nsplit = 1;
   int32_t* amax_idx = nullptr; float* amax_val = nullptr;
+  float* amax_part_val = nullptr; int* amax_part_idx = nullptr; int* amax_tickets = nullptr;
+  float* rope_cs = nullptr;                           // [B][head_dim/2][2] cos/sin of the current step
   float *amax_pack = nullptr, *amax_gather = nullptr, *logits_gather = nullptr;
   int32_t* trace = nullptr; int32_t* trace_count = nullptr; int64_t trace_cap = 0;
   int32_t* prefill_buf = nullptr; int64_t prefill_cap = 0;
@@ -567,10 +569,14 @@ struct cai_session {
 };
 
 __global__ void pack_argmax_kernel(const int32_t* idx, const float* val, int batch, int offset, float* pack) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < batch) { pack[2 * b] = val[b]; pack[2 * b + 1] = __int_as_float(idx[b] + offset); }
 }
 __global__ void pick_argmax_kernel(const float* gathered, int batch, int world, int32_t* idx) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= batch) return;
   float best = -INFINITY; int besti = 0x7fffffff;
@@ -584,6 +590,8 @@ __global__ void pick_argmax_kernel(const float* gathered, int batch, int world, 
 // end of step: next token = argmax, position and cache length advance, argmax appended to the trace
 __global__ void advance_kernel(int32_t* tokens, int32_t* pos, int32_t* len, const int32_t* amax, int batch,
                                int32_t* trace, int32_t* trace_count, int64_t trace_cap) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   const int cnt = *trace_count;
   if (b < batch) {
@@ -604,12 +612,26 @@ static int enqueue_step(cai_session* s) {
   const int QKVW = m->qw_l + 2 * m->kw_l;
   float* x = s->x;
   float* xalt = s->x_alt;
+  auto set_rope = [&](LinearArgs& a, int l) {
+    a.epilogue = EPI_QKV_ROPE; a.rope_cs = s->rope_cs; a.rope_q_width = m->qw_l; a.rope_kv_width = m->kw_l;
+    a.rope_head_dim = c.head_dim; a.rope_kv_heads = m->kv_heads_l; a.rope_max_ctx = s->max_ctx;
+    a.k_cache = s->k_cache + (size_t)l * s->layer_stride; a.v_cache = s->v_cache + (size_t)l * s->layer_stride;
+    a.cache_len_dev = s->len_dev;
+  };
   CAI_TRY(op_embed(ctx, &m->embed, s->tokens_dev, B, x, H));
+  CAI_TRY(op_rope_table(ctx, m->theta, s->pos_dev, B, c.head_dim / 2, s->rope_cs));
+  const bool fuse_rope = !c.qk_norm;     // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
-    CAI_TRY(op_rmsnorm(ctx, x, H, L.attn_norm, s->h, H, B, H, c.rms_eps));
-    {
+    if (linear_can_fuse_norm(&L.wqkv, B)) {
+      LinearArgs a; a.w = &L.wqkv; a.x = x; a.ldx = H; a.y = s->qkv; a.ldy = QKVW; a.batch = B;
+      a.norm_gain = L.attn_norm; a.norm_eps = c.rms_eps;
+      if (fuse_rope) set_rope(a, l);
+      CAI_TRY(linear_launch(ctx, a));
+    } else {
+      CAI_TRY(op_rmsnorm(ctx, x, H, L.attn_norm, s->h, H, B, H, c.rms_eps));
       LinearArgs a; a.w = &L.wqkv; a.x = s->h; a.ldx = H; a.y = s->qkv; a.ldy = QKVW; a.batch = B;
+      if (fuse_rope) set_rope(a, l);
       CAI_TRY(linear_launch(ctx, a));
     }
     {
@@ -620,7 +642,7 @@ static int enqueue_step(cai_session* s) {
       a.head_dim = c.head_dim; a.max_ctx = s->max_ctx; a.theta = m->theta; a.pos_dev = s->pos_dev;
       a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
       a.out = s->att; a.ldo = m->qw_l; a.partial = s->partial; a.nsplit = s->nsplit;
-      CAI_TRY(attn_rope_append(ctx, a));
+      if (!fuse_rope) CAI_TRY(attn_rope_append(ctx, a));
       CAI_TRY(attn_decode(ctx, a));
     }
     // attention output projection + residual
@@ -634,10 +656,12 @@ static int enqueue_step(cai_session* s) {
       CAI_TRY(comm_allreduce(ctx, xalt, (int64_t)B * H));
       float* t = x; x = xalt; xalt = t;
     }
-    CAI_TRY(op_rmsnorm(ctx, x, H, L.ffn_norm, s->h, H, B, H, c.rms_eps));
+    const bool fuse_ffn_norm = !c.n_experts && linear_can_fuse_norm(&L.wgu, B);
+    if (!fuse_ffn_norm) CAI_TRY(op_rmsnorm(ctx, x, H, L.ffn_norm, s->h, H, B, H, c.rms_eps));
     if (!c.n_experts) {
       {
-        LinearArgs a; a.w = &L.wgu; a.x = s->h; a.ldx = H; a.y = s->act; a.ldy = m->inter_l; a.batch = B; a.epilogue = EPI_SWIGLU;
+        LinearArgs a; a.w = &L.wgu; a.x = fuse_ffn_norm ? x : s->h; a.ldx = H; a.y = s->act; a.ldy = m->inter_l; a.batch = B; a.epilogue = EPI_SWIGLU;
+        if (fuse_ffn_norm) { a.norm_gain = L.ffn_norm; a.norm_eps = c.rms_eps; }
         CAI_TRY(linear_launch(ctx, a));
       }
       if (m->tp_size == 1) {
@@ -671,22 +695,26 @@ static int enqueue_step(cai_session* s) {
       CAI_TRY(op_moe_combine(ctx, x, H, s->pair_out, H, s->gates, B, K, H));
     }
   }
-  CAI_TRY(op_rmsnorm(ctx, x, H, m->final_norm, s->h, H, B, H, c.rms_eps));
-  {
+  if (linear_can_fuse_norm(&m->lm_head, B)) {
+    LinearArgs a; a.w = &m->lm_head; a.x = x; a.ldx = H; a.y = s->logits; a.ldy = m->vocab_l; a.batch = B;
+    a.norm_gain = m->final_norm; a.norm_eps = c.rms_eps;
+    CAI_TRY(linear_launch(ctx, a));
+  } else {
+    CAI_TRY(op_rmsnorm(ctx, x, H, m->final_norm, s->h, H, B, H, c.rms_eps));
     LinearArgs a; a.w = &m->lm_head; a.x = s->h; a.ldx = H; a.y = s->logits; a.ldy = m->vocab_l; a.batch = B;
     CAI_TRY(linear_launch(ctx, a));
   }
-  CAI_TRY(op_argmax(ctx, s->logits, m->vocab_l, B, m->vocab_l, s->amax_idx, s->amax_val));
+  CAI_TRY(op_argmax(ctx, s->logits, m->vocab_l, B, m->vocab_l, s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets));
   if (m->tp_size > 1) {
-    pack_argmax_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(s->amax_idx, s->amax_val, B, m->tp_rank * m->vocab_l, s->amax_pack);
+    pdl_launch(ctx, pack_argmax_kernel, dim3((B + 127) / 128), dim3(128), 0, (const int32_t*)s->amax_idx, (const float*)s->amax_val, B, m->tp_rank * m->vocab_l, s->amax_pack);
     CAI_LAUNCHED(ctx);
     CAI_TRY(comm_allgather(ctx, s->amax_pack, s->amax_gather, (int64_t)B * 2));
-    pick_argmax_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(s->amax_gather, B, m->tp_size, s->amax_idx);
+    pdl_launch(ctx, pick_argmax_kernel, dim3((B + 127) / 128), dim3(128), 0, (const float*)s->amax_gather, B, m->tp_size, s->amax_idx);
     CAI_LAUNCHED(ctx);
   }
   if (B > 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "batch above 1024");
-  advance_kernel<<<1, ((B + 31) / 32) * 32, 0, ctx->stream>>>(s->tokens_dev, s->pos_dev, s->len_dev, s->amax_idx, B, s->trace,
-                                                              s->trace_count, s->trace_cap);
+  pdl_launch(ctx, advance_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, s->tokens_dev, s->pos_dev, s->len_dev,
+             (const int32_t*)s->amax_idx, B, s->trace, s->trace_count, s->trace_cap);
   CAI_LAUNCHED(ctx);
   if (x != s->x) return cai_fail(ctx, CAI_ERR_STATE, "internal: residual buffer parity");
   return CAI_OK;
@@ -741,7 +769,7 @@ int cai_session_destroy(cai_session* s) {
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
   void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
                   s->att, s->act, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
-                  s->amax_idx, s->amax_val, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf};
+                  s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf};
   for (void* p : bufs) if (p) cudaFree(p);
   if (s->io_pinned) cudaFreeHost(s->io_pinned);
   s->m->sessions -= 1;
@@ -785,6 +813,8 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   A((void**)&s->logits, (size_t)B * m->vocab_l * 4);
   A((void**)&s->partial, attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim) * 4);
   A((void**)&s->amax_idx, (size_t)B * 4); A((void**)&s->amax_val, (size_t)B * 4);
+  A((void**)&s->amax_part_val, (size_t)B * CAI_ARGMAX_CHUNKS * 4); A((void**)&s->amax_part_idx, (size_t)B * CAI_ARGMAX_CHUNKS * 4);
+  A((void**)&s->amax_tickets, (size_t)B * 4); A((void**)&s->rope_cs, (size_t)B * c.head_dim * 4);
   A((void**)&s->trace, (size_t)s->trace_cap * 4); A((void**)&s->trace_count, 4);
   if (c.n_experts) {
     A((void**)&s->router_logits, (size_t)B * c.n_experts * 4); A((void**)&s->gates, (size_t)B * c.top_k * 4);
@@ -801,6 +831,7 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   CAI_CUDA(ctx, cudaMemsetAsync(s->pos_dev, 0, (size_t)B * 4, ctx->stream));
   CAI_CUDA(ctx, cudaMemsetAsync(s->tokens_dev, 0, (size_t)B * 4, ctx->stream));
   CAI_CUDA(ctx, cudaMemsetAsync(s->trace_count, 0, 4, ctx->stream));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->amax_tickets, 0, (size_t)B * 4, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   *out = s;
   return CAI_OK;

@@ -9,6 +9,8 @@
 // ---------------------------------------------------------------------------
 __global__ void embed_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
                              int64_t sstride, int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   int64_t tok = tokens[b];
   if (tok < 0) tok = 0;
@@ -31,7 +33,7 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
 
 int op_embed(cai_ctx* ctx, const QWeight* t, const int32_t* tokens_dev, int batch, float* out, int64_t ld) {
   ctx->cur_family = FAM_OTHER;
-  embed_kernel<<<batch, 256, 0, ctx->stream>>>(t->type, t->codes, t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld);
+  pdl_launch(ctx, embed_kernel, dim3(batch), dim3(256), 0, t->type, (const void*)t->codes, (const __half*)t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -42,6 +44,8 @@ int op_embed(cai_ctx* ctx, const QWeight* t, const int32_t* tokens_dev, int batc
 __global__ void rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ gain,
                                float* __restrict__ y, int64_t ldy, int depth, float eps) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const float* xr = x + (int64_t)blockIdx.x * ldx;
   float* yr = y + (int64_t)blockIdx.x * ldy;
   float ss = 0.f;
@@ -54,7 +58,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, int64_t ldx, const f
 int op_rmsnorm(cai_ctx* ctx, const float* x, int64_t ldx, const float* gain, float* y, int64_t ldy, int tokens, int depth, float eps) {
   ctx->cur_family = FAM_OTHER;
   int threads = depth >= 2048 ? 512 : (depth >= 512 ? 256 : 128);
-  rmsnorm_kernel<<<tokens, threads, 0, ctx->stream>>>(x, ldx, gain, y, ldy, depth, eps);
+  pdl_launch(ctx, rmsnorm_kernel, dim3(tokens), dim3(threads), 0, x, ldx, gain, y, ldy, depth, eps);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -129,6 +133,8 @@ int op_swiglu(cai_ctx* ctx, const float* x, int64_t ldx, float* y, int64_t ldy, 
 __global__ void topk_gate_kernel(const float* __restrict__ logits, int tokens, int n_experts, int top_k, int renorm,
                                  int32_t* __restrict__ ids, float* __restrict__ gates) {
   extern __shared__ float probs_all[];
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= tokens) return;
@@ -175,31 +181,41 @@ int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, i
   const int warps = 4;
   const size_t smem = (size_t)warps * n_experts * sizeof(float);
   if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "router with %d experts exceeds the kernel's shared memory", n_experts);
-  topk_gate_kernel<<<(tokens + warps - 1) / warps, warps * 32, smem, ctx->stream>>>(logits, tokens, n_experts, top_k, renorm, ids, gates);
+  pdl_launch(ctx, topk_gate_kernel, dim3((tokens + warps - 1) / warps), dim3(warps * 32), smem, logits, tokens, n_experts, top_k, renorm, ids, gates);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
 
 // ---------------------------------------------------------------------------
-// argmax: first index of the maximum of each row.
+// argmax: first index of the maximum of each row. The row is cut into ARGMAX_CHUNKS pieces, one CTA
+// each; the last CTA of a row to finish (atomic ticket, no waiting) merges the per-chunk winners in
+// chunk order, so the result does not depend on timing. Tickets reset themselves.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void argmax_merge(float& best, int& besti, float ob, int oi) {
+  if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+}
 __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int n, int32_t* __restrict__ out_idx,
-                              float* __restrict__ out_val) {
+                              float* __restrict__ out_val, float* __restrict__ part_val, int* __restrict__ part_idx,
+                              int* __restrict__ tickets) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  const float* row = logits + (int64_t)blockIdx.x * ld;
+  __shared__ int s_last;
+  pdl_trigger();
+  pdl_wait();
+  const int row_id = blockIdx.y, chunk = blockIdx.x, chunks = gridDim.x;
+  const float* row = logits + (int64_t)row_id * ld;
+  const int per = (n + chunks - 1) / chunks;
+  const int lo = chunk * per;
+  int hi = lo + per; if (hi > n) hi = n;
   float best = -INFINITY; int besti = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = row[i];
     if (v > best) { best = v; besti = i; }      // strided scan keeps the first index per thread
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-    if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, besti, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, besti, o));
   if (lane == 0) { sv[warp] = best; si[warp] = besti; }
   __syncthreads();
   if (warp == 0) {
@@ -207,21 +223,59 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int 
     best = (lane < nw) ? sv[lane] : -INFINITY;
     besti = (lane < nw) ? si[lane] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+      argmax_merge(best, besti, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, besti, o));
     if (lane == 0) {
-      if (besti == 0x7fffffff) besti = 0;        // every entry NaN or -inf: index 0, like a scan that never updates
-      out_idx[blockIdx.x] = besti;
-      if (out_val) out_val[blockIdx.x] = best;
+      __stcg(part_val + (size_t)row_id * chunks + chunk, best);
+      __stcg(part_idx + (size_t)row_id * chunks + chunk, besti);
+      __threadfence();
+      const int old = atomicAdd(tickets + row_id, 1);
+      s_last = (old == chunks - 1) ? 1 : 0;
+      if (old == chunks - 1) tickets[row_id] = 0;
     }
   }
+  __syncthreads();
+  if (!s_last || warp != 0) return;
+  __threadfence();
+  best = -INFINITY; besti = 0x7fffffff;
+  for (int c = lane; c < chunks; c += 32)
+    argmax_merge(best, besti, __ldcg(part_val + (size_t)row_id * chunks + c), __ldcg(part_idx + (size_t)row_id * chunks + c));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, besti, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, besti, o));
+  if (lane == 0) {
+    if (besti == 0x7fffffff) besti = 0;          // every entry NaN or -inf: index 0, like a scan that never updates
+    out_idx[row_id] = besti;
+    if (out_val) out_val[row_id] = best;
+  }
 }
-int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val) {
+int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val,
+              float* part_val, int* part_idx, int* tickets) {
   ctx->cur_family = FAM_OTHER;
-  argmax_kernel<<<batch, 1024, 0, ctx->stream>>>(logits, ld, n, out_idx, out_val);
+  int chunks = (n + 2047) / 2048;
+  if (chunks > CAI_ARGMAX_CHUNKS) chunks = CAI_ARGMAX_CHUNKS;
+  if (chunks < 1) chunks = 1;
+  pdl_launch(ctx, argmax_kernel, dim3(chunks, batch), dim3(256), 0, logits, ld, n, out_idx, out_val, part_val, part_idx, tickets);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// cos/sin of (float)pos * theta[k] for every sequence of the step: the same values serve every layer
+// and head, so the full-range sincosf (slow for large angles) runs once per step, not once per layer.
+__global__ void rope_table_kernel(const float* __restrict__ theta, const int32_t* __restrict__ pos, int half, float* __restrict__ cs) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x;
+  for (int k = threadIdx.x; k < half; k += blockDim.x) {
+    float s, c;
+    sincosf((float)pos[b] * theta[k], &s, &c);
+    cs[((size_t)b * half + k) * 2] = c;
+    cs[((size_t)b * half + k) * 2 + 1] = s;
+  }
+}
+int op_rope_table(cai_ctx* ctx, const float* theta_dev, const int32_t* pos_dev, int batch, int half, float* cs_dev) {
+  ctx->cur_family = FAM_OTHER;
+  pdl_launch(ctx, rope_table_kernel, dim3(batch), dim3(128), 0, theta_dev, pos_dev, half, cs_dev);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -231,6 +285,8 @@ int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, i
 // ---------------------------------------------------------------------------
 __global__ void moe_combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ pair_out, int64_t ldp,
                                    const float* __restrict__ gates, int top_k, int depth) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= depth) return;
@@ -243,7 +299,7 @@ int op_moe_combine(cai_ctx* ctx, float* x, int64_t ldx, const float* pair_out, i
                    int tokens, int top_k, int depth) {
   ctx->cur_family = FAM_OTHER;
   dim3 grid((depth + 255) / 256, tokens);
-  moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(x, ldx, pair_out, ldp, gates, top_k, depth);
+  pdl_launch(ctx, moe_combine_kernel, grid, dim3(256), 0, x, ldx, pair_out, ldp, gates, top_k, depth);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
