@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
   const int kpart = warp - group * p.ksplit;
 
   pdl_trigger();
-  if (p.expert_ids) pdl_wait();      // the expert choice itself comes from the previous kernel
+  pdl_wait();
 
   // operand selection
   const char* codes = (const char*)p.codes;
@@ -51,72 +51,12 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
   }
   const int64_t K = p.k;
 
-  // rows of this warp
-  const int64_t gidx = (int64_t)blockIdx.x * groups_per_cta + group;
-  int64_t unit0;
-  int64_t rows[RPW];
-  if (p.epi == EPI_SWIGLU) {
-    const int64_t half = p.n >> 1;
-    unit0 = gidx * (RPW / 2);
+  // Activations -> shared memory ONCE per CTA (the CTA then walks many row blocks), with the per-token
+  // RMSNorm of the reference applied on the way when asked: y = gain * (x * inv). Rows beyond the batch
+  // repeat row 0 and are never stored.
+  const float* xbase[NB];
 #pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      int64_t j = unit0 + (r >> 1);
-      if (j >= half) j = half - 1;
-      rows[r] = (r & 1) ? half + j : j;
-    }
-  } else {
-    unit0 = gidx * RPW;
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      int64_t row = unit0 + r;
-      if (row >= p.n) row = p.n - 1;
-      rows[r] = row;
-    }
-  }
-
-  f32x2_t acc2[RPW][NB];
-#pragma unroll
-  for (int r = 0; r < RPW; ++r)
-#pragma unroll
-    for (int b = 0; b < NB; ++b) acc2[r][b] = 0ull;
-
-  // codes per lane chunk (one 16-byte load) and per warp stride
-  constexpr int CHUNK = (TYPE == CAI_TYPE_Q8_0) ? 16 : 32;
-  constexpr int CODE_SHIFT = (TYPE == CAI_TYPE_Q8_0) ? 0 : 1;     // bytes = codes >> shift
-  const int64_t row_bytes = K >> CODE_SHIFT;
-  const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
-  int64_t k0 = ((int64_t)kpart * 32 + lane) * CHUNK;
-
-  // Per-row pointers advance by a fixed stride: no address multiplications inside the loop.
-  const int64_t stride_b = stride >> CODE_SHIFT;                  // bytes of codes per stride
-  const int64_t stride_s = stride >> 5;                           // scales per stride
-  const int iters = (k0 < K) ? (int)((K - k0 + stride - 1) / stride) : 0;
-  const char* wp[RPW];
-  const unsigned short* sp[RPW];
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    wp[r] = codes + rows[r] * row_bytes + (k0 >> CODE_SHIFT);
-    sp[r] = (const unsigned short*)scales + rows[r] * p.sstride + (k0 >> 5);
-  }
-  // The first weight loads do not depend on the previous kernel: they are in flight while it finishes.
-  int4 wv[RPW], wn[RPW];
-  uint32_t sv[RPW], sn[RPW];
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) { wn[r] = make_int4(0, 0, 0, 0); sn[r] = 0; }
-  if (iters > 0) {
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      wn[r] = ldg_stream16(wp[r]);
-      sn[r] = __ldg(sp[r]);
-    }
-  }
-  if (!p.expert_ids) pdl_wait();     // from here on the activations of the previous kernel are read
-
-  // activations -> shared memory (rows beyond the batch repeat row 0 and are never stored), with the
-  // per-token RMSNorm of the reference applied on the way when asked: y = gain * (x * inv)
-  const float* xr[NB];
-#pragma unroll
-  for (int b = 0; b < NB; ++b) xr[b] = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
+  for (int b = 0; b < NB; ++b) xbase[b] = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
   float* red = smem_f;
   if (p.x_in_smem) {
     for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
@@ -126,7 +66,7 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
       *(float4*)(smem_f + i) = *(const float4*)(x + (int64_t)bb * p.ldx + c);
     }
     red = smem_f + (int64_t)NB * K;
-    float* nred = red + (size_t)(blockDim.x >> 5) * (RPW * NB);
+    float* nred = red + (size_t)warps_per_cta * (RPW * NB);
     __syncthreads();
     if (p.norm_gain) {
 #pragma unroll
@@ -141,95 +81,160 @@ __global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
       __syncthreads();
     }
 #pragma unroll
-    for (int b = 0; b < NB; ++b) xr[b] = smem_f + (int64_t)b * K;
+    for (int b = 0; b < NB; ++b) xbase[b] = smem_f + (int64_t)b * K;
   }
 
-#pragma unroll
-  for (int b = 0; b < NB; ++b) xr[b] += k0;
-  for (int it = 0; it < iters; ++it) {
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) { wv[r] = wn[r]; sv[r] = sn[r]; }
-    if (it + 1 < iters) {
+  // codes per lane chunk (one 16-byte load) and per warp stride
+  constexpr int CHUNK = (TYPE == CAI_TYPE_Q8_0) ? 16 : 32;
+  constexpr int CODE_SHIFT = (TYPE == CAI_TYPE_Q8_0) ? 0 : 1;     // bytes = codes >> shift
+  const int64_t row_bytes = K >> CODE_SHIFT;
+  const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
+  const int64_t stride_b = stride >> CODE_SHIFT;                  // bytes of codes per stride
+  const int64_t stride_s = stride >> 5;                           // scales per stride
+  const int64_t k_first = ((int64_t)kpart * 32 + lane) * CHUNK;
+  const int iters = (k_first < K) ? (int)((K - k_first + stride - 1) / stride) : 0;
+  const bool swiglu = (p.epi == EPI_SWIGLU);
+  const int64_t units_total = swiglu ? (p.n >> 1) : p.n;
+  const int units_per_group = swiglu ? (RPW / 2) : RPW;
+
+  // persistent: this CTA takes row blocks blockIdx.x, blockIdx.x + gridDim.x, ...
+  for (int64_t cb = blockIdx.x; cb < p.cta_blocks; cb += gridDim.x) {
+    const int64_t gidx = cb * groups_per_cta + group;
+    const int64_t unit0 = gidx * units_per_group;
+    int64_t rows[RPW];
+    if (swiglu) {
+      const int64_t half = p.n >> 1;
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        wp[r] += stride_b;
-        sp[r] += stride_s;
+        int64_t j = unit0 + (r >> 1);
+        if (j >= half) j = half - 1;
+        rows[r] = (r & 1) ? half + j : j;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        int64_t row = unit0 + r;
+        if (row >= p.n) row = p.n - 1;
+        rows[r] = row;
+      }
+    }
+    // per-row pointers advance by a fixed stride: no address multiplications inside the loop
+    const char* wp[RPW];
+    const unsigned short* sp[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      wp[r] = codes + rows[r] * row_bytes + (k_first >> CODE_SHIFT);
+      sp[r] = (const unsigned short*)scales + rows[r] * p.sstride + (k_first >> 5);
+    }
+    int4 wv[RPW], wn[RPW];
+    uint32_t sv[RPW], sn[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) { wn[r] = make_int4(0, 0, 0, 0); sn[r] = 0; }
+    if (iters > 0) {
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
         wn[r] = ldg_stream16(wp[r]);
         sn[r] = __ldg(sp[r]);
       }
     }
-    f32x2_t part[RPW][NB];
+    f32x2_t acc2[RPW][NB];
 #pragma unroll
     for (int r = 0; r < RPW; ++r)
 #pragma unroll
-      for (int b = 0; b < NB; ++b) part[r][b] = 0ull;
+      for (int b = 0; b < NB; ++b) acc2[r][b] = 0ull;
+    const float* xr[NB];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (TYPE == CAI_TYPE_Q8_0) {
-        float4 xv[NB];
+    for (int b = 0; b < NB; ++b) xr[b] = xbase[b] + k_first;
+
+    for (int it = 0; it < iters; ++it) {
 #pragma unroll
-        for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + 4 * i);
-#pragma unroll
-        for (int r = 0; r < RPW; ++r) {
-          const uint32_t w = ((const uint32_t*)&wv[r])[i];
-#pragma unroll
-          for (int b = 0; b < NB; ++b) part[r][b] = q8_word_fma(w, xv[b], part[r][b]);
-        }
-      } else {
-        float4 xlo[NB], xhi[NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-          xlo[b] = *(const float4*)(xr[b] + 4 * i);
-          xhi[b] = *(const float4*)(xr[b] + 16 + 4 * i);
-        }
+      for (int r = 0; r < RPW; ++r) { wv[r] = wn[r]; sv[r] = sn[r]; }
+      if (it + 1 < iters) {
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
-          const uint32_t w = ((const uint32_t*)&wv[r])[i];
-#pragma unroll
-          for (int b = 0; b < NB; ++b) part[r][b] = q4_word_fma(w, xlo[b], xhi[b], part[r][b]);
+          wp[r] += stride_b;
+          sp[r] += stride_s;
+          wn[r] = ldg_stream16(wp[r]);
+          sn[r] = __ldg(sp[r]);
         }
       }
-    }
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      const float d = half_bits_to_float(sv[r]);
-      const f32x2_t d2 = pack2(d, d);
-#pragma unroll
-      for (int b = 0; b < NB; ++b) acc2[r][b] = fma2(d2, part[r][b], acc2[r][b]);
-    }
-#pragma unroll
-    for (int b = 0; b < NB; ++b) xr[b] += stride;
-  }
-
-  // lanes -> one value per (row, batch)
-  float acc[RPW][NB];
-#pragma unroll
-  for (int r = 0; r < RPW; ++r)
-#pragma unroll
-    for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(sum2(acc2[r][b]));
-
-  if (p.ksplit > 1) {
-    // fixed-order combine of the KSPLIT warps of a group through shared memory
-    float* slot = red + (size_t)warp * (RPW * NB);
-    if (lane == 0) {
+      f32x2_t part[RPW][NB];
 #pragma unroll
       for (int r = 0; r < RPW; ++r)
 #pragma unroll
-        for (int b = 0; b < NB; ++b) slot[r * NB + b] = acc[r][b];
+        for (int b = 0; b < NB; ++b) part[r][b] = 0ull;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (TYPE == CAI_TYPE_Q8_0) {
+          float4 xv[NB];
+#pragma unroll
+          for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + 4 * i);
+#pragma unroll
+          for (int r = 0; r < RPW; ++r) {
+            const uint32_t w = ((const uint32_t*)&wv[r])[i];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) part[r][b] = q8_word_fma(w, xv[b], part[r][b]);
+          }
+        } else {
+          float4 xlo[NB], xhi[NB];
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            xlo[b] = *(const float4*)(xr[b] + 4 * i);
+            xhi[b] = *(const float4*)(xr[b] + 16 + 4 * i);
+          }
+#pragma unroll
+          for (int r = 0; r < RPW; ++r) {
+            const uint32_t w = ((const uint32_t*)&wv[r])[i];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) part[r][b] = q4_word_fma(w, xlo[b], xhi[b], part[r][b]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const float d = half_bits_to_float(sv[r]);
+        const f32x2_t d2 = pack2(d, d);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc2[r][b] = fma2(d2, part[r][b], acc2[r][b]);
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) xr[b] += stride;
     }
-    __syncthreads();
-    if (kpart != 0) return;
+
+    // lanes -> one value per (row, batch)
+    float acc[RPW][NB];
 #pragma unroll
     for (int r = 0; r < RPW; ++r)
 #pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        float s = 0.f;
-        for (int q = 0; q < p.ksplit; ++q) s += red[(size_t)(group * p.ksplit + q) * (RPW * NB) + r * NB + b];
-        acc[r][b] = s;
+      for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(sum2(acc2[r][b]));
+
+    bool store = (unit0 < units_total);
+    if (p.ksplit > 1) {
+      // fixed-order combine of the KSPLIT warps of a group through shared memory
+      float* slot = red + (size_t)warp * (RPW * NB);
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+          for (int b = 0; b < NB; ++b) slot[r * NB + b] = acc[r][b];
       }
+      __syncthreads();
+      if (kpart == 0) {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r)
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            float sum = 0.f;
+            for (int q = 0; q < p.ksplit; ++q) sum += red[(size_t)(group * p.ksplit + q) * (RPW * NB) + r * NB + b];
+            acc[r][b] = sum;
+          }
+      } else {
+        store = false;
+      }
+      __syncthreads();     // the slots are rewritten by the next row block
+    }
+    if (store) gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
   }
-  if (gidx * ((p.epi == EPI_SWIGLU) ? (RPW / 2) : RPW) >= ((p.epi == EPI_SWIGLU) ? (p.n >> 1) : p.n)) return;
-  gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
 }
 
 // Generic path: F32 / F16 weights, any K (scalar loads), warp per row (pair of rows for SwiGLU).
@@ -299,10 +304,27 @@ static int env_int(const char* name, int dflt) {
 
 template <int TYPE, int NB, int RPW>
 static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
+  // (single caller thread per context: the function-local cache below needs no lock)
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
+  // persistent grid: exactly the CTAs that can be resident at once (a host-side query, cached per
+  // instantiation and shared-memory size), each walking several row blocks with the activations staged once
+  static int cached_blocks = 0;
+  static size_t cached_smem = (size_t)-1;
+  if (cached_smem != smem) {
+    int nblk = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW>, threads, smem);
+    if (e != cudaSuccess) return e;
+    cached_blocks = nblk < 1 ? 1 : nblk;
+    cached_smem = smem;
+  }
+  const int64_t resident = (int64_t)ctx->sm_count * cached_blocks;
+  int64_t gx = grid.x;
+  if (gx * grid.y > resident) gx = resident / grid.y;
+  if (gx < 1) gx = 1;
+  grid.x = (unsigned)gx;
   return pdl_launch(ctx, gemv_quant_kernel<TYPE, NB, RPW>, grid, dim3(threads), smem, p);
 }
 template <int TYPE, int NB>
@@ -406,7 +428,10 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   const int groups_per_cta = wpc / ksplit;
   const int units_per_group = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;
   const int64_t groups = (units + units_per_group - 1) / units_per_group;
-  dim3 grid((unsigned)((groups + groups_per_cta - 1) / groups_per_cta), indexed ? a.batch : (unsigned)((a.batch + nb - 1) / nb));
+  p.cta_blocks = (groups + groups_per_cta - 1) / groups_per_cta;
+  // persistent grid: at most a few CTAs per SM, each walking several row blocks with the activations staged once
+  const int64_t ydim = indexed ? a.batch : (a.batch + nb - 1) / nb;
+  dim3 grid((unsigned)p.cta_blocks, (unsigned)ydim);     // x is cut down to the resident CTA count at launch
   // activations in shared memory when they fit beside a healthy number of resident CTAs
   const size_t x_bytes = (size_t)nb * (size_t)w->k * 4;
   p.x_in_smem = (x_bytes <= (size_t)env_int("CAI_GEMV_XSMEM", 64 * 1024)) ? 1 : 0;

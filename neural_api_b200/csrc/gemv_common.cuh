@@ -19,6 +19,7 @@ struct GemvParams {
   int act;
   int epi;
   int ksplit;       // warps cooperating on one row group
+  int64_t cta_blocks;   // row blocks of one CTA's worth of rows; CTAs stride over them
   int x_in_smem;    // activations staged in shared memory by the CTA
   // indexed (expert bank) mode
   const void* const* bank_codes;
