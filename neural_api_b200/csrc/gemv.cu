@@ -18,8 +18,8 @@
 #include "gemv_common.cuh"
 #include <stdlib.h>
 
-template <int TYPE, int NB, int RPW>
-__global__ void __launch_bounds__(256) gemv_quant_kernel(const GemvParams p) {
+template <int TYPE, int NB, int RPW, int MINB>
+__global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams p) {
   extern __shared__ __align__(16) float smem_f[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -302,11 +302,11 @@ static int env_int(const char* name, int dflt) {
   return (s && *s) ? atoi(s) : dflt;
 }
 
-template <int TYPE, int NB, int RPW>
-static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
+template <int TYPE, int NB, int RPW, int MINB>
+static cudaError_t launch_one_b(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
   // (single caller thread per context: the function-local cache below needs no lock)
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   // persistent grid: exactly the CTAs that can be resident at once (a host-side query, cached per
@@ -315,7 +315,7 @@ static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int 
   static size_t cached_smem = (size_t)-1;
   if (cached_smem != smem) {
     int nblk = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW>, threads, smem);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW, MINB>, threads, smem);
     if (e != cudaSuccess) return e;
     cached_blocks = nblk < 1 ? 1 : nblk;
     cached_smem = smem;
@@ -325,7 +325,15 @@ static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int 
   if (gx * grid.y > resident) gx = resident / grid.y;
   if (gx < 1) gx = 1;
   grid.x = (unsigned)gx;
-  return pdl_launch(ctx, gemv_quant_kernel<TYPE, NB, RPW>, grid, dim3(threads), smem, p);
+  return pdl_launch(ctx, gemv_quant_kernel<TYPE, NB, RPW, MINB>, grid, dim3(threads), smem, p);
+}
+// MINB = CTAs per SM the compiler must leave room for (register cap). Measured on B200 for the batch-1,
+// 4-rows-per-warp kernel: 2 (<= 128 registers, none spilled) 4.4 TB/s; 3 (80 registers, spills) 3.5 TB/s;
+// 1 (no cap) 2.7 TB/s. CAI_GEMV_MINB=3 selects the tighter cap for experiments.
+template <int TYPE, int NB, int RPW>
+static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
+  if (NB == 1 && RPW == 4 && env_int("CAI_GEMV_MINB", 2) == 3) return launch_one_b<TYPE, NB, RPW, (NB == 1 && RPW == 4) ? 3 : 2>(ctx, p, grid, threads, smem);
+  return launch_one_b<TYPE, NB, RPW, (NB <= 2) ? 2 : 1>(ctx, p, grid, threads, smem);
 }
 template <int TYPE, int NB>
 static cudaError_t launch_quant(cai_ctx* ctx, const GemvParams& p, int rpw, dim3 grid, int threads, size_t smem) {
@@ -414,7 +422,9 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     const int upg = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;
     const int64_t groups = (units + upg - 1) / upg;
     ksplit = 1;
-    while (ksplit < 8 && groups * ksplit < target_groups && k_iters_1 >= 2 * ksplit) ksplit *= 2;
+    while (ksplit < 8 && groups * ksplit * 2 <= target_groups && k_iters_1 >= 2 * ksplit) ksplit *= 2;
+    // long rows: let the warps of a CTA share them (more loads in flight per row) while each keeps >= 4 strides
+    while (ksplit < 8 && k_iters_1 >= 12 * ksplit && groups * ksplit < 4 * target_groups) ksplit *= 2;
   }
   rpw = env_int("CAI_GEMV_RPW", rpw);
   ksplit = env_int("CAI_GEMV_KSPLIT", ksplit);
