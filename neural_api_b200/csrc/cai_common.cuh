@@ -210,6 +210,11 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a);
 int comm_allreduce(cai_ctx* ctx, float* buf, int64_t count);
 int comm_allgather(cai_ctx* ctx, const float* send, float* recv, int64_t count_per_rank);
 int comm_world(cai_ctx* ctx);
+struct cai_tp_ar;   // one-shot all-reduce over peer memory (comm.cu)
+int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out);   // collective; *out stays NULL when peers cannot be mapped
+void comm_ar_destroy(cai_ctx* ctx, cai_tp_ar* ar);                                 // collective
+float* comm_ar_slot(cai_tp_ar* ar, int site);
+int comm_ar_reduce(cai_ctx* ctx, cai_tp_ar* ar, int site, int64_t n, const float* resid, float* out);
 void comm_destroy(cai_ctx* ctx);
 
 // ---------------------------------------------------------------------------

@@ -38,6 +38,173 @@ int comm_allgather(cai_ctx* ctx, const float* send, float* recv, int64_t count_p
   return CAI_OK;
 }
 
+// ---------------------------------------------------------------------------
+// One-shot all-reduce over NVLink peer memory, fused with the residual add.
+//
+// Tensor-parallel decode sums a [batch, hidden] partial result over the ranks twice per layer; at
+// batch 1 that is 20 KB per rank, where a library all-reduce costs its fixed latency. Here every rank
+// keeps its partial results in a buffer the other ranks map (CUDA IPC); the row-parallel GEMV writes
+// its partial straight into that buffer, then ONE small kernel per rank
+//   1. stores this call's sequence number into every rank's flag word (a remote store),
+//   2. waits (bounded) until all ranks' flags show the number,
+//   3. loads every rank's partial with plain peer loads and adds them in rank order to the residual.
+// All ranks add in the same order, so they stay bit-identical. Every call site of a step owns its slot
+// of the buffer: a slot is rewritten one step later, after at least one more all-reduce, which a rank
+// only passes once every peer has finished reading the earlier slots. No cluster-scope copies, no
+// switch reduction: plain ld/st over mapped peer memory.
+// ---------------------------------------------------------------------------
+struct cai_tp_ar {
+  char* block = nullptr;          // [flags: 64 ints][slots: sites * max_elems floats], cudaMalloc'd, IPC-exported
+  void* peer_block[8] = {nullptr};
+  int* seq_dev = nullptr;         // calls completed so far
+  int* ticket_dev = nullptr;
+  int sites = 0;
+  int64_t max_elems = 0;
+  int rank = 0, world = 1;
+};
+static const size_t AR_FLAG_BYTES = 256;
+
+struct ArParams {
+  const float* peer_slot[8];
+  int* peer_flags[8];
+  int* my_flags;
+  int* seq;
+  int* ticket;
+  int rank, world, n4;
+  const float4* resid;
+  float4* out;
+  int* err;
+};
+
+__global__ void tp_allreduce_kernel(const ArParams p) {
+  __shared__ int s_seq;
+  if (threadIdx.x == 0) s_seq = *(volatile int*)p.seq + 1;
+  __syncthreads();
+  const int seq = s_seq;
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    __threadfence_system();                                   // this rank's partial (written by the previous kernel) first
+    *(volatile int*)(p.peer_flags[threadIdx.x] + p.rank) = seq;
+  }
+  if (threadIdx.x < p.world) {
+    const volatile int* f = (const volatile int*)(p.my_flags + threadIdx.x);
+    bool ok = false;
+    for (int spin = 0; spin < (1 << 26); ++spin) {
+      if (*f >= seq) { ok = true; break; }
+    }
+    if (!ok) *p.err = 1;                                      // give up: the host sees the error word
+  }
+  __syncthreads();
+  __threadfence_system();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.n4; i += gridDim.x * blockDim.x) {
+    float4 acc = p.resid ? p.resid[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < p.world; ++r) {
+      float4 v;
+      const float4* src = (const float4*)p.peer_slot[r] + i;
+      asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    p.out[i] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(p.ticket, 1);
+    if (old == (int)gridDim.x - 1) { *p.ticket = 0; *(volatile int*)p.seq = seq; }
+  }
+}
+
+void comm_ar_destroy(cai_ctx* ctx, cai_tp_ar* ar) {
+  if (!ar) return;
+  // every rank must have finished reading before any rank unmaps or frees
+  if (ctx->comm && ar->seq_dev) {
+    ncclAllReduce(ar->seq_dev, ar->seq_dev, 1, ncclInt, ncclMax, ctx->comm->comm, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+  }
+  for (int r = 0; r < ar->world; ++r)
+    if (r != ar->rank && ar->peer_block[r]) cudaIpcCloseMemHandle(ar->peer_block[r]);
+  if (ar->block) cudaFree(ar->block);
+  if (ar->seq_dev) cudaFree(ar->seq_dev);
+  if (ar->ticket_dev) cudaFree(ar->ticket_dev);
+  delete ar;
+}
+
+// Collective over the communicator: every rank calls it with the same arguments.
+int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out) {
+  *out = nullptr;
+  if (!ctx->comm) return cai_fail(ctx, CAI_ERR_STATE, "communicator not initialised");
+  const char* mode = getenv("CAI_TP_ALLREDUCE");
+  if (mode && !strcmp(mode, "nccl")) return CAI_OK;           // caller falls back to ncclAllReduce
+  const int world = ctx->comm->world, rank = ctx->comm->rank;
+  if (world > 8 || (max_elems % 4)) return CAI_OK;
+  cai_tp_ar* ar = new cai_tp_ar();
+  ar->sites = sites; ar->max_elems = max_elems; ar->rank = rank; ar->world = world;
+  const size_t bytes = AR_FLAG_BYTES + (size_t)sites * (size_t)max_elems * sizeof(float);
+  cudaIpcMemHandle_t mine;
+  cudaIpcMemHandle_t* all_dev = nullptr;
+  std::vector<cudaIpcMemHandle_t> all((size_t)world);
+  int ok = 1;
+  if (cudaMalloc((void**)&ar->block, bytes) != cudaSuccess || cudaMemset(ar->block, 0, bytes) != cudaSuccess ||
+      cudaMalloc((void**)&ar->seq_dev, 4) != cudaSuccess || cudaMemset(ar->seq_dev, 0, 4) != cudaSuccess ||
+      cudaMalloc((void**)&ar->ticket_dev, 4) != cudaSuccess || cudaMemset(ar->ticket_dev, 0, 4) != cudaSuccess ||
+      cudaIpcGetMemHandle(&mine, ar->block) != cudaSuccess ||
+      cudaMalloc((void**)&all_dev, sizeof(cudaIpcMemHandle_t) * (size_t)world) != cudaSuccess)
+    ok = 0;
+  cudaGetLastError();
+  // the handle exchange is collective: run it even after a local failure so that no rank is left waiting
+  if (all_dev) {
+    if (ok) cudaMemcpy(all_dev + rank, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    if (ncclAllGather(all_dev + rank, all_dev, sizeof(cudaIpcMemHandle_t), ncclInt8, ctx->comm->comm, ctx->stream) != ncclSuccess) ok = 0;
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) ok = 0;
+    if (ok) cudaMemcpy(all.data(), all_dev, sizeof(cudaIpcMemHandle_t) * (size_t)world, cudaMemcpyDeviceToHost);
+    cudaFree(all_dev);
+  }
+  if (ok) {
+    ar->peer_block[rank] = ar->block;
+    for (int r = 0; r < world && ok; ++r) {
+      if (r == rank) continue;
+      if (cudaIpcOpenMemHandle(&ar->peer_block[r], all[(size_t)r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { ar->peer_block[r] = nullptr; ok = 0; }
+    }
+    cudaGetLastError();
+  }
+  // agree on the outcome: one rank without peer mappings sends everybody to the library path
+  int* agree = nullptr;
+  int all_ok = 0;
+  if (cudaMalloc((void**)&agree, 4) == cudaSuccess) {
+    cudaMemcpy(agree, &ok, 4, cudaMemcpyHostToDevice);
+    ncclAllReduce(agree, agree, 1, ncclInt, ncclMin, ctx->comm->comm, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(&all_ok, agree, 4, cudaMemcpyDeviceToHost);
+    cudaFree(agree);
+  }
+  if (!all_ok) { comm_ar_destroy(ctx, ar); return CAI_OK; }
+  *out = ar;
+  return CAI_OK;
+}
+
+float* comm_ar_slot(cai_tp_ar* ar, int site) {
+  return (float*)(ar->block + AR_FLAG_BYTES) + (size_t)site * (size_t)ar->max_elems;
+}
+
+// out = resid + sum over ranks of slot[site] (resid may be NULL); n floats, n % 4 == 0.
+int comm_ar_reduce(cai_ctx* ctx, cai_tp_ar* ar, int site, int64_t n, const float* resid, float* out) {
+  if (site < 0 || site >= ar->sites || n > ar->max_elems || (n % 4)) return cai_fail(ctx, CAI_ERR_INVALID, "all-reduce slot %d of %d, %lld elements", site, ar->sites, (long long)n);
+  ArParams p;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < ar->world; ++r) {
+    p.peer_flags[r] = (int*)ar->peer_block[r];
+    p.peer_slot[r] = (const float*)((char*)ar->peer_block[r] + AR_FLAG_BYTES) + (size_t)site * (size_t)ar->max_elems;
+  }
+  p.my_flags = (int*)ar->block; p.seq = ar->seq_dev; p.ticket = ar->ticket_dev;
+  p.rank = ar->rank; p.world = ar->world; p.n4 = (int)(n / 4);
+  p.resid = (const float4*)resid; p.out = (float4*)out; p.err = ctx->err_flag;
+  int blocks = (p.n4 + 255) / 256;
+  if (blocks > 16) blocks = 16;
+  if (blocks < 1) blocks = 1;
+  ctx->cur_family = FAM_COMM;
+  tp_allreduce_kernel<<<blocks, 256, 0, ctx->stream>>>(p);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
 extern "C" {
 
 int cai_comm_unique_id(unsigned char out_id[128]) {

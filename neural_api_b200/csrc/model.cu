@@ -562,6 +562,7 @@ struct cai_session {
   float *amax_pack = nullptr, *amax_gather = nullptr, *logits_gather = nullptr;
   int32_t* trace = nullptr; int32_t* trace_count = nullptr; int64_t trace_cap = 0;
   int32_t* prefill_buf = nullptr; int64_t prefill_cap = 0;
+  cai_tp_ar* ar = nullptr;                            // peer-memory all-reduce (tensor parallel), NULL = NCCL
   cudaGraphExec_t graph_exec = nullptr;
   int64_t graph_kernels = 0;
   bool use_graph = true;
@@ -649,6 +650,12 @@ static int enqueue_step(cai_session* s) {
     if (m->tp_size == 1) {
       LinearArgs a; a.w = &L.wo; a.x = s->att; a.ldx = m->qw_l; a.y = x; a.ldy = H; a.batch = B; a.epilogue = EPI_RESID; a.resid = x;
       CAI_TRY(linear_launch(ctx, a));
+    } else if (s->ar) {
+      // partial result straight into the peer-visible slot, then one kernel: x_new = x + sum over ranks
+      LinearArgs a; a.w = &L.wo; a.x = s->att; a.ldx = m->qw_l; a.y = comm_ar_slot(s->ar, 2 * l); a.ldy = H; a.batch = B;
+      CAI_TRY(linear_launch(ctx, a));
+      CAI_TRY(comm_ar_reduce(ctx, s->ar, 2 * l, (int64_t)B * H, x, xalt));
+      float* t = x; x = xalt; xalt = t;
     } else {
       LinearArgs a; a.w = &L.wo; a.x = s->att; a.ldx = m->qw_l; a.y = xalt; a.ldy = H; a.batch = B;
       if (m->tp_rank == 0) { a.epilogue = EPI_RESID; a.resid = x; }
@@ -667,6 +674,11 @@ static int enqueue_step(cai_session* s) {
       if (m->tp_size == 1) {
         LinearArgs a; a.w = &L.wdown; a.x = s->act; a.ldx = m->inter_l; a.y = x; a.ldy = H; a.batch = B; a.epilogue = EPI_RESID; a.resid = x;
         CAI_TRY(linear_launch(ctx, a));
+      } else if (s->ar) {
+        LinearArgs a; a.w = &L.wdown; a.x = s->act; a.ldx = m->inter_l; a.y = comm_ar_slot(s->ar, 2 * l + 1); a.ldy = H; a.batch = B;
+        CAI_TRY(linear_launch(ctx, a));
+        CAI_TRY(comm_ar_reduce(ctx, s->ar, 2 * l + 1, (int64_t)B * H, x, xalt));
+        float* t = x; x = xalt; xalt = t;
       } else {
         LinearArgs a; a.w = &L.wdown; a.x = s->act; a.ldx = m->inter_l; a.y = xalt; a.ldy = H; a.batch = B;
         if (m->tp_rank == 0) { a.epilogue = EPI_RESID; a.resid = x; }
@@ -767,6 +779,7 @@ int cai_session_destroy(cai_session* s) {
   cudaSetDevice(s->ctx->device);
   cudaStreamSynchronize(s->ctx->stream);
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
+  if (s->ar) comm_ar_destroy(s->ctx, s->ar);
   void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
                   s->att, s->act, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
                   s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf};
@@ -824,6 +837,10 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   if (m->tp_size > 1) {
     A((void**)&s->amax_pack, (size_t)B * 2 * 4); A((void**)&s->amax_gather, (size_t)m->tp_size * B * 2 * 4);
     A((void**)&s->logits_gather, (size_t)m->tp_size * B * m->vocab_l * 4);
+  }
+  if (ok && m->tp_size > 1 && ((int64_t)B * H) % 4 == 0) {
+    // collective: every rank creates its session at the same point
+    if (comm_ar_create(ctx, 2 * c.layers, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
   }
   if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)3 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
   if (!ok) { cai_session_destroy(s); return cai_fail(ctx, CAI_ERR_OOM, "session buffers do not fit on the device"); }
