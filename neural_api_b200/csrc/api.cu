@@ -266,7 +266,7 @@ int cai_linear_forward_dev(cai_linear* lin, const float* x_dev, int batch, float
   CAI_TRY(cai_bind(ctx));
   if (act < 0 || act > 3) return cai_fail(ctx, CAI_ERR_INVALID, "activation opcode %d", act);
   LinearArgs a;
-  a.w = &lin->w; a.x = x_dev; a.ldx = lin->w.k; a.y = y_dev; a.ldy = lin->w.n; a.batch = batch; a.act = act;
+  a.w = &lin->w; a.x = x_dev; a.ldx = lin->w.k; a.y = y_dev; a.ldy = lin->w.n; a.batch = batch; a.act = act; a.path = lin->path;
   return linear_launch(ctx, a);
 }
 
@@ -324,7 +324,6 @@ int cai_linear_dequantize(cai_linear* lin, float* out_host) {
 int cai_linear_set_path(cai_linear* lin, int path) {
   if (!lin) return CAI_ERR_INVALID;
   if (path < 0 || path > 2) return cai_fail(lin->ctx, CAI_ERR_INVALID, "path %d", path);
-  if (path == 2) return cai_fail(lin->ctx, CAI_ERR_UNSUPPORTED, "the tcgen05 GEMM path is not built into this library");
   lin->path = path;
   return CAI_OK;
 }

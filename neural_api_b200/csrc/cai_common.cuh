@@ -142,6 +142,7 @@ struct LinearArgs {
   int epilogue = EPI_STORE;
   const float* resid = nullptr;  // EPI_RESID: y = resid + W x (+bias); ld = ldy
   int act = CAI_ACT_NONE;
+  int path = 0;                  // 0 auto, 1 CUDA-core GEMV only, 2 tensor-core GEMM only
   // Indexed (MoE) mode: per pair p, the weight matrix is banks[expert_ids[p]] and the
   // activation row is x + x_row[p]*ldx (x_row NULL -> p).
   const QWeight* const* bank = nullptr;  // unused (device arrays below are what kernels read)

@@ -296,6 +296,7 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
 }
 
 int gemv_tma_launch(cai_ctx* ctx, GemvParams p, int type, int nb);   // gemv_tma.cu
+int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type);      // gemm_tc.cu
 
 static int env_int(const char* name, int dflt) {
   const char* s = getenv(name);
@@ -403,6 +404,13 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     const int st = gemv_tma_launch(ctx, p, w->type, a.batch >= 3 ? 4 : a.batch);
     if (st != CAI_ERR_UNSUPPORTED) return st;
   }
+  // batches of 9..64 rows are a real contraction: tensor cores (tcgen05), unless the call needs a fused
+  // epilogue only the CUDA-core kernel has, or CAI_GEMM_TC=0
+  if (!indexed && a.batch >= 9 && a.batch <= 64 && a.path != 1 && env_int("CAI_GEMM_TC", 1) != 0) {
+    const int st = gemm_tc_launch(ctx, p, w->type);
+    if (st != CAI_ERR_UNSUPPORTED) return st;
+  }
+  if (a.path == 2) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: the tensor-core path covers batches of 9..64 rows with plain or residual epilogues");
   // batch tile
   int nb = 1;
   if (!indexed) nb = a.batch >= 5 ? 8 : (a.batch >= 3 ? 4 : (a.batch == 2 ? 2 : 1));

@@ -552,6 +552,7 @@ struct cai_session {
   std::vector<int32_t> len_host, len_snap;
   bool have_snap = false;
   float *x = nullptr, *x_alt = nullptr, *h = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
+  float* gu = nullptr;                                // [B][2*inter] un-fused up|gate (tensor-core batches)
   float *router_logits = nullptr, *gates = nullptr, *moe_hidden = nullptr, *pair_out = nullptr;
   int32_t* expert_ids = nullptr;
   float* partial = nullptr;
@@ -621,7 +622,10 @@ static int enqueue_step(cai_session* s) {
   };
   CAI_TRY(op_embed(ctx, &m->embed, s->tokens_dev, B, x, H));
   CAI_TRY(op_rope_table(ctx, m->theta, s->pos_dev, B, c.head_dim / 2, s->rope_cs));
-  const bool fuse_rope = !c.qk_norm;     // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first
+  // Batches of 9..64 rows go through the tensor-core GEMM, which has plain epilogues only: RoPE/append and SwiGLU
+  // then run as their own kernels.
+  const bool tc_batch = (B >= 9 && B <= 64) && (m->layers[0].wqkv.type == CAI_TYPE_Q8_0 || m->layers[0].wqkv.type == CAI_TYPE_Q4_0);
+  const bool fuse_rope = !c.qk_norm && !tc_batch;     // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
     if (linear_can_fuse_norm(&L.wqkv, B)) {
@@ -667,9 +671,15 @@ static int enqueue_step(cai_session* s) {
     if (!fuse_ffn_norm) CAI_TRY(op_rmsnorm(ctx, x, H, L.ffn_norm, s->h, H, B, H, c.rms_eps));
     if (!c.n_experts) {
       {
-        LinearArgs a; a.w = &L.wgu; a.x = fuse_ffn_norm ? x : s->h; a.ldx = H; a.y = s->act; a.ldy = m->inter_l; a.batch = B; a.epilogue = EPI_SWIGLU;
-        if (fuse_ffn_norm) { a.norm_gain = L.ffn_norm; a.norm_eps = c.rms_eps; }
-        CAI_TRY(linear_launch(ctx, a));
+        if (tc_batch && s->gu) {
+          LinearArgs a; a.w = &L.wgu; a.x = s->h; a.ldx = H; a.y = s->gu; a.ldy = 2 * (int64_t)m->inter_l; a.batch = B;
+          CAI_TRY(linear_launch(ctx, a));
+          CAI_TRY(op_swiglu(ctx, s->gu, 2 * (int64_t)m->inter_l, s->act, m->inter_l, B, m->inter_l));
+        } else {
+          LinearArgs a; a.w = &L.wgu; a.x = fuse_ffn_norm ? x : s->h; a.ldx = H; a.y = s->act; a.ldy = m->inter_l; a.batch = B; a.epilogue = EPI_SWIGLU;
+          if (fuse_ffn_norm) { a.norm_gain = L.ffn_norm; a.norm_eps = c.rms_eps; }
+          CAI_TRY(linear_launch(ctx, a));
+        }
       }
       if (m->tp_size == 1) {
         LinearArgs a; a.w = &L.wdown; a.x = s->act; a.ldx = m->inter_l; a.y = x; a.ldy = H; a.batch = B; a.epilogue = EPI_RESID; a.resid = x;
@@ -781,7 +791,7 @@ int cai_session_destroy(cai_session* s) {
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
   if (s->ar) comm_ar_destroy(s->ctx, s->ar);
   void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
-                  s->att, s->act, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
+                  s->att, s->act, s->gu, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
                   s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf};
   for (void* p : bufs) if (p) cudaFree(p);
   if (s->io_pinned) cudaFreeHost(s->io_pinned);
@@ -824,6 +834,7 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   A((void**)&s->qkv, (size_t)B * QKVW * 4); A((void**)&s->att, (size_t)B * m->qw_l * 4);
   A((void**)&s->act, (size_t)B * (m->inter_l ? m->inter_l : 1) * 4);
   A((void**)&s->logits, (size_t)B * m->vocab_l * 4);
+  if (B >= 9 && m->inter_l) A((void**)&s->gu, (size_t)B * 2 * m->inter_l * 4);
   A((void**)&s->partial, attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim) * 4);
   A((void**)&s->amax_idx, (size_t)B * 4); A((void**)&s->amax_val, (size_t)B * 4);
   A((void**)&s->amax_part_val, (size_t)B * CAI_ARGMAX_CHUNKS * 4); A((void**)&s->amax_part_idx, (size_t)B * CAI_ARGMAX_CHUNKS * 4);

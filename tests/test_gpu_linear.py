@@ -13,6 +13,9 @@ pytestmark = pytest.mark.gpu
 # max |y - y_ref| <= TOL * RMS(y_ref). fp32 accumulation in a different order from BLAS;
 # the budget the decode path is held to is 1e-3.
 TOL = 2e-5
+# Batches of 9..64 rows run on the tensor cores with weights and activations split into two bf16 limbs
+# (three MMAs per product): ~1e-5 per product, still two orders inside the 1e-3 budget.
+TOL_TC = 2e-4
 
 
 def make_blocks(ggml_type, n, k, seed):
@@ -51,14 +54,14 @@ def test_linear_sweep_shapes(backend, ggml_type, kn):
             y = lin.finish_and_load_result()
             ref = codecs.linear_fp32(w, x)
             assert y.shape == (b, n)
-            assert rel_err(y, ref) < TOL, (ggml_type, kn, b, rel_err(y, ref))
+            assert rel_err(y, ref) < (TOL if b <= 8 else TOL_TC), (ggml_type, kn, b, rel_err(y, ref))
     finally:
         lin.unprepare_for_compute()
 
 
 @pytest.mark.parametrize("ggml_type", [codecs.GGML_Q8_0, codecs.GGML_Q4_0])
 @pytest.mark.parametrize("n,k", [(1, 32), (2, 64), (37, 96), (129, 1024), (1000, 2080), (5, 27648)])
-@pytest.mark.parametrize("b", [1, 2, 3, 5, 7, 8, 9])
+@pytest.mark.parametrize("b", [1, 2, 3, 5, 7, 8, 9, 17, 33, 64])
 def test_ragged_shapes_and_batches(backend, ggml_type, n, k, b):
     blk = make_blocks(ggml_type, n, k, seed=n * 7 + k)
     w = codecs.dequantize(ggml_type, blk).reshape(n, k)
@@ -71,7 +74,7 @@ def test_ragged_shapes_and_batches(backend, ggml_type, n, k, b):
         lin.compute_quant(x)
         y = lin.finish_and_load_result()
         ref = codecs.linear_fp32(w, x, bias)
-        assert rel_err(y, ref) < TOL
+        assert rel_err(y, ref) < (TOL if b <= 8 else TOL_TC)
     finally:
         lin.unprepare_for_compute()
 

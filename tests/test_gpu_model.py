@@ -247,3 +247,36 @@ def test_synthetic_architectures_match_the_oracle(backend, arch, ggml_type, laye
     finally:
         sess.close()
         model.close()
+
+
+def test_tensor_core_batches_match_single_sequence_sessions(backend):
+    """Sessions of 16 sequences run their linear layers on the tensor cores (bf16-limb split, ~1e-5 per
+    product); every row must still agree with the exact single-sequence path within the 1e-3 logit budget,
+    and pick the same greedy tokens wherever the top-2 margin is not razor thin."""
+    kw = dict(hidden=512, inter=1024, layers=2, heads=8, kv_heads=2, head_dim=64, vocab=2048, rms_eps=1e-6,
+              rope_theta=1e6, qkv_bias=True)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=11, std=0.02)
+    model.finalize()
+    batch, steps = 16, 6
+    rng = np.random.default_rng(4)
+    toks = rng.integers(0, kw["vocab"], (batch, steps)).astype(np.int32)
+    wide = StreamingDecoder(model, 16, batch=batch)
+    one = StreamingDecoder(model, 16, batch=1)
+    try:
+        wide_logits = []
+        for i in range(steps):
+            logits, _ = wide.step_forward(toks[:, i])
+            wide_logits.append(logits.copy())
+        worst = 0.0
+        for b in (0, 7, 15):
+            one.reset()
+            for i in range(steps):
+                ref, _ = one.step_forward([toks[b, i]])
+                rms = float(np.sqrt(np.mean(ref[0].astype(np.float64) ** 2)))
+                worst = max(worst, float(np.max(np.abs(wide_logits[i][b] - ref[0]))) / rms)
+        assert worst < 1e-3, worst
+    finally:
+        wide.close()
+        one.close()
+        model.close()
