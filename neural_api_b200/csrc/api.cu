@@ -92,6 +92,8 @@ int cai_cuda_shutdown(cai_ctx* ctx) {
   if (ctx->l2_flush_buf) cudaFree(ctx->l2_flush_buf);
   if (ctx->gemv_scratch) cudaFree(ctx->gemv_scratch);
   if (ctx->gemv_tickets) cudaFree(ctx->gemv_tickets);
+  if (ctx->tc_xp) cudaFree(ctx->tc_xp);
+  for (int i = 0; i < ctx->tc_xp_n_retired; ++i) cudaFree(ctx->tc_xp_retired[i]);
   if (ctx->err_flag) cudaFreeHost(ctx->err_flag);
   if (ctx->staging_dev) cudaFree(ctx->staging_dev);
   if (ctx->staging_pinned) cudaFreeHost(ctx->staging_pinned);

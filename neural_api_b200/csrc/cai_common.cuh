@@ -36,6 +36,10 @@ struct cai_ctx {
   int gemv_ticket_cap;
   int gemv_scratch_ctas;
   int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out
+  void* tc_xp;               // tensor-core GEMM: activations split into bf16 limbs, tiled (gemm_tc_reserve)
+  size_t tc_xp_bytes;
+  void* tc_xp_retired[32];   // outgrown buffers: captured graphs may still name them, so they live as long as the context
+  int tc_xp_n_retired;
   int use_pdl;               // launch step kernels with programmatic dependent launch
   // per-launch profiling (cai_session_profile): one event after every launch
   int prof_on;
@@ -48,6 +52,8 @@ enum { FAM_LINEAR = 0, FAM_ATTN = 1, FAM_OTHER = 2, FAM_COMM = 3, FAM_COUNT = 4 
 int cai_prof_mark(cai_ctx* ctx, int family);
 
 int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...);
+int env_int(const char* name, int dflt);                    // integer environment knob, gemv.cu
+int gemm_tc_reserve(cai_ctx* ctx, int64_t k, int batch);    // gemm_tc.cu
 
 #define CAI_CUDA(ctx, call)                                                              \
   do {                                                                                   \
@@ -261,6 +267,18 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   __syncthreads();
   float t = (lane < nw) ? red[lane] : 0.f;
   t = warp_sum(t);
+  return t;
+}
+// Block-wide maximum of non-negative values; every thread gets the result.
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_max(t);
   return t;
 }
 // int8 code in byte `i` of a word whose bytes were XOR-ed with 0x80 -> float, exactly.

@@ -2,23 +2,31 @@
 // tensor memory) for batches of 9..64 activation rows, where the work is a real dense
 // contraction:  Y[b][a] = sum_i W[a][i] * X[b][i],  W = d * code (Q8_0 / Q4_0).
 //
-// One CTA owns 128 weight rows (the UMMA M dimension) and walks K in chunks of 64:
-//   * four warps dequantize the chunk (128 rows x 64 codes) to fp32 exactly, split every
-//     value into two bf16 limbs (hi = bf16(v), lo = bf16(v - hi)) and write both as K-major
-//     UMMA operand tiles in shared memory (8x16-byte core matrices, no swizzle); the
-//     activations are split the same way;
-//   * one thread issues, per 16-wide K step, three MMAs  A_hi*B_hi + A_hi*B_lo + A_lo*B_hi
-//     (the lo*lo term is below 2^-16 relative) into one fp32 accumulator tile of N = batch
-//     columns in tensor memory, then commits to an mbarrier;
-//   * two operand stages, so the dequantization of chunk i+1 overlaps the MMAs of chunk i;
-//   * the epilogue reads the accumulators with tcgen05.ld (lane = weight row, column =
-//     batch row) and applies bias / residual / activation before storing y[b][a].
-//   * the tensor core adds into its fp32 accumulator with truncation, which biases long sums towards
-//     zero (measured 2.3e-4 relative at K = 27648 in one accumulator); so every TC_FLUSH chunks
-//     (K = 512) the accumulator tile is read out and added, rounded to nearest, into fp32 registers,
-//     and the next MMA starts a fresh accumulator;
-// Relative error against fp32 arithmetic is ~1e-5 per product, far inside the 1e-3 logit
-// budget; the exact CUDA-core GEMV stays the path for batches up to 8.
+// The block scale d varies along K, so it cannot ride inside one long tensor-core
+// accumulation without rounding d * code to 16 bits. Instead the MMA runs on the integer
+// codes, which fp16 holds exactly, and each 32-wide block gets its own accumulator:
+//
+//   split kernel   every activation row is scaled by a power of two into fp16's range and split
+//                  once per call into two fp16 limbs (x = x0 + x1, each limb the fp16 rounding of
+//                  what is left: 22 significant bits), written in the tile order the MMA reads
+//                  (K-major rows of 128 bytes, 128-byte swizzle), so every CTA of the GEMM just copies its tiles;
+//   GEMM kernel    one CTA owns 128 weight rows (UMMA M) and walks K in chunks of 64 (two blocks):
+//     * 8 worker warps stream the raw code bytes into a shared-memory ring with cp.async (a stage is a run of
+//       128..512 contiguous bytes of each row), turn each chunk into fp16 integers laid out as the UMMA A tile
+//       (one byte-permute and one packed subtract per two codes), and read the accumulators of the previous
+//       chunk out of tensor memory (tcgen05.ld: lane = weight row, column = batch row), adding d * partial
+//       into fp32 registers with one FMA per value, rounded to nearest;
+//     * a ninth warp (one lane) copies the activation tiles in with bulk copies and issues, per 32-block,
+//       2 K-steps x 2 limbs MMAs (fp16 codes x fp16 limbs -> fp32, every product exact) into that block's own
+//       accumulator (two chunks = four accumulators in flight), committing each chunk to an mbarrier.
+//   So the weights enter exactly, the per-block sums are short (the tensor core adds into its accumulator with
+//   truncation, which biases long sums towards zero: 2.3e-4 relative was measured for K = 27648 kept in one
+//   accumulator), and the only approximation left is the limb split of the activations, 2^-22 relative:
+//   measured error against float64 is ~1e-6 of the output RMS, the same as fp32 arithmetic.
+//
+//   What bounds it: instruction issue, not the tensor pipe (3 % busy) - unpacking a byte costs more than
+//   multiplying it - so everything whose value is known when the kernel is compiled is a template parameter, and
+//   the per-thread addressing is hoisted out of the chunk loop.
 //
 // Every mbarrier wait is bounded; tensor memory is freed on every exit path.
 #include "gemv_common.cuh"
@@ -27,47 +35,79 @@
 namespace {
 
 constexpr int TC_M = 128;            // weight rows per CTA = UMMA M
-constexpr int TC_KC = 64;            // K per chunk (4 UMMA K steps of 16)
-constexpr int TC_THREADS = 128;
-constexpr int TC_FLUSH = 8;           // chunks accumulated in tensor memory before the read-out into registers
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+constexpr int TC_KC = 64;            // K per chunk: two 32-blocks, four UMMA K steps of 16
+constexpr int TC_WORKERS = 256;      // threads that stream, convert and read out
+constexpr int TC_THREADS = TC_WORKERS + 32;   // plus the issuing warp
+constexpr int TC_RAW_STAGES = 2;     // ring of raw-code stages
+constexpr int TC_B_STAGES = 3;       // ring of activation tiles (one 64-wide chunk each)
+constexpr int TC_A_BYTES = TC_M * TC_KC * 2;  // fp16 weight tile: 16 KB
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
+
+// Per batch width (rows rounded up to 16, 32 or 64): raw bytes per row and ring stage. Two CTAs share an SM up to
+// 32 rows (<= 112 KB each); 64 rows take 512-byte stages and the SM alone.
+template <int NB> struct TcPlan {
+  static constexpr int SPAN = NB == 16 ? 256 : (NB == 32 ? 128 : 512);
+  static constexpr int B_BYTES = 2 * NB * 128;                                  // two limbs of NB rows x 128 bytes
+  static constexpr int SMEM = 1024 + 2 * TC_A_BYTES + TC_B_STAGES * B_BYTES + TC_RAW_STAGES * TC_M * SPAN;
+  static constexpr int ACC_STRIDE = NB < 32 ? 32 : NB;                          // accumulators start on multiples of 32 columns
+  static constexpr int TMEM_COLS = 4 * ACC_STRIDE;                              // 128, 128, 256: powers of two
+  static constexpr int MIN_CTAS = NB <= 32 ? 2 : 1;
+};
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Bounded wait on an mbarrier phase. try_wait may suspend the thread in hardware up to the hinted time, so a
+// waiting warp does not compete for issue slots with the warps that are working.
 __device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(4000u)
         : "memory");
     if (ok) return true;
   }
   return false;
 }
 
-// Shared-memory matrix descriptor, K-major, no swizzle: 8 rows x 16 bytes core matrices.
-//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4 (between the two K core matrices)
-//   bits [32,46) stride byte offset >> 4 (between 8-row groups)   bits [46,48) version = 1   bits [61,64) layout = 0
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// 16-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros without reading.
+__device__ __forceinline__ void tc_cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void tc_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tc_cp_async_wait(int pending) {
+  if (pending >= 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+  else if (pending == 1) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile in the 128-byte swizzled layout: row r of the tile
+// (64 fp16 = 128 bytes) starts at r * 128, and its 16-byte piece j sits at position j ^ (r & 7); tiles start on
+// 1024-byte boundaries. (The unswizzled core-matrix layout measured ~250 cycles per 128x16x16 MMA here whatever
+// N was: the operand fetch ran at a fraction of the shared-memory bandwidth.)
+//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4 (1 for swizzled K-major)
+//   bits [32,46) stride byte offset >> 4 = 1024 / 16 between 8-row groups   bits [46,48) version = 1
+//   bits [61,64) layout = 2 (128-byte swizzle).  A K step of 16 elements advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
   d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor, kind::f16: D = F32 (bits [4,6) = 1), A = B = BF16 (bits [7,10) = [10,13) = 1),
+// Instruction descriptor, kind::f16: D = F32 (bits [4,6) = 1), A = B = F16 (bits [7,10) = [10,13) = 0),
 // both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29).
 __device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
@@ -78,51 +118,176 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
 }
 
 struct TcParams {
-  const void* codes;
+  const unsigned char* codes;
   const __half* scales;
   const float* bias;
-  const float* x;
-  int64_t ldx;
+  const unsigned char* xp;   // activations, split into limbs and tiled by the split kernel
+  const float* row_unscale;  // per batch row: the power of two that undoes the split kernel's scaling
   float* y;
   int64_t ldy;
   const float* resid;
   int64_t n, k, sstride;
-  int batch, nb;       // nb = batch rounded up to 16 (UMMA N)
+  int batch;
   int act, epi;
   int* err_flag;
 };
 
-// value -> (hi, lo) bf16 limbs, two values packed per 32-bit word
-__device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
-  const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
-  const __nv_bfloat16 al = __float2bfloat16_rn(a - __bfloat162float(ah)), bl = __float2bfloat16_rn(b - __bfloat162float(bh));
-  hi = (uint32_t)__bfloat16_as_ushort(ah) | ((uint32_t)__bfloat16_as_ushort(bh) << 16);
-  lo = (uint32_t)__bfloat16_as_ushort(al) | ((uint32_t)__bfloat16_as_ushort(bl) << 16);
+// ---------------------------------------------------------------------------
+// Activation split. One CTA per (padded) batch row; optional RMSNorm of the row first
+// (inv = 1/sqrt(mean(x^2) + eps), value = gain * (x * inv), the arithmetic of the norm kernel).
+// The row is scaled by a power of two so that its largest magnitude lies in [2^13, 2^14) (exact; keeps
+// every limb inside fp16's range, and the small limbs out of its subnormals), then split into fp16
+// limbs; the GEMM multiplies the row's results by the inverse factor, also exactly.
+// Output: for every 64-wide K chunk, `limbs` tiles of nb rows x 64 fp16 in the swizzled K-major
+// layout of the MMA: byte offset row * 128 + ((k8 ^ (row & 7)) * 16) for the 8 values of K group k8.
+// Rows beyond the batch and columns beyond K are zeros.
+// ---------------------------------------------------------------------------
+__global__ void tc_split_x_kernel(const float* __restrict__ x, int64_t ldx, int batch, int nb, int64_t k, int n_chunks, int limbs,
+                                  const float* __restrict__ norm_gain, float norm_eps, unsigned char* __restrict__ xp,
+                                  float* __restrict__ row_unscale) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const float* xr = x + (int64_t)b * ldx;
+  float inv = 1.f, scale = 1.f;
+  if (b < batch) {
+    if (norm_gain) {
+      float ss = 0.f;
+      for (int64_t c = threadIdx.x; c < k; c += blockDim.x) { const float v = xr[c]; ss = fmaf(v, v, ss); }
+      ss = block_sum(ss, red);
+      inv = 1.0f / sqrtf(ss / (float)k + norm_eps);
+    }
+    float mx = 0.f;
+    for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
+      const float v = norm_gain ? norm_gain[c] * (xr[c] * inv) : xr[c];
+      mx = fmaxf(mx, fabsf(v));
+    }
+    mx = block_max(mx, red);
+    int e = 0;
+    if (mx > 0.f && mx < 3.0e38f) e = 13 - ilogbf(mx);     // mx * 2^e in [2^13, 2^14)
+    if (e > 100) e = 100;
+    if (e < -100) e = -100;
+    scale = ldexpf(1.f, e);
+    if (threadIdx.x == 0) row_unscale[b] = ldexpf(1.f, -e);
+  } else if (threadIdx.x == 0) {
+    row_unscale[b] = 0.f;
+  }
+  const size_t limb_bytes = (size_t)nb * 128, chunk_bytes = (size_t)limbs * limb_bytes;
+  for (int g = threadIdx.x; g < n_chunks * 8; g += blockDim.x) {
+    const int c = g >> 3, k8 = g & 7;
+    const int64_t kk = (int64_t)c * TC_KC + k8 * 8;
+    float v[8];
+    if (b < batch && kk < k) {                            // K is a multiple of 32: a group of 8 is whole or absent
+      const float4 a0 = *(const float4*)(xr + kk), a1 = *(const float4*)(xr + kk + 4);
+      v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+      if (norm_gain) {
+        const float4 g0 = *(const float4*)(norm_gain + kk), g1 = *(const float4*)(norm_gain + kk + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = gg[i] * (v[i] * inv);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= scale;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    unsigned char* dst = xp + (size_t)c * chunk_bytes + (size_t)(b * 128 + ((k8 ^ (b & 7)) * 16));
+    for (int l = 0; l < limbs; ++l) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half h0 = __float2half_rn(v[2 * i]), h1 = __float2half_rn(v[2 * i + 1]);
+        v[2 * i] -= __half2float(h0);                     // exact: the limb is the leading bits of the value
+        v[2 * i + 1] -= __half2float(h1);
+        w[i] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+      }
+      *(uint4*)(dst + (size_t)l * limb_bytes) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
 }
 
-template <int TYPE>
-__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const TcParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t mma_bar[2];
+// two bytes of `w` (selected by `sel`) -> two fp16 integers 1024 + byte, minus `bias2` (packed fp16): exact
+__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t w, uint32_t sel, uint32_t bias2) {
+  uint32_t h;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(h) : "r"(w), "r"(0x64646464u), "r"(sel));
+  asm("sub.f16x2 %0, %1, %2;" : "=r"(h) : "r"(h), "r"(bias2));
+  return h;
+}
+
+__device__ __forceinline__ uint4 tc_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tc_sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// reads this thread's lane of NCOL consecutive accumulator columns (NCOL = 8, 16 or 32)
+template <int NCOL>
+__device__ __forceinline__ void tc_tmem_ld(uint32_t taddr, uint32_t* r) {
+  if (NCOL == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+  } else if (NCOL == 16) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+        "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+  }
+}
+
+template <int TYPE, int NB>
+__global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kernel(const TcParams p) {
+  using Plan = TcPlan<NB>;
+  constexpr int SPAN = Plan::SPAN;                                           // raw code bytes per row and stage
+  constexpr int PPR = SPAN / 16;                                             // 16-byte pieces per row and stage
+  constexpr int PIECES = (TYPE == CAI_TYPE_Q8_0) ? 4 : 2;                    // pieces per row and 64-wide chunk
+  constexpr int SUB = PPR / PIECES;                                          // chunks per stage
+  constexpr int RAW_BYTES = TC_M * SPAN;
+  constexpr int LIMB_BYTES = NB * 128;                                       // one fp16 limb of the activation tile
+  constexpr int B_BYTES = Plan::B_BYTES;
+  constexpr int ACC_STRIDE = Plan::ACC_STRIDE;
+  constexpr int NCOL = NB / 2;                                               // batch columns a worker thread owns
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t mma_bar[2];            // MMAs of chunk c done (tcgen05.commit), c & 1
+  __shared__ __align__(8) uint64_t a_ready[2];            // weight tile of chunk c converted (TC_WORKERS arrivals), c & 1
+  __shared__ __align__(8) uint64_t b_full[TC_B_STAGES];   // activation tile landed (bytes of a bulk copy)
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int NBP = p.nb;                                   // padded batch = UMMA N
-  constexpr int A_BYTES = TC_M * TC_KC * 2;               // one limb of the weight tile: 16 KB
-  const int b_bytes = NBP * TC_KC * 2;                    // one limb of the activation tile
-  const int stage_bytes = 2 * A_BYTES + 2 * b_bytes;      // A_hi, A_lo, B_hi, B_lo
-  constexpr uint32_t LBO = 128, SBO = (TC_KC / 8) * 128;  // core-matrix strides along K / along rows
+  // operand tiles start on 1024-byte boundaries (the swizzle works on absolute shared-memory address bits)
+  const uint32_t smem0 = (tc_smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_st = smem0;                                               // 2 stages of 16 KB
+  const uint32_t b_st = a_st + 2 * TC_A_BYTES;                               // TC_B_STAGES stages, each a multiple of 1 KB
+  const uint32_t raw_st = b_st + TC_B_STAGES * B_BYTES;                      // TC_RAW_STAGES stages
 
-  // tensor memory: one warp allocates the accumulator columns (a power of two >= 32)
-  const uint32_t tmem_cols = NBP <= 32 ? 32u : 64u;
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(&tmem_base_s)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(&tmem_base_s)), "r"((uint32_t)Plan::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&mma_bar[0])) : "memory");
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&mma_bar[1])) : "memory");
+    for (int i = 0; i < 2; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&mma_bar[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem_u32(&a_ready[i])), "r"(TC_WORKERS) : "memory");
+    }
+    for (int i = 0; i < TC_B_STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&b_full[i])) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -130,196 +295,282 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const TcParams p) {
   const uint32_t tmem_d = tmem_base_s;
 
   const int64_t row0 = (int64_t)blockIdx.x * TC_M;
-  int64_t my_row = row0 + tid;                            // thread t dequantizes row t of the tile
-  if (my_row >= p.n) my_row = p.n - 1;
   const int64_t K = p.k;
   const int64_t row_bytes = (TYPE == CAI_TYPE_Q8_0) ? K : (K >> 1);
-  const unsigned char* wrow = (const unsigned char*)p.codes + my_row * row_bytes;
-  const unsigned short* srow = (const unsigned short*)p.scales + my_row * p.sstride;
-  const uint32_t idesc = umma_idesc(TC_M, NBP);
   const int n_chunks = (int)((K + TC_KC - 1) / TC_KC);    // K is a multiple of 32: the last chunk may be half
+  const int n_blocks = (int)(K >> 5);
+  const int n_stages = (n_chunks + SUB - 1) / SUB;
 
-  float acc[64];                                          // this thread's weight row x up to 64 batch columns
-#pragma unroll
-  for (int j = 0; j < 64; ++j) acc[j] = 0.f;
-
-  bool alive = true;
-  for (int c = 0; c < n_chunks; ++c) {
-    const int stage = c & 1;
-    unsigned char* st = smem + (size_t)stage * stage_bytes;
-    // the MMAs that read this stage two chunks ago must be done before it is overwritten
-    if (c >= 2 && alive && !tc_mbar_wait(tc_smem_u32(&mma_bar[stage]), ((c >> 1) - 1) & 1)) {
-      alive = false;
-      if (lane == 0) *p.err_flag = 1;
-    }
-    const int64_t k0 = (int64_t)c * TC_KC;
-    const int klen = (int)((K - k0 < TC_KC) ? (K - k0) : TC_KC);     // 64 or 32
-
-    // ---- weights: row `tid`, 64 codes -> fp32 -> bf16 hi/lo -> 8 x 16-byte core-matrix rows per limb ----
-    {
-      float v[TC_KC];
-      if (TYPE == CAI_TYPE_Q8_0) {
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {                     // two 32-blocks
-          if (q * 32 < klen) {
-            const float d = __half2float(__ushort_as_half(srow[(k0 >> 5) + q]));
-            const int4 w0 = *(const int4*)(wrow + k0 + q * 32), w1 = *(const int4*)(wrow + k0 + q * 32 + 16);
-            const uint32_t ww[8] = {(uint32_t)w0.x, (uint32_t)w0.y, (uint32_t)w0.z, (uint32_t)w0.w,
-                                    (uint32_t)w1.x, (uint32_t)w1.y, (uint32_t)w1.z, (uint32_t)w1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-              for (int j = 0; j < 4; ++j) v[q * 32 + i * 4 + j] = d * (float)((int)((ww[i] >> (8 * j)) & 0xFF) - 128);   // biased codes
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[q * 32 + i] = 0.f;
-          }
+  if (warp == TC_WORKERS / 32) {
+    // =====================================================================================
+    // Issuing warp (one lane): activation-tile copies and the MMAs.
+    // =====================================================================================
+    if (lane == 0) {
+      bool alive = true;
+      const uint32_t idesc = umma_idesc(TC_M, NB);
+      const uint64_t da0 = umma_desc(a_st), db0 = umma_desc(b_st);
+      const uint32_t bar_mma = tc_smem_u32(&mma_bar[0]), bar_a = tc_smem_u32(&a_ready[0]), bar_b = tc_smem_u32(&b_full[0]);
+      auto issue_b = [&](int j, int slot) {
+        if (j < n_chunks) {
+          const uint32_t bar = bar_b + 8u * (uint32_t)slot;
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)B_BYTES) : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           b_st + (uint32_t)(slot * B_BYTES)),
+                       "l"(p.xp + (size_t)j * B_BYTES), "r"((uint32_t)B_BYTES), "r"(bar)
+                       : "memory");
         }
-      } else {
+      };
+      issue_b(0, 0);
+      issue_b(1, 1);
+      int bslot = 0, bphase = 0;                            // ring slot and phase parity of chunk c
+      for (int c = 0; c < n_chunks; ++c) {
+        const int stage = c & 1;
+        // weight tile converted (which also says the workers have read out the accumulators of chunk c-2), activation tile landed
+        if (alive && !tc_mbar_wait(bar_a + 8u * stage, (uint32_t)((c >> 1) & 1))) { alive = false; *p.err_flag = 1; }
+        if (alive && !tc_mbar_wait(bar_b + 8u * bslot, (uint32_t)bphase)) { alive = false; *p.err_flag = 1; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // descriptors differ from the base ones only in the start address field (units of 16 bytes)
+        const uint64_t da = da0 + (uint64_t)((stage * TC_A_BYTES) >> 4);
+        const uint64_t db = db0 + (uint64_t)((bslot * B_BYTES) >> 4);
+        const uint32_t d_t = tmem_d + (uint32_t)(stage * 2 * ACC_STRIDE);
+        // each 32-block into its own fresh accumulator: two K steps of 16 (32 bytes of a 128-byte row each), two limbs
+        umma_f16(d_t, da, db, idesc, 0u);
+        umma_f16(d_t, da, db + (LIMB_BYTES >> 4), idesc, 1u);
+        umma_f16(d_t, da + 2, db + 2, idesc, 1u);
+        umma_f16(d_t, da + 2, db + (LIMB_BYTES >> 4) + 2, idesc, 1u);
+        if (2 * c + 1 < n_blocks) {
+          umma_f16(d_t + ACC_STRIDE, da + 4, db + 4, idesc, 0u);
+          umma_f16(d_t + ACC_STRIDE, da + 4, db + (LIMB_BYTES >> 4) + 4, idesc, 1u);
+          umma_f16(d_t + ACC_STRIDE, da + 6, db + 6, idesc, 1u);
+          umma_f16(d_t + ACC_STRIDE, da + 6, db + (LIMB_BYTES >> 4) + 6, idesc, 1u);
+        }
+        // arrives on the barrier once every MMA issued so far has finished (operands read, accumulators written)
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_mma + 8u * stage) : "memory");
+        // refill the activation ring two chunks ahead: that slot's previous tile was read by the MMAs of chunk c-1
+        if (c >= 1 && alive && !tc_mbar_wait(bar_mma + 8u * (stage ^ 1), (uint32_t)(((c - 1) >> 1) & 1))) { alive = false; *p.err_flag = 1; }
+        issue_b(c + 2, bslot == 0 ? TC_B_STAGES - 1 : bslot - 1);
+        if (++bslot == TC_B_STAGES) { bslot = 0; bphase ^= 1; }
+      }
+    }
+  } else {
+    // =====================================================================================
+    // Worker warps. Read-out role: warp w reads accumulator lanes 32*(w&3).., batch columns [hb*NB/2, (hb+1)*NB/2),
+    // hb = w >> 2. Everything that does not change from chunk to chunk is computed here, once.
+    // =====================================================================================
+    const int lane_q = warp & 3, hb = warp >> 2;
+    int64_t my_row = row0 + lane_q * 32 + lane;
+    const bool row_ok = my_row < p.n;
+    if (!row_ok) my_row = p.n - 1;
+    const uint4* srow = (const uint4*)(p.scales + my_row * p.sstride);     // 8 scales (4 chunks) per 16 bytes
+    uint4 sc_cur = make_uint4(0, 0, 0, 0), sc_next = srow[0];
+    float acc[NCOL];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          if (q * 32 < klen) {
-            const float d = __half2float(__ushort_as_half(srow[(k0 >> 5) + q]));
-            const int4 w0 = *(const int4*)(wrow + ((k0 + q * 32) >> 1));
-            const uint32_t ww[4] = {(uint32_t)w0.x, (uint32_t)w0.y, (uint32_t)w0.z, (uint32_t)w0.w};
+    for (int j = 0; j < NCOL; ++j) acc[j] = 0.f;
+    bool alive = true;
+    const uint32_t bar_mma = tc_smem_u32(&mma_bar[0]), bar_a = tc_smem_u32(&a_ready[0]);
+    const uint32_t t_lane = tmem_d + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(hb * NCOL);
+    const int rmax = (int)((p.n - 1 - row0 < TC_M - 1) ? (p.n - 1 - row0) : (TC_M - 1));   // last valid row of the tile
+
+    // ---- raw-code producer. Item i = tid + 256 t of a stage is 16-byte piece (i % PPR) of row (i / PPR): a thread
+    //      keeps its piece and walks down the rows in steps of 256 / PPR, so source and destination advance by constants.
+    //      The pieces of a row are XOR-swizzled with the row, so that the conversion, which walks rows, reads without
+    //      bank conflicts (the row step is a multiple of 8, so a thread's swizzle is fixed too).
+    constexpr int RSTEP = TC_WORKERS / PPR;
+    const int pr_pc = tid & (PPR - 1), pr_r0 = tid / PPR;
+    const uint32_t pr_dst0 = (uint32_t)(pr_r0 * SPAN + ((pr_pc ^ (pr_r0 & 7)) << 4));
+    const unsigned char* pr_src0 = p.codes + row0 * row_bytes + pr_pc * 16;
+    auto issue_raw = [&](int j) {
+      if (j < n_stages) {
+        const uint32_t dst = raw_st + (uint32_t)((j & (TC_RAW_STAGES - 1)) * RAW_BYTES) + pr_dst0;
+        const int64_t byte0 = (int64_t)j * SPAN;                          // first code byte of the stage within a row
+        const bool valid = byte0 + pr_pc * 16 < row_bytes;                // K tail: zero-fill instead of reading
+        const unsigned char* src = pr_src0 + (valid ? byte0 : 0);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t byte = (ww[i] >> (8 * j)) & 0xFF;       // byte e: element e (low), element e+16 (high)
-                v[q * 32 + i * 4 + j] = d * (float)((int)(byte & 0x0F) - 8);
-                v[q * 32 + 16 + i * 4 + j] = d * (float)((int)(byte >> 4) - 8);
-              }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[q * 32 + i] = 0.f;
-          }
+        for (int t = 0; t < PPR / 2; ++t) {
+          int r = pr_r0 + t * RSTEP;
+          r = r < rmax ? r : rmax;                                        // rows past the matrix re-read its last row
+          tc_cp_async16(dst + (uint32_t)(t * RSTEP * SPAN), src + (int64_t)r * row_bytes, valid ? 16u : 0u);
         }
       }
-      const int m8 = tid >> 3, r8 = tid & 7;
-#pragma unroll
-      for (int k8 = 0; k8 < TC_KC / 8; ++k8) {
-        uint4 hi, lo;
-        split2(v[k8 * 8 + 0], v[k8 * 8 + 1], hi.x, lo.x);
-        split2(v[k8 * 8 + 2], v[k8 * 8 + 3], hi.y, lo.y);
-        split2(v[k8 * 8 + 4], v[k8 * 8 + 5], hi.z, lo.z);
-        split2(v[k8 * 8 + 6], v[k8 * 8 + 7], hi.w, lo.w);
-        const int off = (m8 * (TC_KC / 8) + k8) * 128 + r8 * 16;
-        *(uint4*)(st + off) = hi;
-        *(uint4*)(st + A_BYTES + off) = lo;
-      }
-    }
-    // ---- activations: (batch row, 8-wide K group) items over the 128 threads ----
-    for (int item = tid; item < NBP * (TC_KC / 8); item += TC_THREADS) {
-      const int b = item / (TC_KC / 8), k8 = item % (TC_KC / 8);
-      float xv[8];
-      if (b < p.batch && k8 * 8 < klen) {
-        const float4 a = *(const float4*)(p.x + (int64_t)b * p.ldx + k0 + k8 * 8);
-        const float4 bq = *(const float4*)(p.x + (int64_t)b * p.ldx + k0 + k8 * 8 + 4);
-        xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w; xv[4] = bq.x; xv[5] = bq.y; xv[6] = bq.z; xv[7] = bq.w;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) xv[i] = 0.f;
-      }
-      uint4 hi, lo;
-      split2(xv[0], xv[1], hi.x, lo.x);
-      split2(xv[2], xv[3], hi.y, lo.y);
-      split2(xv[4], xv[5], hi.z, lo.z);
-      split2(xv[6], xv[7], hi.w, lo.w);
-      const int off = ((b >> 3) * (TC_KC / 8) + k8) * 128 + (b & 7) * 16;
-      *(uint4*)(st + 2 * A_BYTES + off) = hi;
-      *(uint4*)(st + 2 * A_BYTES + b_bytes + off) = lo;
-    }
-    // make the generic-proxy writes visible to the tensor-core (async) proxy, then hand over
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_hi = tc_smem_u32(st), a_lo = a_hi + A_BYTES, b_hi = a_hi + 2 * A_BYTES, b_lo = b_hi + b_bytes;
-#pragma unroll
-      for (int ks = 0; ks < TC_KC / 16; ++ks) {
-        const uint32_t koff = ks * 2 * 128;               // two core matrices along K per step
-        const uint64_t dah = umma_desc(a_hi + koff, LBO, SBO), dal = umma_desc(a_lo + koff, LBO, SBO);
-        const uint64_t dbh = umma_desc(b_hi + koff, LBO, SBO), dbl = umma_desc(b_lo + koff, LBO, SBO);
-        umma_bf16(tmem_d, dah, dbh, idesc, ((c % TC_FLUSH) != 0 || ks > 0) ? 1u : 0u);   // fresh accumulator after a read-out
-        umma_bf16(tmem_d, dah, dbl, idesc, 1u);
-        umma_bf16(tmem_d, dal, dbh, idesc, 1u);
-      }
-      // arrives on the barrier once every MMA issued so far has finished reading shared memory
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem_u32(&mma_bar[stage])) : "memory");
-    }
-    if ((c % TC_FLUSH) == TC_FLUSH - 1 || c == n_chunks - 1) {
-      // read the accumulator tile out: wait for this chunk's commit (it covers every MMA issued so far)
-      if (alive && !tc_mbar_wait(tc_smem_u32(&mma_bar[stage]), (c >> 1) & 1)) {
+      tc_cp_async_commit();                                 // one group per stage index, empty past the end
+    };
+
+    // ---- conversion addresses: thread handles row cv_r, pieces cv_q (+2 for its second item) of each chunk
+    const int cv_r = tid & 127, cv_q = tid >> 7, cv_s = cv_r & 7;
+    const uint32_t cv_src = (uint32_t)(cv_r * SPAN);
+    const uint32_t cv_dst = (uint32_t)(cv_r * 128);
+
+    // ---- read-out of chunk cc: acc += d[row][block] * accumulator, for the chunk's (up to) two blocks
+    auto readout = [&](int cc) {
+      if (alive && !tc_mbar_wait(bar_mma + 8u * (cc & 1), (uint32_t)((cc >> 1) & 1))) {
         alive = false;
         if (lane == 0) *p.err_flag = 1;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if ((cc & 3) == 0) {
+        sc_cur = sc_next;
+        if (cc + 4 < n_chunks) sc_next = srow[(cc >> 2) + 1];
+      }
+      const int sel = cc & 3;
+      const uint32_t dw = sel == 0 ? sc_cur.x : (sel == 1 ? sc_cur.y : (sel == 2 ? sc_cur.z : sc_cur.w));
+      const uint32_t taddr = t_lane + (uint32_t)((cc & 1) * 2 * ACC_STRIDE);
+      uint32_t r0[NCOL], r1[NCOL];
+      const bool two = 2 * cc + 1 < n_blocks;
+      tc_tmem_ld<NCOL>(taddr, r0);
+      if (two) tc_tmem_ld<NCOL>(taddr + ACC_STRIDE, r1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const float d0 = __half2float(__ushort_as_half((unsigned short)(dw & 0xFFFF)));
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 16) {
-        if (c0 < NBP) {                                   // warp w reads accumulator lanes 32w..32w+31, 16 columns at a time
-          uint32_t r[16];
-          const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-              : "r"(taddr)
-              : "memory");
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int j = 0; j < NCOL; ++j) acc[j] = fmaf(d0, __uint_as_float(r0[j]), acc[j]);
+      if (two) {
+        const float d1 = __half2float(__ushort_as_half((unsigned short)(dw >> 16)));
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+        for (int j = 0; j < NCOL; ++j) acc[j] = fmaf(d1, __uint_as_float(r1[j]), acc[j]);
+      }
+      // orders the loads above before the arrival that lets the issuing warp overwrite these accumulators
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    };
+
+    for (int j = 0; j < TC_RAW_STAGES; ++j) issue_raw(j);
+
+    int c = 0;
+    for (int rs = 0; rs < n_stages; ++rs) {
+      // (a) this thread's copies of the stage have landed; after the barrier, every worker's
+      tc_cp_async_wait(TC_RAW_STAGES - 1);
+      asm volatile("bar.sync 1, %0;" ::"n"(TC_WORKERS) : "memory");
+      const uint32_t raw = raw_st + (uint32_t)((rs & (TC_RAW_STAGES - 1)) * RAW_BYTES) + cv_src;
+#pragma unroll
+      for (int u = 0; u < SUB; ++u) {
+        if (c < n_chunks) {
+          const int stage = c & 1;
+          // (b) raw codes -> fp16 integers in the swizzled A-tile layout. The A stage was last read by the MMAs of
+          //     chunk c-2, whose completion this thread awaited in the read-out of the previous iteration.
+          const uint32_t a_t = a_st + (uint32_t)(stage * TC_A_BYTES) + cv_dst;
+          if (TYPE == CAI_TYPE_Q8_0) {
+            constexpr uint32_t BIAS = 0x64806480u;          // fp16 1152 = 1024 + 128: stored codes are q + 128
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {                   // row fastest: 8 consecutive threads touch 8 distinct bank groups
+              const int q = cv_q + 2 * t;
+              const uint4 w = tc_lds128(raw + (uint32_t)((((u * 4 + q) ^ cv_s)) << 4));
+              tc_sts128(a_t + (uint32_t)(((2 * q) ^ cv_s) << 4), bytes_to_half2(w.x, 0x4140, BIAS), bytes_to_half2(w.x, 0x4342, BIAS),
+                        bytes_to_half2(w.y, 0x4140, BIAS), bytes_to_half2(w.y, 0x4342, BIAS));
+              tc_sts128(a_t + (uint32_t)(((2 * q + 1) ^ cv_s) << 4), bytes_to_half2(w.z, 0x4140, BIAS), bytes_to_half2(w.z, 0x4342, BIAS),
+                        bytes_to_half2(w.w, 0x4140, BIAS), bytes_to_half2(w.w, 0x4342, BIAS));
+            }
+          } else {
+            constexpr uint32_t BIAS = 0x64086408u;          // fp16 1032 = 1024 + 8
+            const int blk = cv_q;                           // one 16-byte block of 32 nibble codes per thread
+            const uint4 w = tc_lds128(raw + (uint32_t)((((u * 2 + blk) ^ cv_s)) << 4));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { lo[i] = ww[i] & 0x0F0F0F0Fu; hi[i] = (ww[i] >> 4) & 0x0F0F0F0Fu; }
+            // byte e of the block: element e in the low nibble, element e + 16 in the high nibble
+            const int j0 = 4 * blk;
+            tc_sts128(a_t + (uint32_t)(((j0 + 0) ^ cv_s) << 4), bytes_to_half2(lo[0], 0x4140, BIAS), bytes_to_half2(lo[0], 0x4342, BIAS),
+                      bytes_to_half2(lo[1], 0x4140, BIAS), bytes_to_half2(lo[1], 0x4342, BIAS));
+            tc_sts128(a_t + (uint32_t)(((j0 + 1) ^ cv_s) << 4), bytes_to_half2(lo[2], 0x4140, BIAS), bytes_to_half2(lo[2], 0x4342, BIAS),
+                      bytes_to_half2(lo[3], 0x4140, BIAS), bytes_to_half2(lo[3], 0x4342, BIAS));
+            tc_sts128(a_t + (uint32_t)(((j0 + 2) ^ cv_s) << 4), bytes_to_half2(hi[0], 0x4140, BIAS), bytes_to_half2(hi[0], 0x4342, BIAS),
+                      bytes_to_half2(hi[1], 0x4140, BIAS), bytes_to_half2(hi[1], 0x4342, BIAS));
+            tc_sts128(a_t + (uint32_t)(((j0 + 3) ^ cv_s) << 4), bytes_to_half2(hi[2], 0x4140, BIAS), bytes_to_half2(hi[2], 0x4342, BIAS),
+                      bytes_to_half2(hi[3], 0x4140, BIAS), bytes_to_half2(hi[3], 0x4342, BIAS));
+          }
+          // (c) make the stores visible to the tensor-core (async) proxy and tell the issuing warp: the tile of
+          //     chunk c is ready, and this thread is done with the accumulators of chunk c-2
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a + 8u * stage) : "memory");
+          // (d) while the tensor core works on chunk c, fold chunk c-1 into the registers
+          if (c >= 1) readout(c - 1);
+          ++c;
         }
       }
-      // the next MMA (fresh accumulator) is issued only after the __syncthreads of the next chunk,
-      // which every warp reaches after its loads above have completed
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      // (e) the raw slot is free once every worker has converted the stage's last chunk
+      asm volatile("bar.sync 1, %0;" ::"n"(TC_WORKERS) : "memory");
+      issue_raw(rs + TC_RAW_STAGES);
     }
-  }
-  // ---- epilogue: thread = weight row, acc[b] = batch column b ----
-  const int64_t row = row0 + tid;
-  if (row < p.n) {
+    readout(n_chunks - 1);
+    tc_cp_async_wait(0);
+
+    // ---- epilogue: thread = weight row, acc[j] = batch column hb * NB/2 + j ----
+    if (row_ok) {
+      const float bias = p.bias ? p.bias[my_row] : 0.f;
 #pragma unroll
-    for (int b = 0; b < 64; ++b) {
-      if (b < p.batch) {
-        float v = acc[b];
-        if (p.bias) v += p.bias[row];
-        v = apply_act(v, p.act);
-        if (p.epi == EPI_RESID) v += p.resid[(int64_t)b * p.ldy + row];
-        p.y[(int64_t)b * p.ldy + row] = v;
+      for (int j = 0; j < NCOL; ++j) {
+        const int b = hb * NCOL + j;
+        if (b < p.batch) {
+          float v = fmaf(acc[j], p.row_unscale[b], bias);
+          v = apply_act(v, p.act);
+          if (p.epi == EPI_RESID) v += p.resid[(int64_t)b * p.ldy + my_row];
+          p.y[(int64_t)b * p.ldy + my_row] = v;
+        }
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)Plan::TMEM_COLS) : "memory");
+}
+
+template <int TYPE, int NB>
+cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid) {
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcPlan<NB>::SMEM);
+  if (e == cudaSuccess) gemm_tc_kernel<TYPE, NB><<<grid, TC_THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
+  return e;
 }
 
 }  // namespace
+
+// Grows the buffer that holds the split activations. Sessions size it when they are created, so a step
+// that is being captured into a graph never allocates. An outgrown buffer is kept until the context is
+// destroyed, because a graph captured earlier may still name it; sizes at least double, so few are kept.
+int gemm_tc_reserve(cai_ctx* ctx, int64_t k, int batch) {
+  const int nb = batch <= 16 ? 16 : (batch <= 32 ? 32 : 64);
+  size_t need = 256 + (size_t)((k + TC_KC - 1) / TC_KC) * 2 * (size_t)nb * 128;      // 64 row factors, then two limbs per chunk
+  if (need <= ctx->tc_xp_bytes) return CAI_OK;
+  if (need < 2 * ctx->tc_xp_bytes) need = 2 * ctx->tc_xp_bytes;
+  if (need < ((size_t)4 << 20)) need = (size_t)4 << 20;
+  if (ctx->tc_xp) {
+    if (ctx->tc_xp_n_retired >= 32) return cai_fail(ctx, CAI_ERR_OOM, "tensor-core GEMM: activation buffer regrown too often");
+    ctx->tc_xp_retired[ctx->tc_xp_n_retired++] = ctx->tc_xp;
+    ctx->tc_xp = nullptr;
+    ctx->tc_xp_bytes = 0;
+  }
+  CAI_CUDA(ctx, cudaMalloc(&ctx->tc_xp, need));
+  ctx->tc_xp_bytes = need;
+  return CAI_OK;
+}
 
 // Launches the tensor-core GEMM, or returns CAI_ERR_UNSUPPORTED (no message) when the call is outside
 // what it covers: batches of 9..64 rows, plain or residual epilogue, Q8_0 / Q4_0 weights, no expert indexing.
 int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
   if (!ctx->err_flag || g.expert_ids || g.batch < 9 || g.batch > 64) return CAI_ERR_UNSUPPORTED;
   if (g.epi != EPI_STORE && g.epi != EPI_RESID) return CAI_ERR_UNSUPPORTED;
-  if (g.norm_gain || g.row_scale) return CAI_ERR_UNSUPPORTED;
-  if (((uintptr_t)g.x % 16) || (g.ldx % 4)) return CAI_ERR_UNSUPPORTED;
+  if (g.row_scale) return CAI_ERR_UNSUPPORTED;
+  if (((uintptr_t)g.x % 16) || (g.ldx % 4) || ((uintptr_t)g.codes % 16)) return CAI_ERR_UNSUPPORTED;
+  if (g.norm_gain && ((uintptr_t)g.norm_gain % 16)) return CAI_ERR_UNSUPPORTED;
+  CAI_TRY(gemm_tc_reserve(ctx, g.k, g.batch));
+  const int nb = g.batch <= 16 ? 16 : (g.batch <= 32 ? 32 : 64);
   TcParams p;
   memset(&p, 0, sizeof(p));
-  p.codes = g.codes; p.scales = g.scales; p.bias = g.bias; p.x = g.x; p.ldx = g.ldx; p.y = g.y; p.ldy = g.ldy; p.resid = g.resid;
-  p.n = g.n; p.k = g.k; p.sstride = g.sstride; p.batch = g.batch; p.nb = (g.batch + 15) / 16 * 16; p.act = g.act; p.epi = g.epi;
+  p.codes = (const unsigned char*)g.codes; p.scales = g.scales; p.bias = g.bias;
+  p.row_unscale = (const float*)ctx->tc_xp; p.xp = (const unsigned char*)ctx->tc_xp + 256;
+  p.y = g.y; p.ldy = g.ldy; p.resid = g.resid;
+  p.n = g.n; p.k = g.k; p.sstride = g.sstride; p.batch = g.batch; p.act = g.act; p.epi = g.epi;
   p.err_flag = ctx->err_flag;
-  const size_t smem = 2 * (size_t)(2 * TC_M * TC_KC * 2 + 2 * p.nb * TC_KC * 2);
+  const int n_chunks = (int)((g.k + TC_KC - 1) / TC_KC);
+  {
+    const int threads = g.k >= 2048 ? 512 : 256;
+    tc_split_x_kernel<<<nb, threads, 0, ctx->stream>>>(g.x, g.ldx, g.batch, nb, g.k, n_chunks, 2, g.norm_gain, g.norm_eps,
+                                                       (unsigned char*)ctx->tc_xp + 256, (float*)ctx->tc_xp);
+    CAI_LAUNCHED(ctx);
+  }
   const int grid = (int)((g.n + TC_M - 1) / TC_M);
   cudaError_t e;
-  if (type == CAI_TYPE_Q8_0) {
-    e = cudaFuncSetAttribute(gemm_tc_kernel<CAI_TYPE_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) gemm_tc_kernel<CAI_TYPE_Q8_0><<<grid, TC_THREADS, smem, ctx->stream>>>(p);
-  } else {
-    e = cudaFuncSetAttribute(gemm_tc_kernel<CAI_TYPE_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) gemm_tc_kernel<CAI_TYPE_Q4_0><<<grid, TC_THREADS, smem, ctx->stream>>>(p);
-  }
+  if (type == CAI_TYPE_Q8_0)
+    e = nb == 16 ? tc_launch<CAI_TYPE_Q8_0, 16>(ctx, p, grid) : (nb == 32 ? tc_launch<CAI_TYPE_Q8_0, 32>(ctx, p, grid) : tc_launch<CAI_TYPE_Q8_0, 64>(ctx, p, grid));
+  else
+    e = nb == 16 ? tc_launch<CAI_TYPE_Q4_0, 16>(ctx, p, grid) : (nb == 32 ? tc_launch<CAI_TYPE_Q4_0, 32>(ctx, p, grid) : tc_launch<CAI_TYPE_Q4_0, 64>(ctx, p, grid));
   if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "gemm_tc smem attribute -> %s", cudaGetErrorString(e));
   CAI_LAUNCHED(ctx);
   return CAI_OK;

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
 int gemv_tma_launch(cai_ctx* ctx, GemvParams p, int type, int nb);   // gemv_tma.cu
 int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type);      // gemm_tc.cu
 
-static int env_int(const char* name, int dflt) {
+int env_int(const char* name, int dflt) {
   const char* s = getenv(name);
   return (s && *s) ? atoi(s) : dflt;
 }

@@ -854,6 +854,13 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
     if (comm_ar_create(ctx, 2 * c.layers, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
   }
   if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)3 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
+  if (ok && B >= 9 && B <= 64) {
+    // the tensor-core GEMM's activation buffer must exist before a step is captured into a graph
+    int64_t kmax = H;
+    if (m->qw_l > kmax) kmax = m->qw_l;
+    if (m->inter_l > kmax) kmax = m->inter_l;
+    if (gemm_tc_reserve(ctx, kmax, B) != CAI_OK) ok = false;
+  }
   if (!ok) { cai_session_destroy(s); return cai_fail(ctx, CAI_ERR_OOM, "session buffers do not fit on the device"); }
   CAI_CUDA(ctx, cudaMemsetAsync(s->len_dev, 0, (size_t)B * 4, ctx->stream));
   CAI_CUDA(ctx, cudaMemsetAsync(s->pos_dev, 0, (size_t)B * 4, ctx->stream));
