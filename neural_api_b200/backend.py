@@ -211,6 +211,10 @@ class DotProductSharedKernel:
         self.backend._check(self.backend.lib.cai_linear_weight_bytes(self.handle, C.byref(n)))
         return n.value
 
+    def set_path(self, path):
+        """0 = automatic, 1 = CUDA-core GEMV, 2 = tensor-core GEMM (fails on calls that path does not cover)."""
+        self.backend._check(self.backend.lib.cai_linear_set_path(self.handle, int(path)))
+
     def dequantize_weights(self):
         out = np.empty(self.n * self.k, dtype=np.float32)
         self.backend._check(self.backend.lib.cai_linear_dequantize(self.handle, _ptr(out)))

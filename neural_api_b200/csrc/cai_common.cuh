@@ -54,6 +54,7 @@ int cai_prof_mark(cai_ctx* ctx, int family);
 int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...);
 int env_int(const char* name, int dflt);                    // integer environment knob, gemv.cu
 int gemm_tc_reserve(cai_ctx* ctx, int64_t k, int batch);    // gemm_tc.cu
+bool linear_uses_tensor_cores(const struct QWeight* w, int batch);   // gemv.cu: dispatch policy
 
 #define CAI_CUDA(ctx, call)                                                              \
   do {                                                                                   \

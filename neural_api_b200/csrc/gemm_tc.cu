@@ -1,6 +1,7 @@
 // Dequant-fused GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in
 // tensor memory) for batches of 9..64 activation rows, where the work is a real dense
-// contraction:  Y[b][a] = sum_i W[a][i] * X[b][i],  W = d * code (Q8_0 / Q4_0).
+// contraction:  Y[b][a] = sum_i W[a][i] * X[b][i],  W = d * code (Q8_0 / Q4_0). (Batches of 3..8 rows
+// come here too when the matrix is large: the CUDA-core kernel's 8-row tile is slower.)
 //
 // The block scale d varies along K, so it cannot ride inside one long tensor-core
 // accumulation without rounding d * code to 16 bits. Instead the MMA runs on the integer
@@ -36,41 +37,67 @@ namespace {
 
 constexpr int TC_M = 128;            // weight rows per CTA = UMMA M
 constexpr int TC_KC = 64;            // K per chunk: two 32-blocks, four UMMA K steps of 16
-constexpr int TC_WORKERS = 256;      // threads that stream, convert and read out
-constexpr int TC_THREADS = TC_WORKERS + 32;   // plus the issuing warp
+constexpr int TC_DEPTH = 3;          // weight tiles / accumulator sets in flight between conversion and read-out
 constexpr int TC_RAW_STAGES = 2;     // ring of raw-code stages
-constexpr int TC_B_STAGES = 3;       // ring of activation tiles (one 64-wide chunk each)
 constexpr int TC_A_BYTES = TC_M * TC_KC * 2;  // fp16 weight tile: 16 KB
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
 
-// Per batch width (rows rounded up to 16, 32 or 64): raw bytes per row and ring stage. Two CTAs share an SM up to
-// 32 rows (<= 112 KB each); 64 rows take 512-byte stages and the SM alone.
+// Per batch width (rows rounded up to 16, 32 or 64): worker threads, raw bytes per row and ring stage, depth of the
+// activation ring. Two CTAs share an SM up to 32 rows (<= 112 KB and 256 tensor-memory columns each); 64 rows take
+// the SM alone with twice the worker warps.
 template <int NB> struct TcPlan {
-  static constexpr int SPAN = NB == 16 ? 256 : (NB == 32 ? 128 : 512);
+  static constexpr int WORKERS = NB <= 32 ? 256 : 512;
+  static constexpr int THREADS = WORKERS + 32 * (TC_DEPTH + 1);                 // plus one MMA warp per accumulator set and the activation-tile warp
+  static constexpr int SPAN = NB <= 32 ? 128 : 256;
+  static constexpr int B_STAGES = NB == 32 ? 3 : 4;
   static constexpr int B_BYTES = 2 * NB * 128;                                  // two limbs of NB rows x 128 bytes
-  static constexpr int SMEM = 1024 + 2 * TC_A_BYTES + TC_B_STAGES * B_BYTES + TC_RAW_STAGES * TC_M * SPAN;
+  static constexpr int SMEM = 1024 + TC_DEPTH * TC_A_BYTES + B_STAGES * B_BYTES + TC_RAW_STAGES * TC_M * SPAN;
   static constexpr int ACC_STRIDE = NB < 32 ? 32 : NB;                          // accumulators start on multiples of 32 columns
-  static constexpr int TMEM_COLS = 4 * ACC_STRIDE;                              // 128, 128, 256: powers of two
+  static constexpr int TMEM_COLS = NB <= 32 ? 256 : 512;                        // >= TC_DEPTH * 2 * ACC_STRIDE, a power of two
   static constexpr int MIN_CTAS = NB <= 32 ? 2 : 1;
 };
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// Bounded wait on an mbarrier phase. try_wait may suspend the thread in hardware up to the hinted time, so a
-// waiting warp does not compete for issue slots with the warps that are working.
+// Bounded wait on an mbarrier phase for the worker warps: poll, and between polls step aside for a few dozen
+// nanoseconds so that waiting warps do not crowd the issue slots of the working ones. (try_wait's own
+// suspend-time hint is no use here: measured on B200, a hinted try_wait on an incomplete phase came back only
+// after the full hinted time, 4 us for a hint of 4000.)
 __device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(4000u)
+        : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
+    __nanosleep(32);
+  }
+  return false;
+}
+
+// The same wait for the single issuing lanes, with a shorter pause: they should notice completion quickly, but a
+// lane that polls without pause keeps the shared-memory pipeline busy, and every shared-memory instruction of the
+// working warps (loads, stores, arrivals) queues behind its polls.
+__device__ __forceinline__ bool tc_mbar_spin(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT * 4u; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    __nanosleep(20);
   }
   return false;
 }
@@ -114,6 +141,38 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The four MMAs of one 32-block (two K steps of 16 x two activation limbs) into one fresh accumulator, from the low
+// and high words of the A and B descriptors of the block's first K step. Only the start-address field (low word, units
+// of 16 bytes) differs between them: +2 for the second K step, +limb for the second limb. One asm statement, so the
+// lone issuing thread spends a handful of instructions per MMA.
+__device__ __forceinline__ void umma_block(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t limb,
+                                           uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b64 a0, a1, b0, b1, b2, b3;\n"
+      ".reg .b32 t0, t1, t2, t3;\n"
+      "setp.ne.b32 p0, %0, %0;\n"
+      "setp.eq.b32 p1, %0, %0;\n"
+      "mov.b64 a0, {%1, %2};\n"
+      "add.u32 t0, %1, 2;\n"
+      "mov.b64 a1, {t0, %2};\n"
+      "mov.b64 b0, {%3, %4};\n"
+      "add.u32 t1, %3, %5;\n"
+      "mov.b64 b1, {t1, %4};\n"
+      "add.u32 t2, %3, 2;\n"
+      "mov.b64 b2, {t2, %4};\n"
+      "add.u32 t3, t1, 2;\n"
+      "mov.b64 b3, {t3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a0, b0, %6, p0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a0, b1, %6, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b2, %6, p1;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b3, %6, p1;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(limb), "r"(idesc)
       : "memory");
 }
 
@@ -251,8 +310,11 @@ __device__ __forceinline__ void tc_tmem_ld(uint32_t taddr, uint32_t* r) {
 }
 
 template <int TYPE, int NB>
-__global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kernel(const TcParams p) {
+__global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kernel(const TcParams p) {
   using Plan = TcPlan<NB>;
+  constexpr int W = Plan::WORKERS;                                           // worker threads
+  constexpr int D = TC_DEPTH;
+  constexpr int SB = Plan::B_STAGES;
   constexpr int SPAN = Plan::SPAN;                                           // raw code bytes per row and stage
   constexpr int PPR = SPAN / 16;                                             // 16-byte pieces per row and stage
   constexpr int PIECES = (TYPE == CAI_TYPE_Q8_0) ? 4 : 2;                    // pieces per row and 64-wide chunk
@@ -261,31 +323,35 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
   constexpr int LIMB_BYTES = NB * 128;                                       // one fp16 limb of the activation tile
   constexpr int B_BYTES = Plan::B_BYTES;
   constexpr int ACC_STRIDE = Plan::ACC_STRIDE;
-  constexpr int NCOL = NB / 2;                                               // batch columns a worker thread owns
+  constexpr int NCOL = NB / (W / 128);                                       // batch columns a worker thread owns
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t mma_bar[2];            // MMAs of chunk c done (tcgen05.commit), c & 1
-  __shared__ __align__(8) uint64_t a_ready[2];            // weight tile of chunk c converted (TC_WORKERS arrivals), c & 1
-  __shared__ __align__(8) uint64_t b_full[TC_B_STAGES];   // activation tile landed (bytes of a bulk copy)
+  __shared__ __align__(8) uint64_t mma_bar[D];            // MMAs of chunk c done (tcgen05.commit), c % D
+  __shared__ __align__(8) uint64_t a_ready[D];            // weight tile of chunk c converted (one arrival per worker warp), c % D
+  __shared__ __align__(8) uint64_t b_full[SB];            // activation tile landed (bytes of a bulk copy)
+  __shared__ __align__(8) uint64_t b_empty[SB];           // the MMAs that read the activation tile are done (tcgen05.commit)
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // operand tiles start on 1024-byte boundaries (the swizzle works on absolute shared-memory address bits)
   const uint32_t smem0 = (tc_smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t a_st = smem0;                                               // 2 stages of 16 KB
-  const uint32_t b_st = a_st + 2 * TC_A_BYTES;                               // TC_B_STAGES stages, each a multiple of 1 KB
-  const uint32_t raw_st = b_st + TC_B_STAGES * B_BYTES;                      // TC_RAW_STAGES stages
+  const uint32_t a_st = smem0;                                               // D tiles of 16 KB
+  const uint32_t b_st = a_st + D * TC_A_BYTES;                               // SB tiles, each a multiple of 1 KB
+  const uint32_t raw_st = b_st + SB * B_BYTES;                               // TC_RAW_STAGES stages
 
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(&tmem_base_s)), "r"((uint32_t)Plan::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < D; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&mma_bar[i])) : "memory");
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem_u32(&a_ready[i])), "r"(TC_WORKERS) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_smem_u32(&a_ready[i])), "r"(W / 32) : "memory");
     }
-    for (int i = 0; i < TC_B_STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&b_full[i])) : "memory");
+    for (int i = 0; i < SB; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&b_full[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(&b_empty[i])) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -301,63 +367,69 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
   const int n_blocks = (int)(K >> 5);
   const int n_stages = (n_chunks + SUB - 1) / SUB;
 
-  if (warp == TC_WORKERS / 32) {
+  if (warp == W / 32 + D) {
     // =====================================================================================
-    // Issuing warp (one lane): activation-tile copies and the MMAs.
+    // Activation-tile warp (one lane): one bulk copy per chunk (the split kernel wrote the tile in the layout the
+    // MMA reads) into ring slot j % SB, completion counted in bytes on that slot's mbarrier; a slot is refilled once
+    // the MMAs that read it are done.
+    // =====================================================================================
+    if (lane == 0) {
+      const uint32_t bar_f = tc_smem_u32(&b_full[0]), bar_e = tc_smem_u32(&b_empty[0]);
+      int slot = 0;
+      uint32_t eparity = 1;                                 // parity of the "emptied" phase awaited: none on the first lap
+      const unsigned char* src = p.xp;
+      for (int j = 0; j < n_chunks; ++j) {
+        if (j >= SB && !tc_mbar_wait(bar_e + 8u * slot, eparity)) { *p.err_flag = 1; break; }
+        const uint32_t bar = bar_f + 8u * (uint32_t)slot;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)B_BYTES) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                         b_st + (uint32_t)(slot * B_BYTES)),
+                     "l"(src), "r"((uint32_t)B_BYTES), "r"(bar)
+                     : "memory");
+        src += B_BYTES;
+        if (++slot == SB) { slot = 0; eparity ^= 1; }
+      }
+    }
+  } else if (warp >= W / 32) {
+    // =====================================================================================
+    // MMA warps (one lane each), one per accumulator set: warp s issues the chunks c = s, s + D, ... A lone thread
+    // runs slowly on a busy SM (measured ~1600 cycles for the waits, the eight MMAs and the commits of one chunk),
+    // so the chunks are dealt out over D issuing threads.
     // =====================================================================================
     if (lane == 0) {
       bool alive = true;
+      const int set = warp - W / 32;
       const uint32_t idesc = umma_idesc(TC_M, NB);
-      const uint64_t da0 = umma_desc(a_st), db0 = umma_desc(b_st);
-      const uint32_t bar_mma = tc_smem_u32(&mma_bar[0]), bar_a = tc_smem_u32(&a_ready[0]), bar_b = tc_smem_u32(&b_full[0]);
-      auto issue_b = [&](int j, int slot) {
-        if (j < n_chunks) {
-          const uint32_t bar = bar_b + 8u * (uint32_t)slot;
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)B_BYTES) : "memory");
-          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                           b_st + (uint32_t)(slot * B_BYTES)),
-                       "l"(p.xp + (size_t)j * B_BYTES), "r"((uint32_t)B_BYTES), "r"(bar)
-                       : "memory");
-        }
-      };
-      issue_b(0, 0);
-      issue_b(1, 1);
-      int bslot = 0, bphase = 0;                            // ring slot and phase parity of chunk c
-      for (int c = 0; c < n_chunks; ++c) {
-        const int stage = c & 1;
-        // weight tile converted (which also says the workers have read out the accumulators of chunk c-2), activation tile landed
-        if (alive && !tc_mbar_wait(bar_a + 8u * stage, (uint32_t)((c >> 1) & 1))) { alive = false; *p.err_flag = 1; }
-        if (alive && !tc_mbar_wait(bar_b + 8u * bslot, (uint32_t)bphase)) { alive = false; *p.err_flag = 1; }
+      const uint64_t da0 = umma_desc(a_st + (uint32_t)(set * TC_A_BYTES)), db0 = umma_desc(b_st);
+      const uint32_t a_lo = (uint32_t)da0, a_hi = (uint32_t)(da0 >> 32), b_lo0 = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t bar_mma = tc_smem_u32(&mma_bar[set]), bar_a = tc_smem_u32(&a_ready[set]);
+      const uint32_t bar_f = tc_smem_u32(&b_full[0]), bar_e = tc_smem_u32(&b_empty[0]);
+      const uint32_t d_t = tmem_d + (uint32_t)(set * 2 * ACC_STRIDE);
+      uint32_t aparity = 0;
+      for (int c = set; c < n_chunks; c += D) {
+        const int bslot = c % SB;
+        // weight tile converted (which also says the workers have read out the accumulators of chunk c-D), activation tile landed
+        if (alive && !tc_mbar_spin(bar_a, aparity)) { alive = false; *p.err_flag = 1; }
+        if (alive && !tc_mbar_spin(bar_f + 8u * bslot, (uint32_t)((c / SB) & 1))) { alive = false; *p.err_flag = 1; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // descriptors differ from the base ones only in the start address field (units of 16 bytes)
-        const uint64_t da = da0 + (uint64_t)((stage * TC_A_BYTES) >> 4);
-        const uint64_t db = db0 + (uint64_t)((bslot * B_BYTES) >> 4);
-        const uint32_t d_t = tmem_d + (uint32_t)(stage * 2 * ACC_STRIDE);
-        // each 32-block into its own fresh accumulator: two K steps of 16 (32 bytes of a 128-byte row each), two limbs
-        umma_f16(d_t, da, db, idesc, 0u);
-        umma_f16(d_t, da, db + (LIMB_BYTES >> 4), idesc, 1u);
-        umma_f16(d_t, da + 2, db + 2, idesc, 1u);
-        umma_f16(d_t, da + 2, db + (LIMB_BYTES >> 4) + 2, idesc, 1u);
-        if (2 * c + 1 < n_blocks) {
-          umma_f16(d_t + ACC_STRIDE, da + 4, db + 4, idesc, 0u);
-          umma_f16(d_t + ACC_STRIDE, da + 4, db + (LIMB_BYTES >> 4) + 4, idesc, 1u);
-          umma_f16(d_t + ACC_STRIDE, da + 6, db + 6, idesc, 1u);
-          umma_f16(d_t + ACC_STRIDE, da + 6, db + (LIMB_BYTES >> 4) + 6, idesc, 1u);
-        }
-        // arrives on the barrier once every MMA issued so far has finished (operands read, accumulators written)
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_mma + 8u * stage) : "memory");
-        // refill the activation ring two chunks ahead: that slot's previous tile was read by the MMAs of chunk c-1
-        if (c >= 1 && alive && !tc_mbar_wait(bar_mma + 8u * (stage ^ 1), (uint32_t)(((c - 1) >> 1) & 1))) { alive = false; *p.err_flag = 1; }
-        issue_b(c + 2, bslot == 0 ? TC_B_STAGES - 1 : bslot - 1);
-        if (++bslot == TC_B_STAGES) { bslot = 0; bphase ^= 1; }
+        const uint32_t b_lo = b_lo0 + (uint32_t)((bslot * B_BYTES) >> 4);
+        // each 32-block into its own fresh accumulator; the second block starts 64 bytes (4 units) into the rows
+        umma_block(d_t, a_lo, a_hi, b_lo, b_hi, (uint32_t)(LIMB_BYTES >> 4), idesc);
+        if (2 * c + 1 < n_blocks) umma_block(d_t + ACC_STRIDE, a_lo + 4, a_hi, b_lo + 4, b_hi, (uint32_t)(LIMB_BYTES >> 4), idesc);
+        // both arrive once every MMA issued so far by this thread has finished (operands read, accumulators written);
+        // the activation slot's barrier only while someone will still wait on it
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_mma) : "memory");
+        if (c + SB < n_chunks)
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_e + 8u * bslot) : "memory");
+        aparity ^= 1;
       }
     }
   } else {
     // =====================================================================================
-    // Worker warps. Read-out role: warp w reads accumulator lanes 32*(w&3).., batch columns [hb*NB/2, (hb+1)*NB/2),
-    // hb = w >> 2. Everything that does not change from chunk to chunk is computed here, once.
+    // Worker warps. Read-out role: warp w reads accumulator lanes 32*(w&3).., batch columns [cg*NCOL, (cg+1)*NCOL),
+    // cg = w >> 2. Everything that does not change from chunk to chunk is computed here, once.
     // =====================================================================================
-    const int lane_q = warp & 3, hb = warp >> 2;
+    const int lane_q = warp & 3, cg = warp >> 2;
     int64_t my_row = row0 + lane_q * 32 + lane;
     const bool row_ok = my_row < p.n;
     if (!row_ok) my_row = p.n - 1;
@@ -368,14 +440,15 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
     for (int j = 0; j < NCOL; ++j) acc[j] = 0.f;
     bool alive = true;
     const uint32_t bar_mma = tc_smem_u32(&mma_bar[0]), bar_a = tc_smem_u32(&a_ready[0]);
-    const uint32_t t_lane = tmem_d + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(hb * NCOL);
+    const uint32_t t_lane = tmem_d + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(cg * NCOL);
     const int rmax = (int)((p.n - 1 - row0 < TC_M - 1) ? (p.n - 1 - row0) : (TC_M - 1));   // last valid row of the tile
 
-    // ---- raw-code producer. Item i = tid + 256 t of a stage is 16-byte piece (i % PPR) of row (i / PPR): a thread
-    //      keeps its piece and walks down the rows in steps of 256 / PPR, so source and destination advance by constants.
+    // ---- raw-code producer. Item i = tid + W t of a stage is 16-byte piece (i % PPR) of row (i / PPR): a thread
+    //      keeps its piece and walks down the rows in steps of W / PPR, so source and destination advance by constants.
     //      The pieces of a row are XOR-swizzled with the row, so that the conversion, which walks rows, reads without
     //      bank conflicts (the row step is a multiple of 8, so a thread's swizzle is fixed too).
-    constexpr int RSTEP = TC_WORKERS / PPR;
+    constexpr int RSTEP = W / PPR;
+    static_assert(RSTEP % 8 == 0, "row step must keep the swizzle fixed");
     const int pr_pc = tid & (PPR - 1), pr_r0 = tid / PPR;
     const uint32_t pr_dst0 = (uint32_t)(pr_r0 * SPAN + ((pr_pc ^ (pr_r0 & 7)) << 4));
     const unsigned char* pr_src0 = p.codes + row0 * row_bytes + pr_pc * 16;
@@ -386,7 +459,7 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
         const bool valid = byte0 + pr_pc * 16 < row_bytes;                // K tail: zero-fill instead of reading
         const unsigned char* src = pr_src0 + (valid ? byte0 : 0);
 #pragma unroll
-        for (int t = 0; t < PPR / 2; ++t) {
+        for (int t = 0; t < TC_M / RSTEP; ++t) {
           int r = pr_r0 + t * RSTEP;
           r = r < rmax ? r : rmax;                                        // rows past the matrix re-read its last row
           tc_cp_async16(dst + (uint32_t)(t * RSTEP * SPAN), src + (int64_t)r * row_bytes, valid ? 16u : 0u);
@@ -395,71 +468,78 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
       tc_cp_async_commit();                                 // one group per stage index, empty past the end
     };
 
-    // ---- conversion addresses: thread handles row cv_r, pieces cv_q (+2 for its second item) of each chunk
+    // ---- conversion: item i = tid + W t of a chunk is row (i & 127), 16-byte piece (i >> 7) of the chunk's raw bytes
     const int cv_r = tid & 127, cv_q = tid >> 7, cv_s = cv_r & 7;
     const uint32_t cv_src = (uint32_t)(cv_r * SPAN);
     const uint32_t cv_dst = (uint32_t)(cv_r * 128);
 
-    // ---- read-out of chunk cc: acc += d[row][block] * accumulator, for the chunk's (up to) two blocks
-    auto readout = [&](int cc) {
-      if (alive && !tc_mbar_wait(bar_mma + 8u * (cc & 1), (uint32_t)((cc >> 1) & 1))) {
+    // ---- read-out of chunk cc: readout_begin waits for the chunk's MMAs and starts the loads of its (up to) two
+    //      accumulators; readout_end waits for the loads and adds  d[row][block] * accumulator  into acc.
+    uint32_t r0[NCOL], r1[NCOL];
+    auto readout_begin = [&](int cc) {
+      const int set = cc % D;
+      if (alive && !tc_mbar_wait(bar_mma + 8u * set, (uint32_t)((cc / D) & 1))) {
         alive = false;
         if (lane == 0) *p.err_flag = 1;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = t_lane + (uint32_t)(set * 2 * ACC_STRIDE);
+      tc_tmem_ld<NCOL>(taddr, r0);
+      if (2 * cc + 1 < n_blocks) tc_tmem_ld<NCOL>(taddr + ACC_STRIDE, r1);
+    };
+    auto readout_end = [&](int cc) {
       if ((cc & 3) == 0) {
         sc_cur = sc_next;
         if (cc + 4 < n_chunks) sc_next = srow[(cc >> 2) + 1];
       }
       const int sel = cc & 3;
       const uint32_t dw = sel == 0 ? sc_cur.x : (sel == 1 ? sc_cur.y : (sel == 2 ? sc_cur.z : sc_cur.w));
-      const uint32_t taddr = t_lane + (uint32_t)((cc & 1) * 2 * ACC_STRIDE);
-      uint32_t r0[NCOL], r1[NCOL];
-      const bool two = 2 * cc + 1 < n_blocks;
-      tc_tmem_ld<NCOL>(taddr, r0);
-      if (two) tc_tmem_ld<NCOL>(taddr + ACC_STRIDE, r1);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const float d0 = __half2float(__ushort_as_half((unsigned short)(dw & 0xFFFF)));
+      const float d1 = __half2float(__ushort_as_half((unsigned short)(dw >> 16)));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
       for (int j = 0; j < NCOL; ++j) acc[j] = fmaf(d0, __uint_as_float(r0[j]), acc[j]);
-      if (two) {
-        const float d1 = __half2float(__ushort_as_half((unsigned short)(dw >> 16)));
+      if (2 * cc + 1 < n_blocks) {
 #pragma unroll
         for (int j = 0; j < NCOL; ++j) acc[j] = fmaf(d1, __uint_as_float(r1[j]), acc[j]);
       }
-      // orders the loads above before the arrival that lets the issuing warp overwrite these accumulators
+      // orders the loads above before the arrival that lets an MMA warp overwrite these accumulators
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
 
     for (int j = 0; j < TC_RAW_STAGES; ++j) issue_raw(j);
+    // this thread's copies of stage 0 have landed; after the barrier, every worker's
+    tc_cp_async_wait(TC_RAW_STAGES - 1);
+    asm volatile("bar.sync 1, %0;" ::"n"(W) : "memory");
 
     int c = 0;
     for (int rs = 0; rs < n_stages; ++rs) {
-      // (a) this thread's copies of the stage have landed; after the barrier, every worker's
-      tc_cp_async_wait(TC_RAW_STAGES - 1);
-      asm volatile("bar.sync 1, %0;" ::"n"(TC_WORKERS) : "memory");
       const uint32_t raw = raw_st + (uint32_t)((rs & (TC_RAW_STAGES - 1)) * RAW_BYTES) + cv_src;
 #pragma unroll
       for (int u = 0; u < SUB; ++u) {
         if (c < n_chunks) {
-          const int stage = c & 1;
-          // (b) raw codes -> fp16 integers in the swizzled A-tile layout. The A stage was last read by the MMAs of
-          //     chunk c-2, whose completion this thread awaited in the read-out of the previous iteration.
-          const uint32_t a_t = a_st + (uint32_t)(stage * TC_A_BYTES) + cv_dst;
+          const int set = c % D;
+          // (b) raw codes -> fp16 integers in the swizzled A-tile layout. The tile was last read by the MMAs of
+          //     chunk c-D, whose completion this thread awaited in an earlier iteration. Loads first, so that
+          //     their latency overlaps.
+          const uint32_t a_t = a_st + (uint32_t)(set * TC_A_BYTES) + cv_dst;
           if (TYPE == CAI_TYPE_Q8_0) {
             constexpr uint32_t BIAS = 0x64806480u;          // fp16 1152 = 1024 + 128: stored codes are q + 128
+            constexpr int ITEMS = 512 / W;
+            uint4 w[ITEMS];
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {                   // row fastest: 8 consecutive threads touch 8 distinct bank groups
-              const int q = cv_q + 2 * t;
-              const uint4 w = tc_lds128(raw + (uint32_t)((((u * 4 + q) ^ cv_s)) << 4));
-              tc_sts128(a_t + (uint32_t)(((2 * q) ^ cv_s) << 4), bytes_to_half2(w.x, 0x4140, BIAS), bytes_to_half2(w.x, 0x4342, BIAS),
-                        bytes_to_half2(w.y, 0x4140, BIAS), bytes_to_half2(w.y, 0x4342, BIAS));
-              tc_sts128(a_t + (uint32_t)(((2 * q + 1) ^ cv_s) << 4), bytes_to_half2(w.z, 0x4140, BIAS), bytes_to_half2(w.z, 0x4342, BIAS),
-                        bytes_to_half2(w.w, 0x4140, BIAS), bytes_to_half2(w.w, 0x4342, BIAS));
+            for (int t = 0; t < ITEMS; ++t) w[t] = tc_lds128(raw + (uint32_t)((((u * 4 + cv_q + (W / 128) * t) ^ cv_s)) << 4));
+#pragma unroll
+            for (int t = 0; t < ITEMS; ++t) {               // row fastest: 8 consecutive threads touch 8 distinct bank groups
+              const int q = cv_q + (W / 128) * t;
+              tc_sts128(a_t + (uint32_t)(((2 * q) ^ cv_s) << 4), bytes_to_half2(w[t].x, 0x4140, BIAS), bytes_to_half2(w[t].x, 0x4342, BIAS),
+                        bytes_to_half2(w[t].y, 0x4140, BIAS), bytes_to_half2(w[t].y, 0x4342, BIAS));
+              tc_sts128(a_t + (uint32_t)(((2 * q + 1) ^ cv_s) << 4), bytes_to_half2(w[t].z, 0x4140, BIAS), bytes_to_half2(w[t].z, 0x4342, BIAS),
+                        bytes_to_half2(w[t].w, 0x4140, BIAS), bytes_to_half2(w[t].w, 0x4342, BIAS));
             }
-          } else {
+          } else if (tid < 256) {                           // 256 blocks of 32 nibble codes per chunk: one per thread
             constexpr uint32_t BIAS = 0x64086408u;          // fp16 1032 = 1024 + 8
-            const int blk = cv_q;                           // one 16-byte block of 32 nibble codes per thread
+            const int blk = cv_q;
             const uint4 w = tc_lds128(raw + (uint32_t)((((u * 2 + blk) ^ cv_s)) << 4));
             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
             uint32_t lo[4], hi[4];
@@ -476,28 +556,37 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
             tc_sts128(a_t + (uint32_t)(((j0 + 3) ^ cv_s) << 4), bytes_to_half2(hi[2], 0x4140, BIAS), bytes_to_half2(hi[2], 0x4342, BIAS),
                       bytes_to_half2(hi[3], 0x4140, BIAS), bytes_to_half2(hi[3], 0x4342, BIAS));
           }
-          // (c) make the stores visible to the tensor-core (async) proxy and tell the issuing warp: the tile of
-          //     chunk c is ready, and this thread is done with the accumulators of chunk c-2
+          // (c) make the stores visible to the tensor-core (async) proxy and tell the chunk's MMA warp: the tile is
+          //     ready, and this thread is done with the accumulators of chunk c-D (read out in the previous iteration)
+          //     One arrival per warp: 256 separate arrivals on one barrier word serialize.
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a + 8u * stage) : "memory");
-          // (d) while the tensor core works on chunk c, fold chunk c-1 into the registers
-          if (c >= 1) readout(c - 1);
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a + 8u * set) : "memory");
+          // (d) fold chunk c-(D-1) into the registers: its MMAs were issued D-1 iterations ago. (Starting the
+          //     tensor-memory loads before the conversion, to hide their latency, measured no gain, and registers
+          //     with such a load in flight must not be touched, not even by a spill, until the wait.)
+          if (c >= D - 1) {
+            readout_begin(c - (D - 1));
+            readout_end(c - (D - 1));
+          }
           ++c;
         }
       }
-      // (e) the raw slot is free once every worker has converted the stage's last chunk
-      asm volatile("bar.sync 1, %0;" ::"n"(TC_WORKERS) : "memory");
+      // (e) one barrier per stage: this thread's copies of the next stage have landed and it has converted this
+      //     stage's last chunk; after the barrier that holds for every worker, so the slot can be refilled
+      tc_cp_async_wait(0);
+      asm volatile("bar.sync 1, %0;" ::"n"(W) : "memory");
       issue_raw(rs + TC_RAW_STAGES);
     }
-    readout(n_chunks - 1);
+    for (int cc = (n_chunks >= D - 1 ? n_chunks - (D - 1) : 0); cc < n_chunks; ++cc) { readout_begin(cc); readout_end(cc); }
     tc_cp_async_wait(0);
 
-    // ---- epilogue: thread = weight row, acc[j] = batch column hb * NB/2 + j ----
+    // ---- epilogue: thread = weight row, acc[j] = batch column cg * NCOL + j ----
     if (row_ok) {
       const float bias = p.bias ? p.bias[my_row] : 0.f;
 #pragma unroll
       for (int j = 0; j < NCOL; ++j) {
-        const int b = hb * NCOL + j;
+        const int b = cg * NCOL + j;
         if (b < p.batch) {
           float v = fmaf(acc[j], p.row_unscale[b], bias);
           v = apply_act(v, p.act);
@@ -515,7 +604,7 @@ __global__ void __launch_bounds__(TC_THREADS, TcPlan<NB>::MIN_CTAS) gemm_tc_kern
 template <int TYPE, int NB>
 cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid) {
   cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcPlan<NB>::SMEM);
-  if (e == cudaSuccess) gemm_tc_kernel<TYPE, NB><<<grid, TC_THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
+  if (e == cudaSuccess) gemm_tc_kernel<TYPE, NB><<<grid, TcPlan<NB>::THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
   return e;
 }
 
@@ -542,9 +631,10 @@ int gemm_tc_reserve(cai_ctx* ctx, int64_t k, int batch) {
 }
 
 // Launches the tensor-core GEMM, or returns CAI_ERR_UNSUPPORTED (no message) when the call is outside
-// what it covers: batches of 9..64 rows, plain or residual epilogue, Q8_0 / Q4_0 weights, no expert indexing.
+// what it covers: batches of 1..64 rows, plain or residual epilogue, Q8_0 / Q4_0 weights, no expert indexing.
+// (Which batches are worth sending here is the caller's policy.)
 int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
-  if (!ctx->err_flag || g.expert_ids || g.batch < 9 || g.batch > 64) return CAI_ERR_UNSUPPORTED;
+  if (!ctx->err_flag || g.expert_ids || g.batch < 1 || g.batch > 64) return CAI_ERR_UNSUPPORTED;
   if (g.epi != EPI_STORE && g.epi != EPI_RESID) return CAI_ERR_UNSUPPORTED;
   if (g.row_scale) return CAI_ERR_UNSUPPORTED;
   if (((uintptr_t)g.x % 16) || (g.ldx % 4) || ((uintptr_t)g.codes % 16)) return CAI_ERR_UNSUPPORTED;

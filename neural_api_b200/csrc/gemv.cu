@@ -350,6 +350,14 @@ static cudaError_t launch_quant_nb(cai_ctx* ctx, const GemvParams& p, int nb, in
   return launch_quant<TYPE, 8>(ctx, p, rpw, grid, threads, smem);
 }
 
+// Batches the dispatcher sends to the tensor-core GEMM when nothing forces a path.
+bool linear_uses_tensor_cores(const QWeight* w, int batch) {
+  if (!w || (w->type != CAI_TYPE_Q8_0 && w->type != CAI_TYPE_Q4_0)) return false;
+  if (batch > 64) return false;
+  if (batch >= 9) return true;
+  return batch >= 3 && w->n * w->k >= ((int64_t)32 << 20);
+}
+
 bool linear_can_fuse_norm(const QWeight* w, int batch) {
   if (!w || (w->type != CAI_TYPE_Q8_0 && w->type != CAI_TYPE_Q4_0)) return false;
   if (env_int("CAI_FUSE_NORM", 1) == 0) return false;
@@ -405,12 +413,18 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     if (st != CAI_ERR_UNSUPPORTED) return st;
   }
   // batches of 9..64 rows are a real contraction: tensor cores (tcgen05), unless the call needs a fused
-  // epilogue only the CUDA-core kernel has, or CAI_GEMM_TC=0
-  if (!indexed && a.batch >= 9 && a.batch <= 64 && a.path != 1 && env_int("CAI_GEMM_TC", 1) != 0) {
-    const int st = gemm_tc_launch(ctx, p, w->type);
+  // epilogue only the CUDA-core kernel has, or CAI_GEMM_TC=0. Batches of 3..8 rows go there too when the matrix
+  // is large (measured on 5120 x 27648 Q8_0: 78 us on the tensor cores for up to 16 rows, against 180 us at 4 rows
+  // and 316 us at 8 rows for the CUDA-core kernel; 52 us at 2 rows stays); small matrices stay, the tensor-core
+  // path has a floor of ~17 us (two launches, pipeline fill).
+  if (!indexed && a.batch <= 64 && a.path != 1 && env_int("CAI_GEMM_TC", 1) != 0 &&
+      (a.path == 2 || linear_uses_tensor_cores(w, a.batch))) {
+    GemvParams pt = p;
+    pt.norm_gain = a.norm_gain; pt.norm_eps = a.norm_eps;        // the activation-split kernel applies the norm
+    const int st = gemm_tc_launch(ctx, pt, w->type);
     if (st != CAI_ERR_UNSUPPORTED) return st;
   }
-  if (a.path == 2) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: the tensor-core path covers batches of 9..64 rows with plain or residual epilogues");
+  if (a.path == 2) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: the tensor-core path covers batches of up to 64 rows with plain or residual epilogues");
   // batch tile
   int nb = 1;
   if (!indexed) nb = a.batch >= 5 ? 8 : (a.batch >= 3 ? 4 : (a.batch == 2 ? 2 : 1));

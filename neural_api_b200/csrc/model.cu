@@ -622,9 +622,9 @@ static int enqueue_step(cai_session* s) {
   };
   CAI_TRY(op_embed(ctx, &m->embed, s->tokens_dev, B, x, H));
   CAI_TRY(op_rope_table(ctx, m->theta, s->pos_dev, B, c.head_dim / 2, s->rope_cs));
-  // Batches of 9..64 rows go through the tensor-core GEMM, which has plain epilogues only: RoPE/append and SwiGLU
-  // then run as their own kernels.
-  const bool tc_batch = (B >= 9 && B <= 64) && (m->layers[0].wqkv.type == CAI_TYPE_Q8_0 || m->layers[0].wqkv.type == CAI_TYPE_Q4_0);
+  // Batches the dispatcher sends to the tensor-core GEMM (9..64 rows; 3..8 on large matrices) get plain epilogues
+  // only: RoPE/append and SwiGLU then run as their own kernels.
+  const bool tc_batch = linear_uses_tensor_cores(&m->layers[0].wgu, B) || linear_uses_tensor_cores(&m->layers[0].wqkv, B);
   const bool fuse_rope = !c.qk_norm && !tc_batch;     // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
@@ -672,7 +672,8 @@ static int enqueue_step(cai_session* s) {
     if (!c.n_experts) {
       {
         if (tc_batch && s->gu) {
-          LinearArgs a; a.w = &L.wgu; a.x = s->h; a.ldx = H; a.y = s->gu; a.ldy = 2 * (int64_t)m->inter_l; a.batch = B;
+          LinearArgs a; a.w = &L.wgu; a.x = fuse_ffn_norm ? x : s->h; a.ldx = H; a.y = s->gu; a.ldy = 2 * (int64_t)m->inter_l; a.batch = B;
+          if (fuse_ffn_norm) { a.norm_gain = L.ffn_norm; a.norm_eps = c.rms_eps; }
           CAI_TRY(linear_launch(ctx, a));
           CAI_TRY(op_swiglu(ctx, s->gu, 2 * (int64_t)m->inter_l, s->act, m->inter_l, B, m->inter_l));
         } else {
@@ -834,7 +835,7 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   A((void**)&s->qkv, (size_t)B * QKVW * 4); A((void**)&s->att, (size_t)B * m->qw_l * 4);
   A((void**)&s->act, (size_t)B * (m->inter_l ? m->inter_l : 1) * 4);
   A((void**)&s->logits, (size_t)B * m->vocab_l * 4);
-  if (B >= 9 && m->inter_l) A((void**)&s->gu, (size_t)B * 2 * m->inter_l * 4);
+  if (B >= 3 && B <= 64 && m->inter_l) A((void**)&s->gu, (size_t)B * 2 * m->inter_l * 4);
   A((void**)&s->partial, attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim) * 4);
   A((void**)&s->amax_idx, (size_t)B * 4); A((void**)&s->amax_val, (size_t)B * 4);
   A((void**)&s->amax_part_val, (size_t)B * CAI_ARGMAX_CHUNKS * 4); A((void**)&s->amax_part_idx, (size_t)B * CAI_ARGMAX_CHUNKS * 4);
@@ -854,7 +855,7 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
     if (comm_ar_create(ctx, 2 * c.layers, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
   }
   if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)3 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
-  if (ok && B >= 9 && B <= 64) {
+  if (ok && B >= 3 && B <= 64) {
     // the tensor-core GEMM's activation buffer must exist before a step is captured into a graph
     int64_t kmax = H;
     if (m->qw_l > kmax) kmax = m->qw_l;

@@ -13,9 +13,9 @@ pytestmark = pytest.mark.gpu
 # max |y - y_ref| <= TOL * RMS(y_ref). fp32 accumulation in a different order from BLAS;
 # the budget the decode path is held to is 1e-3.
 TOL = 2e-5
-# Batches of 9..64 rows run on the tensor cores with weights and activations split into two bf16 limbs
-# (three MMAs per product): ~1e-5 per product, still two orders inside the 1e-3 budget.
-TOL_TC = 2e-4
+# Batches of 9..64 rows (3..8 on large matrices) run on the tensor cores: exact integer codes times activations
+# split into two fp16 limbs (22 bits), per-block sums scaled in fp32. Measured ~1e-6 of the output RMS.
+TOL_TC = 2e-5
 
 
 def make_blocks(ggml_type, n, k, seed):
@@ -75,6 +75,30 @@ def test_ragged_shapes_and_batches(backend, ggml_type, n, k, b):
         y = lin.finish_and_load_result()
         ref = codecs.linear_fp32(w, x, bias)
         assert rel_err(y, ref) < (TOL if b <= 8 else TOL_TC)
+    finally:
+        lin.unprepare_for_compute()
+
+
+@pytest.mark.parametrize("ggml_type", [codecs.GGML_Q8_0, codecs.GGML_Q4_0])
+@pytest.mark.parametrize("b", [1, 3, 8, 16, 40])
+def test_forced_tensor_core_path_any_batch(backend, ggml_type, b):
+    """cai_linear_set_path(2): the tcgen05 GEMM for every batch it accepts, ragged N and a half K chunk."""
+    n, k = 300, 1056
+    blk = make_blocks(ggml_type, n, k, seed=5)
+    w = codecs.dequantize(ggml_type, blk).reshape(n, k)
+    rng = np.random.default_rng(b)
+    x = (rng.standard_normal((b, k)) * rng.uniform(1e-3, 1e3, (b, 1))).astype(np.float32)     # rows of very different scale
+    lin = DotProductSharedKernel(backend)
+    lin.prepare_for_compute_quant(ggml_type, blk, n, k)
+    try:
+        lin.set_path(2)
+        before = backend.launch_count()
+        lin.compute_quant(x)
+        assert backend.launch_count() - before == 2          # activation split + GEMM
+        y = lin.finish_and_load_result()
+        ref = x.astype(np.float64) @ w.astype(np.float64).T
+        for i in range(b):                                   # per row: each has its own scale
+            assert rel_err(y[i], ref[i]) < TOL_TC
     finally:
         lin.unprepare_for_compute()
 
