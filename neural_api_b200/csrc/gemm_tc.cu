@@ -189,6 +189,10 @@ struct TcParams {
   int batch;
   int act, epi;
   int* err_flag;
+  // K split over blockIdx.y (matrices with few row tiles): CTA (x, y) handles chunks [y * chunks_per_split, ...)
+  // and, when ksplit > 1, stores its unscaled-by-nothing partial sums to part[y][b][row] for the reduce kernel.
+  int ksplit, chunks_per_split;
+  float* part;
 };
 
 // ---------------------------------------------------------------------------
@@ -363,9 +367,14 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
   const int64_t row0 = (int64_t)blockIdx.x * TC_M;
   const int64_t K = p.k;
   const int64_t row_bytes = (TYPE == CAI_TYPE_Q8_0) ? K : (K >> 1);
-  const int n_chunks = (int)((K + TC_KC - 1) / TC_KC);    // K is a multiple of 32: the last chunk may be half
-  const int n_blocks = (int)(K >> 5);
+  // this CTA's K range: chunks [chunk0, chunk0 + n_chunks) of the row (chunk0 is a multiple of 8, so raw stages
+  // and the 16-byte groups of scales stay aligned); the row's last chunk may be half (K is a multiple of 32)
+  const int chunk0 = (int)blockIdx.y * p.chunks_per_split;
+  const int total_chunks = (int)((K + TC_KC - 1) / TC_KC);
+  const int n_chunks = (total_chunks - chunk0 < p.chunks_per_split) ? (total_chunks - chunk0) : p.chunks_per_split;
+  const int n_blocks = (int)(K >> 5) - 2 * chunk0;        // blocks from chunk0 to the end of the row
   const int n_stages = (n_chunks + SUB - 1) / SUB;
+  const int64_t kbyte0 = (int64_t)chunk0 * (TYPE == CAI_TYPE_Q8_0 ? TC_KC : TC_KC / 2);   // first code byte of the range within a row
 
   if (warp == W / 32 + D) {
     // =====================================================================================
@@ -377,7 +386,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
       const uint32_t bar_f = tc_smem_u32(&b_full[0]), bar_e = tc_smem_u32(&b_empty[0]);
       int slot = 0;
       uint32_t eparity = 1;                                 // parity of the "emptied" phase awaited: none on the first lap
-      const unsigned char* src = p.xp;
+      const unsigned char* src = p.xp + (size_t)chunk0 * B_BYTES;
       for (int j = 0; j < n_chunks; ++j) {
         if (j >= SB && !tc_mbar_wait(bar_e + 8u * slot, eparity)) { *p.err_flag = 1; break; }
         const uint32_t bar = bar_f + 8u * (uint32_t)slot;
@@ -433,7 +442,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     int64_t my_row = row0 + lane_q * 32 + lane;
     const bool row_ok = my_row < p.n;
     if (!row_ok) my_row = p.n - 1;
-    const uint4* srow = (const uint4*)(p.scales + my_row * p.sstride);     // 8 scales (4 chunks) per 16 bytes
+    const uint4* srow = (const uint4*)(p.scales + my_row * p.sstride) + (chunk0 >> 2);     // 8 scales (4 chunks) per 16 bytes
     uint4 sc_cur = make_uint4(0, 0, 0, 0), sc_next = srow[0];
     float acc[NCOL];
 #pragma unroll
@@ -451,12 +460,12 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     static_assert(RSTEP % 8 == 0, "row step must keep the swizzle fixed");
     const int pr_pc = tid & (PPR - 1), pr_r0 = tid / PPR;
     const uint32_t pr_dst0 = (uint32_t)(pr_r0 * SPAN + ((pr_pc ^ (pr_r0 & 7)) << 4));
-    const unsigned char* pr_src0 = p.codes + row0 * row_bytes + pr_pc * 16;
+    const unsigned char* pr_src0 = p.codes + row0 * row_bytes + kbyte0 + pr_pc * 16;
     auto issue_raw = [&](int j) {
       if (j < n_stages) {
         const uint32_t dst = raw_st + (uint32_t)((j & (TC_RAW_STAGES - 1)) * RAW_BYTES) + pr_dst0;
         const int64_t byte0 = (int64_t)j * SPAN;                          // first code byte of the stage within a row
-        const bool valid = byte0 + pr_pc * 16 < row_bytes;                // K tail: zero-fill instead of reading
+        const bool valid = kbyte0 + byte0 + pr_pc * 16 < row_bytes;       // K tail: zero-fill instead of reading
         const unsigned char* src = pr_src0 + (valid ? byte0 : 0);
 #pragma unroll
         for (int t = 0; t < TC_M / RSTEP; ++t) {
@@ -582,7 +591,14 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     tc_cp_async_wait(0);
 
     // ---- epilogue: thread = weight row, acc[j] = batch column cg * NCOL + j ----
-    if (row_ok) {
+    if (row_ok && p.ksplit > 1) {
+      float* part = p.part + (size_t)blockIdx.y * (size_t)p.batch * (size_t)p.n + my_row;
+#pragma unroll
+      for (int j = 0; j < NCOL; ++j) {
+        const int b = cg * NCOL + j;
+        if (b < p.batch) part[(size_t)b * (size_t)p.n] = acc[j] * p.row_unscale[b];
+      }
+    } else if (row_ok) {
       const float bias = p.bias ? p.bias[my_row] : 0.f;
 #pragma unroll
       for (int j = 0; j < NCOL; ++j) {
@@ -604,8 +620,22 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
 template <int TYPE, int NB>
 cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid) {
   cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcPlan<NB>::SMEM);
-  if (e == cudaSuccess) gemm_tc_kernel<TYPE, NB><<<grid, TcPlan<NB>::THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
+  if (e == cudaSuccess) gemm_tc_kernel<TYPE, NB><<<dim3((unsigned)grid, (unsigned)p.ksplit), TcPlan<NB>::THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
   return e;
+}
+
+// y[b][row] = act(sum over splits of part[s][b][row] + bias) (+ residual), splits added in index order
+__global__ void tc_reduce_kernel(const float* __restrict__ part, int ksplit, int batch, int64_t n, const float* __restrict__ bias,
+                                 const float* __restrict__ resid, float* __restrict__ y, int64_t ldy, int act, int epi) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)batch * n) return;
+  const int64_t b = i / n, row = i - b * n;
+  float v = 0.f;
+  for (int s = 0; s < ksplit; ++s) v += part[((size_t)s * batch + b) * n + row];
+  if (bias) v += bias[row];
+  v = apply_act(v, act);
+  if (epi == EPI_RESID) v += resid[b * ldy + row];
+  y[b * ldy + row] = v;
 }
 
 }  // namespace
@@ -613,12 +643,19 @@ cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid) {
 // Grows the buffer that holds the split activations. Sessions size it when they are created, so a step
 // that is being captured into a graph never allocates. An outgrown buffer is kept until the context is
 // destroyed, because a graph captured earlier may still name it; sizes at least double, so few are kept.
+// Grows the buffer that holds the split activations. Sessions size it when they are created, so a step
+// that is being captured into a graph never allocates. An outgrown buffer is kept until the context is
+// destroyed, because a graph captured earlier may still name it; sizes at least double, so few are kept.
+constexpr size_t TC_PART_ROWS = 12800;   // K is split only for matrices of at most this many rows ...
+constexpr int TC_MAX_KSPLIT = 8;         // ... into at most this many ranges
+static size_t tc_xp_bytes_for(int64_t k, int nb) { return ((256 + (size_t)((k + TC_KC - 1) / TC_KC) * 2 * (size_t)nb * 128) + 255) & ~(size_t)255; }
+
 int gemm_tc_reserve(cai_ctx* ctx, int64_t k, int batch) {
   const int nb = batch <= 16 ? 16 : (batch <= 32 ? 32 : 64);
-  size_t need = 256 + (size_t)((k + TC_KC - 1) / TC_KC) * 2 * (size_t)nb * 128;      // 64 row factors, then two limbs per chunk
+  // 64 row factors and two limbs per chunk, then the partial sums of a K-split call
+  size_t need = tc_xp_bytes_for(k, nb) + (size_t)TC_MAX_KSPLIT * nb * TC_PART_ROWS * 4;
   if (need <= ctx->tc_xp_bytes) return CAI_OK;
   if (need < 2 * ctx->tc_xp_bytes) need = 2 * ctx->tc_xp_bytes;
-  if (need < ((size_t)4 << 20)) need = (size_t)4 << 20;
   if (ctx->tc_xp) {
     if (ctx->tc_xp_n_retired >= 32) return cai_fail(ctx, CAI_ERR_OOM, "tensor-core GEMM: activation buffer regrown too often");
     ctx->tc_xp_retired[ctx->tc_xp_n_retired++] = ctx->tc_xp;
@@ -656,6 +693,23 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
     CAI_LAUNCHED(ctx);
   }
   const int grid = (int)((g.n + TC_M - 1) / TC_M);
+  // Few row tiles and a long K (down / output projections): split K over blockIdx.y so that the launch fills the
+  // machine (two CTAs per SM), each range a multiple of 8 chunks and at least 16 chunks long.
+  p.ksplit = 1;
+  p.chunks_per_split = n_chunks;
+  if (grid * 2 <= ctx->sm_count && (size_t)g.n <= TC_PART_ROWS && n_chunks >= 32) {
+    int ks = (2 * ctx->sm_count) / grid;
+    if (ks > TC_MAX_KSPLIT) ks = TC_MAX_KSPLIT;
+    ks = env_int("CAI_TC_KSPLIT", ks);
+    if (ks < 1) ks = 1;
+    if (ks > TC_MAX_KSPLIT) ks = TC_MAX_KSPLIT;
+    int cps = (n_chunks + ks - 1) / ks;
+    if (cps < 16) cps = 16;
+    cps = (cps + 7) & ~7;
+    p.chunks_per_split = cps;
+    p.ksplit = (n_chunks + cps - 1) / cps;
+    p.part = (float*)((unsigned char*)ctx->tc_xp + tc_xp_bytes_for(g.k, nb));
+  }
   cudaError_t e;
   if (type == CAI_TYPE_Q8_0)
     e = nb == 16 ? tc_launch<CAI_TYPE_Q8_0, 16>(ctx, p, grid) : (nb == 32 ? tc_launch<CAI_TYPE_Q8_0, 32>(ctx, p, grid) : tc_launch<CAI_TYPE_Q8_0, 64>(ctx, p, grid));
@@ -663,5 +717,10 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
     e = nb == 16 ? tc_launch<CAI_TYPE_Q4_0, 16>(ctx, p, grid) : (nb == 32 ? tc_launch<CAI_TYPE_Q4_0, 32>(ctx, p, grid) : tc_launch<CAI_TYPE_Q4_0, 64>(ctx, p, grid));
   if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "gemm_tc smem attribute -> %s", cudaGetErrorString(e));
   CAI_LAUNCHED(ctx);
+  if (p.ksplit > 1) {
+    const int64_t total = (int64_t)g.batch * g.n;
+    tc_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p.part, p.ksplit, g.batch, g.n, g.bias, g.resid, g.y, g.ldy, g.act, g.epi);
+    CAI_LAUNCHED(ctx);
+  }
   return CAI_OK;
 }
