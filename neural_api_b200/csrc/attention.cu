@@ -25,7 +25,16 @@ struct AttnParams {
   float* out; int64_t ldo;
   float* partial; int nsplit;
   float inv_sqrt_d;
+  int min_chunk;          // fewest cached rows a context split covers (set by the launcher for the kernel it picked)
 };
+
+// Rows per context split: the context spread over nsplit splits, at least min_chunk rows, a multiple of 32.
+// Short contexts use few splits; the other CTAs leave at once. Decode and combine kernels both use this.
+__device__ __forceinline__ int attn_chunk(int n, int nsplit, int min_chunk) {
+  int chunk = (n + nsplit - 1) / nsplit;
+  if (chunk < min_chunk) chunk = min_chunk;
+  return (chunk + 31) & ~31;
+}
 
 __global__ void rope_append_kernel(const AttnParams p) {
   __shared__ float red[32];
@@ -112,9 +121,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
   const bool vec = (nd == 8) && ((hd & 3) == 0);
 
   const int n = p.cache_len[b] + 1;                  // keys after the append
-  // a split covers at least ATTN_MIN_CHUNK rows: short contexts use few splits, the other CTAs leave at once
-  int chunk = (n + p.nsplit - 1) / p.nsplit;
-  if (chunk < ATTN_MIN_CHUNK) chunk = ATTN_MIN_CHUNK;
+  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
   const int used = (n + chunk - 1) / chunk;
   if (split >= used) return;
   const int j_begin = split * chunk;
@@ -261,6 +268,186 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Decode attention for head_dim 64 / 128 and groups of up to 8 query heads: the kernel the long contexts run on.
+// The kernel above spends ~90 warp instructions per cached row (every lane of a 16-lane key group repeats the
+// softmax arithmetic, and the dot products cost 4 shuffle stages per key and head); at 1 KB per row that is several
+// times what HBM could deliver (measured 1.0 TB/s at context 8192). Here a warp works on tiles of 32 rows and
+// changes the meaning of a lane between the two products:
+//   Q.K   lane = row: the lane walks its K row with 16-byte loads (eight in flight), q comes from shared memory
+//         as a broadcast; no cross-lane reduction, the softmax terms are computed once per row;
+//   P.V   lane = 2 or 4 channels: V rows are read coalesced, the probabilities come back from shared memory four rows
+//         at a time as broadcasts; the lane keeps acc[head][its channels].
+// ~50 instructions per row for 5 heads x 128 channels. Online softmax state (m, l, acc) per warp, merged warps ->
+// splits in fixed order exactly like the general kernel (same partial format, same combine kernel).
+// ---------------------------------------------------------------------------
+constexpr int ATTN_TILE_MIN_CHUNK = 128;   // 4 warps x one tile of 32 rows
+
+// (Four CTAs per SM, i.e. at most 128 registers: a context of 8192 rows makes 520 CTAs for 8 KV heads, which then
+// run as one wave of 592 slots; with two or three resident CTAs the tail wave doubled the kernel's time.)
+template <int G, int HD>
+__global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(const AttnParams p) {
+  constexpr int DPL = HD / 32;                         // channels per lane in the P.V phase
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = p.cache_len[b] + 1;                    // rows after the append
+  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
+  const int used = (n + chunk - 1) / chunk;
+  if (split >= used) return;
+  const int j_begin = split * chunk;
+  int j_end = j_begin + chunk; if (j_end > n) j_end = n;
+
+  float* q_s = smem;                                   // [G][HD]
+  float* p_s = q_s + G * HD + (size_t)warp * G * 32;   // this warp's [G][32] probabilities
+  float* merge_s = smem + G * HD + ATTN_WARPS * G * 32;   // [ATTN_WARPS][G][HD + 2]
+  const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * HD;
+  for (int i = threadIdx.x; i < G * HD; i += blockDim.x) q_s[i] = qrow[i];
+  __syncthreads();
+
+  const float* kbase = p.k_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+  const float* vbase = p.v_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+
+  float m[G], l[G], acc[G][DPL];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
+  }
+
+  for (int tile = j_begin + warp * 32; tile < j_end; tile += ATTN_WARPS * 32) {
+    // ---- Q.K, lane = row (rows past the end re-read the last row and are masked below)
+    const int j = tile + lane;
+    const bool valid = j < j_end;
+    const float4* krow = (const float4*)(kbase + (int64_t)(valid ? j : j_end - 1) * HD);
+    float s[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) s[h] = 0.f;
+    // 64 channels (two 128-byte lines of the row, 16 loads in flight) at a time: few dependent round trips to HBM
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c) {
+      float4 k[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) k[i] = krow[c * 16 + i];
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        const float4* q4 = (const float4*)(q_s + h * HD + c * 64);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float4 q = q4[i];
+          s[h] = fmaf(q.x, k[i].x, s[h]); s[h] = fmaf(q.y, k[i].y, s[h]);
+          s[h] = fmaf(q.z, k[i].z, s[h]); s[h] = fmaf(q.w, k[i].w, s[h]);
+        }
+      }
+    }
+    // ---- P.V, lane = DPL channels. The V rows do not depend on the softmax, so the first half of the tile's rows
+    //      is requested before it (masked rows re-read the last row and carry probability 0)
+    const int last = j_end - 1 - tile;                 // index of the tile's last valid row, >= 0
+    float v[16][DPL];
+    auto load_v = [&](int base) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const int r = (base + t <= last) ? (base + t) : last;
+        const float* vrow = vbase + (int64_t)(tile + r) * HD + lane * DPL;
+        if (DPL == 4) {
+          const float4 x = *(const float4*)vrow;
+          v[t][0] = x.x; v[t][1] = x.y; v[t][2 % DPL] = x.z; v[t][3 % DPL] = x.w;
+        } else {
+          const float2 x = *(const float2*)vrow;
+          v[t][0] = x.x; v[t][1] = x.y;
+        }
+      }
+    };
+    auto use_v = [&](int base) {
+#pragma unroll
+      for (int t4 = 0; t4 < 16; t4 += 4) {
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const float4 pr = *(const float4*)(p_s + h * 32 + base + t4);
+#pragma unroll
+          for (int d = 0; d < DPL; ++d) {
+            float a = acc[h][d];
+            a = fmaf(pr.x, v[t4 + 0][d], a); a = fmaf(pr.y, v[t4 + 1][d], a);
+            a = fmaf(pr.z, v[t4 + 2][d], a); a = fmaf(pr.w, v[t4 + 3][d], a);
+            acc[h][d] = a;
+          }
+        }
+      }
+    };
+    load_v(0);
+    // ---- softmax terms of the tile, once per row
+    __syncwarp();                                      // the previous tile's probabilities have been consumed
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float sc = valid ? s[h] * p.inv_sqrt_d : -INFINITY;
+      const float mnew = fmaxf(m[h], warp_max(sc));    // finite: the tile holds at least one row
+      const float pj = valid ? expf(sc - mnew) : 0.f;
+      const float psum = warp_sum(pj);
+      const float corr = expf(m[h] - mnew);            // 0 on the first tile (m = -inf)
+      l[h] = l[h] * corr + psum;
+      m[h] = mnew;
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
+      p_s[h * 32 + lane] = pj;
+    }
+    __syncwarp();
+    use_v(0);
+    if (last >= 16) {
+      load_v(16);
+      use_v(16);
+    }
+  }
+  // ---- warps -> shared memory -> one state per head (a warp that had no tile contributes m = -inf, l = 0)
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
+    if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) dst[2 + lane * DPL + d] = acc[h][d];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int hh = idx / HD, d = idx % HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
+    float lt = 0.f, at = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) {
+      const float* src = merge_s + ((size_t)w * G + hh) * (HD + 2);
+      const float sc = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mx);
+      lt += src[1] * sc;
+      at += src[2 + d] * sc;
+    }
+    const int h = g * G + hh;
+    if (used == 1) {
+      p.out[(int64_t)b * p.ldo + (int64_t)h * HD + d] = (lt > 0.f) ? at / lt : 0.f;
+    } else {
+      float* dst = p.partial + (((int64_t)b * p.q_heads + h) * p.nsplit + split) * (HD + 2);
+      if (d == 0) { dst[0] = mx; dst[1] = lt; }
+      dst[2 + d] = at;
+    }
+  }
+}
+
+template <int HD>
+static void launch_tile(cai_ctx* ctx, int G, dim3 grid, size_t smem, const AttnParams& p) {
+  switch (G) {
+    case 1: pdl_launch(ctx, attn_decode_tile_kernel<1, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 2: pdl_launch(ctx, attn_decode_tile_kernel<2, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 3: pdl_launch(ctx, attn_decode_tile_kernel<3, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 4: pdl_launch(ctx, attn_decode_tile_kernel<4, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 5: pdl_launch(ctx, attn_decode_tile_kernel<5, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 6: pdl_launch(ctx, attn_decode_tile_kernel<6, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 7: pdl_launch(ctx, attn_decode_tile_kernel<7, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    default: pdl_launch(ctx, attn_decode_tile_kernel<8, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+  }
+}
+
 __global__ void attn_combine_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
@@ -268,8 +455,7 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   const int hd = p.head_dim;
   const float* src = p.partial + ((int64_t)b * p.q_heads + h) * (int64_t)p.nsplit * (hd + 2);
   const int n = p.cache_len[b] + 1;
-  int chunk = (n + p.nsplit - 1) / p.nsplit;
-  if (chunk < ATTN_MIN_CHUNK) chunk = ATTN_MIN_CHUNK;
+  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
   const int used = (n + chunk - 1) / chunk;
   if (used == 1) return;                              // the single split wrote the output itself
   float mx = -INFINITY;
@@ -309,6 +495,7 @@ static AttnParams to_params(const AttnArgs& a) {
   p.theta = a.theta; p.pos = a.pos_dev; p.q_norm = a.q_norm; p.k_norm = a.k_norm; p.eps = a.eps;
   p.out = a.out; p.ldo = a.ldo; p.partial = a.partial; p.nsplit = a.nsplit;
   p.inv_sqrt_d = (float)(1.0 / sqrt((double)a.head_dim));
+  p.min_chunk = ATTN_MIN_CHUNK;
   return p;
 }
 
@@ -328,8 +515,23 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
   const int G = a.q_heads / a.kv_heads;
   int lpk = 1;
   while (lpk * 8 < a.head_dim) lpk <<= 1;
-  const AttnParams p = to_params(a);
+  AttnParams p = to_params(a);
   dim3 grid(a.kv_heads, a.nsplit, a.batch);
+  static const int use_tile = [] { const char* e = getenv("CAI_ATTN_TILE"); return (e && *e) ? atoi(e) : 1; }();
+  if (use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8) {
+    p.min_chunk = ATTN_TILE_MIN_CHUNK;
+    const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 32 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
+    if (a.head_dim == 128) launch_tile<128>(ctx, G, grid, tsmem, p);
+    else launch_tile<64>(ctx, G, grid, tsmem, p);
+    CAI_LAUNCHED(ctx);
+    if (a.nsplit > 1) {
+      dim3 cgrid(a.q_heads, a.batch);
+      pdl_launch(ctx, attn_combine_kernel, cgrid, dim3(128), 0, p);
+      CAI_LAUNCHED(ctx);
+    }
+    return CAI_OK;
+  }
+  p.min_chunk = ATTN_MIN_CHUNK;
   const int gt = G >= 8 ? 8 : G;
   const size_t smem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * gt * (a.head_dim + 2)) * sizeof(float);
   if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "attention group of %d heads x %d dims exceeds shared memory", G, a.head_dim);
