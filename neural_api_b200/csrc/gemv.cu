@@ -18,6 +18,15 @@
 #include "gemv_common.cuh"
 #include <stdlib.h>
 
+// Position of activation k (a multiple of 4) in the staged, swizzled row: within each lane segment (16 floats for
+// Q8_0, 32 for Q4_0) the 16-byte pieces are XOR-ed with the segment index, so a quarter-warp's reads of piece i
+// fall on 8 different bank groups.
+template <int TYPE>
+__device__ __forceinline__ int64_t x_phys(int64_t k) {
+  if (TYPE == CAI_TYPE_Q8_0) return (k & ~(int64_t)12) | ((((k >> 2) & 3) ^ ((k >> 5) & 3)) << 2) | (k & 3);
+  return (k & ~(int64_t)28) | ((((k >> 2) & 7) ^ ((k >> 5) & 7)) << 2) | (k & 3);
+}
+
 template <int TYPE, int NB, int RPW, int MINB>
 __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams p) {
   extern __shared__ __align__(16) float smem_f[];
@@ -59,11 +68,15 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
   for (int b = 0; b < NB; ++b) xbase[b] = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
   float* red = smem_f;
   if (p.x_in_smem) {
+    // A lane reads the 16 (Q8_0) or 32 (Q4_0) activations of its codes as 16-byte pieces; with the natural layout
+    // the lanes of a quarter-warp are 64 or 128 bytes apart and collide on 2 or 1 of the 8 bank groups (measured:
+    // 70 % of the shared-memory wavefronts of this kernel were conflict replays). So the pieces of a lane's
+    // segment are stored XOR-ed with the segment index: x_phys() below, undone in the reads by `xsw`.
     for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
       const int b = (int)(i / K);
       const int64_t c = i - (int64_t)b * K;
       const int bb = (b0 + b < p.batch) ? b : 0;
-      *(float4*)(smem_f + i) = *(const float4*)(x + (int64_t)bb * p.ldx + c);
+      *(float4*)(smem_f + (int64_t)b * K + x_phys<TYPE>(c)) = *(const float4*)(x + (int64_t)bb * p.ldx + c);
     }
     red = smem_f + (int64_t)NB * K;
     float* nred = red + (size_t)warps_per_cta * (RPW * NB);
@@ -73,10 +86,10 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
       for (int b = 0; b < NB; ++b) {
         float* xb = smem_f + (int64_t)b * K;
         float ss = 0.f;
-        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) ss = fmaf(xb[c], xb[c], ss);
+        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) { const float v = xb[x_phys<TYPE>(c)]; ss = fmaf(v, v, ss); }
         ss = block_sum(ss, nred);
         const float inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
-        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) xb[c] = p.norm_gain[c] * (xb[c] * inv);
+        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) { float* e = xb + x_phys<TYPE>(c); *e = p.norm_gain[c] * (*e * inv); }
       }
       __syncthreads();
     }
@@ -145,6 +158,9 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     const float* xr[NB];
 #pragma unroll
     for (int b = 0; b < NB; ++b) xr[b] = xbase[b] + k_first;
+    // the XOR the staging applied to this lane's 16-byte pieces (0 when the activations are read from global memory);
+    // k_first and the stride are whole multiples of 32 segments, so it is the same for every stride
+    const int xsw = p.x_in_smem ? ((TYPE == CAI_TYPE_Q8_0) ? ((lane >> 1) & 3) : (lane & 7)) : 0;
 
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
@@ -168,7 +184,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
         if (TYPE == CAI_TYPE_Q8_0) {
           float4 xv[NB];
 #pragma unroll
-          for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + 4 * i);
+          for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + 4 * (i ^ xsw));
 #pragma unroll
           for (int r = 0; r < RPW; ++r) {
             const uint32_t w = ((const uint32_t*)&wv[r])[i];
@@ -179,8 +195,8 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
           float4 xlo[NB], xhi[NB];
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
-            xlo[b] = *(const float4*)(xr[b] + 4 * i);
-            xhi[b] = *(const float4*)(xr[b] + 16 + 4 * i);
+            xlo[b] = *(const float4*)(xr[b] + 4 * (i ^ xsw));
+            xhi[b] = *(const float4*)(xr[b] + 4 * ((4 + i) ^ xsw));
           }
 #pragma unroll
           for (int r = 0; r < RPW; ++r) {
