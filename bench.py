@@ -27,6 +27,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 TYPE_BPW = {8: 34.0 / 32.0, 2: 18.0 / 32.0}          # Q8_0, Q4_0 bytes per weight
+# gemv_quant_kernel on 5120 x 27648 Q8_0 under ncu: dram__bytes_read.sum 150.476 MB + dram__bytes_write.sum 5.032 MB
+# per launch against 150.502 MB of codes and scales (profiles/gemv_quant_q8_0_5120x27648_b1.md)
+GEMV_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0332
 WORKLOAD_DEFAULTS = {
     # arch: (ggml type, seed, batch, context)
     "qwen2.5-32b": (8, 3, 1, 8192),
@@ -363,13 +366,12 @@ def main():
     lin_ms, lin_n = prof["linear"]
     lin_ms_step = lin_ms / res["profile_steps"]
     achieved = res["weight_bytes_rank"] / (lin_ms_step * 1e-3) / 1e9 if lin_ms_step > 0 else 0.0
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(tpath):
-        try:
-            traffic = json.load(open(tpath)).get(args.workload)
-        except Exception:
-            traffic = None
+    # DRAM traffic per launch of the dominant kernel: algorithmic bytes per launch x the ratio of
+    # (dram__bytes_read.sum + dram__bytes_write.sum) to algorithmic bytes that one ncu capture of the kernel measured
+    # on a smaller case (the traffic grows in proportion to the matrix).
+    launches_per_step = lin_n / res["profile_steps"] if res["profile_steps"] else 0
+    bytes_per_launch = res["weight_bytes_rank"] / launches_per_step if launches_per_step else None
+    traffic = GEMV_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_launch if bytes_per_launch else None
     step_bytes = res["weight_bytes_rank"] + res["kv_bytes_step"]
     line = {
         "metric": "decode_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
@@ -381,7 +383,7 @@ def main():
         "gpu_launches": res["launches"],
         "roofline": {"bound": "hbm", "kernel": "gemv_quant_kernel (Q8_0 dequant-fused GEMV)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
-                     "bytes_per_step": res["weight_bytes_rank"], "launches_per_step": lin_n / res["profile_steps"],
+                     "bytes_per_launch": bytes_per_launch, "bytes_per_step": res["weight_bytes_rank"], "launches_per_step": launches_per_step,
                      "ms_per_step_in_kernel": lin_ms_step},
         "step_roofline": {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (res["ms_per_step"] * 1e-3) / 1e9,
                           "frac": step_bytes / (res["ms_per_step"] * 1e-3) / 1e9 / peak, "frac_of_8tbs": step_bytes / (res["ms_per_step"] * 1e-3) / 8e12},
