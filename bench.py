@@ -124,6 +124,12 @@ class CpuSample:
     def __init__(self, arch_kw, ggml_type, ctx):
         from oracle import c_oracle
         self.c = c_oracle
+        # all the host threads this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+        try:
+            usable = len(os.sched_getaffinity(0))
+        except AttributeError:
+            usable = os.cpu_count() or 1
+        c_oracle.set_num_threads(usable)
         kw = arch_kw
         if kw.get("n_experts", 0):
             raise RuntimeError("the C restatement covers dense models")
@@ -190,7 +196,8 @@ def run_reference(args, arch_kw, ggml_type, batch, ctx):
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak" if (args.gpus > 1 and parallel_mode(args) == "dp") else "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, arch_kw, ggml_type, batch, ctx, 1),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": sample.cores, "kind": "port", "sample": sample.desc},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -199,27 +206,39 @@ def run_reference(args, arch_kw, ggml_type, batch, ctx):
     print(json.dumps(line))
 
 
+def parallel_mode(args):
+    if args.parallel != "auto":
+        return args.parallel
+    return "tp" if args.workload == "qwen2.5-32b" else "dp"
+
+
 def workload_config(args, arch_kw, ggml_type, batch, ctx, world):
-    return {"workload": "%s-architecture %s decode, batch %d, context %d, fp32 KV, fp32 activations"
-                        % (args.workload, {8: "Q8_0", 2: "Q4_0"}[ggml_type], batch, ctx),
+    return {"workload": "%s-architecture %s decode, batch %d%s, context %d, fp32 KV, fp32 activations"
+                        % (args.workload, {8: "Q8_0", 2: "Q4_0"}[ggml_type], batch,
+                           " per GPU" if (world > 1 and parallel_mode(args) == "dp") else "", ctx),
             "batch": batch, "context": ctx, "weights": {8: "Q8_0", 2: "Q4_0"}[ggml_type],
-            "parallelism": "tp%d" % world if world > 1 else "single",
+            "parallelism": ("%s%d" % (parallel_mode(args), world)) if world > 1 else "single",
             "l2": "inputs larger than L2 (weights streamed once per step)"}
 
 
-def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, steps, warmup, do_e2e=True, do_profile=True):
-    """Builds the synthetic model, fills the context, and measures. Returns a dict of raw numbers."""
+def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, steps, warmup, do_e2e=True, do_profile=True,
+                 mode="tp"):
+    """Builds the synthetic model, fills the context, and measures. Returns a dict of raw numbers.
+    mode "tp": one job, weights sharded over the ranks; "dp": every rank holds the whole model and decodes its own
+    batch (different prompts), nothing crosses NVLink; the job's tokens/s is the sum."""
     from neural_api_b200.backend import LlamaModel, StreamingDecoder
     from neural_api_b200.configs import ARCHS, arch_config, step_weight_bytes
     from neural_api_b200 import parallel
     kw = ARCHS[arch]
-    model = LlamaModel(backend, arch_config(arch), tp_rank=rank if world > 1 else 0, tp_size=world)
+    tp = world if (world > 1 and mode == "tp") else 1
+    replicas = world if (world > 1 and mode == "dp") else 1
+    model = LlamaModel(backend, arch_config(arch), tp_rank=rank if tp > 1 else 0, tp_size=tp)
     model.init_synthetic(ggml_type, seed=seed, std=0.02)
     model.finalize()
     prof_steps = 2 if do_profile else 0
     max_ctx = ctx + warmup + steps * (2 if do_e2e else 1) + prof_steps + 8
     sess = StreamingDecoder(model, max_ctx, batch=batch)
-    rng = np.random.default_rng(seed)
+    rng = np.random.default_rng(seed + (rank if replicas > 1 else 0))
     prompt = rng.integers(0, kw["vocab"], (batch, ctx)).astype(np.int32)
     t0 = time.perf_counter()
     if ctx > 1:
@@ -246,7 +265,7 @@ def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, 
     launches = backend.launch_count() - launches0
     ms = parallel.max_over_ranks(dist, ms)
     tok = out[-1].copy()
-    res = {"ms_total": ms, "ms_per_step": ms / steps, "tokens_per_s": steps * batch / (ms * 1e-3), "launches": launches,
+    res = {"ms_total": ms, "ms_per_step": ms / steps, "tokens_per_s": steps * batch * replicas / (ms * 1e-3), "launches": launches,
            "clocks": clocks, "prefill_s": prefill_s, "kv_bytes_step": sess.last_kv_bytes(),
            "weight_bytes_rank": model.step_weight_bytes(),
            "weight_bytes_job": step_weight_bytes(kw, TYPE_BPW[ggml_type], tokens_per_step=batch)}
@@ -259,7 +278,7 @@ def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, 
             tok = amax.copy()
         backend.sync()
         e2e_s = parallel.max_over_ranks(dist, time.perf_counter() - t0)
-        res["e2e_tokens_per_s"] = steps * batch / e2e_s
+        res["e2e_tokens_per_s"] = steps * batch * replicas / e2e_s
         res["h2d"] = 8 * batch
         res["d2h"] = batch * kw["vocab"] * 4 + 4 * batch
     if do_profile:
@@ -330,6 +349,9 @@ def main():
     ap.add_argument("--workload", default="qwen2.5-32b", choices=sorted(WORKLOAD_DEFAULTS) + ["linear"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
+    ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "dp"],
+                    help="N > 1: tp = one job sharded tensor-parallel (strong scaling), dp = one replica with its own batch per GPU "
+                         "(weak scaling, no collective on the data path); auto = tp for qwen2.5-32b, dp for the others")
     ap.add_argument("--no-extra", action="store_true", help="skip the Qwen2.5-0.5B side measurement and the CPU baseline")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -355,12 +377,13 @@ def main():
         rank, world, local_rank, dist = parallel.init_process_group("cpu:gloo,cuda:nccl")
     from neural_api_b200.backend import CudaBackend
     backend = CudaBackend(local_rank)
-    if world > 1:
+    mode = parallel_mode(args)
+    if world > 1 and mode == "tp":
         uid = backend.comm_unique_id() if rank == 0 else bytes(128)
         uid = parallel.broadcast_bytes(dist, uid, src=0, length=128)
         backend.comm_init(rank, world, uid)
 
-    res = run_workload(backend, dist, rank, world, args.workload, ggml_type, seed, batch, ctx, args.steps, args.warmup)
+    res = run_workload(backend, dist, rank, world, args.workload, ggml_type, seed, batch, ctx, args.steps, args.warmup, mode=mode)
     peak, peak_kind = measured_peak_gbs()
     prof = res["profile"]
     lin_ms, lin_n = prof["linear"]
@@ -376,7 +399,7 @@ def main():
     line = {
         "metric": "decode_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "weak" if (world > 1 and mode == "dp") else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, arch_kw, ggml_type, batch, ctx, world),
         "clocks": {"sm_mhz": res["clocks"]["sm_mhz"], "sm_max_mhz": res["clocks"]["sm_max_mhz"], "reasons": res["clocks"]["reasons"]},
         "e2e": {"value": res["e2e_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},

@@ -186,6 +186,13 @@ int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, i
 int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val,
               float* part_val, int* part_idx, int* tickets);   // scratch: [batch][CAI_ARGMAX_CHUNKS] x2, tickets [batch] zeroed once
 int op_rope_table(cai_ctx* ctx, const float* theta_dev, const int32_t* pos_dev, int batch, int half, float* cs_dev);
+int op_moe_group(cai_ctx* ctx, const int32_t* expert_ids, int pairs, int n_experts, int tile_rows, int max_tiles,
+                 int32_t* tile_expert, int32_t* tile_pairs);
+// gemm_tc.cu: grouped tensor-core GEMM over the tiles op_moe_group made (16 pairs per tile)
+size_t gemm_tc_group_tile_bytes(int64_t k);
+int gemm_tc_launch_grouped(cai_ctx* ctx, int type, const void* const* bank_codes, const __half* const* bank_scales, int64_t n, int64_t k,
+                           int64_t sstride, const float* x, int64_t ldx, int x_row_div, float* y, int64_t ldy,
+                           const int32_t* tile_expert, const int32_t* tile_pairs, int n_tiles, void* xp_tiles, float* unscale_tiles);
 int op_moe_combine(cai_ctx* ctx, float* x, int64_t ldx, const float* pair_out, int64_t ldp, const float* gates,
                    int tokens, int top_k, int depth);
 int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n);

@@ -193,6 +193,15 @@ struct TcParams {
   // and, when ksplit > 1, stores its unscaled-by-nothing partial sums to part[y][b][row] for the reduce kernel.
   int ksplit, chunks_per_split;
   float* part;
+  // Grouped (mixture-of-experts) mode, 16-row tiles: blockIdx.z = tile t. The tile's weights are bank[tile_expert[t]]
+  // (t is skipped when that is negative), column b of the tile is pair tile_pairs[16 t + b] (negative = unused), whose
+  // result goes to output row `pair`; the tile's split activations start at xp + t * xp_tile_bytes and its row
+  // factors at row_unscale + 16 t.
+  const int32_t* tile_expert;
+  const int32_t* tile_pairs;
+  const void* const* bank_codes;
+  const __half* const* bank_scales;
+  size_t xp_tile_bytes;
 };
 
 // ---------------------------------------------------------------------------
@@ -207,12 +216,25 @@ struct TcParams {
 // ---------------------------------------------------------------------------
 __global__ void tc_split_x_kernel(const float* __restrict__ x, int64_t ldx, int batch, int nb, int64_t k, int n_chunks, int limbs,
                                   const float* __restrict__ norm_gain, float norm_eps, unsigned char* __restrict__ xp,
-                                  float* __restrict__ row_unscale) {
+                                  float* __restrict__ row_unscale, const int32_t* __restrict__ tile_pairs, int x_row_div,
+                                  size_t xp_tile_bytes) {
   __shared__ float red[32];
   const int b = blockIdx.x;
-  const float* xr = x + (int64_t)b * ldx;
+  // grouped mode: tile blockIdx.y gathers its rows through tile_pairs (row of pair p = p / x_row_div)
+  int src_row = b;
+  bool have = b < batch;
+  if (tile_pairs) {
+    const int t = blockIdx.y;
+    if (tile_pairs[(size_t)t * nb] < 0) return;           // pairs fill a tile from slot 0: an empty first slot = an unused tile
+    const int pr = tile_pairs[(size_t)t * nb + b];
+    have = pr >= 0;
+    src_row = have ? pr / x_row_div : 0;
+    xp += (size_t)t * xp_tile_bytes;
+    row_unscale += (size_t)t * nb;
+  }
+  const float* xr = x + (int64_t)src_row * ldx;
   float inv = 1.f, scale = 1.f;
-  if (b < batch) {
+  if (have) {
     if (norm_gain) {
       float ss = 0.f;
       for (int64_t c = threadIdx.x; c < k; c += blockDim.x) { const float v = xr[c]; ss = fmaf(v, v, ss); }
@@ -239,7 +261,7 @@ __global__ void tc_split_x_kernel(const float* __restrict__ x, int64_t ldx, int 
     const int c = g >> 3, k8 = g & 7;
     const int64_t kk = (int64_t)c * TC_KC + k8 * 8;
     float v[8];
-    if (b < batch && kk < k) {                            // K is a multiple of 32: a group of 8 is whole or absent
+    if (have && kk < k) {                                 // K is a multiple of 32: a group of 8 is whole or absent
       const float4 a0 = *(const float4*)(xr + kk), a1 = *(const float4*)(xr + kk + 4);
       v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w; v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
       if (norm_gain) {
@@ -337,6 +359,22 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // operands: the call's matrix, or in grouped mode the expert matrix and activation tile of tile blockIdx.z
+  const unsigned char* w_codes = p.codes;
+  const __half* w_scales = p.scales;
+  const unsigned char* x_tiles = p.xp;
+  const float* unscale = p.row_unscale;
+  const int32_t* out_rows = nullptr;                       // grouped: output row of each tile column
+  if (p.tile_expert) {
+    const int t = blockIdx.z;
+    const int e = p.tile_expert[t];
+    if (e < 0) return;                                     // unused tile: the whole CTA leaves before touching anything
+    w_codes = (const unsigned char*)p.bank_codes[e];
+    w_scales = p.bank_scales[e];
+    x_tiles += (size_t)t * p.xp_tile_bytes;
+    unscale += (size_t)t * NB;
+    out_rows = p.tile_pairs + (size_t)t * NB;
+  }
   // operand tiles start on 1024-byte boundaries (the swizzle works on absolute shared-memory address bits)
   const uint32_t smem0 = (tc_smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_st = smem0;                                               // D tiles of 16 KB
@@ -386,7 +424,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
       const uint32_t bar_f = tc_smem_u32(&b_full[0]), bar_e = tc_smem_u32(&b_empty[0]);
       int slot = 0;
       uint32_t eparity = 1;                                 // parity of the "emptied" phase awaited: none on the first lap
-      const unsigned char* src = p.xp + (size_t)chunk0 * B_BYTES;
+      const unsigned char* src = x_tiles + (size_t)chunk0 * B_BYTES;
       for (int j = 0; j < n_chunks; ++j) {
         if (j >= SB && !tc_mbar_wait(bar_e + 8u * slot, eparity)) { *p.err_flag = 1; break; }
         const uint32_t bar = bar_f + 8u * (uint32_t)slot;
@@ -442,7 +480,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     int64_t my_row = row0 + lane_q * 32 + lane;
     const bool row_ok = my_row < p.n;
     if (!row_ok) my_row = p.n - 1;
-    const uint4* srow = (const uint4*)(p.scales + my_row * p.sstride) + (chunk0 >> 2);     // 8 scales (4 chunks) per 16 bytes
+    const uint4* srow = (const uint4*)(w_scales + my_row * p.sstride) + (chunk0 >> 2);     // 8 scales (4 chunks) per 16 bytes
     uint4 sc_cur = make_uint4(0, 0, 0, 0), sc_next = srow[0];
     float acc[NCOL];
 #pragma unroll
@@ -460,7 +498,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     static_assert(RSTEP % 8 == 0, "row step must keep the swizzle fixed");
     const int pr_pc = tid & (PPR - 1), pr_r0 = tid / PPR;
     const uint32_t pr_dst0 = (uint32_t)(pr_r0 * SPAN + ((pr_pc ^ (pr_r0 & 7)) << 4));
-    const unsigned char* pr_src0 = p.codes + row0 * row_bytes + kbyte0 + pr_pc * 16;
+    const unsigned char* pr_src0 = w_codes + row0 * row_bytes + kbyte0 + pr_pc * 16;
     auto issue_raw = [&](int j) {
       if (j < n_stages) {
         const uint32_t dst = raw_st + (uint32_t)((j & (TC_RAW_STAGES - 1)) * RAW_BYTES) + pr_dst0;
@@ -596,18 +634,19 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
 #pragma unroll
       for (int j = 0; j < NCOL; ++j) {
         const int b = cg * NCOL + j;
-        if (b < p.batch) part[(size_t)b * (size_t)p.n] = acc[j] * p.row_unscale[b];
+        if (b < p.batch) part[(size_t)b * (size_t)p.n] = acc[j] * unscale[b];
       }
     } else if (row_ok) {
       const float bias = p.bias ? p.bias[my_row] : 0.f;
 #pragma unroll
       for (int j = 0; j < NCOL; ++j) {
         const int b = cg * NCOL + j;
-        if (b < p.batch) {
-          float v = fmaf(acc[j], p.row_unscale[b], bias);
+        const int64_t orow = out_rows ? (int64_t)out_rows[b] : (int64_t)b;     // grouped: scatter to the pair's row
+        if (out_rows ? (orow >= 0) : (b < p.batch)) {
+          float v = fmaf(acc[j], unscale[b], bias);
           v = apply_act(v, p.act);
-          if (p.epi == EPI_RESID) v += p.resid[(int64_t)b * p.ldy + my_row];
-          p.y[(int64_t)b * p.ldy + my_row] = v;
+          if (p.epi == EPI_RESID) v += p.resid[orow * p.ldy + my_row];
+          p.y[orow * p.ldy + my_row] = v;
         }
       }
     }
@@ -618,9 +657,10 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
 }
 
 template <int TYPE, int NB>
-cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid) {
+cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid, int tiles = 1) {
   cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcPlan<NB>::SMEM);
-  if (e == cudaSuccess) gemm_tc_kernel<TYPE, NB><<<dim3((unsigned)grid, (unsigned)p.ksplit), TcPlan<NB>::THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
+  if (e == cudaSuccess)
+    gemm_tc_kernel<TYPE, NB><<<dim3((unsigned)grid, (unsigned)p.ksplit, (unsigned)tiles), TcPlan<NB>::THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
   return e;
 }
 
@@ -689,7 +729,7 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
   {
     const int threads = g.k >= 2048 ? 512 : 256;
     tc_split_x_kernel<<<nb, threads, 0, ctx->stream>>>(g.x, g.ldx, g.batch, nb, g.k, n_chunks, 2, g.norm_gain, g.norm_eps,
-                                                       (unsigned char*)ctx->tc_xp + 256, (float*)ctx->tc_xp);
+                                                       (unsigned char*)ctx->tc_xp + 256, (float*)ctx->tc_xp, nullptr, 1, 0);
     CAI_LAUNCHED(ctx);
   }
   const int grid = (int)((g.n + TC_M - 1) / TC_M);
@@ -722,5 +762,37 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
     tc_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p.part, p.ksplit, g.batch, g.n, g.bias, g.resid, g.y, g.ldy, g.act, g.epi);
     CAI_LAUNCHED(ctx);
   }
+  return CAI_OK;
+}
+
+// Bytes of split activations one 16-row tile of a grouped call needs for rows of k values.
+size_t gemm_tc_group_tile_bytes(int64_t k) { return (size_t)((k + TC_KC - 1) / TC_KC) * 2 * 16 * 128; }
+
+// Grouped tensor-core GEMM for a mixture-of-experts layer: n_tiles tiles of up to 16 (token, expert) pairs, all pairs
+// of a tile routed to the same expert (op_moe_group builds the lists). One launch of the activation split and one of
+// the GEMM cover every tile, so an expert's weights are streamed once per 16 pairs instead of once per pair.
+// y row of pair p = p; x row of pair p = p / x_row_div. Plain epilogue.
+int gemm_tc_launch_grouped(cai_ctx* ctx, int type, const void* const* bank_codes, const __half* const* bank_scales, int64_t n, int64_t k,
+                           int64_t sstride, const float* x, int64_t ldx, int x_row_div, float* y, int64_t ldy,
+                           const int32_t* tile_expert, const int32_t* tile_pairs, int n_tiles, void* xp_tiles, float* unscale_tiles) {
+  if (!ctx->err_flag) return cai_fail(ctx, CAI_ERR_STATE, "grouped GEMM: context without error word");
+  if (type != CAI_TYPE_Q8_0 && type != CAI_TYPE_Q4_0) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "grouped GEMM: Q8_0 / Q4_0 experts only");
+  if (((uintptr_t)x % 16) || (ldx % 4) || (k % 32)) return cai_fail(ctx, CAI_ERR_INVALID, "grouped GEMM: activations must be 16-byte aligned, K a multiple of 32");
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.y = y; p.ldy = ldy; p.n = n; p.k = k; p.sstride = sstride; p.batch = 16; p.act = CAI_ACT_NONE; p.epi = EPI_STORE;
+  p.err_flag = ctx->err_flag;
+  p.xp = (const unsigned char*)xp_tiles; p.row_unscale = unscale_tiles;
+  p.tile_expert = tile_expert; p.tile_pairs = tile_pairs; p.bank_codes = bank_codes; p.bank_scales = bank_scales;
+  p.xp_tile_bytes = gemm_tc_group_tile_bytes(k);
+  const int n_chunks = (int)((k + TC_KC - 1) / TC_KC);
+  p.ksplit = 1; p.chunks_per_split = n_chunks;
+  tc_split_x_kernel<<<dim3(16, (unsigned)n_tiles), k >= 2048 ? 512 : 256, 0, ctx->stream>>>(x, ldx, 16, 16, k, n_chunks, 2, nullptr, 0.f, (unsigned char*)xp_tiles,
+                                                                                  unscale_tiles, tile_pairs, x_row_div, p.xp_tile_bytes);
+  CAI_LAUNCHED(ctx);
+  const int grid = (int)((n + TC_M - 1) / TC_M);
+  const cudaError_t e = (type == CAI_TYPE_Q8_0) ? tc_launch<CAI_TYPE_Q8_0, 16>(ctx, p, grid, n_tiles) : tc_launch<CAI_TYPE_Q4_0, 16>(ctx, p, grid, n_tiles);
+  if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "gemm_tc smem attribute -> %s", cudaGetErrorString(e));
+  CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

@@ -555,6 +555,11 @@ struct cai_session {
   float* gu = nullptr;                                // [B][2*inter] un-fused up|gate (tensor-core batches)
   float *router_logits = nullptr, *gates = nullptr, *moe_hidden = nullptr, *pair_out = nullptr;
   int32_t* expert_ids = nullptr;
+  // grouped (tensor-core) expert path: pairs sorted into 16-row tiles per expert
+  int moe_tiles = 0;                       // 0 = the per-pair GEMV path
+  int32_t *tile_expert = nullptr, *tile_pairs = nullptr;
+  float *moe_gu = nullptr, *moe_unscale = nullptr;
+  void* moe_xp = nullptr;
   float* partial = nullptr;
   int nsplit = 1;
   int32_t* amax_idx = nullptr; float* amax_val = nullptr;
@@ -704,6 +709,20 @@ static int enqueue_step(cai_session* s) {
         CAI_TRY(linear_launch(ctx, a));
       }
       CAI_TRY(op_topk_gate(ctx, s->router_logits, B, E, K, c.norm_topk, s->expert_ids, s->gates));
+      if (s->moe_tiles) {
+        // enough pairs per expert: group them by expert and run each expert's matrices once per 16 pairs on the
+        // tensor cores (the per-pair GEMV below streams an expert's weights once per pair)
+        const QWeight& gu = L.exp_gu[0];
+        const QWeight& dn = L.exp_down[0];
+        CAI_TRY(op_moe_group(ctx, s->expert_ids, B * K, E, 16, s->moe_tiles, s->tile_expert, s->tile_pairs));
+        ctx->cur_family = FAM_LINEAR;
+        CAI_TRY(gemm_tc_launch_grouped(ctx, gu.type, L.d_gu_codes, L.d_gu_scales, gu.n, gu.k, gu.sstride, s->h, H, K, s->moe_gu, 2 * (int64_t)Im,
+                                       s->tile_expert, s->tile_pairs, s->moe_tiles, s->moe_xp, s->moe_unscale));
+        CAI_TRY(op_swiglu(ctx, s->moe_gu, 2 * (int64_t)Im, s->moe_hidden, Im, B * K, Im));
+        ctx->cur_family = FAM_LINEAR;
+        CAI_TRY(gemm_tc_launch_grouped(ctx, dn.type, L.d_down_codes, L.d_down_scales, dn.n, dn.k, dn.sstride, s->moe_hidden, Im, 1, s->pair_out, H,
+                                       s->tile_expert, s->tile_pairs, s->moe_tiles, s->moe_xp, s->moe_unscale));
+      } else {
       {
         LinearArgs a; a.w = &L.exp_gu[0]; a.x = s->h; a.ldx = H; a.y = s->moe_hidden; a.ldy = Im; a.batch = B * K;
         a.epilogue = EPI_SWIGLU; a.bank_codes_dev = L.d_gu_codes; a.bank_scales_dev = L.d_gu_scales;
@@ -714,6 +733,7 @@ static int enqueue_step(cai_session* s) {
         LinearArgs a; a.w = &L.exp_down[0]; a.x = s->moe_hidden; a.ldx = Im; a.y = s->pair_out; a.ldy = H; a.batch = B * K;
         a.bank_codes_dev = L.d_down_codes; a.bank_scales_dev = L.d_down_scales; a.expert_ids_dev = s->expert_ids; a.x_row_div = 1;
         CAI_TRY(linear_launch(ctx, a));
+      }
       }
       CAI_TRY(op_moe_combine(ctx, x, H, s->pair_out, H, s->gates, B, K, H));
     }
@@ -793,7 +813,8 @@ int cai_session_destroy(cai_session* s) {
   if (s->ar) comm_ar_destroy(s->ctx, s->ar);
   void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
                   s->att, s->act, s->gu, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
-                  s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf};
+                  s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf,
+                  s->tile_expert, s->tile_pairs, s->moe_gu, s->moe_unscale, s->moe_xp};
   for (void* p : bufs) if (p) cudaFree(p);
   if (s->io_pinned) cudaFreeHost(s->io_pinned);
   s->m->sessions -= 1;
@@ -845,6 +866,22 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
     A((void**)&s->router_logits, (size_t)B * c.n_experts * 4); A((void**)&s->gates, (size_t)B * c.top_k * 4);
     A((void**)&s->expert_ids, (size_t)B * c.top_k * 4);
     A((void**)&s->moe_hidden, (size_t)B * c.top_k * c.moe_inter * 4); A((void**)&s->pair_out, (size_t)B * c.top_k * H * 4);
+    {
+      // Grouped tensor-core path when an expert sees two or more pairs on average (otherwise most tiles would hold one
+      // pair and the per-pair GEMV is the better kernel), quantized experts, whole 32-blocks.
+      const int pairs = B * c.top_k;
+      const QWeight& gu = m->layers[0].exp_gu[0];
+      const bool quant = gu.type == CAI_TYPE_Q8_0 || gu.type == CAI_TYPE_Q4_0;
+      const char* off = getenv("CAI_MOE_GROUPED");
+      if (quant && pairs >= 2 * c.n_experts && pairs <= 4096 && c.n_experts <= 1024 && H % 32 == 0 && c.moe_inter % 32 == 0 &&
+          !(off && *off == '0')) {
+        s->moe_tiles = pairs / 16 + (pairs < c.n_experts ? pairs : c.n_experts) + 1;      // sum over experts of ceil(count / 16) is below this
+        const size_t tile_bytes = gemm_tc_group_tile_bytes(H > c.moe_inter ? H : c.moe_inter);
+        A((void**)&s->tile_expert, (size_t)s->moe_tiles * 4); A((void**)&s->tile_pairs, (size_t)s->moe_tiles * 16 * 4);
+        A((void**)&s->moe_gu, (size_t)pairs * 2 * c.moe_inter * 4);
+        A((void**)&s->moe_unscale, (size_t)s->moe_tiles * 16 * 4); A(&s->moe_xp, (size_t)s->moe_tiles * tile_bytes);
+      }
+    }
   }
   if (m->tp_size > 1) {
     A((void**)&s->amax_pack, (size_t)B * 2 * 4); A((void**)&s->amax_gather, (size_t)m->tp_size * B * 2 * 4);

@@ -314,3 +314,53 @@ int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n) {
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Groups the (token, expert) pairs of a mixture-of-experts layer by expert, into tiles of up to `tile_rows` pairs
+// that share one expert: tile_expert[t] (-1 = unused tile) and tile_pairs[t * tile_rows + i] (-1 = unused slot).
+// Pairs keep their order inside an expert and experts come in index order, so the lists are deterministic.
+// One CTA; pairs <= 4096, experts <= 1024.
+// ---------------------------------------------------------------------------
+__global__ void moe_group_kernel(const int32_t* __restrict__ ids, int pairs, int n_experts, int tile_rows, int max_tiles,
+                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_pairs) {
+  extern __shared__ int32_t sh[];
+  int32_t* s_ids = sh;                       // [pairs]
+  int32_t* s_cnt = sh + pairs;               // [n_experts]
+  int32_t* s_base = s_cnt + n_experts;       // [n_experts + 1] first tile of each expert
+  pdl_trigger();
+  pdl_wait();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) s_ids[i] = ids[i];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) s_cnt[e] = 0;
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+  for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) tile_pairs[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&s_cnt[s_ids[i]], 1);   // counts only: order does not matter
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int e = 0; e < n_experts; ++e) { s_base[e] = t; t += (s_cnt[e] + tile_rows - 1) / tile_rows; }
+    s_base[n_experts] = t;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = s_ids[i];
+    int rank = 0;                             // pairs of the same expert before this one
+    for (int q = 0; q < i; ++q) rank += (s_ids[q] == e) ? 1 : 0;
+    const int t = s_base[e] + rank / tile_rows;
+    if (t < max_tiles) {
+      tile_pairs[(size_t)t * tile_rows + (rank % tile_rows)] = i;
+      if (rank % tile_rows == 0) tile_expert[t] = e;
+    }
+  }
+}
+
+int op_moe_group(cai_ctx* ctx, const int32_t* expert_ids, int pairs, int n_experts, int tile_rows, int max_tiles,
+                 int32_t* tile_expert, int32_t* tile_pairs) {
+  ctx->cur_family = FAM_OTHER;
+  if (pairs < 1 || pairs > 4096 || n_experts < 1 || n_experts > 1024)
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "moe grouping: %d pairs, %d experts", pairs, n_experts);
+  const size_t smem = ((size_t)pairs + 2 * (size_t)n_experts + 1) * sizeof(int32_t);
+  pdl_launch(ctx, moe_group_kernel, dim3(1), dim3(512), smem, expert_ids, pairs, n_experts, tile_rows, max_tiles, tile_expert, tile_pairs);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}

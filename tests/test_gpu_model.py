@@ -283,3 +283,36 @@ def test_tensor_core_batches_match_single_sequence_sessions(backend, batch, dims
         wide.close()
         one.close()
         model.close()
+
+
+def test_grouped_expert_batches_match_single_sequence_sessions(backend):
+    """With two or more (token, expert) pairs per expert on average the expert matrices run grouped on the tensor
+    cores (pairs sorted into 16-row tiles per expert); every sequence must still match its single-sequence session,
+    which runs the per-pair CUDA-core path."""
+    kw = dict(hidden=256, inter=512, layers=2, heads=4, kv_heads=2, head_dim=64, vocab=512, rms_eps=1e-5, rope_theta=1e4,
+              qk_norm=True, n_experts=8, top_k=2, norm_topk=False, moe_inter=128)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=5, std=0.05)
+    model.finalize()
+    batch, steps = 12, 5                      # 24 pairs over 8 experts
+    rng = np.random.default_rng(9)
+    toks = rng.integers(0, kw["vocab"], (batch, steps)).astype(np.int32)
+    wide = StreamingDecoder(model, 8, batch=batch)
+    one = StreamingDecoder(model, 8, batch=1)
+    try:
+        wide_logits = []
+        for i in range(steps):
+            logits, _ = wide.step_forward(toks[:, i])
+            wide_logits.append(logits.copy())
+        worst = 0.0
+        for b in range(batch):
+            one.reset()
+            for i in range(steps):
+                ref, _ = one.step_forward([toks[b, i]])
+                rms = float(np.sqrt(np.mean(ref[0].astype(np.float64) ** 2)))
+                worst = max(worst, float(np.max(np.abs(wide_logits[i][b] - ref[0]))) / rms)
+        assert worst < 1e-3, worst
+    finally:
+        wide.close()
+        one.close()
+        model.close()
