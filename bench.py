@@ -209,7 +209,7 @@ def run_reference(args, arch_kw, ggml_type, batch, ctx):
 def parallel_mode(args):
     if args.parallel != "auto":
         return args.parallel
-    return "tp" if args.workload == "qwen2.5-32b" else "dp"
+    return {"qwen2.5-32b": "tp", "olmoe-1b-7b": "ep"}.get(args.workload, "dp")
 
 
 def workload_config(args, arch_kw, ggml_type, batch, ctx, world):
@@ -231,14 +231,20 @@ def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, 
     from neural_api_b200 import parallel
     kw = ARCHS[arch]
     tp = world if (world > 1 and mode == "tp") else 1
+    ep = world if (world > 1 and mode == "ep") else 1
     replicas = world if (world > 1 and mode == "dp") else 1
-    model = LlamaModel(backend, arch_config(arch), tp_rank=rank if tp > 1 else 0, tp_size=tp)
+    if ep > 1:
+        if batch % ep:
+            raise SystemExit("expert parallelism divides the batch over the GPUs: %d sequences, %d GPUs" % (batch, ep))
+        batch = batch // ep                   # this rank's sequences; the job's batch is unchanged
+        replicas = ep
+    model = LlamaModel(backend, arch_config(arch), tp_rank=rank if tp > 1 else 0, tp_size=tp, ep_rank=rank if ep > 1 else 0, ep_size=ep)
     model.init_synthetic(ggml_type, seed=seed, std=0.02)
     model.finalize()
     prof_steps = 2 if do_profile else 0
     max_ctx = ctx + warmup + steps * (2 if do_e2e else 1) + prof_steps + 8
     sess = StreamingDecoder(model, max_ctx, batch=batch)
-    rng = np.random.default_rng(seed + (rank if replicas > 1 else 0))
+    rng = np.random.default_rng(seed + (rank if replicas > 1 else 0))   # every replica / expert-parallel rank has its own prompts
     prompt = rng.integers(0, kw["vocab"], (batch, ctx)).astype(np.int32)
     t0 = time.perf_counter()
     if ctx > 1:
@@ -349,9 +355,10 @@ def main():
     ap.add_argument("--workload", default="qwen2.5-32b", choices=sorted(WORKLOAD_DEFAULTS) + ["linear"])
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
-    ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "dp"],
+    ap.add_argument("--parallel", default="auto", choices=["auto", "tp", "dp", "ep"],
                     help="N > 1: tp = one job sharded tensor-parallel (strong scaling), dp = one replica with its own batch per GPU "
-                         "(weak scaling, no collective on the data path); auto = tp for qwen2.5-32b, dp for the others")
+                         "(weak scaling, no collective on the data path), ep = experts sharded, the job's sequences divided over the "
+                         "GPUs (strong scaling); auto = tp for qwen2.5-32b, ep for olmoe-1b-7b, dp for the others")
     ap.add_argument("--no-extra", action="store_true", help="skip the Qwen2.5-0.5B side measurement and the CPU baseline")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -378,7 +385,7 @@ def main():
     from neural_api_b200.backend import CudaBackend
     backend = CudaBackend(local_rank)
     mode = parallel_mode(args)
-    if world > 1 and mode == "tp":
+    if world > 1 and mode in ("tp", "ep"):
         uid = backend.comm_unique_id() if rank == 0 else bytes(128)
         uid = parallel.broadcast_bytes(dist, uid, src=0, length=128)
         backend.comm_init(rank, world, uid)

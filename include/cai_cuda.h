@@ -198,6 +198,12 @@ typedef struct cai_llama_config {
 /* tp_size > 1 shards attention heads and MLP columns/rows over tp_size processes
  * (one GPU each); ep_size > 1 shards MoE experts. Neither exists in the reference. */
 int cai_model_create(cai_ctx* ctx, const cai_llama_config* cfg, int tp_rank, int tp_size, cai_model** out);
+/* Expert-parallel creation for mixture-of-experts models (no reference counterpart; the reference is single
+ * process): dense parts replicated, rank ep_rank keeps experts [ep_rank E / ep_size, (ep_rank + 1) E / ep_size),
+ * sessions hold this rank's own sequences. Call cai_comm_init(ctx, ep_rank, ep_size, id) first. Every rank uploads
+ * (or generates) the full tensor set; tensors of other ranks' experts are ignored. All ranks must create their
+ * sessions with the same batch and step them together. */
+int cai_model_create_ep(cai_ctx* ctx, const cai_llama_config* cfg, int ep_rank, int ep_size, cai_model** out_model);
 int cai_model_destroy(cai_model* m);
 /* One tensor under its HF name ("model.layers.3.self_attn.q_proj.weight", ...) in
  * HF layout: rows = out features, cols = in features, `type` blocks along cols

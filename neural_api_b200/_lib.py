@@ -72,6 +72,7 @@ SIGNATURES = {
     "cai_sdpa_step_dev": [_P, _P, _P],
     "cai_sdpa_step_noalloc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "cai_model_create": [_P, C.POINTER(LlamaConfigC), _I, _I, _PP],
+    "cai_model_create_ep": [_P, C.POINTER(LlamaConfigC), _I, _I, _PP],
     "cai_model_destroy": [_P],
     "cai_model_upload_tensor": [_P, C.c_char_p, _I, _P, _I64, _I64, _I],
     "cai_model_init_synthetic": [_P, _I, C.c_uint64, C.c_float],

@@ -315,10 +315,15 @@ def make_config(hidden, inter, layers, heads, kv_heads, head_dim, vocab, rms_eps
 class LlamaModel:
     """The Llama-family graph resident on one GPU (or one tensor-parallel shard)."""
 
-    def __init__(self, backend, cfg, tp_rank=0, tp_size=1):
+    def __init__(self, backend, cfg, tp_rank=0, tp_size=1, ep_rank=0, ep_size=1):
+        """tp_*: tensor-parallel shard of a dense model; ep_*: expert-parallel share of a mixture-of-experts model
+        (dense parts replicated, sessions hold this rank's own sequences)."""
         self.backend, self.cfg = backend, cfg
         h = C.c_void_p()
-        backend._check(backend.lib.cai_model_create(backend.ctx, C.byref(cfg), tp_rank, tp_size, C.byref(h)))
+        if ep_size > 1:
+            backend._check(backend.lib.cai_model_create_ep(backend.ctx, C.byref(cfg), ep_rank, ep_size, C.byref(h)))
+        else:
+            backend._check(backend.lib.cai_model_create(backend.ctx, C.byref(cfg), tp_rank, tp_size, C.byref(h)))
         self.handle = h
 
     def upload_tensor(self, hf_name, ggml_type, data, rows, cols, interleave_head_dim=0):

@@ -186,8 +186,17 @@ int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, i
 int op_argmax(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int n, int32_t* out_idx, float* out_val,
               float* part_val, int* part_idx, int* tickets);   // scratch: [batch][CAI_ARGMAX_CHUNKS] x2, tickets [batch] zeroed once
 int op_rope_table(cai_ctx* ctx, const float* theta_dev, const int32_t* pos_dev, int batch, int half, float* cs_dev);
+// pairs whose expert lies outside [expert_lo, expert_hi) are left out (expert parallelism: another rank owns them)
 int op_moe_group(cai_ctx* ctx, const int32_t* expert_ids, int pairs, int n_experts, int tile_rows, int max_tiles,
-                 int32_t* tile_expert, int32_t* tile_pairs);
+                 int32_t* tile_expert, int32_t* tile_pairs, int expert_lo, int expert_hi);
+// expert parallelism: packs a rank's rows [hidden floats | top_k expert ids | top_k gates] for one all-gather, and the
+// partial combine  y[t][:] = sum over the slots of token t whose expert is in [lo, hi) of gate * pair_out[pair][:]
+int op_moe_pack(cai_ctx* ctx, const float* h, int64_t ldh, const int32_t* ids, const float* gates, int tokens, int hidden, int top_k, int stride,
+                float* packed);
+int op_moe_unpack_ids(cai_ctx* ctx, const float* packed, int tokens, int hidden, int top_k, int stride, int32_t* ids, float* gates);
+int op_moe_combine_partial(cai_ctx* ctx, const float* pair_out, int64_t ldp, const int32_t* ids, const float* gates, int tokens, int top_k,
+                           int hidden, int expert_lo, int expert_hi, float* y, int64_t ldy);
+int op_add_rows(cai_ctx* ctx, float* x, int64_t ldx, const float* y, int64_t ldy, int tokens, int width);
 // gemm_tc.cu: grouped tensor-core GEMM over the tiles op_moe_group made (16 pairs per tile)
 size_t gemm_tc_group_tile_bytes(int64_t k);
 int gemm_tc_launch_grouped(cai_ctx* ctx, int type, const void* const* bank_codes, const __half* const* bank_scales, int64_t n, int64_t k,
@@ -224,7 +233,9 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a);
 // comm.cu
 int comm_allreduce(cai_ctx* ctx, float* buf, int64_t count);
 int comm_allgather(cai_ctx* ctx, const float* send, float* recv, int64_t count_per_rank);
+int comm_reduce_scatter(cai_ctx* ctx, const float* send, float* recv, int64_t count_per_rank);
 int comm_world(cai_ctx* ctx);
+int comm_rank(cai_ctx* ctx);
 struct cai_tp_ar;   // one-shot all-reduce over peer memory (comm.cu)
 int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out);   // collective; *out stays NULL when peers cannot be mapped
 void comm_ar_destroy(cai_ctx* ctx, cai_tp_ar* ar);                                 // collective

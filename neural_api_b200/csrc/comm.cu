@@ -15,6 +15,7 @@ struct cai_comm_state {
   } while (0)
 
 int comm_world(cai_ctx* ctx) { return ctx->comm ? ctx->comm->world : 1; }
+int comm_rank(cai_ctx* ctx) { return ctx->comm ? ctx->comm->rank : 0; }
 
 void comm_destroy(cai_ctx* ctx) {
   if (ctx->comm) {
@@ -34,6 +35,14 @@ int comm_allreduce(cai_ctx* ctx, float* buf, int64_t count) {
 int comm_allgather(cai_ctx* ctx, const float* send, float* recv, int64_t count_per_rank) {
   if (!ctx->comm) return cai_fail(ctx, CAI_ERR_STATE, "communicator not initialised");
   CAI_NCCL(ctx, ncclAllGather(send, recv, (size_t)count_per_rank, ncclFloat, ctx->comm->comm, ctx->stream));
+  if (ctx->prof_on) cai_prof_mark(ctx, FAM_COMM);
+  return CAI_OK;
+}
+
+// recv[rank's slice of count_per_rank floats] = sum over ranks of send[that slice]
+int comm_reduce_scatter(cai_ctx* ctx, const float* send, float* recv, int64_t count_per_rank) {
+  if (!ctx->comm) return cai_fail(ctx, CAI_ERR_STATE, "communicator not initialised");
+  CAI_NCCL(ctx, ncclReduceScatter(send, recv, (size_t)count_per_rank, ncclFloat, ncclSum, ctx->comm->comm, ctx->stream));
   if (ctx->prof_on) cai_prof_mark(ctx, FAM_COMM);
   return CAI_OK;
 }

@@ -67,6 +67,12 @@ struct cai_model {
   cai_ctx* ctx;
   cai_llama_config cfg;
   int tp_rank, tp_size;
+  // expert parallelism (cai_model_create_ep): the dense parts are replicated, rank r owns experts
+  // [r * n_experts / ep_size, (r + 1) * n_experts / ep_size); sessions hold this rank's share of the sequences
+  int ep_rank = 0, ep_size = 1;
+  int expert_lo() const { return ep_rank * (cfg.n_experts / ep_size); }
+  int expert_hi() const { return (ep_rank + 1) * (cfg.n_experts / ep_size); }
+  bool owns_expert(int e) const { return e >= expert_lo() && e < expert_hi(); }
   // local (this rank's) dimensions
   int heads_l, kv_heads_l, qw_l, kw_l, inter_l, vocab_l;
   QWeight embed, lm_head;
@@ -156,6 +162,25 @@ int cai_model_create(cai_ctx* ctx, const cai_llama_config* cfg, int tp_rank, int
   if (c.n_experts)
     for (auto& L : m->layers) { L.exp_gu.resize((size_t)c.n_experts); L.exp_down.resize((size_t)c.n_experts); L.exp_have.assign((size_t)c.n_experts, 0); }
   *out = m;
+  return CAI_OK;
+}
+
+// Expert-parallel twin of cai_model_create for mixture-of-experts models: the dense parts (attention, router,
+// embeddings) are replicated on every rank, rank r keeps experts [r E / n, (r + 1) E / n), and a session holds the
+// rank's own sequences (data parallel outside the expert layers). Per expert layer the ranks all-gather their
+// tokens' normalised activations with the routing decisions, run the pairs routed to their experts, combine them
+// per token and reduce-scatter the partial sums back to the tokens' owners.
+int cai_model_create_ep(cai_ctx* ctx, const cai_llama_config* cfg, int ep_rank, int ep_size, cai_model** out) {
+  CAI_TRY(cai_bind(ctx));
+  if (!cfg || !out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_create_ep: null argument");
+  if (ep_size < 1 || ep_rank < 0 || ep_rank >= ep_size) return cai_fail(ctx, CAI_ERR_INVALID, "ep rank %d of %d", ep_rank, ep_size);
+  if (ep_size > 1) {
+    if (cfg->n_experts < 1 || (cfg->n_experts % ep_size)) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "expert parallelism needs n_experts divisible by ep_size");
+    if (comm_world(ctx) != ep_size || comm_rank(ctx) != ep_rank) return cai_fail(ctx, CAI_ERR_STATE, "call cai_comm_init with this rank and world == ep_size first");
+  }
+  CAI_TRY(cai_model_create(ctx, cfg, 0, 1, out));
+  (*out)->ep_rank = ep_rank;
+  (*out)->ep_size = ep_size;
   return CAI_OK;
 }
 
@@ -285,6 +310,7 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
     }
     case T_EXP_GATE: case T_EXP_UP: case T_EXP_DOWN: {
       if (!c.n_experts || t.expert < 0 || t.expert >= c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': expert index", hf_name);
+      if (!m->owns_expert(t.expert)) return CAI_OK;         // expert parallelism: another rank keeps this expert
       const int Im = c.moe_inter;
       if (t.kind == T_EXP_DOWN) {
         NEED_SHAPE(H, Im);
@@ -382,6 +408,7 @@ int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std) {
       CAI_TRY(qweight_init_synthetic(ctx, &L.router, seed, tid + 10, std, 0, 0, H));
       L.have |= HAVE_ROUTER;
       for (int e = 0; e < c.n_experts; ++e) {
+        if (!m->owns_expert(e)) continue;
         const uint64_t etid = 100000 + ((uint64_t)l * (uint64_t)c.n_experts + (uint64_t)e) * 4;
         QWeight* gu = &L.exp_gu[(size_t)e];
         CAI_TRY(ensure_weight(ctx, gu, type, 2 * (int64_t)Im, H));
@@ -497,9 +524,11 @@ int cai_model_finalize(cai_model* m) {
     L.wqkv.bias = L.qkv_bias;     // alias; freed through qkv_bias
     if (c.n_experts) {
       std::vector<const void*> gc, gs, dc, ds;
+      const int e0 = m->expert_lo();
       for (int e = 0; e < c.n_experts; ++e) {
+        if (!m->owns_expert(e)) { gc.push_back(nullptr); gs.push_back(nullptr); dc.push_back(nullptr); ds.push_back(nullptr); continue; }
         if (L.exp_have[(size_t)e] != 7) return cai_fail(ctx, CAI_ERR_STATE, "layer %d expert %d is missing tensors", l, e);
-        if (L.exp_gu[(size_t)e].type != L.exp_gu[0].type || L.exp_down[(size_t)e].type != L.exp_down[0].type)
+        if (L.exp_gu[(size_t)e].type != L.exp_gu[(size_t)e0].type || L.exp_down[(size_t)e].type != L.exp_down[(size_t)e0].type)
           return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "experts of one layer must share a storage type");
         gc.push_back(L.exp_gu[(size_t)e].codes); gs.push_back(L.exp_gu[(size_t)e].scales);
         dc.push_back(L.exp_down[(size_t)e].codes); ds.push_back(L.exp_down[(size_t)e].scales);
@@ -526,7 +555,7 @@ int cai_model_step_weight_bytes(cai_model* m, int64_t* out_bytes) {
     if (m->cfg.n_experts) {
       b += (int64_t)L.router.bytes();
       // one token touches top_k experts
-      b += (int64_t)m->cfg.top_k * (int64_t)(L.exp_gu[0].bytes() + L.exp_down[0].bytes());
+      b += (int64_t)m->cfg.top_k * (int64_t)(L.exp_gu[(size_t)m->expert_lo()].bytes() + L.exp_down[(size_t)m->expert_lo()].bytes());
     } else {
       b += (int64_t)(L.wgu.bytes() + L.wdown.bytes());
     }
@@ -560,6 +589,9 @@ struct cai_session {
   int32_t *tile_expert = nullptr, *tile_pairs = nullptr;
   float *moe_gu = nullptr, *moe_unscale = nullptr;
   void* moe_xp = nullptr;
+  // expert parallelism: the gathered tokens of all ranks
+  float *ep_pack = nullptr, *ep_all = nullptr, *ep_gates = nullptr, *ep_part = nullptr, *ep_mine = nullptr;
+  int32_t* ep_ids = nullptr;
   float* partial = nullptr;
   int nsplit = 1;
   int32_t* amax_idx = nullptr; float* amax_val = nullptr;
@@ -709,12 +741,34 @@ static int enqueue_step(cai_session* s) {
         CAI_TRY(linear_launch(ctx, a));
       }
       CAI_TRY(op_topk_gate(ctx, s->router_logits, B, E, K, c.norm_topk, s->expert_ids, s->gates));
+      if (m->ep_size > 1) {
+        // Expert parallel: gather every rank's rows [h | ids | gates], run the pairs of MY experts for ALL tokens
+        // (grouped, on the tensor cores), combine them per token, and reduce-scatter the partial sums to the owners.
+        const int Bg = B * m->ep_size, W = (H + 2 * K + 3) & ~3;
+        const QWeight& gu = L.exp_gu[(size_t)m->expert_lo()];
+        const QWeight& dn = L.exp_down[(size_t)m->expert_lo()];
+        CAI_TRY(op_moe_pack(ctx, s->h, H, s->expert_ids, s->gates, B, H, K, W, s->ep_pack));
+        CAI_TRY(comm_allgather(ctx, s->ep_pack, s->ep_all, (int64_t)B * W));
+        CAI_TRY(op_moe_unpack_ids(ctx, s->ep_all, Bg, H, K, W, s->ep_ids, s->ep_gates));
+        CAI_TRY(op_moe_group(ctx, s->ep_ids, Bg * K, E, 16, s->moe_tiles, s->tile_expert, s->tile_pairs, m->expert_lo(), m->expert_hi()));
+        ctx->cur_family = FAM_LINEAR;
+        CAI_TRY(gemm_tc_launch_grouped(ctx, gu.type, L.d_gu_codes, L.d_gu_scales, gu.n, gu.k, gu.sstride, s->ep_all, W, K, s->moe_gu, 2 * (int64_t)Im,
+                                       s->tile_expert, s->tile_pairs, s->moe_tiles, s->moe_xp, s->moe_unscale));
+        CAI_TRY(op_swiglu(ctx, s->moe_gu, 2 * (int64_t)Im, s->moe_hidden, Im, Bg * K, Im));
+        ctx->cur_family = FAM_LINEAR;
+        CAI_TRY(gemm_tc_launch_grouped(ctx, dn.type, L.d_down_codes, L.d_down_scales, dn.n, dn.k, dn.sstride, s->moe_hidden, Im, 1, s->pair_out, H,
+                                       s->tile_expert, s->tile_pairs, s->moe_tiles, s->moe_xp, s->moe_unscale));
+        CAI_TRY(op_moe_combine_partial(ctx, s->pair_out, H, s->ep_ids, s->ep_gates, Bg, K, H, m->expert_lo(), m->expert_hi(), s->ep_part, H));
+        CAI_TRY(comm_reduce_scatter(ctx, s->ep_part, s->ep_mine, (int64_t)B * H));
+        CAI_TRY(op_add_rows(ctx, x, H, s->ep_mine, H, B, H));
+        continue;
+      }
       if (s->moe_tiles) {
         // enough pairs per expert: group them by expert and run each expert's matrices once per 16 pairs on the
         // tensor cores (the per-pair GEMV below streams an expert's weights once per pair)
         const QWeight& gu = L.exp_gu[0];
         const QWeight& dn = L.exp_down[0];
-        CAI_TRY(op_moe_group(ctx, s->expert_ids, B * K, E, 16, s->moe_tiles, s->tile_expert, s->tile_pairs));
+        CAI_TRY(op_moe_group(ctx, s->expert_ids, B * K, E, 16, s->moe_tiles, s->tile_expert, s->tile_pairs, 0, E));
         ctx->cur_family = FAM_LINEAR;
         CAI_TRY(gemm_tc_launch_grouped(ctx, gu.type, L.d_gu_codes, L.d_gu_scales, gu.n, gu.k, gu.sstride, s->h, H, K, s->moe_gu, 2 * (int64_t)Im,
                                        s->tile_expert, s->tile_pairs, s->moe_tiles, s->moe_xp, s->moe_unscale));
@@ -814,7 +868,8 @@ int cai_session_destroy(cai_session* s) {
   void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
                   s->att, s->act, s->gu, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
                   s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf,
-                  s->tile_expert, s->tile_pairs, s->moe_gu, s->moe_unscale, s->moe_xp};
+                  s->tile_expert, s->tile_pairs, s->moe_gu, s->moe_unscale, s->moe_xp,
+                  s->ep_pack, s->ep_all, s->ep_gates, s->ep_part, s->ep_mine, s->ep_ids};
   for (void* p : bufs) if (p) cudaFree(p);
   if (s->io_pinned) cudaFreeHost(s->io_pinned);
   s->m->sessions -= 1;
@@ -865,21 +920,34 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   if (c.n_experts) {
     A((void**)&s->router_logits, (size_t)B * c.n_experts * 4); A((void**)&s->gates, (size_t)B * c.top_k * 4);
     A((void**)&s->expert_ids, (size_t)B * c.top_k * 4);
-    A((void**)&s->moe_hidden, (size_t)B * c.top_k * c.moe_inter * 4); A((void**)&s->pair_out, (size_t)B * c.top_k * H * 4);
+    const int Bm = B * m->ep_size;             // sequences whose pairs this rank may have to run (all ranks' under expert parallelism)
+    const int pairs = Bm * c.top_k;
+    A((void**)&s->moe_hidden, (size_t)pairs * c.moe_inter * 4); A((void**)&s->pair_out, (size_t)pairs * H * 4);
     {
       // Grouped tensor-core path when an expert sees two or more pairs on average (otherwise most tiles would hold one
-      // pair and the per-pair GEMV is the better kernel), quantized experts, whole 32-blocks.
-      const int pairs = B * c.top_k;
-      const QWeight& gu = m->layers[0].exp_gu[0];
+      // pair and the per-pair GEMV is the better kernel), quantized experts, whole 32-blocks. Expert parallelism
+      // always takes it.
+      const QWeight& gu = m->layers[0].exp_gu[(size_t)m->expert_lo()];
       const bool quant = gu.type == CAI_TYPE_Q8_0 || gu.type == CAI_TYPE_Q4_0;
       const char* off = getenv("CAI_MOE_GROUPED");
-      if (quant && pairs >= 2 * c.n_experts && pairs <= 4096 && c.n_experts <= 1024 && H % 32 == 0 && c.moe_inter % 32 == 0 &&
-          !(off && *off == '0')) {
-        s->moe_tiles = pairs / 16 + (pairs < c.n_experts ? pairs : c.n_experts) + 1;      // sum over experts of ceil(count / 16) is below this
+      const bool can = quant && pairs <= 4096 && c.n_experts <= 1024 && H % 32 == 0 && c.moe_inter % 32 == 0;
+      if (m->ep_size > 1 && !can) {
+        cai_session_destroy(s);
+        return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "expert parallelism needs Q8_0 / Q4_0 experts, at most 4096 (token, expert) pairs per step and 32-aligned widths");
+      }
+      if (can && (m->ep_size > 1 || (pairs >= 2 * c.n_experts && !(off && *off == '0')))) {
+        const int local_experts = c.n_experts / m->ep_size;
+        s->moe_tiles = pairs / 16 + (pairs < local_experts ? pairs : local_experts) + 1;  // sum over experts of ceil(count / 16) is below this
         const size_t tile_bytes = gemm_tc_group_tile_bytes(H > c.moe_inter ? H : c.moe_inter);
         A((void**)&s->tile_expert, (size_t)s->moe_tiles * 4); A((void**)&s->tile_pairs, (size_t)s->moe_tiles * 16 * 4);
         A((void**)&s->moe_gu, (size_t)pairs * 2 * c.moe_inter * 4);
         A((void**)&s->moe_unscale, (size_t)s->moe_tiles * 16 * 4); A(&s->moe_xp, (size_t)s->moe_tiles * tile_bytes);
+      }
+      if (m->ep_size > 1) {
+        const size_t W = ((size_t)H + 2 * (size_t)c.top_k + 3) & ~(size_t)3;       // packed row: h | ids | gates, padded to 16 bytes
+        A((void**)&s->ep_pack, (size_t)B * W * 4); A((void**)&s->ep_all, (size_t)Bm * W * 4);
+        A((void**)&s->ep_ids, (size_t)pairs * 4); A((void**)&s->ep_gates, (size_t)pairs * 4);
+        A((void**)&s->ep_part, (size_t)Bm * H * 4); A((void**)&s->ep_mine, (size_t)B * H * 4);
       }
     }
   }

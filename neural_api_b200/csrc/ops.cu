@@ -322,19 +322,23 @@ int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n) {
 // One CTA; pairs <= 4096, experts <= 1024.
 // ---------------------------------------------------------------------------
 __global__ void moe_group_kernel(const int32_t* __restrict__ ids, int pairs, int n_experts, int tile_rows, int max_tiles,
-                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_pairs) {
+                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_pairs, int expert_lo, int expert_hi) {
   extern __shared__ int32_t sh[];
   int32_t* s_ids = sh;                       // [pairs]
   int32_t* s_cnt = sh + pairs;               // [n_experts]
   int32_t* s_base = s_cnt + n_experts;       // [n_experts + 1] first tile of each expert
   pdl_trigger();
   pdl_wait();
-  for (int i = threadIdx.x; i < pairs; i += blockDim.x) s_ids[i] = ids[i];
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    s_ids[i] = (e >= expert_lo && e < expert_hi) ? e : -1;     // -1: another rank's expert
+  }
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) s_cnt[e] = 0;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
   for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) tile_pairs[i] = -1;
   __syncthreads();
-  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&s_cnt[s_ids[i]], 1);   // counts only: order does not matter
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+    if (s_ids[i] >= 0) atomicAdd(&s_cnt[s_ids[i]], 1);      // counts only: order does not matter
   __syncthreads();
   if (threadIdx.x == 0) {
     int t = 0;
@@ -344,6 +348,7 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ ids, int pairs, int
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int e = s_ids[i];
+    if (e < 0) continue;
     int rank = 0;                             // pairs of the same expert before this one
     for (int q = 0; q < i; ++q) rank += (s_ids[q] == e) ? 1 : 0;
     const int t = s_base[e] + rank / tile_rows;
@@ -355,12 +360,87 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ ids, int pairs, int
 }
 
 int op_moe_group(cai_ctx* ctx, const int32_t* expert_ids, int pairs, int n_experts, int tile_rows, int max_tiles,
-                 int32_t* tile_expert, int32_t* tile_pairs) {
+                 int32_t* tile_expert, int32_t* tile_pairs, int expert_lo, int expert_hi) {
   ctx->cur_family = FAM_OTHER;
   if (pairs < 1 || pairs > 4096 || n_experts < 1 || n_experts > 1024)
     return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "moe grouping: %d pairs, %d experts", pairs, n_experts);
   const size_t smem = ((size_t)pairs + 2 * (size_t)n_experts + 1) * sizeof(int32_t);
-  pdl_launch(ctx, moe_group_kernel, dim3(1), dim3(512), smem, expert_ids, pairs, n_experts, tile_rows, max_tiles, tile_expert, tile_pairs);
+  pdl_launch(ctx, moe_group_kernel, dim3(1), dim3(512), smem, expert_ids, pairs, n_experts, tile_rows, max_tiles, tile_expert, tile_pairs,
+             expert_lo, expert_hi);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Expert parallelism helpers. A rank's tokens travel as rows [hidden floats | top_k ids (bit-cast) | top_k gates].
+// ---------------------------------------------------------------------------
+__global__ void moe_pack_kernel(const float* __restrict__ h, int64_t ldh, const int32_t* __restrict__ ids, const float* __restrict__ gates,
+                                int hidden, int top_k, int stride, float* __restrict__ packed) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  float* row = packed + (size_t)t * stride;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) row[c] = h[(int64_t)t * ldh + c];
+  for (int k = threadIdx.x; k < top_k; k += blockDim.x) {
+    row[hidden + k] = __int_as_float(ids[t * top_k + k]);
+    row[hidden + top_k + k] = gates[t * top_k + k];
+  }
+}
+int op_moe_pack(cai_ctx* ctx, const float* h, int64_t ldh, const int32_t* ids, const float* gates, int tokens, int hidden, int top_k, int stride,
+                float* packed) {
+  ctx->cur_family = FAM_OTHER;
+  pdl_launch(ctx, moe_pack_kernel, dim3(tokens), dim3(256), 0, h, ldh, ids, gates, hidden, top_k, stride, packed);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+__global__ void moe_unpack_ids_kernel(const float* __restrict__ packed, int tokens, int hidden, int top_k, int stride,
+                                      int32_t* __restrict__ ids, float* __restrict__ gates) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= tokens * top_k) return;
+  const int t = i / top_k, k = i - t * top_k;
+  const float* row = packed + (size_t)t * stride;
+  ids[i] = __float_as_int(row[hidden + k]);
+  gates[i] = row[hidden + top_k + k];
+}
+int op_moe_unpack_ids(cai_ctx* ctx, const float* packed, int tokens, int hidden, int top_k, int stride, int32_t* ids, float* gates) {
+  ctx->cur_family = FAM_OTHER;
+  pdl_launch(ctx, moe_unpack_ids_kernel, dim3((tokens * top_k + 255) / 256), dim3(256), 0, packed, tokens, hidden, top_k, stride, ids, gates);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+__global__ void moe_combine_partial_kernel(const float* __restrict__ pair_out, int64_t ldp, const int32_t* __restrict__ ids,
+                                           const float* __restrict__ gates, int top_k, int hidden, int expert_lo, int expert_hi,
+                                           float* __restrict__ y, int64_t ldy) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top_k; ++k) {                       // slots in order: the sum does not depend on the rank count
+      const int e = ids[t * top_k + k];
+      if (e >= expert_lo && e < expert_hi) acc += gates[t * top_k + k] * pair_out[(int64_t)(t * top_k + k) * ldp + c];
+    }
+    y[(int64_t)t * ldy + c] = acc;
+  }
+}
+int op_moe_combine_partial(cai_ctx* ctx, const float* pair_out, int64_t ldp, const int32_t* ids, const float* gates, int tokens, int top_k,
+                           int hidden, int expert_lo, int expert_hi, float* y, int64_t ldy) {
+  ctx->cur_family = FAM_OTHER;
+  pdl_launch(ctx, moe_combine_partial_kernel, dim3(tokens), dim3(256), 0, pair_out, ldp, ids, gates, top_k, hidden, expert_lo, expert_hi, y, ldy);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+__global__ void add_rows_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, int64_t ldy, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) x[(int64_t)t * ldx + c] += y[(int64_t)t * ldy + c];
+}
+int op_add_rows(cai_ctx* ctx, float* x, int64_t ldx, const float* y, int64_t ldy, int tokens, int width) {
+  ctx->cur_family = FAM_OTHER;
+  pdl_launch(ctx, add_rows_kernel, dim3(tokens), dim3(256), 0, x, ldx, y, ldy, width);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

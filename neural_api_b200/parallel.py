@@ -81,3 +81,24 @@ def sum_over_ranks(dist, value):
     t = torch.tensor([float(value)], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t.item())
+
+
+def ep_expert_range(n_experts, rank, world):
+    """Experts [lo, hi) that rank `rank` of an expert-parallel group keeps (the rule of cai_model_create_ep)."""
+    if world < 1 or n_experts % world:
+        raise ValueError("n_experts %d does not divide over %d ranks" % (n_experts, world))
+    per = n_experts // world
+    return rank * per, (rank + 1) * per
+
+
+def ep_group_pairs(expert_ids, lo, hi, tile_rows=16):
+    """Host mirror of the device grouping (op_moe_group): the (token, slot) pairs whose expert lies in [lo, hi),
+    grouped by expert in index order and cut into tiles of at most tile_rows pairs; pairs keep their order inside an
+    expert. Returns a list of (expert, [pair indices])."""
+    tiles = []
+    flat = [int(e) for e in expert_ids]
+    for e in range(lo, hi):
+        mine = [i for i, v in enumerate(flat) if v == e]
+        for k in range(0, len(mine), tile_rows):
+            tiles.append((e, mine[k:k + tile_rows]))
+    return tiles

@@ -55,6 +55,7 @@ function cai_sdpa_reset(s: PCaiSdpa): cint; cdecl; external CaiLib;
 function cai_sdpa_truncate(s: PCaiSdpa; committed_len: cint): cint; cdecl; external CaiLib;
 function cai_sdpa_step_dev(s: PCaiSdpa; qkv_row_dev, out_dev: Pointer): cint; cdecl; external CaiLib;
 function cai_model_create(ctx: PCaiCtx; const cfg: TCaiLlamaConfig; tp_rank, tp_size: cint; out m: PCaiModel): cint; cdecl; external CaiLib;
+function cai_model_create_ep(ctx: PCaiCtx; const cfg: TCaiLlamaConfig; ep_rank, ep_size: cint; out m: PCaiModel): cint; cdecl; external CaiLib;
 function cai_model_destroy(m: PCaiModel): cint; cdecl; external CaiLib;
 function cai_model_upload_tensor(m: PCaiModel; hf_name: PChar; ggml_type: cint; data: Pointer; rows, cols: cint64; interleave_head_dim: cint): cint; cdecl; external CaiLib;
 function cai_model_finalize(m: PCaiModel): cint; cdecl; external CaiLib;

@@ -14,13 +14,67 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 from neural_api_b200 import parallel  # noqa: E402
-from oracle.forward import (LlamaConfig, OracleModel, OracleSession, rms_norm, rope_interleaved, swiglu)  # noqa: E402
+from oracle.forward import (LlamaConfig, OracleModel, OracleSession, rms_norm, rope_interleaved, router_gates, softmax_row,  # noqa: E402
+                            swiglu)
 
 
 def allreduce(a):
     t = torch.from_numpy(np.ascontiguousarray(a))
     dist.all_reduce(t)
     return t.numpy()
+
+
+def expert_parallel_check(rank, world):
+    """The expert-parallel exchange of one mixture-of-experts layer, replayed with numpy and gloo: every rank owns
+    its tokens and a share of the experts; rows [h | ids | gates] are all-gathered, each rank runs the pairs of ITS
+    experts for ALL tokens (grouped by expert like the device does), combines them per token, and a reduce-scatter
+    returns the sums to the tokens' owners. Must equal the unsharded oracle arithmetic."""
+    H, I, E, K, per_rank = 32, 16, 8, 2, 3
+    rng = np.random.default_rng(11)         # same seed on every rank: same weights, same tokens
+    router = (rng.standard_normal((E, H)) * 0.3).astype(np.float32)
+    experts = [dict(up=(rng.standard_normal((I, H)) * 0.2).astype(np.float32), gate=(rng.standard_normal((I, H)) * 0.2).astype(np.float32),
+                    down=(rng.standard_normal((H, I)) * 0.2).astype(np.float32)) for _ in range(E)]
+    h_all = rng.standard_normal((per_rank * world, H)).astype(np.float32)
+    mine = slice(rank * per_rank, (rank + 1) * per_rank)
+    # local routing, packed rows, all-gather
+    rows = []
+    for h in h_all[mine]:
+        order, gates = router_gates(softmax_row(router @ h), K, True)
+        rows.append(np.concatenate([h, order.astype(np.int32).view(np.float32), gates.astype(np.float32)]))
+    packed = torch.from_numpy(np.stack(rows).astype(np.float32))
+    gathered = [torch.zeros_like(packed) for _ in range(world)]
+    dist.all_gather(gathered, packed)
+    allrows = np.concatenate([t.numpy() for t in gathered])
+    ids = allrows[:, H:H + K].copy().view(np.int32)
+    gates = allrows[:, H + K:H + 2 * K]
+    assert np.array_equal(allrows[:, :H], h_all)
+    lo, hi = parallel.ep_expert_range(E, rank, world)
+    pair_out = np.zeros((per_rank * world * K, H), np.float32)
+    seen = 0
+    for e, pairs in parallel.ep_group_pairs(ids.reshape(-1), lo, hi, tile_rows=4):
+        assert lo <= e < hi and 0 < len(pairs) <= 4
+        for p in pairs:
+            hrow = allrows[p // K, :H]
+            fused = np.concatenate([experts[e]["up"] @ hrow, experts[e]["gate"] @ hrow])
+            pair_out[p] = experts[e]["down"] @ swiglu(fused, I)
+            seen += 1
+    assert seen == int(np.sum((ids >= lo) & (ids < hi)))
+    part = np.zeros((per_rank * world, H), np.float32)
+    for t in range(per_rank * world):
+        for k in range(K):
+            if lo <= ids[t, k] < hi:
+                part[t] += gates[t, k] * pair_out[t * K + k]
+    out = torch.zeros(per_rank, H)
+    dist.reduce_scatter(out, [torch.from_numpy(part[r * per_rank:(r + 1) * per_rank].copy()) for r in range(world)])
+    # unsharded oracle arithmetic for my tokens
+    for i, h in enumerate(h_all[mine]):
+        order, g = router_gates(softmax_row(router @ h), K, True)
+        y = np.zeros(H, np.float32)
+        for e_id, gate in zip(order, g):
+            ex = experts[int(e_id)]
+            fused = np.concatenate([ex["up"] @ h, ex["gate"] @ h])
+            y = y + gate * (ex["down"] @ swiglu(fused, I))
+        assert float(np.max(np.abs(out[i].numpy() - y))) < 1e-5
 
 
 def main():
@@ -93,6 +147,7 @@ def main():
         ref = full.step(tok, pos)
         err = float(np.max(np.abs(logits - ref)))
         assert err < 1e-5, (pos, err)
+    expert_parallel_check(rank, world)
     dist.barrier()
     if rank == 0:
         print("DIST_CPU_OK")

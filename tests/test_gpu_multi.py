@@ -1,4 +1,4 @@
-"""Tensor-parallel decode over NCCL on 2+ GPUs: N-GPU result == 1-GPU result.
+"""Tensor-parallel and expert-parallel decode over NCCL on 2+ GPUs: N-GPU result == 1-GPU result.
 Skipped on a single-GPU box (the sharding arithmetic is covered on CPU by test_dist_cpu.py)."""
 import os
 import socket
@@ -37,3 +37,14 @@ def test_tensor_parallel_matches_single_gpu(world):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-5000:]
     assert "TP_GPU_OK" in r.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_matches_single_gpu(world):
+    if gpu_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "ep_gpu_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-5000:]
+    assert "EP_GPU_OK" in r.stdout
