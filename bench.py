@@ -213,16 +213,17 @@ def parallel_mode(args):
 
 
 def workload_config(args, arch_kw, ggml_type, batch, ctx, world):
-    return {"workload": "%s-architecture %s decode, batch %d%s, context %d, fp32 KV, fp32 activations"
+    return {"workload": "%s-architecture %s decode, batch %d%s, context %d, %s KV, fp32 activations"
                         % (args.workload, {8: "Q8_0", 2: "Q4_0"}[ggml_type], batch,
-                           " per GPU" if (world > 1 and parallel_mode(args) == "dp") else "", ctx),
+                           " per GPU" if (world > 1 and parallel_mode(args) == "dp") else "", ctx,
+                           "int8" if getattr(args, "kv", "f32") == "int8" else "fp32"),
             "batch": batch, "context": ctx, "weights": {8: "Q8_0", 2: "Q4_0"}[ggml_type],
             "parallelism": ("%s%d" % (parallel_mode(args), world)) if world > 1 else "single",
             "l2": "inputs larger than L2 (weights streamed once per step)"}
 
 
 def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, steps, warmup, do_e2e=True, do_profile=True,
-                 mode="tp"):
+                 mode="tp", kv="f32"):
     """Builds the synthetic model, fills the context, and measures. Returns a dict of raw numbers.
     mode "tp": one job, weights sharded over the ranks; "dp": every rank holds the whole model and decodes its own
     batch (different prompts), nothing crosses NVLink; the job's tokens/s is the sum."""
@@ -243,7 +244,8 @@ def run_workload(backend, dist, rank, world, arch, ggml_type, seed, batch, ctx, 
     model.finalize()
     prof_steps = 2 if do_profile else 0
     max_ctx = ctx + warmup + steps * (2 if do_e2e else 1) + prof_steps + 8
-    sess = StreamingDecoder(model, max_ctx, batch=batch)
+    from neural_api_b200.backend import TYPE_F32, TYPE_I8
+    sess = StreamingDecoder(model, max_ctx, batch=batch, kv_type=TYPE_I8 if kv == "int8" else TYPE_F32)
     rng = np.random.default_rng(seed + (rank if replicas > 1 else 0))   # every replica / expert-parallel rank has its own prompts
     prompt = rng.integers(0, kw["vocab"], (batch, ctx)).astype(np.int32)
     t0 = time.perf_counter()
@@ -359,6 +361,8 @@ def main():
                     help="N > 1: tp = one job sharded tensor-parallel (strong scaling), dp = one replica with its own batch per GPU "
                          "(weak scaling, no collective on the data path), ep = experts sharded, the job's sequences divided over the "
                          "GPUs (strong scaling); auto = tp for qwen2.5-32b, ep for olmoe-1b-7b, dp for the others")
+    ap.add_argument("--kv", default="f32", choices=["f32", "int8"],
+                    help="KV cache: fp32, or the reference's default int8 rows (codes + one fp32 scale per head and position)")
     ap.add_argument("--no-extra", action="store_true", help="skip the Qwen2.5-0.5B side measurement and the CPU baseline")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -390,7 +394,8 @@ def main():
         uid = parallel.broadcast_bytes(dist, uid, src=0, length=128)
         backend.comm_init(rank, world, uid)
 
-    res = run_workload(backend, dist, rank, world, args.workload, ggml_type, seed, batch, ctx, args.steps, args.warmup, mode=mode)
+    res = run_workload(backend, dist, rank, world, args.workload, ggml_type, seed, batch, ctx, args.steps, args.warmup, mode=mode,
+                       kv=args.kv)
     peak, peak_kind = measured_peak_gbs()
     prof = res["profile"]
     lin_ms, lin_n = prof["linear"]

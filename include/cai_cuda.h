@@ -50,7 +50,9 @@ enum {
   CAI_TYPE_F32 = 0,
   CAI_TYPE_F16 = 1,
   CAI_TYPE_Q4_0 = 2,  /* 18-byte blocks of 32: fp16 d, 16 nibble bytes; x = d*(nib-8)  (neuralgguf.pas:822-845) */
-  CAI_TYPE_Q8_0 = 8   /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
+  CAI_TYPE_Q8_0 = 8,  /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
+  CAI_TYPE_I8 = 24    /* KV cache only: int8 codes + one fp32 scale per (head, position) row, scale = maxabs/127
+                         (neural/neural.cl:2500-2687, TNNetFusedSDPA.BeginIncrementalDecode(MaxCtx, Int8KV = true)) */
 };
 
 /* Activation opcodes of the fused linear epilogue; the numbering of
@@ -233,7 +235,9 @@ int cai_model_step_weight_bytes(cai_model* m, int64_t* out_bytes);
  * :5686-5694 Reset, :5696-5712 StepForward, :5714-5720 TruncateTo, :5759-5843
  * Snapshot/RestoreSnapshot). `batch` independent sequences step together; the
  * reference has one sequence per session, so per-sequence results must equal the
- * single-sequence path. kv_type: CAI_TYPE_F32 (the --kv-fp32 cache). */
+ * single-sequence path. kv_type: CAI_TYPE_F32 (the --kv-fp32 cache) or CAI_TYPE_I8 (the reference's default
+ * int8 cache: rows quantized when appended, scales folded into the attention sums; head_dim 64 or 128, groups of
+ * up to 8 query heads per KV head). */
 int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_session** out);
 int cai_session_destroy(cai_session* s);
 int cai_session_reset(cai_session* s, int seq /* -1 = all */);

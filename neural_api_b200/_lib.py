@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(HERE, "libcai_cuda.so")
 
 CAI_OK = 0
 TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
+TYPE_I8 = 24          # KV cache only: int8 codes + one fp32 scale per row
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 STATUS_NAMES = {0: "CAI_OK", 1: "CAI_ERR_INVALID", 2: "CAI_ERR_CUDA", 3: "CAI_ERR_OOM",
                 4: "CAI_ERR_STATE", 5: "CAI_ERR_UNSUPPORTED", 6: "CAI_ERR_COMM"}

@@ -19,7 +19,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import CaiError, LlamaConfigC, TYPE_F16, TYPE_F32, TYPE_Q4_0, TYPE_Q8_0  # noqa: F401
+from ._lib import CaiError, LlamaConfigC, TYPE_F16, TYPE_F32, TYPE_I8, TYPE_Q4_0, TYPE_Q8_0  # noqa: F401
 
 
 def _ptr(a):
@@ -368,6 +368,7 @@ class StreamingDecoder:
     """KV-cached decode session over `batch` independent sequences."""
 
     def __init__(self, model, max_context, batch=1, kv_type=TYPE_F32):
+        """kv_type: TYPE_F32, or TYPE_I8 for the reference's int8 cache (BeginIncrementalDecode(MaxCtx, Int8KV))."""
         self.model, self.backend, self.batch = model, model.backend, batch
         self.vocab = model.cfg.vocab
         h = C.c_void_p()

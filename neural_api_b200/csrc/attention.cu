@@ -12,7 +12,7 @@
 //                 order. Scores are scaled by 1/sqrt(hd) after the dot product and
 //                 the sum is divided once at the end, as in the reference kernel.
 //   combine     : merges the per-split partial states.
-#include "cai_common.cuh"
+#include "gemv_common.cuh"      // packed fp32x2 arithmetic
 #include <math.h>
 
 struct AttnParams {
@@ -26,6 +26,7 @@ struct AttnParams {
   float* partial; int nsplit;
   float inv_sqrt_d;
   int min_chunk;          // fewest cached rows a context split covers (set by the launcher for the kernel it picked)
+  int8_t* k_codes; int8_t* v_codes; float* k_scales; float* v_scales;     // int8 cache (k_codes != NULL)
 };
 
 // Rows per context split: the context spread over nsplit splits, at least min_chunk rows, a multiple of 32.
@@ -88,6 +89,87 @@ __global__ void rope_append_kernel(const AttnParams p) {
   for (int c = threadIdx.x; c < kw; c += blockDim.x) {
     const int g = c / hd, d = c % hd;
     p.v_cache[(((int64_t)b * p.kv_heads + g) * p.max_ctx + slot) * hd + d] = row[qw + kw + c];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RoPE + append into the int8 KV cache. Same front end as rope_append_kernel (optional full-width q/k norm, Q
+// rotated in place); the rotated K row and the V row of the token are staged in shared memory, then one warp per
+// (kv head, K|V) quantizes its row in the reference's cache format: one symmetric fp32 scale per row,
+// scale = maxabs / 127 over the finite magnitudes, code = clamp(rint(v * (1 / maxabs) * 127), -127, 127) with the
+// multiplications in that order and round-half-to-even; a zero or denormal row maximum gives zero codes and
+// scale 1; NaN -> 0, infinities clamp.
+// ---------------------------------------------------------------------------
+__global__ void rope_append_int8_kernel(const AttnParams p) {
+  extern __shared__ float kv_s[];                    // [kw] rotated K, then [kw] V
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const int hd = p.head_dim;
+  const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
+  float* row = p.qkv + (int64_t)b * p.ld;
+  const int slot = p.cache_len[b];
+  if (slot >= p.max_ctx) return;
+  float inv_q = 1.f, inv_k = 1.f;
+  if (p.q_norm) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < qw; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+    ss = block_sum(ss, red);
+    inv_q = 1.0f / sqrtf(ss / (float)qw + p.eps);
+    ss = 0.f;
+    for (int c = threadIdx.x; c < kw; c += blockDim.x) ss = fmaf(row[qw + c], row[qw + c], ss);
+    ss = block_sum(ss, red);
+    inv_k = 1.0f / sqrtf(ss / (float)kw + p.eps);
+  }
+  const int pos = p.pos ? p.pos[b] : slot;
+  const int half_hd = hd >> 1;
+  for (int pr = threadIdx.x; pr < (qw >> 1); pr += blockDim.x) {
+    float x0 = row[2 * pr], x1 = row[2 * pr + 1];
+    if (p.q_norm) { x0 = p.q_norm[2 * pr] * (x0 * inv_q); x1 = p.q_norm[2 * pr + 1] * (x1 * inv_q); }
+    if (p.theta) {
+      float s, c;
+      sincosf((float)pos * p.theta[pr % half_hd], &s, &c);
+      const float y0 = c * x0 - s * x1, y1 = s * x0 + c * x1;
+      x0 = y0; x1 = y1;
+    }
+    row[2 * pr] = x0; row[2 * pr + 1] = x1;
+  }
+  for (int pr = threadIdx.x; pr < (kw >> 1); pr += blockDim.x) {
+    float x0 = row[qw + 2 * pr], x1 = row[qw + 2 * pr + 1];
+    if (p.k_norm) { x0 = p.k_norm[2 * pr] * (x0 * inv_k); x1 = p.k_norm[2 * pr + 1] * (x1 * inv_k); }
+    if (p.theta) {
+      float s, c;
+      sincosf((float)pos * p.theta[pr % half_hd], &s, &c);
+      const float y0 = c * x0 - s * x1, y1 = s * x0 + c * x1;
+      x0 = y0; x1 = y1;
+    }
+    kv_s[2 * pr] = x0; kv_s[2 * pr + 1] = x1;
+  }
+  for (int c = threadIdx.x; c < kw; c += blockDim.x) kv_s[kw + c] = row[qw + kw + c];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int task = warp; task < 2 * p.kv_heads; task += nwarps) {
+    const int part = task / p.kv_heads, g = task - part * p.kv_heads;     // part 0 = K, 1 = V
+    const float* src = kv_s + (size_t)part * kw + (size_t)g * hd;
+    float m = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      const float a = fabsf(src[d]);
+      if (__float_as_uint(a) <= 0x7F7FFFFFu) m = fmaxf(m, a);            // finite magnitudes only
+    }
+    m = warp_max(m);
+    const bool usable = __float_as_uint(m) >= 0x00800000u;                // a normal number
+    const float row_scale = usable ? (m / 127.0f) : 1.0f;
+    const float recip = usable ? (1.0f / m) : 0.0f;
+    const int64_t rowi = ((int64_t)b * p.kv_heads + g) * p.max_ctx + slot;
+    int8_t* codes = (part == 0 ? p.k_codes : p.v_codes) + rowi * hd;
+    if (lane == 0) (part == 0 ? p.k_scales : p.v_scales)[rowi] = row_scale;
+    for (int d = lane; d < hd; d += 32) {
+      const float v = src[d];
+      float scaled = v * recip * 127.0f;
+      if (__float_as_uint(fabsf(v)) > 0x7F800000u) scaled = 0.f;          // NaN
+      codes[d] = (int8_t)fminf(fmaxf(rintf(scaled), -127.0f), 127.0f);
+    }
   }
 }
 
@@ -289,6 +371,7 @@ constexpr int ATTN_TILE_MIN_CHUNK = 128;   // 4 warps x one tile of 32 rows
 template <int G, int HD>
 __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(const AttnParams p) {
   constexpr int DPL = HD / 32;                         // channels per lane in the P.V phase
+  constexpr int DP2 = DPL / 2;                         // ... as packed pairs
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -301,15 +384,185 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
   const int j_begin = split * chunk;
   int j_end = j_begin + chunk; if (j_end > n) j_end = n;
 
-  float* q_s = smem;                                   // [G][HD]
-  float* p_s = q_s + G * HD + (size_t)warp * G * 32;   // this warp's [G][32] probabilities
-  float* merge_s = smem + G * HD + ATTN_WARPS * G * 32;   // [ATTN_WARPS][G][HD + 2]
+  // All multiply-adds are packed pairs (fma.rn.f32x2: two IEEE fp32 FMAs per instruction), which halves the
+  // instruction count of both products; the probabilities are kept in shared memory as (p, p) pairs for that.
+  float* q_s = smem;                                                   // [G][HD]
+  f32x2_t* p_s = (f32x2_t*)(q_s + G * HD) + (size_t)warp * G * 32;     // this warp's [G][32] pairs (p, p)
+  float* merge_s = smem + G * HD + ATTN_WARPS * G * 64;                // [ATTN_WARPS][G][HD + 2]
   const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * HD;
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x) q_s[i] = qrow[i];
   __syncthreads();
 
   const float* kbase = p.k_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
   const float* vbase = p.v_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+
+  float m[G], l[G];
+  f32x2_t acc[G][DP2];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DP2; ++d) acc[h][d] = 0ull;
+  }
+
+  for (int tile = j_begin + warp * 32; tile < j_end; tile += ATTN_WARPS * 32) {
+    // ---- Q.K, lane = row (rows past the end re-read the last row and are masked below)
+    const int j = tile + lane;
+    const bool valid = j < j_end;
+    const ulonglong2* krow = (const ulonglong2*)(kbase + (int64_t)(valid ? j : j_end - 1) * HD);
+    f32x2_t s2[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) s2[h] = 0ull;
+    // 64 channels (two 128-byte lines of the row, 16 loads in flight) at a time: few dependent round trips to HBM
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c) {
+      ulonglong2 k[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) k[i] = krow[c * 16 + i];
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        const ulonglong2* q2 = (const ulonglong2*)(q_s + h * HD + c * 64);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const ulonglong2 q = q2[i];
+          s2[h] = fma2(q.x, k[i].x, s2[h]);
+          s2[h] = fma2(q.y, k[i].y, s2[h]);
+        }
+      }
+    }
+    // ---- P.V, lane = DPL channels. The V rows do not depend on the softmax, so the first half of the tile's rows
+    //      is requested before it (masked rows re-read the last row and carry probability 0)
+    const int last = j_end - 1 - tile;                 // index of the tile's last valid row, >= 0
+    f32x2_t v[16][DP2];
+    auto load_v = [&](int base) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const int r = (base + t <= last) ? (base + t) : last;
+        const float* vrow = vbase + (int64_t)(tile + r) * HD + lane * DPL;
+        if (DPL == 4) {
+          const ulonglong2 x = *(const ulonglong2*)vrow;
+          v[t][0] = x.x; v[t][DP2 - 1] = x.y;
+        } else {
+          v[t][0] = *(const f32x2_t*)vrow;
+        }
+      }
+    };
+    auto use_v = [&](int base) {
+#pragma unroll
+      for (int t2 = 0; t2 < 16; t2 += 2) {
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const ulonglong2 pr = *(const ulonglong2*)(p_s + h * 32 + base + t2);   // (p, p) of two rows
+#pragma unroll
+          for (int d = 0; d < DP2; ++d) {
+            acc[h][d] = fma2(pr.x, v[t2 + 0][d], acc[h][d]);
+            acc[h][d] = fma2(pr.y, v[t2 + 1][d], acc[h][d]);
+          }
+        }
+      }
+    };
+    load_v(0);
+    // ---- softmax terms of the tile, once per row
+    __syncwarp();                                      // the previous tile's probabilities have been consumed
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float sc = valid ? sum2(s2[h]) * p.inv_sqrt_d : -INFINITY;
+      const float mnew = fmaxf(m[h], warp_max(sc));    // finite: the tile holds at least one row
+      const float pj = valid ? expf(sc - mnew) : 0.f;
+      const float psum = warp_sum(pj);
+      const float corr = expf(m[h] - mnew);            // 0 on the first tile (m = -inf)
+      l[h] = l[h] * corr + psum;
+      m[h] = mnew;
+      const f32x2_t corr2 = pack2(corr, corr);
+#pragma unroll
+      for (int d = 0; d < DP2; ++d) acc[h][d] = fma2(acc[h][d], corr2, 0ull);
+      p_s[h * 32 + lane] = pack2(pj, pj);
+    }
+    __syncwarp();
+    use_v(0);
+    if (last >= 16) {
+      load_v(16);
+      use_v(16);
+    }
+  }
+  // ---- warps -> shared memory -> one state per head (a warp that had no tile contributes m = -inf, l = 0)
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
+    if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
+#pragma unroll
+    for (int d = 0; d < DP2; ++d) {
+      float lo, hi;
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[h][d]));
+      dst[2 + lane * DPL + 2 * d] = lo;
+      dst[2 + lane * DPL + 2 * d + 1] = hi;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int hh = idx / HD, d = idx % HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
+    float lt = 0.f, at = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATTN_WARPS; ++w) {
+      const float* src = merge_s + ((size_t)w * G + hh) * (HD + 2);
+      const float sc = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mx);
+      lt += src[1] * sc;
+      at += src[2 + d] * sc;
+    }
+    const int h = g * G + hh;
+    if (used == 1) {
+      p.out[(int64_t)b * p.ldo + (int64_t)h * HD + d] = (lt > 0.f) ? at / lt : 0.f;
+    } else {
+      float* dst = p.partial + (((int64_t)b * p.q_heads + h) * p.nsplit + split) * (HD + 2);
+      if (d == 0) { dst[0] = mx; dst[1] = lt; }
+      dst[2 + d] = at;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The tiled decode kernel over the int8 KV cache (the reference's cai_sdpa_decode_int8 arithmetic): the codes go
+// straight into the dot products and each row's scale enters once, outside the element loop:
+//   score_j = (sum_d q_d * kcode_jd) * (kscale_j / sqrt(hd)),   out = sum_j (p_j * vscale_j) * vcode_j / sum_j p_j.
+// A row is 64 or 128 bytes of codes plus one scale, a quarter of the fp32 cache's traffic. Same tiling as the fp32
+// kernel: lane = row for Q.K (the row's codes in 16-byte loads, converted exactly through the 2^23 constant),
+// lane = 2 or 4 channels for P.V (one 2- or 4-byte load per row).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float s8_to_float(uint32_t w_xor80, int i) {
+  // byte i of a word whose bytes were XOR-ed with 0x80: (0x4B000000 | u) is 8388608 + u, minus 8388736 leaves the int8
+  return __uint_as_float(__byte_perm(w_xor80, 0x4B000000u, 0x7650u + (uint32_t)i)) - 8388736.0f;
+}
+
+template <int G, int HD>
+__global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kernel(const AttnParams p) {
+  constexpr int DPL = HD / 32;
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = p.cache_len[b] + 1;
+  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
+  const int used = (n + chunk - 1) / chunk;
+  if (split >= used) return;
+  const int j_begin = split * chunk;
+  int j_end = j_begin + chunk; if (j_end > n) j_end = n;
+
+  float* q_s = smem;                                   // [G][HD]
+  float* p_s = q_s + G * HD + (size_t)warp * G * 32;   // this warp's [G][32] probabilities x value scales
+  float* merge_s = smem + G * HD + ATTN_WARPS * G * 32;
+  const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * HD;
+  for (int i = threadIdx.x; i < G * HD; i += blockDim.x) q_s[i] = qrow[i];
+  __syncthreads();
+
+  const int64_t plane = ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx;
+  const int8_t* kbase = p.k_codes + plane * HD;
+  const int8_t* vbase = p.v_codes + plane * HD;
+  const float* ksc = p.k_scales + plane;
+  const float* vsc = p.v_scales + plane;
 
   float m[G], l[G], acc[G][DPL];
 #pragma unroll
@@ -320,88 +573,82 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
   }
 
   for (int tile = j_begin + warp * 32; tile < j_end; tile += ATTN_WARPS * 32) {
-    // ---- Q.K, lane = row (rows past the end re-read the last row and are masked below)
     const int j = tile + lane;
     const bool valid = j < j_end;
-    const float4* krow = (const float4*)(kbase + (int64_t)(valid ? j : j_end - 1) * HD);
+    const int jr = valid ? j : j_end - 1;              // rows past the end re-read the last row and are masked
+    const uint4* krow = (const uint4*)(kbase + (int64_t)jr * HD);
+    const float kscale = ksc[jr] * p.inv_sqrt_d;
+    const float vscale = vsc[jr];
     float s[G];
 #pragma unroll
     for (int h = 0; h < G; ++h) s[h] = 0.f;
-    // 64 channels (two 128-byte lines of the row, 16 loads in flight) at a time: few dependent round trips to HBM
+    uint4 kw[HD / 16];
 #pragma unroll
-    for (int c = 0; c < HD / 64; ++c) {
-      float4 k[16];
+    for (int i = 0; i < HD / 16; ++i) kw[i] = krow[i];   // the whole row of codes in flight
 #pragma unroll
-      for (int i = 0; i < 16; ++i) k[i] = krow[c * 16 + i];
+    for (int i = 0; i < HD / 16; ++i) {
+      const uint32_t w4[4] = {kw[i].x ^ 0x80808080u, kw[i].y ^ 0x80808080u, kw[i].z ^ 0x80808080u, kw[i].w ^ 0x80808080u};
+      float kf[16];
+#pragma unroll
+      for (int t = 0; t < 16; ++t) kf[t] = s8_to_float(w4[t >> 2], t & 3);
 #pragma unroll
       for (int h = 0; h < G; ++h) {
-        const float4* q4 = (const float4*)(q_s + h * HD + c * 64);
+        const float4* q4 = (const float4*)(q_s + h * HD + i * 16);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float4 q = q4[i];
-          s[h] = fmaf(q.x, k[i].x, s[h]); s[h] = fmaf(q.y, k[i].y, s[h]);
-          s[h] = fmaf(q.z, k[i].z, s[h]); s[h] = fmaf(q.w, k[i].w, s[h]);
+        for (int t = 0; t < 4; ++t) {
+          const float4 q = q4[t];
+          s[h] = fmaf(q.x, kf[4 * t + 0], s[h]); s[h] = fmaf(q.y, kf[4 * t + 1], s[h]);
+          s[h] = fmaf(q.z, kf[4 * t + 2], s[h]); s[h] = fmaf(q.w, kf[4 * t + 3], s[h]);
         }
       }
     }
-    // ---- P.V, lane = DPL channels. The V rows do not depend on the softmax, so the first half of the tile's rows
-    //      is requested before it (masked rows re-read the last row and carry probability 0)
-    const int last = j_end - 1 - tile;                 // index of the tile's last valid row, >= 0
-    float v[16][DPL];
-    auto load_v = [&](int base) {
+    // the tile's V codes: lane = DPL channels, 32 rows (masked rows re-read the last row and carry probability 0)
+    const int last = j_end - 1 - tile;
+    uint32_t vw[32];
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        const int r = (base + t <= last) ? (base + t) : last;
-        const float* vrow = vbase + (int64_t)(tile + r) * HD + lane * DPL;
-        if (DPL == 4) {
-          const float4 x = *(const float4*)vrow;
-          v[t][0] = x.x; v[t][1] = x.y; v[t][2 % DPL] = x.z; v[t][3 % DPL] = x.w;
-        } else {
-          const float2 x = *(const float2*)vrow;
-          v[t][0] = x.x; v[t][1] = x.y;
-        }
-      }
-    };
-    auto use_v = [&](int base) {
-#pragma unroll
-      for (int t4 = 0; t4 < 16; t4 += 4) {
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-          const float4 pr = *(const float4*)(p_s + h * 32 + base + t4);
-#pragma unroll
-          for (int d = 0; d < DPL; ++d) {
-            float a = acc[h][d];
-            a = fmaf(pr.x, v[t4 + 0][d], a); a = fmaf(pr.y, v[t4 + 1][d], a);
-            a = fmaf(pr.z, v[t4 + 2][d], a); a = fmaf(pr.w, v[t4 + 3][d], a);
-            acc[h][d] = a;
-          }
-        }
-      }
-    };
-    load_v(0);
-    // ---- softmax terms of the tile, once per row
-    __syncwarp();                                      // the previous tile's probabilities have been consumed
+    for (int t = 0; t < 32; ++t) {
+      const int r = (t <= last) ? t : last;
+      const int8_t* vrow = vbase + (int64_t)(tile + r) * HD + lane * DPL;
+      vw[t] = (DPL == 4) ? *(const uint32_t*)vrow : (uint32_t)*(const unsigned short*)vrow;
+    }
+    __syncwarp();
 #pragma unroll
     for (int h = 0; h < G; ++h) {
-      const float sc = valid ? s[h] * p.inv_sqrt_d : -INFINITY;
-      const float mnew = fmaxf(m[h], warp_max(sc));    // finite: the tile holds at least one row
+      const float sc = valid ? s[h] * kscale : -INFINITY;
+      const float mnew = fmaxf(m[h], warp_max(sc));
       const float pj = valid ? expf(sc - mnew) : 0.f;
       const float psum = warp_sum(pj);
-      const float corr = expf(m[h] - mnew);            // 0 on the first tile (m = -inf)
+      const float corr = expf(m[h] - mnew);
       l[h] = l[h] * corr + psum;
       m[h] = mnew;
 #pragma unroll
       for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
-      p_s[h * 32 + lane] = pj;
+      p_s[h * 32 + lane] = pj * vscale;                 // the value scale rides with the probability
     }
     __syncwarp();
-    use_v(0);
-    if (last >= 16) {
-      load_v(16);
-      use_v(16);
+#pragma unroll
+    for (int t4 = 0; t4 < 32; t4 += 4) {
+      if (t4 > last) break;
+      float vf[4][DPL];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t w = vw[t4 + t] ^ 0x80808080u;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) vf[t][d] = s8_to_float(w, d);
+      }
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        const float4 pr = *(const float4*)(p_s + h * 32 + t4);
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) {
+          float a = acc[h][d];
+          a = fmaf(pr.x, vf[0][d], a); a = fmaf(pr.y, vf[1][d], a);
+          a = fmaf(pr.z, vf[2][d], a); a = fmaf(pr.w, vf[3][d], a);
+          acc[h][d] = a;
+        }
+      }
     }
   }
-  // ---- warps -> shared memory -> one state per head (a warp that had no tile contributes m = -inf, l = 0)
 #pragma unroll
   for (int h = 0; h < G; ++h) {
     float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
@@ -431,6 +678,20 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
       if (d == 0) { dst[0] = mx; dst[1] = lt; }
       dst[2 + d] = at;
     }
+  }
+}
+
+template <int HD>
+static void launch_tile_int8(cai_ctx* ctx, int G, dim3 grid, size_t smem, const AttnParams& p) {
+  switch (G) {
+    case 1: pdl_launch(ctx, attn_decode_tile_int8_kernel<1, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 2: pdl_launch(ctx, attn_decode_tile_int8_kernel<2, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 3: pdl_launch(ctx, attn_decode_tile_int8_kernel<3, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 4: pdl_launch(ctx, attn_decode_tile_int8_kernel<4, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 5: pdl_launch(ctx, attn_decode_tile_int8_kernel<5, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 6: pdl_launch(ctx, attn_decode_tile_int8_kernel<6, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    case 7: pdl_launch(ctx, attn_decode_tile_int8_kernel<7, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
+    default: pdl_launch(ctx, attn_decode_tile_int8_kernel<8, HD>, grid, dim3(ATTN_WARPS * 32), smem, p); break;
   }
 }
 
@@ -496,12 +757,25 @@ static AttnParams to_params(const AttnArgs& a) {
   p.out = a.out; p.ldo = a.ldo; p.partial = a.partial; p.nsplit = a.nsplit;
   p.inv_sqrt_d = (float)(1.0 / sqrt((double)a.head_dim));
   p.min_chunk = ATTN_MIN_CHUNK;
+  p.k_codes = a.k_codes; p.v_codes = a.v_codes; p.k_scales = a.k_scales; p.v_scales = a.v_scales;
   return p;
+}
+
+// true when the int8 KV cache can serve this shape (the tiled kernels only)
+bool attn_int8_supported(int q_heads, int kv_heads, int head_dim) {
+  return kv_heads > 0 && (q_heads % kv_heads) == 0 && (q_heads / kv_heads) <= 8 && (head_dim == 64 || head_dim == 128);
 }
 
 int attn_rope_append(cai_ctx* ctx, const AttnArgs& a) {
   ctx->cur_family = FAM_ATTN;
   if (a.head_dim % 2) return cai_fail(ctx, CAI_ERR_INVALID, "head_dim must be even");
+  if (a.k_codes) {
+    const size_t smem = (size_t)2 * a.kv_heads * a.head_dim * sizeof(float);
+    if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 KV append: %d kv heads x %d dims exceed shared memory", a.kv_heads, a.head_dim);
+    pdl_launch(ctx, rope_append_int8_kernel, dim3(a.batch), dim3(256), smem, to_params(a));
+    CAI_LAUNCHED(ctx);
+    return CAI_OK;
+  }
   pdl_launch(ctx, rope_append_kernel, dim3(a.batch), dim3(256), 0, to_params(a));
   CAI_LAUNCHED(ctx);
   return CAI_OK;
@@ -518,9 +792,24 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
   AttnParams p = to_params(a);
   dim3 grid(a.kv_heads, a.nsplit, a.batch);
   static const int use_tile = [] { const char* e = getenv("CAI_ATTN_TILE"); return (e && *e) ? atoi(e) : 1; }();
-  if (use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8) {
+  if (a.k_codes) {
+    if (!attn_int8_supported(a.q_heads, a.kv_heads, a.head_dim))
+      return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 KV cache: head_dim 64 or 128 and groups of up to 8 query heads");
     p.min_chunk = ATTN_TILE_MIN_CHUNK;
     const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 32 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
+    if (a.head_dim == 128) launch_tile_int8<128>(ctx, G, grid, tsmem, p);
+    else launch_tile_int8<64>(ctx, G, grid, tsmem, p);
+    CAI_LAUNCHED(ctx);
+    if (a.nsplit > 1) {
+      dim3 cgrid(a.q_heads, a.batch);
+      pdl_launch(ctx, attn_combine_kernel, cgrid, dim3(128), 0, p);
+      CAI_LAUNCHED(ctx);
+    }
+    return CAI_OK;
+  }
+  if (use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8) {
+    p.min_chunk = ATTN_TILE_MIN_CHUNK;
+    const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 64 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
     if (a.head_dim == 128) launch_tile<128>(ctx, G, grid, tsmem, p);
     else launch_tile<64>(ctx, G, grid, tsmem, p);
     CAI_LAUNCHED(ctx);

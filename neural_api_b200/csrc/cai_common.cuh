@@ -224,9 +224,16 @@ struct AttnArgs {
   int64_t ldo = 0;
   float* partial = nullptr;     // scratch: [B][q_heads][nsplit][hd + 2]
   int nsplit = 1;
+  // int8 KV cache (set k_codes to use it; k_cache / v_cache are then ignored): codes [B][kv_heads][max_ctx][hd],
+  // one fp32 scale per (sequence, kv head, position) row [B][kv_heads][max_ctx]
+  int8_t* k_codes = nullptr;
+  int8_t* v_codes = nullptr;
+  float* k_scales = nullptr;
+  float* v_scales = nullptr;
 };
 int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx);
 size_t attn_partial_floats(int batch, int q_heads, int nsplit, int head_dim);
+bool attn_int8_supported(int q_heads, int kv_heads, int head_dim);
 int attn_rope_append(cai_ctx* ctx, const AttnArgs& a);
 int attn_decode(cai_ctx* ctx, const AttnArgs& a);
 

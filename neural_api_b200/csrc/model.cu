@@ -573,9 +573,15 @@ struct cai_session {
   cai_model* m;
   cai_ctx* ctx;
   int max_ctx, batch;
-  float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][max_ctx][hd]
+  float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][max_ctx][hd]; int8 codes when kv_int8
   float *k_snap = nullptr, *v_snap = nullptr;
-  size_t layer_stride = 0;                            // floats per layer
+  size_t layer_stride = 0;                            // elements per layer
+  bool kv_int8 = false;                               // the reference's int8 cache: codes above + one fp32 scale per row
+  float *k_scales = nullptr, *v_scales = nullptr;     // [layers][B][kv_heads_l][max_ctx]
+  float *k_scales_snap = nullptr, *v_scales_snap = nullptr;
+  size_t scale_stride = 0;                            // scales per layer
+  size_t cache_bytes() const { return layer_stride * (size_t)m->cfg.layers * (kv_int8 ? 1 : 4); }
+  size_t scale_bytes() const { return scale_stride * (size_t)m->cfg.layers * 4; }
   int32_t *tokens_dev = nullptr, *pos_dev = nullptr, *len_dev = nullptr;
   int32_t* io_pinned = nullptr;                       // [3][B] tokens, pos, len
   std::vector<int32_t> len_host, len_snap;
@@ -662,7 +668,9 @@ static int enqueue_step(cai_session* s) {
   // Batches the dispatcher sends to the tensor-core GEMM (9..64 rows; 3..8 on large matrices) get plain epilogues
   // only: RoPE/append and SwiGLU then run as their own kernels.
   const bool tc_batch = linear_uses_tensor_cores(&m->layers[0].wgu, B) || linear_uses_tensor_cores(&m->layers[0].wqkv, B);
-  const bool fuse_rope = !c.qk_norm && !tc_batch;     // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first
+  // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first, the batch runs on the
+  // tensor cores, or the cache is int8 (a row's scale needs the whole row)
+  const bool fuse_rope = !c.qk_norm && !tc_batch && !s->kv_int8;
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
     if (linear_can_fuse_norm(&L.wqkv, B)) {
@@ -679,7 +687,12 @@ static int enqueue_step(cai_session* s) {
     {
       AttnArgs a;
       a.qkv = s->qkv; a.ld = QKVW;
-      a.k_cache = s->k_cache + (size_t)l * s->layer_stride; a.v_cache = s->v_cache + (size_t)l * s->layer_stride;
+      if (s->kv_int8) {
+        a.k_codes = (int8_t*)s->k_cache + (size_t)l * s->layer_stride; a.v_codes = (int8_t*)s->v_cache + (size_t)l * s->layer_stride;
+        a.k_scales = s->k_scales + (size_t)l * s->scale_stride; a.v_scales = s->v_scales + (size_t)l * s->scale_stride;
+      } else {
+        a.k_cache = s->k_cache + (size_t)l * s->layer_stride; a.v_cache = s->v_cache + (size_t)l * s->layer_stride;
+      }
       a.cache_len_dev = s->len_dev; a.batch = B; a.q_heads = m->heads_l; a.kv_heads = m->kv_heads_l;
       a.head_dim = c.head_dim; a.max_ctx = s->max_ctx; a.theta = m->theta; a.pos_dev = s->pos_dev;
       a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
@@ -869,7 +882,8 @@ int cai_session_destroy(cai_session* s) {
                   s->att, s->act, s->gu, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
                   s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf,
                   s->tile_expert, s->tile_pairs, s->moe_gu, s->moe_unscale, s->moe_xp,
-                  s->ep_pack, s->ep_all, s->ep_gates, s->ep_part, s->ep_mine, s->ep_ids};
+                  s->ep_pack, s->ep_all, s->ep_gates, s->ep_part, s->ep_mine, s->ep_ids,
+                  s->k_scales, s->v_scales, s->k_scales_snap, s->v_scales_snap};
   for (void* p : bufs) if (p) cudaFree(p);
   if (s->io_pinned) cudaFreeHost(s->io_pinned);
   s->m->sessions -= 1;
@@ -885,10 +899,14 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   *out = nullptr;
   if (!m->finalized) return cai_fail(ctx, CAI_ERR_STATE, "call cai_model_finalize before creating sessions");
   if (max_ctx < 1 || batch < 1 || batch > 1024) return cai_fail(ctx, CAI_ERR_INVALID, "max_ctx %d batch %d", max_ctx, batch);
-  if (kv_type != CAI_TYPE_F32) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "only the fp32 KV cache is built");
+  if (kv_type != CAI_TYPE_F32 && kv_type != CAI_TYPE_I8) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "KV cache type %d: fp32 (0) or int8 (24)", kv_type);
   const cai_llama_config& c = m->cfg;
+  const bool kv_int8 = kv_type == CAI_TYPE_I8;
+  if (kv_int8 && !attn_int8_supported(m->heads_l, m->kv_heads_l, c.head_dim))
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "the int8 KV cache needs head_dim 64 or 128 and at most 8 query heads per KV head");
   const size_t layer_stride = (size_t)batch * m->kv_heads_l * max_ctx * c.head_dim;
-  const size_t cache_bytes = layer_stride * (size_t)c.layers * 4;
+  const size_t scale_stride = (size_t)batch * m->kv_heads_l * max_ctx;
+  const size_t cache_bytes = layer_stride * (size_t)c.layers * (kv_int8 ? 1 : 4) + (kv_int8 ? scale_stride * (size_t)c.layers * 4 : 0);
   size_t free_b = 0, total_b = 0;
   CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
   if (2 * cache_bytes + ((size_t)256 << 20) > free_b)
@@ -896,6 +914,7 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   cai_session* s = new (std::nothrow) cai_session();
   if (!s) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
   s->m = m; s->ctx = ctx; s->max_ctx = max_ctx; s->batch = batch; s->layer_stride = layer_stride;
+  s->kv_int8 = kv_int8; s->scale_stride = scale_stride;
   s->len_host.assign((size_t)batch, 0);
   m->sessions += 1;
   const char* ng = getenv("CAI_NO_GRAPH");
@@ -905,7 +924,8 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   s->trace_cap = (int64_t)max_ctx * B;
   bool ok = true;
   auto A = [&](void** p, size_t bytes) { if (ok && cudaMalloc(p, bytes ? bytes : 4) != cudaSuccess) { cudaGetLastError(); ok = false; } };
-  A((void**)&s->k_cache, cache_bytes); A((void**)&s->v_cache, cache_bytes);
+  A((void**)&s->k_cache, s->cache_bytes()); A((void**)&s->v_cache, s->cache_bytes());
+  if (kv_int8) { A((void**)&s->k_scales, s->scale_bytes()); A((void**)&s->v_scales, s->scale_bytes()); }
   A((void**)&s->tokens_dev, (size_t)B * 4); A((void**)&s->pos_dev, (size_t)B * 4); A((void**)&s->len_dev, (size_t)B * 4);
   A((void**)&s->x, (size_t)B * H * 4); A((void**)&s->x_alt, (size_t)B * H * 4); A((void**)&s->h, (size_t)B * H * 4);
   A((void**)&s->qkv, (size_t)B * QKVW * 4); A((void**)&s->att, (size_t)B * m->qw_l * 4);
@@ -1131,16 +1151,24 @@ int cai_session_snapshot(cai_session* s) {
   if (!s) return CAI_ERR_INVALID;
   cai_ctx* ctx = s->ctx;
   CAI_TRY(cai_bind(ctx));
-  const size_t bytes = s->layer_stride * (size_t)s->m->cfg.layers * 4;
+  const size_t bytes = s->cache_bytes(), sbytes = s->kv_int8 ? s->scale_bytes() : 0;
   if (!s->k_snap) {
     size_t free_b = 0, total_b = 0;
     CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
-    if (2 * bytes + ((size_t)64 << 20) > free_b) return cai_fail(ctx, CAI_ERR_OOM, "snapshot of %zu bytes does not fit", 2 * bytes);
+    if (2 * (bytes + sbytes) + ((size_t)64 << 20) > free_b) return cai_fail(ctx, CAI_ERR_OOM, "snapshot of %zu bytes does not fit", 2 * (bytes + sbytes));
     CAI_CUDA(ctx, cudaMalloc((void**)&s->k_snap, bytes));
     CAI_CUDA(ctx, cudaMalloc((void**)&s->v_snap, bytes));
+    if (sbytes) {
+      CAI_CUDA(ctx, cudaMalloc((void**)&s->k_scales_snap, sbytes));
+      CAI_CUDA(ctx, cudaMalloc((void**)&s->v_scales_snap, sbytes));
+    }
   }
   CAI_CUDA(ctx, cudaMemcpyAsync(s->k_snap, s->k_cache, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   CAI_CUDA(ctx, cudaMemcpyAsync(s->v_snap, s->v_cache, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  if (sbytes) {
+    CAI_CUDA(ctx, cudaMemcpyAsync(s->k_scales_snap, s->k_scales, sbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    CAI_CUDA(ctx, cudaMemcpyAsync(s->v_scales_snap, s->v_scales, sbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  }
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   s->len_snap = s->len_host;
   s->have_snap = true;
@@ -1152,9 +1180,13 @@ int cai_session_restore(cai_session* s) {
   cai_ctx* ctx = s->ctx;
   CAI_TRY(cai_bind(ctx));
   if (!s->have_snap) return cai_fail(ctx, CAI_ERR_STATE, "no snapshot to restore");
-  const size_t bytes = s->layer_stride * (size_t)s->m->cfg.layers * 4;
+  const size_t bytes = s->cache_bytes();
   CAI_CUDA(ctx, cudaMemcpyAsync(s->k_cache, s->k_snap, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   CAI_CUDA(ctx, cudaMemcpyAsync(s->v_cache, s->v_snap, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  if (s->kv_int8) {
+    CAI_CUDA(ctx, cudaMemcpyAsync(s->k_scales, s->k_scales_snap, s->scale_bytes(), cudaMemcpyDeviceToDevice, ctx->stream));
+    CAI_CUDA(ctx, cudaMemcpyAsync(s->v_scales, s->v_scales_snap, s->scale_bytes(), cudaMemcpyDeviceToDevice, ctx->stream));
+  }
   s->len_host = s->len_snap;
   return push_len(s);
 }
@@ -1169,7 +1201,9 @@ int cai_session_last_kv_bytes(cai_session* s, int64_t* out_bytes) {
   if (!s || !out_bytes) return CAI_ERR_INVALID;
   int64_t rows = 0;
   for (int l : s->len_host) rows += l;
-  *out_bytes = rows * 2 * (int64_t)s->m->kw_l * 4 * (int64_t)s->m->cfg.layers;
+  // per cached row and layer: K and V, head_dim values (4 bytes, or 1 byte + a 4-byte scale per head in the int8 cache)
+  const int64_t per_row = s->kv_int8 ? (int64_t)s->m->kw_l + 4 * (int64_t)s->m->kv_heads_l : (int64_t)s->m->kw_l * 4;
+  *out_bytes = rows * 2 * per_row * (int64_t)s->m->cfg.layers;
   return CAI_OK;
 }
 

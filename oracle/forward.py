@@ -245,16 +245,43 @@ def softmax_row(x):
     return e / np.sum(e, dtype=x.dtype)
 
 
+def quantize_cache_row(row):
+    """The int8 KV-cache row format (neural/neural.cl:2500-2581, the device twin of
+    TNNetScaledDotProductAttention.QuantizeCacheRow): one symmetric fp32 scale per (head, position) row,
+    scale = maxabs / 127 over the finite magnitudes, codes = clamp(rint(v * (1 / maxabs) * 127), -127, 127) with
+    round-half-to-even, multiplied in that order; a row whose maximum is zero or denormal gives zero codes and scale 1;
+    NaN -> 0, infinities clamp. Returns (int8 codes, fp32 scale)."""
+    v = np.asarray(row, dtype=np.float32)
+    a = np.abs(v)
+    finite = np.isfinite(a)
+    maxabs = np.float32(np.max(a[finite])) if np.any(finite) else np.float32(0.0)
+    if maxabs < np.float32(1.1754944e-38):            # below the smallest normal single
+        return np.zeros(v.shape, dtype=np.int8), np.float32(1.0)
+    recip = np.float32(1.0) / maxabs
+    scaled = (v * recip).astype(np.float32) * np.float32(127.0)
+    scaled = np.where(np.isnan(v), np.float32(0.0), scaled).astype(np.float32)
+    codes = np.clip(np.rint(scaled), -127.0, 127.0).astype(np.int8)        # np.rint rounds half to even
+    return codes, np.float32(maxabs / np.float32(127.0))
+
+
 class OracleSession:
     """One sequence, one KV cache per layer, head-major [kv_head][pos][d]
-    (neural/neural.cl:2343-2346)."""
+    (neural/neural.cl:2343-2346). kv_int8 keeps the cache as int8 codes with one fp32 scale per row and folds the
+    scales into the score and the value sum exactly like cai_sdpa_decode_int8 (neural/neural.cl:2583-2687)."""
 
-    def __init__(self, model, max_ctx):
+    def __init__(self, model, max_ctx, kv_int8=False):
         self.m = model
         cfg = model.cfg
         self.max_ctx = max_ctx
-        self.k = np.zeros((cfg.layers, cfg.kv_heads, max_ctx, cfg.head_dim), dtype=model.dtype)
-        self.v = np.zeros_like(self.k)
+        self.kv_int8 = kv_int8
+        if kv_int8:
+            self.k = np.zeros((cfg.layers, cfg.kv_heads, max_ctx, cfg.head_dim), dtype=np.int8)
+            self.v = np.zeros_like(self.k)
+            self.k_scale = np.ones((cfg.layers, cfg.kv_heads, max_ctx), dtype=np.float32)
+            self.v_scale = np.ones_like(self.k_scale)
+        else:
+            self.k = np.zeros((cfg.layers, cfg.kv_heads, max_ctx, cfg.head_dim), dtype=model.dtype)
+            self.v = np.zeros_like(self.k)
         self.length = 0
 
     def reset(self):
@@ -296,18 +323,31 @@ class OracleSession:
                 k = rms_norm(k, b["k_norm"], cfg.rms_eps)
             q = rope_interleaved(q, pos, m.theta, hd)
             k = rope_interleaved(k, pos, m.theta, hd)
-            self.k[li, :, slot, :] = k.reshape(cfg.kv_heads, hd)
-            self.v[li, :, slot, :] = v.reshape(cfg.kv_heads, hd)
+            if self.kv_int8:
+                for g in range(cfg.kv_heads):
+                    self.k[li, g, slot], self.k_scale[li, g, slot] = quantize_cache_row(k[g * hd:(g + 1) * hd])
+                    self.v[li, g, slot], self.v_scale[li, g, slot] = quantize_cache_row(v[g * hd:(g + 1) * hd])
+            else:
+                self.k[li, :, slot, :] = k.reshape(cfg.kv_heads, hd)
+                self.v[li, :, slot, :] = v.reshape(cfg.kv_heads, hd)
             n = slot + 1
             att = np.empty(cfg.q_width, dtype=dt)
             for hq in range(cfg.heads):
                 g = hq // group
                 qh = q[hq * hd:(hq + 1) * hd]
-                sc = (self.k[li, g, :n, :] @ qh) * inv_sqrt      # scale after the dot (neural.cl:2450)
+                if self.kv_int8:
+                    # raw code dot, then one scalar per row: kscale * 1/sqrt(d) (neural.cl:2636-2639)
+                    sc = (self.k[li, g, :n, :].astype(dt) @ qh) * (self.k_scale[li, g, :n].astype(dt) * inv_sqrt)
+                else:
+                    sc = (self.k[li, g, :n, :] @ qh) * inv_sqrt      # scale after the dot (neural.cl:2450)
                 mx = np.max(sc)
                 e = np.exp(sc - mx)
                 den = np.sum(e, dtype=dt)
-                att[hq * hd:(hq + 1) * hd] = (e @ self.v[li, g, :n, :]) / den   # divide once at the end
+                if self.kv_int8:
+                    # (e_j * vscale_j) * code, summed, divided once at the end (neural.cl:2679-2684)
+                    att[hq * hd:(hq + 1) * hd] = ((e * self.v_scale[li, g, :n].astype(dt)) @ self.v[li, g, :n, :].astype(dt)) / den
+                else:
+                    att[hq * hd:(hq + 1) * hd] = (e @ self.v[li, g, :n, :]) / den   # divide once at the end
             x = x + b["wo"] @ att
             h = rms_norm(x, b["ffn_norm"], cfg.rms_eps)
             if cfg.n_experts:

@@ -188,3 +188,32 @@ def test_streamed_equals_full_forward_and_truncate():
     assert np.array_equal(again, rows[5])
     toks, _ = greedy_decode(model, s[:4], 4)
     assert len(toks) == 4
+
+
+def test_int8_kv_cache_row_format_and_drift():
+    """The int8 KV row rule of the reference's device kernel (neural/neural.cl:2500-2581): scale = maxabs / 127,
+    round half to even, |v - scale * code| <= scale / 2, zero row -> zero codes and unit scale; and a model decoded
+    over the int8 cache drifts from the fp32-cache logits by a small, non-zero amount (the reference's own 1e-3
+    gate, tests/TestNeuralNumerical.pas:69604-69609, compares two int8-cache implementations, as the GPU test does)."""
+    from oracle.forward import quantize_cache_row
+    rng = np.random.default_rng(3)
+    row = rng.standard_normal(128).astype(np.float32)
+    codes, scale = quantize_cache_row(row)
+    assert codes.dtype == np.int8 and np.abs(codes).max() == 127 and scale == np.float32(np.abs(row).max() / np.float32(127))
+    assert np.all(np.abs(row - scale * codes.astype(np.float32)) <= scale / 2 * (1 + 1e-6))
+    half = quantize_cache_row(np.float32([127.0, 0.5, 1.5, 2.5, -0.5, -1.5]))[0]
+    assert list(half) == [127, 0, 2, 2, 0, -2]                    # ties to even
+    z, zs = quantize_cache_row(np.zeros(64, np.float32))
+    assert not z.any() and zs == np.float32(1.0)
+    bad, _ = quantize_cache_row(np.float32([1.0, np.nan, np.inf, -np.inf]))
+    assert list(bad) == [127, 0, 127, -127]
+    cfg_json, tensors, seqs, gold = golden_hf_case("tiny_llama")
+    cfg = LlamaConfig.from_hf(cfg_json)
+    model = OracleModel.from_hf_tensors(cfg, tensors)
+    f32 = OracleSession(model, 16)
+    i8 = OracleSession(model, 16, kv_int8=True)
+    worst = 0.0
+    for t in seqs[0]:
+        a, b = f32.step(int(t)), i8.step(int(t))
+        worst = max(worst, float(np.max(np.abs(a - b))) / float(np.max(np.abs(a))))
+    assert 0 < worst < 1e-1
