@@ -7,8 +7,9 @@
 
 A step is one greedy decode step (one token per sequence) of the workload through the
 whole layer stack. Default workload: Qwen2.5-32B-shaped dense model, Q8_0 weights
-(synthetic N(0, 0.02), seed 3), batch 1, context 8192 filled by feeding random prompt
-tokens one at a time, fp32 KV cache; with N > 1 GPUs the attention heads and MLP
+(synthetic N(0, 0.02), seed 3), batch 1, context 8192 filled from random prompt tokens by
+cai_session_prefill (64 / batch positions per sequence and step on the tensor-core path; tests hold it
+equal to the reference's token-at-a-time prefill), fp32 KV cache; with N > 1 GPUs the attention heads and MLP
 columns/rows are sharded tensor-parallel (strong scaling: the job is the same at every N).
 Prints ONE JSON line on rank 0.
 """

@@ -27,6 +27,7 @@ struct AttnParams {
   float inv_sqrt_d;
   int min_chunk;          // fewest cached rows a context split covers (set by the launcher for the kernel it picked)
   int8_t* k_codes; int8_t* v_codes; float* k_scales; float* v_scales;     // int8 cache (k_codes != NULL)
+  const int32_t* seq_index;                                               // cache sequence of each batch row (NULL = the row itself)
 };
 
 // Rows per context split: the context spread over nsplit splits, at least min_chunk rows, a multiple of 32.
@@ -42,6 +43,7 @@ __global__ void rope_append_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x;
+  const int bs = p.seq_index ? p.seq_index[b] : b;     // the cache sequence this row appends to
   const int hd = p.head_dim;
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
   float* row = p.qkv + (int64_t)b * p.ld;
@@ -83,12 +85,12 @@ __global__ void rope_append_kernel(const AttnParams p) {
       x0 = y0; x1 = y1;
     }
     const int g = (2 * pr) / hd, d = (2 * pr) % hd;
-    float* dst = p.k_cache + (((int64_t)b * p.kv_heads + g) * p.max_ctx + slot) * hd + d;
+    float* dst = p.k_cache + (((int64_t)bs * p.kv_heads + g) * p.max_ctx + slot) * hd + d;
     dst[0] = x0; dst[1] = x1;
   }
   for (int c = threadIdx.x; c < kw; c += blockDim.x) {
     const int g = c / hd, d = c % hd;
-    p.v_cache[(((int64_t)b * p.kv_heads + g) * p.max_ctx + slot) * hd + d] = row[qw + kw + c];
+    p.v_cache[(((int64_t)bs * p.kv_heads + g) * p.max_ctx + slot) * hd + d] = row[qw + kw + c];
   }
 }
 
@@ -106,6 +108,7 @@ __global__ void rope_append_int8_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x;
+  const int bs = p.seq_index ? p.seq_index[b] : b;     // the cache sequence this row appends to
   const int hd = p.head_dim;
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
   float* row = p.qkv + (int64_t)b * p.ld;
@@ -161,7 +164,7 @@ __global__ void rope_append_int8_kernel(const AttnParams p) {
     const bool usable = __float_as_uint(m) >= 0x00800000u;                // a normal number
     const float row_scale = usable ? (m / 127.0f) : 1.0f;
     const float recip = usable ? (1.0f / m) : 0.0f;
-    const int64_t rowi = ((int64_t)b * p.kv_heads + g) * p.max_ctx + slot;
+    const int64_t rowi = ((int64_t)bs * p.kv_heads + g) * p.max_ctx + slot;
     int8_t* codes = (part == 0 ? p.k_codes : p.v_codes) + rowi * hd;
     if (lane == 0) (part == 0 ? p.k_scales : p.v_scales)[rowi] = row_scale;
     for (int d = lane; d < hd; d += 32) {
@@ -215,8 +218,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
   for (int i = threadIdx.x; i < G * hd; i += blockDim.x) q_s[i] = qrow[i];
   __syncthreads();
 
-  const float* kbase = p.k_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * hd;
-  const float* vbase = p.v_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * hd;
+  const int bs = p.seq_index ? p.seq_index[b] : b;
+  const float* kbase = p.k_cache + ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx * hd;
+  const float* vbase = p.v_cache + ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx * hd;
   const int key_stride = ATTN_WARPS * kpw;
 
   for (int h0 = 0; h0 < G; h0 += GT) {
@@ -393,8 +397,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x) q_s[i] = qrow[i];
   __syncthreads();
 
-  const float* kbase = p.k_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
-  const float* vbase = p.v_cache + ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+  const int bs = p.seq_index ? p.seq_index[b] : b;
+  const float* kbase = p.k_cache + ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+  const float* vbase = p.v_cache + ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
 
   float m[G], l[G];
   f32x2_t acc[G][DP2];
@@ -558,7 +563,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x) q_s[i] = qrow[i];
   __syncthreads();
 
-  const int64_t plane = ((int64_t)b * p.kv_heads + g) * (int64_t)p.max_ctx;
+  const int bs = p.seq_index ? p.seq_index[b] : b;
+  const int64_t plane = ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx;
   const int8_t* kbase = p.k_codes + plane * HD;
   const int8_t* vbase = p.v_codes + plane * HD;
   const float* ksc = p.k_scales + plane;
@@ -758,6 +764,7 @@ static AttnParams to_params(const AttnArgs& a) {
   p.inv_sqrt_d = (float)(1.0 / sqrt((double)a.head_dim));
   p.min_chunk = ATTN_MIN_CHUNK;
   p.k_codes = a.k_codes; p.v_codes = a.v_codes; p.k_scales = a.k_scales; p.v_scales = a.v_scales;
+  p.seq_index = a.seq_index_dev;
   return p;
 }
 

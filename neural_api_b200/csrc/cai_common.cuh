@@ -230,6 +230,9 @@ struct AttnArgs {
   int8_t* v_codes = nullptr;
   float* k_scales = nullptr;
   float* v_scales = nullptr;
+  // optional: row r of the batch belongs to sequence seq_index[r] of the cache (several rows may be consecutive
+  // positions of ONE sequence: chunked prefill); NULL = row r is sequence r. cache_len_dev stays per row.
+  const int32_t* seq_index_dev = nullptr;
 };
 int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx);
 size_t attn_partial_floats(int batch, int q_heads, int nsplit, int head_dim);

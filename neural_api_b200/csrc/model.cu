@@ -576,6 +576,13 @@ struct cai_session {
   float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][max_ctx][hd]; int8 codes when kv_int8
   float *k_snap = nullptr, *v_snap = nullptr;
   size_t layer_stride = 0;                            // elements per layer
+  // chunked prefill: a helper session of C rows per sequence that BORROWS this session's caches (kv_owner set in the
+  // helper: its rows are consecutive positions of the owner's sequences, seq_index_dev says which) and stops before
+  // the LM head
+  cai_session* wide = nullptr;
+  cai_session* kv_owner = nullptr;
+  int32_t* seq_index_dev = nullptr;
+  int wide_chunk = 0;                                 // positions per sequence and helper step
   bool kv_int8 = false;                               // the reference's int8 cache: codes above + one fp32 scale per row
   float *k_scales = nullptr, *v_scales = nullptr;     // [layers][B][kv_heads_l][max_ctx]
   float *k_scales_snap = nullptr, *v_scales_snap = nullptr;
@@ -583,7 +590,7 @@ struct cai_session {
   size_t cache_bytes() const { return layer_stride * (size_t)m->cfg.layers * (kv_int8 ? 1 : 4); }
   size_t scale_bytes() const { return scale_stride * (size_t)m->cfg.layers * 4; }
   int32_t *tokens_dev = nullptr, *pos_dev = nullptr, *len_dev = nullptr;
-  int32_t* io_pinned = nullptr;                       // [3][B] tokens, pos, len
+  int32_t* io_pinned = nullptr;                       // [4][B] tokens, pos, len, sequence index
   std::vector<int32_t> len_host, len_snap;
   bool have_snap = false;
   float *x = nullptr, *x_alt = nullptr, *h = nullptr, *qkv = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
@@ -670,7 +677,7 @@ static int enqueue_step(cai_session* s) {
   const bool tc_batch = linear_uses_tensor_cores(&m->layers[0].wgu, B) || linear_uses_tensor_cores(&m->layers[0].wqkv, B);
   // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first, the batch runs on the
   // tensor cores, or the cache is int8 (a row's scale needs the whole row)
-  const bool fuse_rope = !c.qk_norm && !tc_batch && !s->kv_int8;
+  const bool fuse_rope = !c.qk_norm && !tc_batch && !s->kv_int8 && !s->kv_owner;
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
     if (linear_can_fuse_norm(&L.wqkv, B)) {
@@ -693,6 +700,7 @@ static int enqueue_step(cai_session* s) {
       } else {
         a.k_cache = s->k_cache + (size_t)l * s->layer_stride; a.v_cache = s->v_cache + (size_t)l * s->layer_stride;
       }
+      a.seq_index_dev = s->seq_index_dev;
       a.cache_len_dev = s->len_dev; a.batch = B; a.q_heads = m->heads_l; a.kv_heads = m->kv_heads_l;
       a.head_dim = c.head_dim; a.max_ctx = s->max_ctx; a.theta = m->theta; a.pos_dev = s->pos_dev;
       a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
@@ -805,6 +813,11 @@ static int enqueue_step(cai_session* s) {
       CAI_TRY(op_moe_combine(ctx, x, H, s->pair_out, H, s->gates, B, K, H));
     }
   }
+  if (s->kv_owner) {
+    // prefill helper: only the caches matter, no logits, no argmax, no advance (the host sets the next chunk's rows)
+    if (x != s->x) return cai_fail(ctx, CAI_ERR_STATE, "internal: residual buffer parity");
+    return CAI_OK;
+  }
   if (linear_can_fuse_norm(&m->lm_head, B)) {
     LinearArgs a; a.w = &m->lm_head; a.x = x; a.ldx = H; a.y = s->logits; a.ldy = m->vocab_l; a.batch = B;
     a.norm_gain = m->final_norm; a.norm_eps = c.rms_eps;
@@ -876,9 +889,11 @@ int cai_session_destroy(cai_session* s) {
   if (!s) return CAI_ERR_INVALID;
   cudaSetDevice(s->ctx->device);
   cudaStreamSynchronize(s->ctx->stream);
+  if (s->wide) { cai_session_destroy(s->wide); s->wide = nullptr; }
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
   if (s->ar) comm_ar_destroy(s->ctx, s->ar);
-  void* bufs[] = {s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
+  if (s->kv_owner) { s->k_cache = s->v_cache = nullptr; s->k_scales = s->v_scales = nullptr; }   // borrowed
+  void* bufs[] = {s->seq_index_dev, s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
                   s->att, s->act, s->gu, s->logits, s->router_logits, s->gates, s->moe_hidden, s->pair_out, s->expert_ids, s->partial,
                   s->amax_idx, s->amax_val, s->amax_part_val, s->amax_part_idx, s->amax_tickets, s->rope_cs, s->amax_pack, s->amax_gather, s->logits_gather, s->trace, s->trace_count, s->prefill_buf,
                   s->tile_expert, s->tile_pairs, s->moe_gu, s->moe_unscale, s->moe_xp,
@@ -891,7 +906,14 @@ int cai_session_destroy(cai_session* s) {
   return CAI_OK;
 }
 
+static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type, cai_session* kv_owner, cai_session** out);
+
 int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_session** out) {
+  return session_create_impl(m, max_ctx, batch, kv_type, nullptr, out);
+}
+
+// kv_owner != NULL: a prefill helper whose `batch` rows index into the owner's caches (nothing is allocated for them)
+static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type, cai_session* kv_owner, cai_session** out) {
   if (!m) return CAI_ERR_INVALID;
   cai_ctx* ctx = m->ctx;
   CAI_TRY(cai_bind(ctx));
@@ -904,9 +926,10 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   const bool kv_int8 = kv_type == CAI_TYPE_I8;
   if (kv_int8 && !attn_int8_supported(m->heads_l, m->kv_heads_l, c.head_dim))
     return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "the int8 KV cache needs head_dim 64 or 128 and at most 8 query heads per KV head");
-  const size_t layer_stride = (size_t)batch * m->kv_heads_l * max_ctx * c.head_dim;
-  const size_t scale_stride = (size_t)batch * m->kv_heads_l * max_ctx;
-  const size_t cache_bytes = layer_stride * (size_t)c.layers * (kv_int8 ? 1 : 4) + (kv_int8 ? scale_stride * (size_t)c.layers * 4 : 0);
+  const int cache_seqs = kv_owner ? kv_owner->batch : batch;
+  const size_t layer_stride = (size_t)cache_seqs * m->kv_heads_l * max_ctx * c.head_dim;
+  const size_t scale_stride = (size_t)cache_seqs * m->kv_heads_l * max_ctx;
+  const size_t cache_bytes = kv_owner ? 0 : layer_stride * (size_t)c.layers * (kv_int8 ? 1 : 4) + (kv_int8 ? scale_stride * (size_t)c.layers * 4 : 0);
   size_t free_b = 0, total_b = 0;
   CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
   if (2 * cache_bytes + ((size_t)256 << 20) > free_b)
@@ -924,8 +947,14 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
   s->trace_cap = (int64_t)max_ctx * B;
   bool ok = true;
   auto A = [&](void** p, size_t bytes) { if (ok && cudaMalloc(p, bytes ? bytes : 4) != cudaSuccess) { cudaGetLastError(); ok = false; } };
-  A((void**)&s->k_cache, s->cache_bytes()); A((void**)&s->v_cache, s->cache_bytes());
-  if (kv_int8) { A((void**)&s->k_scales, s->scale_bytes()); A((void**)&s->v_scales, s->scale_bytes()); }
+  if (kv_owner) {
+    s->kv_owner = kv_owner;
+    s->k_cache = kv_owner->k_cache; s->v_cache = kv_owner->v_cache; s->k_scales = kv_owner->k_scales; s->v_scales = kv_owner->v_scales;
+    A((void**)&s->seq_index_dev, (size_t)B * 4);
+  } else {
+    A((void**)&s->k_cache, s->cache_bytes()); A((void**)&s->v_cache, s->cache_bytes());
+    if (kv_int8) { A((void**)&s->k_scales, s->scale_bytes()); A((void**)&s->v_scales, s->scale_bytes()); }
+  }
   A((void**)&s->tokens_dev, (size_t)B * 4); A((void**)&s->pos_dev, (size_t)B * 4); A((void**)&s->len_dev, (size_t)B * 4);
   A((void**)&s->x, (size_t)B * H * 4); A((void**)&s->x_alt, (size_t)B * H * 4); A((void**)&s->h, (size_t)B * H * 4);
   A((void**)&s->qkv, (size_t)B * QKVW * 4); A((void**)&s->att, (size_t)B * m->qw_l * 4);
@@ -975,11 +1004,11 @@ int cai_session_create(cai_model* m, int max_ctx, int batch, int kv_type, cai_se
     A((void**)&s->amax_pack, (size_t)B * 2 * 4); A((void**)&s->amax_gather, (size_t)m->tp_size * B * 2 * 4);
     A((void**)&s->logits_gather, (size_t)m->tp_size * B * m->vocab_l * 4);
   }
-  if (ok && m->tp_size > 1 && ((int64_t)B * H) % 4 == 0) {
+  if (ok && !kv_owner && m->tp_size > 1 && ((int64_t)B * H) % 4 == 0) {
     // collective: every rank creates its session at the same point
     if (comm_ar_create(ctx, 2 * c.layers, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
   }
-  if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)3 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
+  if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)4 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
   if (ok && B >= 3 && B <= 64) {
     // the tensor-core GEMM's activation buffer must exist before a step is captured into a graph
     int64_t kmax = H;
@@ -1099,23 +1128,66 @@ int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens
     CAI_CUDA(ctx, cudaMalloc((void**)&s->prefill_buf, (size_t)need * 4));
     s->prefill_cap = need;
   }
+  for (int64_t i = 0; i < need; ++i)
+    if (tokens_host[i] < 0 || tokens_host[i] >= vocab) return cai_fail(ctx, CAI_ERR_INVALID, "token id %d outside the vocabulary of %d", tokens_host[i], vocab);
+  // Chunked prefill: C consecutive positions of every sequence per step (B x C <= 64 rows, the tensor-core GEMM's
+  // batch), through a helper session that appends to and attends over THIS session's caches: row (b, i) of a chunk is
+  // position len[b] + i of sequence b and sees the rows before it, the chunk's own earlier rows included. The
+  // reference prefills one token at a time (neural/neuralchatengine.pas:1466-1470); the caches come out the same
+  // up to the arithmetic of the batched kernels (tests compare the two). CAI_PREFILL_CHUNK=0 turns it off. What is
+  // left over after the whole chunks goes through the token-at-a-time loop below.
+  int done = 0;
+  {
+    const char* off = getenv("CAI_PREFILL_CHUNK");
+    const int C = (B <= 32) ? 64 / B : 0;
+    if (C >= 2 && n_tokens >= C && !(off && *off == '0') && !s->kv_owner) {
+      if (!s->wide) {
+        cai_session* w = nullptr;
+        const int st = session_create_impl(s->m, s->max_ctx, B * C, s->kv_int8 ? CAI_TYPE_I8 : CAI_TYPE_F32, s, &w);
+        if (st == CAI_OK) { s->wide = w; s->wide_chunk = C; }
+        else if (st != CAI_ERR_OOM) return st;             // no room for the helper: keep the token-at-a-time path
+      }
+      cai_session* w = s->wide;
+      if (w) {
+        const int R = B * C;
+        for (; done + C <= n_tokens; done += C) {
+          int32_t* pin = w->io_pinned;
+          for (int b = 0; b < B; ++b)
+            for (int i = 0; i < C; ++i) {
+              const int r = b * C + i, at = s->len_host[(size_t)b] + done + i;
+              pin[r] = tokens_host[(size_t)b * n_tokens + done + i];
+              pin[R + r] = at;                               // absolute position = cache slot during prefill
+              pin[2 * R + r] = at;                           // rows of the sequence cached before this one
+              pin[3 * R + r] = b;
+            }
+          CAI_CUDA(ctx, cudaMemcpyAsync(w->tokens_dev, pin, (size_t)R * 4, cudaMemcpyHostToDevice, ctx->stream));
+          CAI_CUDA(ctx, cudaMemcpyAsync(w->pos_dev, pin + R, (size_t)R * 4, cudaMemcpyHostToDevice, ctx->stream));
+          CAI_CUDA(ctx, cudaMemcpyAsync(w->len_dev, pin + 2 * R, (size_t)R * 4, cudaMemcpyHostToDevice, ctx->stream));
+          CAI_CUDA(ctx, cudaMemcpyAsync(w->seq_index_dev, pin + 3 * R, (size_t)R * 4, cudaMemcpyHostToDevice, ctx->stream));
+          CAI_TRY(run_step(w));
+          CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned rows are rewritten for the next chunk
+        }
+        for (auto& l : s->len_host) l += done;
+        CAI_TRY(push_len(s));
+        if (done == n_tokens) return CAI_OK;
+      }
+    }
+  }
+  tokens_host += done;                                       // column offset: rows keep the stride n_tokens
+  const int n_left = n_tokens - done;
   // step-major copy: row i holds the i-th token of every sequence
   std::vector<int32_t> stepmajor((size_t)need);
   for (int b = 0; b < B; ++b)
-    for (int i = 0; i < n_tokens; ++i) {
-      const int32_t t = tokens_host[(size_t)b * n_tokens + i];
-      if (t < 0 || t >= vocab) return cai_fail(ctx, CAI_ERR_INVALID, "token id %d outside the vocabulary of %d", t, vocab);
-      stepmajor[(size_t)i * B + b] = t;
-    }
-  CAI_CUDA(ctx, cudaMemcpyAsync(s->prefill_buf, stepmajor.data(), (size_t)need * 4, cudaMemcpyHostToDevice, ctx->stream));
+    for (int i = 0; i < n_left; ++i) stepmajor[(size_t)i * B + b] = tokens_host[(size_t)b * n_tokens + i];
+  CAI_CUDA(ctx, cudaMemcpyAsync(s->prefill_buf, stepmajor.data(), (size_t)n_left * B * 4, cudaMemcpyHostToDevice, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   std::vector<int32_t> first(stepmajor.begin(), stepmajor.begin() + B);
   CAI_TRY(stage_inputs(s, first.data(), nullptr));
-  for (int i = 0; i < n_tokens; ++i) {
+  for (int i = 0; i < n_left; ++i) {
     CAI_CUDA(ctx, cudaMemcpyAsync(s->tokens_dev, s->prefill_buf + (size_t)i * B, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     CAI_TRY(run_step(s));
   }
-  for (auto& l : s->len_host) l += n_tokens;
+  for (auto& l : s->len_host) l += n_left;
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return CAI_OK;
 }

@@ -379,3 +379,39 @@ def test_int8_kv_cache_is_refused_for_shapes_it_does_not_cover(backend):
             StreamingDecoder(model, 8, kv_type=TYPE_I8)
     finally:
         model.close()
+
+
+@pytest.mark.parametrize("batch,kv_type", [(1, TYPE_F32), (2, TYPE_F32), (2, TYPE_I8), (16, TYPE_F32)])
+def test_chunked_prefill_equals_token_at_a_time_prefill(backend, batch, kv_type):
+    """cai_session_prefill fills the caches in chunks of 64 / batch positions per sequence through the tensor-core
+    path; the reference prefills one token at a time (neural/neuralchatengine.pas:1466-1470). The decode steps that
+    follow must not tell the difference beyond the arithmetic of the batched kernels (and, for the int8 cache, the
+    odd code that rounds the other way)."""
+    import os
+    kw = dict(hidden=512, inter=1024, layers=2, heads=8, kv_heads=2, head_dim=64, vocab=1024, rms_eps=1e-6, rope_theta=1e4,
+              qkv_bias=True)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=13, std=0.03)
+    model.finalize()
+    rng = np.random.default_rng(6)
+    n_prompt = 150                                      # whole chunks plus a remainder for every batch size here
+    prompt = rng.integers(0, kw["vocab"], (batch, n_prompt)).astype(np.int32)
+    nxt = rng.integers(0, kw["vocab"], (batch, 3)).astype(np.int32)
+    outs = []
+    try:
+        for chunked in ("1", "0"):
+            os.environ["CAI_PREFILL_CHUNK"] = chunked
+            sess = StreamingDecoder(model, 192, batch=batch, kv_type=kv_type)
+            try:
+                sess.prefill(prompt)
+                assert sess.cache_length(batch - 1) == n_prompt
+                rows = [sess.step_forward(nxt[:, i])[0].copy() for i in range(3)]
+                outs.append(np.stack(rows))
+            finally:
+                sess.close()
+    finally:
+        os.environ.pop("CAI_PREFILL_CHUNK", None)
+        model.close()
+    rms = float(np.sqrt(np.mean(outs[1].astype(np.float64) ** 2)))
+    worst = float(np.max(np.abs(outs[0] - outs[1]))) / rms
+    assert worst < (5e-3 if kv_type == TYPE_I8 else 1e-4), worst
