@@ -27,7 +27,38 @@ __device__ __forceinline__ int64_t x_phys(int64_t k) {
   return (k & ~(int64_t)28) | ((((k >> 2) & 7) ^ ((k >> 5) & 7)) << 2) | (k & 3);
 }
 
-template <int TYPE, int NB, int RPW, int MINB>
+// cp.async pieces of the ring variant (16 bytes, L2 only; a source size of 0 zero-fills the destination)
+__device__ __forceinline__ void gv_cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void gv_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most depth-2 of this thread's copy groups are still in flight
+__device__ __forceinline__ void gv_cp_async_wait_depth(int depth) {
+  if (depth >= 8) asm volatile("cp.async.wait_group 6;" ::: "memory");
+  else if (depth == 7) asm volatile("cp.async.wait_group 5;" ::: "memory");
+  else if (depth == 6) asm volatile("cp.async.wait_group 4;" ::: "memory");
+  else if (depth == 5) asm volatile("cp.async.wait_group 3;" ::: "memory");
+  else if (depth == 4) asm volatile("cp.async.wait_group 2;" ::: "memory");
+  else if (depth == 3) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ int4 gv_lds16(uint32_t addr) {
+  int4 v;
+  asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t gv_lds_u16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
+// RING = false: a lane keeps the next stride's codes in registers while it consumes the current one.
+// RING = true: every warp owns a ring of p.ring_depth stages in shared memory (per stage RPW x 512 bytes of codes
+// and the RPW x CHUNK scales that go with them) filled by cp.async, depth-1 strides ahead of the arithmetic: three
+// to five times the bytes in flight per SM at no register cost. A lane copies and reads back its own 16 code
+// bytes; the scales are copied by the first lanes and read by all (hence the warp barrier per stride).
+template <int TYPE, int NB, int RPW, int MINB, bool RING>
 __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams p) {
   extern __shared__ __align__(16) float smem_f[];
   const int lane = threadIdx.x & 31;
@@ -36,8 +67,102 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
   const int groups_per_cta = warps_per_cta / p.ksplit;
   const int group = warp / p.ksplit;
   const int kpart = warp - group * p.ksplit;
+  // codes per lane chunk (one 16-byte load) and per warp stride
+  constexpr int CHUNK = (TYPE == CAI_TYPE_Q8_0) ? 16 : 32;
+  constexpr int CODE_SHIFT = (TYPE == CAI_TYPE_Q8_0) ? 0 : 1;     // bytes = codes >> shift
+  const int64_t K = p.k;
+  const int64_t row_bytes = K >> CODE_SHIFT;
+  const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
+  const int64_t stride_b = stride >> CODE_SHIFT;                  // bytes of codes per stride
+  const int64_t stride_s = stride >> 5;                           // scales per stride
+  const int64_t k_first = ((int64_t)kpart * 32 + lane) * CHUNK;
+  const int iters = (k_first < K) ? (int)((K - k_first + stride - 1) / stride) : 0;
+  // ring variant: warp-uniform trip count (lane 0's), stage geometry, this warp's ring
+  constexpr int SC16 = CHUNK * 2 / 16;                            // 16-byte pieces of one row's scales per stride
+  constexpr int STAGE_BYTES = RPW * (512 + CHUNK * 2);
+  const int64_t k_first_w = (int64_t)kpart * 32 * CHUNK;
+  const int iters_w = (k_first_w < K) ? (int)((K - k_first_w + stride - 1) / stride) : 0;
+  const uint32_t ring_w = (uint32_t)__cvta_generic_to_shared((char*)smem_f + p.ring_off) + warp * p.ring_depth * STAGE_BYTES;
+  const bool swiglu = (p.epi == EPI_SWIGLU);
+  const int64_t units_total = swiglu ? (p.n >> 1) : p.n;
+  const int units_per_group = swiglu ? (RPW / 2) : RPW;
+
+
+  // Ring variant: the fill cursor runs ring_depth-1 strides ahead of the arithmetic, straight across row-block
+  // boundaries, and is primed before the wait on the preceding kernel: weights are constants, only the
+  // activations depend on it, so the first strides stream in while the activations are staged and normed.
+  int64_t fcb = blockIdx.x;           // row block being fetched, and the stride within it
+  int fit = 0, fill_slot = 0, read_slot = 0;
+  const char* fwp[RPW];
+  const char* fscp = nullptr;         // copy lanes: this lane's 16-byte piece of one row's scales
+  int64_t fsc_idx = 0;                // its first scale index within the row
+  const uint32_t fsc_dst = ring_w + RPW * 512 + (lane / SC16) * (CHUNK * 2) + (lane % SC16) * 16;
+  auto block_row = [&](int64_t cb, int r) -> int64_t {
+    const int64_t unit0 = (cb * groups_per_cta + group) * units_per_group;
+    if (swiglu) {
+      const int64_t half = p.n >> 1;
+      int64_t j = unit0 + (r >> 1);
+      if (j >= half) j = half - 1;
+      return (r & 1) ? half + j : j;
+    }
+    const int64_t row = unit0 + r;
+    return row >= p.n ? p.n - 1 : row;
+  };
+  auto fill_setup = [&]() {
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int64_t row = block_row(fcb, r);
+      fwp[r] = (const char*)p.codes + row * row_bytes + (k_first >> CODE_SHIFT);
+      if (lane / SC16 == r) {
+        fsc_idx = (k_first_w >> 5) + (lane % SC16) * 8;
+        fscp = (const char*)((const unsigned short*)p.scales + row * p.sstride + fsc_idx);
+      }
+    }
+  };
+  auto fill_one = [&]() {
+    if (fcb < p.cta_blocks && iters_w > 0) {
+      const uint32_t ok = (fit < iters) ? 16u : 0u;
+      const uint32_t dst = ring_w + fill_slot * STAGE_BYTES + lane * 16;
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        gv_cp_async16(dst + r * 512, ok ? fwp[r] : (const char*)p.codes, ok);
+        fwp[r] += stride_b;
+      }
+      if (lane < RPW * SC16) {
+        const uint32_t sok = (fsc_idx < (K >> 5)) ? 16u : 0u;
+        gv_cp_async16(fsc_dst + fill_slot * STAGE_BYTES, sok ? fscp : (const char*)p.scales, sok);
+        fscp += stride_s * 2;
+        fsc_idx += stride_s;
+      }
+      if (++fit == iters_w) {
+        fit = 0;
+        fcb += gridDim.x;
+        if (fcb < p.cta_blocks) fill_setup();
+      }
+    }
+    gv_cp_async_commit();               // one group per stride, empty past the end
+    fill_slot = (fill_slot + 1 == p.ring_depth) ? 0 : fill_slot + 1;
+  };
 
   pdl_trigger();
+  if constexpr (RING) {
+    if (fcb < p.cta_blocks && iters_w > 0) fill_setup();
+    for (int s = 0; s < p.ring_depth - 1; ++s) fill_one();
+  }
+  // One-pass staging (rows of up to 256 * XU float4): a thread holds its XU pieces of the row in registers, so the
+  // loads are all in flight at once and the RMSNorm needs no second trip through shared memory. The norm gains are
+  // constants and are fetched here, ahead of the wait on the preceding kernel.
+  constexpr int XU = 8;
+  const int K4 = (int)(K >> 2);
+  const bool one_pass = p.x_in_smem && K4 <= 256 * XU && blockDim.x == 256 && ((uintptr_t)p.norm_gain & 15) == 0;
+  float4 gain4[XU];
+  if (one_pass && p.norm_gain) {
+#pragma unroll
+    for (int u = 0; u < XU; ++u) {
+      const int c4 = threadIdx.x + u * 256;
+      gain4[u] = (c4 < K4) ? __ldg((const float4*)p.norm_gain + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   pdl_wait();
 
   // operand selection
@@ -58,7 +183,6 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
   } else {
     x = p.x + (int64_t)b0 * p.ldx;
   }
-  const int64_t K = p.k;
 
   // Activations -> shared memory ONCE per CTA (the CTA then walks many row blocks), with the per-token
   // RMSNorm of the reference applied on the way when asked: y = gain * (x * inv). Rows beyond the batch
@@ -72,43 +196,64 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     // the lanes of a quarter-warp are 64 or 128 bytes apart and collide on 2 or 1 of the 8 bank groups (measured:
     // 70 % of the shared-memory wavefronts of this kernel were conflict replays). So the pieces of a lane's
     // segment are stored XOR-ed with the segment index: x_phys() below, undone in the reads by `xsw`.
-    for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
-      const int b = (int)(i / K);
-      const int64_t c = i - (int64_t)b * K;
-      const int bb = (b0 + b < p.batch) ? b : 0;
-      *(float4*)(smem_f + (int64_t)b * K + x_phys<TYPE>(c)) = *(const float4*)(x + (int64_t)bb * p.ldx + c);
-    }
     red = smem_f + (int64_t)NB * K;
     float* nred = red + (size_t)warps_per_cta * (RPW * NB);
-    __syncthreads();
-    if (p.norm_gain) {
+    if (one_pass) {
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        float* xb = smem_f + (int64_t)b * K;
-        float ss = 0.f;
-        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) { const float v = xb[x_phys<TYPE>(c)]; ss = fmaf(v, v, ss); }
-        ss = block_sum(ss, nred);
-        const float inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
-        for (int64_t c = threadIdx.x; c < K; c += blockDim.x) { float* e = xb + x_phys<TYPE>(c); *e = p.norm_gain[c] * (*e * inv); }
+        const float* xg = x + (int64_t)((b0 + b < p.batch) ? b : 0) * p.ldx;
+        float4 xv[XU];
+#pragma unroll
+        for (int u = 0; u < XU; ++u) {
+          const int c4 = threadIdx.x + u * 256;
+          xv[u] = (c4 < K4) ? __ldcg((const float4*)xg + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (p.norm_gain) {
+          float ss = 0.f;
+#pragma unroll
+          for (int u = 0; u < XU; ++u) {
+            ss = fmaf(xv[u].x, xv[u].x, ss); ss = fmaf(xv[u].y, xv[u].y, ss);
+            ss = fmaf(xv[u].z, xv[u].z, ss); ss = fmaf(xv[u].w, xv[u].w, ss);
+          }
+          ss = block_sum(ss, nred);
+          const float inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
+#pragma unroll
+          for (int u = 0; u < XU; ++u) {
+            xv[u].x = gain4[u].x * (xv[u].x * inv); xv[u].y = gain4[u].y * (xv[u].y * inv);
+            xv[u].z = gain4[u].z * (xv[u].z * inv); xv[u].w = gain4[u].w * (xv[u].w * inv);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < XU; ++u) {
+          const int c4 = threadIdx.x + u * 256;
+          if (c4 < K4) *(float4*)(smem_f + (int64_t)b * K + x_phys<TYPE>((int64_t)c4 * 4)) = xv[u];
+        }
       }
       __syncthreads();
+    } else {
+      for (int64_t i = (int64_t)threadIdx.x * 4; i < (int64_t)NB * K; i += (int64_t)blockDim.x * 4) {
+        const int b = (int)(i / K);
+        const int64_t c = i - (int64_t)b * K;
+        const int bb = (b0 + b < p.batch) ? b : 0;
+        *(float4*)(smem_f + (int64_t)b * K + x_phys<TYPE>(c)) = *(const float4*)(x + (int64_t)bb * p.ldx + c);
+      }
+      __syncthreads();
+      if (p.norm_gain) {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          float* xb = smem_f + (int64_t)b * K;
+          float ss = 0.f;
+          for (int64_t c = threadIdx.x; c < K; c += blockDim.x) { const float v = xb[x_phys<TYPE>(c)]; ss = fmaf(v, v, ss); }
+          ss = block_sum(ss, nred);
+          const float inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
+          for (int64_t c = threadIdx.x; c < K; c += blockDim.x) { float* e = xb + x_phys<TYPE>(c); *e = p.norm_gain[c] * (*e * inv); }
+        }
+        __syncthreads();
+      }
     }
 #pragma unroll
     for (int b = 0; b < NB; ++b) xbase[b] = smem_f + (int64_t)b * K;
   }
-
-  // codes per lane chunk (one 16-byte load) and per warp stride
-  constexpr int CHUNK = (TYPE == CAI_TYPE_Q8_0) ? 16 : 32;
-  constexpr int CODE_SHIFT = (TYPE == CAI_TYPE_Q8_0) ? 0 : 1;     // bytes = codes >> shift
-  const int64_t row_bytes = K >> CODE_SHIFT;
-  const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
-  const int64_t stride_b = stride >> CODE_SHIFT;                  // bytes of codes per stride
-  const int64_t stride_s = stride >> 5;                           // scales per stride
-  const int64_t k_first = ((int64_t)kpart * 32 + lane) * CHUNK;
-  const int iters = (k_first < K) ? (int)((K - k_first + stride - 1) / stride) : 0;
-  const bool swiglu = (p.epi == EPI_SWIGLU);
-  const int64_t units_total = swiglu ? (p.n >> 1) : p.n;
-  const int units_per_group = swiglu ? (RPW / 2) : RPW;
 
   // persistent: this CTA takes row blocks blockIdx.x, blockIdx.x + gridDim.x, ...
   for (int64_t cb = blockIdx.x; cb < p.cta_blocks; cb += gridDim.x) {
@@ -141,13 +286,15 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     }
     int4 wv[RPW], wn[RPW];
     uint32_t sv[RPW], sn[RPW];
+    if constexpr (!RING) {
 #pragma unroll
-    for (int r = 0; r < RPW; ++r) { wn[r] = make_int4(0, 0, 0, 0); sn[r] = 0; }
-    if (iters > 0) {
+      for (int r = 0; r < RPW; ++r) { wn[r] = make_int4(0, 0, 0, 0); sn[r] = 0; }
+      if (iters > 0) {
 #pragma unroll
-      for (int r = 0; r < RPW; ++r) {
-        wn[r] = ldg_stream16(wp[r]);
-        sn[r] = __ldg(sp[r]);
+        for (int r = 0; r < RPW; ++r) {
+          wn[r] = ldg_stream16(wp[r]);
+          sn[r] = __ldg(sp[r]);
+        }
       }
     }
     f32x2_t acc2[RPW][NB];
@@ -162,16 +309,30 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     // k_first and the stride are whole multiples of 32 segments, so it is the same for every stride
     const int xsw = p.x_in_smem ? ((TYPE == CAI_TYPE_Q8_0) ? ((lane >> 1) & 3) : (lane & 7)) : 0;
 
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int r = 0; r < RPW; ++r) { wv[r] = wn[r]; sv[r] = sn[r]; }
-      if (it + 1 < iters) {
+    for (int it = 0; it < (RING ? iters_w : iters); ++it) {
+      if constexpr (RING) {
+        gv_cp_async_wait_depth(p.ring_depth);     // stage `it` of this lane has landed
+        __syncwarp();                             // ... and so have the scales the copy lanes fetched
+        fill_one();                               // refills the slot read in the previous stride
+        const uint32_t src = ring_w + read_slot * STAGE_BYTES;
+        read_slot = (read_slot + 1 == p.ring_depth) ? 0 : read_slot + 1;
+        if (it >= iters) continue;                // this lane's codes lie beyond K in the last stride
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
-          wp[r] += stride_b;
-          sp[r] += stride_s;
-          wn[r] = ldg_stream16(wp[r]);
-          sn[r] = __ldg(sp[r]);
+          wv[r] = gv_lds16(src + r * 512 + lane * 16);
+          sv[r] = gv_lds_u16(src + RPW * 512 + r * (CHUNK * 2) + ((lane * CHUNK) >> 5) * 2);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) { wv[r] = wn[r]; sv[r] = sn[r]; }
+        if (it + 1 < iters) {
+#pragma unroll
+          for (int r = 0; r < RPW; ++r) {
+            wp[r] += stride_b;
+            sp[r] += stride_s;
+            wn[r] = ldg_stream16(wp[r]);
+            sn[r] = __ldg(sp[r]);
+          }
         }
       }
       f32x2_t part[RPW][NB];
@@ -319,11 +480,11 @@ int env_int(const char* name, int dflt) {
   return (s && *s) ? atoi(s) : dflt;
 }
 
-template <int TYPE, int NB, int RPW, int MINB>
+template <int TYPE, int NB, int RPW, int MINB, bool RING = false>
 static cudaError_t launch_one_b(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
   // (single caller thread per context: the function-local cache below needs no lock)
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_quant_kernel<TYPE, NB, RPW, MINB, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   // persistent grid: exactly the CTAs that can be resident at once (a host-side query, cached per
@@ -332,7 +493,7 @@ static cudaError_t launch_one_b(cai_ctx* ctx, const GemvParams& p, dim3 grid, in
   static size_t cached_smem = (size_t)-1;
   if (cached_smem != smem) {
     int nblk = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW, MINB>, threads, smem);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW, MINB, RING>, threads, smem);
     if (e != cudaSuccess) return e;
     cached_blocks = nblk < 1 ? 1 : nblk;
     cached_smem = smem;
@@ -342,13 +503,16 @@ static cudaError_t launch_one_b(cai_ctx* ctx, const GemvParams& p, dim3 grid, in
   if (gx * grid.y > resident) gx = resident / grid.y;
   if (gx < 1) gx = 1;
   grid.x = (unsigned)gx;
-  return pdl_launch(ctx, gemv_quant_kernel<TYPE, NB, RPW, MINB>, grid, dim3(threads), smem, p);
+  return pdl_launch(ctx, gemv_quant_kernel<TYPE, NB, RPW, MINB, RING>, grid, dim3(threads), smem, p);
 }
 // MINB = CTAs per SM the compiler must leave room for (register cap). Measured on B200 for the batch-1,
 // 4-rows-per-warp kernel: 2 (<= 128 registers, none spilled) 4.4 TB/s; 3 (80 registers, spills) 3.5 TB/s;
 // 1 (no cap) 2.7 TB/s. CAI_GEMV_MINB=3 selects the tighter cap for experiments.
 template <int TYPE, int NB, int RPW>
 static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int threads, size_t smem) {
+  if constexpr (NB <= 2) {
+    if (p.ring_depth > 0) return launch_one_b<TYPE, NB, RPW, 2, true>(ctx, p, grid, threads, smem);
+  }
   if (NB == 1 && RPW == 4 && env_int("CAI_GEMV_MINB", 2) == 3) return launch_one_b<TYPE, NB, RPW, (NB == 1 && RPW == 4) ? 3 : 2>(ctx, p, grid, threads, smem);
   return launch_one_b<TYPE, NB, RPW, (NB <= 2) ? 2 : 1>(ctx, p, grid, threads, smem);
 }
@@ -487,7 +651,27 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     if (!p.x_in_smem) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: fused RMSNorm needs the activations to fit in shared memory");
     p.norm_gain = a.norm_gain; p.norm_eps = a.norm_eps;
   }
-  const size_t smem = (p.x_in_smem ? x_bytes + 32 * sizeof(float) : 0) + (size_t)wpc * rpw * nb * sizeof(float);
+  size_t smem = (p.x_in_smem ? x_bytes + 32 * sizeof(float) : 0) + (size_t)wpc * rpw * nb * sizeof(float);
+  // Ring variant: by default for single-row Q8_0 products whose activations sit in shared memory, 4 stages
+  // (measured on B200 against the register prefetch: 5120 x 152064 0.74 -> 0.84 of the copy peak, 5120 x 27648
+  // 0.63 -> 0.66; slower for K = 27648, whose activations live in L1 and lose it to the rings, for 2-row tiles
+  // and for Q4_0, which stay on registers). CAI_GEMV_RING=0 turns it off, N >= 2 forces up to N stages on every
+  // shape the variant covers (batch tiles of 1 and 2 rows, as many stages as fit with two CTAs per SM).
+  {
+    int want = env_int("CAI_GEMV_RING", -1);
+    if (want < 0) want = (nb == 1 && w->type == CAI_TYPE_Q8_0 && p.x_in_smem) ? 4 : 0;
+    const size_t stage = (size_t)wpc * rpw * (512 + lane_chunk * 2);
+    const size_t base = (smem + 15) & ~(size_t)15;
+    const size_t budget = 108 * 1024;
+    int depth = 0;
+    if (want >= 2 && !indexed && nb <= 2 && (w->k % 32) == 0 && (w->sstride % 8) == 0 && ((uintptr_t)w->scales % 16) == 0 &&
+        ((uintptr_t)w->codes % 16) == 0 && base + 2 * stage <= budget) {
+      depth = (int)((budget - base) / stage);
+      if (depth > want) depth = want;
+      if (depth > 8) depth = 8;
+    }
+    if (depth >= 2) { p.ring_depth = depth; p.ring_off = (int)base; smem = base + (size_t)depth * stage; }
+  }
   cudaError_t e;
   if (w->type == CAI_TYPE_Q8_0) e = launch_quant_nb<CAI_TYPE_Q8_0>(ctx, p, nb, rpw, grid, threads, smem);
   else e = launch_quant_nb<CAI_TYPE_Q4_0>(ctx, p, nb, rpw, grid, threads, smem);

@@ -21,6 +21,8 @@ struct GemvParams {
   int ksplit;       // warps cooperating on one row group
   int64_t cta_blocks;   // row blocks of one CTA's worth of rows; CTAs stride over them
   int x_in_smem;    // activations staged in shared memory by the CTA
+  int ring_depth;   // stages of the per-warp cp.async ring (ring variant of the kernel), 0 = register prefetch
+  int ring_off;     // byte offset of the rings in dynamic shared memory (16-byte aligned)
   // indexed (expert bank) mode
   const void* const* bank_codes;
   const __half* const* bank_scales;
