@@ -149,17 +149,19 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     if (fcb < p.cta_blocks && iters_w > 0) fill_setup();
     for (int s = 0; s < p.ring_depth - 1; ++s) fill_one();
   }
-  // One-pass staging (rows of up to 256 * XU float4): a thread holds its XU pieces of the row in registers, so the
-  // loads are all in flight at once and the RMSNorm needs no second trip through shared memory. The norm gains are
-  // constants and are fetched here, ahead of the wait on the preceding kernel.
+  // One-pass staging (rows of up to threads * XU float4): a thread holds its XU pieces of the row in registers, so
+  // the loads are all in flight at once and the RMSNorm needs no second trip through shared memory. The norm gains
+  // are constants and are fetched here, ahead of the wait on the preceding kernel.
   constexpr int XU = 8;
   const int K4 = (int)(K >> 2);
-  const bool one_pass = p.x_in_smem && K4 <= 256 * XU && blockDim.x == 256 && ((uintptr_t)p.norm_gain & 15) == 0;
-  float4 gain4[XU];
+  const int nthreads = blockDim.x;
+  constexpr int GU = 8;                 // pieces per thread when the norm is fused (the gains ride along in registers)
+  const bool one_pass = p.x_in_smem && K4 <= nthreads * (p.norm_gain ? GU : XU) && ((uintptr_t)p.norm_gain & 15) == 0;
+  float4 gain4[GU];
   if (one_pass && p.norm_gain) {
 #pragma unroll
-    for (int u = 0; u < XU; ++u) {
-      const int c4 = threadIdx.x + u * 256;
+    for (int u = 0; u < GU; ++u) {
+      const int c4 = threadIdx.x + u * nthreads;
       gain4[u] = (c4 < K4) ? __ldg((const float4*)p.norm_gain + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     // 70 % of the shared-memory wavefronts of this kernel were conflict replays). So the pieces of a lane's
     // segment are stored XOR-ed with the segment index: x_phys() below, undone in the reads by `xsw`.
     red = smem_f + (int64_t)NB * K;
-    float* nred = red + (size_t)warps_per_cta * (RPW * NB);
+    float* nred = red + (size_t)2 * warps_per_cta * (RPW * NB);
     if (one_pass) {
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
@@ -205,27 +207,27 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
         float4 xv[XU];
 #pragma unroll
         for (int u = 0; u < XU; ++u) {
-          const int c4 = threadIdx.x + u * 256;
+          const int c4 = threadIdx.x + u * nthreads;
           xv[u] = (c4 < K4) ? __ldcg((const float4*)xg + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         if (p.norm_gain) {
           float ss = 0.f;
 #pragma unroll
-          for (int u = 0; u < XU; ++u) {
+          for (int u = 0; u < GU; ++u) {
             ss = fmaf(xv[u].x, xv[u].x, ss); ss = fmaf(xv[u].y, xv[u].y, ss);
             ss = fmaf(xv[u].z, xv[u].z, ss); ss = fmaf(xv[u].w, xv[u].w, ss);
           }
           ss = block_sum(ss, nred);
           const float inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
 #pragma unroll
-          for (int u = 0; u < XU; ++u) {
+          for (int u = 0; u < GU; ++u) {
             xv[u].x = gain4[u].x * (xv[u].x * inv); xv[u].y = gain4[u].y * (xv[u].y * inv);
             xv[u].z = gain4[u].z * (xv[u].z * inv); xv[u].w = gain4[u].w * (xv[u].w * inv);
           }
         }
 #pragma unroll
         for (int u = 0; u < XU; ++u) {
-          const int c4 = threadIdx.x + u * 256;
+          const int c4 = threadIdx.x + u * nthreads;
           if (c4 < K4) *(float4*)(smem_f + (int64_t)b * K + x_phys<TYPE>((int64_t)c4 * 4)) = xv[u];
         }
       }
@@ -256,9 +258,17 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
   }
 
   // persistent: this CTA takes row blocks blockIdx.x, blockIdx.x + gridDim.x, ...
+  int slot_set = 0;
   for (int64_t cb = blockIdx.x; cb < p.cta_blocks; cb += gridDim.x) {
     const int64_t gidx = cb * groups_per_cta + group;
     const int64_t unit0 = gidx * units_per_group;
+    // the residual a lane will add in the epilogue, fetched now so that its latency hides behind the strides
+    float resid_pre = 0.f;
+    if (p.epi == EPI_RESID && kpart == 0 && lane < RPW * NB) {
+      const int r = lane / NB, b = lane - r * NB;
+      if (unit0 + r < p.n && b0 + b < p.batch)
+        resid_pre = __ldcg(p.resid + (int64_t)(p.expert_ids ? pair : (b0 + b)) * p.ldy + unit0 + r);
+    }
     int64_t rows[RPW];
     if (swiglu) {
       const int64_t half = p.n >> 1;
@@ -388,7 +398,11 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     bool store = (unit0 < units_total);
     if (p.ksplit > 1) {
       // fixed-order combine of the KSPLIT warps of a group through shared memory
-      float* slot = red + (size_t)warp * (RPW * NB);
+      // (two sets of slots, alternating per row block: the warps that only contribute go straight on to the next
+      // block, whose partial sums land in the other set, so one barrier per block is enough)
+      const float* set = red + (size_t)slot_set * warps_per_cta * (RPW * NB);
+      float* slot = red + ((size_t)slot_set * warps_per_cta + warp) * (RPW * NB);
+      slot_set ^= 1;
       if (lane == 0) {
 #pragma unroll
         for (int r = 0; r < RPW; ++r)
@@ -402,15 +416,14 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
             float sum = 0.f;
-            for (int q = 0; q < p.ksplit; ++q) sum += red[(size_t)(group * p.ksplit + q) * (RPW * NB) + r * NB + b];
+            for (int q = 0; q < p.ksplit; ++q) sum += set[(size_t)(group * p.ksplit + q) * (RPW * NB) + r * NB + b];
             acc[r][b] = sum;
           }
       } else {
         store = false;
       }
-      __syncthreads();     // the slots are rewritten by the next row block
     }
-    if (store) gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
+    if (store) gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias, resid_pre, true);
   }
 }
 
@@ -491,12 +504,14 @@ static cudaError_t launch_one_b(cai_ctx* ctx, const GemvParams& p, dim3 grid, in
   // instantiation and shared-memory size), each walking several row blocks with the activations staged once
   static int cached_blocks = 0;
   static size_t cached_smem = (size_t)-1;
-  if (cached_smem != smem) {
+  static int cached_threads = 0;
+  if (cached_smem != smem || cached_threads != threads) {
     int nblk = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW, MINB, RING>, threads, smem);
     if (e != cudaSuccess) return e;
     cached_blocks = nblk < 1 ? 1 : nblk;
     cached_smem = smem;
+    cached_threads = threads;
   }
   const int64_t resident = (int64_t)ctx->sm_count * cached_blocks;
   int64_t gx = grid.x;
@@ -635,38 +650,43 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   if (nb == 8 && rpw == 4) rpw = 2;
   if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) ksplit = 1;
   p.ksplit = ksplit;
-  const int threads = 256;
-  const int wpc = threads / 32;
-  const int groups_per_cta = wpc / ksplit;
   const int units_per_group = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;
   const int64_t groups = (units + units_per_group - 1) / units_per_group;
-  p.cta_blocks = (groups + groups_per_cta - 1) / groups_per_cta;
-  // persistent grid: at most a few CTAs per SM, each walking several row blocks with the activations staged once
   const int64_t ydim = indexed ? a.batch : (a.batch + nb - 1) / nb;
-  dim3 grid((unsigned)p.cta_blocks, (unsigned)ydim);     // x is cut down to the resident CTA count at launch
   // activations in shared memory when they fit beside a healthy number of resident CTAs
   const size_t x_bytes = (size_t)nb * (size_t)w->k * 4;
   p.x_in_smem = (x_bytes <= (size_t)env_int("CAI_GEMV_XSMEM", 64 * 1024)) ? 1 : 0;
+  const bool ring_ok = !indexed && nb <= 2 && (w->k % 32) == 0 && (w->sstride % 8) == 0 && ((uintptr_t)w->scales % 16) == 0 &&
+                       ((uintptr_t)w->codes % 16) == 0;
+  int want = env_int("CAI_GEMV_RING", -1);
+  const size_t stage_warp = (size_t)rpw * (512 + lane_chunk * 2);      // ring bytes of one warp and stage
+  const int threads = 256;
+  const size_t smem_budget = 108 * 1024;         // two CTAs per SM
+  const int wpc = threads / 32;
+  const int groups_per_cta = wpc / ksplit;
+  p.cta_blocks = (groups + groups_per_cta - 1) / groups_per_cta;
+  // persistent grid: at most a few CTAs per SM, each walking several row blocks with the activations staged once
+  dim3 grid((unsigned)p.cta_blocks, (unsigned)ydim);     // x is cut down to the resident CTA count at launch
   if (a.norm_gain) {
     if (!p.x_in_smem) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: fused RMSNorm needs the activations to fit in shared memory");
     p.norm_gain = a.norm_gain; p.norm_eps = a.norm_eps;
   }
-  size_t smem = (p.x_in_smem ? x_bytes + 32 * sizeof(float) : 0) + (size_t)wpc * rpw * nb * sizeof(float);
-  // Ring variant: by default for single-row Q8_0 products whose activations sit in shared memory, 4 stages
-  // (measured on B200 against the register prefetch: 5120 x 152064 0.74 -> 0.84 of the copy peak, 5120 x 27648
-  // 0.63 -> 0.66; slower for K = 27648, whose activations live in L1 and lose it to the rings, for 2-row tiles
-  // and for Q4_0, which stay on registers). CAI_GEMV_RING=0 turns it off, N >= 2 forces up to N stages on every
-  // shape the variant covers (batch tiles of 1 and 2 rows, as many stages as fit with two CTAs per SM).
+  size_t smem = (p.x_in_smem ? x_bytes + 32 * sizeof(float) : 0) + (size_t)2 * wpc * rpw * nb * sizeof(float);
+  // Ring variant: by default for single-row Q8_0 products, 4 stages when the activations sit in shared memory,
+  // 3 when they are read through L1 (K = 27648: deeper rings take the L1 capacity the 108 KB row needs).
+  // Measured on B200 against the register prefetch: 5120 x 152064 0.74 -> 0.84 of the copy peak, 5120 x 55296
+  // 0.70 -> 0.77, 27648 x 5120 0.55 -> 0.58; slower for 2-row tiles and for Q4_0, which stay on registers.
+  // CAI_GEMV_RING=0 turns it off, N >= 2 forces up to N stages on every shape the variant covers (batch tiles of
+  // 1 and 2 rows, as many stages as fit). Also measured and not kept: an L2 prefetch of the first row block ahead
+  // of the dependency wait (-4 % on the whole 32B step), one 16-warp CTA per SM with the long row staged once
+  // (no gain), 9..13-warp CTAs for matrices between one and two 8-warp CTAs per SM (qkv slower, wo equal).
   {
-    int want = env_int("CAI_GEMV_RING", -1);
-    if (want < 0) want = (nb == 1 && w->type == CAI_TYPE_Q8_0 && p.x_in_smem) ? 4 : 0;
-    const size_t stage = (size_t)wpc * rpw * (512 + lane_chunk * 2);
+    if (want < 0) want = (nb == 1 && w->type == CAI_TYPE_Q8_0) ? (p.x_in_smem ? 4 : 3) : 0;
+    const size_t stage = (size_t)wpc * stage_warp;
     const size_t base = (smem + 15) & ~(size_t)15;
-    const size_t budget = 108 * 1024;
     int depth = 0;
-    if (want >= 2 && !indexed && nb <= 2 && (w->k % 32) == 0 && (w->sstride % 8) == 0 && ((uintptr_t)w->scales % 16) == 0 &&
-        ((uintptr_t)w->codes % 16) == 0 && base + 2 * stage <= budget) {
-      depth = (int)((budget - base) / stage);
+    if (want >= 2 && ring_ok && base + 2 * stage <= smem_budget) {
+      depth = (int)((smem_budget - base) / stage);
       if (depth > want) depth = want;
       if (depth > 8) depth = 8;
     }

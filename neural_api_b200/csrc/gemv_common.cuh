@@ -124,9 +124,11 @@ __device__ __forceinline__ float swish(float b) {
 
 // Writes the outputs of one row group. acc[r][b] are complete sums held by every
 // lane; lane `r*NB + b` (mod 32) does the store.
+// With resid_fetched, lane r*NB + b already holds the residual element of output (row unit0 + r, batch row b).
 template <int NB, int RPW>
 __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const float (&acc)[RPW][NB], int64_t unit0,
-                                              int b0, int pair, const float* bias) {
+                                              int b0, int pair, const float* bias, float resid_pre = 0.f,
+                                              bool resid_fetched = false) {
   const int lane = threadIdx.x & 31;
   if (p.epi == EPI_QKV_ROPE) {
     // rows come in (even, odd) pairs = the interleaved RoPE pairs (2k, 2k+1) of a head
@@ -191,7 +193,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const float (
         v = apply_act(v, p.act);
         const int64_t yrow = p.expert_ids ? pair : (b0 + b);
         if (p.row_scale) v *= p.row_scale[yrow];
-        if (p.epi == EPI_RESID) v += p.resid[yrow * p.ldy + row];
+        if (p.epi == EPI_RESID) v += resid_fetched ? resid_pre : p.resid[yrow * p.ldy + row];
         p.y[yrow * p.ldy + row] = v;
       }
     }
