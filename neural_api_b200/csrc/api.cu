@@ -74,8 +74,11 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
   }
   *ctx->err_flag = 0;
   {
+    // CAI_PDL=1 / 0 forces programmatic dependent launch on / off; unset, every session decides for its model
+    // (measured on B200: +11 % tokens/s on the 0.5B model, whose step is launch-bound, -5 % on the 32B model)
     const char* e = getenv("CAI_PDL");
-    ctx->use_pdl = (e && *e == '1') ? 1 : 0;   // measured neutral (0.5B) to 5 % slower (32B) on B200: off unless CAI_PDL=1
+    ctx->pdl_mode = (e && *e) ? ((*e == '1') ? 1 : 0) : -1;
+    ctx->use_pdl = ctx->pdl_mode == 1 ? 1 : 0;
   }
   *out_ctx = ctx;
   return CAI_OK;

@@ -41,6 +41,7 @@ struct cai_ctx {
   void* tc_xp_retired[32];   // outgrown buffers: captured graphs may still name them, so they live as long as the context
   int tc_xp_n_retired;
   int use_pdl;               // launch step kernels with programmatic dependent launch
+  int pdl_mode;              // 1 / 0: forced on / off by the environment, -1: each session decides
   // per-launch profiling (cai_session_profile): one event after every launch
   int prof_on;
   int cur_family;            // FAM_* of the launches being enqueued

@@ -617,6 +617,7 @@ struct cai_session {
   cudaGraphExec_t graph_exec = nullptr;
   int64_t graph_kernels = 0;
   bool use_graph = true;
+  int use_pdl = 0;            // programmatic dependent launch for this session's step kernels
   std::vector<float> host_gather;
 };
 
@@ -657,6 +658,7 @@ __global__ void advance_kernel(int32_t* tokens, int32_t* pos, int32_t* len, cons
 }
 
 static int enqueue_step(cai_session* s) {
+  s->ctx->use_pdl = s->use_pdl;
   cai_model* m = s->m;
   cai_ctx* ctx = s->ctx;
   const cai_llama_config& c = m->cfg;
@@ -942,6 +944,10 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   m->sessions += 1;
   const char* ng = getenv("CAI_NO_GRAPH");
   s->use_graph = !(ng && *ng && *ng != '0');
+  // Programmatic dependent launch pays when the step is a chain of short kernels (the next kernel's CTAs are
+  // resident and primed when the previous one drains); on the 32B model, whose kernels each stream > 100 MB, it
+  // measured slower. Rule: on when one layer's MLP weights are below 24 M elements.
+  s->use_pdl = ctx->pdl_mode >= 0 ? ctx->pdl_mode : (((int64_t)c.hidden * m->inter_l * 3 < ((int64_t)24 << 20)) ? 1 : 0);
   const int B = batch, H = c.hidden, QKVW = m->qw_l + 2 * m->kw_l;
   s->nsplit = attn_nsplit(ctx, B, m->kv_heads_l, max_ctx);
   s->trace_cap = (int64_t)max_ctx * B;
