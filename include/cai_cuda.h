@@ -72,6 +72,15 @@ int cai_cuda_last_error(cai_ctx* ctx, char* buf, int buf_len);
 int cai_cuda_device_info(cai_ctx* ctx, int* sm_count, int64_t* total_bytes);
 /* Number of kernels this library has launched on the context since init. */
 int cai_cuda_launch_count(cai_ctx* ctx, int64_t* out_count);
+/* Longest time a kernel of this library waits on another CTA or another GPU (grid barrier of the step kernel,
+ * arrival words of the tensor-parallel exchange) before it gives up, raises the context's error word and returns;
+ * the next synchronizing entry point then reports CAI_ERR_CUDA and the context stays usable. Default 2 s
+ * (environment CAI_WAIT_LIMIT_US). No reference counterpart: the OpenCL backend has no device-side waits. */
+int cai_cuda_set_wait_limit_us(cai_ctx* ctx, unsigned limit_us);
+/* Failure-path self-test: makes one such wait run out on purpose (no peer needed, nothing hangs).
+ * which = 0: the all-reduce kernel waiting for a rank that does not exist; 1: the step kernel's grid barrier with one
+ * arrival missing. Returns CAI_ERR_CUDA when the time-out path worked as designed. No reference counterpart. */
+int cai_selftest_wait_timeout(cai_ctx* ctx, int which, unsigned limit_us);
 
 /* Device buffers: the cl_mem create/write/read calls of TEasyOpenCLV
  * (neural/neuralopencl.pas:167-202). */
@@ -168,7 +177,10 @@ int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev);
  * CAI_ERR_UNSUPPORTED. The call performs no cudaMalloc / cudaFree and launches on the context's stream
  * without synchronizing. Its first call on a device looks up the array's device address; make that
  * first call before any stream capture. All calls share the array: two calls that overlap on the GPU
- * (different streams, different contexts on one device) race; nothing in it needs clearing between calls. */
+ * (different streams, different contexts on one device) race; nothing in it needs clearing between calls.
+ * Precondition: 0 <= *cache_len_dev < max_ctx (there must be room for the row this call appends). The host
+ * cannot see that word, so the kernels check it: outside the range they touch neither cache nor output and raise
+ * the context's error word, which cai_dev_sync then reports as CAI_ERR_STATE. */
 int cai_sdpa_step_noalloc(cai_ctx* ctx, float* qkv_row_dev, float* k_cache_dev, float* v_cache_dev,
                           const int32_t* cache_len_dev, int q_heads, int kv_heads, int head_dim, int max_ctx,
                           float* out_dev);
@@ -271,6 +283,10 @@ int cai_session_snapshot(cai_session* s);
 int cai_session_restore(cai_session* s);
 /* Device logits of the last step, [batch*vocab] (this rank's shard when tp_size > 1). */
 int cai_session_logits_dev(cai_session* s, const float** out_dev);
+/* 1 when the session runs each step as ONE persistent kernel (dense model, one sequence, Q8_0 weights, fp32 cache,
+ * head_dim 64 or 128; environment CAI_STEP_KERNEL=0 turns it off), 0 when it enqueues one kernel per operator the way
+ * the reference enqueues one OpenCL kernel per layer (neural/neuralopencl.pas:946-1056). */
+int cai_session_uses_step_kernel(cai_session* s, int* out_flag);
 /* Bytes of KV cache the last step read (for the roofline arithmetic). */
 int cai_session_last_kv_bytes(cai_session* s, int64_t* out_bytes);
 

@@ -44,6 +44,8 @@ SIGNATURES = {
     "cai_cuda_last_error": [_P, C.c_char_p, _I],
     "cai_cuda_device_info": [_P, C.POINTER(_I), C.POINTER(_I64)],
     "cai_cuda_launch_count": [_P, C.POINTER(_I64)],
+    "cai_cuda_set_wait_limit_us": [_P, C.c_uint],
+    "cai_selftest_wait_timeout": [_P, _I, C.c_uint],
     "cai_dev_alloc": [_P, _I64, _PP],
     "cai_dev_free": [_P, _P],
     "cai_memcpy_h2d": [_P, _P, _P, _I64],
@@ -92,6 +94,7 @@ SIGNATURES = {
     "cai_session_snapshot": [_P],
     "cai_session_restore": [_P],
     "cai_session_logits_dev": [_P, _PP],
+    "cai_session_uses_step_kernel": [_P, C.POINTER(_I)],
     "cai_session_last_kv_bytes": [_P, C.POINTER(_I64)],
     "cai_comm_unique_id": [_P],
     "cai_comm_init": [_P, _I, _I, _P],

@@ -98,6 +98,14 @@ class CudaBackend:
     def sync(self):
         self._check(self.lib.cai_dev_sync(self.ctx))
 
+    def set_wait_limit_us(self, limit_us):
+        """Longest device-side wait on another CTA or GPU before a kernel gives up and raises the error word."""
+        self._check(self.lib.cai_cuda_set_wait_limit_us(self.ctx, int(limit_us)))
+
+    def selftest_wait_timeout(self, which, limit_us):
+        """Makes one bounded device-side wait run out on purpose; returns the status the library reports for it."""
+        return int(self.lib.cai_selftest_wait_timeout(self.ctx, int(which), int(limit_us)))
+
     def timer_begin(self):
         self._check(self.lib.cai_timer_begin(self.ctx))
 
@@ -423,6 +431,13 @@ class StreamingDecoder:
 
     def restore_snapshot(self):
         self.backend._check(self.backend.lib.cai_session_restore(self.handle))
+
+    @property
+    def uses_step_kernel(self):
+        """True when every step of this session is one persistent kernel (False: one kernel per operator)."""
+        f = C.c_int()
+        self.backend._check(self.backend.lib.cai_session_uses_step_kernel(self.handle, C.byref(f)))
+        return bool(f.value)
 
     def last_kv_bytes(self):
         n = C.c_int64()

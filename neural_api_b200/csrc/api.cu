@@ -17,7 +17,12 @@ int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...) {
 
 int cai_check_device_error(cai_ctx* ctx) {
   if (ctx->err_flag && *(volatile int*)ctx->err_flag) {
+    const int code = *(volatile int*)ctx->err_flag;
     *ctx->err_flag = 0;
+    if (code == 2)
+      return cai_fail(ctx, CAI_ERR_STATE, "a kernel refused a cache length outside [0, max_ctx): nothing was appended or attended");
+    if (code == 3)
+      return cai_fail(ctx, CAI_ERR_INVALID, "a kernel met a router row without a finite maximum (NaN logits): expert ids were clamped");
     return cai_fail(ctx, CAI_ERR_CUDA, "a kernel gave up a bounded wait (device error word raised)");
   }
   return CAI_OK;
@@ -73,6 +78,7 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
     return CAI_ERR_CUDA;
   }
   *ctx->err_flag = 0;
+  ctx->wait_limit_us = (unsigned)env_int("CAI_WAIT_LIMIT_US", 2000000);
   {
     // CAI_PDL=1 / 0 forces programmatic dependent launch on / off; unset, every session decides for its model
     // (measured on B200: +11 % tokens/s on the 0.5B model, whose step is launch-bound, -5 % on the 32B model)
@@ -81,6 +87,12 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
     ctx->use_pdl = ctx->pdl_mode == 1 ? 1 : 0;
   }
   *out_ctx = ctx;
+  return CAI_OK;
+}
+
+int cai_cuda_set_wait_limit_us(cai_ctx* ctx, unsigned limit_us) {
+  if (!ctx || limit_us < 1) return CAI_ERR_INVALID;
+  ctx->wait_limit_us = limit_us;
   return CAI_OK;
 }
 

@@ -28,7 +28,18 @@ struct AttnParams {
   int min_chunk;          // fewest cached rows a context split covers (set by the launcher for the kernel it picked)
   int8_t* k_codes; int8_t* v_codes; float* k_scales; float* v_scales;     // int8 cache (k_codes != NULL)
   const int32_t* seq_index;                                               // cache sequence of each batch row (NULL = the row itself)
+  int* err;               // device-visible error word: 2 = a cache length outside [0, max_ctx) was refused
 };
+
+// The number of cached rows comes from a device word the host cannot always vouch for (the allocation-free entry
+// point's caller owns it). A length outside [0, max_ctx) would put the appended row, and the rows the decode
+// kernels walk, outside the cache: refuse it (no access at all), raise the error word, and let every kernel of the
+// step leave in the same way.
+__device__ __forceinline__ bool attn_len_ok(const AttnParams& p, int len) {
+  if (len >= 0 && len < p.max_ctx) return true;
+  if (threadIdx.x == 0 && p.err) *p.err = 2;
+  return false;
+}
 
 // Rows per context split: the context spread over nsplit splits, at least min_chunk rows, a multiple of 32.
 // Short contexts use few splits; the other CTAs leave at once. Decode and combine kernels both use this.
@@ -48,7 +59,7 @@ __global__ void rope_append_kernel(const AttnParams p) {
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
   float* row = p.qkv + (int64_t)b * p.ld;
   const int slot = p.cache_len[b];
-  if (slot >= p.max_ctx) return;
+  if (!attn_len_ok(p, slot)) return;
   float inv_q = 1.f, inv_k = 1.f;
   if (p.q_norm) {
     float ss = 0.f;
@@ -113,7 +124,7 @@ __global__ void rope_append_int8_kernel(const AttnParams p) {
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
   float* row = p.qkv + (int64_t)b * p.ld;
   const int slot = p.cache_len[b];
-  if (slot >= p.max_ctx) return;
+  if (!attn_len_ok(p, slot)) return;
   float inv_q = 1.f, inv_k = 1.f;
   if (p.q_norm) {
     float ss = 0.f;
@@ -205,6 +216,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
   int nd = hd - d0; nd = nd > 8 ? 8 : (nd < 0 ? 0 : nd);
   const bool vec = (nd == 8) && ((hd & 3) == 0);
 
+  if (!attn_len_ok(p, p.cache_len[b])) return;
   const int n = p.cache_len[b] + 1;                  // keys after the append
   const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
   const int used = (n + chunk - 1) / chunk;
@@ -381,6 +393,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
   pdl_wait();
   const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!attn_len_ok(p, p.cache_len[b])) return;
   const int n = p.cache_len[b] + 1;                    // rows after the append
   const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
   const int used = (n + chunk - 1) / chunk;
@@ -549,6 +562,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
   pdl_wait();
   const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (!attn_len_ok(p, p.cache_len[b])) return;
   const int n = p.cache_len[b] + 1;
   const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
   const int used = (n + chunk - 1) / chunk;
@@ -721,6 +735,7 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   const int h = blockIdx.x, b = blockIdx.y;
   const int hd = p.head_dim;
   const float* src = p.partial + ((int64_t)b * p.q_heads + h) * (int64_t)p.nsplit * (hd + 2);
+  if (!attn_len_ok(p, p.cache_len[b])) return;
   const int n = p.cache_len[b] + 1;
   const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
   const int used = (n + chunk - 1) / chunk;
@@ -755,8 +770,9 @@ size_t attn_partial_floats(int batch, int q_heads, int nsplit, int head_dim) {
   return (size_t)batch * q_heads * nsplit * (head_dim + 2);
 }
 
-static AttnParams to_params(const AttnArgs& a) {
+static AttnParams to_params(cai_ctx* ctx, const AttnArgs& a) {
   AttnParams p;
+  p.err = ctx->err_flag;
   p.qkv = a.qkv; p.ld = a.ld; p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.cache_len = a.cache_len_dev;
   p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.head_dim = a.head_dim; p.max_ctx = a.max_ctx;
   p.theta = a.theta; p.pos = a.pos_dev; p.q_norm = a.q_norm; p.k_norm = a.k_norm; p.eps = a.eps;
@@ -779,11 +795,11 @@ int attn_rope_append(cai_ctx* ctx, const AttnArgs& a) {
   if (a.k_codes) {
     const size_t smem = (size_t)2 * a.kv_heads * a.head_dim * sizeof(float);
     if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 KV append: %d kv heads x %d dims exceed shared memory", a.kv_heads, a.head_dim);
-    pdl_launch(ctx, rope_append_int8_kernel, dim3(a.batch), dim3(256), smem, to_params(a));
+    pdl_launch(ctx, rope_append_int8_kernel, dim3(a.batch), dim3(256), smem, to_params(ctx, a));
     CAI_LAUNCHED(ctx);
     return CAI_OK;
   }
-  pdl_launch(ctx, rope_append_kernel, dim3(a.batch), dim3(256), 0, to_params(a));
+  pdl_launch(ctx, rope_append_kernel, dim3(a.batch), dim3(256), 0, to_params(ctx, a));
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -796,7 +812,7 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
   const int G = a.q_heads / a.kv_heads;
   int lpk = 1;
   while (lpk * 8 < a.head_dim) lpk <<= 1;
-  AttnParams p = to_params(a);
+  AttnParams p = to_params(ctx, a);
   dim3 grid(a.kv_heads, a.nsplit, a.batch);
   static const int use_tile = [] { const char* e = getenv("CAI_ATTN_TILE"); return (e && *e) ? atoi(e) : 1; }();
   if (a.k_codes) {

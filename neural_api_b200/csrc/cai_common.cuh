@@ -35,7 +35,9 @@ struct cai_ctx {
   int* gemv_tickets;
   int gemv_ticket_cap;
   int gemv_scratch_ctas;
-  int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out
+  int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out (1), that refused a
+                             // cache length outside the cache (2) or that met an unusable router row (3)
+  unsigned wait_limit_us;    // how long a device-side wait on another CTA or GPU may last before it gives up
   void* tc_xp;               // tensor-core GEMM: activations split into bf16 limbs, tiled (gemm_tc_reserve)
   size_t tc_xp_bytes;
   void* tc_xp_retired[32];   // outgrown buffers: captured graphs may still name them, so they live as long as the context
@@ -276,6 +278,12 @@ static inline cudaError_t pdl_launch(cai_ctx* ctx, void (*kernel)(KArgs...), dim
   attr[0].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
   cfg.attrs = attr; cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+// Nanoseconds of the GPU's global timer: the clock the bounded waits measure themselves against.
+__device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

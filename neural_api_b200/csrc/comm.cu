@@ -1,5 +1,6 @@
 // Multi-GPU plumbing: one process per GPU, NCCL communicator on the context's stream.
 #include "cai_common.cuh"
+#include "step_kernel.cuh"
 #include <nccl.h>
 
 struct cai_comm_state {
@@ -65,7 +66,7 @@ int comm_reduce_scatter(cai_ctx* ctx, const float* send, float* recv, int64_t co
 struct cai_tp_ar {
   char* block = nullptr;          // [flags: 64 ints][slots: sites * max_elems floats], cudaMalloc'd, IPC-exported
   void* peer_block[8] = {nullptr};
-  int* seq_dev = nullptr;         // calls completed so far
+  int* seq_dev = nullptr;         // [0] calls completed so far, [1] "a wait ran out" word
   int* ticket_dev = nullptr;
   int sites = 0;
   int64_t max_elems = 0;
@@ -83,6 +84,8 @@ struct ArParams {
   const float4* resid;
   float4* out;
   int* err;
+  int* gave_up;            // device word of this rank: set by the first wait that ran out
+  unsigned wait_limit_us;
 };
 
 __global__ void tp_allreduce_kernel(const ArParams p) {
@@ -95,12 +98,18 @@ __global__ void tp_allreduce_kernel(const ArParams p) {
     *(volatile int*)(p.peer_flags[threadIdx.x] + p.rank) = seq;
   }
   if (threadIdx.x < p.world) {
+    // Bounded wait, measured on the global timer. Once a wait of this rank has run out, later calls do not wait
+    // again (a missing peer must cost one time limit, not one per call site of every step).
     const volatile int* f = (const volatile int*)(p.my_flags + threadIdx.x);
-    bool ok = false;
-    for (int spin = 0; spin < (1 << 26); ++spin) {
-      if (*f >= seq) { ok = true; break; }
+    bool ok = *f >= seq;
+    if (!ok && *(volatile int*)p.gave_up == 0) {
+      const unsigned long long t0 = gtime_ns(), limit = (unsigned long long)p.wait_limit_us * 1000ull;
+      while (true) {
+        if (*f >= seq) { ok = true; break; }
+        if (gtime_ns() - t0 > limit) break;
+      }
     }
-    if (!ok) *p.err = 1;                                      // give up: the host sees the error word
+    if (!ok) { *p.err = 1; *(volatile int*)p.gave_up = 1; }   // give up: the host sees the error word
   }
   __syncthreads();
   __threadfence_system();
@@ -148,23 +157,26 @@ int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out) 
   ar->sites = sites; ar->max_elems = max_elems; ar->rank = rank; ar->world = world;
   const size_t bytes = AR_FLAG_BYTES + (size_t)sites * (size_t)max_elems * sizeof(float);
   cudaIpcMemHandle_t mine;
+  memset(&mine, 0, sizeof(mine));
   cudaIpcMemHandle_t* all_dev = nullptr;
   std::vector<cudaIpcMemHandle_t> all((size_t)world);
   int ok = 1;
   if (cudaMalloc((void**)&ar->block, bytes) != cudaSuccess || cudaMemset(ar->block, 0, bytes) != cudaSuccess ||
-      cudaMalloc((void**)&ar->seq_dev, 4) != cudaSuccess || cudaMemset(ar->seq_dev, 0, 4) != cudaSuccess ||
+      cudaMalloc((void**)&ar->seq_dev, 8) != cudaSuccess || cudaMemset(ar->seq_dev, 0, 8) != cudaSuccess ||
       cudaMalloc((void**)&ar->ticket_dev, 4) != cudaSuccess || cudaMemset(ar->ticket_dev, 0, 4) != cudaSuccess ||
-      cudaIpcGetMemHandle(&mine, ar->block) != cudaSuccess ||
-      cudaMalloc((void**)&all_dev, sizeof(cudaIpcMemHandle_t) * (size_t)world) != cudaSuccess)
+      cudaIpcGetMemHandle(&mine, ar->block) != cudaSuccess)
     ok = 0;
   cudaGetLastError();
-  // the handle exchange is collective: run it even after a local failure so that no rank is left waiting
+  // The handle exchange is collective and must run on every rank whatever happened above, or the others would be left
+  // waiting inside the library: it goes through the context's upload staging buffer (allocated at start-up or here;
+  // if even that fails the rank has no device memory at all and the communicator is lost anyway).
+  if (cai_ensure_staging(ctx, sizeof(cudaIpcMemHandle_t) * (size_t)world) == CAI_OK) all_dev = (cudaIpcMemHandle_t*)ctx->staging_dev;
+  else ok = 0;
   if (all_dev) {
-    if (ok) cudaMemcpy(all_dev + rank, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    cudaMemcpy(all_dev + rank, &mine, sizeof(mine), cudaMemcpyHostToDevice);
     if (ncclAllGather(all_dev + rank, all_dev, sizeof(cudaIpcMemHandle_t), ncclInt8, ctx->comm->comm, ctx->stream) != ncclSuccess) ok = 0;
     if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) ok = 0;
     if (ok) cudaMemcpy(all.data(), all_dev, sizeof(cudaIpcMemHandle_t) * (size_t)world, cudaMemcpyDeviceToHost);
-    cudaFree(all_dev);
   }
   if (ok) {
     ar->peer_block[rank] = ar->block;
@@ -189,6 +201,22 @@ int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out) 
   return CAI_OK;
 }
 
+// The raw view of the exchange buffers for kernels that do the flag protocol themselves (the persistent step kernel).
+int comm_ar_exchange(cai_tp_ar* ar, TpExchange* out) {
+  if (!ar || !out) return CAI_ERR_INVALID;
+  memset(out, 0, sizeof(*out));
+  out->rank = ar->rank; out->world = ar->world;
+  out->my_flags = (int*)ar->block;
+  out->my_slots = (float*)(ar->block + AR_FLAG_BYTES);
+  for (int r = 0; r < ar->world; ++r) {
+    out->peer_flags[r] = (int*)ar->peer_block[r];
+    out->peer_slots[r] = (const float*)((char*)ar->peer_block[r] + AR_FLAG_BYTES);
+  }
+  out->max_elems = ar->max_elems; out->sites = ar->sites;
+  out->seq = ar->seq_dev; out->gave_up = ar->seq_dev + 1;
+  return CAI_OK;
+}
+
 float* comm_ar_slot(cai_tp_ar* ar, int site) {
   return (float*)(ar->block + AR_FLAG_BYTES) + (size_t)site * (size_t)ar->max_elems;
 }
@@ -202,9 +230,9 @@ int comm_ar_reduce(cai_ctx* ctx, cai_tp_ar* ar, int site, int64_t n, const float
     p.peer_flags[r] = (int*)ar->peer_block[r];
     p.peer_slot[r] = (const float*)((char*)ar->peer_block[r] + AR_FLAG_BYTES) + (size_t)site * (size_t)ar->max_elems;
   }
-  p.my_flags = (int*)ar->block; p.seq = ar->seq_dev; p.ticket = ar->ticket_dev;
+  p.my_flags = (int*)ar->block; p.seq = ar->seq_dev; p.gave_up = ar->seq_dev + 1; p.ticket = ar->ticket_dev;
   p.rank = ar->rank; p.world = ar->world; p.n4 = (int)(n / 4);
-  p.resid = (const float4*)resid; p.out = (float4*)out; p.err = ctx->err_flag;
+  p.resid = (const float4*)resid; p.out = (float4*)out; p.err = ctx->err_flag; p.wait_limit_us = ctx->wait_limit_us;
   // one 16-byte element per thread while that fits the machine: a remote load costs ~2 us, so a thread should not
   // walk many of them (at batch 64 the 16-block cap this used to have made a 1.3 MB reduction take ~60 us)
   int blocks = (p.n4 + 255) / 256;
@@ -216,7 +244,45 @@ int comm_ar_reduce(cai_ctx* ctx, cai_tp_ar* ar, int site, int64_t n, const float
   return CAI_OK;
 }
 
+int step_barrier_selftest(cai_ctx* ctx, unsigned limit_us);   // step_kernel.cu
+
 extern "C" {
+
+// Makes a device-side bounded wait run out on purpose, without any peer and without hanging anything:
+//   which = 0: the tensor-parallel all-reduce kernel as rank 0 of a world of 2 whose second rank does not exist (its
+//              arrival word is a local buffer nobody writes);
+//   which = 1: the grid barrier of the persistent step kernel with one arrival more expected than CTAs launched.
+// Each gives up after limit_us, raises the context's error word and returns; the status is what the next
+// synchronizing call would report (CAI_ERR_CUDA when the time-out path worked).
+int cai_selftest_wait_timeout(cai_ctx* ctx, int which, unsigned limit_us) {
+  CAI_TRY(cai_bind(ctx));
+  if (limit_us < 1 || limit_us > 5000000) return cai_fail(ctx, CAI_ERR_INVALID, "cai_selftest_wait_timeout: limit %u us outside 1..5000000", limit_us);
+  if (which == 1) return step_barrier_selftest(ctx, limit_us);
+  if (which != 0) return cai_fail(ctx, CAI_ERR_INVALID, "cai_selftest_wait_timeout: which = %d", which);
+  char* buf = nullptr;
+  const size_t bytes = 2 * AR_FLAG_BYTES + 2 * 64 * sizeof(float) + 64;
+  CAI_CUDA(ctx, cudaMalloc((void**)&buf, bytes));
+  CAI_CUDA(ctx, cudaMemsetAsync(buf, 0, bytes, ctx->stream));
+  ArParams p;
+  memset(&p, 0, sizeof(p));
+  p.my_flags = (int*)buf;                              // [0] is raised by the kernel itself, [1] by nobody
+  p.peer_flags[0] = (int*)buf;
+  p.peer_flags[1] = (int*)(buf + AR_FLAG_BYTES);       // the missing rank's words: local, never read
+  p.peer_slot[0] = (const float*)(buf + 2 * AR_FLAG_BYTES);
+  p.peer_slot[1] = p.peer_slot[0] + 64;
+  p.seq = (int*)(buf + 2 * AR_FLAG_BYTES + 2 * 64 * sizeof(float));
+  p.gave_up = p.seq + 1; p.ticket = p.seq + 2;
+  p.rank = 0; p.world = 2; p.n4 = 16;
+  p.resid = nullptr; p.out = (float4*)(buf + 2 * AR_FLAG_BYTES);
+  p.err = ctx->err_flag; p.wait_limit_us = limit_us;
+  tp_allreduce_kernel<<<1, 256, 0, ctx->stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  cudaFree(buf);
+  if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "all-reduce self-test -> %s", cudaGetErrorString(e));
+  ctx->launches++;
+  return cai_check_device_error(ctx);
+}
 
 int cai_comm_unique_id(unsigned char out_id[128]) {
   if (!out_id) return CAI_ERR_INVALID;

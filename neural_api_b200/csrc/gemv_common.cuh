@@ -104,6 +104,41 @@ __device__ __forceinline__ f32x2_t q4_word_fma(uint32_t w, const float4& xlo, co
   return acc;
 }
 
+// Position of activation k (a multiple of 4) in the staged, swizzled row: within each lane segment (16 floats for
+// Q8_0, 32 for Q4_0) the 16-byte pieces are XOR-ed with the segment index, so a quarter-warp's reads of piece i
+// fall on 8 different bank groups.
+template <int TYPE>
+__device__ __forceinline__ int64_t x_phys(int64_t k) {
+  if (TYPE == CAI_TYPE_Q8_0) return (k & ~(int64_t)12) | ((((k >> 2) & 3) ^ ((k >> 5) & 3)) << 2) | (k & 3);
+  return (k & ~(int64_t)28) | ((((k >> 2) & 7) ^ ((k >> 5) & 7)) << 2) | (k & 3);
+}
+
+// cp.async pieces of the ring variant (16 bytes, L2 only; a source size of 0 zero-fills the destination)
+__device__ __forceinline__ void gv_cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void gv_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most depth-2 of this thread's copy groups are still in flight
+__device__ __forceinline__ void gv_cp_async_wait_depth(int depth) {
+  if (depth >= 8) asm volatile("cp.async.wait_group 6;" ::: "memory");
+  else if (depth == 7) asm volatile("cp.async.wait_group 5;" ::: "memory");
+  else if (depth == 6) asm volatile("cp.async.wait_group 4;" ::: "memory");
+  else if (depth == 5) asm volatile("cp.async.wait_group 3;" ::: "memory");
+  else if (depth == 4) asm volatile("cp.async.wait_group 2;" ::: "memory");
+  else if (depth == 3) asm volatile("cp.async.wait_group 1;" ::: "memory");
+  else asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ int4 gv_lds16(uint32_t addr) {
+  int4 v;
+  asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t gv_lds_u16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
 __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == CAI_ACT_RELU) return v > 0.f ? v : 0.f;
   if (act == CAI_ACT_SIGMOID) {

@@ -6,6 +6,7 @@
 // matrix with the up rows first and the gate rows second, experts laid out the
 // same way per expert.
 #include "cai_common.cuh"
+#include "step_kernel.cuh"
 #include <new>
 #include <math.h>
 #include <stdlib.h>
@@ -619,6 +620,9 @@ struct cai_session {
   bool use_graph = true;
   int use_pdl = 0;            // programmatic dependent launch for this session's step kernels
   std::vector<float> host_gather;
+  // one persistent kernel per step (dense, one sequence, Q8_0, fp32 cache); NULL = one launch per operator
+  StepPlan* plan = nullptr;
+  unsigned long long* plan_ts = nullptr;              // device buffer of the phase trace (cai_session_profile)
 };
 
 __global__ void pack_argmax_kernel(const int32_t* idx, const float* val, int batch, int offset, float* pack) {
@@ -661,6 +665,7 @@ static int enqueue_step(cai_session* s) {
   s->ctx->use_pdl = s->use_pdl;
   cai_model* m = s->m;
   cai_ctx* ctx = s->ctx;
+  if (s->plan) return step_plan_enqueue(ctx, s->plan, nullptr);
   const cai_llama_config& c = m->cfg;
   const int B = s->batch, H = c.hidden;
   const int QKVW = m->qw_l + 2 * m->kw_l;
@@ -848,7 +853,7 @@ static int enqueue_step(cai_session* s) {
 // Runs one step: through the captured CUDA graph when enabled, else eagerly.
 static int run_step(cai_session* s) {
   cai_ctx* ctx = s->ctx;
-  if (!s->use_graph) return enqueue_step(s);
+  if (!s->use_graph || s->plan) return enqueue_step(s);     // the persistent step kernel is one launch: a graph adds nothing
   if (!s->graph_exec) {
     const int64_t before = ctx->launches;
     cudaGraph_t graph = nullptr;
@@ -877,6 +882,19 @@ static int push_len(cai_session* s) {
   return CAI_OK;
 }
 
+// Reports a raised device error word; a step kernel that gave up a wait leaves its barrier words behind, which are
+// cleared here so that the session stays usable.
+static int session_check(cai_session* s) {
+  const int st = cai_check_device_error(s->ctx);
+  if (st != CAI_OK && s->plan) {
+    char keep[sizeof(s->ctx->err)];
+    memcpy(keep, s->ctx->err, sizeof(keep));
+    step_plan_reset_sync(s->ctx, s->plan);
+    memcpy(s->ctx->err, keep, sizeof(keep));
+  }
+  return st;
+}
+
 static int check_room(cai_session* s, int steps) {
   for (int b = 0; b < s->batch; ++b)
     if (s->len_host[(size_t)b] + steps > s->max_ctx)
@@ -893,6 +911,8 @@ int cai_session_destroy(cai_session* s) {
   cudaStreamSynchronize(s->ctx->stream);
   if (s->wide) { cai_session_destroy(s->wide); s->wide = nullptr; }
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
+  if (s->plan) step_plan_destroy(s->plan);
+  if (s->plan_ts) cudaFree(s->plan_ts);
   if (s->ar) comm_ar_destroy(s->ctx, s->ar);
   if (s->kv_owner) { s->k_cache = s->v_cache = nullptr; s->k_scales = s->v_scales = nullptr; }   // borrowed
   void* bufs[] = {s->seq_index_dev, s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
@@ -967,7 +987,16 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   A((void**)&s->act, (size_t)B * (m->inter_l ? m->inter_l : 1) * 4);
   A((void**)&s->logits, (size_t)B * m->vocab_l * 4);
   if (B >= 3 && B <= 64 && m->inter_l) A((void**)&s->gu, (size_t)B * 2 * m->inter_l * 4);
-  A((void**)&s->partial, attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim) * 4);
+  size_t partial_floats = attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim);
+  if (B == 1) {
+    // the persistent step kernel deals about one (kv head, context split) item to every SM
+    int ns = ctx->sm_count / m->kv_heads_l;
+    if (ns > (max_ctx + 31) / 32) ns = (max_ctx + 31) / 32;
+    if (ns < 1) ns = 1;
+    const size_t need = attn_partial_floats(1, m->heads_l, ns, c.head_dim);
+    if (need > partial_floats) partial_floats = need;
+  }
+  A((void**)&s->partial, partial_floats * 4);
   A((void**)&s->amax_idx, (size_t)B * 4); A((void**)&s->amax_val, (size_t)B * 4);
   A((void**)&s->amax_part_val, (size_t)B * CAI_ARGMAX_CHUNKS * 4); A((void**)&s->amax_part_idx, (size_t)B * CAI_ARGMAX_CHUNKS * 4);
   A((void**)&s->amax_tickets, (size_t)B * 4); A((void**)&s->rope_cs, (size_t)B * c.head_dim * 4);
@@ -1012,7 +1041,7 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   }
   if (ok && !kv_owner && m->tp_size > 1 && ((int64_t)B * H) % 4 == 0) {
     // collective: every rank creates its session at the same point
-    if (comm_ar_create(ctx, 2 * c.layers, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
+    if (comm_ar_create(ctx, 2 * c.layers + 1, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
   }
   if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)4 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
   if (ok && B >= 3 && B <= 64) {
@@ -1029,6 +1058,28 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   CAI_CUDA(ctx, cudaMemsetAsync(s->trace_count, 0, 4, ctx->stream));
   CAI_CUDA(ctx, cudaMemsetAsync(s->amax_tickets, 0, (size_t)B * 4, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (B == 1 && !kv_owner && !kv_int8 && !c.n_experts && !c.qk_norm && (m->tp_size == 1 || s->ar)) {
+    // the whole step as one persistent kernel when the model is inside what it covers; otherwise (status
+    // CAI_ERR_UNSUPPORTED) the session keeps one launch per operator
+    StepSetup u;
+    u.layers = c.layers; u.hidden = H; u.q_heads = m->heads_l; u.kv_heads = m->kv_heads_l; u.head_dim = c.head_dim;
+    u.inter = m->inter_l; u.vocab = m->vocab_l; u.max_ctx = max_ctx; u.rms_eps = c.rms_eps;
+    u.embed = &m->embed; u.lm_head = &m->lm_head; u.final_norm = m->final_norm; u.theta = m->theta;
+    u.layer.resize((size_t)c.layers);
+    for (int l = 0; l < c.layers; ++l) {
+      LayerW& L = m->layers[(size_t)l];
+      StepLayerSetup& d = u.layer[(size_t)l];
+      d.wqkv = &L.wqkv; d.wo = &L.wo; d.wgu = &L.wgu; d.wdown = &L.wdown; d.attn_norm = L.attn_norm; d.ffn_norm = L.ffn_norm;
+      d.k_cache = s->k_cache + (size_t)l * s->layer_stride; d.v_cache = s->v_cache + (size_t)l * s->layer_stride;
+    }
+    u.tokens = s->tokens_dev; u.pos = s->pos_dev; u.len = s->len_dev;
+    u.xres = s->x; u.qbuf = s->qkv; u.att = s->att; u.act = s->act; u.logits = s->logits; u.partial = s->partial;
+    u.partial_floats = partial_floats;
+    u.amax_idx = s->amax_idx; u.amax_val = s->amax_val; u.trace = s->trace; u.trace_count = s->trace_count; u.trace_cap = s->trace_cap;
+    u.ar = s->ar; u.tp_rank = m->tp_rank; u.tp_world = m->tp_size; u.vocab_offset = m->tp_rank * m->vocab_l;
+    const int st = step_plan_create(ctx, u, &s->plan);
+    if (st != CAI_OK && st != CAI_ERR_UNSUPPORTED) { cai_session_destroy(s); return cai_fail(ctx, st, "step kernel set-up failed"); }
+  }
   *out = s;
   return CAI_OK;
 }
@@ -1095,7 +1146,7 @@ int cai_session_step(cai_session* s, const int32_t* tokens_host, const int32_t* 
   }
   if (argmax_out_host) CAI_CUDA(ctx, cudaMemcpyAsync(argmax_out_host, s->amax_idx, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  CAI_TRY(cai_check_device_error(ctx));
+  CAI_TRY(session_check(s));
   if (logits_out_host && m->tp_size > 1) {
     for (int r = 0; r < m->tp_size; ++r)
       for (int b = 0; b < B; ++b)
@@ -1117,7 +1168,7 @@ int cai_session_decode_greedy(cai_session* s, const int32_t* tokens_host, int n_
   if (out_tokens_host)
     CAI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, s->trace, (size_t)n_steps * s->batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return CAI_OK;
+  return session_check(s);
 }
 
 int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens) {
@@ -1175,7 +1226,7 @@ int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens
         }
         for (auto& l : s->len_host) l += done;
         CAI_TRY(push_len(s));
-        if (done == n_tokens) return CAI_OK;
+        if (done == n_tokens) return session_check(s);
       }
     }
   }
@@ -1195,7 +1246,7 @@ int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens
   }
   for (auto& l : s->len_host) l += n_left;
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return CAI_OK;
+  return session_check(s);
 }
 
 int cai_session_profile(cai_session* s, const int32_t* tokens_host, int n_steps, float* out_ms, int64_t* out_launches) {
@@ -1207,6 +1258,28 @@ int cai_session_profile(cai_session* s, const int32_t* tokens_host, int n_steps,
   CAI_TRY(stage_inputs(s, tokens_host, nullptr));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   for (int f = 0; f < FAM_COUNT; ++f) { out_ms[f] = 0.f; out_launches[f] = 0; }
+  if (s->plan) {
+    // persistent step kernel: CTA 0 stamps the global timer at every phase boundary; a phase's time is the span
+    // between two stamps, booked to the family of the phase that ended (products, attention, exchanges, the rest)
+    const int tl = step_plan_trace_len(s->plan);
+    if (!s->plan_ts) CAI_CUDA(ctx, cudaMalloc((void**)&s->plan_ts, (size_t)tl * 8));
+    std::vector<unsigned long long> ts((size_t)tl);
+    for (int i = 0; i < n_steps; ++i) {
+      CAI_CUDA(ctx, cudaMemsetAsync(s->plan_ts, 0, 8, ctx->stream));
+      CAI_TRY(step_plan_enqueue(ctx, s->plan, s->plan_ts));
+      CAI_CUDA(ctx, cudaMemcpyAsync(ts.data(), s->plan_ts, (size_t)tl * 8, cudaMemcpyDeviceToHost, ctx->stream));
+      CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      const int n = (int)ts[0];
+      for (int k = 1; k < n && 2 + 2 * k < tl; ++k) {
+        const int f = (int)ts[(size_t)(2 + 2 * k)];
+        if (f < 0 || f >= FAM_COUNT) continue;
+        out_ms[f] += (float)((double)(ts[(size_t)(1 + 2 * k)] - ts[(size_t)(1 + 2 * (k - 1))]) * 1e-6);
+        out_launches[f] += 1;
+      }
+    }
+    for (auto& l : s->len_host) l += n_steps;
+    return session_check(s);
+  }
   ctx->prof_n = 0;
   ctx->prof_on = 1;
   int st = cai_prof_mark(ctx, FAM_OTHER);     // origin event
@@ -1222,7 +1295,7 @@ int cai_session_profile(cai_session* s, const int32_t* tokens_host, int n_steps,
     out_ms[f] += ms;
     out_launches[f] += 1;
   }
-  return CAI_OK;
+  return session_check(s);
 }
 
 int cai_session_snapshot(cai_session* s) {
@@ -1272,6 +1345,12 @@ int cai_session_restore(cai_session* s) {
 int cai_session_logits_dev(cai_session* s, const float** out_dev) {
   if (!s || !out_dev) return CAI_ERR_INVALID;
   *out_dev = s->logits;
+  return CAI_OK;
+}
+
+int cai_session_uses_step_kernel(cai_session* s, int* out_flag) {
+  if (!s || !out_flag) return CAI_ERR_INVALID;
+  *out_flag = s->plan ? 1 : 0;
   return CAI_OK;
 }
 

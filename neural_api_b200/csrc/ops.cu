@@ -131,7 +131,7 @@ int op_swiglu(cai_ctx* ctx, const float* x, int64_t ldx, float* y, int64_t ldy, 
 // renormalisation of the survivors. One warp per token.
 // ---------------------------------------------------------------------------
 __global__ void topk_gate_kernel(const float* __restrict__ logits, int tokens, int n_experts, int top_k, int renorm,
-                                 int32_t* __restrict__ ids, float* __restrict__ gates) {
+                                 int32_t* __restrict__ ids, float* __restrict__ gates, int* __restrict__ err) {
   extern __shared__ float probs_all[];
   pdl_trigger();
   pdl_wait();
@@ -162,6 +162,16 @@ __global__ void topk_gate_kernel(const float* __restrict__ logits, int tokens, i
       const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
       if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
     }
+    if (besti == 0x7fffffff) {
+      // No candidate: the row holds NaN (or only -inf) logits, so no probability compares >= 0. Keep the ids in
+      // range (slot s takes expert s, which no earlier slot can hold when the whole row is unusable; otherwise the
+      // lowest untaken expert), give the slot no weight, and raise the error word: one non-finite activation
+      // must end as a status, not as an out-of-range expert index in the kernels that follow.
+      int pick = 0;
+      for (int e = 0; e < n_experts; ++e) if (probs[e] != -1.0f) { pick = e; break; }
+      besti = pick; best = 0.f;
+      if (lane == 0 && err) *err = 3;
+    }
     if (lane == 0) {
       ids[(int64_t)t * top_k + s] = besti;
       gates[(int64_t)t * top_k + s] = best;
@@ -170,7 +180,7 @@ __global__ void topk_gate_kernel(const float* __restrict__ logits, int tokens, i
     kept_sum += best;
     __syncwarp();
   }
-  if (renorm && lane == 0)
+  if (renorm && lane == 0 && kept_sum > 0.f)
     for (int s = 0; s < top_k; ++s) gates[(int64_t)t * top_k + s] = gates[(int64_t)t * top_k + s] / kept_sum;
 }
 
@@ -181,7 +191,7 @@ int op_topk_gate(cai_ctx* ctx, const float* logits, int tokens, int n_experts, i
   const int warps = 4;
   const size_t smem = (size_t)warps * n_experts * sizeof(float);
   if (smem > 48 * 1024) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "router with %d experts exceeds the kernel's shared memory", n_experts);
-  pdl_launch(ctx, topk_gate_kernel, dim3((tokens + warps - 1) / warps), dim3(warps * 32), smem, logits, tokens, n_experts, top_k, renorm, ids, gates);
+  pdl_launch(ctx, topk_gate_kernel, dim3((tokens + warps - 1) / warps), dim3(warps * 32), smem, logits, tokens, n_experts, top_k, renorm, ids, gates, ctx->err_flag);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

@@ -28,13 +28,18 @@ def free_port():
     return port
 
 
+@pytest.mark.parametrize("allreduce", ["peer", "nccl"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_tensor_parallel_matches_single_gpu(world):
+def test_tensor_parallel_matches_single_gpu(world, allreduce):
     if gpu_count() < world:
         pytest.skip("needs %d GPUs" % world)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "tp_gpu_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    env = dict(os.environ)
+    env.pop("CAI_TP_ALLREDUCE", None)
+    if allreduce == "nccl":
+        env["CAI_TP_ALLREDUCE"] = "nccl"          # the library all-reduce instead of the peer-memory kernel
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-5000:]
     assert "TP_GPU_OK" in r.stdout
 
