@@ -287,6 +287,12 @@ int cai_session_logits_dev(cai_session* s, const float** out_dev);
  * head_dim 64 or 128; environment CAI_STEP_KERNEL=0 turns it off), 0 when it enqueues one kernel per operator the way
  * the reference enqueues one OpenCL kernel per layer (neural/neuralopencl.pas:946-1056). */
 int cai_session_uses_step_kernel(cai_session* s, int* out_flag);
+/* One decode step of a step-kernel session with the phase trace switched on: CTA 0 stamps the GPU's global timer
+ * when it leaves each grid barrier. out_ns[k] = nanoseconds since the kernel's first stamp, out_family[k] = what ended
+ * there (0 a matrix product, 1 attention or the merge of its splits, 2 anything else, 3 an exchange between GPUs);
+ * *out_n entries, at most cap. Feeds tokens_host[1] like cai_session_step and advances the session by one position.
+ * The finer-grained sibling of cai_session_profile. */
+int cai_session_step_trace(cai_session* s, const int32_t* tokens_host, int64_t* out_ns, int32_t* out_family, int cap, int* out_n);
 /* Bytes of KV cache the last step read (for the roofline arithmetic). */
 int cai_session_last_kv_bytes(cai_session* s, int64_t* out_bytes);
 

@@ -95,6 +95,7 @@ SIGNATURES = {
     "cai_session_restore": [_P],
     "cai_session_logits_dev": [_P, _PP],
     "cai_session_uses_step_kernel": [_P, C.POINTER(_I)],
+    "cai_session_step_trace": [_P, _P, C.POINTER(_I64), C.POINTER(C.c_int32), _I, C.POINTER(_I)],
     "cai_session_last_kv_bytes": [_P, C.POINTER(_I64)],
     "cai_comm_unique_id": [_P],
     "cai_comm_init": [_P, _I, _I, _P],

@@ -432,6 +432,15 @@ class StreamingDecoder:
     def restore_snapshot(self):
         self.backend._check(self.backend.lib.cai_session_restore(self.handle))
 
+    def step_trace(self, tokens, cap=4096):
+        """One step with the phase trace on; returns (ns since the kernel's first stamp, family per stamp)."""
+        tok = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))
+        ns = (C.c_int64 * cap)()
+        fam = (C.c_int32 * cap)()
+        n = C.c_int()
+        self.backend._check(self.backend.lib.cai_session_step_trace(self.handle, _ptr(tok), ns, fam, cap, C.byref(n)))
+        return np.asarray(ns[:n.value], dtype=np.int64), np.asarray(fam[:n.value], dtype=np.int32)
+
     @property
     def uses_step_kernel(self):
         """True when every step of this session is one persistent kernel (False: one kernel per operator)."""

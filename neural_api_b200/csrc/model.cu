@@ -1270,11 +1270,13 @@ int cai_session_profile(cai_session* s, const int32_t* tokens_host, int n_steps,
       CAI_CUDA(ctx, cudaMemcpyAsync(ts.data(), s->plan_ts, (size_t)tl * 8, cudaMemcpyDeviceToHost, ctx->stream));
       CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       const int n = (int)ts[0];
+      unsigned long long prev = ts[1];
       for (int k = 1; k < n && 2 + 2 * k < tl; ++k) {
         const int f = (int)ts[(size_t)(2 + 2 * k)];
-        if (f < 0 || f >= FAM_COUNT) continue;
-        out_ms[f] += (float)((double)(ts[(size_t)(1 + 2 * k)] - ts[(size_t)(1 + 2 * (k - 1))]) * 1e-6);
+        if (f < 0 || f >= FAM_COUNT) continue;               // stamps inside a phase
+        out_ms[f] += (float)((double)(ts[(size_t)(1 + 2 * k)] - prev) * 1e-6);
         out_launches[f] += 1;
+        prev = ts[(size_t)(1 + 2 * k)];
       }
     }
     for (auto& l : s->len_host) l += n_steps;
@@ -1346,6 +1348,33 @@ int cai_session_logits_dev(cai_session* s, const float** out_dev) {
   if (!s || !out_dev) return CAI_ERR_INVALID;
   *out_dev = s->logits;
   return CAI_OK;
+}
+
+int cai_session_step_trace(cai_session* s, const int32_t* tokens_host, int64_t* out_ns, int32_t* out_family, int cap, int* out_n) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host || !out_ns || !out_family || !out_n || cap < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_step_trace: bad argument");
+  if (!s->plan) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "cai_session_step_trace: the session does not run the persistent step kernel");
+  CAI_TRY(check_room(s, 1));
+  CAI_TRY(stage_inputs(s, tokens_host, nullptr));
+  const int tl = step_plan_trace_len(s->plan);
+  if (!s->plan_ts) CAI_CUDA(ctx, cudaMalloc((void**)&s->plan_ts, (size_t)tl * 8));
+  std::vector<unsigned long long> ts((size_t)tl);
+  CAI_CUDA(ctx, cudaMemsetAsync(s->plan_ts, 0, 8, ctx->stream));
+  CAI_TRY(step_plan_enqueue(ctx, s->plan, s->plan_ts));
+  CAI_CUDA(ctx, cudaMemcpyAsync(ts.data(), s->plan_ts, (size_t)tl * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (auto& l : s->len_host) l += 1;
+  int n = (int)ts[0];
+  if (2 + 2 * (n - 1) >= tl) n = (tl - 1) / 2;
+  if (n > cap) n = cap;
+  for (int k = 0; k < n; ++k) {
+    out_ns[k] = (int64_t)(ts[(size_t)(1 + 2 * k)] - ts[1]);
+    out_family[k] = (int32_t)ts[(size_t)(2 + 2 * k)];
+  }
+  *out_n = n;
+  return session_check(s);
 }
 
 int cai_session_uses_step_kernel(cai_session* s, int* out_flag) {

@@ -87,6 +87,7 @@ struct SkParams {
   unsigned* sync;                // [0] arrivals of this launch, [1] abort word
   int* err; unsigned limit_us;
   unsigned long long* ts;        // optional phase trace: [0] entries, then (time, family) pairs
+  int fine;                      // also stamp inside the phases (families 4 staged, 5 products done, 6 epilogue done)
   int ring_depth;
   int off_slots, off_misc, off_tab, off_ring;     // byte offsets in dynamic shared memory
   SkTp tp;
@@ -660,7 +661,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     const SkLayerDev L = tab_lay[l];
     // ---- [q|k|v]: RMSNorm in the staging; RoPE and the KV append in the epilogue
     sk_stage_normed(P, xs, red, P.xres, l == 0 ? token : -1, L.attn_norm, (l == 0 && blockIdx.x == 0) ? P.xres : nullptr);
+    if (P.fine) sk_trace(P, nts, 4);
     sk_gemv(P, MK_QKV, f, rd_slot, tab, ring_w, xs, slots, lane, warp);
+    if (P.fine) sk_trace(P, nts, 5);
     __syncthreads();
     {
       const SkMat& M = P.mat[MK_QKV];
@@ -690,10 +693,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
         }
       }
     }
+    if (P.fine) sk_trace(P, nts, 6);
     SK_SYNC(true);
     sk_trace(P, nts, FAM_LINEAR);
     // ---- attention over the cache
     sk_attention<G, HD>(P, L, xs, n, chunk, used, lane, warp);
+    if (P.fine) sk_trace(P, nts, 6);
     SK_SYNC(true);
     sk_trace(P, nts, FAM_ATTN);
     if (!fold) {
@@ -705,7 +710,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
       sk_stage_merge<HD>(P, xs, used);
     }
     // ---- O + residual
+    if (P.fine) sk_trace(P, nts, 4);
     sk_gemv(P, MK_O, f, rd_slot, tab, ring_w, xs, slots, lane, warp);
+    if (P.fine) sk_trace(P, nts, 5);
     __syncthreads();
     {
       const SkMat& M = P.mat[MK_O];
@@ -1088,7 +1095,7 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
     P.tp.max_elems = ex.max_elems; P.tp.seq = ex.seq; P.tp.gave_up = ex.gave_up; P.tp.vocab_offset = s.vocab_offset;
   }
   // phases per step: per layer 4 products + attention (+ merge) (+ 2 exchanges), head, advance, start
-  p->trace_len = 1 + 2 * (s.layers * 8 + 4);
+  p->trace_len = 1 + 2 * (s.layers * 16 + 4);
   *out = p;
   return CAI_OK;
 }
@@ -1098,6 +1105,7 @@ int step_plan_trace_len(const StepPlan* p) { return p->trace_len; }
 int step_plan_enqueue(cai_ctx* ctx, StepPlan* p, unsigned long long* ts_dev) {
   SkParams P = p->P;
   P.ts = ts_dev;
+  P.fine = (ts_dev && env_int("CAI_STEP_TRACE_FINE", 0)) ? 1 : 0;
   P.limit_us = ctx->wait_limit_us;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
