@@ -29,6 +29,7 @@ struct AttnParams {
   int8_t* k_codes; int8_t* v_codes; float* k_scales; float* v_scales;     // int8 cache (k_codes != NULL)
   const int32_t* seq_index;                                               // cache sequence of each batch row (NULL = the row itself)
   int* err;               // device-visible error word: 2 = a cache length outside [0, max_ctx) was refused
+  int k_blocked;          // K cache block-transposed (cai_k_blocked_index)
 };
 
 // The number of cached rows comes from a device word the host cannot always vouch for (the allocation-free entry
@@ -96,7 +97,8 @@ __global__ void rope_append_kernel(const AttnParams p) {
       x0 = y0; x1 = y1;
     }
     const int g = (2 * pr) / hd, d = (2 * pr) % hd;
-    float* dst = p.k_cache + (((int64_t)bs * p.kv_heads + g) * p.max_ctx + slot) * hd + d;
+    float* dst = p.k_cache + ((int64_t)bs * p.kv_heads + g) * p.max_ctx * hd +
+                 (p.k_blocked ? (int64_t)cai_k_blocked_index(slot, d, hd) : (int64_t)slot * hd + d);
     dst[0] = x0; dst[1] = x1;
   }
   for (int c = threadIdx.x; c < kw; c += blockDim.x) {
@@ -427,16 +429,21 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
     // ---- Q.K, lane = row (rows past the end re-read the last row and are masked below)
     const int j = tile + lane;
     const bool valid = j < j_end;
-    const ulonglong2* krow = (const ulonglong2*)(kbase + (int64_t)(valid ? j : j_end - 1) * HD);
+    const int jr = valid ? j : j_end - 1;
+    // row layout: the lane's own row, piece after piece; block-transposed layout: piece p of the 32 rows of the lane's
+    // block is 512 contiguous bytes (a fully coalesced load per instruction)
+    const ulonglong2* krow = p.k_blocked ? (const ulonglong2*)(kbase + (int64_t)(jr >> 5) * 32 * HD) + (jr & 31)
+                                         : (const ulonglong2*)(kbase + (int64_t)jr * HD);
+    const int kstep = p.k_blocked ? 32 : 1;              // 16-byte units between consecutive pieces of a row
     f32x2_t s2[G];
 #pragma unroll
     for (int h = 0; h < G; ++h) s2[h] = 0ull;
-    // 64 channels (two 128-byte lines of the row, 16 loads in flight) at a time: few dependent round trips to HBM
+    // 64 channels (16 loads in flight) at a time: few dependent round trips to HBM
 #pragma unroll
     for (int c = 0; c < HD / 64; ++c) {
       ulonglong2 k[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) k[i] = krow[c * 16 + i];
+      for (int i = 0; i < 16; ++i) k[i] = krow[(c * 16 + i) * kstep];
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         const ulonglong2* q2 = (const ulonglong2*)(q_s + h * HD + c * 64);
@@ -781,10 +788,16 @@ static AttnParams to_params(cai_ctx* ctx, const AttnArgs& a) {
   p.min_chunk = ATTN_MIN_CHUNK;
   p.k_codes = a.k_codes; p.v_codes = a.v_codes; p.k_scales = a.k_scales; p.v_scales = a.v_scales;
   p.seq_index = a.seq_index_dev;
+  p.k_blocked = a.k_blocked;
   return p;
 }
 
 // true when the int8 KV cache can serve this shape (the tiled kernels only)
+// true when the fp32 K cache of this shape may use the block-transposed layout (the tiled kernel serves it)
+bool attn_k_blocked_supported(int q_heads, int kv_heads, int head_dim) {
+  static const int use_tile = [] { const char* e = getenv("CAI_ATTN_TILE"); return (e && *e) ? atoi(e) : 1; }();
+  return use_tile && kv_heads > 0 && (q_heads % kv_heads) == 0 && (q_heads / kv_heads) <= 8 && (head_dim == 64 || head_dim == 128);
+}
 bool attn_int8_supported(int q_heads, int kv_heads, int head_dim) {
   return kv_heads > 0 && (q_heads % kv_heads) == 0 && (q_heads / kv_heads) <= 8 && (head_dim == 64 || head_dim == 128);
 }
@@ -830,6 +843,8 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
     }
     return CAI_OK;
   }
+  if (a.k_blocked && !(use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8 && (a.max_ctx % 32) == 0))
+    return cai_fail(ctx, CAI_ERR_STATE, "internal: block-transposed K cache outside the tiled attention kernel");
   if (use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8) {
     p.min_chunk = ATTN_TILE_MIN_CHUNK;
     const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 64 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);

@@ -167,6 +167,7 @@ struct LinearArgs {
   int rope_q_width = 0, rope_kv_width = 0, rope_head_dim = 0, rope_kv_heads = 0, rope_max_ctx = 0;
   float* k_cache = nullptr;
   float* v_cache = nullptr;
+  int k_blocked = 0;                     // K cache in the block-transposed layout (cai_k_blocked_index)
   const int32_t* cache_len_dev = nullptr;
   const float* norm_gain = nullptr;      // fuse y = W (gain * x * inv_rms(x)): the preceding TNNetTokenRMSNorm
   float norm_eps = 0.f;
@@ -233,6 +234,9 @@ struct AttnArgs {
   int8_t* v_codes = nullptr;
   float* k_scales = nullptr;
   float* v_scales = nullptr;
+  // K cache layout: 0 = [pos][d] rows as the reference keeps them (neural/neural.cl:2343-2346), 1 = block-transposed
+  // (cai_k_blocked_index; sessions use it, max_ctx must then be a multiple of 32 and head_dim of 4)
+  int k_blocked = 0;
   // optional: row r of the batch belongs to sequence seq_index[r] of the cache (several rows may be consecutive
   // positions of ONE sequence: chunked prefill); NULL = row r is sequence r. cache_len_dev stays per row.
   const int32_t* seq_index_dev = nullptr;
@@ -240,6 +244,7 @@ struct AttnArgs {
 int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx);
 size_t attn_partial_floats(int batch, int q_heads, int nsplit, int head_dim);
 bool attn_int8_supported(int q_heads, int kv_heads, int head_dim);
+bool attn_k_blocked_supported(int q_heads, int kv_heads, int head_dim);
 int attn_rope_append(cai_ctx* ctx, const AttnArgs& a);
 int attn_decode(cai_ctx* ctx, const AttnArgs& a);
 
@@ -260,6 +265,15 @@ void comm_destroy(cai_ctx* ctx);
 // device helpers
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
+// Block-transposed K cache of a session (one KV head): positions in blocks of 32; inside a block the 16-byte piece
+// (4 channels) p of position r lies at float offset (p * 32 + r) * 4. The decode kernels walk K with "lane = position":
+// in this layout the 32 lanes of a warp read 512 contiguous bytes per instruction, and a block's pieces 8 s .. 8 s + 7
+// are one contiguous 4 KB run that an asynchronous copy can land in shared memory as it is. (The reference's row
+// layout [pos][d] makes the same access 32 separate 512-byte-strided pieces.) V keeps the row layout: it is walked
+// with "lane = channels".
+__host__ __device__ __forceinline__ size_t cai_k_blocked_index(int pos, int d, int head_dim) {
+  return ((size_t)(pos >> 5) * (size_t)(head_dim >> 2) + (size_t)(d >> 2)) * 128 + (size_t)(pos & 31) * 4 + (size_t)(d & 3);
+}
 // Programmatic dependent launch. A kernel launched through pdl_launch may start while the kernel
 // before it in the stream is still running; it must call pdl_wait() before it touches anything that
 // kernel wrote (pdl_wait returns once the previous kernel has completed and its writes are visible),

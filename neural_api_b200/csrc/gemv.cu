@@ -547,7 +547,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
         a.rope_q_width + 2 * a.rope_kv_width != w->n || (a.rope_q_width % a.rope_head_dim) || (a.rope_kv_width % a.rope_head_dim))
       return cai_fail(ctx, CAI_ERR_INVALID, "linear: inconsistent fused RoPE / KV-append arguments");
     p.rope_cs = a.rope_cs; p.rope_q_width = a.rope_q_width; p.rope_kv_width = a.rope_kv_width; p.rope_head_dim = a.rope_head_dim;
-    p.rope_kv_heads = a.rope_kv_heads; p.rope_max_ctx = a.rope_max_ctx; p.k_cache = a.k_cache; p.v_cache = a.v_cache;
+    p.rope_kv_heads = a.rope_kv_heads; p.rope_max_ctx = a.rope_max_ctx; p.k_cache = a.k_cache; p.v_cache = a.v_cache; p.k_blocked = a.k_blocked;
     p.cache_len = a.cache_len_dev;
   }
   const int64_t units = (a.epilogue == EPI_SWIGLU) ? w->n / 2 : w->n;

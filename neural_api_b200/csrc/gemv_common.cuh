@@ -35,6 +35,7 @@ struct GemvParams {
   // EPI_QKV_ROPE
   const float* rope_cs;
   int rope_q_width, rope_kv_width, rope_head_dim, rope_kv_heads, rope_max_ctx;
+  int k_blocked;
   float* k_cache;
   float* v_cache;
   const int32_t* cache_len;
@@ -191,8 +192,10 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const float (
             const bool is_k = row < p.rope_q_width + p.rope_kv_width;
             const int64_t rr = row - p.rope_q_width - (is_k ? 0 : p.rope_kv_width);
             const int64_t g = rr / hd, d = rr % hd;
-            float* dst = (is_k ? p.k_cache : p.v_cache) +
-                         (((int64_t)bi * p.rope_kv_heads + g) * p.rope_max_ctx + p.cache_len[bi]) * hd + d;
+            const int slot = p.cache_len[bi];
+            const int64_t head0 = ((int64_t)bi * p.rope_kv_heads + g) * p.rope_max_ctx * hd;
+            float* dst = (is_k ? p.k_cache : p.v_cache) + head0 +
+                         ((is_k && p.k_blocked) ? (int64_t)cai_k_blocked_index(slot, (int)d, hd) : (int64_t)slot * hd + d);
             dst[0] = v0; dst[1] = v1;
           }
         }

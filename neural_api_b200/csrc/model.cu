@@ -574,7 +574,9 @@ struct cai_session {
   cai_model* m;
   cai_ctx* ctx;
   int max_ctx, batch;
-  float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][max_ctx][hd]; int8 codes when kv_int8
+  int ctx_pitch = 0;                                  // positions per KV head in the caches: max_ctx rounded up to 32
+  int k_blocked = 0;                                  // fp32 K cache block-transposed (cai_k_blocked_index)
+  float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][ctx_pitch][hd]; int8 codes when kv_int8
   float *k_snap = nullptr, *v_snap = nullptr;
   size_t layer_stride = 0;                            // elements per layer
   // chunked prefill: a helper session of C rows per sequence that BORROWS this session's caches (kv_owner set in the
@@ -673,7 +675,7 @@ static int enqueue_step(cai_session* s) {
   float* xalt = s->x_alt;
   auto set_rope = [&](LinearArgs& a, int l) {
     a.epilogue = EPI_QKV_ROPE; a.rope_cs = s->rope_cs; a.rope_q_width = m->qw_l; a.rope_kv_width = m->kw_l;
-    a.rope_head_dim = c.head_dim; a.rope_kv_heads = m->kv_heads_l; a.rope_max_ctx = s->max_ctx;
+    a.rope_head_dim = c.head_dim; a.rope_kv_heads = m->kv_heads_l; a.rope_max_ctx = s->ctx_pitch; a.k_blocked = s->k_blocked;
     a.k_cache = s->k_cache + (size_t)l * s->layer_stride; a.v_cache = s->v_cache + (size_t)l * s->layer_stride;
     a.cache_len_dev = s->len_dev;
   };
@@ -709,7 +711,7 @@ static int enqueue_step(cai_session* s) {
       }
       a.seq_index_dev = s->seq_index_dev;
       a.cache_len_dev = s->len_dev; a.batch = B; a.q_heads = m->heads_l; a.kv_heads = m->kv_heads_l;
-      a.head_dim = c.head_dim; a.max_ctx = s->max_ctx; a.theta = m->theta; a.pos_dev = s->pos_dev;
+      a.head_dim = c.head_dim; a.max_ctx = s->ctx_pitch; a.k_blocked = s->k_blocked; a.theta = m->theta; a.pos_dev = s->pos_dev;
       a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
       a.out = s->att; a.ldo = m->qw_l; a.partial = s->partial; a.nsplit = s->nsplit;
       if (!fuse_rope) CAI_TRY(attn_rope_append(ctx, a));
@@ -949,8 +951,9 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   if (kv_int8 && !attn_int8_supported(m->heads_l, m->kv_heads_l, c.head_dim))
     return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "the int8 KV cache needs head_dim 64 or 128 and at most 8 query heads per KV head");
   const int cache_seqs = kv_owner ? kv_owner->batch : batch;
-  const size_t layer_stride = (size_t)cache_seqs * m->kv_heads_l * max_ctx * c.head_dim;
-  const size_t scale_stride = (size_t)cache_seqs * m->kv_heads_l * max_ctx;
+  const int ctx_pitch = (max_ctx + 31) & ~31;
+  const size_t layer_stride = (size_t)cache_seqs * m->kv_heads_l * ctx_pitch * c.head_dim;
+  const size_t scale_stride = (size_t)cache_seqs * m->kv_heads_l * ctx_pitch;
   const size_t cache_bytes = kv_owner ? 0 : layer_stride * (size_t)c.layers * (kv_int8 ? 1 : 4) + (kv_int8 ? scale_stride * (size_t)c.layers * 4 : 0);
   size_t free_b = 0, total_b = 0;
   CAI_CUDA(ctx, cudaMemGetInfo(&free_b, &total_b));
@@ -959,6 +962,8 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   cai_session* s = new (std::nothrow) cai_session();
   if (!s) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
   s->m = m; s->ctx = ctx; s->max_ctx = max_ctx; s->batch = batch; s->layer_stride = layer_stride;
+  s->ctx_pitch = ctx_pitch;
+  s->k_blocked = kv_owner ? kv_owner->k_blocked : ((!kv_int8 && attn_k_blocked_supported(m->heads_l, m->kv_heads_l, c.head_dim)) ? 1 : 0);
   s->kv_int8 = kv_int8; s->scale_stride = scale_stride;
   s->len_host.assign((size_t)batch, 0);
   m->sessions += 1;
@@ -1063,7 +1068,7 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
     // CAI_ERR_UNSUPPORTED) the session keeps one launch per operator
     StepSetup u;
     u.layers = c.layers; u.hidden = H; u.q_heads = m->heads_l; u.kv_heads = m->kv_heads_l; u.head_dim = c.head_dim;
-    u.inter = m->inter_l; u.vocab = m->vocab_l; u.max_ctx = max_ctx; u.rms_eps = c.rms_eps;
+    u.inter = m->inter_l; u.vocab = m->vocab_l; u.max_ctx = ctx_pitch; u.k_blocked = s->k_blocked; u.rms_eps = c.rms_eps;
     u.embed = &m->embed; u.lm_head = &m->lm_head; u.final_norm = m->final_norm; u.theta = m->theta;
     u.layer.resize((size_t)c.layers);
     for (int l = 0; l < c.layers; ++l) {

@@ -89,7 +89,8 @@ struct SkParams {
   unsigned long long* ts;        // optional phase trace: [0] entries, then (time, family) pairs
   int fine;                      // also stamp inside the phases (families 4 staged, 5 products done, 6 epilogue done)
   int ring_depth;
-  int off_slots, off_misc, off_tab, off_ring;     // byte offsets in dynamic shared memory
+  int off_xs, off_slots, off_misc, off_tab, off_ring;     // byte offsets in dynamic shared memory
+  int at_warps, at_depth;        // attention: warps that take tiles, stages of their rings
   SkTp tp;
 };
 
@@ -140,6 +141,7 @@ __device__ __forceinline__ void sk_trace(const SkParams& P, int& n, int family) 
 // ---------------------------------------------------------------------------------------------------------------
 struct SkFill {
   int gi, kind, t, T, c, c_end, rg0, slot, k_lane, s_idx;
+  int hold;                      // the cursor stopped in front of an O matrix (the attention phase borrows the rings)
   const uint8_t* codes; const __half* scales;
   const uint8_t* wp[SK_RPW];
   const __half* sp;
@@ -169,8 +171,12 @@ __device__ __forceinline__ void sk_tile_setup(const SkParams& P, SkFill& f, int 
   f.k_lane = f.c * 512 + lane * 16;
 }
 
-__device__ __forceinline__ void sk_next_matrix(const SkParams& P, SkFill& f, const SkPtrs* tab, int lane, int warp) {
+// cross_o = false: the cursor stops in front of an O matrix (f.hold): the attention phase that precedes it uses
+// the rings' shared memory for the K and V rows, and the step resumes the cursor when that phase is over.
+__device__ __forceinline__ void sk_next_matrix(const SkParams& P, SkFill& f, const SkPtrs* tab, int lane, int warp, bool cross_o = false) {
   while (true) {
+    if (!cross_o && f.gi + 1 < P.n_mats - 1 && ((f.gi + 1) & 3) == MK_O) { f.hold = 1; return; }
+    cross_o = false;
     ++f.gi;
     if (f.gi >= P.n_mats) return;
     f.kind = (f.gi == P.n_mats - 1) ? MK_HEAD : (f.gi & 3);
@@ -189,7 +195,7 @@ __device__ __forceinline__ void sk_next_matrix(const SkParams& P, SkFill& f, con
 
 // Copies the cursor's next chunk into the ring (one commit group per call, empty once the step's tiles are through).
 __device__ __forceinline__ void sk_fill_one(const SkParams& P, SkFill& f, const SkPtrs* tab, uint32_t ring_w, int lane, int warp) {
-  if (f.gi < P.n_mats) {
+  if (!f.hold && f.gi < P.n_mats) {
     const int K = P.mat[f.kind].K;
     const uint32_t ok = (f.k_lane < K) ? 16u : 0u;
     const uint32_t dst = ring_w + f.slot * SK_STAGE + lane * 16;
@@ -377,44 +383,81 @@ __device__ __forceinline__ void sk_stage_merge(const SkParams& P, float* xs, int
   __syncthreads();
 }
 
-// The same merge as its own phase (long contexts): outputs dealt over the whole grid, result to P.att.
+// The same merge as its own phase (long contexts): one warp per 4 outputs, the lanes take the splits (lane, lane + 32,
+// ...), each lane merges its own splits in order and the lanes are then combined with one max and five sums over the
+// warp. The outputs are dealt over all warps of the grid; result to P.att.
 template <int HD>
 __device__ __forceinline__ void sk_merge_phase(const SkParams& P, int used) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int K4 = P.qw >> 2;
-  for (int c4 = blockIdx.x + gridDim.x * threadIdx.x; c4 < K4; c4 += gridDim.x * SK_THREADS) {
+  for (int c4 = blockIdx.x + gridDim.x * warp; c4 < K4; c4 += gridDim.x * SK_WARPS) {
     const int h = (c4 * 4) / HD, d = (c4 * 4) - h * HD;
     const float* src = P.partial + (size_t)h * P.nsplit_max * (HD + 2);
-    float mx = -INFINITY;
-    for (int s = 0; s < used; ++s) mx = fmaxf(mx, __ldcg(src + (size_t)s * (HD + 2)));
-    float lt = 0.f;
+    float mx = -INFINITY, lt = 0.f;
     float4 at = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < used; ++s) {
+    for (int s = lane; s < used; s += 32) {
       const float2 ml = __ldcg((const float2*)(src + (size_t)s * (HD + 2)));
-      const float sc = (ml.x == -INFINITY) ? 0.f : expf(ml.x - mx);
       const float2 a0 = __ldcg((const float2*)(src + (size_t)s * (HD + 2) + 2 + d));
       const float2 a1 = __ldcg((const float2*)(src + (size_t)s * (HD + 2) + 4 + d));
-      lt += ml.y * sc;
-      at.x += a0.x * sc; at.y += a0.y * sc; at.z += a1.x * sc; at.w += a1.y * sc;
+      if (ml.x == -INFINITY) continue;
+      const float mnew = fmaxf(mx, ml.x);
+      const float ca = (mx == -INFINITY) ? 0.f : expf(mx - mnew), cb = expf(ml.x - mnew);
+      lt = lt * ca + ml.y * cb;
+      at.x = at.x * ca + a0.x * cb; at.y = at.y * ca + a0.y * cb; at.z = at.z * ca + a1.x * cb; at.w = at.w * ca + a1.y * cb;
+      mx = mnew;
     }
-    float4 y;
-    y.x = (lt > 0.f) ? at.x / lt : 0.f; y.y = (lt > 0.f) ? at.y / lt : 0.f;
-    y.z = (lt > 0.f) ? at.z / lt : 0.f; y.w = (lt > 0.f) ? at.w / lt : 0.f;
-    *((float4*)P.att + c4) = y;
+    const float mall = warp_max(mx);
+    const float sc = (mx == -INFINITY) ? 0.f : expf(mx - mall);
+    lt = warp_sum(lt * sc);
+    at.x = warp_sum(at.x * sc); at.y = warp_sum(at.y * sc); at.z = warp_sum(at.z * sc); at.w = warp_sum(at.w * sc);
+    if (lane == 0) {
+      float4 y;
+      y.x = (lt > 0.f) ? at.x / lt : 0.f; y.y = (lt > 0.f) ? at.y / lt : 0.f;
+      y.z = (lt > 0.f) ? at.z / lt : 0.f; y.w = (lt > 0.f) ? at.w / lt : 0.f;
+      *((float4*)P.att + c4) = y;
+    }
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// attention over the cache: items (kv head, context split) dealt to the CTAs; inside an item a warp takes tiles of
+// attention over the cache: items (kv head, context split) dealt to the CTAs; inside an item 8 warps take tiles of
 // 32 rows (lane = row for Q.K, lane = 2 or 4 channels for P.V), online softmax per warp, warps merged in warp order.
+//
+// With this kernel's shared-memory carve-out the L1 cache is a few tens of KB: ordinary loads of K and V rows cannot
+// keep enough lines in flight (measured: 2.2 TB/s). So the rows come in through cp.async, which needs no L1 line:
+// every attention warp owns a ring of 4 KB stages. A tile is KS stages of K (32 rows x 32 channels: in the sessions'
+// block-transposed K cache that is one contiguous 4 KB run, already laid out [piece][row] for conflict-free lane = row
+// reads) followed by VG stages of V (whole
+// rows, as they lie in the cache). The fill runs AT_DEPTH - 1 stages ahead of the arithmetic, straight across tiles.
+// Rows past the end of the split are fetched from the split's last row (finite values) and carry probability 0.
 // ---------------------------------------------------------------------------------------------------------------
+constexpr int AT_STAGE = 4096;
+
+// shared memory of the phase: q [G][HD] | probabilities [warps][G][32] | rings [warps][depth][AT_STAGE], which become
+// the merge area [warps][G][HD + 2] once the rows are through
+static __host__ __device__ inline int at_rings_offset(int G, int HD, int warps) { return ((G * HD * 4 + warps * G * 32 * 4) + 127) & ~127; }
+static __host__ __device__ inline int at_smem_bytes(int G, int HD, int warps, int depth) {
+  const int ring = warps * depth * AT_STAGE, merge = warps * G * (HD + 2) * 4;
+  return at_rings_offset(G, HD, warps) + (ring > merge ? ring : merge);
+}
+
 template <int G, int HD>
-__device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev& L, float* smem_f, int n, int chunk, int used,
+__device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev& L, unsigned char* smem, int n, int chunk, int used,
                                              int lane, int warp) {
+  constexpr int KS = HD / 32;                    // K stages per tile (32 channels each)
+  constexpr int VR = AT_STAGE / (HD * 4);        // rows per V stage
+  constexpr int VG = 32 / VR;                    // V stages per tile
+  constexpr int SPT = KS + VG;                   // stages per tile
+  constexpr int RP = HD / 4;                     // 16-byte pieces per row
   constexpr int DPL = HD / 32;
   constexpr int DP2 = DPL / 2;
-  float* q_s = smem_f;                                                   // [G][HD]
-  f32x2_t* p_s = (f32x2_t*)(q_s + G * HD) + (size_t)warp * G * 32;       // this warp's [G][32] pairs (p, p)
-  float* merge_s = smem_f + G * HD + SK_WARPS * G * 64;                  // [SK_WARPS][G][HD + 2]
+  const int AT_WARPS = P.at_warps, AT_DEPTH = P.at_depth;
+  const int aw = warp < AT_WARPS ? warp : 0;
+  float* q_s = (float*)smem;                                                        // [G][HD]
+  float* p_s = q_s + G * HD + (size_t)aw * G * 32;                                  // this warp's [G][32] probabilities
+  unsigned char* rings = smem + at_rings_offset(G, HD, AT_WARPS);
+  float* merge_s = (float*)rings;                                                   // [AT_WARPS][G][HD + 2], after the loop
+  const uint32_t ring_a = (uint32_t)__cvta_generic_to_shared(rings) + (uint32_t)aw * AT_DEPTH * AT_STAGE;
   const int items = P.kv_heads * used;
   for (int item = blockIdx.x; item < items; item += gridDim.x) {
     const int g = item / used, split = item - g * used;
@@ -423,8 +466,6 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
     __syncthreads();                                                     // the previous item's shared memory is free
     for (int i = threadIdx.x; i < G * HD; i += SK_THREADS) q_s[i] = __ldcg(P.qbuf + (size_t)g * G * HD + i);
     __syncthreads();
-    const float* kbase = L.k_cache + (size_t)g * (size_t)P.max_ctx * HD;
-    const float* vbase = L.v_cache + (size_t)g * (size_t)P.max_ctx * HD;
     float m[G], l[G];
     f32x2_t acc[G][DP2];
 #pragma unroll
@@ -433,102 +474,142 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
 #pragma unroll
       for (int d = 0; d < DP2; ++d) acc[h][d] = 0ull;
     }
-    for (int tile = j_begin + warp * 32; tile < j_end; tile += SK_WARPS * 32) {
-      const int j = tile + lane;
-      const bool valid = j < j_end;
-      const ulonglong2* krow = (const ulonglong2*)(kbase + (size_t)(valid ? j : j_end - 1) * HD);
-      f32x2_t s2[G];
+    if (warp < AT_WARPS) {
+      const float* kbase = L.k_cache + (size_t)g * (size_t)P.max_ctx * HD;
+      const float* vbase = L.v_cache + (size_t)g * (size_t)P.max_ctx * HD;
+      const int n_tiles = (j_end - j_begin + 31) >> 5;
+      const int my_tiles = (warp < n_tiles) ? (n_tiles - warp + AT_WARPS - 1) / AT_WARPS : 0;
+      const int total = my_tiles * SPT;
+      int fs = 0, fslot = 0, rslot = 0;
+      // copies stage `fs` of this warp's sequence into ring slot `fslot` (an empty group past the end)
+      auto issue = [&]() {
+        if (fs < total) {
+          const int ti = fs / SPT, st = fs - ti * SPT;
+          const int tile = j_begin + 32 * (warp + AT_WARPS * ti);
+          const int last = j_end - 1 - tile;
+          const uint32_t dst = ring_a + fslot * AT_STAGE;
+          if (st < KS) {
+            // pieces 8 st .. 8 st + 7 of the tile's 32-row block: one contiguous 4 KB run, [piece][row] in memory and
+            // in the stage alike. (Rows past the end of the cache's filled part hold whatever was there: their scores
+            // are masked and never reach a sum.)
+            const float* srcg = kbase + (size_t)(tile >> 5) * 32 * HD + (size_t)st * 1024;
 #pragma unroll
-      for (int h = 0; h < G; ++h) s2[h] = 0ull;
-#pragma unroll
-      for (int c = 0; c < HD / 64; ++c) {
-        ulonglong2 k[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) k[i] = krow[c * 16 + i];
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-          const ulonglong2* q2 = (const ulonglong2*)(q_s + h * HD + c * 64);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const ulonglong2 q = q2[i];
-            s2[h] = fma2(q.x, k[i].x, s2[h]);
-            s2[h] = fma2(q.y, k[i].y, s2[h]);
-          }
-        }
-      }
-      const int last = j_end - 1 - tile;
-      f32x2_t v[16][DP2];
-      auto load_v = [&](int base) {
-#pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          const int r = (base + t <= last) ? (base + t) : last;
-          const float* vrow = vbase + (size_t)(tile + r) * HD + lane * DPL;
-          if (DPL == 4) {
-            const ulonglong2 x = *(const ulonglong2*)vrow;
-            v[t][0] = x.x; v[t][DP2 - 1] = x.y;
+            for (int j = 0; j < 8; ++j) gv_cp_async16(dst + (j * 32 + lane) * 16, srcg + (j * 32 + lane) * 4, 16u);
           } else {
-            v[t][0] = *(const f32x2_t*)vrow;
+            const int v0 = (st - KS) * VR;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int idx = j * 32 + lane;
+              const int row = v0 + idx / RP, cp = idx - (idx / RP) * RP;
+              const int rc = row <= last ? row : last;
+              gv_cp_async16(dst + idx * 16, vbase + (size_t)(tile + rc) * HD + cp * 4, 16u);
+            }
           }
+          ++fs;
         }
+        gv_cp_async_commit();
+        fslot = (fslot + 1 == AT_DEPTH) ? 0 : fslot + 1;
       };
-      auto use_v = [&](int base) {
+      auto next_stage = [&]() -> uint32_t {
+        gv_cp_async_wait_depth(AT_DEPTH);
+        __syncwarp();
+        issue();
+        const uint32_t src = ring_a + rslot * AT_STAGE;
+        rslot = (rslot + 1 == AT_DEPTH) ? 0 : rslot + 1;
+        return src;
+      };
+#pragma unroll 1
+      for (int s = 0; s < AT_DEPTH - 1; ++s) issue();
+#pragma unroll 1
+      for (int ti = 0; ti < my_tiles; ++ti) {
+        const int tile = j_begin + 32 * (warp + AT_WARPS * ti);
+        const bool valid = tile + lane < j_end;
+        const int last = j_end - 1 - tile;
+        f32x2_t s2[G];
 #pragma unroll
-        for (int t2 = 0; t2 < 16; t2 += 2) {
+        for (int h = 0; h < G; ++h) s2[h] = 0ull;
+#pragma unroll 1
+        for (int st = 0; st < KS; ++st) {
+          const uint32_t src = next_stage();
 #pragma unroll
-          for (int h = 0; h < G; ++h) {
-            const ulonglong2 pr = *(const ulonglong2*)(p_s + h * 32 + base + t2);
+          for (int pc = 0; pc < 8; ++pc) {
+            ulonglong2 k;
+            asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(k.x), "=l"(k.y) : "r"(src + (pc * 32 + lane) * 16));
 #pragma unroll
-            for (int d = 0; d < DP2; ++d) {
-              acc[h][d] = fma2(pr.x, v[t2 + 0][d], acc[h][d]);
-              acc[h][d] = fma2(pr.y, v[t2 + 1][d], acc[h][d]);
+            for (int h = 0; h < G; ++h) {
+              const ulonglong2 q = *(const ulonglong2*)(q_s + h * HD + st * 32 + pc * 4);
+              s2[h] = fma2(q.x, k.x, s2[h]);
+              s2[h] = fma2(q.y, k.y, s2[h]);
             }
           }
         }
-      };
-      load_v(0);
-      __syncwarp();
+        __syncwarp();                                      // the previous tile's probabilities have been consumed
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const float sc = valid ? sum2(s2[h]) * P.inv_sqrt_d : -INFINITY;
+          const float mnew = fmaxf(m[h], warp_max(sc));    // finite: the tile holds at least one row
+          const float pj = valid ? expf(sc - mnew) : 0.f;
+          const float psum = warp_sum(pj);
+          const float corr = expf(m[h] - mnew);            // 0 on the first tile (m = -inf)
+          l[h] = l[h] * corr + psum;
+          m[h] = mnew;
+          const f32x2_t corr2 = pack2(corr, corr);
+#pragma unroll
+          for (int d = 0; d < DP2; ++d) acc[h][d] = fma2(acc[h][d], corr2, 0ull);
+          p_s[h * 32 + lane] = pj;
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int vg = 0; vg < VG; ++vg) {
+          const uint32_t src = next_stage();
+          if (vg * VR > last) continue;                    // a whole stage of masked rows
+#pragma unroll
+          for (int r = 0; r < VR; r += 2) {
+            f32x2_t v0[DP2], v1[DP2];
+            if (DPL == 4) {
+              asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v0[0]), "=l"(v0[DP2 - 1]) : "r"(src + r * (HD * 4) + lane * 16));
+              asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v1[0]), "=l"(v1[DP2 - 1]) : "r"(src + (r + 1) * (HD * 4) + lane * 16));
+            } else {
+              asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v0[0]) : "r"(src + r * (HD * 4) + lane * 8));
+              asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v1[0]) : "r"(src + (r + 1) * (HD * 4) + lane * 8));
+            }
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+              const float2 pr = *(const float2*)(p_s + h * 32 + vg * VR + r);          // the probabilities of two rows
+              const f32x2_t p0 = pack2(pr.x, pr.x), p1 = pack2(pr.y, pr.y);
+#pragma unroll
+              for (int d = 0; d < DP2; ++d) {
+                acc[h][d] = fma2(p0, v0[d], acc[h][d]);
+                acc[h][d] = fma2(p1, v1[d], acc[h][d]);
+              }
+            }
+          }
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");     // the rings become the merge area below
+    }
+    __syncthreads();
+    if (warp < AT_WARPS) {
 #pragma unroll
       for (int h = 0; h < G; ++h) {
-        const float sc = valid ? sum2(s2[h]) * P.inv_sqrt_d : -INFINITY;
-        const float mnew = fmaxf(m[h], warp_max(sc));
-        const float pj = valid ? expf(sc - mnew) : 0.f;
-        const float psum = warp_sum(pj);
-        const float corr = expf(m[h] - mnew);
-        l[h] = l[h] * corr + psum;
-        m[h] = mnew;
-        const f32x2_t corr2 = pack2(corr, corr);
+        float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
+        if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
 #pragma unroll
-        for (int d = 0; d < DP2; ++d) acc[h][d] = fma2(acc[h][d], corr2, 0ull);
-        p_s[h * 32 + lane] = pack2(pj, pj);
-      }
-      __syncwarp();
-      use_v(0);
-      if (last >= 16) {
-        load_v(16);
-        use_v(16);
-      }
-    }
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-      float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
-      if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
-#pragma unroll
-      for (int d = 0; d < DP2; ++d) {
-        float lo, hi;
-        asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[h][d]));
-        dst[2 + lane * DPL + 2 * d] = lo;
-        dst[2 + lane * DPL + 2 * d + 1] = hi;
+        for (int d = 0; d < DP2; ++d) {
+          float lo, hi;
+          asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[h][d]));
+          dst[2 + lane * DPL + 2 * d] = lo;
+          dst[2 + lane * DPL + 2 * d + 1] = hi;
+        }
       }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * HD; idx += SK_THREADS) {
       const int hh = idx / HD, d = idx - hh * HD;
       float mx = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
+      for (int w = 0; w < AT_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
       float lt = 0.f, at = 0.f;
-#pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) {
+      for (int w = 0; w < AT_WARPS; ++w) {
         const float* src = merge_s + ((size_t)w * G + hh) * (HD + 2);
         const float sc = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mx);
         lt += src[1] * sc;
@@ -596,7 +677,7 @@ __device__ __forceinline__ void sk_drain() { asm volatile("cp.async.wait_all;" :
 template <int G, int HD>
 __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
   extern __shared__ __align__(16) unsigned char sk_smem[];
-  float* xs = (float*)sk_smem;                                     // staged input row; attention scratch
+  float* xs = (float*)(sk_smem + P.off_xs);                        // staged input row (the attention phase uses everything from here up)
   float* slots = (float*)(sk_smem + P.off_slots);
   float* red = (float*)(sk_smem + P.off_misc);                     // [32]
   int* s_flag = (int*)(sk_smem + P.off_misc + 128);
@@ -636,7 +717,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
   __syncthreads();
 
   SkFill f;
-  f.gi = -1; f.slot = 0; f.kind = 0; f.t = 0; f.T = 0; f.c = 0; f.c_end = 0; f.rg0 = 0; f.k_lane = 0; f.s_idx = 0;
+  f.gi = -1; f.slot = 0; f.kind = 0; f.hold = 0; f.t = 0; f.T = 0; f.c = 0; f.c_end = 0; f.rg0 = 0; f.k_lane = 0; f.s_idx = 0;
   f.codes = nullptr; f.scales = nullptr; f.sp = nullptr;
 #pragma unroll
   for (int r = 0; r < SK_RPW; ++r) f.wp[r] = nullptr;
@@ -687,7 +768,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
             const bool is_k = row < P.qw + P.kw;
             const int rr = row - P.qw - (is_k ? 0 : P.kw);
             const int g = rr / HD, d = rr - g * HD;
-            float* dst = (is_k ? L.k_cache : L.v_cache) + ((size_t)g * P.max_ctx + len) * HD + d;
+            float* dst = is_k ? L.k_cache + (size_t)g * P.max_ctx * HD + cai_k_blocked_index(len, d, HD)
+                              : L.v_cache + ((size_t)g * P.max_ctx + len) * HD + d;
             *(float2*)dst = make_float2(v0, v1);
           }
         }
@@ -697,7 +779,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     SK_SYNC(true);
     sk_trace(P, nts, FAM_LINEAR);
     // ---- attention over the cache
-    sk_attention<G, HD>(P, L, xs, n, chunk, used, lane, warp);
+    sk_drain();                                                      // (the cursor is on hold: nothing of the rings is in flight or unread)
+    sk_attention<G, HD>(P, L, (unsigned char*)xs, n, chunk, used, lane, warp);
+    // the rings are the weights' again: resume the cursor at the O matrix and prime
+    __syncthreads();
+    f.hold = 0; f.slot = rd_slot;
+    sk_next_matrix(P, f, tab, lane, warp, true);
+    for (int s = 0; s < P.ring_depth - 1; ++s) sk_fill_one(P, f, tab, ring_w, lane, warp);
     if (P.fine) sk_trace(P, nts, 6);
     SK_SYNC(true);
     sk_trace(P, nts, FAM_ATTN);
@@ -988,6 +1076,7 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
   }
   if (((uintptr_t)s.final_norm % 16) || (qw % 4) || (s.hidden % 4)) return CAI_ERR_UNSUPPORTED;
   if (s.tp_world > 1 && (!s.ar || s.tp_world > 8)) return CAI_ERR_UNSUPPORTED;
+  if (!s.k_blocked || (s.max_ctx % 32)) return CAI_ERR_UNSUPPORTED;
 
   StepPlan* p = new (std::nothrow) StepPlan();
   if (!p) return CAI_ERR_OOM;
@@ -1031,28 +1120,39 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
     const size_t need = (size_t)((P.mat[k].n_rg + grid - 1) / grid) * P.mat[k].ksplit * SK_RPW;
     if (need > slot_floats) slot_floats = need;
   }
-  const size_t attn_floats = (size_t)G * HD + (size_t)SK_WARPS * G * 64 + (size_t)SK_WARPS * G * (HD + 2);
-  size_t xs_bytes = (size_t)kmax * 4;
-  size_t slot_bytes = (slot_floats * 4 + 15) & ~(size_t)15;
-  if (xs_bytes + slot_bytes < attn_floats * 4) xs_bytes = attn_floats * 4 - slot_bytes;
-  xs_bytes = (xs_bytes + 15) & ~(size_t)15;
-  const size_t misc_bytes = 320 + (size_t)HD * 4;
-  const size_t tab_bytes = (((size_t)s.layers * sizeof(SkLayerDev) + 15) & ~(size_t)15) + (size_t)P.n_mats * sizeof(SkPtrs);
-  P.off_slots = (int)xs_bytes;
-  P.off_misc = (int)(xs_bytes + slot_bytes);
-  P.off_tab = (int)((P.off_misc + misc_bytes + 15) & ~(size_t)15);
-  P.off_ring = (int)((P.off_tab + tab_bytes + 127) & ~(size_t)127);
+  // layout: small words | pointer tables | staged row | partial-sum slots | weight rings. The attention phase takes
+  // everything from the staged row up (the fill cursor is on hold then, nothing else lives there).
   int max_smem = 0;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device);
+  const size_t misc_bytes = 320 + (size_t)HD * 4;
+  const size_t tab_bytes = (((size_t)s.layers * sizeof(SkLayerDev) + 15) & ~(size_t)15) + (size_t)P.n_mats * sizeof(SkPtrs);
+  P.off_misc = 0;
+  P.off_tab = (int)((misc_bytes + 15) & ~(size_t)15);
+  P.off_xs = (int)(((size_t)P.off_tab + tab_bytes + 127) & ~(size_t)127);
+  const size_t xs_bytes = ((size_t)kmax * 4 + 15) & ~(size_t)15;
+  const size_t slot_bytes = (slot_floats * 4 + 15) & ~(size_t)15;
+  P.off_slots = (int)(P.off_xs + xs_bytes);
+  P.off_ring = (int)(((size_t)P.off_slots + slot_bytes + 127) & ~(size_t)127);
   const size_t stage_all = (size_t)SK_WARPS * SK_STAGE;
-  int depth = (int)(((size_t)max_smem - (size_t)P.off_ring) / stage_all);
-  if ((size_t)P.off_ring >= (size_t)max_smem) depth = 0;
+  int depth = ((size_t)P.off_ring < (size_t)max_smem) ? (int)(((size_t)max_smem - (size_t)P.off_ring) / stage_all) : 0;
   const int want = env_int("CAI_STEP_RING", 4);
   if (depth > want) depth = want;
   if (depth > 8) depth = 8;
   if (depth < 2) { delete p; return CAI_ERR_UNSUPPORTED; }
   P.ring_depth = depth;
-  p->smem = (size_t)P.off_ring + (size_t)depth * stage_all;
+  p->smem = (size_t)max_smem;                          // one CTA per SM in any case: the attention phase uses what the rings leave
+  {
+    const int avail = max_smem - P.off_xs;
+    int aw = SK_WARPS, ad = 0;
+    for (; aw >= 4; aw >>= 1) {
+      for (ad = 4; ad >= 2; --ad) if (at_smem_bytes(G, HD, aw, ad) <= avail) break;
+      if (ad >= 3 || (aw == 4 && ad >= 2)) break;
+    }
+    if (aw < 4 || ad < 2) { delete p; return CAI_ERR_UNSUPPORTED; }
+    aw = env_int("CAI_STEP_AT_WARPS", aw); ad = env_int("CAI_STEP_AT_DEPTH", ad);
+    if ((aw != 4 && aw != 8 && aw != 16) || ad < 2 || ad > 8 || at_smem_bytes(G, HD, aw, ad) > avail) { delete p; return CAI_ERR_UNSUPPORTED; }
+    P.at_warps = aw; P.at_depth = ad;
+  }
 
   // device tables
   std::vector<SkPtrs> ptrs((size_t)P.n_mats);

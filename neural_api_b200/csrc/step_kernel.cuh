@@ -14,6 +14,7 @@ struct cai_tp_ar;
 struct StepSetup {
   int layers, hidden, q_heads, kv_heads, head_dim, inter, vocab, max_ctx;   // this rank's (local) sizes
   float rms_eps;
+  int k_blocked = 0;                  // K caches block-transposed (cai_k_blocked_index); max_ctx is then a multiple of 32
   const QWeight* embed;
   const QWeight* lm_head;
   const float* final_norm;
