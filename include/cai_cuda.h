@@ -283,6 +283,13 @@ int cai_session_snapshot(cai_session* s);
 int cai_session_restore(cai_session* s);
 /* Device logits of the last step, [batch*vocab] (this rank's shard when tp_size > 1). */
 int cai_session_logits_dev(cai_session* s, const float** out_dev);
+/* One cached K row and V row of (layer, sequence, KV head, position), whatever the internal cache layout: the
+ * check hook that TNNetFusedSDPA's CaptureCacheState / the FKCache, FKCacheCodes, FKCacheScale fields give the
+ * reference's tests (tests/TestNeuralFusedSDPA.pas:329-420). fp32 cache: head_dim floats into k_out_host / v_out_host
+ * (the code and scale outputs may be NULL). int8 cache: head_dim codes into k_codes_host / v_codes_host, the two row
+ * scales into scales_host[0..1], and, when given, code * scale into k_out_host / v_out_host. */
+int cai_session_read_kv_row(cai_session* s, int layer, int seq, int kv_head, int pos, float* k_out_host, float* v_out_host,
+                            int8_t* k_codes_host, int8_t* v_codes_host, float* scales_host);
 /* 1 when the session runs each step as ONE persistent kernel (dense model, one sequence, Q8_0 weights, fp32 cache,
  * head_dim 64 or 128; environment CAI_STEP_KERNEL=0 turns it off), 0 when it enqueues one kernel per operator the way
  * the reference enqueues one OpenCL kernel per layer (neural/neuralopencl.pas:946-1056). */

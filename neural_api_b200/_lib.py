@@ -94,6 +94,7 @@ SIGNATURES = {
     "cai_session_snapshot": [_P],
     "cai_session_restore": [_P],
     "cai_session_logits_dev": [_P, _PP],
+    "cai_session_read_kv_row": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P],
     "cai_session_uses_step_kernel": [_P, C.POINTER(_I)],
     "cai_session_step_trace": [_P, _P, C.POINTER(_I64), C.POINTER(C.c_int32), _I, C.POINTER(_I)],
     "cai_session_last_kv_bytes": [_P, C.POINTER(_I64)],

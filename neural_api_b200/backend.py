@@ -432,6 +432,18 @@ class StreamingDecoder:
     def restore_snapshot(self):
         self.backend._check(self.backend.lib.cai_session_restore(self.handle))
 
+    def read_kv_row(self, layer, pos, kv_head=0, seq=0, int8=False):
+        """One cached row: (k, v) floats for the fp32 cache; (k_codes, v_codes, k_scale, v_scale) for the int8 cache."""
+        hd = self.model.cfg.head_dim
+        k = np.empty(hd, dtype=np.float32)
+        v = np.empty(hd, dtype=np.float32)
+        kc = np.empty(hd, dtype=np.int8)
+        vc = np.empty(hd, dtype=np.int8)
+        sc = np.empty(2, dtype=np.float32)
+        self.backend._check(self.backend.lib.cai_session_read_kv_row(self.handle, layer, seq, kv_head, pos, _ptr(k), _ptr(v),
+                                                                    _ptr(kc), _ptr(vc), _ptr(sc)))
+        return (kc, vc, float(sc[0]), float(sc[1])) if int8 else (k, v)
+
     def step_trace(self, tokens, cap=4096):
         """One step with the phase trace on; returns (ns since the kernel's first stamp, family per stamp)."""
         tok = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))

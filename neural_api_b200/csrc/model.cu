@@ -1382,6 +1382,46 @@ int cai_session_step_trace(cai_session* s, const int32_t* tokens_host, int64_t* 
   return session_check(s);
 }
 
+int cai_session_read_kv_row(cai_session* s, int layer, int seq, int kv_head, int pos, float* k_out_host, float* v_out_host,
+                            int8_t* k_codes_host, int8_t* v_codes_host, float* scales_host) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  cai_session* o = s->kv_owner ? s->kv_owner : s;
+  const cai_llama_config& c = s->m->cfg;
+  const int hd = c.head_dim;
+  if (layer < 0 || layer >= c.layers || seq < 0 || seq >= o->batch || kv_head < 0 || kv_head >= s->m->kv_heads_l || pos < 0 ||
+      pos >= o->len_host[(size_t)seq])
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_read_kv_row: layer %d sequence %d head %d position %d outside the cached rows", layer, seq, kv_head, pos);
+  const size_t head0 = (size_t)layer * o->layer_stride + ((size_t)seq * s->m->kv_heads_l + kv_head) * (size_t)o->ctx_pitch * hd;
+  const size_t row0 = head0 + (size_t)pos * hd;
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (o->kv_int8) {
+    if (!k_codes_host || !v_codes_host || !scales_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_read_kv_row: the int8 cache needs code and scale outputs");
+    const size_t srow = (size_t)layer * o->scale_stride + ((size_t)seq * s->m->kv_heads_l + kv_head) * (size_t)o->ctx_pitch + pos;
+    CAI_CUDA(ctx, cudaMemcpy(k_codes_host, (const int8_t*)o->k_cache + row0, (size_t)hd, cudaMemcpyDeviceToHost));
+    CAI_CUDA(ctx, cudaMemcpy(v_codes_host, (const int8_t*)o->v_cache + row0, (size_t)hd, cudaMemcpyDeviceToHost));
+    CAI_CUDA(ctx, cudaMemcpy(scales_host, o->k_scales + srow, 4, cudaMemcpyDeviceToHost));
+    CAI_CUDA(ctx, cudaMemcpy(scales_host + 1, o->v_scales + srow, 4, cudaMemcpyDeviceToHost));
+    for (int d = 0; d < hd; ++d) {
+      if (k_out_host) k_out_host[d] = scales_host[0] * (float)k_codes_host[d];
+      if (v_out_host) v_out_host[d] = scales_host[1] * (float)v_codes_host[d];
+    }
+    return CAI_OK;
+  }
+  if (!k_out_host || !v_out_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_read_kv_row: null output");
+  if (o->k_blocked) {
+    // piece p (4 channels) of position pos: float offset (p * 32 + pos % 32) * 4 inside the position's 32-row block
+    const float* blk = o->k_cache + head0 + (size_t)(pos >> 5) * 32 * hd + (size_t)(pos & 31) * 4;
+    CAI_CUDA(ctx, cudaMemcpy2D(k_out_host, 16, blk, 32 * 16, 16, (size_t)(hd / 4), cudaMemcpyDeviceToHost));
+  } else {
+    CAI_CUDA(ctx, cudaMemcpy(k_out_host, o->k_cache + row0, (size_t)hd * 4, cudaMemcpyDeviceToHost));
+  }
+  CAI_CUDA(ctx, cudaMemcpy(v_out_host, o->v_cache + row0, (size_t)hd * 4, cudaMemcpyDeviceToHost));
+  if (scales_host) { scales_host[0] = 1.f; scales_host[1] = 1.f; }
+  return CAI_OK;
+}
+
 int cai_session_uses_step_kernel(cai_session* s, int* out_flag) {
   if (!s || !out_flag) return CAI_ERR_INVALID;
   *out_flag = s->plan ? 1 : 0;

@@ -277,8 +277,9 @@ __global__ void synth_weight_kernel(int type, void* __restrict__ codes, __half* 
       const float amax = warp_max(fabsf(v));
       const float scale = amax / 127.0f;
       const float inv = (scale == 0.f) ? 0.f : 1.0f / scale;
-      const float q = v * inv;
-      int e = (q >= 0.f) ? (int)truncf(q + 0.5f) : (int)truncf(q - 0.5f);
+      // (explicitly un-fused: the writer rounds the product, then the sum; a fused multiply-add would round once)
+      const float q = __fmul_rn(v, inv);
+      int e = (q >= 0.f) ? (int)truncf(__fadd_rn(q, 0.5f)) : (int)truncf(__fadd_rn(q, -0.5f));
       e = e > 127 ? 127 : (e < -127 ? -127 : e);
       ((uint8_t*)codes)[row * k + col] = (uint8_t)(e + 128);    // biased resident form
       if (lane == 0) scales[row * sstride + kb] = __float2half_rn(scale);
@@ -295,7 +296,7 @@ __global__ void synth_weight_kernel(int type, void* __restrict__ codes, __half* 
       }
       const float d = bestv / -8.0f;
       const float id = (d == 0.f) ? 0.f : 1.0f / d;
-      int c = (int)truncf(v * id + 8.5f);
+      int c = (int)truncf(__fadd_rn(__fmul_rn(v, id), 8.5f));        // product rounded, then the sum, as in ggml
       c = c > 15 ? 15 : (c < 0 ? 0 : c);
       const int hi = __shfl_down_sync(0xffffffffu, c, 16);
       if (lane < 16) ((uint8_t*)codes)[b * 16 + lane] = (uint8_t)(c | (hi << 4));

@@ -1,0 +1,189 @@
+"""Parity cases that close holes between the other GPU tests: the device quantizer behind the synthetic weights, the
+grouped tensor-core expert path at the OLMoE shape against the oracle, and the int8 KV cache's codes and scales."""
+import numpy as np
+import pytest
+
+from neural_api_b200.backend import LlamaModel, StreamingDecoder, make_config, TYPE_F32, TYPE_I8, TYPE_Q4_0, TYPE_Q8_0
+from oracle import codecs
+from oracle.forward import LlamaConfig, OracleModel, OracleSession, argmax_first, quantize_cache_row, rms_norm, rope_interleaved
+
+pytestmark = pytest.mark.gpu
+
+
+def _names(kw):
+    names = ["model.embed_tokens.weight"]
+    for l in range(kw["layers"]):
+        p = "model.layers.%d." % l
+        names += [p + s for s in ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                                  "self_attn.o_proj.weight")]
+        if kw.get("n_experts", 0):
+            names.append(p + "mlp.gate.weight")
+            for e in range(kw["n_experts"]):
+                names += [p + "mlp.experts.%d.%s.weight" % (e, n) for n in ("gate_proj", "up_proj", "down_proj")]
+        else:
+            names += [p + s for s in ("mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")]
+    return names
+
+
+@pytest.mark.parametrize("ggml_type", [TYPE_Q8_0, TYPE_Q4_0])
+def test_device_quantizer_reproduces_the_oracle_quantizer_byte_for_byte(backend, ggml_type):
+    """cai_model_init_synthetic draws N(0, std) from a generator keyed by (seed, tensor, element) and quantizes on the
+    device. The same model initialised as F32 gives the draws themselves; its Q8_0 / Q4_0 twin must hold exactly the
+    blocks the oracle's quantizer (the GGUF writer's Q8_0 rule, neural/neuralgguf.pas:1950-1993; ggml's Q4_0 rule)
+    makes of those draws."""
+    kw = dict(hidden=256, inter=512, layers=2, heads=4, kv_heads=2, head_dim=64, vocab=512, rms_eps=1e-6, rope_theta=1e4)
+    cfg = make_config(**kw)
+    mf = LlamaModel(backend, cfg)
+    mf.init_synthetic(TYPE_F32, seed=9, std=0.02)
+    mq = LlamaModel(backend, cfg)
+    mq.init_synthetic(ggml_type, seed=9, std=0.02)
+    quant = codecs.quantize_q8_0 if ggml_type == TYPE_Q8_0 else codecs.quantize_q4_0
+    try:
+        checked = 0
+        for name in _names(kw):
+            draws, ty, rows, cols = mf.read_tensor(name, 1 << 22)
+            assert ty == TYPE_F32
+            x = draws[:rows * cols * 4].view(np.float32).reshape(rows, cols)
+            blocks, tyq, r2, c2 = mq.read_tensor(name, 1 << 22)
+            assert (tyq, r2, c2) == (ggml_type, rows, cols)
+            nbytes = rows * codecs.block_bytes_per_row(ggml_type, cols)
+            assert np.array_equal(blocks[:nbytes], quant(x)), name
+            checked += 1
+        assert checked == 1 + 7 * kw["layers"]
+    finally:
+        mf.close()
+        mq.close()
+
+
+def test_grouped_expert_path_at_the_olmoe_shape_matches_the_oracle(backend):
+    """One OLMoE-shaped layer (hidden 2048, 16 heads of 128, 64 experts, top-8, expert width 1024, full-width q/k norm;
+    vocabulary cut), 32 sequences: 256 (token, expert) pairs per step, 4 per expert on average, so the expert products
+    run as grouped tensor-core GEMMs over 16-row tiles. Every sequence's logits against the oracle's one-sequence
+    forward, 1e-3 of the logit RMS, and the same greedy token."""
+    kw = dict(hidden=2048, inter=1024, layers=1, heads=16, kv_heads=16, head_dim=128, vocab=1024, rms_eps=1e-5, rope_theta=1e4,
+              qk_norm=True, n_experts=64, top_k=8, norm_topk=False, moe_inter=1024)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=2, std=0.02)
+    model.finalize()
+    cfg = LlamaConfig(**kw)
+    names = _names(kw) + ["model.norm.weight", "lm_head.weight"]
+    for l in range(kw["layers"]):
+        p = "model.layers.%d." % l
+        names += [p + s for s in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_norm.weight",
+                                  "self_attn.k_norm.weight")]
+    tensors = {}
+    for n in names:
+        buf, ty, rows, cols = model.read_tensor(n, 8 << 20)
+        w = codecs.dequantize(ty, buf[:rows * codecs.block_bytes_per_row(ty, cols)])
+        tensors[n] = w.reshape(rows, cols) if rows > 1 else w
+    oracle = OracleModel.from_hf_tensors(cfg, tensors, interleave=False)
+    batch, n_prompt, n_new = 32, 5, 3
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, kw["vocab"], (batch, n_prompt)).astype(np.int32)
+    sess = StreamingDecoder(model, n_prompt + n_new + 2, batch=batch)
+    osess = [OracleSession(oracle, n_prompt + n_new + 2) for _ in range(batch)]
+    try:
+        for i in range(n_prompt - 1):                       # token-at-a-time on both sides
+            sess.step_forward(prompt[:, i], want_logits=False)
+            for b in range(batch):
+                osess[b].step(int(prompt[b, i]))
+        tok = prompt[:, -1].copy()
+        worst = 0.0
+        for _ in range(n_new):
+            logits, amax = sess.step_forward(tok)
+            nxt = np.empty(batch, dtype=np.int32)
+            for b in range(batch):
+                ref = osess[b].step(int(tok[b]))
+                rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+                worst = max(worst, float(np.max(np.abs(logits[b] - ref))) / rms)
+                nxt[b] = argmax_first(ref)
+            assert np.array_equal(amax, nxt)
+            tok = nxt
+        assert worst < 1e-3, worst
+    finally:
+        sess.close()
+        model.close()
+
+
+def test_int8_cache_rows_hold_the_reference_codes_and_scales(backend):
+    """The rows the append kernel writes into the int8 cache against quantize_cache_row (the reference's row format,
+    neural/neural.cl:2500-2581). Layer 0's K and V rows depend on the token's embedding only, so device and oracle
+    quantize (almost) the same fp32 values: scales agree to float rounding and a code may differ by one unit only where
+    the scaled value sits within rounding of a half-way point."""
+    kw = dict(hidden=256, inter=512, layers=2, heads=8, kv_heads=2, head_dim=64, vocab=512, rms_eps=1e-6, rope_theta=1e4,
+              qkv_bias=True)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=21, std=0.05)
+    model.finalize()
+    cfg = LlamaConfig(**kw)
+    names = _names(kw) + ["model.norm.weight"]
+    for l in range(kw["layers"]):
+        p = "model.layers.%d." % l
+        names += [p + s for s in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_proj.bias",
+                                  "self_attn.k_proj.bias", "self_attn.v_proj.bias")]
+    tensors = {}
+    for n in names:
+        buf, ty, rows, cols = model.read_tensor(n, 1 << 22)
+        w = codecs.dequantize(ty, buf[:rows * codecs.block_bytes_per_row(ty, cols)])
+        tensors[n] = w.reshape(rows, cols) if rows > 1 else w
+    oracle = OracleModel.from_hf_tensors(cfg, tensors, interleave=False)
+    b0 = oracle.blocks[0]
+    hd = cfg.head_dim
+    rng = np.random.default_rng(8)
+    toks = rng.integers(0, kw["vocab"], 40)
+    sess = StreamingDecoder(model, 64, kv_type=TYPE_I8)
+    try:
+        for t in toks:
+            sess.step_forward([int(t)], want_logits=False)
+        total = exact = 0
+        for pos, t in enumerate(toks):
+            h = rms_norm(oracle.embed[int(t)].astype(np.float32), b0["attn_norm"], cfg.rms_eps)
+            k = rope_interleaved(b0["wk"] @ h + b0["bk"], pos, oracle.theta, hd)
+            v = b0["wv"] @ h + b0["bv"]
+            for g in range(cfg.kv_heads):
+                kc, vc, ks, vs = sess.read_kv_row(0, pos, kv_head=g, int8=True)
+                for dev_codes, dev_scale, row in ((kc, ks, k[g * hd:(g + 1) * hd]), (vc, vs, v[g * hd:(g + 1) * hd])):
+                    ref_codes, ref_scale = quantize_cache_row(row)
+                    assert abs(dev_scale - float(ref_scale)) <= 2e-6 * abs(float(ref_scale))
+                    diff = np.abs(dev_codes.astype(np.int32) - ref_codes.astype(np.int32))
+                    assert int(diff.max()) <= 1
+                    total += diff.size
+                    exact += int(np.sum(diff == 0))
+        assert exact >= 0.995 * total, (exact, total)
+    finally:
+        sess.close()
+        model.close()
+
+
+def test_fp32_cache_rows_read_back_in_row_order(backend):
+    """The sessions' K cache is kept block-transposed for the kernels; cai_session_read_kv_row must hand back plain rows:
+    layer 0's K and V rows against the oracle's."""
+    kw = dict(hidden=256, inter=512, layers=1, heads=4, kv_heads=2, head_dim=64, vocab=512, rms_eps=1e-6, rope_theta=1e4)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=5, std=0.05)
+    model.finalize()
+    cfg = LlamaConfig(**kw)
+    names = _names(kw) + ["model.norm.weight", "lm_head.weight", "model.layers.0.input_layernorm.weight",
+                          "model.layers.0.post_attention_layernorm.weight"]
+    tensors = {}
+    for n in names:
+        buf, ty, rows, cols = model.read_tensor(n, 1 << 22)
+        w = codecs.dequantize(ty, buf[:rows * codecs.block_bytes_per_row(ty, cols)])
+        tensors[n] = w.reshape(rows, cols) if rows > 1 else w
+    oracle = OracleModel.from_hf_tensors(cfg, tensors, interleave=False)
+    osess = OracleSession(oracle, 80)
+    rng = np.random.default_rng(1)
+    toks = rng.integers(0, kw["vocab"], 70)                # crosses two 32-row blocks
+    sess = StreamingDecoder(model, 80)
+    try:
+        for t in toks:
+            sess.step_forward([int(t)], want_logits=False)
+            osess.step(int(t))
+        for pos in (0, 1, 31, 32, 33, 63, 64, 69):
+            for g in range(cfg.kv_heads):
+                k, v = sess.read_kv_row(0, pos, kv_head=g)
+                assert np.max(np.abs(k - osess.k[0, g, pos])) < 1e-5
+                assert np.max(np.abs(v - osess.v[0, g, pos])) < 1e-5
+    finally:
+        sess.close()
+        model.close()
