@@ -1063,7 +1063,15 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   CAI_CUDA(ctx, cudaMemsetAsync(s->trace_count, 0, 4, ctx->stream));
   CAI_CUDA(ctx, cudaMemsetAsync(s->amax_tickets, 0, (size_t)B * 4, ctx->stream));
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  if (B == 1 && !kv_owner && !kv_int8 && !c.n_experts && !c.qk_norm && (m->tp_size == 1 || s->ar)) {
+  // Which sessions take the persistent step kernel when nothing forces it (CAI_STEP_KERNEL=1 / 0): a phase of that
+  // kernel costs 6-10 us whatever it streams (grid barrier, staging, the slowest warp), a launch of the per-operator
+  // path ~5 us; measured on B200, the step kernel wins where a layer's products are large (Qwen2.5-32B shape: 9.07 against
+  // 9.96 ms per step) and loses on small layers (Qwen2.5-0.5B shape: 0.95 against 0.78 ms). Rule: on when one layer's
+  // MLP weights on this rank reach 24 M elements, and for every tensor-parallel session (there the alternative pays two
+  // extra launches per layer for the sums over the ranks).
+  const int step_mode = env_int("CAI_STEP_KERNEL", -1);
+  const bool step_auto = ((int64_t)c.hidden * m->inter_l * 3 >= ((int64_t)24 << 20)) || m->tp_size > 1;
+  if (B == 1 && !kv_owner && !kv_int8 && !c.n_experts && !c.qk_norm && (m->tp_size == 1 || s->ar) && (step_mode == 1 || (step_mode < 0 && step_auto))) {
     // the whole step as one persistent kernel when the model is inside what it covers; otherwise (status
     // CAI_ERR_UNSUPPORTED) the session keeps one launch per operator
     StepSetup u;

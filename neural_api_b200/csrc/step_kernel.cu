@@ -1053,7 +1053,7 @@ void step_plan_destroy(StepPlan* p) {
 
 int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
   *out = nullptr;
-  if (env_int("CAI_STEP_KERNEL", 1) == 0) return CAI_ERR_UNSUPPORTED;
+  if (env_int("CAI_STEP_KERNEL", -1) == 0) return CAI_ERR_UNSUPPORTED;
   if (s.kv_heads < 1 || (s.q_heads % s.kv_heads)) return CAI_ERR_UNSUPPORTED;
   const int G = s.q_heads / s.kv_heads, HD = s.head_dim;
   StepFn fn = pick_kernel(G, HD);

@@ -154,7 +154,8 @@ def test_step_kernel_refuses_a_full_context_on_the_host(backend):
     model = LlamaModel(backend, make_config(**kw))
     model.init_synthetic(TYPE_Q8_0, seed=1, std=0.02)
     model.finalize()
-    sess = StreamingDecoder(model, 4)
+    with _env("CAI_STEP_KERNEL", "1"):
+        sess = StreamingDecoder(model, 4)
     try:
         assert sess.uses_step_kernel
         for i in range(4):

@@ -40,6 +40,21 @@ def main():
         tp_tokens.append(tok.copy())
     dev_tokens = sess.decode_greedy(tok, 4)           # the on-device greedy loop under TP
     sess.close()
+    # one sequence: the persistent step kernel, whose sums over the ranks happen inside the kernel (peer loads)
+    os.environ["CAI_STEP_KERNEL"] = "1"
+    sess1 = StreamingDecoder(model, 64, batch=1)
+    used_step_kernel = sess1.uses_step_kernel
+    sess1.prefill(prompt[:1, :-1])
+    tok1 = prompt[:1, -1].copy()
+    sk_logits, sk_tokens = [], []
+    for _ in range(steps):
+        logits, amax = sess1.step_forward(tok1)
+        sk_logits.append(logits.copy())
+        tok1 = amax.copy()
+        sk_tokens.append(tok1.copy())
+    sk_dev = sess1.decode_greedy(tok1, 4)
+    sess1.close()
+    os.environ.pop("CAI_STEP_KERNEL", None)
     model.close()
     ok = 1.0
     if rank == 0:
@@ -64,6 +79,27 @@ def main():
         if worst > 1e-4:
             ok = 0.0
         print("TP worst relative logit difference %.3e over %d ranks" % (worst, world))
+        # the one-sequence session against the single-GPU launch-per-operator path
+        os.environ["CAI_STEP_KERNEL"] = "0"
+        s2 = StreamingDecoder(m1, 64, batch=1)
+        os.environ.pop("CAI_STEP_KERNEL", None)
+        s2.prefill(prompt[:1, :-1])
+        tok = prompt[:1, -1].copy()
+        worst1 = 0.0
+        for i in range(steps):
+            logits, amax = s2.step_forward(tok)
+            rms = float(np.sqrt(np.mean(logits.astype(np.float64) ** 2)))
+            worst1 = max(worst1, float(np.max(np.abs(logits - sk_logits[i]))) / rms)
+            if not np.array_equal(amax, sk_tokens[i]):
+                ok = 0.0
+            tok = amax.copy()
+        if not np.array_equal(s2.decode_greedy(tok, 4), sk_dev):
+            ok = 0.0
+        s2.close()
+        uses_peer = os.environ.get("CAI_TP_ALLREDUCE", "") != "nccl"
+        if worst1 > 1e-4 or (uses_peer and not used_step_kernel):
+            ok = 0.0
+        print("TP step kernel (%s) worst relative logit difference %.3e" % ("on" if used_step_kernel else "off", worst1))
         s1.close()
         m1.close()
         single.close()
