@@ -1046,7 +1046,10 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   }
   if (ok && !kv_owner && m->tp_size > 1 && ((int64_t)B * H) % 4 == 0) {
     // collective: every rank creates its session at the same point
-    if (comm_ar_create(ctx, 2 * c.layers + 1, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
+    // slots: one per call site of the per-operator path; the step kernel's row exchange needs 4 x world rows of pairs
+    // and one more slot for the argmax exchange
+    const int sites = (2 * c.layers + 1 > 4 * m->tp_size + 1) ? 2 * c.layers + 1 : 4 * m->tp_size + 1;
+    if (comm_ar_create(ctx, sites, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
   }
   if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)4 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
   if (ok && B >= 3 && B <= 64) {

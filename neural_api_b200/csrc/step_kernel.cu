@@ -25,11 +25,10 @@
 // the parts in part order and applies the epilogue. The host picks ksplit per matrix kind to balance the warps.
 // Reduction orders are fixed: results do not depend on timing.
 //
-// Tensor parallel: the O and down products leave this rank's partial sums in a peer-visible slot; after the grid
-// barrier CTA 0 raises this rank's arrival word on every peer, every CTA waits (bounded) for all peers' words, CTA c
-// sums slice c of the row over the ranks in rank order with plain peer loads (+ residual) into the local residual
-// stream, and a second grid barrier releases the next phase. No separate all-reduce launches, no library call, no
-// cluster-scope copy of any kind.
+// The residual stream is handed from the O and down products to the next phase without a grid barrier: every value
+// travels as a (value, tag) pair that the readers poll (sk_row_handover). Tensor parallel: the CTA that owns an output
+// row pushes its partial sum to every rank with plain stores over mapped peer memory and adds the ranks' sums of its
+// rows in rank order. No separate all-reduce launches, no library call, no cluster-scope copy of any kind.
 #include "gemv_common.cuh"
 #include "step_kernel.cuh"
 #include <math.h>
@@ -60,6 +59,7 @@ struct SkLayerDev { const float* attn_norm; const float* ffn_norm; const float* 
 
 struct SkTp {
   int rank, world;
+  float* peer_ll1[8];      // every rank's row-exchange area: pairs [2 parities][world][hidden] of (partial sum, tag)
   int* my_flags;
   int* peer_flags[8];
   float* my_slots;
@@ -68,6 +68,7 @@ struct SkTp {
   int* seq;
   int* gave_up;
   int vocab_offset;
+  int argmax_site;         // slot of the (value, index) exchange at the end of the step
 };
 
 struct SkParams {
@@ -84,7 +85,9 @@ struct SkParams {
   int nsplit_max;
   float* cand_val; int* cand_idx;
   int32_t* amax_idx; float* amax_val; int32_t* trace; int32_t* trace_count; long long trace_cap;
-  unsigned* sync;                // [0] arrivals of this launch, [1] abort word
+  int use_ll;                    // hand the residual stream over as tagged pairs (else: store, grid barrier, load)
+  float* ll2;                    // pairs [2 parities][hidden] of (residual stream value, tag): the row every CTA stages next
+  unsigned* sync;                // [0] arrivals of this launch, [1] abort word, [2] tags handed out so far
   int* err; unsigned limit_us;
   unsigned long long* ts;        // optional phase trace: [0] entries, then (time, family) pairs
   int fine;                      // also stamp inside the phases (families 4 staged, 5 products done, 6 epilogue done)
@@ -284,11 +287,16 @@ __device__ __forceinline__ float sk_slot_sum(const float* slots, int rgl, int ks
 // activation staging (every CTA holds the whole input row of the phase, swizzled like the GEMV kernels' rows)
 // ---------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float4 sk_ldcg4(const float* p) { return __ldcg((const float4*)p); }
+__device__ __forceinline__ bool sk_pair_wait2(const SkParams& P, const float* p, int tag, float& v0, float& v1);
 
-// x = gain * (src * inv_rms(src)); src is a row in global memory (emb_tok < 0) or row emb_tok of the embedding
-// table, dequantized on the fly. keep_raw (CTA 0 at layer 0): also store the raw row as the residual stream.
-__device__ __forceinline__ void sk_stage_normed(const SkParams& P, float* xs, float* red, const float* src, int emb_tok,
-                                                const float* gain, float* keep_raw) {
+// x = gain * (src * inv_rms(src)); src is row emb_tok of the embedding table, dequantized on the fly (emb_tok >= 0), or
+// the residual stream (emb_tok < 0): as tagged pairs (`src` points at the pairs, `tag` != 0 is the hand-over waited
+// for) or, tag == 0, as a plain row.
+// keep_raw (CTA 0 at layer 0): also store the raw row as the residual stream. False when a poll ran out of time.
+template <bool LL>
+__device__ __forceinline__ bool sk_stage_normed(const SkParams& P, float* xs, float* red, const float* src, int emb_tok,
+                                                const float* gain, float* keep_raw, int tag = 0) {
+  bool ok = true;
   const int K = P.hidden, K4 = K >> 2;
   float4 xv[SK_XU], gv[SK_XU];
 #pragma unroll
@@ -299,7 +307,12 @@ __device__ __forceinline__ void sk_stage_normed(const SkParams& P, float* xs, fl
     if (c4 < K4) {
       gv[u] = __ldg((const float4*)gain + c4);
       if (emb_tok < 0) {
-        xv[u] = sk_ldcg4(src + 4 * c4);
+        if constexpr (LL) {
+          ok = sk_pair_wait2(P, src + 8 * c4, tag, xv[u].x, xv[u].y) && ok;
+          ok = sk_pair_wait2(P, src + 8 * c4 + 4, tag, xv[u].z, xv[u].w) && ok;
+        } else {
+          xv[u] = sk_ldcg4(src + 4 * c4);            // plain row in global memory (a grid barrier came before)
+        }
       } else {
         const uint32_t w = __ldg((const uint32_t*)(P.emb_codes + (size_t)emb_tok * K) + c4);
         const float d = __half2float(__ldg(P.emb_scales + (size_t)emb_tok * P.emb_sstride + (c4 >> 3)));
@@ -335,7 +348,9 @@ __device__ __forceinline__ void sk_stage_normed(const SkParams& P, float* xs, fl
       *(float4*)(xs + x_phys<CAI_TYPE_Q8_0>((int64_t)c4 * 4)) = y;
     }
   }
+  if constexpr (LL) return __syncthreads_and(ok ? 1 : 0) != 0;
   __syncthreads();
+  return true;
 }
 
 __device__ __forceinline__ void sk_stage_copy(float* xs, const float* src, int K) {
@@ -623,44 +638,78 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// sum of this rank's partial row with the peers' (tensor parallel): slice c of the row on CTA c
+// hand-over of the residual stream between phases without a grid barrier
+//
+// The O and down products end in the residual stream x (hidden floats), and the next phase needs ALL of x on EVERY
+// CTA. Instead of "store, grid barrier, load" each value travels as an 8-byte pair (value, tag) written with one store
+// (8-byte stores are single-copy atomic, so a reader sees the value and its tag together); the tag is a number that is
+// new for every hand-over of every step, and a reader simply re-reads a pair until the tag is the one it waits for.
+// One store-to-load latency replaces barrier + load, and a CTA whose rows are done does not wait for the slowest CTA
+// before it starts to collect the others' rows.
+//   one GPU:  the CTA that owns row r writes x[r] = x[r] + sum_r and the pair (x[r], tag) into `ll2`; every CTA's
+//             staging polls the hidden pairs of ll2.
+//   N GPUs:   the owner first pushes (sum_r, tag) into EVERY rank's `ll1[parity][its rank][r]` (plain stores over
+//             mapped peer memory), then collects the N partial sums of its own rows from its own ll1 (the owners of
+//             the same rows on the other ranks pushed them), adds them in rank order to x[r], and continues as above.
+// Two parities alternate: a pair is rewritten two hand-overs later, which no rank can reach before every CTA of every
+// rank has read the earlier one (each hand-over needs rows from all CTAs of all ranks, and a CTA sends its rows only
+// after its own staging of the previous hand-over). Every poll is bounded on the global timer.
 // ---------------------------------------------------------------------------------------------------------------
-// Returns false when a wait ran out. `site` selects the slot, `k` is this exchange's number within the step.
-__device__ __forceinline__ bool sk_exchange_wait(const SkParams& P, int seq, int* s_flag) {
-  if (threadIdx.x == 0) *s_flag = 1;
-  __syncthreads();
-  if (blockIdx.x == 0 && threadIdx.x < P.tp.world) {
-    __threadfence_system();                                    // the partial row (visible on this GPU since the barrier) first
-    *(volatile int*)(P.tp.peer_flags[threadIdx.x] + P.tp.rank) = seq;
-  }
-  if (threadIdx.x < P.tp.world) {
-    const volatile int* fl = (const volatile int*)(P.tp.my_flags + threadIdx.x);
-    bool ok = *fl >= seq;
-    if (!ok && *(volatile int*)P.tp.gave_up == 0) {
-      const unsigned long long t0 = gtime_ns(), limit = (unsigned long long)P.limit_us * 1000ull;
-      while (true) {
-        if (*fl >= seq) { ok = true; break; }
-        if (gtime_ns() - t0 > limit) break;
-      }
+__device__ __forceinline__ void sk_pair_store(float* p, float v, int tag) {
+  asm volatile("st.volatile.global.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(v), "f"(__int_as_float(tag)) : "memory");
+}
+// Polls one pair until its tag is `tag`; false when the time limit ran out (or the step is being abandoned).
+__device__ __forceinline__ bool sk_pair_wait(const SkParams& P, const float* p, int tag, float& v) {
+  float a, t;
+  asm volatile("ld.volatile.global.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(t) : "l"(p) : "memory");
+  if (__float_as_int(t) == tag) { v = a; return true; }
+  const unsigned long long t0 = gtime_ns(), limit = (unsigned long long)P.limit_us * 1000ull;
+  unsigned polls = 0;
+  while (true) {
+    asm volatile("ld.volatile.global.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(t) : "l"(p) : "memory");
+    if (__float_as_int(t) == tag) { v = a; return true; }
+    if ((++polls & 63u) == 0) {
+      if (*(volatile unsigned*)(P.sync + 1)) return false;
+      if (gtime_ns() - t0 > limit) { *(volatile unsigned*)(P.sync + 1) = 1u; *P.err = 1; return false; }
     }
-    if (!ok) { *P.err = 1; *(volatile int*)P.tp.gave_up = 1; *(volatile unsigned*)(P.sync + 1) = 1u; *s_flag = 0; }
   }
-  __syncthreads();
-  __threadfence_system();
-  return *s_flag != 0;
 }
 
-__device__ __forceinline__ void sk_exchange_sum(const SkParams& P, int site, const float* resid, float* out, int n4) {
-  for (int i = blockIdx.x + gridDim.x * threadIdx.x; i < n4; i += gridDim.x * SK_THREADS) {
-    float4 acc = sk_ldcg4(resid + 4 * i);
-    for (int r = 0; r < P.tp.world; ++r) {
-      float4 v;
-      const float4* src = (const float4*)(P.tp.peer_slots[r] + (size_t)site * P.tp.max_elems) + i;
-      asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src));
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+// Two neighbouring pairs with one 16-byte load.
+__device__ __forceinline__ bool sk_pair_wait2(const SkParams& P, const float* p, int tag, float& v0, float& v1) {
+  float a, ta, b, tb;
+  const unsigned long long t0 = gtime_ns(), limit = (unsigned long long)P.limit_us * 1000ull;
+  unsigned polls = 0;
+  while (true) {
+    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(ta), "=f"(b), "=f"(tb) : "l"(p) : "memory");
+    if (__float_as_int(ta) == tag && __float_as_int(tb) == tag) { v0 = a; v1 = b; return true; }
+    if ((++polls & 63u) == 0) {
+      if (*(volatile unsigned*)(P.sync + 1)) return false;
+      if (gtime_ns() - t0 > limit) { *(volatile unsigned*)(P.sync + 1) = 1u; *P.err = 1; return false; }
     }
-    *((float4*)out + i) = acc;
   }
+}
+
+// End of an O / down phase for output row `row` with this rank's sum `v`: returns false on a time-out.
+__device__ __forceinline__ bool sk_row_handover(const SkParams& P, int row, float v, int tag) {
+  const int par = tag & 1;
+  float x = __ldcg(P.xres + row);
+  bool ok = true;
+  if (P.tp.world > 1) {
+    const size_t at = ((size_t)(par * P.tp.world + P.tp.rank) * P.hidden + row) * 2;
+    for (int r = 0; r < P.tp.world; ++r) sk_pair_store(P.tp.peer_ll1[r] + at, v, tag);
+    const float* mine = P.tp.peer_ll1[P.tp.rank];
+    for (int r = 0; r < P.tp.world; ++r) {
+      float part = 0.f;
+      ok = sk_pair_wait(P, mine + ((size_t)(par * P.tp.world + r) * P.hidden + row) * 2, tag, part) && ok;
+      x += part;
+    }
+  } else {
+    x += v;
+  }
+  P.xres[row] = x;
+  sk_pair_store(P.ll2 + ((size_t)par * P.hidden + row) * 2, x, tag);
+  return ok;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -674,7 +723,7 @@ __device__ __forceinline__ void sk_exchange_sum(const SkParams& P, int site, con
 
 __device__ __forceinline__ void sk_drain() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <int G, int HD>
+template <int G, int HD, bool LL>
 __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
   extern __shared__ __align__(16) unsigned char sk_smem[];
   float* xs = (float*)(sk_smem + P.off_xs);                        // staged input row (the attention phase uses everything from here up)
@@ -699,6 +748,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
   if (token >= P.emb_rows) token = P.emb_rows - 1;
   const int pos = P.pos[0];
   const int tp_seq0 = (P.tp.world > 1) ? *(volatile int*)P.tp.seq : 0;
+  const int tag0 = LL ? (int)*(volatile unsigned*)(P.sync + 2) : 0;   // tags handed out by the steps before this one
 
   // pointer tables and this step's RoPE table into shared memory, then the ring is primed
   {
@@ -741,7 +791,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
   for (int l = 0; l < P.layers; ++l) {
     const SkLayerDev L = tab_lay[l];
     // ---- [q|k|v]: RMSNorm in the staging; RoPE and the KV append in the epilogue
-    sk_stage_normed(P, xs, red, P.xres, l == 0 ? token : -1, L.attn_norm, (l == 0 && blockIdx.x == 0) ? P.xres : nullptr);
+    if (!sk_stage_normed<LL>(P, xs, red, LL ? P.ll2 + (size_t)((tag0 + 2 * l) & 1) * P.hidden * 2 : P.xres, l == 0 ? token : -1,
+                             L.attn_norm, (l == 0 && blockIdx.x == 0) ? P.xres : nullptr, tag0 + 2 * l)) { sk_drain(); return; }
     if (P.fine) sk_trace(P, nts, 4);
     sk_gemv(P, MK_QKV, f, rd_slot, tab, ring_w, xs, slots, lane, warp);
     if (P.fine) sk_trace(P, nts, 5);
@@ -805,26 +856,25 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     {
       const SkMat& M = P.mat[MK_O];
       const int rg0 = sk_rg_begin(M.n_rg, blockIdx.x, gridDim.x), rg1 = sk_rg_begin(M.n_rg, blockIdx.x + 1, gridDim.x);
-      float* out = tp ? P.tp.my_slots + (size_t)(2 * l) * P.tp.max_elems : P.xres;
-      for (int i = threadIdx.x; i < (rg1 - rg0) * 4; i += SK_THREADS) {
-        const int row = 4 * rg0 + i;
-        if (row < M.n_rows) {
-          float v = sk_slot_sum(slots, i >> 2, M.ksplit, i & 3);
-          if (!tp) v += __ldcg(P.xres + row);
-          out[row] = v;
+      if constexpr (LL) {
+        bool ok = true;
+        for (int i = threadIdx.x; i < (rg1 - rg0) * 4; i += SK_THREADS) {
+          const int row = 4 * rg0 + i;
+          if (row < M.n_rows) ok = sk_row_handover(P, row, sk_slot_sum(slots, i >> 2, M.ksplit, i & 3), tag0 + 2 * l + 1) && ok;
+        }
+        if (__syncthreads_or(ok ? 0 : 1)) { sk_drain(); return; }
+      } else {
+        for (int i = threadIdx.x; i < (rg1 - rg0) * 4; i += SK_THREADS) {
+          const int row = 4 * rg0 + i;
+          if (row < M.n_rows) P.xres[row] = sk_slot_sum(slots, i >> 2, M.ksplit, i & 3) + __ldcg(P.xres + row);
         }
       }
     }
-    SK_SYNC(true);
+    if constexpr (!LL) SK_SYNC(true);
     sk_trace(P, nts, FAM_LINEAR);
-    if (tp) {
-      if (!sk_exchange_wait(P, tp_seq0 + (++tp_k), s_flag)) { sk_drain(); return; }
-      sk_exchange_sum(P, 2 * l, P.xres, P.xres, P.hidden >> 2);
-      SK_SYNC(true);
-      sk_trace(P, nts, FAM_COMM);
-    }
     // ---- [up|gate]: RMSNorm in the staging, SwiGLU in the epilogue
-    sk_stage_normed(P, xs, red, P.xres, -1, L.ffn_norm, nullptr);
+    if (!sk_stage_normed<LL>(P, xs, red, LL ? P.ll2 + (size_t)((tag0 + 2 * l + 1) & 1) * P.hidden * 2 : P.xres, -1, L.ffn_norm, nullptr,
+                             tag0 + 2 * l + 1)) { sk_drain(); return; }
     sk_gemv(P, MK_GU, f, rd_slot, tab, ring_w, xs, slots, lane, warp);
     __syncthreads();
     {
@@ -848,28 +898,27 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     {
       const SkMat& M = P.mat[MK_DOWN];
       const int rg0 = sk_rg_begin(M.n_rg, blockIdx.x, gridDim.x), rg1 = sk_rg_begin(M.n_rg, blockIdx.x + 1, gridDim.x);
-      float* out = tp ? P.tp.my_slots + (size_t)(2 * l + 1) * P.tp.max_elems : P.xres;
-      for (int i = threadIdx.x; i < (rg1 - rg0) * 4; i += SK_THREADS) {
-        const int row = 4 * rg0 + i;
-        if (row < M.n_rows) {
-          float v = sk_slot_sum(slots, i >> 2, M.ksplit, i & 3);
-          if (!tp) v += __ldcg(P.xres + row);
-          out[row] = v;
+      if constexpr (LL) {
+        bool ok = true;
+        for (int i = threadIdx.x; i < (rg1 - rg0) * 4; i += SK_THREADS) {
+          const int row = 4 * rg0 + i;
+          if (row < M.n_rows) ok = sk_row_handover(P, row, sk_slot_sum(slots, i >> 2, M.ksplit, i & 3), tag0 + 2 * l + 2) && ok;
+        }
+        if (__syncthreads_or(ok ? 0 : 1)) { sk_drain(); return; }
+      } else {
+        for (int i = threadIdx.x; i < (rg1 - rg0) * 4; i += SK_THREADS) {
+          const int row = 4 * rg0 + i;
+          if (row < M.n_rows) P.xres[row] = sk_slot_sum(slots, i >> 2, M.ksplit, i & 3) + __ldcg(P.xres + row);
         }
       }
     }
-    SK_SYNC(true);
+    if constexpr (!LL) SK_SYNC(true);
     sk_trace(P, nts, FAM_LINEAR);
-    if (tp) {
-      if (!sk_exchange_wait(P, tp_seq0 + (++tp_k), s_flag)) { sk_drain(); return; }
-      sk_exchange_sum(P, 2 * l + 1, P.xres, P.xres, P.hidden >> 2);
-      SK_SYNC(true);
-      sk_trace(P, nts, FAM_COMM);
-    }
   }
 
   // ---- LM head (final norm in the staging) + this CTA's first maximum
-  sk_stage_normed(P, xs, red, P.xres, -1, P.final_norm, nullptr);
+  if (!sk_stage_normed<LL>(P, xs, red, LL ? P.ll2 + (size_t)((tag0 + 2 * P.layers) & 1) * P.hidden * 2 : P.xres, -1, P.final_norm, nullptr,
+                           tag0 + 2 * P.layers)) { sk_drain(); return; }
   sk_gemv(P, MK_HEAD, f, rd_slot, tab, ring_w, xs, slots, lane, warp);
   __syncthreads();
   {
@@ -922,7 +971,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     bool ok = true;
     if (tp) {
       // every rank's (value, global index) through the last slot; all ranks pick the same winner
-      const int site = 2 * P.layers;
+      const int site = P.tp.argmax_site;
       besti += P.tp.vocab_offset;
       if (lane == 0) {
         float* mine = P.tp.my_slots + (size_t)site * P.tp.max_elems;
@@ -969,6 +1018,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
       *P.trace_count = cnt + 1;
       if (tp) *(volatile int*)P.tp.seq = tp_seq0 + tp_k;
     }
+    if (LL && lane == 0) *(volatile unsigned*)(P.sync + 2) = (unsigned)(tag0 + 2 * P.layers);   // (every CTA read tag0 before the first barrier)
     if (lane == 0) {
       __threadfence();
       *(volatile unsigned*)P.sync = 0u;                             // every other CTA has arrived and left
@@ -998,13 +1048,14 @@ struct StepPlan {
   SkLayerDev* lay_dev = nullptr;
   float* cand_val = nullptr;
   int* cand_idx = nullptr;
+  float* ll2 = nullptr;
   unsigned* sync_dev = nullptr;
   int trace_len = 0;
 };
 
 typedef void (*StepFn)(const SkParams);
-static StepFn pick_kernel(int G, int HD) {
-#define SK_CASE(g, hd) if (G == g && HD == hd) return step_kernel<g, hd>
+static StepFn pick_kernel(int G, int HD, bool ll) {
+#define SK_CASE(g, hd) if (G == g && HD == hd) return ll ? step_kernel<g, hd, true> : step_kernel<g, hd, false>
   SK_CASE(1, 64); SK_CASE(2, 64); SK_CASE(4, 64); SK_CASE(7, 64); SK_CASE(8, 64);
   SK_CASE(1, 128); SK_CASE(2, 128); SK_CASE(4, 128); SK_CASE(5, 128); SK_CASE(8, 128);
 #undef SK_CASE
@@ -1047,6 +1098,7 @@ void step_plan_destroy(StepPlan* p) {
   if (p->lay_dev) cudaFree(p->lay_dev);
   if (p->cand_val) cudaFree(p->cand_val);
   if (p->cand_idx) cudaFree(p->cand_idx);
+  if (p->ll2) cudaFree(p->ll2);
   if (p->sync_dev) cudaFree(p->sync_dev);
   delete p;
 }
@@ -1056,7 +1108,11 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
   if (env_int("CAI_STEP_KERNEL", -1) == 0) return CAI_ERR_UNSUPPORTED;
   if (s.kv_heads < 1 || (s.q_heads % s.kv_heads)) return CAI_ERR_UNSUPPORTED;
   const int G = s.q_heads / s.kv_heads, HD = s.head_dim;
-  StepFn fn = pick_kernel(G, HD);
+  // Tagged-pair hand-over of the residual stream: always between GPUs (it replaces a flag exchange and two grid
+  // barriers per sum over the ranks); on one GPU it measured 4 % faster on the Qwen2.5-0.5B shape and 4 % slower on the
+  // Qwen2.5-32B shape than the grid barrier, so there it serves small layers only. CAI_STEP_LL=0/1 forces it on one GPU.
+  const bool use_ll = s.tp_world > 1 || env_int("CAI_STEP_LL", ((int64_t)s.hidden * s.inter * 3 < ((int64_t)24 << 20)) ? 1 : 0) != 0;
+  StepFn fn = pick_kernel(G, HD, use_ll);
   if (!fn) return CAI_ERR_UNSUPPORTED;
   if (s.hidden > SK_THREADS * SK_XU * 4 || (s.hidden % 32) || (s.inter % 32) || s.layers < 1) return CAI_ERR_UNSUPPORTED;
   if (!q8_ok(s.embed) || !q8_ok(s.lm_head) || s.embed->k != s.hidden || s.lm_head->k != s.hidden) return CAI_ERR_UNSUPPORTED;
@@ -1170,11 +1226,13 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
             cudaMalloc((void**)&p->lay_dev, lay.size() * sizeof(SkLayerDev) + 16) == cudaSuccess &&
             cudaMalloc((void**)&p->cand_val, (size_t)grid * 4) == cudaSuccess &&
             cudaMalloc((void**)&p->cand_idx, (size_t)grid * 4) == cudaSuccess &&
-            cudaMalloc((void**)&p->sync_dev, 16) == cudaSuccess;
+            cudaMalloc((void**)&p->sync_dev, 16) == cudaSuccess &&
+            cudaMalloc((void**)&p->ll2, (size_t)4 * s.hidden * sizeof(float)) == cudaSuccess;
   if (ok) {
     ok = cudaMemcpyAsync(p->ptrs_dev, ptrs.data(), ptrs.size() * sizeof(SkPtrs), cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
          cudaMemcpyAsync(p->lay_dev, lay.data(), lay.size() * sizeof(SkLayerDev), cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
-         cudaMemsetAsync(p->sync_dev, 0, 16, ctx->stream) == cudaSuccess && cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+         cudaMemsetAsync(p->sync_dev, 0, 16, ctx->stream) == cudaSuccess &&
+         cudaMemsetAsync(p->ll2, 0, (size_t)4 * s.hidden * sizeof(float), ctx->stream) == cudaSuccess && cudaStreamSynchronize(ctx->stream) == cudaSuccess;
   }
   if (ok) ok = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smem) == cudaSuccess;
   if (ok) {
@@ -1182,17 +1240,22 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
     ok = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, (const void*)fn, SK_THREADS, p->smem) == cudaSuccess && nblk >= 1;
   }
   if (!ok) { cudaGetLastError(); step_plan_destroy(p); return CAI_ERR_UNSUPPORTED; }
-  P.ptrs = p->ptrs_dev; P.lay = p->lay_dev; P.cand_val = p->cand_val; P.cand_idx = p->cand_idx; P.sync = p->sync_dev;
+  P.ptrs = p->ptrs_dev; P.lay = p->lay_dev; P.cand_val = p->cand_val; P.cand_idx = p->cand_idx; P.sync = p->sync_dev; P.ll2 = p->ll2;
+  P.use_ll = use_ll ? 1 : 0;
   P.tp.world = 1; P.tp.rank = 0;
   if (s.tp_world > 1) {
     TpExchange ex;
-    if (comm_ar_exchange(s.ar, &ex) != CAI_OK || ex.sites < 2 * s.layers + 1 || ex.max_elems < s.hidden || (ex.max_elems % 4)) {
+    if (comm_ar_exchange(s.ar, &ex) != CAI_OK || ex.sites < 2 || ex.max_elems < s.hidden || (ex.max_elems % 4)) {
       step_plan_destroy(p);
       return CAI_ERR_UNSUPPORTED;
     }
     P.tp.rank = ex.rank; P.tp.world = ex.world; P.tp.my_flags = ex.my_flags; P.tp.my_slots = ex.my_slots;
     for (int r = 0; r < 8; ++r) { P.tp.peer_flags[r] = ex.peer_flags[r]; P.tp.peer_slots[r] = ex.peer_slots[r]; }
     P.tp.max_elems = ex.max_elems; P.tp.seq = ex.seq; P.tp.gave_up = ex.gave_up; P.tp.vocab_offset = s.vocab_offset;
+    // the row exchange lives at the start of the slot area, the argmax exchange in the last slot
+    P.tp.argmax_site = ex.sites - 1;
+    if ((int64_t)(ex.sites - 1) * ex.max_elems < (int64_t)4 * ex.world * s.hidden) { step_plan_destroy(p); return CAI_ERR_UNSUPPORTED; }
+    for (int r = 0; r < ex.world; ++r) P.tp.peer_ll1[r] = (float*)ex.peer_slots[r];
   }
   // phases per step: per layer 4 products + attention (+ merge) (+ 2 exchanges), head, advance, start
   p->trace_len = 1 + 2 * (s.layers * 16 + 4);
@@ -1222,7 +1285,7 @@ int step_plan_enqueue(cai_ctx* ctx, StepPlan* p, unsigned long long* ts_dev) {
 }
 
 int step_plan_reset_sync(cai_ctx* ctx, StepPlan* p) {
-  CAI_CUDA(ctx, cudaMemsetAsync(p->sync_dev, 0, 16, ctx->stream));
+  CAI_CUDA(ctx, cudaMemsetAsync(p->sync_dev, 0, 8, ctx->stream));     // arrivals and the abort word; the tag counter keeps counting
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return CAI_OK;
 }
