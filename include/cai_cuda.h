@@ -51,6 +51,12 @@ enum {
   CAI_TYPE_F16 = 1,
   CAI_TYPE_Q4_0 = 2,  /* 18-byte blocks of 32: fp16 d, 16 nibble bytes; x = d*(nib-8)  (neuralgguf.pas:822-845) */
   CAI_TYPE_Q8_0 = 8,  /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
+  CAI_TYPE_I8ROW = 124, /* the reference's own int8 weights (what ChatTerminal runs by default): int8 codes [N][K] and ONE fp32
+                         scale per output row, scale = maxabs/127, code = Round(v * (1/maxabs) * 127) with round-half-to-even
+                         (TNNetVolume.QuantizeInt8 / MaxAbsFinite, neural/neuralvolume.pas:12471-12562); the product is the raw
+                         sum of code * x in fp32 with the row scale applied once after the sum (DotProductsTiledInt8,
+                         :12693-12745). Not a ggml id. Host row format of this library: K code bytes followed by the row's
+                         4-byte scale; K % 16 == 0 */
   CAI_TYPE_I8 = 24    /* KV cache only: int8 codes + one fp32 scale per (head, position) row, scale = maxabs/127
                          (neural/neural.cl:2500-2687, TNNetFusedSDPA.BeginIncrementalDecode(MaxCtx, Int8KV = true)) */
 };
@@ -118,6 +124,14 @@ int cai_dequantize(cai_ctx* ctx, int type, const void* blocks_host, int64_t rows
 /* ------------------------------------------------------------------------- */
 int cai_linear_create(cai_ctx* ctx, int type, const void* blocks_host, int64_t n_rows, int64_t k_cols,
                       const float* bias_host /* nullable, N floats */, cai_linear** out);
+/* The same layer from the reference's int8 container (GetInt8QuantData: Codes[n*K + i], Scales[n],
+ * tests/TestNeuralPretrained.pas:7004-7016), i.e. TDotProductSharedKernel.PrepareForComputeInt8
+ * (neural/neuralopencl.pas:844-891) without re-quantizing anything. K % 16 == 0. */
+int cai_linear_create_int8(cai_ctx* ctx, const int8_t* codes_host, const float* scales_host, int64_t n_rows, int64_t k_cols,
+                           const float* bias_host /* nullable */, cai_linear** out);
+/* QuantizeInt8 + MaxAbsFinite on the device for `rows` rows of `cols` floats (neural/neuralvolume.pas:12471-12562):
+ * codes_out_host[rows*cols], scales_out_host[rows] (scale = maxabs/127; 0 for an all-zero row). */
+int cai_quantize_int8_rows(cai_ctx* ctx, const float* w_host, int64_t rows, int64_t cols, int8_t* codes_out_host, float* scales_out_host);
 int cai_linear_destroy(cai_linear* lin);
 int cai_linear_forward(cai_linear* lin, const float* x_host, int batch, float* y_host, int act);
 int cai_linear_forward_dev(cai_linear* lin, const float* x_dev, int batch, float* y_dev, int act);
@@ -229,6 +243,10 @@ int cai_model_destroy(cai_model* m);
  * passes the FULL tensor and the library keeps this rank's slice. */
 int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const void* data_host,
                             int64_t rows, int64_t cols, int interleave_head_dim);
+/* The importer's pQuantizeInt8 switch (neural/neuralpretrained.pas:14876-14888): when on, every F32 / F16 matrix uploaded
+ * afterwards is quantized row by row to CAI_TYPE_I8ROW as it arrives (embedding and LM head included) and the model
+ * runs on the int8 kernels. Call before the first upload. */
+int cai_model_set_int8_weights(cai_model* m, int on);
 /* Fills every tensor on the device: weights N(0, std) from a counter-based
  * generator keyed by (seed, tensor, global element index), quantized to `type`
  * with the GGUF writer's Q8_0 rule (neural/neuralgguf.pas:1950-1993) or ggml's Q4_0

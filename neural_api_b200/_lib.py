@@ -11,7 +11,8 @@ LIB_PATH = os.path.join(HERE, "libcai_cuda.so")
 
 CAI_OK = 0
 TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
-TYPE_I8 = 24          # KV cache only: int8 codes + one fp32 scale per row
+TYPE_I8 = 24              # KV cache only: int8 codes + one fp32 scale per row
+TYPE_I8ROW = 124          # the reference's int8 weights: int8 codes [N][K] + one fp32 scale per output row
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
 STATUS_NAMES = {0: "CAI_OK", 1: "CAI_ERR_INVALID", 2: "CAI_ERR_CUDA", 3: "CAI_ERR_OOM",
                 4: "CAI_ERR_STATE", 5: "CAI_ERR_UNSUPPORTED", 6: "CAI_ERR_COMM"}
@@ -56,6 +57,8 @@ SIGNATURES = {
     "cai_flush_l2": [_P],
     "cai_dequantize": [_P, _I, _P, _I64, _I64, _P],
     "cai_linear_create": [_P, _I, _P, _I64, _I64, _P, _PP],
+    "cai_linear_create_int8": [_P, _P, _P, _I64, _I64, _P, _PP],
+    "cai_quantize_int8_rows": [_P, _P, _I64, _I64, _P, _P],
     "cai_linear_destroy": [_P],
     "cai_linear_forward": [_P, _P, _I, _P, _I],
     "cai_linear_forward_dev": [_P, _P, _I, _P, _I],
@@ -78,6 +81,7 @@ SIGNATURES = {
     "cai_model_create_ep": [_P, C.POINTER(LlamaConfigC), _I, _I, _PP],
     "cai_model_destroy": [_P],
     "cai_model_upload_tensor": [_P, C.c_char_p, _I, _P, _I64, _I64, _I],
+    "cai_model_set_int8_weights": [_P, _I],
     "cai_model_init_synthetic": [_P, _I, C.c_uint64, C.c_float],
     "cai_model_read_tensor": [_P, C.c_char_p, _P, _I64, C.POINTER(_I), C.POINTER(_I64), C.POINTER(_I64)],
     "cai_model_finalize": [_P],

@@ -19,7 +19,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import CaiError, LlamaConfigC, TYPE_F16, TYPE_F32, TYPE_I8, TYPE_Q4_0, TYPE_Q8_0  # noqa: F401
+from ._lib import CaiError, LlamaConfigC, TYPE_F16, TYPE_F32, TYPE_I8, TYPE_I8ROW, TYPE_Q4_0, TYPE_Q8_0  # noqa: F401
 
 
 def _ptr(a):
@@ -97,6 +97,15 @@ class CudaBackend:
 
     def sync(self):
         self._check(self.lib.cai_dev_sync(self.ctx))
+
+    def quantize_int8_rows(self, w):
+        """QuantizeInt8 per row on the device: returns (int8 codes [rows, cols], fp32 scales [rows])."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        rows, cols = w.shape
+        codes = np.empty((rows, cols), dtype=np.int8)
+        scales = np.empty(rows, dtype=np.float32)
+        self._check(self.lib.cai_quantize_int8_rows(self.ctx, _ptr(w), rows, cols, _ptr(codes), _ptr(scales)))
+        return codes, scales
 
     def set_wait_limit_us(self, limit_us):
         """Longest device-side wait on another CTA or GPU before a kernel gives up and raises the error word."""
@@ -207,6 +216,19 @@ class DotProductSharedKernel:
         h = C.c_void_p()
         bias_p = _ptr(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
         b._check(b.lib.cai_linear_create(b.ctx, ggml_type, _ptr(blocks), num_as, size, bias_p, C.byref(h)))
+        self.handle, self.n, self.k = h, num_as, size
+        return 0
+
+    def prepare_for_compute_int8(self, codes, scales, num_as, size, bias=None):
+        """PrepareForComputeInt8 proper (neuralopencl.pas:844-891): the reference's int8 container as it is,
+        codes[num_as * size] int8 and one fp32 scale per row (GetInt8QuantData)."""
+        self.unprepare_for_compute()
+        b = self.backend
+        codes = np.ascontiguousarray(codes, dtype=np.int8).reshape(-1)
+        scales = np.ascontiguousarray(scales, dtype=np.float32).reshape(-1)
+        h = C.c_void_p()
+        bias_p = _ptr(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
+        b._check(b.lib.cai_linear_create_int8(b.ctx, _ptr(codes), _ptr(scales), num_as, size, bias_p, C.byref(h)))
         self.handle, self.n, self.k = h, num_as, size
         return 0
 
@@ -347,6 +369,10 @@ class LlamaModel:
             rows, cols = (w.shape if w.ndim == 2 else (1, w.size))
             perm = hd if (interleave and any(s in name for s in ("q_proj", "k_proj", "q_norm", "k_norm"))) else 0
             self.upload_tensor(name, TYPE_F32, w, rows, cols, perm)
+
+    def set_int8_weights(self, on=True):
+        """The importer's pQuantizeInt8: F32 matrices uploaded afterwards are stored as int8 rows."""
+        self.backend._check(self.backend.lib.cai_model_set_int8_weights(self.handle, int(bool(on))))
 
     def init_synthetic(self, ggml_type, seed, std=0.02):
         self.backend._check(self.backend.lib.cai_model_init_synthetic(self.handle, ggml_type, seed, std))

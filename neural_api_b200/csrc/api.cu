@@ -266,6 +266,47 @@ int cai_linear_create(cai_ctx* ctx, int type, const void* blocks_host, int64_t n
   return CAI_OK;
 }
 
+int cai_linear_create_int8(cai_ctx* ctx, const int8_t* codes_host, const float* scales_host, int64_t n_rows, int64_t k_cols,
+                           const float* bias_host, cai_linear** out) {
+  CAI_TRY(cai_bind(ctx));
+  if (!out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_create_int8: null output");
+  *out = nullptr;
+  if (!codes_host || !scales_host || n_rows < 1 || k_cols < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_create_int8: bad argument");
+  // the library's host row format for this type: K codes, then the row's scale
+  std::vector<unsigned char> rows((size_t)n_rows * ((size_t)k_cols + 4));
+  for (int64_t r = 0; r < n_rows; ++r) {
+    unsigned char* dst = rows.data() + (size_t)r * ((size_t)k_cols + 4);
+    memcpy(dst, codes_host + (size_t)r * (size_t)k_cols, (size_t)k_cols);
+    memcpy(dst + k_cols, scales_host + r, 4);
+  }
+  return cai_linear_create(ctx, CAI_TYPE_I8ROW, rows.data(), n_rows, k_cols, bias_host, out);
+}
+
+int cai_quantize_int8_rows(cai_ctx* ctx, const float* w_host, int64_t rows, int64_t cols, int8_t* codes_out_host, float* scales_out_host) {
+  CAI_TRY(cai_bind(ctx));
+  if (!w_host || !codes_out_host || !scales_out_host || rows < 1 || cols < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_quantize_int8_rows: bad argument");
+  float* x_dev = nullptr; uint8_t* c_dev = nullptr; float* s_dev = nullptr;
+  const size_t n = (size_t)rows * (size_t)cols;
+  int st = CAI_OK;
+  if (cudaMalloc((void**)&x_dev, n * 4) != cudaSuccess || cudaMalloc((void**)&c_dev, n) != cudaSuccess || cudaMalloc((void**)&s_dev, (size_t)rows * 4) != cudaSuccess) {
+    cudaGetLastError();
+    st = cai_fail(ctx, CAI_ERR_OOM, "cai_quantize_int8_rows: device allocation failed");
+  }
+  if (st == CAI_OK && cudaMemcpyAsync(x_dev, w_host, n * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) st = cai_fail(ctx, CAI_ERR_CUDA, "upload failed");
+  if (st == CAI_OK) st = quantize_rows_i8_dev(ctx, x_dev, rows, cols, c_dev, s_dev);
+  if (st == CAI_OK) {
+    cudaError_t e = cudaMemcpyAsync(codes_out_host, c_dev, n, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(scales_out_host, s_dev, (size_t)rows * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) st = cai_fail(ctx, CAI_ERR_CUDA, "cai_quantize_int8_rows -> %s", cudaGetErrorString(e));
+    else for (size_t i = 0; i < n; ++i) codes_out_host[i] = (int8_t)((int)(unsigned char)codes_out_host[i] - 128);   // resident codes are biased
+  }
+  if (x_dev) cudaFree(x_dev);
+  if (c_dev) cudaFree(c_dev);
+  if (s_dev) cudaFree(s_dev);
+  return st;
+}
+
 int cai_linear_destroy(cai_linear* lin) {
   if (!lin) return CAI_ERR_INVALID;
   cudaSetDevice(lin->ctx->device);

@@ -109,6 +109,7 @@ struct QWeight {
   int64_t sstride = 0;         // halves between scale rows: K/32 rounded up to 8
   void* codes = nullptr;
   __half* scales = nullptr;
+  float* rscale = nullptr;     // CAI_TYPE_I8ROW: one fp32 scale per row (codes are int8 + 128, like Q8_0's)
   float* bias = nullptr;       // optional, N floats
   bool owns = true;            // false for row-range views (tied LM head shard)
   bool present = false;
@@ -132,6 +133,10 @@ int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows,
                    int64_t row0, int64_t col0, int interleave_head_dim);
 int qweight_download_blocks(cai_ctx* ctx, const QWeight* w, void* out_host, size_t cap);
 int qweight_dequantize_to_dev(cai_ctx* ctx, const QWeight* w, float* out_dev);
+// F32 host rows -> I8ROW storage, quantized on the device row by row (w allocated as CAI_TYPE_I8ROW); optional row gather
+int qweight_upload_quantize_i8(cai_ctx* ctx, QWeight* w, const float* host, int64_t src_rows, int64_t src_cols, int64_t row0, int64_t col0,
+                               int interleave_head_dim);
+int quantize_rows_i8_dev(cai_ctx* ctx, const float* x_dev, int64_t rows, int64_t cols, uint8_t* codes_biased_dev, float* scales_dev);
 int qweight_init_synthetic(cai_ctx* ctx, QWeight* w, uint64_t seed, uint64_t tensor_id, float std,
                            int64_t global_row0, int64_t global_col0, int64_t global_cols);
 int vec_init_synthetic(cai_ctx* ctx, float* v, int64_t n, uint64_t seed, uint64_t tensor_id, float std,

@@ -33,8 +33,11 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
   const int group = warp / p.ksplit;
   const int kpart = warp - group * p.ksplit;
   // codes per lane chunk (one 16-byte load) and per warp stride
-  constexpr int CHUNK = (TYPE == CAI_TYPE_Q8_0) ? 16 : 32;
-  constexpr int CODE_SHIFT = (TYPE == CAI_TYPE_Q8_0) ? 0 : 1;     // bytes = codes >> shift
+  // (CAI_TYPE_I8ROW rows are stored like Q8_0 codes, int8 + 128, without a scale plane: the row's fp32 scale multiplies
+  // the finished sum, the way DotProductsTiledInt8 applies Scales[a] after the raw code reduction)
+  constexpr int CHUNK = (TYPE != CAI_TYPE_Q4_0) ? 16 : 32;
+  constexpr int CODE_SHIFT = (TYPE != CAI_TYPE_Q4_0) ? 0 : 1;     // bytes = codes >> shift
+  constexpr bool HAS_BLOCK_SCALES = (TYPE != CAI_TYPE_I8ROW);
   const int64_t K = p.k;
   const int64_t row_bytes = K >> CODE_SHIFT;
   const int64_t stride = (int64_t)p.ksplit * 32 * CHUNK;
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
       wp[r] = codes + rows[r] * row_bytes + (k_first >> CODE_SHIFT);
-      sp[r] = (const unsigned short*)scales + rows[r] * p.sstride + (k_first >> 5);
+      sp[r] = HAS_BLOCK_SCALES ? (const unsigned short*)scales + rows[r] * p.sstride + (k_first >> 5) : nullptr;
     }
     int4 wv[RPW], wn[RPW];
     uint32_t sv[RPW], sn[RPW];
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
           wn[r] = ldg_stream16(wp[r]);
-          sn[r] = __ldg(sp[r]);
+          if (HAS_BLOCK_SCALES) sn[r] = __ldg(sp[r]);
         }
       }
     }
@@ -282,7 +285,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
     for (int b = 0; b < NB; ++b) xr[b] = xbase[b] + k_first;
     // the XOR the staging applied to this lane's 16-byte pieces (0 when the activations are read from global memory);
     // k_first and the stride are whole multiples of 32 segments, so it is the same for every stride
-    const int xsw = p.x_in_smem ? ((TYPE == CAI_TYPE_Q8_0) ? ((lane >> 1) & 3) : (lane & 7)) : 0;
+    const int xsw = p.x_in_smem ? ((TYPE != CAI_TYPE_Q4_0) ? ((lane >> 1) & 3) : (lane & 7)) : 0;
 
     for (int it = 0; it < (RING ? iters_w : iters); ++it) {
       if constexpr (RING) {
@@ -304,9 +307,8 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
 #pragma unroll
           for (int r = 0; r < RPW; ++r) {
             wp[r] += stride_b;
-            sp[r] += stride_s;
             wn[r] = ldg_stream16(wp[r]);
-            sn[r] = __ldg(sp[r]);
+            if (HAS_BLOCK_SCALES) { sp[r] += stride_s; sn[r] = __ldg(sp[r]); }
           }
         }
       }
@@ -317,7 +319,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
         for (int b = 0; b < NB; ++b) part[r][b] = 0ull;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        if (TYPE == CAI_TYPE_Q8_0) {
+        if (TYPE != CAI_TYPE_Q4_0) {
           float4 xv[NB];
 #pragma unroll
           for (int b = 0; b < NB; ++b) xv[b] = *(const float4*)(xr[b] + 4 * (i ^ xsw));
@@ -344,7 +346,7 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
       }
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        const float d = half_bits_to_float(sv[r]);
+        const float d = HAS_BLOCK_SCALES ? half_bits_to_float(sv[r]) : 1.0f;
         const f32x2_t d2 = pack2(d, d);
 #pragma unroll
         for (int b = 0; b < NB; ++b) acc2[r][b] = fma2(d2, part[r][b], acc2[r][b]);
@@ -386,6 +388,14 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
           }
       } else {
         store = false;
+      }
+    }
+    if (store && !HAS_BLOCK_SCALES) {
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const float rs = p.out_scale[rows[r]];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) acc[r][b] *= rs;
       }
     }
     if (store) gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias, resid_pre, true);
@@ -519,7 +529,7 @@ bool linear_uses_tensor_cores(const QWeight* w, int batch) {
 }
 
 bool linear_can_fuse_norm(const QWeight* w, int batch) {
-  if (!w || (w->type != CAI_TYPE_Q8_0 && w->type != CAI_TYPE_Q4_0)) return false;
+  if (!w || (w->type != CAI_TYPE_Q8_0 && w->type != CAI_TYPE_Q4_0 && w->type != CAI_TYPE_I8ROW)) return false;
   if (env_int("CAI_FUSE_NORM", 1) == 0) return false;
   const int nb = batch >= 5 ? 8 : (batch >= 3 ? 4 : (batch == 2 ? 2 : 1));
   if (batch > 8) return false;       // several batch tiles would each redo the norm; keep the separate kernel
@@ -551,7 +561,8 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     p.cache_len = a.cache_len_dev;
   }
   const int64_t units = (a.epilogue == EPI_SWIGLU) ? w->n / 2 : w->n;
-  const bool quant = (w->type == CAI_TYPE_Q8_0 || w->type == CAI_TYPE_Q4_0);
+  const bool quant = (w->type == CAI_TYPE_Q8_0 || w->type == CAI_TYPE_Q4_0 || w->type == CAI_TYPE_I8ROW);
+  p.out_scale = w->rscale;
   if (!quant) {
     const int threads = 128;
     const int wpc = threads / 32;
@@ -590,7 +601,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   if (!indexed) nb = a.batch >= 5 ? 8 : (a.batch >= 3 ? 4 : (a.batch == 2 ? 2 : 1));
   // Rows per warp / warps per row group: every CTA of the launch should be resident at once (one wave)
   // with as many 16-byte loads in flight as possible; small-N / large-K shapes split K over the warps of a CTA.
-  const int64_t lane_chunk = (w->type == CAI_TYPE_Q8_0) ? 16 : 32;
+  const int64_t lane_chunk = (w->type != CAI_TYPE_Q4_0) ? 16 : 32;
   const int64_t k_iters_1 = (w->k + lane_chunk * 32 - 1) / (lane_chunk * 32);   // strides of one warp alone
   int rpw, ksplit;
   const int64_t target_groups = (int64_t)ctx->sm_count * 16;   // warps' worth of row groups for a full machine
@@ -621,7 +632,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   // activations in shared memory when they fit beside a healthy number of resident CTAs
   const size_t x_bytes = (size_t)nb * (size_t)w->k * 4;
   p.x_in_smem = (x_bytes <= (size_t)env_int("CAI_GEMV_XSMEM", 64 * 1024)) ? 1 : 0;
-  const bool ring_ok = !indexed && nb <= 2 && (w->k % 32) == 0 && (w->sstride % 8) == 0 && ((uintptr_t)w->scales % 16) == 0 &&
+  const bool ring_ok = w->type != CAI_TYPE_I8ROW && !indexed && nb <= 2 && (w->k % 32) == 0 && (w->sstride % 8) == 0 && ((uintptr_t)w->scales % 16) == 0 &&
                        ((uintptr_t)w->codes % 16) == 0;
   int want = env_int("CAI_GEMV_RING", -1);
   const size_t stage_warp = (size_t)rpw * (512 + lane_chunk * 2);      // ring bytes of one warp and stage
@@ -659,6 +670,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   }
   cudaError_t e;
   if (w->type == CAI_TYPE_Q8_0) e = launch_quant_nb<CAI_TYPE_Q8_0>(ctx, p, nb, rpw, grid, threads, smem);
+  else if (w->type == CAI_TYPE_I8ROW) e = launch_quant_nb<CAI_TYPE_I8ROW>(ctx, p, nb, rpw, grid, threads, smem);
   else e = launch_quant_nb<CAI_TYPE_Q4_0>(ctx, p, nb, rpw, grid, threads, smem);
   if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "gemv launch setup -> %s", cudaGetErrorString(e));
   CAI_LAUNCHED(ctx);

@@ -29,6 +29,7 @@ struct GemvParams {
   const int32_t* expert_ids;
   int x_row_div;
   const float* row_scale;
+  const float* out_scale;   // CAI_TYPE_I8ROW: one fp32 scale per weight row, applied to the finished sum (before the bias)
   int* err_flag;    // set by a kernel whose bounded wait ran out
   const float* norm_gain;   // fused per-token RMSNorm of the input (needs x_in_smem), NULL = none
   float norm_eps;
@@ -110,7 +111,7 @@ __device__ __forceinline__ f32x2_t q4_word_fma(uint32_t w, const float4& xlo, co
 // fall on 8 different bank groups.
 template <int TYPE>
 __device__ __forceinline__ int64_t x_phys(int64_t k) {
-  if (TYPE == CAI_TYPE_Q8_0) return (k & ~(int64_t)12) | ((((k >> 2) & 3) ^ ((k >> 5) & 3)) << 2) | (k & 3);
+  if (TYPE != CAI_TYPE_Q4_0) return (k & ~(int64_t)12) | ((((k >> 2) & 3) ^ ((k >> 5) & 3)) << 2) | (k & 3);
   return (k & ~(int64_t)28) | ((((k >> 2) & 7) ^ ((k >> 5) & 7)) << 2) | (k & 3);
 }
 

@@ -83,6 +83,7 @@ struct cai_model {
   std::vector<LayerW> layers;
   bool finalized = false;
   int sessions = 0;
+  bool int8_weights = false;     // quantize F32 matrices to int8 rows as they are uploaded (the importer's pQuantizeInt8)
 };
 
 static int ensure_weight(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
@@ -222,18 +223,25 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
   if (type != CAI_TYPE_F32 || vec_len() != (n))                                                                 \
     return cai_fail(ctx, CAI_ERR_INVALID, "'%s': expected an F32 vector of %lld", hf_name, (long long)(n))
   m->finalized = false;
+  // the importer's pQuantizeInt8: F32 matrices become int8 rows (one fp32 scale per row) as they arrive
+  const bool q8 = m->int8_weights && type == CAI_TYPE_F32;
+  const int stype = q8 ? CAI_TYPE_I8ROW : type;
+  auto put = [&](QWeight* w, int64_t row0, int64_t col0, int interleave) -> int {
+    if (q8) return qweight_upload_quantize_i8(ctx, w, (const float*)data_host, rows, cols, row0, col0, interleave);
+    return qweight_upload(ctx, w, data_host, rows, cols, row0, col0, interleave);
+  };
   switch (t.kind) {
     case T_EMBED: {
       NEED_SHAPE(c.vocab, H);
-      CAI_TRY(ensure_weight(ctx, &m->embed, type, c.vocab, H));
-      CAI_TRY(qweight_upload(ctx, &m->embed, data_host, rows, cols, 0, 0, 0));
+      CAI_TRY(ensure_weight(ctx, &m->embed, stype, c.vocab, H));
+      CAI_TRY(put(&m->embed, 0, 0, 0));
       m->have_embed = true;
       return CAI_OK;
     }
     case T_LM_HEAD: {
       NEED_SHAPE(c.vocab, H);
-      CAI_TRY(ensure_weight(ctx, &m->lm_head, type, m->vocab_l, H));
-      CAI_TRY(qweight_upload(ctx, &m->lm_head, data_host, rows, cols, (int64_t)r * m->vocab_l, 0, 0));
+      CAI_TRY(ensure_weight(ctx, &m->lm_head, stype, m->vocab_l, H));
+      CAI_TRY(put(&m->lm_head, (int64_t)r * m->vocab_l, 0, 0));
       m->have_head = true;
       return CAI_OK;
     }
@@ -258,11 +266,11 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
     case T_Q: case T_K: case T_V: {
       const bool isq = t.kind == T_Q;
       NEED_SHAPE(isq ? QW : KW, H);
-      CAI_TRY(ensure_weight(ctx, &L.wqkv, type, qkv_rows, H));
+      CAI_TRY(ensure_weight(ctx, &L.wqkv, stype, qkv_rows, H));
       const int64_t nloc = isq ? m->qw_l : m->kw_l;
       const int64_t dst0 = isq ? 0 : (t.kind == T_K ? m->qw_l : m->qw_l + m->kw_l);
       QWeight view = qweight_rows_view(L.wqkv, dst0, nloc);
-      CAI_TRY(qweight_upload(ctx, &view, data_host, rows, cols, (int64_t)r * nloc, 0, t.kind == T_V ? 0 : interleave_head_dim));
+      CAI_TRY(put(&view, (int64_t)r * nloc, 0, t.kind == T_V ? 0 : interleave_head_dim));
       L.have |= isq ? HAVE_Q : (t.kind == T_K ? HAVE_K : HAVE_V);
       return CAI_OK;
     }
@@ -278,26 +286,26 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
     }
     case T_O: {
       NEED_SHAPE(H, QW);
-      CAI_TRY(ensure_weight(ctx, &L.wo, type, H, m->qw_l));
-      CAI_TRY(qweight_upload(ctx, &L.wo, data_host, rows, cols, 0, (int64_t)r * m->qw_l, 0));
+      CAI_TRY(ensure_weight(ctx, &L.wo, stype, H, m->qw_l));
+      CAI_TRY(put(&L.wo, 0, (int64_t)r * m->qw_l, 0));
       L.have |= HAVE_O;
       return CAI_OK;
     }
     case T_GATE: case T_UP: {
       if (c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': dense MLP tensor in an MoE configuration", hf_name);
       NEED_SHAPE(c.inter, H);
-      CAI_TRY(ensure_weight(ctx, &L.wgu, type, 2 * (int64_t)m->inter_l, H));
+      CAI_TRY(ensure_weight(ctx, &L.wgu, stype, 2 * (int64_t)m->inter_l, H));
       // up rows first, gate rows second
       QWeight view = qweight_rows_view(L.wgu, t.kind == T_UP ? 0 : m->inter_l, m->inter_l);
-      CAI_TRY(qweight_upload(ctx, &view, data_host, rows, cols, (int64_t)r * m->inter_l, 0, 0));
+      CAI_TRY(put(&view, (int64_t)r * m->inter_l, 0, 0));
       L.have |= (t.kind == T_UP) ? HAVE_UP : HAVE_GATE;
       return CAI_OK;
     }
     case T_DOWN: {
       if (c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': dense MLP tensor in an MoE configuration", hf_name);
       NEED_SHAPE(H, c.inter);
-      CAI_TRY(ensure_weight(ctx, &L.wdown, type, H, m->inter_l));
-      CAI_TRY(qweight_upload(ctx, &L.wdown, data_host, rows, cols, 0, (int64_t)r * m->inter_l, 0));
+      CAI_TRY(ensure_weight(ctx, &L.wdown, stype, H, m->inter_l));
+      CAI_TRY(put(&L.wdown, 0, (int64_t)r * m->inter_l, 0));
       L.have |= HAVE_DOWN;
       return CAI_OK;
     }
@@ -337,6 +345,16 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
   return cai_fail(ctx, CAI_ERR_INVALID, "'%s': unhandled tensor", hf_name);
 }
 
+int cai_model_set_int8_weights(cai_model* m, int on) {
+  if (!m) return CAI_ERR_INVALID;
+  cai_ctx* ctx = m->ctx;
+  if (m->sessions > 0) return cai_fail(ctx, CAI_ERR_STATE, "weights are immutable while sessions exist");
+  if (on && (m->cfg.n_experts > 0 || m->tp_size > 1))
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8-on-upload covers dense single-GPU models (a row's scale spans the whole row; expert banks keep their storage type)");
+  m->int8_weights = on != 0;
+  return CAI_OK;
+}
+
 int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std) {
   if (!m) return CAI_ERR_INVALID;
   cai_ctx* ctx = m->ctx;
@@ -346,6 +364,8 @@ int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std) {
   const int H = c.hidden, QW = c.heads * c.head_dim, KW = c.kv_heads * c.head_dim, r = m->tp_rank;
   if ((H % 32) || (QW % 32) || (c.n_experts ? (c.moe_inter % 32) : (c.inter % 32)))
     return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "synthetic init needs 32-aligned widths");
+  if (type == CAI_TYPE_I8ROW && (c.n_experts > 0 || m->tp_size > 1))
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "synthetic int8 rows cover dense single-GPU models");
   m->finalized = false;
   CAI_TRY(ensure_weight(ctx, &m->embed, type, c.vocab, H));
   CAI_TRY(qweight_init_synthetic(ctx, &m->embed, seed, 9000, std, 0, 0, H));

@@ -8,7 +8,8 @@
 // token 0 is a real row)
 // ---------------------------------------------------------------------------
 __global__ void embed_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
-                             int64_t sstride, int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld) {
+                             int64_t sstride, int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld,
+                             const float* __restrict__ rscale) {
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x;
@@ -25,7 +26,8 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
       const uint8_t byte = ((const uint8_t*)codes)[blk * 16 + (e & 15)];
       const int nib = (e < 16) ? (byte & 0x0F) : (byte >> 4);
       v = __half2float(scales[tok * sstride + c / CAI_QK]) * (float)(nib - 8);
-    } else if (type == CAI_TYPE_F16) v = __half2float(((const __half*)codes)[i]);
+    } else if (type == CAI_TYPE_I8ROW) v = rscale[tok] * (float)((int)((const uint8_t*)codes)[i] - 128);
+    else if (type == CAI_TYPE_F16) v = __half2float(((const __half*)codes)[i]);
     else v = ((const float*)codes)[i];
     out[(int64_t)b * ld + c] = v;
   }
@@ -33,7 +35,7 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
 
 int op_embed(cai_ctx* ctx, const QWeight* t, const int32_t* tokens_dev, int batch, float* out, int64_t ld) {
   ctx->cur_family = FAM_OTHER;
-  pdl_launch(ctx, embed_kernel, dim3(batch), dim3(256), 0, t->type, (const void*)t->codes, (const __half*)t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld);
+  pdl_launch(ctx, embed_kernel, dim3(batch), dim3(256), 0, t->type, (const void*)t->codes, (const __half*)t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld, (const float*)t->rscale);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

@@ -42,7 +42,8 @@ constexpr int SK_WARPS = 16;
 constexpr int SK_RPW = 4;
 constexpr int SK_STAGE = SK_RPW * (512 + 32);        // bytes of one ring stage: 4 x 512 codes + 4 x 16 fp16 scales
 constexpr int SK_XU = 4;                             // float4 pieces per thread of a normed row (hidden <= 8192)
-constexpr int SK_FOLD_FLOATS = 16384;                // splits x q_width up to which the O staging merges the splits itself
+constexpr int SK_FOLD_FLOATS = 49152;                // splits x q_width up to which the O staging merges the splits itself
+constexpr int SK_FOLD_MAX_CHUNK = 512;               // ... and the longest split worth accepting for that (one 32-row tile per warp)
 constexpr int SK_MIN_CHUNK = 64;                     // fewest cached rows of a context split
 enum { MK_QKV = 0, MK_O = 1, MK_GU = 2, MK_DOWN = 3, MK_HEAD = 4 };
 
@@ -479,8 +480,6 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
     const int j_begin = split * chunk;
     int j_end = j_begin + chunk; if (j_end > n) j_end = n;
     __syncthreads();                                                     // the previous item's shared memory is free
-    for (int i = threadIdx.x; i < G * HD; i += SK_THREADS) q_s[i] = __ldcg(P.qbuf + (size_t)g * G * HD + i);
-    __syncthreads();
     float m[G], l[G];
     f32x2_t acc[G][DP2];
 #pragma unroll
@@ -535,6 +534,9 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
       };
 #pragma unroll 1
       for (int s = 0; s < AT_DEPTH - 1; ++s) issue();
+      // (the cached rows are on their way: now fetch this step's query rows)
+      for (int i = threadIdx.x; i < G * HD; i += AT_WARPS * 32) q_s[i] = __ldcg(P.qbuf + (size_t)g * G * HD + i);
+      asm volatile("bar.sync 1, %0;" ::"r"(AT_WARPS * 32) : "memory");       // the attention warps only
 #pragma unroll 1
       for (int ti = 0; ti < my_tiles; ++ti) {
         const int tile = j_begin + 32 * (warp + AT_WARPS * ti);
@@ -604,7 +606,9 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
       asm volatile("cp.async.wait_all;" ::: "memory");     // the rings become the merge area below
     }
     __syncthreads();
-    if (warp < AT_WARPS) {
+    const int n_tiles_all = (j_end - j_begin + 31) >> 5;
+    const int nw = n_tiles_all < AT_WARPS ? n_tiles_all : AT_WARPS;      // warps that had a tile
+    if (warp < nw) {
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
@@ -622,9 +626,9 @@ __device__ __forceinline__ void sk_attention(const SkParams& P, const SkLayerDev
     for (int idx = threadIdx.x; idx < G * HD; idx += SK_THREADS) {
       const int hh = idx / HD, d = idx - hh * HD;
       float mx = -INFINITY;
-      for (int w = 0; w < AT_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
+      for (int w = 0; w < nw; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
       float lt = 0.f, at = 0.f;
-      for (int w = 0; w < AT_WARPS; ++w) {
+      for (int w = 0; w < nw; ++w) {
         const float* src = merge_s + ((size_t)w * G + hh) * (HD + 2);
         const float sc = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mx);
         lt += src[1] * sc;
@@ -784,6 +788,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
   int chunk = (n + P.nsplit_max - 1) / P.nsplit_max;
   if (chunk < SK_MIN_CHUNK) chunk = SK_MIN_CHUNK;
   chunk = (chunk + 31) & ~31;
+  {
+    // Fewer, longer splits when that lets the O staging merge them itself: a phase of this kernel costs microseconds
+    // whatever it moves, so the separate merge phase (and its grid barrier) is worth more than the last bit of
+    // parallelism over the context, as long as a split stays within one 32-row tile per warp.
+    const int max_fold = SK_FOLD_FLOATS / P.qw;
+    if (max_fold >= 1) {
+      const int c2 = (((n + max_fold - 1) / max_fold) + 31) & ~31;
+      if (c2 > chunk && c2 <= SK_FOLD_MAX_CHUNK) chunk = c2;
+    }
+  }
   const int used = (n + chunk - 1) / chunk;
   const bool fold = used * P.qw <= SK_FOLD_FLOATS;
   const bool tp = P.tp.world > 1;

@@ -9,17 +9,19 @@ size_t cai_type_row_bytes(int type, int64_t k) {
     case CAI_TYPE_F16: return (size_t)k * 2;
     case CAI_TYPE_Q8_0: return (size_t)(k / CAI_QK) * CAI_Q8_0_BLOCK_BYTES;
     case CAI_TYPE_Q4_0: return (size_t)(k / CAI_QK) * CAI_Q4_0_BLOCK_BYTES;
+    case CAI_TYPE_I8ROW: return (size_t)k + 4;      // codes, then the row's fp32 scale
   }
   return 0;
 }
 bool cai_type_supported(int type) {
-  return type == CAI_TYPE_F32 || type == CAI_TYPE_F16 || type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0;
+  return type == CAI_TYPE_F32 || type == CAI_TYPE_F16 || type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0 || type == CAI_TYPE_I8ROW;
 }
 size_t QWeight::row_code_bytes() const {
   switch (type) {
     case CAI_TYPE_F32: return (size_t)k * 4;
     case CAI_TYPE_F16: return (size_t)k * 2;
     case CAI_TYPE_Q8_0: return (size_t)k;
+    case CAI_TYPE_I8ROW: return (size_t)k;
     case CAI_TYPE_Q4_0: return (size_t)k / 2;
   }
   return 0;
@@ -27,6 +29,7 @@ size_t QWeight::row_code_bytes() const {
 size_t QWeight::code_bytes() const { return (size_t)n * row_code_bytes(); }
 size_t QWeight::scale_bytes() const {
   if (type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0) return (size_t)n * (size_t)(k / CAI_QK) * 2;
+  if (type == CAI_TYPE_I8ROW) return (size_t)n * 4;
   return 0;
 }
 size_t QWeight::scale_alloc_bytes() const {
@@ -39,6 +42,8 @@ int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
   if (n <= 0 || k <= 0) return cai_fail(ctx, CAI_ERR_INVALID, "weight shape %lld x %lld", (long long)n, (long long)k);
   if ((type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0) && (k % CAI_QK) != 0)
     return cai_fail(ctx, CAI_ERR_INVALID, "quantized rows need a multiple of 32 columns, got %lld", (long long)k);
+  if (type == CAI_TYPE_I8ROW && (k % 16) != 0)
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 rows need a multiple of 16 columns, got %lld", (long long)k);
   qweight_free(w);
   w->type = type; w->n = n; w->k = k; w->owns = true; w->present = false;
   // scale rows padded to 8 halves so that every row (and every 256-column tile of it) starts on a
@@ -54,6 +59,9 @@ int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
   if (sb) {
     if (cudaMalloc((void**)&w->scales, sb + 64) != cudaSuccess) { cudaGetLastError(); cudaFree(w->codes); w->codes = nullptr; return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(%zu) failed", sb); }
   }
+  if (type == CAI_TYPE_I8ROW) {
+    if (cudaMalloc((void**)&w->rscale, (size_t)n * 4 + 64) != cudaSuccess) { cudaGetLastError(); cudaFree(w->codes); w->codes = nullptr; return cai_fail(ctx, CAI_ERR_OOM, "cudaMalloc(row scales) failed"); }
+  }
   return CAI_OK;
 }
 
@@ -61,9 +69,10 @@ void qweight_free(QWeight* w) {
   if (w->owns) {
     if (w->codes) cudaFree(w->codes);
     if (w->scales) cudaFree(w->scales);
+    if (w->rscale) cudaFree(w->rscale);
     if (w->bias) cudaFree(w->bias);
   }
-  w->codes = nullptr; w->scales = nullptr; w->bias = nullptr; w->present = false; w->n = w->k = 0; w->type = -1;
+  w->codes = nullptr; w->scales = nullptr; w->rscale = nullptr; w->bias = nullptr; w->present = false; w->n = w->k = 0; w->type = -1;
 }
 
 QWeight qweight_rows_view(const QWeight& w, int64_t row0, int64_t nrows) {
@@ -72,6 +81,7 @@ QWeight qweight_rows_view(const QWeight& w, int64_t row0, int64_t nrows) {
   v.n = nrows;
   v.codes = (char*)w.codes + (size_t)row0 * w.row_code_bytes();
   v.scales = w.scales ? w.scales + (size_t)row0 * (size_t)w.sstride : nullptr;
+  v.rscale = w.rscale ? w.rscale + row0 : nullptr;
   v.bias = w.bias ? w.bias + row0 : nullptr;
   return v;
 }
@@ -115,6 +125,79 @@ __global__ void unpack_blocks_kernel(uint16_t* __restrict__ dst, int64_t nrows, 
   }
 }
 
+// ---------------------------------------------------------------------------
+// int8 rows (CAI_TYPE_I8ROW): staged host rows [K codes | fp32 scale] <-> planes (codes biased by 128, row scales)
+// ---------------------------------------------------------------------------
+__global__ void repack_i8rows_kernel(const uint32_t* __restrict__ src, int64_t nrows, int64_t k, uint32_t* __restrict__ codes,
+                                     float* __restrict__ rscale) {
+  const int64_t wpr = k / 4 + 1;                        // 32-bit words per staged row
+  const int64_t total = nrows * wpr;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / wpr, j = i - row * wpr;
+    if (j == wpr - 1) rscale[row] = __uint_as_float(src[i]);
+    else codes[row * (k / 4) + j] = src[i] ^ 0x80808080u;
+  }
+}
+__global__ void unpack_i8rows_kernel(uint32_t* __restrict__ dst, int64_t nrows, int64_t k, const uint32_t* __restrict__ codes,
+                                     const float* __restrict__ rscale) {
+  const int64_t wpr = k / 4 + 1;
+  const int64_t total = nrows * wpr;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / wpr, j = i - row * wpr;
+    dst[i] = (j == wpr - 1) ? __float_as_uint(rscale[row]) : (codes[row * (k / 4) + j] ^ 0x80808080u);
+  }
+}
+
+// TNNetVolume.MaxAbsFinite + QuantizeInt8, scalar form (neural/neuralvolume.pas:12471-12562), one CTA per row:
+// maxabs over the finite magnitudes; scale = maxabs / 127; code = Round(v * (1 / maxabs) * 127) with the products
+// in that order (every intermediate bounded by 1), clamped to +-127 (which is what maps +-Inf), round-half-to-even,
+// NaN -> 0; a denormal row maximum scales in double (127 / maxabs), a zero row gives zero codes and scale 0.
+// Codes are stored biased by 128 like the resident Q8_0 codes. `gen` != 0: the row is not read but drawn:
+// std * N(0,1) keyed by (seed, tensor, global element), the synthetic initialisation.
+__device__ __forceinline__ float keyed_normal(uint64_t seed, uint64_t tensor_id, uint64_t elem);
+__global__ void quantize_i8rows_kernel(const float* __restrict__ x, int64_t k, uint8_t* __restrict__ codes, float* __restrict__ rscale,
+                                       int gen, uint64_t seed, uint64_t tensor_id, float std, int64_t grow0, int64_t gcol0, int64_t gcols) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  auto value = [&](int64_t c) -> float {
+    if (gen) return std * keyed_normal(seed, tensor_id, (uint64_t)(grow0 + row) * (uint64_t)gcols + (uint64_t)(gcol0 + c));
+    return x[row * k + c];
+  };
+  float m = 0.f;
+  for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
+    const float a = fabsf(value(c));
+    if (__float_as_uint(a) <= 0x7F7FFFFFu) m = fmaxf(m, a);            // finite magnitudes only (NaN and Inf fail the test)
+  }
+  m = block_max(m, red);
+  if (threadIdx.x == 0) rscale[row] = m / 127.0f;
+  const bool denormal = m > 0.f && __float_as_uint(m) < 0x00800000u;
+  const float recip = (m > 0.f && !denormal) ? __fdiv_rn(1.0f, m) : 0.f;
+  const double inv_d = denormal ? 127.0 / (double)m : 0.0;
+  for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
+    const float v = value(c);
+    int code = 0;
+    if (m > 0.f && !(__float_as_uint(fabsf(v)) > 0x7F800000u)) {       // not NaN
+      if (denormal) {
+        float vc = v > m ? m : (v < -m ? -m : v);
+        double sc = rint((double)vc * inv_d);
+        code = (int)(sc > 127.0 ? 127.0 : (sc < -127.0 ? -127.0 : sc));
+      } else {
+        float sc = __fmul_rn(__fmul_rn(v, recip), 127.0f);
+        sc = sc > 127.0f ? 127.0f : (sc < -127.0f ? -127.0f : sc);
+        code = (int)rintf(sc);
+      }
+    }
+    codes[row * k + c] = (uint8_t)(code + 128);
+  }
+}
+
+int quantize_rows_i8_dev(cai_ctx* ctx, const float* x_dev, int64_t rows, int64_t cols, uint8_t* codes_biased_dev, float* scales_dev) {
+  if (rows < 1 || rows > 0x7fffffff) return cai_fail(ctx, CAI_ERR_INVALID, "quantize: %lld rows", (long long)rows);
+  quantize_i8rows_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x_dev, cols, codes_biased_dev, scales_dev, 0, 0, 0, 0.f, 0, 0, 0);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
 static inline int64_t interleave_src_row(int64_t t, int hd) {
   const int64_t h = t / hd, r = t % hd;
   return h * hd + ((r % 2 == 0) ? r / 2 : r / 2 + hd / 2);
@@ -130,8 +213,10 @@ int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows,
   if (quant && (col0 % CAI_QK || src_cols % CAI_QK)) return cai_fail(ctx, CAI_ERR_INVALID, "column slice must align to 32-element blocks");
   if (interleave_head_dim > 0 && (interleave_head_dim % 2 || src_rows % interleave_head_dim))
     return cai_fail(ctx, CAI_ERR_INVALID, "row interleave needs rows %% head_dim == 0 and an even head_dim");
+  const bool i8row = w->type == CAI_TYPE_I8ROW;
+  if (i8row && (col0 % 4)) return cai_fail(ctx, CAI_ERR_INVALID, "column slice of int8 rows must align to 4 codes");
   const size_t src_row_bytes = cai_type_row_bytes(w->type, src_cols);
-  const size_t col_off = cai_type_row_bytes(w->type, col0);
+  const size_t col_off = i8row ? (size_t)col0 : cai_type_row_bytes(w->type, col0);
   const size_t row_bytes = cai_type_row_bytes(w->type, w->k);
   const size_t chunk_cap = 32u << 20;
   CAI_TRY(cai_ensure_staging(ctx, chunk_cap));
@@ -143,9 +228,22 @@ int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows,
     for (int64_t t = 0; t < nr; ++t) {
       int64_t g = row0 + r + t;
       if (interleave_head_dim > 0) g = interleave_src_row(g, interleave_head_dim);
-      memcpy(pin + (size_t)t * row_bytes, (const char*)host + (size_t)g * src_row_bytes + col_off, row_bytes);
+      if (i8row) {      // the slice of the codes, then the scale that closes the source row
+        memcpy(pin + (size_t)t * row_bytes, (const char*)host + (size_t)g * src_row_bytes + col_off, (size_t)w->k);
+        memcpy(pin + (size_t)t * row_bytes + (size_t)w->k, (const char*)host + (size_t)g * src_row_bytes + (size_t)src_cols, 4);
+      } else {
+        memcpy(pin + (size_t)t * row_bytes, (const char*)host + (size_t)g * src_row_bytes + col_off, row_bytes);
+      }
     }
-    if (!quant) {
+    if (i8row) {
+      CAI_CUDA(ctx, cudaMemcpyAsync(ctx->staging_dev, pin, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, ctx->stream));
+      const int threads = 256;
+      int64_t want = (nr * (w->k / 4 + 1) + threads - 1) / threads;
+      const int blocks = (int)(want > 65535 ? 65535 : (want < 1 ? 1 : want));
+      repack_i8rows_kernel<<<blocks, threads, 0, ctx->stream>>>((const uint32_t*)ctx->staging_dev, nr, w->k,
+          (uint32_t*)((char*)w->codes + (size_t)r * w->row_code_bytes()), w->rscale + r);
+      CAI_LAUNCHED(ctx);
+    } else if (!quant) {
       CAI_CUDA(ctx, cudaMemcpyAsync((char*)w->codes + (size_t)r * row_bytes, pin, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, ctx->stream));
     } else {
       CAI_CUDA(ctx, cudaMemcpyAsync(ctx->staging_dev, pin, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -167,10 +265,54 @@ int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows,
   return CAI_OK;
 }
 
+int qweight_upload_quantize_i8(cai_ctx* ctx, QWeight* w, const float* host, int64_t src_rows, int64_t src_cols, int64_t row0, int64_t col0,
+                               int interleave_head_dim) {
+  if (!host || w->type != CAI_TYPE_I8ROW) return cai_fail(ctx, CAI_ERR_INVALID, "int8 quantizing upload: bad argument");
+  if (row0 < 0 || col0 < 0 || row0 + w->n > src_rows || col0 + w->k > src_cols) return cai_fail(ctx, CAI_ERR_INVALID, "slice outside the tensor");
+  if (col0 != 0 || w->k != src_cols)
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "a row's int8 scale covers the whole row: quantize before sharding columns");
+  const size_t row_bytes = (size_t)w->k * 4;
+  const size_t chunk_cap = 32u << 20;
+  CAI_TRY(cai_ensure_staging(ctx, chunk_cap));
+  const int64_t rows_per_chunk = (int64_t)(chunk_cap / row_bytes);
+  if (rows_per_chunk < 1) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "row of %zu bytes exceeds the staging buffer", row_bytes);
+  for (int64_t r = 0; r < w->n; r += rows_per_chunk) {
+    const int64_t nr = (w->n - r < rows_per_chunk) ? (w->n - r) : rows_per_chunk;
+    char* pin = (char*)ctx->staging_pinned;
+    for (int64_t t = 0; t < nr; ++t) {
+      int64_t g = row0 + r + t;
+      if (interleave_head_dim > 0) g = interleave_src_row(g, interleave_head_dim);
+      memcpy(pin + (size_t)t * row_bytes, (const char*)host + (size_t)g * (size_t)src_cols * 4, row_bytes);
+    }
+    CAI_CUDA(ctx, cudaMemcpyAsync(ctx->staging_dev, pin, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    CAI_TRY(quantize_rows_i8_dev(ctx, (const float*)ctx->staging_dev, nr, w->k, (uint8_t*)w->codes + (size_t)r * (size_t)w->k, w->rscale + r));
+    CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  }
+  w->present = true;
+  return CAI_OK;
+}
+
 int qweight_download_blocks(cai_ctx* ctx, const QWeight* w, void* out_host, size_t cap) {
   const size_t row_bytes = cai_type_row_bytes(w->type, w->k);
   if ((size_t)w->n * row_bytes > cap) return cai_fail(ctx, CAI_ERR_INVALID, "host buffer of %zu bytes is too small for %zu", cap, (size_t)w->n * row_bytes);
   const bool quant = (w->type == CAI_TYPE_Q8_0 || w->type == CAI_TYPE_Q4_0);
+  if (w->type == CAI_TYPE_I8ROW) {
+    const size_t chunk_cap = 32u << 20;
+    CAI_TRY(cai_ensure_staging(ctx, chunk_cap));
+    const int64_t rows_per_chunk = (int64_t)(chunk_cap / row_bytes);
+    if (rows_per_chunk < 1) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "row too large for staging");
+    for (int64_t r = 0; r < w->n; r += rows_per_chunk) {
+      const int64_t nr = (w->n - r < rows_per_chunk) ? (w->n - r) : rows_per_chunk;
+      int64_t want = (nr * (w->k / 4 + 1) + 255) / 256;
+      const int blocks = (int)(want > 65535 ? 65535 : (want < 1 ? 1 : want));
+      unpack_i8rows_kernel<<<blocks, 256, 0, ctx->stream>>>((uint32_t*)ctx->staging_dev, nr, w->k,
+          (const uint32_t*)((const char*)w->codes + (size_t)r * w->row_code_bytes()), w->rscale + r);
+      CAI_LAUNCHED(ctx);
+      CAI_CUDA(ctx, cudaMemcpyAsync((char*)out_host + (size_t)r * row_bytes, ctx->staging_dev, (size_t)nr * row_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+      CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return CAI_OK;
+  }
   if (!quant) {
     CAI_CUDA(ctx, cudaMemcpyAsync(out_host, w->codes, (size_t)w->n * row_bytes, cudaMemcpyDeviceToHost, ctx->stream));
     CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -205,7 +347,7 @@ int qweight_download_blocks(cai_ctx* ctx, const QWeight* w, void* out_host, size
 // __half2float is exact for every half, subnormals included.
 // ---------------------------------------------------------------------------
 __global__ void dequant_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
-                               int64_t n_elems, int64_t k, int64_t sstride, float* __restrict__ out) {
+                               int64_t n_elems, int64_t k, int64_t sstride, float* __restrict__ out, const float* __restrict__ rscale) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += (int64_t)gridDim.x * blockDim.x) {
     float v;
     if (type == CAI_TYPE_Q8_0) {
@@ -218,6 +360,8 @@ __global__ void dequant_kernel(int type, const void* __restrict__ codes, const _
       const int nib = (e < 16) ? (byte & 0x0F) : (byte >> 4);
       const float d = __half2float(scales[(i / k) * sstride + (i % k) / CAI_QK]);
       v = d * (float)(nib - 8);
+    } else if (type == CAI_TYPE_I8ROW) {
+      v = rscale[i / k] * (float)((int)((const uint8_t*)codes)[i] - 128);      // DequantizeInt8: code * row scale
     } else if (type == CAI_TYPE_F16) {
       v = __half2float(((const __half*)codes)[i]);
     } else {
@@ -232,7 +376,7 @@ int qweight_dequantize_to_dev(cai_ctx* ctx, const QWeight* w, float* out_dev) {
   const int threads = 256;
   int64_t want = (n_elems + threads - 1) / threads;
   const int blocks = (int)(want > 148 * 32 ? 148 * 32 : want);
-  dequant_kernel<<<blocks, threads, 0, ctx->stream>>>(w->type, w->codes, w->scales, n_elems, w->k, w->sstride, out_dev);
+  dequant_kernel<<<blocks, threads, 0, ctx->stream>>>(w->type, w->codes, w->scales, n_elems, w->k, w->sstride, out_dev, w->rscale);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -314,6 +458,13 @@ __global__ void synth_vec_kernel(float* __restrict__ v, int64_t n, uint64_t seed
 int qweight_init_synthetic(cai_ctx* ctx, QWeight* w, uint64_t seed, uint64_t tensor_id, float std,
                            int64_t global_row0, int64_t global_col0, int64_t global_cols) {
   if (w->k % CAI_QK) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "synthetic init needs a multiple of 32 columns");
+  if (w->type == CAI_TYPE_I8ROW) {
+    quantize_i8rows_kernel<<<(unsigned)w->n, 256, 0, ctx->stream>>>(nullptr, w->k, (uint8_t*)w->codes, w->rscale, 1, seed, tensor_id, std,
+                                                                   global_row0, global_col0, global_cols);
+    CAI_LAUNCHED(ctx);
+    w->present = true;
+    return CAI_OK;
+  }
   const int64_t nblk = w->n * (w->k / CAI_QK);
   const int threads = 256;
   int64_t want = (nblk * 32 + threads - 1) / threads;

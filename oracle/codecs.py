@@ -23,6 +23,7 @@ GGML_F32 = 0
 GGML_F16 = 1
 GGML_Q4_0 = 2
 GGML_Q8_0 = 8
+GGML_I8ROW = 124      # not a ggml id: int8 rows + one fp32 scale per row, host row = K codes then the scale
 
 
 def half_to_single(bits):
@@ -190,7 +191,66 @@ def quantize_q4_0(x):
     return out.reshape(-1)
 
 
+def quantize_int8_rows(w):
+    """float32 [rows, K] -> (int8 codes [rows, K], float32 scales [rows]): the reference's own weight format.
+
+    TNNetVolume.MaxAbsFinite + QuantizeInt8, scalar form (neural/neuralvolume.pas:12471-12562): maxabs over the
+    finite magnitudes of the row; scale = maxabs / 127; code = Round(v * (1 / maxabs) * 127), the two products in
+    that order in single precision, clamped to +-127 (which maps +-Inf), Pascal Round = half to even, NaN -> 0; a
+    denormal row maximum scales in double precision (127 / maxabs); an all-zero row keeps zero codes (scale 0).
+    """
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, k = w.shape
+    codes = np.zeros((rows, k), dtype=np.int8)
+    scales = np.zeros(rows, dtype=np.float32)
+    min_single = np.float32(1.1754943508222875e-38)
+    for r in range(rows):
+        v = w[r]
+        a = np.abs(v)
+        fin = np.isfinite(a)
+        m = np.float32(a[fin].max()) if fin.any() else np.float32(0)
+        scales[r] = m / np.float32(127.0)
+        if m <= 0:
+            continue
+        nan = np.isnan(v)
+        if m < min_single:
+            vc = np.clip(v.astype(np.float64), -float(m), float(m))
+            sc = np.rint(vc * (127.0 / float(m)))
+        else:
+            recip = np.float32(1.0) / m
+            with np.errstate(over="ignore", invalid="ignore"):
+                sc = ((v * recip).astype(np.float32) * np.float32(127.0)).astype(np.float32)
+            sc = np.rint(np.clip(sc, -127.0, 127.0))
+        sc = np.where(nan, 0.0, np.clip(sc, -127.0, 127.0))
+        codes[r] = sc.astype(np.int8)
+    return codes, scales
+
+
+def linear_int8_rows(codes, scales, x, bias=None):
+    """y[b, a] = (sum_i codes[a, i] * x[b, i]) * scales[a] (+ bias): the raw code reduction in fp32 with the row's scale
+    applied once after the sum, DotProductsTiledInt8 (neural/neuralvolume.pas:12693-12745). Accumulates in float64 and
+    rounds once, so it serves as the exact value both fp32 orders are compared against."""
+    acc = x.astype(np.float64) @ codes.astype(np.float64).T
+    y = acc * scales.astype(np.float64)[None, :]
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64)[None, :]
+    return y.astype(np.float32)
+
+
+def split_int8_rows(raw, rows, k):
+    """Host rows of the int8-row type ([K code bytes | fp32 scale] per row) -> (int8 codes [rows, K], fp32 scales [rows])."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)[:rows * (k + 4)].reshape(rows, k + 4)
+    return raw[:, :k].copy().view(np.int8), raw[:, k:].copy().view(np.float32).reshape(rows)
+
+
+def dequantize_int8_rows(codes, scales):
+    """DequantizeInt8: code * row scale (one fp32 multiply)."""
+    return (codes.astype(np.float32) * scales.astype(np.float32)[:, None]).astype(np.float32)
+
+
 def block_bytes_per_row(ggml_type, k):
+    if ggml_type == GGML_I8ROW:
+        return k + 4
     if ggml_type == GGML_Q8_0:
         return k // QK * Q8_0_BLOCK_BYTES
     if ggml_type == GGML_Q4_0:

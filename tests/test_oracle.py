@@ -217,3 +217,47 @@ def test_int8_kv_cache_row_format_and_drift():
         a, b = f32.step(int(t)), i8.step(int(t))
         worst = max(worst, float(np.max(np.abs(a - b))) / float(np.max(np.abs(a))))
     assert 0 < worst < 1e-1
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the reference's own int8 weight rows (TNNetVolume.QuantizeInt8, neural/neuralvolume.pas:12471-12562)
+# ---------------------------------------------------------------------------------------------------------------
+def test_int8_row_quantizer_round_trip_bound_and_edge_values():
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((64, 96)) * 0.05).astype(np.float32)
+    codes, scales = codecs.quantize_int8_rows(w)
+    back = codecs.dequantize_int8_rows(codes, scales)
+    # |dw| <= scale / 2 per row, the reference's own round-trip gate (tests/TestNeuralPretrained.pas:3668-3703)
+    assert np.all(np.abs(back - w) <= scales[:, None] * 0.5 * (1 + 1e-5) + 1e-12)
+    assert np.all(np.abs(codes.astype(np.int32)).max(axis=1) == 127)          # every row uses the full range
+    # NaN -> 0, infinities clamp, a zero row stays zero with scale 0, the maximum ignores non-finite values
+    edge = np.zeros((3, 32), dtype=np.float32)
+    edge[0, :4] = [np.nan, np.inf, -np.inf, 2.0]
+    edge[0, 4] = -1.0
+    edge[2, 0] = np.float32(1e-40)                                         # denormal row maximum: scaled in double
+    edge[2, 1] = np.float32(-5e-41)
+    codes, scales = codecs.quantize_int8_rows(edge)
+    assert codes[0, :5].tolist() == [0, 127, -127, 127, -64] and scales[0] == np.float32(2.0) / np.float32(127.0)
+    assert not codes[1].any() and scales[1] == 0
+    assert codes[2, 0] == 127 and codes[2, 1] == -64 and scales[2] > 0       # -63.5 rounds to the even neighbour
+    # round half to even on exact half-way points: v = maxabs * (k + 0.5) / 127 for small k
+    row = np.zeros((1, 32), dtype=np.float32)
+    row[0, 0] = 127.0
+    row[0, 1:5] = [0.5, 1.5, 2.5, -3.5]
+    codes, _ = codecs.quantize_int8_rows(row)
+    got = codes[0, 1:5].tolist()
+    want = [int(np.rint(np.float32(np.float32(v * np.float32(1.0 / 127.0)) * np.float32(127.0)))) for v in (0.5, 1.5, 2.5, -3.5)]
+    assert got == want
+
+
+def test_int8_row_linear_applies_the_scale_after_the_raw_code_sum():
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal((8, 64)) * 0.1).astype(np.float32)
+    x = rng.standard_normal((2, 64)).astype(np.float32)
+    codes, scales = codecs.quantize_int8_rows(w)
+    y = codecs.linear_int8_rows(codes, scales, x)
+    ref = x.astype(np.float64) @ codecs.dequantize_int8_rows(codes, scales).astype(np.float64).T
+    assert np.max(np.abs(y - ref)) < 1e-5
+    raw = np.concatenate([codes.view(np.uint8), scales.view(np.uint8).reshape(8, 4)], axis=1).reshape(-1)
+    c2, s2 = codecs.split_int8_rows(raw, 8, 64)
+    assert np.array_equal(c2, codes) and np.array_equal(s2, scales)
