@@ -273,6 +273,11 @@ int cai_session_destroy(cai_session* s);
 int cai_session_reset(cai_session* s, int seq /* -1 = all */);
 int cai_session_truncate(cai_session* s, int seq, int committed_len);
 int cai_session_cache_len(cai_session* s, int seq, int* out_len);
+/* Benchmark aid, no reference counterpart: zeroes the KV caches and declares n_rows positions cached in every sequence,
+ * so that decode steps can be timed at a long context without paying for its prefill (64 sequences x 8192 positions of
+ * a 32B model are half a million prefill tokens). The rows are zeros, not the model's: logits of such a session mean
+ * nothing, its timing is that of any session with n_rows cached rows. */
+int cai_session_fill_for_benchmark(cai_session* s, int n_rows);
 /* One width-1 forward per sequence. tokens_host[batch]; abs_pos_host[batch] may be
  * NULL (= cache length, the position StepForward writes into every RoPE layer).
  * logits_out_host (batch*vocab floats) and argmax_out_host (batch ints, first

@@ -91,6 +91,7 @@ SIGNATURES = {
     "cai_session_reset": [_P, _I],
     "cai_session_truncate": [_P, _I, _I],
     "cai_session_cache_len": [_P, _I, C.POINTER(_I)],
+    "cai_session_fill_for_benchmark": [_P, _I],
     "cai_session_step": [_P, _P, _P, _P, _P],
     "cai_session_decode_greedy": [_P, _P, _I, _P],
     "cai_session_prefill": [_P, _P, _I],

@@ -422,6 +422,10 @@ class StreamingDecoder:
         self.backend._check(self.backend.lib.cai_session_cache_len(self.handle, seq, C.byref(n)))
         return n.value
 
+    def fill_for_benchmark(self, n_rows):
+        """Zeroes the caches and declares n_rows cached positions per sequence (timing aid; the rows are not the model's)."""
+        self.backend._check(self.backend.lib.cai_session_fill_for_benchmark(self.handle, int(n_rows)))
+
     def step_forward(self, tokens, abs_pos=None, want_logits=True):
         """One width-1 forward per sequence; returns (logits [batch, vocab] or None, argmax [batch])."""
         tok = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))

@@ -67,12 +67,7 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
     delete ctx;
     return CAI_ERR_CUDA;
   }
-  ctx->gemv_scratch_ctas = 2 * ctx->sm_count;
-  ctx->gemv_ticket_cap = 65536;
-  if (cudaMalloc((void**)&ctx->gemv_scratch, (size_t)ctx->gemv_scratch_ctas * 2 * 32 * 4 * sizeof(float)) != cudaSuccess ||
-      cudaMalloc((void**)&ctx->gemv_tickets, (size_t)ctx->gemv_ticket_cap * sizeof(int)) != cudaSuccess ||
-      cudaMemset(ctx->gemv_tickets, 0, (size_t)ctx->gemv_ticket_cap * sizeof(int)) != cudaSuccess ||
-      cudaHostAlloc((void**)&ctx->err_flag, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+  if (cudaHostAlloc((void**)&ctx->err_flag, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
     cudaGetLastError();
     cai_cuda_shutdown(ctx);
     return CAI_ERR_CUDA;
@@ -105,8 +100,6 @@ int cai_cuda_shutdown(cai_ctx* ctx) {
   free(ctx->prof_events);
   free(ctx->prof_family);
   if (ctx->l2_flush_buf) cudaFree(ctx->l2_flush_buf);
-  if (ctx->gemv_scratch) cudaFree(ctx->gemv_scratch);
-  if (ctx->gemv_tickets) cudaFree(ctx->gemv_tickets);
   if (ctx->tc_xp) cudaFree(ctx->tc_xp);
   for (int i = 0; i < ctx->tc_xp_n_retired; ++i) cudaFree(ctx->tc_xp_retired[i]);
   if (ctx->err_flag) cudaFreeHost(ctx->err_flag);
@@ -437,6 +430,8 @@ struct cai_sdpa {
   float* partial = nullptr;
   int nsplit = 1;
   int len = 0;
+  int ctx_pitch = 0;             // positions per KV head in the caches (max_ctx rounded up to 32)
+  int k_blocked = 0;             // K cache block-transposed (the caches are private to the object)
 };
 
 extern "C" {
@@ -450,7 +445,9 @@ int cai_sdpa_create(cai_ctx* ctx, int q_heads, int kv_heads, int head_dim, int m
   cai_sdpa* s = new (std::nothrow) cai_sdpa();
   if (!s) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
   s->ctx = ctx; s->q_heads = q_heads; s->kv_heads = kv_heads; s->head_dim = head_dim; s->max_ctx = max_ctx;
-  const size_t cache = (size_t)kv_heads * max_ctx * head_dim * 4;
+  s->ctx_pitch = (max_ctx + 31) & ~31;
+  s->k_blocked = attn_k_blocked_supported(q_heads, kv_heads, head_dim) ? 1 : 0;
+  const size_t cache = (size_t)kv_heads * s->ctx_pitch * head_dim * 4;
   s->nsplit = attn_nsplit(ctx, 1, kv_heads, max_ctx);
   const size_t rowf = (size_t)(q_heads + 2 * kv_heads) * head_dim;
   bool ok = cudaMalloc((void**)&s->k_cache, cache) == cudaSuccess && cudaMalloc((void**)&s->v_cache, cache) == cudaSuccess &&
@@ -505,7 +502,7 @@ int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev) {
   CAI_CUDA(ctx, cudaMemcpyAsync(s->row_dev, qkv_row_dev, rowf * 4, cudaMemcpyDeviceToDevice, ctx->stream));
   AttnArgs a;
   a.qkv = s->row_dev; a.ld = (int64_t)rowf; a.k_cache = s->k_cache; a.v_cache = s->v_cache; a.cache_len_dev = s->len_dev;
-  a.batch = 1; a.q_heads = s->q_heads; a.kv_heads = s->kv_heads; a.head_dim = s->head_dim; a.max_ctx = s->max_ctx;
+  a.batch = 1; a.q_heads = s->q_heads; a.kv_heads = s->kv_heads; a.head_dim = s->head_dim; a.max_ctx = s->ctx_pitch; a.k_blocked = s->k_blocked;
   a.out = out_dev; a.ldo = (int64_t)s->q_heads * s->head_dim; a.partial = s->partial; a.nsplit = s->nsplit;
   CAI_TRY(attn_rope_append(ctx, a));
   CAI_TRY(attn_decode(ctx, a));

@@ -30,11 +30,6 @@ struct cai_ctx {
   size_t staging_bytes;
   void* staging_pinned;      // upload staging (pinned host)
   cai_comm_state* comm;      // NULL until cai_comm_init
-  // stream-K GEMV: partial sums of row groups shared by several CTAs, arrival tickets, error word
-  float* gemv_scratch;
-  int* gemv_tickets;
-  int gemv_ticket_cap;
-  int gemv_scratch_ctas;
   int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out (1), that refused a
                              // cache length outside the cache (2) or that met an unusable router row (3)
   unsigned wait_limit_us;    // how long a device-side wait on another CTA or GPU may last before it gives up

@@ -460,7 +460,6 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
   gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
 }
 
-int gemv_tma_launch(cai_ctx* ctx, GemvParams p, int type, int nb);   // gemv_tma.cu
 int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type);      // gemm_tc.cu
 
 int env_int(const char* name, int dflt) {
@@ -476,17 +475,19 @@ static cudaError_t launch_one_b(cai_ctx* ctx, const GemvParams& p, dim3 grid, in
     if (e != cudaSuccess) return e;
   }
   // persistent grid: exactly the CTAs that can be resident at once (a host-side query, cached per
-  // instantiation and shared-memory size), each walking several row blocks with the activations staged once
+  // instantiation, device and shared-memory size), each walking several row blocks with the activations staged once
   static int cached_blocks = 0;
   static size_t cached_smem = (size_t)-1;
   static int cached_threads = 0;
-  if (cached_smem != smem || cached_threads != threads) {
+  static int cached_device = -1;
+  if (cached_smem != smem || cached_threads != threads || cached_device != ctx->device) {
     int nblk = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, gemv_quant_kernel<TYPE, NB, RPW, MINB, RING>, threads, smem);
     if (e != cudaSuccess) return e;
     cached_blocks = nblk < 1 ? 1 : nblk;
     cached_smem = smem;
     cached_threads = threads;
+    cached_device = ctx->device;
   }
   const int64_t resident = (int64_t)ctx->sm_count * cached_blocks;
   int64_t gx = grid.x;
@@ -508,7 +509,9 @@ static cudaError_t launch_one(cai_ctx* ctx, const GemvParams& p, dim3 grid, int 
 }
 template <int TYPE, int NB>
 static cudaError_t launch_quant(cai_ctx* ctx, const GemvParams& p, int rpw, dim3 grid, int threads, size_t smem) {
-  if (rpw == 4) return launch_one<TYPE, NB, 4>(ctx, p, grid, threads, smem);
+  if constexpr (NB <= 2) {                       // wider batch tiles never take 4 rows per warp (the dispatcher caps them at 2)
+    if (rpw == 4) return launch_one<TYPE, NB, 4>(ctx, p, grid, threads, smem);
+  }
   if (rpw == 2) return launch_one<TYPE, NB, 2>(ctx, p, grid, threads, smem);
   return launch_one<TYPE, NB, 1>(ctx, p, grid, threads, smem);
 }
@@ -576,13 +579,6 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     return CAI_OK;
   }
   if ((a.ldx % 4) || ((uintptr_t)a.x % 16)) return cai_fail(ctx, CAI_ERR_INVALID, "linear: activations must be 16-byte aligned with ldx %% 4 == 0");
-  // stream-K kernel with bulk-copy (TMA) staging, opt-in with CAI_GEMV_PATH=2: on B200 it measured
-  // 3.0 TB/s against 4.0 TB/s for the register-staged kernel below on the 5120 x 55296 Q8_0 matrix
-  // (its per-row bulk copies are small; both kernels are bound by the integer pipe that unpacks codes).
-  if (!indexed && a.batch <= 4 && !a.norm_gain && a.epilogue != EPI_QKV_ROPE && env_int("CAI_GEMV_PATH", 0) == 2) {
-    const int st = gemv_tma_launch(ctx, p, w->type, a.batch >= 3 ? 4 : a.batch);
-    if (st != CAI_ERR_UNSUPPORTED) return st;
-  }
   // batches of 9..64 rows are a real contraction: tensor cores (tcgen05), unless the call needs a fused
   // epilogue only the CUDA-core kernel has, or CAI_GEMM_TC=0. Batches of 3..8 rows go there too when the matrix
   // is large (measured on 5120 x 27648 Q8_0: 78 us on the tensor cores for up to 16 rows, against 180 us at 4 rows
@@ -623,7 +619,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   ksplit = env_int("CAI_GEMV_KSPLIT", ksplit);
   if (rpw != 1 && rpw != 2 && rpw != 4) rpw = 2;
   if ((a.epilogue == EPI_SWIGLU || a.epilogue == EPI_QKV_ROPE) && rpw == 1) rpw = 2;
-  if (nb == 8 && rpw == 4) rpw = 2;
+  if (nb >= 4 && rpw == 4) rpw = 2;
   if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) ksplit = 1;
   p.ksplit = ksplit;
   const int units_per_group = (a.epilogue == EPI_SWIGLU) ? rpw / 2 : rpw;

@@ -1138,6 +1138,29 @@ int cai_session_truncate(cai_session* s, int seq, int committed_len) {
   return push_len(s);
 }
 
+int cai_session_fill_for_benchmark(cai_session* s, int n_rows) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (s->kv_owner) return cai_fail(ctx, CAI_ERR_STATE, "cai_session_fill_for_benchmark: not on a prefill helper");
+  if (n_rows < 0 || n_rows > s->max_ctx) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_fill_for_benchmark: %d rows of %d", n_rows, s->max_ctx);
+  CAI_CUDA(ctx, cudaMemsetAsync(s->k_cache, 0, s->cache_bytes(), ctx->stream));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->v_cache, 0, s->cache_bytes(), ctx->stream));
+  if (s->kv_int8) {
+    // scale 1 with zero codes: the row format's own encoding of an all-zero row
+    std::vector<float> ones(1 << 20, 1.0f);
+    const size_t total = s->scale_stride * (size_t)s->m->cfg.layers;
+    for (size_t at = 0; at < total; at += ones.size()) {
+      const size_t nn = total - at < ones.size() ? total - at : ones.size();
+      CAI_CUDA(ctx, cudaMemcpyAsync(s->k_scales + at, ones.data(), nn * 4, cudaMemcpyHostToDevice, ctx->stream));
+      CAI_CUDA(ctx, cudaMemcpyAsync(s->v_scales + at, ones.data(), nn * 4, cudaMemcpyHostToDevice, ctx->stream));
+      CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+  }
+  for (auto& l : s->len_host) l = n_rows;
+  return push_len(s);
+}
+
 int cai_session_cache_len(cai_session* s, int seq, int* out_len) {
   if (!s || !out_len) return CAI_ERR_INVALID;
   if (seq < 0 || seq >= s->batch) return cai_fail(s->ctx, CAI_ERR_INVALID, "sequence %d of %d", seq, s->batch);

@@ -118,7 +118,9 @@ def pack_kats(out_dir):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+    ref = sys.argv[1]
     fix = os.path.join(ref, "tests", "fixtures")
     out_dir = os.path.dirname(os.path.abspath(__file__))
     for name in ("tiny_llama", "tiny_qwen2", "tiny_olmoe", "tiny_mixtral"):
