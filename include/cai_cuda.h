@@ -175,6 +175,9 @@ int cai_sdpa_destroy(cai_sdpa* s);
 int cai_sdpa_reset(cai_sdpa* s);
 int cai_sdpa_truncate(cai_sdpa* s, int committed_len);
 int cai_sdpa_cache_len(cai_sdpa* s, int* out_len);
+/* The layer's Window and EnableEviction (see cai_session_set_window / cai_session_enable_eviction). */
+int cai_sdpa_set_window(cai_sdpa* s, int window);
+int cai_sdpa_enable_eviction(cai_sdpa* s, int sink_tokens, int recent_window);
 /* Appends the row's K,V at slot CacheLength, then attends the row's Q over the
  * whole cache. out_dev: q_heads*head_dim floats. */
 int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev);
@@ -273,6 +276,17 @@ int cai_session_destroy(cai_session* s);
 int cai_session_reset(cai_session* s, int seq /* -1 = all */);
 int cai_session_truncate(cai_session* s, int seq, int committed_len);
 int cai_session_cache_len(cai_session* s, int seq, int* out_len);
+/* TNNetStreamingDecoder.EnableEviction / DisableEviction (neural/neuraldecode.pas:1257-1276, 5722-5727): StreamingLLM.
+ * Every layer keeps the first sink_tokens rows and the most recent recent_window rows; a stream then runs forever in
+ * a cache of sink_tokens + recent_window rows (<= max_ctx). Keys keep the rotation of their original position and the
+ * query its true absolute position, so surviving pairs attend at their exact distance. While a sequence is no longer
+ * than sink_tokens + recent_window the output is that of the unbounded session. (0, 0) turns it off. Here the rows
+ * live as sinks + a ring instead of being shifted down one by one; the set of live rows is the reference's.
+ * cai_session_cache_len keeps counting positions; the rows held are min(len, sink_tokens + recent_window). */
+int cai_session_enable_eviction(cai_session* s, int sink_tokens, int recent_window);
+/* Sliding-window attention on every layer: a step attends over the most recent `window` cached rows only (the new row
+ * included), TNNetFusedSDPA's Window (jStart, neural/neural.cl:2437-2438). 0 = the whole cache. */
+int cai_session_set_window(cai_session* s, int window);
 /* Benchmark aid, no reference counterpart: zeroes the KV caches and declares n_rows positions cached in every sequence,
  * so that decode steps can be timed at a long context without paying for its prefill (64 sequences x 8192 positions of
  * a 32B model are half a million prefill tokens). The rows are zeros, not the model's: logits of such a session mean
@@ -291,6 +305,30 @@ int cai_session_step(cai_session* s, const int32_t* tokens_host, const int32_t* 
  * No host round trip between steps. */
 int cai_session_decode_greedy(cai_session* s, const int32_t* tokens_host, int n_steps,
                               int32_t* out_tokens_host);
+/* Sampling without shipping the logits row to the host (the reference's samplers sort 152k scores per token on the
+ * CPU, docs/OPTIMIZATION-GUIDE.md:1914-1919).
+ * cai_session_step_topk: one step, then the candidate window the reference's samplers work on: the k (<= 64) largest
+ * scores of softmax(logits / temperature) over the whole vocabulary, descending, ties to the lower id, as ids and
+ * probabilities per sequence (TNNetSamplerBase.SelectTopCandidates, neural/neuralvolume.pas:991-1030, with
+ * TNNetTemperatureProcessor applied first). The host's own sampler and random generator then pick: 8 k bytes per
+ * sequence come back instead of 4 * vocab.
+ * cai_session_decode_sampled: the whole loop on the device. Per step and sequence the draw of
+ * TNNetSamplerWeightedTopK.SampleFromSorted (:4749-4785) over that window, optionally cut to the nucleus first (the
+ * shortest prefix whose probabilities sum above top_p; top_p <= 0 or >= 1 keeps the window): Roll = u * KeptSum, the
+ * first candidate whose running sum exceeds Roll. u comes from uniforms_host[step * batch + seq] when given, else from
+ * a counter-based generator keyed by (seed, step counted from 1, sequence) that cai_sampling_uniform reproduces.
+ * out_tokens_host[n_steps * batch] nullable. Single-GPU sessions (the vocabulary must not be sharded). */
+typedef struct cai_sampling {
+  float temperature;   /* > 0; 1 = off */
+  int32_t top_k;       /* 1..64 */
+  float top_p;         /* nucleus mass; <= 0 or >= 1 = off */
+  uint64_t seed;
+} cai_sampling;
+int cai_session_step_topk(cai_session* s, const int32_t* tokens_host, const int32_t* abs_pos_host, int k, float temperature,
+                          int32_t* ids_out_host, float* probs_out_host);
+int cai_session_decode_sampled(cai_session* s, const int32_t* tokens_host, int n_steps, const cai_sampling* opt,
+                               const float* uniforms_host /* nullable */, int32_t* out_tokens_host);
+int cai_sampling_uniform(uint64_t seed, uint64_t step, uint64_t seq, float* out_u);
 /* Feeds n_tokens per sequence (tokens_host[seq*n_tokens + i]) one position at a
  * time without reading anything back: the prefill loop of GenerateFromIds
  * (neural/neuralchatengine.pas:1466-1470). */

@@ -25,6 +25,10 @@ class CaiError(RuntimeError):
         self.message = message
 
 
+class SamplingC(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("seed", C.c_uint64)]
+
+
 class LlamaConfigC(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("inter", C.c_int32), ("layers", C.c_int32), ("heads", C.c_int32),
                 ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("vocab", C.c_int32),
@@ -75,6 +79,8 @@ SIGNATURES = {
     "cai_sdpa_reset": [_P],
     "cai_sdpa_truncate": [_P, _I],
     "cai_sdpa_cache_len": [_P, C.POINTER(_I)],
+    "cai_sdpa_set_window": [_P, _I],
+    "cai_sdpa_enable_eviction": [_P, _I, _I],
     "cai_sdpa_step_dev": [_P, _P, _P],
     "cai_sdpa_step_noalloc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "cai_model_create": [_P, C.POINTER(LlamaConfigC), _I, _I, _PP],
@@ -92,8 +98,13 @@ SIGNATURES = {
     "cai_session_truncate": [_P, _I, _I],
     "cai_session_cache_len": [_P, _I, C.POINTER(_I)],
     "cai_session_fill_for_benchmark": [_P, _I],
+    "cai_session_enable_eviction": [_P, _I, _I],
+    "cai_session_set_window": [_P, _I],
     "cai_session_step": [_P, _P, _P, _P, _P],
     "cai_session_decode_greedy": [_P, _P, _I, _P],
+    "cai_session_step_topk": [_P, _P, _P, _I, C.c_float, _P, _P],
+    "cai_session_decode_sampled": [_P, _P, _I, _P, _P, _P],
+    "cai_sampling_uniform": [C.c_uint64, C.c_uint64, C.c_uint64, C.POINTER(C.c_float)],
     "cai_session_prefill": [_P, _P, _I],
     "cai_session_profile": [_P, _P, _I, C.POINTER(C.c_float), C.POINTER(_I64)],
     "cai_session_snapshot": [_P],

@@ -19,7 +19,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import CaiError, LlamaConfigC, TYPE_F16, TYPE_F32, TYPE_I8, TYPE_I8ROW, TYPE_Q4_0, TYPE_Q8_0  # noqa: F401
+from ._lib import CaiError, LlamaConfigC, SamplingC, TYPE_F16, TYPE_F32, TYPE_I8, TYPE_I8ROW, TYPE_Q4_0, TYPE_Q8_0  # noqa: F401
 
 
 def _ptr(a):
@@ -322,6 +322,12 @@ class FusedSDPA:
         self.backend._check(self.backend.lib.cai_sdpa_cache_len(self.handle, C.byref(n)))
         return n.value
 
+    def set_window(self, window):
+        self.backend._check(self.backend.lib.cai_sdpa_set_window(self.handle, int(window)))
+
+    def enable_eviction(self, sink_tokens, recent_window):
+        self.backend._check(self.backend.lib.cai_sdpa_enable_eviction(self.handle, int(sink_tokens), int(recent_window)))
+
     def compute_cached_token(self, qkv_row):
         """Input row [allQ | allK | allV]; returns q_heads*head_dim outputs."""
         b = self.backend
@@ -422,6 +428,14 @@ class StreamingDecoder:
         self.backend._check(self.backend.lib.cai_session_cache_len(self.handle, seq, C.byref(n)))
         return n.value
 
+    def enable_eviction(self, sink_tokens, recent_window):
+        """StreamingLLM: keep the first sink_tokens rows and the most recent recent_window rows (0, 0 = off)."""
+        self.backend._check(self.backend.lib.cai_session_enable_eviction(self.handle, int(sink_tokens), int(recent_window)))
+
+    def set_window(self, window):
+        """Sliding-window attention: only the most recent `window` rows (0 = the whole cache)."""
+        self.backend._check(self.backend.lib.cai_session_set_window(self.handle, int(window)))
+
     def fill_for_benchmark(self, n_rows):
         """Zeroes the caches and declares n_rows cached positions per sequence (timing aid; the rows are not the model's)."""
         self.backend._check(self.backend.lib.cai_session_fill_for_benchmark(self.handle, int(n_rows)))
@@ -442,6 +456,26 @@ class StreamingDecoder:
         tok = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))
         out = np.empty((n_steps, self.batch), dtype=np.int32)
         self.backend._check(self.backend.lib.cai_session_decode_greedy(self.handle, _ptr(tok), n_steps, _ptr(out)))
+        return out
+
+    def step_topk(self, tokens, k, temperature=1.0, abs_pos=None):
+        """One step; returns the sampler's candidate window per sequence: (ids [batch, k], probabilities [batch, k])."""
+        tok = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))
+        pos = None if abs_pos is None else np.ascontiguousarray(np.asarray(abs_pos, dtype=np.int32).reshape(self.batch))
+        ids = np.empty((self.batch, k), dtype=np.int32)
+        probs = np.empty((self.batch, k), dtype=np.float32)
+        self.backend._check(self.backend.lib.cai_session_step_topk(self.handle, _ptr(tok), _ptr(pos) if pos is not None else None, k,
+                                                                  float(temperature), _ptr(ids), _ptr(probs)))
+        return ids, probs
+
+    def decode_sampled(self, tokens, n_steps, temperature=1.0, top_k=40, top_p=0.0, seed=0, uniforms=None):
+        """The sampled generation loop on the device; uniforms [n_steps, batch] optional (else the keyed generator)."""
+        tok = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))
+        opt = SamplingC(float(temperature), int(top_k), float(top_p), int(seed))
+        out = np.empty((n_steps, self.batch), dtype=np.int32)
+        u = None if uniforms is None else np.ascontiguousarray(np.asarray(uniforms, dtype=np.float32).reshape(n_steps, self.batch))
+        self.backend._check(self.backend.lib.cai_session_decode_sampled(self.handle, _ptr(tok), n_steps, C.byref(opt),
+                                                                       _ptr(u) if u is not None else None, _ptr(out)))
         return out
 
     def prefill(self, tokens):

@@ -432,6 +432,7 @@ struct cai_sdpa {
   int len = 0;
   int ctx_pitch = 0;             // positions per KV head in the caches (max_ctx rounded up to 32)
   int k_blocked = 0;             // K cache block-transposed (the caches are private to the object)
+  int window = 0, evict_sinks = 0, evict_window = 0;
 };
 
 extern "C" {
@@ -484,7 +485,25 @@ int cai_sdpa_reset(cai_sdpa* s) { return s ? sdpa_set_len(s, 0) : CAI_ERR_INVALI
 int cai_sdpa_truncate(cai_sdpa* s, int committed_len) {
   if (!s) return CAI_ERR_INVALID;
   if (committed_len < 0 || committed_len > s->len) return cai_fail(s->ctx, CAI_ERR_INVALID, "truncate to %d outside the committed prefix of %d", committed_len, s->len);
+  if (s->evict_window > 0 && s->len > s->evict_sinks + s->evict_window && committed_len != s->len)
+    return cai_fail(s->ctx, CAI_ERR_STATE, "truncate after eviction has dropped rows");
   return sdpa_set_len(s, committed_len);
+}
+int cai_sdpa_set_window(cai_sdpa* s, int window) {
+  if (!s) return CAI_ERR_INVALID;
+  if (window < 0) return cai_fail(s->ctx, CAI_ERR_INVALID, "window %d", window);
+  s->window = window;
+  return CAI_OK;
+}
+int cai_sdpa_enable_eviction(cai_sdpa* s, int sink_tokens, int recent_window) {
+  if (!s) return CAI_ERR_INVALID;
+  if (sink_tokens < 0 || recent_window < 0 || (recent_window == 0 && sink_tokens != 0) || sink_tokens + recent_window > s->max_ctx)
+    return cai_fail(s->ctx, CAI_ERR_INVALID, "eviction with %d sinks + %d recent rows in a cache of %d", sink_tokens, recent_window, s->max_ctx);
+  const int cap = recent_window > 0 ? sink_tokens + recent_window : s->max_ctx;
+  if (s->len > cap || (s->evict_window > 0 && s->len > s->evict_sinks + s->evict_window))
+    return cai_fail(s->ctx, CAI_ERR_STATE, "the policy can change only while the cache holds no more rows than it keeps");
+  s->evict_sinks = sink_tokens; s->evict_window = recent_window;
+  return CAI_OK;
 }
 int cai_sdpa_cache_len(cai_sdpa* s, int* out_len) {
   if (!s || !out_len) return CAI_ERR_INVALID;
@@ -497,12 +516,13 @@ int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev) {
   cai_ctx* ctx = s->ctx;
   CAI_TRY(cai_bind(ctx));
   if (!qkv_row_dev || !out_dev) return cai_fail(ctx, CAI_ERR_INVALID, "cai_sdpa_step_dev: null buffer");
-  if (s->len >= s->max_ctx) return cai_fail(ctx, CAI_ERR_STATE, "attention cache is full (%d rows)", s->max_ctx);
+  if (s->len >= s->max_ctx && s->evict_window == 0) return cai_fail(ctx, CAI_ERR_STATE, "attention cache is full (%d rows)", s->max_ctx);
   const size_t rowf = (size_t)(s->q_heads + 2 * s->kv_heads) * s->head_dim;
   CAI_CUDA(ctx, cudaMemcpyAsync(s->row_dev, qkv_row_dev, rowf * 4, cudaMemcpyDeviceToDevice, ctx->stream));
   AttnArgs a;
   a.qkv = s->row_dev; a.ld = (int64_t)rowf; a.k_cache = s->k_cache; a.v_cache = s->v_cache; a.cache_len_dev = s->len_dev;
   a.batch = 1; a.q_heads = s->q_heads; a.kv_heads = s->kv_heads; a.head_dim = s->head_dim; a.max_ctx = s->ctx_pitch; a.k_blocked = s->k_blocked;
+  a.window = s->window; a.evict_sinks = s->evict_sinks; a.evict_window = s->evict_window;
   a.out = out_dev; a.ldo = (int64_t)s->q_heads * s->head_dim; a.partial = s->partial; a.nsplit = s->nsplit;
   CAI_TRY(attn_rope_append(ctx, a));
   CAI_TRY(attn_decode(ctx, a));

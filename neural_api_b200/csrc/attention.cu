@@ -30,14 +30,31 @@ struct AttnParams {
   const int32_t* seq_index;                                               // cache sequence of each batch row (NULL = the row itself)
   int* err;               // device-visible error word: 2 = a cache length outside [0, max_ctx) was refused
   int k_blocked;          // K cache block-transposed (cai_k_blocked_index)
+  // which cached rows a step sees (TNNetFusedSDPA's Window and EnableEviction):
+  int window;             // > 0: only the most recent `window` rows (sliding-window layers, jStart of neural/neural.cl:2437-2438)
+  int evict_sinks, evict_window;   // evict_window > 0: StreamingLLM, the first `sinks` rows and the most recent `window` rows live
 };
 
 // The number of cached rows comes from a device word the host cannot always vouch for (the allocation-free entry
 // point's caller owns it). A length outside [0, max_ctx) would put the appended row, and the rows the decode
 // kernels walk, outside the cache: refuse it (no access at all), raise the error word, and let every kernel of the
 // step leave in the same way.
+// Where the row of a step that finds `len` rows before it goes. Eviction keeps the rows physically as the first `sinks`
+// slots plus a ring of `window` slots: the row of position len >= sinks + window overwrites the oldest non-sink row.
+// (The reference shifts the surviving rows down by one instead, neural/neuraldecode.pas:1257-1310; the set of live rows
+// is the same, and keys keep their original rotation either way.)
+__device__ __forceinline__ int attn_slot(const AttnParams& p, int len) {
+  const int cap = p.evict_sinks + p.evict_window;
+  return (p.evict_window > 0 && len >= cap) ? p.evict_sinks + (len - p.evict_sinks) % p.evict_window : len;
+}
+// The cached rows [base, n) a step attends over, the new row included.
+__device__ __forceinline__ void attn_range(const AttnParams& p, int len, int& base, int& n) {
+  n = len + 1; base = 0;
+  if (p.evict_window > 0) { const int cap = p.evict_sinks + p.evict_window; if (n > cap) n = cap; }
+  else if (p.window > 0 && n > p.window) base = n - p.window;
+}
 __device__ __forceinline__ bool attn_len_ok(const AttnParams& p, int len) {
-  if (len >= 0 && len < p.max_ctx) return true;
+  if (len >= 0 && (len < p.max_ctx || p.evict_window > 0)) return true;
   if (threadIdx.x == 0 && p.err) *p.err = 2;
   return false;
 }
@@ -59,8 +76,8 @@ __global__ void rope_append_kernel(const AttnParams p) {
   const int hd = p.head_dim;
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
   float* row = p.qkv + (int64_t)b * p.ld;
-  const int slot = p.cache_len[b];
-  if (!attn_len_ok(p, slot)) return;
+  if (!attn_len_ok(p, p.cache_len[b])) return;
+  const int slot = attn_slot(p, p.cache_len[b]);
   float inv_q = 1.f, inv_k = 1.f;
   if (p.q_norm) {
     float ss = 0.f;
@@ -72,7 +89,7 @@ __global__ void rope_append_kernel(const AttnParams p) {
     ss = block_sum(ss, red);
     inv_k = 1.0f / sqrtf(ss / (float)kw + p.eps);
   }
-  const int pos = p.pos ? p.pos[b] : slot;
+  const int pos = p.pos ? p.pos[b] : p.cache_len[b];
   const int half_hd = hd >> 1;
   // Q pairs, in place
   for (int pr = threadIdx.x; pr < (qw >> 1); pr += blockDim.x) {
@@ -125,8 +142,8 @@ __global__ void rope_append_int8_kernel(const AttnParams p) {
   const int hd = p.head_dim;
   const int qw = p.q_heads * hd, kw = p.kv_heads * hd;
   float* row = p.qkv + (int64_t)b * p.ld;
-  const int slot = p.cache_len[b];
-  if (!attn_len_ok(p, slot)) return;
+  if (!attn_len_ok(p, p.cache_len[b])) return;
+  const int slot = attn_slot(p, p.cache_len[b]);
   float inv_q = 1.f, inv_k = 1.f;
   if (p.q_norm) {
     float ss = 0.f;
@@ -138,7 +155,7 @@ __global__ void rope_append_int8_kernel(const AttnParams p) {
     ss = block_sum(ss, red);
     inv_k = 1.0f / sqrtf(ss / (float)kw + p.eps);
   }
-  const int pos = p.pos ? p.pos[b] : slot;
+  const int pos = p.pos ? p.pos[b] : p.cache_len[b];
   const int half_hd = hd >> 1;
   for (int pr = threadIdx.x; pr < (qw >> 1); pr += blockDim.x) {
     float x0 = row[2 * pr], x1 = row[2 * pr + 1];
@@ -179,12 +196,17 @@ __global__ void rope_append_int8_kernel(const AttnParams p) {
     const float recip = usable ? (1.0f / m) : 0.0f;
     const int64_t rowi = ((int64_t)bs * p.kv_heads + g) * p.max_ctx + slot;
     int8_t* codes = (part == 0 ? p.k_codes : p.v_codes) + rowi * hd;
+    // block-transposed K codes: the row's codes go to their places inside the position's 32-row block
+    int8_t* khead = p.k_codes + ((int64_t)bs * p.kv_heads + g) * p.max_ctx * hd;
+    const bool blocked = (part == 0) && p.k_blocked;
     if (lane == 0) (part == 0 ? p.k_scales : p.v_scales)[rowi] = row_scale;
     for (int d = lane; d < hd; d += 32) {
       const float v = src[d];
       float scaled = v * recip * 127.0f;
       if (__float_as_uint(fabsf(v)) > 0x7F800000u) scaled = 0.f;          // NaN
-      codes[d] = (int8_t)fminf(fmaxf(rintf(scaled), -127.0f), 127.0f);
+      const int8_t code = (int8_t)fminf(fmaxf(rintf(scaled), -127.0f), 127.0f);
+      if (blocked) khead[cai_k_blocked_index_i8(slot, d, hd)] = code;
+      else codes[d] = code;
     }
   }
 }
@@ -219,11 +241,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attn_decode_kernel(const Attn
   const bool vec = (nd == 8) && ((hd & 3) == 0);
 
   if (!attn_len_ok(p, p.cache_len[b])) return;
-  const int n = p.cache_len[b] + 1;                  // keys after the append
-  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
-  const int used = (n + chunk - 1) / chunk;
+  int base, n;                                         // the step attends over rows [base, n)
+  attn_range(p, p.cache_len[b], base, n);
+  const int chunk = attn_chunk(n - base, p.nsplit, p.min_chunk);
+  const int used = (n - base + chunk - 1) / chunk;
   if (split >= used) return;
-  const int j_begin = split * chunk;
+  const int j_begin = base + split * chunk;
   int j_end = j_begin + chunk; if (j_end > n) j_end = n;
 
   float* q_s = smem;                                  // [G][hd]
@@ -396,11 +419,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_kernel(co
   const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (!attn_len_ok(p, p.cache_len[b])) return;
-  const int n = p.cache_len[b] + 1;                    // rows after the append
-  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
-  const int used = (n + chunk - 1) / chunk;
+  int base, n;                                         // the step attends over rows [base, n)
+  attn_range(p, p.cache_len[b], base, n);
+  const int chunk = attn_chunk(n - base, p.nsplit, p.min_chunk);
+  const int used = (n - base + chunk - 1) / chunk;
   if (split >= used) return;
-  const int j_begin = split * chunk;
+  const int j_begin = base + split * chunk;
   int j_end = j_begin + chunk; if (j_end > n) j_end = n;
 
   // All multiply-adds are packed pairs (fma.rn.f32x2: two IEEE fp32 FMAs per instruction), which halves the
@@ -570,11 +594,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
   const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (!attn_len_ok(p, p.cache_len[b])) return;
-  const int n = p.cache_len[b] + 1;
-  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
-  const int used = (n + chunk - 1) / chunk;
+  int base, n;                                         // the step attends over rows [base, n)
+  attn_range(p, p.cache_len[b], base, n);
+  const int chunk = attn_chunk(n - base, p.nsplit, p.min_chunk);
+  const int used = (n - base + chunk - 1) / chunk;
   if (split >= used) return;
-  const int j_begin = split * chunk;
+  const int j_begin = base + split * chunk;
   int j_end = j_begin + chunk; if (j_end > n) j_end = n;
 
   float* q_s = smem;                                   // [G][HD]
@@ -603,7 +628,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
     const int j = tile + lane;
     const bool valid = j < j_end;
     const int jr = valid ? j : j_end - 1;              // rows past the end re-read the last row and are masked
-    const uint4* krow = (const uint4*)(kbase + (int64_t)jr * HD);
+    // row layout: the lane's own row; block-transposed: piece i of the block's 32 rows is 512 contiguous bytes
+    const uint4* krow = p.k_blocked ? (const uint4*)(kbase + (int64_t)(jr >> 5) * 32 * HD) + (jr & 31) : (const uint4*)(kbase + (int64_t)jr * HD);
+    const int kstep = p.k_blocked ? 32 : 1;
     const float kscale = ksc[jr] * p.inv_sqrt_d;
     const float vscale = vsc[jr];
     float s[G];
@@ -611,7 +638,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
     for (int h = 0; h < G; ++h) s[h] = 0.f;
     uint4 kw[HD / 16];
 #pragma unroll
-    for (int i = 0; i < HD / 16; ++i) kw[i] = krow[i];   // the whole row of codes in flight
+    for (int i = 0; i < HD / 16; ++i) kw[i] = krow[i * kstep];   // the whole row of codes in flight
 #pragma unroll
     for (int i = 0; i < HD / 16; ++i) {
       const uint32_t w4[4] = {kw[i].x ^ 0x80808080u, kw[i].y ^ 0x80808080u, kw[i].z ^ 0x80808080u, kw[i].w ^ 0x80808080u};
@@ -743,9 +770,10 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   const int hd = p.head_dim;
   const float* src = p.partial + ((int64_t)b * p.q_heads + h) * (int64_t)p.nsplit * (hd + 2);
   if (!attn_len_ok(p, p.cache_len[b])) return;
-  const int n = p.cache_len[b] + 1;
-  const int chunk = attn_chunk(n, p.nsplit, p.min_chunk);
-  const int used = (n + chunk - 1) / chunk;
+  int base, n;                                         // the step attends over rows [base, n)
+  attn_range(p, p.cache_len[b], base, n);
+  const int chunk = attn_chunk(n - base, p.nsplit, p.min_chunk);
+  const int used = (n - base + chunk - 1) / chunk;
   if (used == 1) return;                              // the single split wrote the output itself
   float mx = -INFINITY;
   for (int s = 0; s < used; ++s) mx = fmaxf(mx, src[(size_t)s * (hd + 2)]);
@@ -789,6 +817,7 @@ static AttnParams to_params(cai_ctx* ctx, const AttnArgs& a) {
   p.k_codes = a.k_codes; p.v_codes = a.v_codes; p.k_scales = a.k_scales; p.v_scales = a.v_scales;
   p.seq_index = a.seq_index_dev;
   p.k_blocked = a.k_blocked;
+  p.window = a.window; p.evict_sinks = a.evict_sinks; p.evict_window = a.evict_window;
   return p;
 }
 

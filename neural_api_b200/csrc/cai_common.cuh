@@ -237,6 +237,9 @@ struct AttnArgs {
   // K cache layout: 0 = [pos][d] rows as the reference keeps them (neural/neural.cl:2343-2346), 1 = block-transposed
   // (cai_k_blocked_index; sessions use it, max_ctx must then be a multiple of 32 and head_dim of 4)
   int k_blocked = 0;
+  // rows a step sees: sliding window (> 0: the most recent `window` rows) or StreamingLLM eviction (evict_window > 0: the
+  // first evict_sinks rows + the most recent evict_window rows, kept as sinks + a ring)
+  int window = 0, evict_sinks = 0, evict_window = 0;
   // optional: row r of the batch belongs to sequence seq_index[r] of the cache (several rows may be consecutive
   // positions of ONE sequence: chunked prefill); NULL = row r is sequence r. cache_len_dev stays per row.
   const int32_t* seq_index_dev = nullptr;
@@ -247,6 +250,12 @@ bool attn_int8_supported(int q_heads, int kv_heads, int head_dim);
 bool attn_k_blocked_supported(int q_heads, int kv_heads, int head_dim);
 int attn_rope_append(cai_ctx* ctx, const AttnArgs& a);
 int attn_decode(cai_ctx* ctx, const AttnArgs& a);
+
+// sample.cu
+int sample_scratch_floats(int batch);
+int sample_launch(cai_ctx* ctx, const float* logits, int64_t ld, int batch, int vocab, int k, float temperature, float top_p,
+                  unsigned long long seed, const float* uniforms_dev, float* scratch, int32_t* ids_out_dev, float* probs_out_dev,
+                  int32_t* tokens_dev, int32_t* trace_dev, const int32_t* trace_count_dev, long long trace_cap, int32_t* drawn_out_dev);
 
 // comm.cu
 int comm_allreduce(cai_ctx* ctx, float* buf, int64_t count);
@@ -271,6 +280,10 @@ void comm_destroy(cai_ctx* ctx);
 // are one contiguous 4 KB run that an asynchronous copy can land in shared memory as it is. (The reference's row
 // layout [pos][d] makes the same access 32 separate 512-byte-strided pieces.) V keeps the row layout: it is walked
 // with "lane = channels".
+// The int8 cache's K codes, same idea with 16-byte pieces of 16 codes: byte offset of code d of position pos.
+__host__ __device__ __forceinline__ size_t cai_k_blocked_index_i8(int pos, int d, int head_dim) {
+  return ((size_t)(pos >> 5) * (size_t)(head_dim >> 4) + (size_t)(d >> 4)) * 512 + (size_t)(pos & 31) * 16 + (size_t)(d & 15);
+}
 __host__ __device__ __forceinline__ size_t cai_k_blocked_index(int pos, int d, int head_dim) {
   return ((size_t)(pos >> 5) * (size_t)(head_dim >> 2) + (size_t)(d >> 2)) * 128 + (size_t)(pos & 31) * 4 + (size_t)(d & 3);
 }

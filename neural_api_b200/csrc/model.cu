@@ -595,7 +595,9 @@ struct cai_session {
   cai_ctx* ctx;
   int max_ctx, batch;
   int ctx_pitch = 0;                                  // positions per KV head in the caches: max_ctx rounded up to 32
-  int k_blocked = 0;                                  // fp32 K cache block-transposed (cai_k_blocked_index)
+  int k_blocked = 0;                                  // K cache block-transposed (cai_k_blocked_index)
+  int window = 0;                                     // > 0: every layer attends over the most recent `window` rows only
+  int evict_sinks = 0, evict_window = 0;              // evict_window > 0: StreamingLLM (sinks + a ring of recent rows)
   float *k_cache = nullptr, *v_cache = nullptr;       // [layers][B][kv_heads_l][ctx_pitch][hd]; int8 codes when kv_int8
   float *k_snap = nullptr, *v_snap = nullptr;
   size_t layer_stride = 0;                            // elements per layer
@@ -645,6 +647,8 @@ struct cai_session {
   // one persistent kernel per step (dense, one sequence, Q8_0, fp32 cache); NULL = one launch per operator
   StepPlan* plan = nullptr;
   unsigned long long* plan_ts = nullptr;              // device buffer of the phase trace (cai_session_profile)
+  // device sampling (cai_session_step_topk / cai_session_decode_sampled): allocated on first use
+  float* sample_scratch = nullptr; int32_t* sample_ids = nullptr; float* sample_probs = nullptr; float* sample_u = nullptr;
 };
 
 __global__ void pack_argmax_kernel(const int32_t* idx, const float* val, int batch, int offset, float* pack) {
@@ -706,7 +710,7 @@ static int enqueue_step(cai_session* s) {
   const bool tc_batch = linear_uses_tensor_cores(&m->layers[0].wgu, B) || linear_uses_tensor_cores(&m->layers[0].wqkv, B);
   // RoPE + KV append ride in the [q|k|v] epilogue unless q/k need a full-width norm first, the batch runs on the
   // tensor cores, or the cache is int8 (a row's scale needs the whole row)
-  const bool fuse_rope = !c.qk_norm && !tc_batch && !s->kv_int8 && !s->kv_owner;
+  const bool fuse_rope = !c.qk_norm && !tc_batch && !s->kv_int8 && !s->kv_owner && !s->evict_window;
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
     if (linear_can_fuse_norm(&L.wqkv, B)) {
@@ -732,6 +736,7 @@ static int enqueue_step(cai_session* s) {
       a.seq_index_dev = s->seq_index_dev;
       a.cache_len_dev = s->len_dev; a.batch = B; a.q_heads = m->heads_l; a.kv_heads = m->kv_heads_l;
       a.head_dim = c.head_dim; a.max_ctx = s->ctx_pitch; a.k_blocked = s->k_blocked; a.theta = m->theta; a.pos_dev = s->pos_dev;
+      { cai_session* o = s->kv_owner ? s->kv_owner : s; a.window = o->window; a.evict_sinks = o->evict_sinks; a.evict_window = o->evict_window; }
       a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
       a.out = s->att; a.ldo = m->qw_l; a.partial = s->partial; a.nsplit = s->nsplit;
       if (!fuse_rope) CAI_TRY(attn_rope_append(ctx, a));
@@ -918,6 +923,7 @@ static int session_check(cai_session* s) {
 }
 
 static int check_room(cai_session* s, int steps) {
+  if (s->evict_window > 0) return CAI_OK;                   // a stream with eviction never fills its cache
   for (int b = 0; b < s->batch; ++b)
     if (s->len_host[(size_t)b] + steps > s->max_ctx)
       return cai_fail(s->ctx, CAI_ERR_STATE, "context full: sequence %d holds %d of %d positions, %d more requested", b,
@@ -935,6 +941,10 @@ int cai_session_destroy(cai_session* s) {
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
   if (s->plan) step_plan_destroy(s->plan);
   if (s->plan_ts) cudaFree(s->plan_ts);
+  if (s->sample_scratch) cudaFree(s->sample_scratch);
+  if (s->sample_ids) cudaFree(s->sample_ids);
+  if (s->sample_probs) cudaFree(s->sample_probs);
+  if (s->sample_u) cudaFree(s->sample_u);
   if (s->ar) comm_ar_destroy(s->ctx, s->ar);
   if (s->kv_owner) { s->k_cache = s->v_cache = nullptr; s->k_scales = s->v_scales = nullptr; }   // borrowed
   void* bufs[] = {s->seq_index_dev, s->k_cache, s->v_cache, s->k_snap, s->v_snap, s->tokens_dev, s->pos_dev, s->len_dev, s->x, s->x_alt, s->h, s->qkv,
@@ -983,7 +993,7 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   if (!s) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
   s->m = m; s->ctx = ctx; s->max_ctx = max_ctx; s->batch = batch; s->layer_stride = layer_stride;
   s->ctx_pitch = ctx_pitch;
-  s->k_blocked = kv_owner ? kv_owner->k_blocked : ((!kv_int8 && attn_k_blocked_supported(m->heads_l, m->kv_heads_l, c.head_dim)) ? 1 : 0);
+  s->k_blocked = kv_owner ? kv_owner->k_blocked : (attn_k_blocked_supported(m->heads_l, m->kv_heads_l, c.head_dim) ? 1 : 0);
   s->kv_int8 = kv_int8; s->scale_stride = scale_stride;
   s->len_host.assign((size_t)batch, 0);
   m->sessions += 1;
@@ -1134,6 +1144,8 @@ int cai_session_truncate(cai_session* s, int seq, int committed_len) {
   if (seq < 0 || seq >= s->batch) return cai_fail(s->ctx, CAI_ERR_INVALID, "sequence %d of %d", seq, s->batch);
   if (committed_len < 0 || committed_len > s->len_host[(size_t)seq])
     return cai_fail(s->ctx, CAI_ERR_INVALID, "truncate to %d outside the committed prefix of %d", committed_len, s->len_host[(size_t)seq]);
+  if (s->evict_window > 0 && s->len_host[(size_t)seq] > s->evict_sinks + s->evict_window && committed_len != s->len_host[(size_t)seq])
+    return cai_fail(s->ctx, CAI_ERR_STATE, "truncate after eviction has dropped rows: the rows a shorter prefix needs are gone");
   s->len_host[(size_t)seq] = committed_len;
   return push_len(s);
 }
@@ -1159,6 +1171,42 @@ int cai_session_fill_for_benchmark(cai_session* s, int n_rows) {
   }
   for (auto& l : s->len_host) l = n_rows;
   return push_len(s);
+}
+
+// A change of what the steps see invalidates anything captured with the old parameters.
+static void session_drop_captured(cai_session* s) {
+  if (s->graph_exec) { cudaGraphExecDestroy(s->graph_exec); s->graph_exec = nullptr; }
+  if (s->plan) { step_plan_destroy(s->plan); s->plan = nullptr; }      // the persistent step kernel attends over the whole cache
+  if (s->wide) { cai_session_destroy(s->wide); s->wide = nullptr; }
+}
+
+int cai_session_enable_eviction(cai_session* s, int sink_tokens, int recent_window) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (s->kv_owner) return cai_fail(ctx, CAI_ERR_STATE, "not on a prefill helper");
+  if (sink_tokens < 0 || recent_window < 0 || (recent_window == 0 && sink_tokens != 0) || sink_tokens + recent_window > s->max_ctx)
+    return cai_fail(ctx, CAI_ERR_INVALID, "eviction with %d sinks + %d recent rows in a cache of %d", sink_tokens, recent_window, s->max_ctx);
+  const int cap = recent_window > 0 ? sink_tokens + recent_window : s->max_ctx;
+  for (int l : s->len_host)
+    if (l > cap || (s->evict_window > 0 && l > s->evict_sinks + s->evict_window))
+      return cai_fail(ctx, CAI_ERR_STATE, "the policy can change only while every sequence holds no more rows than it keeps");
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  session_drop_captured(s);
+  s->evict_sinks = sink_tokens; s->evict_window = recent_window;
+  return CAI_OK;
+}
+
+int cai_session_set_window(cai_session* s, int window) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (s->kv_owner) return cai_fail(ctx, CAI_ERR_STATE, "not on a prefill helper");
+  if (window < 0) return cai_fail(ctx, CAI_ERR_INVALID, "window %d", window);
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  session_drop_captured(s);
+  s->window = window;
+  return CAI_OK;
 }
 
 int cai_session_cache_len(cai_session* s, int seq, int* out_len) {
@@ -1230,6 +1278,65 @@ int cai_session_decode_greedy(cai_session* s, const int32_t* tokens_host, int n_
   return session_check(s);
 }
 
+static int sample_ensure(cai_session* s) {
+  cai_ctx* ctx = s->ctx;
+  if (s->m->tp_size > 1) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "device sampling needs the whole logits row on one GPU (tensor-parallel sessions shard the vocabulary)");
+  if (s->sample_scratch) return CAI_OK;
+  const int B = s->batch;
+  CAI_CUDA(ctx, cudaMalloc((void**)&s->sample_scratch, (size_t)sample_scratch_floats(B) * 4));
+  CAI_CUDA(ctx, cudaMalloc((void**)&s->sample_ids, (size_t)B * 64 * 4));
+  CAI_CUDA(ctx, cudaMalloc((void**)&s->sample_probs, (size_t)B * 64 * 4));
+  CAI_CUDA(ctx, cudaMalloc((void**)&s->sample_u, (size_t)B * 4));
+  return CAI_OK;
+}
+
+int cai_session_step_topk(cai_session* s, const int32_t* tokens_host, const int32_t* abs_pos_host, int k, float temperature,
+                          int32_t* ids_out_host, float* probs_out_host) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host || !ids_out_host || !probs_out_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_step_topk: null argument");
+  CAI_TRY(sample_ensure(s));
+  CAI_TRY(check_room(s, 1));
+  CAI_TRY(stage_inputs(s, tokens_host, abs_pos_host));
+  CAI_TRY(run_step(s));
+  for (auto& l : s->len_host) l += 1;
+  CAI_TRY(sample_launch(ctx, s->logits, s->m->vocab_l, s->batch, s->m->vocab_l, k, temperature, 0.f, 0ull, nullptr, s->sample_scratch,
+                        s->sample_ids, s->sample_probs, nullptr, nullptr, nullptr, 0, nullptr));
+  CAI_CUDA(ctx, cudaMemcpyAsync(ids_out_host, s->sample_ids, (size_t)s->batch * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaMemcpyAsync(probs_out_host, s->sample_probs, (size_t)s->batch * k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return session_check(s);
+}
+
+int cai_session_decode_sampled(cai_session* s, const int32_t* tokens_host, int n_steps, const cai_sampling* opt, const float* uniforms_host,
+                               int32_t* out_tokens_host) {
+  if (!s) return CAI_ERR_INVALID;
+  cai_ctx* ctx = s->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!tokens_host || n_steps < 1 || !opt) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_decode_sampled: bad argument");
+  if (opt->top_k < 1 || opt->top_k > 64) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "cai_session_decode_sampled: top_k %d outside 1..64", opt->top_k);
+  CAI_TRY(sample_ensure(s));
+  CAI_TRY(check_room(s, n_steps));
+  CAI_TRY(stage_inputs(s, tokens_host, nullptr));
+  CAI_CUDA(ctx, cudaMemsetAsync(s->trace_count, 0, 4, ctx->stream));
+  for (int i = 0; i < n_steps; ++i) {
+    if (uniforms_host) {
+      CAI_CUDA(ctx, cudaMemcpyAsync(s->sample_u, uniforms_host + (size_t)i * s->batch, (size_t)s->batch * 4, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    CAI_TRY(run_step(s));                      // forward + greedy advance; the draw below replaces the token it chose
+    CAI_TRY(sample_launch(ctx, s->logits, s->m->vocab_l, s->batch, s->m->vocab_l, opt->top_k, opt->temperature, opt->top_p, opt->seed,
+                          uniforms_host ? s->sample_u : nullptr, s->sample_scratch, nullptr, nullptr, s->tokens_dev, s->trace, s->trace_count,
+                          s->trace_cap, nullptr));
+    if (uniforms_host) CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));     // the pageable source row is reused by nothing, but keep it simple
+  }
+  for (auto& l : s->len_host) l += n_steps;
+  if (out_tokens_host)
+    CAI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, s->trace, (size_t)n_steps * s->batch * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return session_check(s);
+}
+
 int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens) {
   if (!s) return CAI_ERR_INVALID;
   cai_ctx* ctx = s->ctx;
@@ -1256,7 +1363,7 @@ int cai_session_prefill(cai_session* s, const int32_t* tokens_host, int n_tokens
   {
     const char* off = getenv("CAI_PREFILL_CHUNK");
     const int C = (B <= 32) ? 64 / B : 0;
-    if (C >= 2 && n_tokens >= C && !(off && *off == '0') && !s->kv_owner) {
+    if (C >= 2 && n_tokens >= C && !(off && *off == '0') && !s->kv_owner && !s->evict_window) {
       if (!s->wide) {
         cai_session* w = nullptr;
         const int st = session_create_impl(s->m, s->max_ctx, B * C, s->kv_int8 ? CAI_TYPE_I8 : CAI_TYPE_F32, s, &w);
@@ -1447,13 +1554,24 @@ int cai_session_read_kv_row(cai_session* s, int layer, int seq, int kv_head, int
   if (layer < 0 || layer >= c.layers || seq < 0 || seq >= o->batch || kv_head < 0 || kv_head >= s->m->kv_heads_l || pos < 0 ||
       pos >= o->len_host[(size_t)seq])
     return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_read_kv_row: layer %d sequence %d head %d position %d outside the cached rows", layer, seq, kv_head, pos);
+  if (o->evict_window > 0 && o->len_host[(size_t)seq] > o->evict_sinks + o->evict_window) {
+    // rows live as sinks + a ring: positions between the sinks and the recent window are gone
+    if (pos >= o->evict_sinks && pos < o->len_host[(size_t)seq] - o->evict_window)
+      return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_read_kv_row: position %d was evicted", pos);
+    if (pos >= o->evict_sinks) pos = o->evict_sinks + (pos - o->evict_sinks) % o->evict_window;
+  }
   const size_t head0 = (size_t)layer * o->layer_stride + ((size_t)seq * s->m->kv_heads_l + kv_head) * (size_t)o->ctx_pitch * hd;
   const size_t row0 = head0 + (size_t)pos * hd;
   CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (o->kv_int8) {
     if (!k_codes_host || !v_codes_host || !scales_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_session_read_kv_row: the int8 cache needs code and scale outputs");
     const size_t srow = (size_t)layer * o->scale_stride + ((size_t)seq * s->m->kv_heads_l + kv_head) * (size_t)o->ctx_pitch + pos;
-    CAI_CUDA(ctx, cudaMemcpy(k_codes_host, (const int8_t*)o->k_cache + row0, (size_t)hd, cudaMemcpyDeviceToHost));
+    if (o->k_blocked) {
+      const int8_t* blk = (const int8_t*)o->k_cache + head0 + (size_t)(pos >> 5) * 32 * hd + (size_t)(pos & 31) * 16;
+      CAI_CUDA(ctx, cudaMemcpy2D(k_codes_host, 16, blk, 32 * 16, 16, (size_t)(hd / 16), cudaMemcpyDeviceToHost));
+    } else {
+      CAI_CUDA(ctx, cudaMemcpy(k_codes_host, (const int8_t*)o->k_cache + row0, (size_t)hd, cudaMemcpyDeviceToHost));
+    }
     CAI_CUDA(ctx, cudaMemcpy(v_codes_host, (const int8_t*)o->v_cache + row0, (size_t)hd, cudaMemcpyDeviceToHost));
     CAI_CUDA(ctx, cudaMemcpy(scales_host, o->k_scales + srow, 4, cudaMemcpyDeviceToHost));
     CAI_CUDA(ctx, cudaMemcpy(scales_host + 1, o->v_scales + srow, 4, cudaMemcpyDeviceToHost));
@@ -1485,7 +1603,12 @@ int cai_session_uses_step_kernel(cai_session* s, int* out_flag) {
 int cai_session_last_kv_bytes(cai_session* s, int64_t* out_bytes) {
   if (!s || !out_bytes) return CAI_ERR_INVALID;
   int64_t rows = 0;
-  for (int l : s->len_host) rows += l;
+  for (int l : s->len_host) {
+    int live = l;
+    if (s->evict_window > 0 && live > s->evict_sinks + s->evict_window) live = s->evict_sinks + s->evict_window;
+    else if (s->window > 0 && live > s->window) live = s->window;
+    rows += live;
+  }
   // per cached row and layer: K and V, head_dim values (4 bytes, or 1 byte + a 4-byte scale per head in the int8 cache)
   const int64_t per_row = s->kv_int8 ? (int64_t)s->m->kw_l + 4 * (int64_t)s->m->kv_heads_l : (int64_t)s->m->kw_l * 4;
   *out_bytes = rows * 2 * per_row * (int64_t)s->m->cfg.layers;

@@ -269,7 +269,13 @@ class OracleSession:
     (neural/neural.cl:2343-2346). kv_int8 keeps the cache as int8 codes with one fp32 scale per row and folds the
     scales into the score and the value sum exactly like cai_sdpa_decode_int8 (neural/neural.cl:2583-2687)."""
 
-    def __init__(self, model, max_ctx, kv_int8=False):
+    def __init__(self, model, max_ctx, kv_int8=False, window=0, evict=None):
+        """window > 0: every layer attends over the most recent `window` rows (TNNetFusedSDPA's Window, jStart of
+        neural/neural.cl:2437-2438). evict = (sinks, recent): StreamingLLM, the first `sinks` rows and the most recent
+        `recent` rows stay (TNNetStreamingDecoder.EnableEviction, neural/neuraldecode.pas:1257-1276); rows keep the
+        rotation of their original position. The oracle keeps every row and selects; max_ctx bounds positions here."""
+        self.window = window
+        self.evict = evict
         self.m = model
         cfg = model.cfg
         self.max_ctx = max_ctx
@@ -331,23 +337,28 @@ class OracleSession:
                 self.k[li, :, slot, :] = k.reshape(cfg.kv_heads, hd)
                 self.v[li, :, slot, :] = v.reshape(cfg.kv_heads, hd)
             n = slot + 1
+            rows = np.arange(n)
+            if self.evict is not None and n > self.evict[0] + self.evict[1]:
+                rows = np.concatenate([np.arange(self.evict[0]), np.arange(n - self.evict[1], n)])
+            elif self.window > 0 and n > self.window:
+                rows = np.arange(n - self.window, n)
             att = np.empty(cfg.q_width, dtype=dt)
             for hq in range(cfg.heads):
                 g = hq // group
                 qh = q[hq * hd:(hq + 1) * hd]
                 if self.kv_int8:
                     # raw code dot, then one scalar per row: kscale * 1/sqrt(d) (neural.cl:2636-2639)
-                    sc = (self.k[li, g, :n, :].astype(dt) @ qh) * (self.k_scale[li, g, :n].astype(dt) * inv_sqrt)
+                    sc = (self.k[li, g, rows, :].astype(dt) @ qh) * (self.k_scale[li, g, rows].astype(dt) * inv_sqrt)
                 else:
-                    sc = (self.k[li, g, :n, :] @ qh) * inv_sqrt      # scale after the dot (neural.cl:2450)
+                    sc = (self.k[li, g, rows, :] @ qh) * inv_sqrt    # scale after the dot (neural.cl:2450)
                 mx = np.max(sc)
                 e = np.exp(sc - mx)
                 den = np.sum(e, dtype=dt)
                 if self.kv_int8:
                     # (e_j * vscale_j) * code, summed, divided once at the end (neural.cl:2679-2684)
-                    att[hq * hd:(hq + 1) * hd] = ((e * self.v_scale[li, g, :n].astype(dt)) @ self.v[li, g, :n, :].astype(dt)) / den
+                    att[hq * hd:(hq + 1) * hd] = ((e * self.v_scale[li, g, rows].astype(dt)) @ self.v[li, g, rows, :].astype(dt)) / den
                 else:
-                    att[hq * hd:(hq + 1) * hd] = (e @ self.v[li, g, :n, :]) / den   # divide once at the end
+                    att[hq * hd:(hq + 1) * hd] = (e @ self.v[li, g, rows, :]) / den   # divide once at the end
             x = x + b["wo"] @ att
             h = rms_norm(x, b["ffn_norm"], cfg.rms_eps)
             if cfg.n_experts:
@@ -389,3 +400,42 @@ def greedy_decode(model, prompt, n_new, max_ctx=None):
         out.append(tok)
         rows.append(logits)
     return out, rows
+
+
+def sampler_window(logits, k, temperature=1.0):
+    """The candidate window the reference's samplers work on: scores = softmax(logits / temperature) over the whole row
+    (TNNetTemperatureProcessor, neural/neuralchatengine.pas:1387-1388; the samplers take a post-softmax volume), sorted
+    descending with ties to the lower id, truncated to the top k (TNNetSamplerBase.SelectTopCandidates,
+    neural/neuralvolume.pas:991-1030). Returns (ids, probabilities)."""
+    z = np.asarray(logits, dtype=np.float64) / float(temperature)
+    z = np.where(np.isnan(z), -np.inf, z)
+    p = np.exp(z - np.max(z))
+    p = p / p.sum()
+    order = np.argsort(-z, kind="stable")[:k]
+    return order.astype(np.int32), p[order].astype(np.float32)
+
+
+def weighted_draw(ids, probs, u, top_p=0.0):
+    """TNNetSamplerWeightedTopK.SampleFromSorted (neural/neuralvolume.pas:4749-4785) over a window, optionally cut to the
+    nucleus first (the shortest prefix whose mass exceeds top_p): Roll = u * KeptSum; the first candidate whose running
+    sum exceeds Roll; the last kept candidate as the numeric-safety fallback. fp32 running sums, as on the device."""
+    n_keep = len(ids)
+    if 0.0 < top_p < 1.0:
+        cum = np.float32(0)
+        for j, pj in enumerate(probs):
+            cum = np.float32(cum + pj)
+            if cum > np.float32(top_p):
+                n_keep = j + 1
+                break
+    kept = np.float32(0)
+    for pj in probs[:n_keep]:
+        kept = np.float32(kept + pj)
+    if not kept > 0:
+        return int(ids[0])
+    roll = np.float32(np.float32(u) * kept)
+    cum = np.float32(0)
+    for j in range(n_keep):
+        cum = np.float32(cum + probs[j])
+        if roll < cum:
+            return int(ids[j])
+    return int(ids[n_keep - 1])
