@@ -37,7 +37,7 @@ TYPE_BPW = {8: 34.0 / 32.0, 2: 18.0 / 32.0}          # Q8_0, Q4_0 bytes per weig
 # 150.502 MB of codes and scales; STEP_KERNEL_TRAFFIC is the same ratio for one launch of the persistent step kernel
 # (weights + cached K and V rows) on a depth-cut model.
 GEMV_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0332
-STEP_KERNEL_TRAFFIC_PER_ALGORITHMIC_BYTE = None      # filled in from the step kernel's ncu capture; None = not measured
+STEP_KERNEL_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0042    # 1898.532 MB read + 6.480 MB written for 1896.989 MB (2-layer cut, context 2048)
 WORKLOAD_DEFAULTS = {
     # arch: (ggml type, seed, batch, context)
     "qwen2.5-32b": (8, 3, 1, 8192),
