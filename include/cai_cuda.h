@@ -51,6 +51,17 @@ enum {
   CAI_TYPE_F16 = 1,
   CAI_TYPE_Q4_0 = 2,  /* 18-byte blocks of 32: fp16 d, 16 nibble bytes; x = d*(nib-8)  (neuralgguf.pas:822-845) */
   CAI_TYPE_Q8_0 = 8,  /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
+  /* Load-time formats: accepted by cai_model_upload_tensor, cai_linear_create, cai_dequantize and the GGUF loader; decoded
+     on the device to fp32 when they arrive, as the reference's reader does (DecodeGGMLSpan, neuralgguf.pas:1471-1523), and
+     resident as F32 (or as CAI_TYPE_I8ROW under cai_model_set_int8_weights). Block rules: neuralgguf.pas:448-945. */
+  CAI_TYPE_Q4_1 = 3,  /* 20-byte blocks of 32 */
+  CAI_TYPE_Q5_0 = 6,  /* 22-byte blocks of 32 */
+  CAI_TYPE_Q5_1 = 7,  /* 24-byte blocks of 32 */
+  CAI_TYPE_Q2_K = 10, /* 84-byte super-blocks of 256 */
+  CAI_TYPE_Q3_K = 11, /* 110-byte super-blocks of 256 */
+  CAI_TYPE_Q4_K = 12, /* 144-byte super-blocks of 256 */
+  CAI_TYPE_Q5_K = 13, /* 176-byte super-blocks of 256 */
+  CAI_TYPE_Q6_K = 14, /* 210-byte super-blocks of 256 */
   CAI_TYPE_I8ROW = 124, /* the reference's own int8 weights (what ChatTerminal runs by default): int8 codes [N][K] and ONE fp32
                          scale per output row, scale = maxabs/127, code = Round(v * (1/maxabs) * 127) with round-half-to-even
                          (TNNetVolume.QuantizeInt8 / MaxAbsFinite, neural/neuralvolume.pas:12471-12562); the product is the raw
@@ -259,6 +270,52 @@ int cai_model_init_synthetic(cai_model* m, int type, uint64_t seed, float std);
  * out_bytes_cap guards the host buffer; rows/cols/type of the slice are returned. */
 int cai_model_read_tensor(cai_model* m, const char* hf_name, void* out_host, int64_t out_bytes_cap,
                           int* out_type, int64_t* out_rows, int64_t* out_cols);
+/* ------------------------------------------------------------------------- */
+/* GGUF files on the C side. Replaces TNNetGGUFReader                         */
+/* (neural/neuralgguf.pas:168-243; ParseFile :1072-1220; metadata getters     */
+/* :1263-1344; LoadTensorFlat :1674+) and the GGUF importers                  */
+/* BuildLlamaFromGGUFEx / BuildFromGGUFEx (neural/neuralpretrained.pas:       */
+/* 17484-17876). Versions 2 and 3; the reader's checks and refusals follow    */
+/* the reference's (bad magic, implausible counts or dimensions, empty or     */
+/* duplicate names, nested arrays, rows that are not whole blocks, a data     */
+/* range outside the file). A reader needs no GPU; decoding does.             */
+/* ------------------------------------------------------------------------- */
+typedef struct cai_gguf cai_gguf;
+/* err_buf (nullable) receives the reason when the file is refused (CAI_ERR_INVALID). */
+int cai_gguf_open(const char* path, cai_gguf** out, char* err_buf, int err_len);
+int cai_gguf_close(cai_gguf* g);
+int cai_gguf_last_error(cai_gguf* g, char* buf, int buf_len);
+/* Any pointer may be NULL. data_start = file offset of the aligned data section. */
+int cai_gguf_info(cai_gguf* g, int* version, int* alignment, int64_t* n_meta, int64_t* n_tensors, int64_t* data_start);
+/* Metadata. value_type is the GGUF value type id (8 string, 9 array, ...). The getters follow GetMetaInt / GetMetaFloat /
+ * GetMetaString: a missing key sets *found = 0 and leaves *out alone (the caller's default stands); a key of another type
+ * is CAI_ERR_INVALID. Integers of every width and bools read as int; ints also read as float. */
+int cai_gguf_meta_key(cai_gguf* g, int64_t index, char* key_buf, int key_cap, int* value_type);
+int cai_gguf_meta_int(cai_gguf* g, const char* key, int64_t* out, int* found);
+int cai_gguf_meta_float(cai_gguf* g, const char* key, double* out, int* found);
+int cai_gguf_meta_string(cai_gguf* g, const char* key, char* buf, int cap, int* found);
+int cai_gguf_meta_array_count(cai_gguf* g, const char* key, int64_t* out_count);   /* 0 when the key is absent */
+/* Tensor table. shape8 is in served order, contiguous axis LAST (the stored ggml dims reversed, :1157-1162): a linear
+ * weight reads [out, in]. data_begin is relative to the data section; data_bytes is 0 for a type without a decoder. */
+int cai_gguf_tensor_info(cai_gguf* g, int64_t index, char* name_buf, int name_cap, int* type, int* ndims, int64_t* shape8,
+                         int64_t* data_begin, int64_t* data_bytes);
+int cai_gguf_find_tensor(cai_gguf* g, const char* name, int64_t* out_index);       /* -1 when absent */
+int cai_gguf_read_raw(cai_gguf* g, int64_t index, void* out_host, int64_t cap_bytes);
+/* DecodeGGMLSpan on the device: n_elems elements of `type` blocks (host bytes) -> fp32 (host), bit-identical to the
+ * reference's decoders for F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K. */
+int cai_gguf_decode(cai_ctx* ctx, int type, const void* raw_host, int64_t n_elems, float* out_host);
+/* LoadTensorFlat: tensor `index` decoded to fp32 in flat row-major order. */
+int cai_gguf_load_tensor(cai_ctx* ctx, cai_gguf* g, int64_t index, float* out_host, int64_t cap_elems);
+/* Metadata -> configuration (architectures llama and qwen2; anything else CAI_ERR_UNSUPPORTED, as are RoPE position
+ * interpolation with a factor other than 1 and qwen2 sliding-window files). max_positions (nullable) = <arch>.context_length. */
+int cai_gguf_llama_config(cai_gguf* g, cai_llama_config* cfg, int64_t* max_positions);
+/* BuildFromGGUFEx: opens the file, builds the configuration, creates the model (this rank's shard when tp_size > 1),
+ * uploads every tensor under its HF name and finalizes. q/k rows stay in their stored order, which is the interleaved
+ * rotary order the graph runs in (the reference's reader de-interleaves and its loader re-interleaves:
+ * neuralgguf.pas:428-438, neuralpretrained.pas:14792-14812). quantize_int8 = the importer's pQuantizeInt8. */
+int cai_model_load_gguf(cai_ctx* ctx, const char* path, int tp_rank, int tp_size, int quantize_int8, cai_model** out_model,
+                        cai_llama_config* out_cfg /* nullable */, int64_t* out_max_positions /* nullable */);
+
 /* Verifies every tensor the configuration needs is present; required before sessions. */
 int cai_model_finalize(cai_model* m);
 /* Bytes of matrix weights one decode step streams on this rank (codes + scales). */

@@ -11,6 +11,8 @@ LIB_PATH = os.path.join(HERE, "libcai_cuda.so")
 
 CAI_OK = 0
 TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
+TYPE_Q4_1, TYPE_Q5_0, TYPE_Q5_1 = 3, 6, 7                                  # load-time formats: decoded to fp32 on arrival
+TYPE_Q2_K, TYPE_Q3_K, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K = 10, 11, 12, 13, 14
 TYPE_I8 = 24              # KV cache only: int8 codes + one fp32 scale per row
 TYPE_I8ROW = 124          # the reference's int8 weights: int8 codes [N][K] + one fp32 scale per output row
 ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_TANH = 0, 1, 2, 3
@@ -87,6 +89,23 @@ SIGNATURES = {
     "cai_model_create_ep": [_P, C.POINTER(LlamaConfigC), _I, _I, _PP],
     "cai_model_destroy": [_P],
     "cai_model_upload_tensor": [_P, C.c_char_p, _I, _P, _I64, _I64, _I],
+    "cai_gguf_open": [C.c_char_p, _PP, C.c_char_p, _I],
+    "cai_gguf_close": [_P],
+    "cai_gguf_last_error": [_P, C.c_char_p, _I],
+    "cai_gguf_info": [_P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64)],
+    "cai_gguf_meta_key": [_P, _I64, C.c_char_p, _I, C.POINTER(_I)],
+    "cai_gguf_meta_int": [_P, C.c_char_p, C.POINTER(_I64), C.POINTER(_I)],
+    "cai_gguf_meta_float": [_P, C.c_char_p, C.POINTER(C.c_double), C.POINTER(_I)],
+    "cai_gguf_meta_string": [_P, C.c_char_p, C.c_char_p, _I, C.POINTER(_I)],
+    "cai_gguf_meta_array_count": [_P, C.c_char_p, C.POINTER(_I64)],
+    "cai_gguf_tensor_info": [_P, _I64, C.c_char_p, _I, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I64), C.POINTER(_I64),
+                             C.POINTER(_I64)],
+    "cai_gguf_find_tensor": [_P, C.c_char_p, C.POINTER(_I64)],
+    "cai_gguf_read_raw": [_P, _I64, _P, _I64],
+    "cai_gguf_decode": [_P, _I, _P, _I64, _P],
+    "cai_gguf_load_tensor": [_P, _P, _I64, _P, _I64],
+    "cai_gguf_llama_config": [_P, C.POINTER(LlamaConfigC), C.POINTER(_I64)],
+    "cai_model_load_gguf": [_P, C.c_char_p, _I, _I, _I, _PP, C.POINTER(LlamaConfigC), C.POINTER(_I64)],
     "cai_model_set_int8_weights": [_P, _I],
     "cai_model_init_synthetic": [_P, _I, C.c_uint64, C.c_float],
     "cai_model_read_tensor": [_P, C.c_char_p, _P, _I64, C.POINTER(_I), C.POINTER(_I64), C.POINTER(_I64)],

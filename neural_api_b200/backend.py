@@ -133,6 +133,13 @@ class CudaBackend:
         self._check(self.lib.cai_dequantize(self.ctx, ggml_type, _ptr(blocks), rows, cols, _ptr(out)))
         return out
 
+    def gguf_decode(self, ggml_type, raw, n_elems):
+        """DecodeGGMLSpan on the device: raw block bytes of any ggml type the reader decodes -> fp32."""
+        raw = np.ascontiguousarray(raw)
+        out = np.empty(n_elems, dtype=np.float32)
+        self._check(self.lib.cai_gguf_decode(self.ctx, ggml_type, _ptr(raw), n_elems, _ptr(out)))
+        return out
+
     # -- layer shims on device buffers --------------------------------------
     def rmsnorm(self, x, gain, eps):
         x = np.ascontiguousarray(x, dtype=np.float32)
@@ -342,6 +349,107 @@ class FusedSDPA:
             dout.free()
 
 
+class GGUFError(CaiError):
+    """A file the reader refused (the reference's EGGUFError)."""
+
+
+class GGUFReader:
+    """TNNetGGUFReader: header, metadata and tensor table of one GGUF file, parsed by the library (no GPU needed to
+    open a file or read its tables; decoding a tensor runs on the GPU of the backend passed to load_tensor)."""
+
+    def __init__(self, path):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        err = C.create_string_buffer(512)
+        st = self.lib.cai_gguf_open(str(path).encode(), C.byref(h), err, 512)
+        if st != _lib.CAI_OK:
+            raise GGUFError(st, err.value.decode(errors="replace"))
+        self.handle = h
+        ver, al, nm, nt, ds = C.c_int(), C.c_int(), C.c_int64(), C.c_int64(), C.c_int64()
+        self._check(self.lib.cai_gguf_info(h, C.byref(ver), C.byref(al), C.byref(nm), C.byref(nt), C.byref(ds)))
+        self.version, self.alignment, self.data_start = ver.value, al.value, ds.value
+        self.meta_count, self.tensor_count = nm.value, nt.value
+
+    def _check(self, st):
+        if st != _lib.CAI_OK:
+            buf = C.create_string_buffer(512)
+            self.lib.cai_gguf_last_error(self.handle, buf, 512)
+            raise GGUFError(st, buf.value.decode(errors="replace"))
+
+    def meta_keys(self):
+        out = []
+        buf, vt = C.create_string_buffer(512), C.c_int()
+        for i in range(self.meta_count):
+            self._check(self.lib.cai_gguf_meta_key(self.handle, i, buf, 512, C.byref(vt)))
+            out.append((buf.value.decode(), vt.value))
+        return out
+
+    def get_meta_int(self, key, default):
+        v, found = C.c_int64(), C.c_int()
+        self._check(self.lib.cai_gguf_meta_int(self.handle, key.encode(), C.byref(v), C.byref(found)))
+        return v.value if found.value else default
+
+    def get_meta_float(self, key, default):
+        v, found = C.c_double(), C.c_int()
+        self._check(self.lib.cai_gguf_meta_float(self.handle, key.encode(), C.byref(v), C.byref(found)))
+        return v.value if found.value else default
+
+    def get_meta_string(self, key, default):
+        buf, found = C.create_string_buffer(4096), C.c_int()
+        self._check(self.lib.cai_gguf_meta_string(self.handle, key.encode(), buf, 4096, C.byref(found)))
+        return buf.value.decode(errors="replace") if found.value else default
+
+    def get_meta_array_count(self, key):
+        v = C.c_int64()
+        self._check(self.lib.cai_gguf_meta_array_count(self.handle, key.encode(), C.byref(v)))
+        return v.value
+
+    def tensor_info(self, index):
+        """(name, ggml type, shape with the contiguous axis last, data offset within the data section, bytes)."""
+        name, ty, nd = C.create_string_buffer(512), C.c_int(), C.c_int()
+        shape = (C.c_int64 * 8)()
+        beg, nbytes = C.c_int64(), C.c_int64()
+        self._check(self.lib.cai_gguf_tensor_info(self.handle, index, name, 512, C.byref(ty), C.byref(nd), shape,
+                                                  C.byref(beg), C.byref(nbytes)))
+        return name.value.decode(), ty.value, [int(shape[i]) for i in range(nd.value)], beg.value, nbytes.value
+
+    def find_tensor(self, name):
+        v = C.c_int64()
+        self._check(self.lib.cai_gguf_find_tensor(self.handle, name.encode(), C.byref(v)))
+        return v.value
+
+    def has_tensor(self, name):
+        return self.find_tensor(name) >= 0
+
+    def read_raw(self, index):
+        nbytes = self.tensor_info(index)[4]
+        buf = np.empty(max(nbytes, 1), dtype=np.uint8)
+        self._check(self.lib.cai_gguf_read_raw(self.handle, index, _ptr(buf), nbytes))
+        return buf[:nbytes]
+
+    def load_tensor(self, backend, name):
+        """LoadTensorFlat: the tensor decoded to fp32 on the backend's GPU, in its served shape."""
+        idx = self.find_tensor(name)
+        if idx < 0:
+            raise KeyError(name)
+        shape = self.tensor_info(idx)[2]
+        n = int(np.prod(shape))
+        out = np.empty(n, dtype=np.float32)
+        backend._check(self.lib.cai_gguf_load_tensor(backend.ctx, self.handle, idx, _ptr(out), n))
+        return out.reshape(shape)
+
+    def llama_config(self):
+        """(LlamaConfigC, context_length) from the metadata, as BuildFromGGUFEx derives them."""
+        cfg, mp = LlamaConfigC(), C.c_int64()
+        self._check(self.lib.cai_gguf_llama_config(self.handle, C.byref(cfg), C.byref(mp)))
+        return cfg, mp.value
+
+    def close(self):
+        if self.handle:
+            self.lib.cai_gguf_close(self.handle)
+            self.handle = None
+
+
 def make_config(hidden, inter, layers, heads, kv_heads, head_dim, vocab, rms_eps=1e-5, rope_theta=10000.0,
                 tie_embeddings=False, qkv_bias=False, qk_norm=False, n_experts=0, top_k=0, norm_topk=False, moe_inter=0):
     return LlamaConfigC(hidden, inter, layers, heads, kv_heads, head_dim, vocab, rms_eps, rope_theta,
@@ -361,6 +469,18 @@ class LlamaModel:
         else:
             backend._check(backend.lib.cai_model_create(backend.ctx, C.byref(cfg), tp_rank, tp_size, C.byref(h)))
         self.handle = h
+
+    @classmethod
+    def from_gguf(cls, backend, path, tp_rank=0, tp_size=1, quantize_int8=False):
+        """BuildFromGGUFEx: the whole file parsed, decoded and uploaded by the library. Returns the finalized model;
+        model.max_positions carries the file's context_length."""
+        self = cls.__new__(cls)
+        self.backend = backend
+        h, cfg, mp = C.c_void_p(), LlamaConfigC(), C.c_int64()
+        backend._check(backend.lib.cai_model_load_gguf(backend.ctx, str(path).encode(), tp_rank, tp_size, int(bool(quantize_int8)),
+                                                       C.byref(h), C.byref(cfg), C.byref(mp)))
+        self.handle, self.cfg, self.max_positions = h, cfg, mp.value
+        return self
 
     def upload_tensor(self, hf_name, ggml_type, data, rows, cols, interleave_head_dim=0):
         data = np.ascontiguousarray(data)

@@ -191,6 +191,7 @@ int cai_flush_l2(cai_ctx* ctx) {
 int cai_dequantize(cai_ctx* ctx, int type, const void* blocks_host, int64_t rows, int64_t cols, float* out_host) {
   CAI_TRY(cai_bind(ctx));
   if (!blocks_host || !out_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_dequantize: null buffer");
+  if (gguf_type_needs_decode(type)) return gguf_decode_host(ctx, type, blocks_host, rows * cols, out_host);
   QWeight w;
   int st = qweight_alloc(ctx, &w, type, rows, cols);
   if (st != CAI_OK) return st;
@@ -241,6 +242,13 @@ int cai_linear_create(cai_ctx* ctx, int type, const void* blocks_host, int64_t n
   CAI_TRY(cai_bind(ctx));
   if (!out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_create: null output");
   *out = nullptr;
+  if (gguf_type_needs_decode(type)) {
+    // Q4_1 / Q5_x / K-quants: decoded once at load (DecodeGGMLSpan, neural/neuralgguf.pas:1471-1523), resident as F32
+    if (!blocks_host || n_rows < 1 || k_cols < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_linear_create: bad argument");
+    std::vector<float> f32((size_t)n_rows * (size_t)k_cols);
+    CAI_TRY(gguf_decode_host(ctx, type, blocks_host, n_rows * k_cols, f32.data()));
+    return cai_linear_create(ctx, CAI_TYPE_F32, f32.data(), n_rows, k_cols, bias_host, out);
+  }
   cai_linear* lin = new (std::nothrow) cai_linear();
   if (!lin) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
   lin->ctx = ctx;

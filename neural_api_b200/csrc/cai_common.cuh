@@ -87,6 +87,12 @@ static inline int cai_bind(cai_ctx* ctx) {
 }
 
 int cai_ensure_staging(cai_ctx* ctx, size_t bytes);
+// gguf.cu: ggml types the linear kernels do not read directly (Q4_1, Q5_0, Q5_1, Q2_K .. Q6_K) are decoded on the
+// device to fp32, as the reference's reader does at load time, and continue as F32 tensors
+bool gguf_type_needs_decode(int type);
+int gguf_decode_host(cai_ctx* ctx, int type, const void* raw_host, int64_t n_elems, float* out_host);
+int gguf_upload_decoded(struct cai_model* m, cai_ctx* ctx, const char* hf_name, int type, const void* data_host, int64_t rows, int64_t cols,
+                        int interleave_head_dim);
 
 // ---------------------------------------------------------------------------
 // Resident weight matrix. GGUF blocks are split into planes when uploaded so

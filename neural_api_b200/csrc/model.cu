@@ -206,6 +206,7 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
   CAI_TRY(cai_bind(ctx));
   if (!hf_name || !data_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_upload_tensor: null argument");
   if (m->sessions > 0) return cai_fail(ctx, CAI_ERR_STATE, "weights are immutable while sessions exist");
+  if (gguf_type_needs_decode(type)) return gguf_upload_decoded(m, ctx, hf_name, type, data_host, rows, cols, interleave_head_dim);
   const cai_llama_config& c = m->cfg;
   const TName t = parse_name(hf_name);
   if (t.kind == T_IGNORE) return CAI_OK;

@@ -117,6 +117,46 @@ def pack_kats(out_dir):
     print("packed kats")
 
 
+def pack_gguf_files(fix, out_dir):
+    """The reference's GGUF fixtures as whole files (the C-side reader parses files, not tensors), the K-quant
+    reference dequantisations of tests/fixtures/tiny_kquant_ref.json (tests/TestNeuralPretrained.pas:5931-6020) and the
+    next-token logits of the F32 checkpoint twin (tiny_llama_logits.json) for the file-to-logits check."""
+    payload = {}
+    for f in ("tiny_kquant.gguf", "tiny_llama_q8.gguf", "tiny_llama_f16.gguf", "tiny_llama_f32.gguf"):
+        payload["file::" + f] = np.frombuffer(open(os.path.join(fix, f), "rb").read(), dtype=np.uint8)
+    ref = json.load(open(os.path.join(fix, "tiny_kquant_ref.json")))
+    payload["kquant::ref_f32"] = np.asarray(ref["ref_f32"], dtype=np.float32)
+    for k, v in ref["dequant"].items():
+        payload["kquant::" + k] = np.asarray(v, dtype=np.float32)
+    gold = json.load(open(os.path.join(fix, "tiny_llama_logits.json")))
+    payload["tiny_llama::sequences"] = np.asarray(gold["sequences"], dtype=np.int32)
+    payload["tiny_llama::logits"] = np.asarray(gold["logits"], dtype=np.float64)
+    np.savez_compressed(os.path.join(out_dir, "gguf_files.npz"), **payload)
+    print("packed gguf_files", sorted(payload))
+
+
+def pack_block_kats(out_dir):
+    """Seeded random blocks of every ggml type the reader decodes, with the `gguf` package's dequantisation of them
+    (the external oracle the reference's own fixture generators use, tools/make_kquant_gguf_fixture.py)."""
+    from gguf.quants import dequantize
+    from gguf.constants import GGMLQuantizationType as T
+    geometry = {2: (18, [0]), 3: (20, [0, 2]), 6: (22, [0]), 7: (24, [0, 2]), 8: (34, [0]), 10: (84, [80, 82]),
+                11: (110, [108]), 12: (144, [0, 2]), 13: (176, [0, 2]), 14: (210, [208])}
+    rng = np.random.default_rng(20240611)
+    payload = {}
+    n_blocks = 48
+    for t, (bb, f16_at) in geometry.items():
+        raw = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+        for off in f16_at:                       # finite scales, a few subnormal and negative ones among them
+            h = (rng.standard_normal(n_blocks) * 0.05).astype(np.float16)
+            h[0], h[1], h[2] = np.float16(6e-8), np.float16(-3.1e-5), np.float16(0.0)
+            raw[:, off:off + 2] = h.view(np.uint8).reshape(n_blocks, 2)
+        payload["raw::%d" % t] = raw.reshape(-1)
+        payload["deq::%d" % t] = np.asarray(dequantize(raw.reshape(-1), T(t)), dtype=np.float32).reshape(-1)
+    np.savez_compressed(os.path.join(out_dir, "block_kats.npz"), **payload)
+    print("packed block_kats", len(payload) // 2, "types")
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path of the reference checkout>")
@@ -130,6 +170,8 @@ def main():
     pack_gguf_case(fix, "tiny_llama_f16.gguf", None, "tiny_llama_config.json",
                    "tiny_llama_f16_gguf", out_dir)
     pack_kats(out_dir)
+    pack_gguf_files(fix, out_dir)
+    pack_block_kats(out_dir)
 
 
 if __name__ == "__main__":

@@ -41,6 +41,24 @@ def test_binding_table_matches_the_header(lib):
     assert sorted(_lib.SIGNATURES) == declared_symbols()
 
 
+def test_pascal_unit_declares_every_symbol_with_the_header_arity():
+    """neuralcuda.pas cannot be compiled here (no Free Pascal), so its external declarations are checked as text:
+    one per header symbol, same number of parameters."""
+    text = open(os.path.join(ROOT, "include", "cai_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    header = {n: len(a.split(",")) for n, a in re.findall(r"\bint\s+(cai_[a-z0-9_]+)\s*\(([^;]*?)\)\s*;", text, flags=re.S)}
+    pas = open(os.path.join(ROOT, "neural_api_b200", "pascal", "neuralcuda.pas")).read()
+    decls = dict(re.findall(r"function (cai_[a-z0-9_]+)\((.*?)\): cint; cdecl; external CaiLib;", pas))
+    assert sorted(decls) == sorted(header)
+    for name, params in decls.items():
+        n = 0
+        for group in params.split(";"):                      # "a, b: cint" declares two parameters
+            n += len(group.split(":")[0].split(","))
+        assert n == header[name], name
+    for const in ("CAI_TYPE_I8 = 24", "CAI_TYPE_I8ROW = 124", "CAI_TYPE_Q4_K = 12", "CAI_TYPE_Q6_K = 14"):
+        assert const in pas
+
+
 def test_config_struct_layout():
     from neural_api_b200._lib import LlamaConfigC
     assert C.sizeof(LlamaConfigC) == 16 * 4
