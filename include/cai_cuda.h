@@ -177,6 +177,25 @@ int cai_swiglu_dev(cai_ctx* ctx, const float* x_dev, float* y_dev, int tokens, i
 int cai_topk_gate_dev(cai_ctx* ctx, const float* router_logits_dev, int tokens, int n_experts,
                       int top_k, int renorm, int32_t* expert_ids_dev, float* gates_dev);
 
+/* Mixture-of-experts expert bank, layer at a time: TNNetMoEExpertBankGateUp(E, I, ...) and TNNetMoEExpertBankDown(E, H)
+ * (wiring neural/neuralpretrained.pas:15347-15388; device twin of the down bank cai_moe_expert_down,
+ * neural/neural.cl:2709-2807; semantics tests/TestNeuralLayersExtra.pas:7773-7906). The bank holds, per expert, the up and
+ * gate matrices [expert_width, hidden] and the down matrix [hidden, expert_width] in one storage type (F32, F16, Q8_0,
+ * Q4_0), bias-free. Slots: token t's j-th selected expert is slot_expert[t*top_k + j] with gate slot_gate[t*top_k + j]
+ * (what cai_topk_gate_dev writes); every token fills all top_k slots.
+ *   cai_moe_gate_up_dev: hidden_out[(t*top_k + j)*expert_width + d] = up_e(x_t)[d] * swish(gate_e(x_t)[d])
+ *   cai_moe_down_dev:    out[t*hidden + h] = sum over j, in slot order, of slot_gate * down_e(hidden_(t,j))[h]
+ * which = 0 up, 1 gate, 2 down in cai_moe_bank_upload; blocks are rows in `type` blocks along the input width. */
+typedef struct cai_moe_bank cai_moe_bank;
+int cai_moe_bank_create(cai_ctx* ctx, int n_experts, int hidden, int expert_width, int type, cai_moe_bank** out);
+int cai_moe_bank_destroy(cai_moe_bank* b);
+int cai_moe_bank_upload(cai_moe_bank* b, int expert, int which, const void* blocks_host);
+int cai_moe_bank_finalize(cai_moe_bank* b);
+int cai_moe_gate_up_dev(cai_moe_bank* b, const float* x_dev, const int32_t* slot_expert_dev, int tokens, int top_k,
+                        float* hidden_out_dev);
+int cai_moe_down_dev(cai_moe_bank* b, const float* hidden_dev, const int32_t* slot_expert_dev, const float* slot_gate_dev,
+                     int tokens, int top_k, float* out_dev);
+
 /* Fused GQA attention with a KV cache: TNNetFusedSDPA in incremental-decode mode
  * (BeginIncrementalDecode / ResetCache / TruncateCache / CacheLength,
  * tests/TestNeuralFusedSDPA.pas:226-236, 329-420; kernels neural/neural.cl:2354-2379,

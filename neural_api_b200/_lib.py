@@ -89,6 +89,12 @@ SIGNATURES = {
     "cai_model_create_ep": [_P, C.POINTER(LlamaConfigC), _I, _I, _PP],
     "cai_model_destroy": [_P],
     "cai_model_upload_tensor": [_P, C.c_char_p, _I, _P, _I64, _I64, _I],
+    "cai_moe_bank_create": [_P, _I, _I, _I, _I, _PP],
+    "cai_moe_bank_destroy": [_P],
+    "cai_moe_bank_upload": [_P, _I, _I, _P],
+    "cai_moe_bank_finalize": [_P],
+    "cai_moe_gate_up_dev": [_P, _P, _P, _I, _I, _P],
+    "cai_moe_down_dev": [_P, _P, _P, _P, _I, _I, _P],
     "cai_gguf_open": [C.c_char_p, _PP, C.c_char_p, _I],
     "cai_gguf_close": [_P],
     "cai_gguf_last_error": [_P, C.c_char_p, _I],

@@ -349,6 +349,37 @@ class FusedSDPA:
             dout.free()
 
 
+class MoEExpertBank:
+    """TNNetMoEExpertBankGateUp + TNNetMoEExpertBankDown of one layer, resident on the device: per expert the up, gate and
+    down matrices; gate_up() emits the selected experts' SwiGLU hidden packed by slot, down() the gate-weighted sum."""
+
+    def __init__(self, backend, n_experts, hidden, expert_width, ggml_type=TYPE_F32):
+        self.backend, self.n_experts, self.hidden, self.width = backend, n_experts, hidden, expert_width
+        h = C.c_void_p()
+        backend._check(backend.lib.cai_moe_bank_create(backend.ctx, n_experts, hidden, expert_width, ggml_type, C.byref(h)))
+        self.handle = h
+
+    def upload(self, expert, which, blocks):
+        """which: 'up' | 'gate' (rows [expert_width, hidden]) | 'down' (rows [hidden, expert_width])."""
+        blocks = np.ascontiguousarray(blocks)
+        self.backend._check(self.backend.lib.cai_moe_bank_upload(self.handle, expert, {"up": 0, "gate": 1, "down": 2}[which], _ptr(blocks)))
+
+    def finalize(self):
+        self.backend._check(self.backend.lib.cai_moe_bank_finalize(self.handle))
+
+    def gate_up(self, x_dev, slot_expert_dev, tokens, top_k, hidden_out_dev):
+        self.backend._check(self.backend.lib.cai_moe_gate_up_dev(self.handle, x_dev.ptr, slot_expert_dev.ptr, tokens, top_k, hidden_out_dev.ptr))
+
+    def down(self, hidden_dev, slot_expert_dev, slot_gate_dev, tokens, top_k, out_dev):
+        self.backend._check(self.backend.lib.cai_moe_down_dev(self.handle, hidden_dev.ptr, slot_expert_dev.ptr, slot_gate_dev.ptr,
+                                                              tokens, top_k, out_dev.ptr))
+
+    def close(self):
+        if self.handle:
+            self.backend.lib.cai_moe_bank_destroy(self.handle)
+            self.handle = None
+
+
 class GGUFError(CaiError):
     """A file the reader refused (the reference's EGGUFError)."""
 

@@ -541,3 +541,137 @@ int cai_sdpa_step_dev(cai_sdpa* s, const float* qkv_row_dev, float* out_dev) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Mixture-of-experts expert bank, layer at a time: TNNetMoEExpertBankGateUp / TNNetMoEExpertBankDown
+// (wiring neural/neuralpretrained.pas:15347-15388; device twin of the down bank neural/neural.cl:2709-2807;
+// semantics tests/TestNeuralLayersExtra.pas:7773-7906)
+// ---------------------------------------------------------------------------
+struct cai_moe_bank {
+  cai_ctx* ctx;
+  int n_experts, hidden, width, type;
+  std::vector<QWeight> gu, down;        // per expert: [up rows | gate rows] x hidden, hidden x width
+  std::vector<int> have;                // bit 0 up, 1 gate, 2 down
+  const void** d_gu_codes = nullptr; const __half** d_gu_scales = nullptr;
+  const void** d_down_codes = nullptr; const __half** d_down_scales = nullptr;
+  float* pair_out = nullptr; int64_t pair_cap = 0;
+  bool finalized = false;
+};
+
+static int bank_ptrs(cai_ctx* ctx, const void*** dst, const std::vector<const void*>& src) {
+  if (*dst) cudaFree((void*)*dst);
+  *dst = nullptr;
+  CAI_CUDA(ctx, cudaMalloc((void**)dst, src.size() * sizeof(void*)));
+  CAI_CUDA(ctx, cudaMemcpyAsync((void*)*dst, src.data(), src.size() * sizeof(void*), cudaMemcpyHostToDevice, ctx->stream));
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return CAI_OK;
+}
+
+extern "C" {
+
+int cai_moe_bank_create(cai_ctx* ctx, int n_experts, int hidden, int expert_width, int type, cai_moe_bank** out) {
+  CAI_TRY(cai_bind(ctx));
+  if (!out) return cai_fail(ctx, CAI_ERR_INVALID, "cai_moe_bank_create: null output");
+  *out = nullptr;
+  if (n_experts < 1 || hidden < 1 || expert_width < 1) return cai_fail(ctx, CAI_ERR_INVALID, "cai_moe_bank_create: bad shape");
+  if (type != CAI_TYPE_F32 && type != CAI_TYPE_F16 && type != CAI_TYPE_Q8_0 && type != CAI_TYPE_Q4_0)
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "expert banks hold F32, F16, Q8_0 or Q4_0 matrices");
+  cai_moe_bank* b = new (std::nothrow) cai_moe_bank();
+  if (!b) return cai_fail(ctx, CAI_ERR_OOM, "host allocation failed");
+  b->ctx = ctx; b->n_experts = n_experts; b->hidden = hidden; b->width = expert_width; b->type = type;
+  b->gu.resize((size_t)n_experts); b->down.resize((size_t)n_experts); b->have.assign((size_t)n_experts, 0);
+  *out = b;
+  return CAI_OK;
+}
+
+int cai_moe_bank_destroy(cai_moe_bank* b) {
+  if (!b) return CAI_ERR_INVALID;
+  cai_bind(b->ctx);
+  for (auto& w : b->gu) qweight_free(&w);
+  for (auto& w : b->down) qweight_free(&w);
+  if (b->d_gu_codes) cudaFree((void*)b->d_gu_codes);
+  if (b->d_gu_scales) cudaFree((void*)b->d_gu_scales);
+  if (b->d_down_codes) cudaFree((void*)b->d_down_codes);
+  if (b->d_down_scales) cudaFree((void*)b->d_down_scales);
+  if (b->pair_out) cudaFree(b->pair_out);
+  delete b;
+  return CAI_OK;
+}
+
+int cai_moe_bank_upload(cai_moe_bank* b, int expert, int which, const void* blocks_host) {
+  if (!b) return CAI_ERR_INVALID;
+  cai_ctx* ctx = b->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!blocks_host || expert < 0 || expert >= b->n_experts || which < 0 || which > 2)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_moe_bank_upload: bad argument");
+  b->finalized = false;
+  if (which == 2) {
+    QWeight* w = &b->down[(size_t)expert];
+    if (!w->codes) CAI_TRY(qweight_alloc(ctx, w, b->type, b->hidden, b->width));
+    CAI_TRY(qweight_upload(ctx, w, blocks_host, b->hidden, b->width, 0, 0, 0));
+  } else {
+    QWeight* w = &b->gu[(size_t)expert];
+    if (!w->codes) CAI_TRY(qweight_alloc(ctx, w, b->type, 2 * (int64_t)b->width, b->hidden));
+    QWeight view = qweight_rows_view(*w, which == 0 ? 0 : b->width, b->width);      // up rows first, gate rows second
+    CAI_TRY(qweight_upload(ctx, &view, blocks_host, b->width, b->hidden, 0, 0, 0));
+    w->present = true;
+  }
+  b->have[(size_t)expert] |= 1 << which;
+  return CAI_OK;
+}
+
+int cai_moe_bank_finalize(cai_moe_bank* b) {
+  if (!b) return CAI_ERR_INVALID;
+  cai_ctx* ctx = b->ctx;
+  CAI_TRY(cai_bind(ctx));
+  std::vector<const void*> gc, gs, dc, ds;
+  for (int e = 0; e < b->n_experts; ++e) {
+    if (b->have[(size_t)e] != 7) return cai_fail(ctx, CAI_ERR_STATE, "expert %d is missing matrices (have mask 0x%x)", e, b->have[(size_t)e]);
+    gc.push_back(b->gu[(size_t)e].codes); gs.push_back(b->gu[(size_t)e].scales);
+    dc.push_back(b->down[(size_t)e].codes); ds.push_back(b->down[(size_t)e].scales);
+  }
+  CAI_TRY(bank_ptrs(ctx, &b->d_gu_codes, gc));
+  CAI_TRY(bank_ptrs(ctx, (const void***)&b->d_gu_scales, gs));
+  CAI_TRY(bank_ptrs(ctx, &b->d_down_codes, dc));
+  CAI_TRY(bank_ptrs(ctx, (const void***)&b->d_down_scales, ds));
+  b->finalized = true;
+  return CAI_OK;
+}
+
+int cai_moe_gate_up_dev(cai_moe_bank* b, const float* x_dev, const int32_t* slot_expert_dev, int tokens, int top_k, float* hidden_out_dev) {
+  if (!b) return CAI_ERR_INVALID;
+  cai_ctx* ctx = b->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!b->finalized) return cai_fail(ctx, CAI_ERR_STATE, "cai_moe_bank_finalize first");
+  if (!x_dev || !slot_expert_dev || !hidden_out_dev || tokens < 1 || top_k < 1 || top_k > b->n_experts)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_moe_gate_up_dev: bad argument");
+  LinearArgs a; a.w = &b->gu[0]; a.x = x_dev; a.ldx = b->hidden; a.y = hidden_out_dev; a.ldy = b->width; a.batch = tokens * top_k;
+  a.epilogue = EPI_SWIGLU; a.bank_codes_dev = b->d_gu_codes; a.bank_scales_dev = b->d_gu_scales;
+  a.expert_ids_dev = slot_expert_dev; a.x_row_div = top_k;
+  return linear_launch(ctx, a);
+}
+
+int cai_moe_down_dev(cai_moe_bank* b, const float* hidden_dev, const int32_t* slot_expert_dev, const float* slot_gate_dev, int tokens, int top_k,
+                     float* out_dev) {
+  if (!b) return CAI_ERR_INVALID;
+  cai_ctx* ctx = b->ctx;
+  CAI_TRY(cai_bind(ctx));
+  if (!b->finalized) return cai_fail(ctx, CAI_ERR_STATE, "cai_moe_bank_finalize first");
+  if (!hidden_dev || !slot_expert_dev || !slot_gate_dev || !out_dev || tokens < 1 || top_k < 1 || top_k > b->n_experts)
+    return cai_fail(ctx, CAI_ERR_INVALID, "cai_moe_down_dev: bad argument");
+  const int64_t pairs = (int64_t)tokens * top_k;
+  if (pairs > b->pair_cap) {
+    if (b->pair_out) cudaFree(b->pair_out);
+    b->pair_out = nullptr; b->pair_cap = 0;
+    CAI_CUDA(ctx, cudaMalloc((void**)&b->pair_out, (size_t)pairs * b->hidden * 4));
+    b->pair_cap = pairs;
+  }
+  LinearArgs a; a.w = &b->down[0]; a.x = hidden_dev; a.ldx = b->width; a.y = b->pair_out; a.ldy = b->hidden; a.batch = (int)pairs;
+  a.bank_codes_dev = b->d_down_codes; a.bank_scales_dev = b->d_down_scales; a.expert_ids_dev = slot_expert_dev; a.x_row_div = 1;
+  CAI_TRY(linear_launch(ctx, a));
+  // out[t] = sum over the token's slots, in slot order, of gate * down_e(hidden)   (acc = mad(g, d, acc), neural.cl:2749)
+  CAI_CUDA(ctx, cudaMemsetAsync(out_dev, 0, (size_t)tokens * b->hidden * 4, ctx->stream));
+  return op_moe_combine(ctx, out_dev, b->hidden, b->pair_out, b->hidden, slot_gate_dev, tokens, top_k, b->hidden);
+}
+
+}  // extern "C"

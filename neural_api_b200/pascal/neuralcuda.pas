@@ -32,7 +32,7 @@ const
   CAI_ACT_NONE = 0; CAI_ACT_RELU = 1; CAI_ACT_SIGMOID = 2; CAI_ACT_TANH = 3;
 
 type
-  PCaiCtx = Pointer; PCaiLinear = Pointer; PCaiSdpa = Pointer; PCaiModel = Pointer; PCaiSession = Pointer; PCaiGguf = Pointer;
+  PCaiCtx = Pointer; PCaiLinear = Pointer; PCaiSdpa = Pointer; PCaiModel = Pointer; PCaiSession = Pointer; PCaiGguf = Pointer; PCaiMoeBank = Pointer;
   PPSingle = ^PSingle;
 
   TCaiLlamaConfig = record
@@ -79,6 +79,12 @@ function cai_rmsnorm_dev(ctx: PCaiCtx; x_dev: PSingle; gain_dev: PSingle; y_dev:
 function cai_rope_dev(ctx: PCaiCtx; x_dev: PSingle; tokens: cint; depth: cint; head_dim: cint; position_offset: cint; theta_base: cfloat): cint; cdecl; external CaiLib;
 function cai_swiglu_dev(ctx: PCaiCtx; x_dev: PSingle; y_dev: PSingle; tokens: cint; half_depth: cint): cint; cdecl; external CaiLib;
 function cai_topk_gate_dev(ctx: PCaiCtx; router_logits_dev: PSingle; tokens: cint; n_experts: cint; top_k: cint; renorm: cint; expert_ids_dev: pcint32; gates_dev: PSingle): cint; cdecl; external CaiLib;
+function cai_moe_bank_create(ctx: PCaiCtx; n_experts: cint; hidden: cint; expert_width: cint; type_: cint; out out_: PCaiMoeBank): cint; cdecl; external CaiLib;
+function cai_moe_bank_destroy(b: PCaiMoeBank): cint; cdecl; external CaiLib;
+function cai_moe_bank_upload(b: PCaiMoeBank; expert: cint; which: cint; blocks_host: Pointer): cint; cdecl; external CaiLib;
+function cai_moe_bank_finalize(b: PCaiMoeBank): cint; cdecl; external CaiLib;
+function cai_moe_gate_up_dev(b: PCaiMoeBank; x_dev: PSingle; slot_expert_dev: pcint32; tokens: cint; top_k: cint; hidden_out_dev: PSingle): cint; cdecl; external CaiLib;
+function cai_moe_down_dev(b: PCaiMoeBank; hidden_dev: PSingle; slot_expert_dev: pcint32; slot_gate_dev: PSingle; tokens: cint; top_k: cint; out_dev: PSingle): cint; cdecl; external CaiLib;
 function cai_sdpa_create(ctx: PCaiCtx; q_heads: cint; kv_heads: cint; head_dim: cint; max_ctx: cint; out out_: PCaiSdpa): cint; cdecl; external CaiLib;
 function cai_sdpa_destroy(s: PCaiSdpa): cint; cdecl; external CaiLib;
 function cai_sdpa_reset(s: PCaiSdpa): cint; cdecl; external CaiLib;

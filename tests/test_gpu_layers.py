@@ -136,3 +136,63 @@ def test_fused_sdpa_cache_full_is_an_error(backend):
             sdpa.compute_cached_token(row)
     finally:
         sdpa.end_incremental_decode()
+
+
+@pytest.mark.parametrize("ggml_type,tokens,n_experts,top_k,hidden,width", [
+    (0, 5, 4, 2, 64, 96),            # F32 banks, the shape class of the reference's bank parity test
+    (8, 3, 8, 2, 256, 128),          # Q8_0 banks (Mixtral-like top-2)
+    (8, 9, 16, 8, 128, 64),          # top-8 of 16 (OLMoE-like routing), more pairs than experts
+])
+def test_moe_expert_bank_layer_shim(backend, ggml_type, tokens, n_experts, top_k, hidden, width):
+    """TNNetMoEExpertBankGateUp / Down through the layer-granular entry points against the per-expert reference graph
+    (tests/TestNeuralLayersExtra.pas:7773-7906, tolerance 1e-4): out[t] = sum_j gate_j * down_e(up_e(x) * swish(gate_e(x)))."""
+    from neural_api_b200.backend import MoEExpertBank
+    from oracle import codecs
+    from oracle.forward import router_gates, softmax_row, swiglu
+    rng = np.random.default_rng(tokens * 131 + n_experts)
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    logits = rng.standard_normal((tokens, n_experts)).astype(np.float32)
+    bank = MoEExpertBank(backend, n_experts, hidden, width, ggml_type)
+    mats = []
+    for e in range(n_experts):
+        up = (rng.standard_normal((width, hidden)) * 0.1).astype(np.float32)
+        gate = (rng.standard_normal((width, hidden)) * 0.1).astype(np.float32)
+        down = (rng.standard_normal((hidden, width)) * 0.1).astype(np.float32)
+        if ggml_type == 8:
+            blocks = [codecs.quantize_q8_0(m) for m in (up, gate, down)]
+            up, gate, down = (codecs.dequantize_q8_0(b).reshape(m.shape) for b, m in zip(blocks, (up, gate, down)))
+        else:
+            blocks = [up, gate, down]
+        for which, b in zip(("up", "gate", "down"), blocks):
+            bank.upload(e, which, b)
+        mats.append((up, gate, down))
+    with pytest.raises(Exception):
+        bank.gate_up(backend.to_device(x), backend.to_device(np.zeros(4, np.int32)), tokens, top_k, backend.alloc(16))   # finalize first
+    bank.finalize()
+    ids, gates = backend.topk_gate(logits, top_k, True)
+    want_hidden = np.zeros((tokens * top_k, width), dtype=np.float32)
+    want = np.zeros((tokens, hidden), dtype=np.float64)
+    for t in range(tokens):
+        order, g = router_gates(softmax_row(logits[t]), top_k, True)
+        assert list(order) == list(ids[t])
+        for j, e in enumerate(order):
+            up, gate, down = mats[int(e)]
+            fused = np.concatenate([up @ x[t], gate @ x[t]]).astype(np.float32)
+            h = swiglu(fused, width)
+            want_hidden[t * top_k + j] = h
+            want[t] += float(g[j]) * (down.astype(np.float64) @ h.astype(np.float64))
+    dx, dids, dg = backend.to_device(x), backend.to_device(ids.reshape(-1)), backend.to_device(gates.reshape(-1))
+    dh, dout = backend.alloc(tokens * top_k * width * 4), backend.alloc(tokens * hidden * 4)
+    try:
+        bank.gate_up(dx, dids, tokens, top_k, dh)
+        got_hidden = dh.read(np.float32, tokens * top_k * width).reshape(tokens * top_k, width)
+        assert np.max(np.abs(got_hidden - want_hidden)) < 1e-4
+        bank.down(dh, dids, dg, tokens, top_k, dout)
+        got = dout.read(np.float32, tokens * hidden).reshape(tokens, hidden)
+        assert np.max(np.abs(got - want)) < 1e-4
+        bank.down(dh, dids, dg, tokens, top_k, dout)                     # the output is overwritten, not accumulated
+        assert np.array_equal(dout.read(np.float32, tokens * hidden).reshape(tokens, hidden), got)
+    finally:
+        for b in (dx, dids, dg, dh, dout):
+            b.free()
+        bank.close()

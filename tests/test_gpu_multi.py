@@ -44,7 +44,7 @@ def test_tensor_parallel_matches_single_gpu(world, allreduce):
     assert "TP_GPU_OK" in r.stdout
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_expert_parallel_matches_single_gpu(world):
     if gpu_count() < world:
         pytest.skip("needs %d GPUs" % world)
