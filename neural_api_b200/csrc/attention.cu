@@ -735,6 +735,244 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same attention with the cached rows staged through shared memory by cp.async instead of ordinary loads.
+// The kernel above is a chain of dependent round trips per warp (K pieces, then V rows, then the next tile), so the
+// memory pipe idles between them: 3.5 TB/s at context 8192 (long-scoreboard stall of 5 warps per issue). Here every
+// warp owns a ring of RING_DEPTH stages of 4 KB and the fill runs RING_DEPTH - 1 stages ahead of the arithmetic,
+// straight across tiles: a tile of 32 rows is HD/32 stages of K (32 rows x 32 channels: one contiguous 4 KB run of the
+// block-transposed cache, already [piece][row] for conflict-free lane = row reads) followed by its V rows (whole rows).
+// Needs the block-transposed K cache and rows [0, n) (no sliding window: its first row is not on a block boundary).
+// Same partial format and combine kernel as the kernels above; same fixed merge orders.
+// ---------------------------------------------------------------------------
+constexpr int RING_STAGE = 4096;
+constexpr int RING_DEPTH = 4;
+constexpr int RING_WARPS = 4;
+static __host__ __device__ inline int ring_rings_offset(int G, int HD) { return ((G * HD * 4 + RING_WARPS * G * 32 * 4) + 127) & ~127; }
+static __host__ __device__ inline int ring_smem_bytes(int G, int HD) {
+  const int ring = RING_WARPS * RING_DEPTH * RING_STAGE, merge = RING_WARPS * G * (HD + 2) * 4;
+  return ring_rings_offset(G, HD) + (ring > merge ? ring : merge);
+}
+
+template <int G, int HD>
+__global__ void __launch_bounds__(RING_WARPS * 32, 3) attn_decode_ring_kernel(const AttnParams p) {
+  constexpr int KS = HD / 32;                    // K stages per tile (32 channels each)
+  constexpr int VR = RING_STAGE / (HD * 4);      // rows per V stage
+  constexpr int VG = 32 / VR;                    // V stages per tile
+  constexpr int SPT = KS + VG;                   // stages per tile
+  constexpr int RP = HD / 4;                     // 16-byte pieces per row
+  constexpr int DPL = HD / 32;
+  constexpr int DP2 = DPL / 2;
+  extern __shared__ __align__(128) unsigned char ring_smem[];
+  pdl_trigger();
+  const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_wait();
+  if (!attn_len_ok(p, p.cache_len[b])) return;
+  int base, n;
+  attn_range(p, p.cache_len[b], base, n);              // base == 0 here (the launcher keeps windowed steps off this kernel)
+  const int chunk = attn_chunk(n - base, p.nsplit, p.min_chunk);
+  const int used = (n - base + chunk - 1) / chunk;
+  if (split >= used) return;
+  const int j_begin = base + split * chunk;
+  int j_end = j_begin + chunk; if (j_end > n) j_end = n;
+
+  float* q_s = (float*)ring_smem;                                                   // [G][HD]
+  float* p_s = q_s + G * HD + (size_t)warp * G * 32;                                // this warp's [G][32] probabilities
+  unsigned char* rings = ring_smem + ring_rings_offset(G, HD);
+  float* merge_s = (float*)rings;                                                   // [RING_WARPS][G][HD + 2], after the loop
+  const uint32_t ring_a = (uint32_t)__cvta_generic_to_shared(rings) + (uint32_t)warp * RING_DEPTH * RING_STAGE;
+
+  const int bs = p.seq_index ? p.seq_index[b] : b;
+  const float* kbase = p.k_cache + ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+  const float* vbase = p.v_cache + ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx * HD;
+
+  float m[G], l[G];
+  f32x2_t acc[G][DP2];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DP2; ++d) acc[h][d] = 0ull;
+  }
+  const int n_tiles = (j_end - j_begin + 31) >> 5;
+  const int my_tiles = (warp < n_tiles) ? (n_tiles - warp + RING_WARPS - 1) / RING_WARPS : 0;
+  const int total = my_tiles * SPT;
+  int fs = 0, fslot = 0, rslot = 0;
+  // copies stage `fs` of this warp's sequence into ring slot `fslot` (an empty group past the end)
+  auto issue = [&]() {
+    if (fs < total) {
+      const int ti = fs / SPT, st = fs - ti * SPT;
+      const int tile = j_begin + 32 * (warp + RING_WARPS * ti);
+      const int last = j_end - 1 - tile;
+      const uint32_t dst = ring_a + fslot * RING_STAGE;
+      if (st < KS) {
+        // pieces 8 st .. 8 st + 7 of the tile's 32-row block: [piece][row] in memory and in the stage alike. (Rows past
+        // the filled part of the cache hold whatever was there: their scores are masked and never reach a sum.)
+        const float* srcg = kbase + (size_t)(tile >> 5) * 32 * HD + (size_t)st * 1024;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gv_cp_async16(dst + (j * 32 + lane) * 16, srcg + (j * 32 + lane) * 4, 16u);
+      } else {
+        const int v0 = (st - KS) * VR;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int idx = j * 32 + lane;
+          const int row = v0 + idx / RP, cp = idx - (idx / RP) * RP;
+          const int rc = row <= last ? row : last;
+          gv_cp_async16(dst + idx * 16, vbase + (size_t)(tile + rc) * HD + cp * 4, 16u);
+        }
+      }
+      ++fs;
+    }
+    gv_cp_async_commit();
+    fslot = (fslot + 1 == RING_DEPTH) ? 0 : fslot + 1;
+  };
+  auto next_stage = [&]() -> uint32_t {
+    gv_cp_async_wait_depth(RING_DEPTH);
+    __syncwarp();
+    issue();
+    const uint32_t src = ring_a + rslot * RING_STAGE;
+    rslot = (rslot + 1 == RING_DEPTH) ? 0 : rslot + 1;
+    return src;
+  };
+#pragma unroll 1
+  for (int s = 0; s < RING_DEPTH - 1; ++s) issue();
+  // (the cached rows are on their way: now fetch this step's query rows)
+  const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * HD;
+  for (int i = threadIdx.x; i < G * HD; i += RING_WARPS * 32) q_s[i] = qrow[i];
+  __syncthreads();
+#pragma unroll 1
+  for (int ti = 0; ti < my_tiles; ++ti) {
+    const int tile = j_begin + 32 * (warp + RING_WARPS * ti);
+    const bool valid = tile + lane < j_end;
+    const int last = j_end - 1 - tile;
+    f32x2_t s2[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) s2[h] = 0ull;
+#pragma unroll 1
+    for (int st = 0; st < KS; ++st) {
+      const uint32_t src = next_stage();
+#pragma unroll
+      for (int pc = 0; pc < 8; ++pc) {
+        ulonglong2 k;
+        asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(k.x), "=l"(k.y) : "r"(src + (pc * 32 + lane) * 16));
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const ulonglong2 q = *(const ulonglong2*)(q_s + h * HD + st * 32 + pc * 4);
+          s2[h] = fma2(q.x, k.x, s2[h]);
+          s2[h] = fma2(q.y, k.y, s2[h]);
+        }
+      }
+    }
+    __syncwarp();                                      // the previous tile's probabilities have been consumed
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float sc = valid ? sum2(s2[h]) * p.inv_sqrt_d : -INFINITY;
+      const float mnew = fmaxf(m[h], warp_max(sc));    // finite: the tile holds at least one row
+      const float pj = valid ? expf(sc - mnew) : 0.f;
+      const float psum = warp_sum(pj);
+      const float corr = expf(m[h] - mnew);            // 0 on the first tile (m = -inf)
+      l[h] = l[h] * corr + psum;
+      m[h] = mnew;
+      const f32x2_t corr2 = pack2(corr, corr);
+#pragma unroll
+      for (int d = 0; d < DP2; ++d) acc[h][d] = fma2(acc[h][d], corr2, 0ull);
+      p_s[h * 32 + lane] = pj;
+    }
+    __syncwarp();
+#pragma unroll 1
+    for (int vg = 0; vg < VG; ++vg) {
+      const uint32_t src = next_stage();
+      if (vg * VR > last) continue;                    // a whole stage of masked rows
+#pragma unroll
+      for (int r = 0; r < VR; r += 2) {
+        f32x2_t v0[DP2], v1[DP2];
+        if (DPL == 4) {
+          asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v0[0]), "=l"(v0[DP2 - 1]) : "r"(src + r * (HD * 4) + lane * 16));
+          asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v1[0]), "=l"(v1[DP2 - 1]) : "r"(src + (r + 1) * (HD * 4) + lane * 16));
+        } else {
+          asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v0[0]) : "r"(src + r * (HD * 4) + lane * 8));
+          asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v1[0]) : "r"(src + (r + 1) * (HD * 4) + lane * 8));
+        }
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const float2 pr = *(const float2*)(p_s + h * 32 + vg * VR + r);          // the probabilities of two rows
+          const f32x2_t p0 = pack2(pr.x, pr.x), p1 = pack2(pr.y, pr.y);
+#pragma unroll
+          for (int d = 0; d < DP2; ++d) {
+            acc[h][d] = fma2(p0, v0[d], acc[h][d]);
+            acc[h][d] = fma2(p1, v1[d], acc[h][d]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");       // the rings become the merge area below
+  __syncthreads();
+  // ---- warps -> shared memory -> one state per head (a warp that had no tile contributes m = -inf, l = 0)
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
+    if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
+#pragma unroll
+    for (int d = 0; d < DP2; ++d) {
+      float lo, hi;
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[h][d]));
+      dst[2 + lane * DPL + 2 * d] = lo;
+      dst[2 + lane * DPL + 2 * d + 1] = hi;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int hh = idx / HD, d = idx % HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < RING_WARPS; ++w) mx = fmaxf(mx, merge_s[((size_t)w * G + hh) * (HD + 2)]);
+    float lt = 0.f, at = 0.f;
+#pragma unroll
+    for (int w = 0; w < RING_WARPS; ++w) {
+      const float* src = merge_s + ((size_t)w * G + hh) * (HD + 2);
+      const float sc = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mx);
+      lt += src[1] * sc;
+      at += src[2 + d] * sc;
+    }
+    const int h = g * G + hh;
+    if (used == 1) {
+      p.out[(int64_t)b * p.ldo + (int64_t)h * HD + d] = (lt > 0.f) ? at / lt : 0.f;
+    } else {
+      float* dst = p.partial + (((int64_t)b * p.q_heads + h) * p.nsplit + split) * (HD + 2);
+      if (d == 0) { dst[0] = mx; dst[1] = lt; }
+      dst[2 + d] = at;
+    }
+  }
+}
+
+template <int G, int HD>
+static int launch_ring_one(cai_ctx* ctx, dim3 grid, const AttnParams& p) {
+  static bool configured[64] = {false};
+  const size_t smem = (size_t)ring_smem_bytes(G, HD);
+  const int dev = ctx->device;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    CAI_CUDA(ctx, cudaFuncSetAttribute(attn_decode_ring_kernel<G, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = true;
+  }
+  pdl_launch(ctx, attn_decode_ring_kernel<G, HD>, grid, dim3(RING_WARPS * 32), smem, p);
+  return CAI_OK;
+}
+template <int HD>
+static int launch_ring(cai_ctx* ctx, int G, dim3 grid, const AttnParams& p) {
+  switch (G) {
+    case 1: return launch_ring_one<1, HD>(ctx, grid, p);
+    case 2: return launch_ring_one<2, HD>(ctx, grid, p);
+    case 3: return launch_ring_one<3, HD>(ctx, grid, p);
+    case 4: return launch_ring_one<4, HD>(ctx, grid, p);
+    case 5: return launch_ring_one<5, HD>(ctx, grid, p);
+    case 6: return launch_ring_one<6, HD>(ctx, grid, p);
+    case 7: return launch_ring_one<7, HD>(ctx, grid, p);
+    default: return launch_ring_one<8, HD>(ctx, grid, p);
+  }
+}
+
 template <int HD>
 static void launch_tile_int8(cai_ctx* ctx, int G, dim3 grid, size_t smem, const AttnParams& p) {
   switch (G) {
@@ -874,6 +1112,28 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
   }
   if (a.k_blocked && !(use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8 && (a.max_ctx % 32) == 0))
     return cai_fail(ctx, CAI_ERR_STATE, "internal: block-transposed K cache outside the tiled attention kernel");
+  static const int use_ring = [] { const char* e = getenv("CAI_ATTN_RING"); return (e && *e) ? atoi(e) : 1; }();
+  if (use_tile && use_ring && a.k_blocked && a.window <= 0 && (a.head_dim == 128 || a.head_dim == 64) && G <= 8) {
+    // the cp.async kernel: rows [0, n) of the block-transposed cache. Three CTAs fit an SM (64 KB of rings each), so
+    // the full context is cut into about that many splits: one wave, every warp walking several tiles through its ring
+    p.min_chunk = ATTN_TILE_MIN_CHUNK;
+    {
+      const int64_t lanes = (int64_t)a.batch * a.kv_heads;
+      const int64_t target = (3 * (int64_t)ctx->sm_count) / lanes;
+      if (target >= 1) {
+        const int mc = (int)((((int64_t)a.max_ctx + target - 1) / target + 31) & ~(int64_t)31);
+        if (mc > p.min_chunk) p.min_chunk = mc;
+      }
+    }
+    CAI_TRY(a.head_dim == 128 ? launch_ring<128>(ctx, G, grid, p) : launch_ring<64>(ctx, G, grid, p));
+    CAI_LAUNCHED(ctx);
+    if (a.nsplit > 1) {
+      dim3 cgrid(a.q_heads, a.batch);
+      pdl_launch(ctx, attn_combine_kernel, cgrid, dim3(128), 0, p);
+      CAI_LAUNCHED(ctx);
+    }
+    return CAI_OK;
+  }
   if (use_tile && (a.head_dim == 128 || a.head_dim == 64) && G <= 8) {
     p.min_chunk = ATTN_TILE_MIN_CHUNK;
     const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 64 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
