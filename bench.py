@@ -505,6 +505,9 @@ def main():
                          "GPUs (strong scaling); auto = tp for qwen2.5-32b, ep for olmoe-1b-7b, dp for the others")
     ap.add_argument("--kv", default="f32", choices=["f32", "int8"],
                     help="KV cache: fp32, or the reference's default int8 rows (codes + one fp32 scale per head and position)")
+    ap.add_argument("--fill", default="prefill", choices=["prefill", "zeros"],
+                    help="how the context is produced: by cai_session_prefill from random tokens, or declared over zeroed caches "
+                         "(large batch x context products, where a real prefill takes minutes; decode timing does not depend on the values)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of the `also` block and the CPU baseline")
     ap.add_argument("--layers", type=int, default=None,
                     help="depth cut of the architecture (profiling captures on a small case; the workload string says so)")
@@ -544,7 +547,7 @@ def main():
 
     model = build_model(backend, rank, world, args.workload, ggml_type, seed, mode)
     res = run_workload(backend, dist, rank, world, args.workload, ggml_type, seed, batch, ctx, args.steps, args.warmup, mode=mode,
-                       kv=args.kv, model=model)
+                       kv=args.kv, model=model, fill=args.fill)
     peak, peak_kind = measured_peak_gbs()
     prof = res["profile"]
     lin_ms, lin_n = prof["linear"]

@@ -616,13 +616,19 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
   const float* ksc = p.k_scales + plane;
   const float* vsc = p.v_scales + plane;
 
-  float m[G], l[G], acc[G][DPL];
+  // All multiply-adds are packed pairs (fma.rn.f32x2), as in the fp32 kernel: the codes of two neighbouring channels
+  // become one register pair (two byte-permutes into the 2^23 constant and ONE packed subtract), which nearly halves
+  // the instruction count of a kernel that is bound by instruction issue, not by its quarter-size rows.
+  constexpr int DP2 = DPL / 2;
+  float m[G], l[G];
+  f32x2_t acc[G][DP2];
 #pragma unroll
   for (int h = 0; h < G; ++h) {
     m[h] = -INFINITY; l[h] = 0.f;
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) acc[h][d] = 0.f;
+    for (int d = 0; d < DP2; ++d) acc[h][d] = 0ull;
   }
+  const f32x2_t negc = pack2(-8388736.0f, -8388736.0f);
 
   for (int tile = j_begin + warp * 32; tile < j_end; tile += ATTN_WARPS * 32) {
     const int j = tile + lane;
@@ -633,26 +639,29 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
     const int kstep = p.k_blocked ? 32 : 1;
     const float kscale = ksc[jr] * p.inv_sqrt_d;
     const float vscale = vsc[jr];
-    float s[G];
+    f32x2_t s2[G];
 #pragma unroll
-    for (int h = 0; h < G; ++h) s[h] = 0.f;
+    for (int h = 0; h < G; ++h) s2[h] = 0ull;
     uint4 kw[HD / 16];
 #pragma unroll
     for (int i = 0; i < HD / 16; ++i) kw[i] = krow[i * kstep];   // the whole row of codes in flight
 #pragma unroll
     for (int i = 0; i < HD / 16; ++i) {
       const uint32_t w4[4] = {kw[i].x ^ 0x80808080u, kw[i].y ^ 0x80808080u, kw[i].z ^ 0x80808080u, kw[i].w ^ 0x80808080u};
-      float kf[16];
+      f32x2_t kp[8];
 #pragma unroll
-      for (int t = 0; t < 16; ++t) kf[t] = s8_to_float(w4[t >> 2], t & 3);
+      for (int t = 0; t < 4; ++t) {
+        kp[2 * t] = add2(pack2(__uint_as_float(__byte_perm(w4[t], 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(w4[t], 0x4B000000u, 0x7651u))), negc);
+        kp[2 * t + 1] = add2(pack2(__uint_as_float(__byte_perm(w4[t], 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(w4[t], 0x4B000000u, 0x7653u))), negc);
+      }
 #pragma unroll
       for (int h = 0; h < G; ++h) {
-        const float4* q4 = (const float4*)(q_s + h * HD + i * 16);
+        const ulonglong2* q2 = (const ulonglong2*)(q_s + h * HD + i * 16);
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          const float4 q = q4[t];
-          s[h] = fmaf(q.x, kf[4 * t + 0], s[h]); s[h] = fmaf(q.y, kf[4 * t + 1], s[h]);
-          s[h] = fmaf(q.z, kf[4 * t + 2], s[h]); s[h] = fmaf(q.w, kf[4 * t + 3], s[h]);
+          const ulonglong2 q = q2[t];
+          s2[h] = fma2(q.x, kp[2 * t], s2[h]);
+          s2[h] = fma2(q.y, kp[2 * t + 1], s2[h]);
         }
       }
     }
@@ -668,36 +677,39 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
     __syncwarp();
 #pragma unroll
     for (int h = 0; h < G; ++h) {
-      const float sc = valid ? s[h] * kscale : -INFINITY;
+      const float sc = valid ? sum2(s2[h]) * kscale : -INFINITY;
       const float mnew = fmaxf(m[h], warp_max(sc));
       const float pj = valid ? expf(sc - mnew) : 0.f;
       const float psum = warp_sum(pj);
       const float corr = expf(m[h] - mnew);
       l[h] = l[h] * corr + psum;
       m[h] = mnew;
+      const f32x2_t corr2 = pack2(corr, corr);
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) acc[h][d] *= corr;
+      for (int d = 0; d < DP2; ++d) acc[h][d] = fma2(acc[h][d], corr2, 0ull);
       p_s[h * 32 + lane] = pj * vscale;                 // the value scale rides with the probability
     }
     __syncwarp();
 #pragma unroll
     for (int t4 = 0; t4 < 32; t4 += 4) {
       if (t4 > last) break;
-      float vf[4][DPL];
+      f32x2_t vf[4][DP2];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const uint32_t w = vw[t4 + t] ^ 0x80808080u;
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) vf[t][d] = s8_to_float(w, d);
+        vf[t][0] = add2(pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7651u))), negc);
+        if (DP2 == 2)
+          vf[t][DP2 - 1] = add2(pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7653u))), negc);
       }
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         const float4 pr = *(const float4*)(p_s + h * 32 + t4);
+        const f32x2_t p0 = pack2(pr.x, pr.x), p1 = pack2(pr.y, pr.y), p2 = pack2(pr.z, pr.z), p3 = pack2(pr.w, pr.w);
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) {
-          float a = acc[h][d];
-          a = fmaf(pr.x, vf[0][d], a); a = fmaf(pr.y, vf[1][d], a);
-          a = fmaf(pr.z, vf[2][d], a); a = fmaf(pr.w, vf[3][d], a);
+        for (int d = 0; d < DP2; ++d) {
+          f32x2_t a = acc[h][d];
+          a = fma2(p0, vf[0][d], a); a = fma2(p1, vf[1][d], a);
+          a = fma2(p2, vf[2][d], a); a = fma2(p3, vf[3][d], a);
           acc[h][d] = a;
         }
       }
@@ -708,7 +720,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
     float* dst = merge_s + ((size_t)warp * G + h) * (HD + 2);
     if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) dst[2 + lane * DPL + d] = acc[h][d];
+    for (int d = 0; d < DP2; ++d) {
+      float lo, hi;
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[h][d]));
+      dst[2 + lane * DPL + 2 * d] = lo;
+      dst[2 + lane * DPL + 2 * d + 1] = hi;
+    }
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
