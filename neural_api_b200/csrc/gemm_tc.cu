@@ -482,9 +482,12 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     if (!row_ok) my_row = p.n - 1;
     const uint4* srow = (const uint4*)(w_scales + my_row * p.sstride) + (chunk0 >> 2);     // 8 scales (4 chunks) per 16 bytes
     uint4 sc_cur = make_uint4(0, 0, 0, 0), sc_next = srow[0];
-    float acc[NCOL];
+    // the running sums of a thread's NCOL batch columns, as packed pairs: one fma.rn.f32x2 adds d * accumulator for two
+    // columns (each lane an IEEE fused multiply-add, so the result equals the one-column form bit for bit)
+    static_assert(NCOL % 2 == 0, "batch columns per thread come in pairs");
+    f32x2_t acc2[NCOL / 2];
 #pragma unroll
-    for (int j = 0; j < NCOL; ++j) acc[j] = 0.f;
+    for (int j = 0; j < NCOL / 2; ++j) acc2[j] = 0ull;
     bool alive = true;
     const uint32_t bar_mma = tc_smem_u32(&mma_bar[0]), bar_a = tc_smem_u32(&a_ready[0]);
     const uint32_t t_lane = tmem_d + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(cg * NCOL);
@@ -544,11 +547,12 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
       const float d0 = __half2float(__ushort_as_half((unsigned short)(dw & 0xFFFF)));
       const float d1 = __half2float(__ushort_as_half((unsigned short)(dw >> 16)));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const f32x2_t dd0 = pack2(d0, d0), dd1 = pack2(d1, d1);
 #pragma unroll
-      for (int j = 0; j < NCOL; ++j) acc[j] = fmaf(d0, __uint_as_float(r0[j]), acc[j]);
+      for (int j = 0; j < NCOL / 2; ++j) acc2[j] = fma2(dd0, pack2(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1])), acc2[j]);
       if (2 * cc + 1 < n_blocks) {
 #pragma unroll
-        for (int j = 0; j < NCOL; ++j) acc[j] = fmaf(d1, __uint_as_float(r1[j]), acc[j]);
+        for (int j = 0; j < NCOL / 2; ++j) acc2[j] = fma2(dd1, pack2(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1])), acc2[j]);
       }
       // orders the loads above before the arrival that lets an MMA warp overwrite these accumulators
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -629,6 +633,9 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     tc_cp_async_wait(0);
 
     // ---- epilogue: thread = weight row, acc[j] = batch column cg * NCOL + j ----
+    float acc[NCOL];
+#pragma unroll
+    for (int j = 0; j < NCOL / 2; ++j) asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[2 * j]), "=f"(acc[2 * j + 1]) : "l"(acc2[j]));
     if (row_ok && p.ksplit > 1) {
       float* part = p.part + (size_t)blockIdx.y * (size_t)p.batch * (size_t)p.n + my_row;
 #pragma unroll

@@ -44,6 +44,8 @@ constexpr int SK_STAGE = SK_RPW * (512 + 32);        // bytes of one ring stage:
 constexpr int SK_XU = 4;                             // float4 pieces per thread of a normed row (hidden <= 8192)
 constexpr int SK_FOLD_FLOATS = 49152;                // splits x q_width up to which the O staging merges the splits itself
 constexpr int SK_FOLD_MAX_CHUNK = 512;               // ... and the longest split worth accepting for that (one 32-row tile per warp)
+constexpr int SK_FOLD_MAX_SPLITS = 8;                // ... and the most splits: the fold walks them one after the other in every CTA
+                                                     // (measured: 64 splits cost the O staging 13 us, the merge phase + its barrier 5)
 constexpr int SK_MIN_CHUNK = 64;                     // fewest cached rows of a context split
 enum { MK_QKV = 0, MK_O = 1, MK_GU = 2, MK_DOWN = 3, MK_HEAD = 4 };
 
@@ -792,14 +794,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     // Fewer, longer splits when that lets the O staging merge them itself: a phase of this kernel costs microseconds
     // whatever it moves, so the separate merge phase (and its grid barrier) is worth more than the last bit of
     // parallelism over the context, as long as a split stays within one 32-row tile per warp.
-    const int max_fold = SK_FOLD_FLOATS / P.qw;
+    int max_fold = SK_FOLD_FLOATS / P.qw;
+    if (max_fold > SK_FOLD_MAX_SPLITS) max_fold = SK_FOLD_MAX_SPLITS;
     if (max_fold >= 1) {
       const int c2 = (((n + max_fold - 1) / max_fold) + 31) & ~31;
       if (c2 > chunk && c2 <= SK_FOLD_MAX_CHUNK) chunk = c2;
     }
   }
   const int used = (n + chunk - 1) / chunk;
-  const bool fold = used * P.qw <= SK_FOLD_FLOATS;
+  const bool fold = used <= SK_FOLD_MAX_SPLITS && used * P.qw <= SK_FOLD_FLOATS;
   const bool tp = P.tp.world > 1;
 
   for (int l = 0; l < P.layers; ++l) {
@@ -1213,10 +1216,21 @@ int step_plan_create(cai_ctx* ctx, const StepSetup& s, StepPlan** out) {
   p->smem = (size_t)max_smem;                          // one CTA per SM in any case: the attention phase uses what the rings leave
   {
     const int avail = max_smem - P.off_xs;
+    // Tiles of 32 rows an item holds at full context. Few of them (tensor-parallel shards: few KV heads, so many short
+    // splits): a handful of warps with rings deep enough to have ALL stages of a tile in flight at once, because the
+    // phase is then one round trip to memory; many: every warp, as deep as fits.
+    int chunk_full = (s.max_ctx + P.nsplit_max - 1) / P.nsplit_max;
+    if (chunk_full < SK_MIN_CHUNK) chunk_full = SK_MIN_CHUNK;
+    const int tiles_item = (chunk_full + 31) / 32;
     int aw = SK_WARPS, ad = 0;
-    for (; aw >= 4; aw >>= 1) {
-      for (ad = 4; ad >= 2; --ad) if (at_smem_bytes(G, HD, aw, ad) <= avail) break;
-      if (ad >= 3 || (aw == 4 && ad >= 2)) break;
+    if (tiles_item <= 4) {
+      aw = 4;
+      for (ad = 8; ad >= 2; --ad) if (at_smem_bytes(G, HD, aw, ad) <= avail) break;
+    } else {
+      for (; aw >= 4; aw >>= 1) {
+        for (ad = 4; ad >= 2; --ad) if (at_smem_bytes(G, HD, aw, ad) <= avail) break;
+        if (ad >= 3 || (aw == 4 && ad >= 2)) break;
+      }
     }
     if (aw < 4 || ad < 2) { delete p; return CAI_ERR_UNSUPPORTED; }
     aw = env_int("CAI_STEP_AT_WARPS", aw); ad = env_int("CAI_STEP_AT_DEPTH", ad);
