@@ -443,18 +443,20 @@ def run_linear(args):
     the L2 cache, activations and outputs resident on the device. One step = one pass over every copy."""
     from neural_api_b200.backend import CudaBackend, DotProductSharedKernel
     k, n = (int(v) for v in args.kn.lower().split("x"))
-    ggml_type = {"q8_0": 8, "q4_0": 2}[args.type]
+    # type -> (ggml id, block bytes, block elements, byte offsets of the block's fp16 scales)
+    ggml_type, bb, be, f16_at = {"q8_0": (8, 34, 32, (0,)), "q4_0": (2, 18, 32, (0,)), "q4_k": (12, 144, 256, (0, 2)),
+                                 "q5_k": (13, 176, 256, (0, 2)), "q6_k": (14, 210, 256, (208,))}[args.type]
     batch = args.batch or 1
     backend = CudaBackend(0)
     rng = np.random.default_rng(0)
-    nblk = n * k // 32
-    bb = 34 if ggml_type == 8 else 18
+    nblk = n * k // be
     wbytes = nblk * bb
     copies = max(2, int((300 << 20) // wbytes) + 1)
     lins = []
     for c in range(copies):
         blk = rng.integers(0, 256, (nblk, bb), dtype=np.uint8)
-        blk[:, :2] = np.asarray(rng.uniform(0.001, 0.05, nblk), dtype=np.float16).view(np.uint8).reshape(-1, 2)
+        for off in f16_at:
+            blk[:, off:off + 2] = np.asarray(rng.uniform(0.001, 0.05, nblk), dtype=np.float16).view(np.uint8).reshape(-1, 2)
         lin = DotProductSharedKernel(backend)
         lin.prepare_for_compute_quant(ggml_type, blk.reshape(-1), n, k)
         lins.append(lin)
@@ -490,7 +492,7 @@ def run_linear(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kn", default="5120x27648", help="linear workload: KxN")
-    ap.add_argument("--type", default="q8_0", choices=["q8_0", "q4_0"], help="linear workload: block type")
+    ap.add_argument("--type", default="q8_0", choices=["q8_0", "q4_0", "q4_k", "q5_k", "q6_k"], help="linear workload: block type")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)

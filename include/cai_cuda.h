@@ -51,6 +51,12 @@ enum {
   CAI_TYPE_F16 = 1,
   CAI_TYPE_Q4_0 = 2,  /* 18-byte blocks of 32: fp16 d, 16 nibble bytes; x = d*(nib-8)  (neuralgguf.pas:822-845) */
   CAI_TYPE_Q8_0 = 8,  /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
+  /* K-quants that stay resident as the file's raw super-blocks of 256 (rows are whole super-blocks, K % 256 == 0) and run
+     on their own dequant-fused GEMV; weights are formed exactly as the reference's decoders form them
+     (DequantizeQ4K / Q5K / Q6K, neuralgguf.pas:474-738). Batches run in groups of up to 4 rows per pass. */
+  CAI_TYPE_Q4_K = 12, /* 144-byte super-blocks */
+  CAI_TYPE_Q5_K = 13, /* 176-byte super-blocks */
+  CAI_TYPE_Q6_K = 14, /* 210-byte super-blocks */
   /* Load-time formats: accepted by cai_model_upload_tensor, cai_linear_create, cai_dequantize and the GGUF loader; decoded
      on the device to fp32 when they arrive, as the reference's reader does (DecodeGGMLSpan, neuralgguf.pas:1471-1523), and
      resident as F32 (or as CAI_TYPE_I8ROW under cai_model_set_int8_weights). Block rules: neuralgguf.pas:448-945. */
@@ -59,9 +65,6 @@ enum {
   CAI_TYPE_Q5_1 = 7,  /* 24-byte blocks of 32 */
   CAI_TYPE_Q2_K = 10, /* 84-byte super-blocks of 256 */
   CAI_TYPE_Q3_K = 11, /* 110-byte super-blocks of 256 */
-  CAI_TYPE_Q4_K = 12, /* 144-byte super-blocks of 256 */
-  CAI_TYPE_Q5_K = 13, /* 176-byte super-blocks of 256 */
-  CAI_TYPE_Q6_K = 14, /* 210-byte super-blocks of 256 */
   CAI_TYPE_I8ROW = 124, /* the reference's own int8 weights (what ChatTerminal runs by default): int8 codes [N][K] and ONE fp32
                          scale per output row, scale = maxabs/127, code = Round(v * (1/maxabs) * 127) with round-half-to-even
                          (TNNetVolume.QuantizeInt8 / MaxAbsFinite, neural/neuralvolume.pas:12471-12562); the product is the raw

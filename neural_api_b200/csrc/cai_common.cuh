@@ -123,6 +123,7 @@ struct QWeight {
 
 size_t cai_type_row_bytes(int type, int64_t k);   // bytes of one GGUF row of k elements
 bool cai_type_supported(int type);
+bool cai_type_is_kquant(int type);                 // Q4_K / Q5_K / Q6_K: resident as the file's raw super-blocks
 
 int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k);
 void qweight_free(QWeight* w);

@@ -16,6 +16,7 @@
 // memory in a fixed order. Activations are staged once per CTA in shared memory
 // when they fit.
 #include "gemv_common.cuh"
+#include "gguf_blocks.cuh"
 #include <stdlib.h>
 
 // RING = false: a lane keeps the next stride's codes in registers while it consumes the current one.
@@ -460,6 +461,87 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
   gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
 }
 
+// K-quant path (Q4_K / Q5_K / Q6_K resident as the file's raw super-blocks): a warp owns a pair of rows and walks
+// their super-blocks; per super-block a lane decodes eight weights of each row EXACTLY as the reference's decoder
+// forms them (d * sc rounded, times the code, rounded, minus dmin * mn: neural/neuralgguf.pas:448-738) and multiplies
+// them with its eight activations, fetched once for both rows. Traffic is the file's 4.5 / 5.5 / 6.6 bits per weight
+// instead of the 32 of a tensor decoded at load. Same epilogues as the other GEMVs.
+template <int TYPE, int NB>
+__global__ void __launch_bounds__(256) gemv_kq_kernel(const GemvParams p) {
+  constexpr int BB = ggufdev::KQ<TYPE>::BB;
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps_per_cta = blockDim.x >> 5;
+  const uint8_t* codes = (const uint8_t*)p.codes;
+  const float* bias = p.bias;
+  int b0 = blockIdx.y * NB;
+  int pair = 0;
+  const float* x;
+  if (p.expert_ids) {
+    pair = blockIdx.y;
+    const int e = p.expert_ids[pair];
+    codes = (const uint8_t*)p.bank_codes[e];
+    bias = nullptr;
+    x = p.x + (int64_t)(pair / p.x_row_div) * p.ldx;
+    b0 = 0;
+  } else {
+    x = p.x + (int64_t)b0 * p.ldx;
+  }
+  constexpr int RPW = 2;
+  const int64_t gidx = (int64_t)blockIdx.x * warps_per_cta + warp;
+  const bool sw = (p.epi == EPI_SWIGLU);
+  const int64_t half = p.n >> 1;
+  const int64_t unit0 = sw ? gidx : gidx * RPW;
+  if (unit0 >= (sw ? half : p.n)) return;
+  int64_t rows[RPW];
+  if (sw) { rows[0] = unit0; rows[1] = half + unit0; }
+  else { rows[0] = unit0; rows[1] = (unit0 + 1 < p.n) ? unit0 + 1 : unit0; }
+  const int64_t n_sb = p.k >> 8;
+  const int64_t row_bytes = n_sb * BB;
+  int ea, eb;
+  ggufdev::kq_lane_elements<TYPE>(lane, ea, eb);
+  float acc[RPW][NB];
+#pragma unroll
+  for (int r = 0; r < RPW; ++r)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
+  for (int64_t sb = 0; sb < n_sb; ++sb) {
+    float4 xa[NB], xb[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      const int bb = (b0 + b < p.batch) ? b : 0;
+      const float* xr = x + (int64_t)bb * p.ldx + (sb << 8);
+      xa[b] = *(const float4*)(xr + ea);
+      xb[b] = *(const float4*)(xr + eb);
+    }
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      float w[8];
+      ggufdev::kq_decode8<TYPE>(codes + rows[r] * row_bytes + sb * BB, lane, w);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float a = acc[r][b];
+        a = fmaf(w[0], xa[b].x, a); a = fmaf(w[1], xa[b].y, a); a = fmaf(w[2], xa[b].z, a); a = fmaf(w[3], xa[b].w, a);
+        a = fmaf(w[4], xb[b].x, a); a = fmaf(w[5], xb[b].y, a); a = fmaf(w[6], xb[b].z, a); a = fmaf(w[7], xb[b].w, a);
+        acc[r][b] = a;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RPW; ++r)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) acc[r][b] = warp_sum(acc[r][b]);
+  gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
+}
+
+template <int TYPE>
+static void launch_kq(cai_ctx* ctx, int nb, dim3 grid, int threads, const GemvParams& p) {
+  if (nb == 4) pdl_launch(ctx, gemv_kq_kernel<TYPE, 4>, grid, dim3(threads), 0, p);
+  else pdl_launch(ctx, gemv_kq_kernel<TYPE, 1>, grid, dim3(threads), 0, p);
+}
+
 int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type);      // gemm_tc.cu
 
 int env_int(const char* name, int dflt) {
@@ -573,7 +655,13 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     const int nb = indexed ? 1 : (a.batch >= 4 ? 4 : 1);
     dim3 grid((unsigned)((groups + wpc - 1) / wpc), indexed ? a.batch : (unsigned)((a.batch + nb - 1) / nb));
     if (a.norm_gain) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: fused RMSNorm needs quantized weights");
-    if (nb == 4) pdl_launch(ctx, gemv_generic_kernel<4>, grid, dim3(threads), 0, p, w->type);
+    if (cai_type_is_kquant(w->type)) {
+      if ((a.ldx % 4) || ((uintptr_t)a.x % 16)) return cai_fail(ctx, CAI_ERR_INVALID, "linear: activations must be 16-byte aligned with ldx %% 4 == 0");
+      if (w->type == CAI_TYPE_Q4_K) launch_kq<CAI_TYPE_Q4_K>(ctx, nb, grid, threads, p);
+      else if (w->type == CAI_TYPE_Q5_K) launch_kq<CAI_TYPE_Q5_K>(ctx, nb, grid, threads, p);
+      else launch_kq<CAI_TYPE_Q6_K>(ctx, nb, grid, threads, p);
+    }
+    else if (nb == 4) pdl_launch(ctx, gemv_generic_kernel<4>, grid, dim3(threads), 0, p, w->type);
     else pdl_launch(ctx, gemv_generic_kernel<1>, grid, dim3(threads), 0, p, w->type);
     CAI_LAUNCHED(ctx);
     return CAI_OK;

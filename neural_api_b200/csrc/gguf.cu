@@ -6,6 +6,7 @@
 //   decoders      DequantizeQ4K ... DequantizeQ5_1      neural/neuralgguf.pas:448-945
 //   model loader  BuildLlamaFromGGUFEx, BuildFromGGUFEx neural/neuralpretrained.pas:17484-17876
 #include "cai_common.cuh"
+#include "gguf_blocks.cuh"
 
 #include <cerrno>
 #include <cstdarg>
@@ -46,111 +47,8 @@ static const char* ggml_type_name(int t) {
   }
 }
 
-// ---------------------------------------------------------------------------
-// device decoders: one thread per output element; every product and sum is rounded on its own (no fused
-// multiply-add), which is how the reference's single-precision expressions evaluate
-// ---------------------------------------------------------------------------
 namespace {
-
-__device__ __forceinline__ float f16_at(const uint8_t* p) {
-  const unsigned short bits = (unsigned short)(p[0] | (p[1] << 8));
-  return __half2float(__ushort_as_half(bits));
-}
-
-// 6-bit scale and min j of a Q4_K / Q5_K super-block (DequantizeQ4KScaleMin, neural/neuralgguf.pas:448-465)
-__device__ __forceinline__ void scale_min_k4(const uint8_t* s, int j, int* sc, int* mn) {
-  if (j < 4) {
-    *sc = s[j] & 0x3F;
-    *mn = s[j + 4] & 0x3F;
-  } else {
-    const int d = s[j - 4], m = s[j], md = s[j + 4];
-    *sc = (md & 0x0F) | ((d >> 2) & 0x30);
-    *mn = (md >> 4) | ((m >> 2) & 0x30);
-  }
-}
-
-__device__ __forceinline__ int legacy_nibble(const uint8_t* qs, int e) {     // LegacyNibble, :811-817
-  return e < 16 ? (qs[e] & 0x0F) : (qs[e - 16] >> 4);
-}
-
-__device__ float decode_element(int type, const uint8_t* __restrict__ blk, int e) {
-  switch (type) {
-    case 2: {                                                                 // Q4_0, :822-845
-      const float d = f16_at(blk);
-      return __fmul_rn(d, (float)(legacy_nibble(blk + 2, e) - 8));
-    }
-    case 3: {                                                                 // Q4_1, :850-874
-      const float d = f16_at(blk), m = f16_at(blk + 2);
-      return __fadd_rn(__fmul_rn(d, (float)legacy_nibble(blk + 4, e)), m);
-    }
-    case 6: {                                                                 // Q5_0, :879-908
-      const float d = f16_at(blk);
-      const unsigned qh = blk[2] | (blk[3] << 8) | (blk[4] << 16) | ((unsigned)blk[5] << 24);
-      const int q = legacy_nibble(blk + 6, e) | (int)(((qh >> e) & 1u) << 4);
-      return __fmul_rn(d, (float)(q - 16));
-    }
-    case 7: {                                                                 // Q5_1, :913-945
-      const float d = f16_at(blk), m = f16_at(blk + 2);
-      const unsigned qh = blk[4] | (blk[5] << 8) | (blk[6] << 16) | ((unsigned)blk[7] << 24);
-      const int q = legacy_nibble(blk + 8, e) | (int)(((qh >> e) & 1u) << 4);
-      return __fadd_rn(__fmul_rn(d, (float)q), m);
-    }
-    case 8: {                                                                 // Q8_0, :1487-1503
-      const float d = f16_at(blk);
-      return __fmul_rn((float)(int8_t)blk[2 + e], d);
-    }
-    case 10: {                                                                // Q2_K, :606-660
-      const int sb = e >> 4;
-      const int scb = blk[sb];
-      const float d = f16_at(blk + 80), dmin = f16_at(blk + 82);
-      const float dl = __fmul_rn(d, (float)(scb & 0x0F)), ml = __fmul_rn(dmin, (float)(scb >> 4));
-      const int c = e >> 7, s = (e & 127) >> 5, p = e & 31;
-      const int q = (blk[16 + c * 32 + p] >> (2 * s)) & 3;
-      return __fsub_rn(__fmul_rn(dl, (float)q), ml);
-    }
-    case 11: {                                                                // Q3_K, :762-806
-      const int j = e >> 4;
-      const uint8_t* sp = blk + 96;
-      int lsc = sp[j & 7];
-      lsc = j < 8 ? (lsc & 0x0F) : ((lsc >> 4) & 0x0F);
-      const int hsc = (sp[8 + (j & 3)] >> ((j >> 2) * 2)) & 3;
-      const int scale = (int)(int8_t)(uint8_t)(lsc | (hsc << 4)) - 32;
-      const float dl = __fmul_rn(f16_at(blk + 108), (float)scale);
-      const int h0 = e >> 7, s = (e & 127) >> 5, p = e & 31;
-      const int ql = (blk[32 + h0 * 32 + p] >> (2 * s)) & 3;
-      const int hb = (blk[p] >> (e >> 5)) & 1;
-      return __fmul_rn(dl, (float)(ql - ((hb ^ 1) << 2)));
-    }
-    case 12: {                                                                // Q4_K, :474-520
-      const int j = e >> 5, i = e & 31;
-      int sc, mn;
-      scale_min_k4(blk + 4, j, &sc, &mn);
-      const float dl = __fmul_rn(f16_at(blk), (float)sc), ml = __fmul_rn(f16_at(blk + 2), (float)mn);
-      const int pb = blk[16 + (j >> 1) * 32 + i];
-      const int q = (j & 1) ? (pb >> 4) : (pb & 0x0F);
-      return __fsub_rn(__fmul_rn(dl, (float)q), ml);
-    }
-    case 13: {                                                                // Q5_K, :536-590
-      const int j = e >> 5, i = e & 31;
-      int sc, mn;
-      scale_min_k4(blk + 4, j, &sc, &mn);
-      const float dl = __fmul_rn(f16_at(blk), (float)sc), ml = __fmul_rn(f16_at(blk + 2), (float)mn);
-      const int pb = blk[48 + (j >> 1) * 32 + i];
-      const int q = ((j & 1) ? (pb >> 4) : (pb & 0x0F)) | (((blk[16 + i] >> j) & 1) << 4);
-      return __fsub_rn(__fmul_rn(dl, (float)q), ml);
-    }
-    case 14: {                                                                // Q6_K, :676-738
-      const int g = e >> 4;
-      const float dl = __fmul_rn(f16_at(blk + 208), (float)(int8_t)blk[192 + g]);
-      const int hi = e >> 7, r = e & 127;
-      int ql = blk[hi * 64 + (e & 63)];
-      ql = r < 64 ? (ql & 0x0F) : (ql >> 4);
-      const int qh = (blk[128 + hi * 32 + (e & 31)] >> ((r >> 5) * 2)) & 3;
-      return __fmul_rn(dl, (float)((ql | (qh << 4)) - 32));
-    }
-    default: return 0.f;
-  }
-}
+using namespace ggufdev;
 
 __global__ void gguf_decode_kernel(int type, int block_bytes, int block_elems, const uint8_t* __restrict__ raw, int64_t n_elems,
                                    float* __restrict__ out) {
@@ -734,5 +632,6 @@ int gguf_upload_decoded(cai_model* m, cai_ctx* ctx, const char* hf_name, int typ
 }
 
 bool gguf_type_needs_decode(int type) {
-  return type == 3 || type == 6 || type == 7 || (type >= 10 && type <= 14);
+  // Q4_K, Q5_K and Q6_K stay resident as raw super-blocks (the K-quant GEMV reads them); the others become fp32
+  return type == 3 || type == 6 || type == 7 || type == 10 || type == 11;
 }

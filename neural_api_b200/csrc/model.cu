@@ -206,9 +206,20 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
   CAI_TRY(cai_bind(ctx));
   if (!hf_name || !data_host) return cai_fail(ctx, CAI_ERR_INVALID, "cai_model_upload_tensor: null argument");
   if (m->sessions > 0) return cai_fail(ctx, CAI_ERR_STATE, "weights are immutable while sessions exist");
-  if (gguf_type_needs_decode(type)) return gguf_upload_decoded(m, ctx, hf_name, type, data_host, rows, cols, interleave_head_dim);
   const cai_llama_config& c = m->cfg;
   const TName t = parse_name(hf_name);
+  {
+    // Formats no kernel reads directly are decoded to fp32 here and continue as F32 tensors. The resident K-quants
+    // take the same route when the int8 switch is on (int8 rows are made from fp32 rows) and when a tensor-parallel
+    // column split of O / down would cut through a 256-element super-block.
+    bool decode = gguf_type_needs_decode(type);
+    if (cai_type_is_kquant(type)) {
+      if (m->int8_weights) decode = true;
+      if (m->tp_size > 1 && ((t.kind == T_O && (m->qw_l % 256)) || (t.kind == T_DOWN && (m->inter_l % 256)))) decode = true;
+      if (rows == 1 || t.kind == T_ROUTER) decode = true;         // vectors are fp32 on the device; the router stays on the plain path
+    }
+    if (decode) return gguf_upload_decoded(m, ctx, hf_name, type, data_host, rows, cols, interleave_head_dim);
+  }
   if (t.kind == T_IGNORE) return CAI_OK;
   if (t.kind == T_UNKNOWN) return cai_fail(ctx, CAI_ERR_INVALID, "unknown tensor name '%s'", hf_name);
   if (t.layer >= c.layers) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': layer %d of %d", hf_name, t.layer, c.layers);

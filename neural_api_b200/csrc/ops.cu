@@ -1,6 +1,7 @@
 // Small per-token operators of the decode step: embedding gather, RMSNorm, RoPE,
 // SwiGLU, router softmax/top-k, argmax, MoE combine.
 #include "cai_common.cuh"
+#include "gguf_blocks.cuh"
 #include <math.h>
 
 // ---------------------------------------------------------------------------
@@ -28,6 +29,10 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
       v = __half2float(scales[tok * sstride + c / CAI_QK]) * (float)(nib - 8);
     } else if (type == CAI_TYPE_I8ROW) v = rscale[tok] * (float)((int)((const uint8_t*)codes)[i] - 128);
     else if (type == CAI_TYPE_F16) v = __half2float(((const __half*)codes)[i]);
+    else if (type == CAI_TYPE_Q4_K || type == CAI_TYPE_Q5_K || type == CAI_TYPE_Q6_K) {
+      const int bb = type == CAI_TYPE_Q4_K ? 144 : (type == CAI_TYPE_Q5_K ? 176 : 210);
+      v = ggufdev::decode_element(type, (const uint8_t*)codes + (i >> 8) * bb, (int)(i & 255));
+    }
     else v = ((const float*)codes)[i];
     out[(int64_t)b * ld + c] = v;
   }

@@ -2,6 +2,7 @@
 // the inverse (download as GGUF blocks), bit-exact dequantization, and on-device
 // synthetic initialisation with the GGUF quantizer rules.
 #include "cai_common.cuh"
+#include "gguf_blocks.cuh"
 
 size_t cai_type_row_bytes(int type, int64_t k) {
   switch (type) {
@@ -10,11 +11,17 @@ size_t cai_type_row_bytes(int type, int64_t k) {
     case CAI_TYPE_Q8_0: return (size_t)(k / CAI_QK) * CAI_Q8_0_BLOCK_BYTES;
     case CAI_TYPE_Q4_0: return (size_t)(k / CAI_QK) * CAI_Q4_0_BLOCK_BYTES;
     case CAI_TYPE_I8ROW: return (size_t)k + 4;      // codes, then the row's fp32 scale
+    case CAI_TYPE_Q4_K: return (size_t)(k / 256) * 144;
+    case CAI_TYPE_Q5_K: return (size_t)(k / 256) * 176;
+    case CAI_TYPE_Q6_K: return (size_t)(k / 256) * 210;
   }
   return 0;
 }
+// K-quants that stay resident as the file's raw super-blocks (rows of K / 256 blocks, no separate scale plane)
+bool cai_type_is_kquant(int type) { return type == CAI_TYPE_Q4_K || type == CAI_TYPE_Q5_K || type == CAI_TYPE_Q6_K; }
 bool cai_type_supported(int type) {
-  return type == CAI_TYPE_F32 || type == CAI_TYPE_F16 || type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0 || type == CAI_TYPE_I8ROW;
+  return type == CAI_TYPE_F32 || type == CAI_TYPE_F16 || type == CAI_TYPE_Q8_0 || type == CAI_TYPE_Q4_0 || type == CAI_TYPE_I8ROW ||
+         cai_type_is_kquant(type);
 }
 size_t QWeight::row_code_bytes() const {
   switch (type) {
@@ -23,6 +30,7 @@ size_t QWeight::row_code_bytes() const {
     case CAI_TYPE_Q8_0: return (size_t)k;
     case CAI_TYPE_I8ROW: return (size_t)k;
     case CAI_TYPE_Q4_0: return (size_t)k / 2;
+    case CAI_TYPE_Q4_K: case CAI_TYPE_Q5_K: case CAI_TYPE_Q6_K: return cai_type_row_bytes(type, k);
   }
   return 0;
 }
@@ -44,6 +52,8 @@ int qweight_alloc(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t k) {
     return cai_fail(ctx, CAI_ERR_INVALID, "quantized rows need a multiple of 32 columns, got %lld", (long long)k);
   if (type == CAI_TYPE_I8ROW && (k % 16) != 0)
     return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 rows need a multiple of 16 columns, got %lld", (long long)k);
+  if (cai_type_is_kquant(type) && (k % 256) != 0)
+    return cai_fail(ctx, CAI_ERR_INVALID, "K-quant rows are whole super-blocks of 256 columns, got %lld", (long long)k);
   qweight_free(w);
   w->type = type; w->n = n; w->k = k; w->owns = true; w->present = false;
   // scale rows padded to 8 halves so that every row (and every 256-column tile of it) starts on a
@@ -211,6 +221,8 @@ int qweight_upload(cai_ctx* ctx, QWeight* w, const void* host, int64_t src_rows,
                     (long long)row0, (long long)w->n, (long long)col0, (long long)w->k, (long long)src_rows, (long long)src_cols);
   const bool quant = (w->type == CAI_TYPE_Q8_0 || w->type == CAI_TYPE_Q4_0);
   if (quant && (col0 % CAI_QK || src_cols % CAI_QK)) return cai_fail(ctx, CAI_ERR_INVALID, "column slice must align to 32-element blocks");
+  if (cai_type_is_kquant(w->type) && (col0 % 256 || src_cols % 256))
+    return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "column slice of a K-quant tensor must align to 256-element super-blocks");
   if (interleave_head_dim > 0 && (interleave_head_dim % 2 || src_rows % interleave_head_dim))
     return cai_fail(ctx, CAI_ERR_INVALID, "row interleave needs rows %% head_dim == 0 and an even head_dim");
   const bool i8row = w->type == CAI_TYPE_I8ROW;
@@ -364,6 +376,9 @@ __global__ void dequant_kernel(int type, const void* __restrict__ codes, const _
       v = rscale[i / k] * (float)((int)((const uint8_t*)codes)[i] - 128);      // DequantizeInt8: code * row scale
     } else if (type == CAI_TYPE_F16) {
       v = __half2float(((const __half*)codes)[i]);
+    } else if (type == CAI_TYPE_Q4_K || type == CAI_TYPE_Q5_K || type == CAI_TYPE_Q6_K) {
+      const int bb = type == CAI_TYPE_Q4_K ? 144 : (type == CAI_TYPE_Q5_K ? 176 : 210);
+      v = ggufdev::decode_element(type, (const uint8_t*)codes + (i >> 8) * bb, (int)(i & 255));    // rows are whole super-blocks
     } else {
       v = ((const float*)codes)[i];
     }

@@ -163,7 +163,7 @@ def _random_blocks(rng, gtype, n_elems, scale):
 def _kquant_qwen2_file(path, seed=11):
     """A two-layer qwen2 file whose matrices use every load-time format; rows of 256 columns so that K-quants fit."""
     rng = np.random.default_rng(seed)
-    H, I, L, NH, NKV, V = 256, 512, 2, 4, 2, 96
+    H, I, L, NH, NKV, V = 256, 512, 3, 4, 2, 96
     hd = H // NH
     tensors = [("token_embd.weight", [H, V], 12, _random_blocks(rng, 12, V * H, 0.05)),
                ("output_norm.weight", [H], 1, (1 + 0.1 * rng.standard_normal(H)).astype(np.float16).view(np.uint8)),
@@ -177,6 +177,8 @@ def _kquant_qwen2_file(path, seed=11):
         for i, (n, dims, t) in enumerate(kinds):
             if l == 1:                                   # second layer: rotate the formats, add the directly resident ones
                 t = [14, 8, 2, 12, 13, 10, 11][i]
+            if l == 2:                                   # third layer: whole groups in one resident K-quant (fused q|k|v and up|gate)
+                t = [14, 14, 14, 13, 13, 13, 12][i]
             tensors.append((pre + n, dims, t, _random_blocks(rng, t, dims[0] * dims[1], 0.04)))
         for n, width in (("attn_q.bias", NH * hd), ("attn_k.bias", NKV * hd), ("attn_v.bias", NKV * hd)):
             tensors.append((pre + n, [width], 0, (0.1 * rng.standard_normal(width)).astype(np.float32)))
@@ -200,11 +202,19 @@ def test_kquant_and_legacy_formats_from_file_to_logits(backend, tmp_path):
             rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
             assert np.all(np.isfinite(logits))
             assert np.max(np.abs(logits[0] - ref)) < 1e-3 * max(rms, 1.0)
-        # the decoded tensors are resident as F32, bit-equal to the reader's decode (one of each family)
+        # the load-time formats are resident as F32, bit-equal to the reader's decode (one of each family)
         for hf, rows, cols in (("model.layers.0.self_attn.o_proj.weight", 256, 256), ("model.layers.1.mlp.down_proj.weight", 256, 512)):
             buf, ty, r, c = model.read_tensor(hf, rows * cols * 4)
             assert (ty, r, c) == (0, rows, cols)
             assert np.array_equal(buf[:rows * cols * 4].view(np.float32).reshape(rows, cols), oracle_tensor(p, hf))
+        # Q4_K / Q5_K / Q6_K stay resident as the file's own super-blocks
+        g = GF.GGUFFile(p)
+        for name, hf, tid in (("blk.0.ffn_down.weight", "model.layers.0.mlp.down_proj.weight", 12),
+                              ("blk.2.attn_output.weight", "model.layers.2.self_attn.o_proj.weight", 13),
+                              ("output.weight", "lm_head.weight", 14)):
+            raw = g.raw(name)
+            buf, ty, r, c = model.read_tensor(hf, raw.size)
+            assert ty == tid and np.array_equal(buf[:raw.size], raw)
     finally:
         sess.close()
         model.close()
@@ -240,19 +250,26 @@ def test_int8_switch_on_a_kquant_file(backend, tmp_path):
         s32.close(); s8.close(); m32.close(); m8.close()
 
 
-def test_linear_layer_from_kquant_blocks(backend):
-    """cai_linear_create with a load-time format: decoded once, resident as F32, product = fp32 dot over the decoded rows."""
-    rng = np.random.default_rng(9)
-    n, k = 96, 512
-    raw = _random_blocks(rng, 12, n * k, 0.05)
-    w = GF.dequantize_q4_k(raw).reshape(n, k)
+@pytest.mark.parametrize("gtype", [12, 13, 14, 11, 7])
+@pytest.mark.parametrize("batch", [1, 3, 6])
+def test_linear_layer_from_kquant_blocks(backend, gtype, batch):
+    """cai_linear_create on raw GGUF blocks. Q4_K / Q5_K / Q6_K stay resident and run the K-quant GEMV; the other formats
+    are decoded once and run as F32. Either way the product is the fp32 dot over the reference's decoded rows, and the
+    resident weights dequantize to those rows bit for bit."""
+    rng = np.random.default_rng(9 + gtype)
+    n, k = 97, 768                                   # an odd row count: the last warp's second row repeats its first
+    raw = _random_blocks(rng, gtype, n * k, 0.05)
+    w = GF.decode_span(gtype, raw).reshape(n, k)
+    bias = rng.standard_normal(n).astype(np.float32)
     lin = DotProductSharedKernel(backend)
-    lin.prepare_for_compute_quant(12, raw, n, k)
-    x = rng.standard_normal((2, k)).astype(np.float32)
+    lin.prepare_for_compute_quant(gtype, raw, n, k, bias=bias)
+    assert np.array_equal(lin.dequantize_weights().view(np.uint32), w.view(np.uint32))
+    assert lin.weight_bytes() == (raw.size if gtype in (12, 13, 14) else n * k * 4)
+    x = rng.standard_normal((batch, k)).astype(np.float32)
     lin.compute_quant(x)
     y = lin.finish_and_load_result()
-    ref = x.astype(np.float64) @ w.astype(np.float64).T
-    assert np.max(np.abs(y - ref)) < 1e-4 * max(1.0, float(np.max(np.abs(ref))))
+    ref = x.astype(np.float64) @ w.astype(np.float64).T + bias
+    assert np.max(np.abs(y - ref)) < 2e-5 * float(np.sqrt(np.mean(ref ** 2)))
     lin.unprepare_for_compute()
 
 

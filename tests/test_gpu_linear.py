@@ -180,7 +180,7 @@ def test_errors_are_statuses_not_crashes(backend):
         lin.prepare_for_compute_quant(codecs.GGML_Q8_0, np.zeros(34, dtype=np.uint8), 1, 33)
     with pytest.raises(CaiError, match="not supported"):
         lin.prepare_for_compute_quant(30, np.zeros(64, dtype=np.uint8), 1, 32)     # BF16: no reader decodes it
-    with pytest.raises(CaiError, match="whole number"):
+    with pytest.raises(CaiError, match="whole super-blocks"):
         lin.prepare_for_compute_quant(12, np.zeros(144, dtype=np.uint8), 1, 32)    # Q4_K rows are super-blocks of 256
     with pytest.raises(CaiError):
         backend.alloc(1 << 50)                                                     # rejected before cudaMalloc
