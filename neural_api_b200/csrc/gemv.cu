@@ -462,10 +462,25 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
 }
 
 // K-quant path (Q4_K / Q5_K / Q6_K resident as the file's raw super-blocks): a warp owns a pair of rows and walks
-// their super-blocks; per super-block a lane decodes eight weights of each row EXACTLY as the reference's decoder
-// forms them (d * sc rounded, times the code, rounded, minus dmin * mn: neural/neuralgguf.pas:448-738) and multiplies
-// them with its eight activations, fetched once for both rows. Traffic is the file's 4.5 / 5.5 / 6.6 bits per weight
-// instead of the 32 of a tensor decoded at load. Same epilogues as the other GEMVs.
+// their super-blocks; per super-block a lane holds two runs of four codes of each row. As for Q8_0 / Q4_0 the block
+// arithmetic is regrouped so that the scale meets a sum instead of every code:
+//     sum_t (dl * code_t - ml) * x_t  =  dl * (sum_t code_t * x_t)  -  ml * (sum_t x_t),
+// with dl = d * sc and ml = dmin * mn rounded once each, exactly as the reference's decoders form them
+// (neural/neuralgguf.pas:448-738); codes become floats exactly (byte-permute into the 2^23 constant), the sums are
+// packed fp32 FMAs, and sum_t x_t is shared by the two rows. Traffic is the file's 4.5 / 5.5 / 6.6 bits per weight instead of the 32 of a tensor
+// decoded at load. Same epilogues as the other GEMVs.
+// four codes (one per byte of w, minus `bias`) times four activations -> sum
+template <int TYPE>
+__device__ __forceinline__ float kq_dot4(uint32_t w, const float4& x) {
+  const float c = -(8388608.0f + ggufdev::KQBias<TYPE>::value);
+  const f32x2_t negc = pack2(c, c);
+  const f32x2_t f01 = add2(pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7651u))), negc);
+  const f32x2_t f23 = add2(pack2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7652u)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7653u))), negc);
+  f32x2_t s = fma2(f01, pack2(x.x, x.y), 0ull);
+  s = fma2(f23, pack2(x.z, x.w), s);
+  return sum2(s);
+}
+
 template <int TYPE, int NB>
 __global__ void __launch_bounds__(256) gemv_kq_kernel(const GemvParams p) {
   constexpr int BB = ggufdev::KQ<TYPE>::BB;
@@ -507,25 +522,49 @@ __global__ void __launch_bounds__(256) gemv_kq_kernel(const GemvParams p) {
   for (int r = 0; r < RPW; ++r)
 #pragma unroll
     for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-  for (int64_t sb = 0; sb < n_sb; ++sb) {
-    float4 xa[NB], xb[NB];
+  const uint8_t* rowp[RPW];
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      const int bb = (b0 + b < p.batch) ? b : 0;
-      const float* xr = x + (int64_t)bb * p.ldx + (sb << 8);
-      xa[b] = *(const float4*)(xr + ea);
-      xb[b] = *(const float4*)(xr + eb);
+  for (int r = 0; r < RPW; ++r) rowp[r] = codes + rows[r] * row_bytes;
+  // U super-blocks of both rows are requested together (a lane's share of a super-block is ~36 bytes: one at a time
+  // leaves the memory pipe nearly empty), then consumed
+  constexpr int U = (NB == 1) ? 4 : 2;
+  for (int64_t sb0 = 0; sb0 < n_sb; sb0 += U) {
+    ggufdev::KQRaw raw[U][RPW];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t sb = (sb0 + u < n_sb) ? sb0 + u : n_sb - 1;
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) ggufdev::kq_fetch<TYPE>(rowp[r] + sb * BB, lane, raw[u][r]);
     }
 #pragma unroll
-    for (int r = 0; r < RPW; ++r) {
-      float w[8];
-      ggufdev::kq_decode8<TYPE>(codes + rows[r] * row_bytes + sb * BB, lane, w);
+    for (int u = 0; u < U; ++u) {
+      if (sb0 + u < n_sb) {
+        const int64_t sb = sb0 + u;
+        float4 xa[NB], xb[NB];
+        float sxa[NB], sxb[NB];
 #pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        float a = acc[r][b];
-        a = fmaf(w[0], xa[b].x, a); a = fmaf(w[1], xa[b].y, a); a = fmaf(w[2], xa[b].z, a); a = fmaf(w[3], xa[b].w, a);
-        a = fmaf(w[4], xb[b].x, a); a = fmaf(w[5], xb[b].y, a); a = fmaf(w[6], xb[b].z, a); a = fmaf(w[7], xb[b].w, a);
-        acc[r][b] = a;
+        for (int b = 0; b < NB; ++b) {
+          const int bb = (b0 + b < p.batch) ? b : 0;
+          const float* xr = x + (int64_t)bb * p.ldx + (sb << 8);
+          xa[b] = *(const float4*)(xr + ea);
+          xb[b] = *(const float4*)(xr + eb);
+          sxa[b] = (xa[b].x + xa[b].y) + (xa[b].z + xa[b].w);
+          sxb[b] = (xb[b].x + xb[b].y) + (xb[b].z + xb[b].w);
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          uint32_t wa, wb;
+          float dla, mla, dlb, mlb;
+          ggufdev::kq_runs<TYPE>(raw[u][r], lane, wa, wb, dla, mla, dlb, mlb);
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            float a = acc[r][b];
+            a = fmaf(dla, kq_dot4<TYPE>(wa, xa[b]), a);
+            a = fmaf(dlb, kq_dot4<TYPE>(wb, xb[b]), a);
+            if (TYPE != CAI_TYPE_Q6_K) { a = fmaf(-mla, sxa[b], a); a = fmaf(-mlb, sxb[b], a); }
+            acc[r][b] = a;
+          }
+        }
       }
     }
   }

@@ -128,49 +128,74 @@ __device__ __forceinline__ void kq_lane_elements(int lane, int& ea, int& eb) {
   else { ea = (lane >> 3) * 64 + (lane & 7) * 4; eb = ea + 32; }
 }
 
+// The bytes of a super-block a lane needs, fetched ahead of their use (the GEMV requests the next super-block's before
+// it computes on the current one's): Q4_K / Q5_K blocks are 16-byte aligned, so the 16-byte head (d, dmin, the twelve
+// packed scale bytes) is one load; Q6_K blocks (210 bytes) are only 2-byte aligned and are read in 16-bit pieces.
+struct KQRaw {
+  uint4 head;          // Q4_K / Q5_K: bytes 0..15.  Q6_K: x = the two group scales (bytes), y = d (fp16 bits)
+  uint32_t q;          // the lane's four code bytes
+  uint32_t h;          // Q5_K: its four bytes of the fifth-bit plane.  Q6_K: its four bytes of the high-bit plane
+};
+
 template <int TYPE>
-__device__ __forceinline__ void kq_decode8(const uint8_t* __restrict__ blk, int lane, float (&w)[8]) {
+__device__ __forceinline__ void kq_fetch(const uint8_t* __restrict__ blk, int lane, KQRaw& r) {
   if (TYPE == 12 || TYPE == 13) {
-    const int c = lane >> 3, i0 = (lane & 7) * 4;
-    const float d = f16_at(blk), dmin = f16_at(blk + 2);
-    int sc0, mn0, sc1, mn1;
-    scale_min_k4(blk + 4, 2 * c, &sc0, &mn0);
-    scale_min_k4(blk + 4, 2 * c + 1, &sc1, &mn1);
-    const float dl0 = __fmul_rn(d, (float)sc0), ml0 = __fmul_rn(dmin, (float)mn0);
-    const float dl1 = __fmul_rn(d, (float)sc1), ml1 = __fmul_rn(dmin, (float)mn1);
-    const uint32_t q = *(const uint32_t*)(blk + (TYPE == 12 ? 16 : 48) + 4 * lane);          // blocks are 16-byte aligned
-    uint32_t h = 0;
-    if (TYPE == 13) h = *(const uint32_t*)(blk + 16 + i0);                                    // the fifth-bit plane, bytes i0 .. i0 + 3
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      int lo = (q >> (8 * t)) & 0x0F, hi = (q >> (8 * t + 4)) & 0x0F;
-      if (TYPE == 13) {
-        const uint32_t hb = (h >> (8 * t)) & 0xFF;
-        lo |= ((hb >> (2 * c)) & 1) << 4;
-        hi |= ((hb >> (2 * c + 1)) & 1) << 4;
-      }
-      w[t] = __fsub_rn(__fmul_rn(dl0, (float)lo), ml0);
-      w[4 + t] = __fsub_rn(__fmul_rn(dl1, (float)hi), ml1);
-    }
+    r.head = *(const uint4*)blk;
+    r.q = *(const uint32_t*)(blk + (TYPE == 12 ? 16 : 48) + 4 * lane);
+    r.h = (TYPE == 13) ? *(const uint32_t*)(blk + 16 + (lane & 7) * 4) : 0u;
   } else {
     const int half = lane >> 4, pos = (lane & 15) * 4;
-    const float d = f16_at(blk + 208);
     const int g = half * 8 + (pos >> 4);
-    const float dl0 = __fmul_rn(d, (float)(int8_t)blk[192 + g]), dl1 = __fmul_rn(d, (float)(int8_t)blk[192 + g + 4]);
-    // 210-byte blocks are only 2-byte aligned: two 16-bit loads per word
     const unsigned short* ql16 = (const unsigned short*)(blk + half * 64 + pos);
     const unsigned short* qh16 = (const unsigned short*)(blk + 128 + half * 32 + (pos & 31));
-    const uint32_t ql = (uint32_t)ql16[0] | ((uint32_t)ql16[1] << 16);
-    const uint32_t qh = (uint32_t)qh16[0] | ((uint32_t)qh16[1] << 16);
-    const int sh0 = 2 * (pos >> 5), sh1 = sh0 + 4;
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const uint32_t lb = (ql >> (8 * t)) & 0xFF, hb = (qh >> (8 * t)) & 0xFF;
-      const int q0 = (int)((lb & 0x0F) | (((hb >> sh0) & 3) << 4)) - 32;
-      const int q1 = (int)((lb >> 4) | (((hb >> sh1) & 3) << 4)) - 32;
-      w[t] = __fmul_rn(dl0, (float)q0);
-      w[4 + t] = __fmul_rn(dl1, (float)q1);
+    r.q = (uint32_t)ql16[0] | ((uint32_t)ql16[1] << 16);
+    r.h = (uint32_t)qh16[0] | ((uint32_t)qh16[1] << 16);
+    r.head.x = (uint32_t)blk[192 + g] | ((uint32_t)blk[192 + g + 4] << 8);
+    r.head.y = (uint32_t)*(const unsigned short*)(blk + 208);
+    r.head.z = r.head.w = 0u;
+  }
+}
+
+// The lane's two runs of a super-block as what the GEMV multiplies with: four codes per run packed one per byte (wa, wb),
+// the run's scale dl = d * sc (rounded once, as the reference forms it) and its offset ml = dmin * mn (0 for Q6_K, whose
+// codes are centred by `KQ_BIAS` instead):  weight = dl * (code - KQ_BIAS) - ml.
+template <int TYPE> struct KQBias { static constexpr float value = 0.f; };
+template <> struct KQBias<14> { static constexpr float value = 32.f; };
+
+template <int TYPE>
+__device__ __forceinline__ void kq_runs(const KQRaw& r, int lane, uint32_t& wa, uint32_t& wb, float& dla, float& mla, float& dlb, float& mlb) {
+  if (TYPE == 12 || TYPE == 13) {
+    const int c = lane >> 3;
+    const float d = __half2float(__ushort_as_half((unsigned short)(r.head.x & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(r.head.x >> 16)));
+    // sub-blocks 2c and 2c+1 (DequantizeQ4KScaleMin): both come from byte pair (2c & 3, (2c & 3) + 1) of the three
+    // packed groups; sub-blocks 0..3 use six bits of the first two groups, 4..7 splice the third group in
+    const int sh = (2 * c & 3) * 8;
+    const uint32_t dd = r.head.y >> sh, mm = r.head.z >> sh, md = r.head.w >> sh;
+    int sc0, mn0, sc1, mn1;
+    if (c < 2) {
+      sc0 = dd & 0x3F; mn0 = mm & 0x3F;
+      sc1 = (dd >> 8) & 0x3F; mn1 = (mm >> 8) & 0x3F;
+    } else {
+      sc0 = (md & 0x0F) | ((dd >> 2) & 0x30); mn0 = ((md >> 4) & 0x0F) | ((mm >> 2) & 0x30);
+      sc1 = ((md >> 8) & 0x0F) | ((dd >> 10) & 0x30); mn1 = ((md >> 12) & 0x0F) | ((mm >> 10) & 0x30);
     }
+    dla = __fmul_rn(d, (float)sc0); mla = __fmul_rn(dmin, (float)mn0);
+    dlb = __fmul_rn(d, (float)sc1); mlb = __fmul_rn(dmin, (float)mn1);
+    wa = r.q & 0x0F0F0F0Fu;
+    wb = (r.q >> 4) & 0x0F0F0F0Fu;
+    if (TYPE == 13) {                                    // the fifth bit of sub-block j is bit j of the plane's byte
+      wa |= ((r.h >> (2 * c)) & 0x01010101u) << 4;
+      wb |= ((r.h >> (2 * c + 1)) & 0x01010101u) << 4;
+    }
+  } else {
+    const int pos = (lane & 15) * 4;
+    const float d = __half2float(__ushort_as_half((unsigned short)r.head.y));
+    dla = __fmul_rn(d, (float)(int8_t)(r.head.x & 0xFF)); dlb = __fmul_rn(d, (float)(int8_t)((r.head.x >> 8) & 0xFF));
+    mla = mlb = 0.f;
+    const int sh0 = 2 * (pos >> 5), sh1 = sh0 + 4;
+    wa = (r.q & 0x0F0F0F0Fu) | (((r.h >> sh0) & 0x03030303u) << 4);
+    wb = ((r.q >> 4) & 0x0F0F0F0Fu) | (((r.h >> sh1) & 0x03030303u) << 4);
   }
 }
 
