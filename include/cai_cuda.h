@@ -52,8 +52,11 @@ enum {
   CAI_TYPE_Q4_0 = 2,  /* 18-byte blocks of 32: fp16 d, 16 nibble bytes; x = d*(nib-8)  (neuralgguf.pas:822-845) */
   CAI_TYPE_Q8_0 = 8,  /* 34-byte blocks of 32: fp16 d, 32 int8;          x = d*q        (neuralgguf.pas:1487-1503) */
   /* K-quants that stay resident as the file's raw super-blocks of 256 (rows are whole super-blocks, K % 256 == 0) and run
-     on their own dequant-fused GEMV; weights are formed exactly as the reference's decoders form them
-     (DequantizeQ4K / Q5K / Q6K, neuralgguf.pas:474-738). Batches run in groups of up to 4 rows per pass. */
+     on their own dequant-fused GEMV. The resident blocks dequantize exactly as the reference's decoders do
+     (DequantizeQ4K / Q5K / Q6K, neuralgguf.pas:474-738: cai_linear_dequantize, cai_model_read_tensor); the product
+     regroups a run's arithmetic as dl * sum(code * x) - ml * sum(x) with dl = d * sc and ml = dmin * mn rounded as the
+     decoder rounds them, the way the Q8_0 / Q4_0 kernels apply a block scale to a sum. Batches run in groups of up to
+     4 rows per pass. */
   CAI_TYPE_Q4_K = 12, /* 144-byte super-blocks */
   CAI_TYPE_Q5_K = 13, /* 176-byte super-blocks */
   CAI_TYPE_Q6_K = 14, /* 210-byte super-blocks */

@@ -219,6 +219,8 @@ __global__ void tc_split_x_kernel(const float* __restrict__ x, int64_t ldx, int 
                                   float* __restrict__ row_unscale, const int32_t* __restrict__ tile_pairs, int x_row_div,
                                   size_t xp_tile_bytes) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();                     // the previous GEMM may still be reading the tile buffer this kernel rewrites
   const int b = blockIdx.x;
   // grouped mode: tile blockIdx.y gathers its rows through tile_pairs (row of pair p = p / x_row_div)
   int src_row = b;
@@ -359,6 +361,11 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Programmatic dependent launch: this kernel may start while its predecessor drains. Tensor-memory allocation,
+  // barrier set-up and the first stages of weight codes do not depend on it; every role waits (pdl_wait) before it
+  // touches what the predecessor wrote (activation tiles, row factors, residual, the tile lists of a grouped call).
+  pdl_trigger();
+  if (p.tile_expert) pdl_wait();
   // operands: the call's matrix, or in grouped mode the expert matrix and activation tile of tile blockIdx.z
   const unsigned char* w_codes = p.codes;
   const __half* w_scales = p.scales;
@@ -421,6 +428,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     // the MMAs that read it are done.
     // =====================================================================================
     if (lane == 0) {
+      pdl_wait();                                           // the tiles are the split kernel's output
       const uint32_t bar_f = tc_smem_u32(&b_full[0]), bar_e = tc_smem_u32(&b_empty[0]);
       int slot = 0;
       uint32_t eparity = 1;                                 // parity of the "emptied" phase awaited: none on the first lap
@@ -559,6 +567,7 @@ __global__ void __launch_bounds__(TcPlan<NB>::THREADS, TcPlan<NB>::MIN_CTAS) gem
     };
 
     for (int j = 0; j < TC_RAW_STAGES; ++j) issue_raw(j);
+    pdl_wait();                                             // (weights are constants: their first stages are already on the way)
     // this thread's copies of stage 0 have landed; after the barrier, every worker's
     tc_cp_async_wait(TC_RAW_STAGES - 1);
     asm volatile("bar.sync 1, %0;" ::"n"(W) : "memory");
@@ -667,13 +676,15 @@ template <int TYPE, int NB>
 cudaError_t tc_launch(cai_ctx* ctx, const TcParams& p, int grid, int tiles = 1) {
   cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcPlan<NB>::SMEM);
   if (e == cudaSuccess)
-    gemm_tc_kernel<TYPE, NB><<<dim3((unsigned)grid, (unsigned)p.ksplit, (unsigned)tiles), TcPlan<NB>::THREADS, TcPlan<NB>::SMEM, ctx->stream>>>(p);
+    e = pdl_launch(ctx, gemm_tc_kernel<TYPE, NB>, dim3((unsigned)grid, (unsigned)p.ksplit, (unsigned)tiles), dim3(TcPlan<NB>::THREADS), (size_t)TcPlan<NB>::SMEM, p);
   return e;
 }
 
 // y[b][row] = act(sum over splits of part[s][b][row] + bias) (+ residual), splits added in index order
 __global__ void tc_reduce_kernel(const float* __restrict__ part, int ksplit, int batch, int64_t n, const float* __restrict__ bias,
                                  const float* __restrict__ resid, float* __restrict__ y, int64_t ldy, int act, int epi) {
+  pdl_trigger();
+  pdl_wait();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (int64_t)batch * n) return;
   const int64_t b = i / n, row = i - b * n;
@@ -735,8 +746,8 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
   const int n_chunks = (int)((g.k + TC_KC - 1) / TC_KC);
   {
     const int threads = g.k >= 2048 ? 512 : 256;
-    tc_split_x_kernel<<<nb, threads, 0, ctx->stream>>>(g.x, g.ldx, g.batch, nb, g.k, n_chunks, 2, g.norm_gain, g.norm_eps,
-                                                       (unsigned char*)ctx->tc_xp + 256, (float*)ctx->tc_xp, nullptr, 1, 0);
+    pdl_launch(ctx, tc_split_x_kernel, dim3(nb), dim3(threads), 0, g.x, g.ldx, g.batch, nb, g.k, n_chunks, 2, g.norm_gain, g.norm_eps,
+               (unsigned char*)ctx->tc_xp + 256, (float*)ctx->tc_xp, (const int32_t*)nullptr, 1, (size_t)0);
     CAI_LAUNCHED(ctx);
   }
   const int grid = (int)((g.n + TC_M - 1) / TC_M);
@@ -766,7 +777,7 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
   CAI_LAUNCHED(ctx);
   if (p.ksplit > 1) {
     const int64_t total = (int64_t)g.batch * g.n;
-    tc_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p.part, p.ksplit, g.batch, g.n, g.bias, g.resid, g.y, g.ldy, g.act, g.epi);
+    pdl_launch(ctx, tc_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (const float*)p.part, p.ksplit, g.batch, g.n, g.bias, g.resid, g.y, g.ldy, g.act, g.epi);
     CAI_LAUNCHED(ctx);
   }
   return CAI_OK;
@@ -794,8 +805,8 @@ int gemm_tc_launch_grouped(cai_ctx* ctx, int type, const void* const* bank_codes
   p.xp_tile_bytes = gemm_tc_group_tile_bytes(k);
   const int n_chunks = (int)((k + TC_KC - 1) / TC_KC);
   p.ksplit = 1; p.chunks_per_split = n_chunks;
-  tc_split_x_kernel<<<dim3(16, (unsigned)n_tiles), k >= 2048 ? 512 : 256, 0, ctx->stream>>>(x, ldx, 16, 16, k, n_chunks, 2, nullptr, 0.f, (unsigned char*)xp_tiles,
-                                                                                  unscale_tiles, tile_pairs, x_row_div, p.xp_tile_bytes);
+  pdl_launch(ctx, tc_split_x_kernel, dim3(16, (unsigned)n_tiles), dim3(k >= 2048 ? 512 : 256), 0, x, ldx, 16, 16, k, n_chunks, 2, (const float*)nullptr, 0.f,
+             (unsigned char*)xp_tiles, unscale_tiles, tile_pairs, x_row_div, p.xp_tile_bytes);
   CAI_LAUNCHED(ctx);
   const int grid = (int)((n + TC_M - 1) / TC_M);
   const cudaError_t e = (type == CAI_TYPE_Q8_0) ? tc_launch<CAI_TYPE_Q8_0, 16>(ctx, p, grid, n_tiles) : tc_launch<CAI_TYPE_Q4_0, 16>(ctx, p, grid, n_tiles);

@@ -440,7 +440,39 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
   for (int r = 0; r < RPW; ++r)
 #pragma unroll
     for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-  for (int64_t i = lane; i < p.k; i += 32) {
+  // rows whose width and addresses allow it go four elements per lane and step (16-byte loads of fp32 rows, 8-byte
+  // loads of fp16 rows): a K-quant file's mixed-format [q|k|v] group, decoded to fp32 at load, is a large matrix
+  int64_t i0 = 0;
+  const bool vec4 = (p.k % 4) == 0 && (p.ldx % 4) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)codes % 16) == 0;
+  if (vec4) {
+    const int64_t k4 = p.k >> 2;
+    for (int64_t i4 = lane; i4 < k4; i4 += 32) {
+      float4 w[RPW];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        if (type == CAI_TYPE_F16) {
+          const uint2 h = *(const uint2*)((const __half*)codes + rows[r] * p.k + 4 * i4);
+          const float2 a = __half22float2(*(const __half2*)&h.x), c = __half22float2(*(const __half2*)&h.y);
+          w[r] = make_float4(a.x, a.y, c.x, c.y);
+        } else {
+          w[r] = *(const float4*)((const float*)codes + rows[r] * p.k + 4 * i4);
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int bb = (b0 + b < p.batch) ? b : 0;
+        const float4 xv = *(const float4*)(x + (int64_t)bb * p.ldx + 4 * i4);
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          float a = acc[r][b];
+          a = fmaf(w[r].x, xv.x, a); a = fmaf(w[r].y, xv.y, a); a = fmaf(w[r].z, xv.z, a); a = fmaf(w[r].w, xv.w, a);
+          acc[r][b] = a;
+        }
+      }
+    }
+    i0 = p.k;
+  }
+  for (int64_t i = i0 + lane; i < p.k; i += 32) {
     float w[RPW];
 #pragma unroll
     for (int r = 0; r < RPW; ++r)
