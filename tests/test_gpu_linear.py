@@ -94,7 +94,7 @@ def test_forced_tensor_core_path_any_batch(backend, ggml_type, b):
         lin.set_path(2)
         before = backend.launch_count()
         lin.compute_quant(x)
-        assert backend.launch_count() - before == 2          # activation split + GEMM
+        assert backend.launch_count() - before in (2, 3)     # activation split + GEMM (+ the sum over K ranges)
         y = lin.finish_and_load_result()
         ref = x.astype(np.float64) @ w.astype(np.float64).T
         for i in range(b):                                   # per row: each has its own scale
