@@ -751,14 +751,15 @@ int gemm_tc_launch(cai_ctx* ctx, const GemvParams& g, int type) {
     CAI_LAUNCHED(ctx);
   }
   const int grid = (int)((g.n + TC_M - 1) / TC_M);
-  // Few row tiles and a long K (down / output projections): split K over blockIdx.y so that the launch fills the
-  // machine (two CTAs per SM), each range a multiple of 8 chunks.
+  // Fewer row tiles than SMs: split K over blockIdx.y so that the launch fills the machine (two CTAs per SM), each
+  // range a multiple of 8 chunks. (Matrices with 75..148 row tiles were left whole at first; splitting them in two
+  // measured 4 % on the TinyLlama step although it adds the launch that sums the ranges.)
   p.ksplit = 1;
   p.chunks_per_split = n_chunks;
   // (ranges of 8 chunks, the shortest the stage geometry allows, measured 8 % faster than 16 on the 2048-wide matrices
   // of the TinyLlama shape: those launches are latency chains, and a CTA's chain is as long as its K range)
   const int min_cps = env_int("CAI_TC_MINCPS", 8);
-  if (grid * 2 <= ctx->sm_count && (size_t)g.n <= TC_PART_ROWS && n_chunks >= 2 * min_cps) {
+  if (grid <= ctx->sm_count && (size_t)g.n <= TC_PART_ROWS && n_chunks >= 2 * min_cps) {
     int ks = (2 * ctx->sm_count) / grid;
     if (ks > TC_MAX_KSPLIT) ks = TC_MAX_KSPLIT;
     ks = env_int("CAI_TC_KSPLIT", ks);
