@@ -275,6 +275,11 @@ int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out);
 void comm_ar_destroy(cai_ctx* ctx, cai_tp_ar* ar);                                 // collective
 float* comm_ar_slot(cai_tp_ar* ar, int site);
 int comm_ar_reduce(cai_ctx* ctx, cai_tp_ar* ar, int site, int64_t n, const float* resid, float* out);
+// expert-parallel dispatch / combine over the same slots (comm.cu)
+int comm_ep_dispatch(cai_ctx* ctx, cai_tp_ar* ar, int site, int tokens, int stride, int hidden, int top_k, int expert_lo, int expert_hi,
+                     float* all, int32_t* ids_out, float* gates_out);
+int comm_ep_combine(cai_ctx* ctx, cai_tp_ar* ar, int site, int tokens, int hidden, int top_k, int experts_per_rank, const int32_t* my_ids,
+                    float* x, int64_t ldx);
 void comm_destroy(cai_ctx* ctx);
 
 // ---------------------------------------------------------------------------

@@ -130,6 +130,195 @@ __global__ void tp_allreduce_kernel(const ArParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Expert-parallel exchange over the same peer-mapped slots: the dispatch and the combine of a mixture-of-experts
+// layer as two kernels instead of two library collectives.
+//   dispatch  every rank has packed its tokens' rows [hidden | top_k ids | top_k gates] into its own slot. After the
+//             arrival exchange (same sequence-numbered flags as above) a rank pulls, from every peer, the ids and
+//             gates of all tokens and the hidden row of those tokens that route to at least one of ITS experts - the
+//             others never reach a tile, so their rows stay unread (at 8 ranks and top-8 of 64 experts a third of them).
+//   combine   every rank has written, for all tokens, the gate-weighted sum over its own experts into its slot. The
+//             owner of a token adds, in rank order, the sums of the ranks that host one of the token's experts to the
+//             residual stream (bit-identical whatever the rank count's timing; no atomics).
+// A slot is rewritten one step later, after 2 x layers - 1 further exchanges, which a rank only passes once every peer
+// has finished the earlier ones. Plain ld / st over mapped peer memory; every wait is bounded on the global timer.
+// ---------------------------------------------------------------------------
+struct EpParams {
+  const float* peer_slot[8];
+  int* peer_flags[8];
+  int* my_flags;
+  int* seq;
+  int* ticket;
+  int* err;
+  int* gave_up;
+  unsigned wait_limit_us;
+  int rank, world;
+  int tokens, stride, hidden, top_k;     // tokens per rank; floats per packed row
+  int expert_lo, expert_hi, experts_per_rank;
+  float* all;                            // dispatch: [world * tokens][stride] gathered rows
+  int32_t* ids_out; float* gates_out;    // dispatch: [world * tokens][top_k]
+  float* x; int64_t ldx;                 // combine: residual stream of this rank's tokens, updated in place
+  const int32_t* my_ids;                 // combine: [tokens][top_k] expert ids of this rank's tokens
+};
+
+// arrival exchange of one call: returns the call's sequence number (every thread), false in *ok when a wait ran out
+__device__ __forceinline__ int ep_arrive_and_wait(const EpParams& p, int* s_seq) {
+  if (threadIdx.x == 0) *s_seq = *(volatile int*)p.seq + 1;
+  __syncthreads();
+  const int seq = *s_seq;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < p.world) {
+    __threadfence_system();                                   // this rank's slot (written by the previous kernel) first
+    *(volatile int*)(p.peer_flags[threadIdx.x] + p.rank) = seq;
+  }
+  if (threadIdx.x < p.world) {
+    const volatile int* f = (const volatile int*)(p.my_flags + threadIdx.x);
+    bool ok = *f >= seq;
+    if (!ok && *(volatile int*)p.gave_up == 0) {
+      const unsigned long long t0 = gtime_ns(), limit = (unsigned long long)p.wait_limit_us * 1000ull;
+      while (true) {
+        if (*f >= seq) { ok = true; break; }
+        if (gtime_ns() - t0 > limit) break;
+      }
+    }
+    if (!ok) { *p.err = 1; *(volatile int*)p.gave_up = 1; }
+  }
+  __syncthreads();
+  __threadfence_system();
+  return seq;
+}
+__device__ __forceinline__ void ep_finish(const EpParams& p, int seq) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(p.ticket, 1);
+    if (old == (int)(gridDim.x * gridDim.y) - 1) { *p.ticket = 0; *(volatile int*)p.seq = seq; }
+  }
+}
+__device__ __forceinline__ float4 ep_ld4(const float* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+// grid.x = world * tokens (one CTA per gathered row)
+__global__ void ep_dispatch_kernel(const EpParams p) {
+  __shared__ int s_seq;
+  __shared__ int s_need;
+  const int seq = ep_arrive_and_wait(p, &s_seq);
+  const int row = blockIdx.x;
+  const int r = row / p.tokens, t = row - r * p.tokens;
+  const float* src = p.peer_slot[r] + (size_t)t * p.stride;
+  float* dst = p.all + (size_t)row * p.stride;
+  if (threadIdx.x == 0) s_need = 0;
+  __syncthreads();
+  if (threadIdx.x < p.top_k) {
+    float idf, g;
+    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(idf) : "l"(src + p.hidden + threadIdx.x));
+    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(g) : "l"(src + p.hidden + p.top_k + threadIdx.x));
+    const int e = __float_as_int(idf);
+    dst[p.hidden + threadIdx.x] = idf;
+    dst[p.hidden + p.top_k + threadIdx.x] = g;
+    p.ids_out[row * p.top_k + threadIdx.x] = e;
+    p.gates_out[row * p.top_k + threadIdx.x] = g;
+    if (e >= p.expert_lo && e < p.expert_hi) s_need = 1;
+  }
+  __syncthreads();
+  if (s_need) {
+    // a remote load costs ~2 us: a thread requests its pieces (up to four) together, then stores them
+    for (int c0 = threadIdx.x * 4; c0 < p.hidden; c0 += blockDim.x * 16) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x * 4;
+        if (c < p.hidden) v[u] = ep_ld4(src + c);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x * 4;
+        if (c < p.hidden) *(float4*)(dst + c) = v[u];
+      }
+    }
+  }
+  ep_finish(p, seq);
+}
+
+// grid = (tokens, column blocks): x[t] += sum in rank order of the partial sums of the ranks that host one of t's experts
+__global__ void ep_combine_kernel(const EpParams p) {
+  __shared__ int s_seq;
+  __shared__ int s_mask;
+  const int seq = ep_arrive_and_wait(p, &s_seq);
+  const int t = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int mask = 0;
+    for (int k = 0; k < p.top_k; ++k) {
+      const int e = p.my_ids[t * p.top_k + k];
+      if (e >= 0) mask |= 1 << (e / p.experts_per_rank);
+    }
+    s_mask = mask;
+  }
+  __syncthreads();
+  const int mask = s_mask;
+  const size_t grow = (size_t)(p.rank * p.tokens + t) * (size_t)p.hidden;
+  const int cols_per_block = (((p.hidden / 4) + gridDim.y - 1) / gridDim.y) * 4;
+  const int c_begin = blockIdx.y * cols_per_block;
+  int c_end = c_begin + cols_per_block; if (c_end > p.hidden) c_end = p.hidden;
+  for (int c = c_begin + threadIdx.x * 4; c < c_end; c += blockDim.x * 4) {
+    // all ranks' pieces are requested together (a remote load costs ~2 us), then added in rank order
+    float4 v[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.world && ((mask >> r) & 1)) v[r] = ep_ld4(p.peer_slot[r] + grow + c);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.world && ((mask >> r) & 1)) { sum.x += v[r].x; sum.y += v[r].y; sum.z += v[r].z; sum.w += v[r].w; }
+    float4* xp = (float4*)(p.x + (int64_t)t * p.ldx + c);
+    float4 xv = *xp;
+    xv.x += sum.x; xv.y += sum.y; xv.z += sum.z; xv.w += sum.w;
+    *xp = xv;
+  }
+  ep_finish(p, seq);
+}
+
+static void ep_fill(EpParams& p, cai_ctx* ctx, cai_tp_ar* ar, int site) {
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < ar->world; ++r) {
+    p.peer_flags[r] = (int*)ar->peer_block[r];
+    p.peer_slot[r] = (const float*)((char*)ar->peer_block[r] + AR_FLAG_BYTES) + (size_t)site * (size_t)ar->max_elems;
+  }
+  p.my_flags = (int*)ar->block; p.seq = ar->seq_dev; p.gave_up = ar->seq_dev + 1; p.ticket = ar->ticket_dev;
+  p.rank = ar->rank; p.world = ar->world; p.err = ctx->err_flag; p.wait_limit_us = ctx->wait_limit_us;
+}
+
+int comm_ep_dispatch(cai_ctx* ctx, cai_tp_ar* ar, int site, int tokens, int stride, int hidden, int top_k, int expert_lo, int expert_hi,
+                     float* all, int32_t* ids_out, float* gates_out) {
+  if (site < 0 || site >= ar->sites || (int64_t)tokens * stride > ar->max_elems || (hidden % 4) || (stride % 4) || top_k > 256)
+    return cai_fail(ctx, CAI_ERR_INVALID, "expert dispatch: slot %d of %d, %d rows of %d", site, ar->sites, tokens, stride);
+  EpParams p;
+  ep_fill(p, ctx, ar, site);
+  p.tokens = tokens; p.stride = stride; p.hidden = hidden; p.top_k = top_k; p.expert_lo = expert_lo; p.expert_hi = expert_hi;
+  p.all = all; p.ids_out = ids_out; p.gates_out = gates_out;
+  ctx->cur_family = FAM_COMM;
+  ep_dispatch_kernel<<<dim3((unsigned)(ar->world * tokens)), 256, 0, ctx->stream>>>(p);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
+int comm_ep_combine(cai_ctx* ctx, cai_tp_ar* ar, int site, int tokens, int hidden, int top_k, int experts_per_rank, const int32_t* my_ids,
+                    float* x, int64_t ldx) {
+  if (site < 0 || site >= ar->sites || (int64_t)ar->world * tokens * hidden > ar->max_elems || (hidden % 4) || (ldx % 4))
+    return cai_fail(ctx, CAI_ERR_INVALID, "expert combine: slot %d of %d, %d rows of %d", site, ar->sites, ar->world * tokens, hidden);
+  EpParams p;
+  ep_fill(p, ctx, ar, site);
+  p.tokens = tokens; p.hidden = hidden; p.top_k = top_k; p.experts_per_rank = experts_per_rank; p.my_ids = my_ids; p.x = x; p.ldx = ldx;
+  int yblocks = (2 * ctx->sm_count) / (tokens > 0 ? tokens : 1);
+  if (yblocks < 1) yblocks = 1;
+  if (yblocks > 8) yblocks = 8;
+  ctx->cur_family = FAM_COMM;
+  ep_combine_kernel<<<dim3((unsigned)tokens, (unsigned)yblocks), 256, 0, ctx->stream>>>(p);
+  CAI_LAUNCHED(ctx);
+  return CAI_OK;
+}
+
 void comm_ar_destroy(cai_ctx* ctx, cai_tp_ar* ar) {
   if (!ar) return;
   // every rank must have finished reading before any rank unmaps or frees
@@ -150,7 +339,7 @@ int comm_ar_create(cai_ctx* ctx, int sites, int64_t max_elems, cai_tp_ar** out) 
   *out = nullptr;
   if (!ctx->comm) return cai_fail(ctx, CAI_ERR_STATE, "communicator not initialised");
   const char* mode = getenv("CAI_TP_ALLREDUCE");
-  if (mode && !strcmp(mode, "nccl")) return CAI_OK;           // caller falls back to ncclAllReduce
+  if (mode && !strcmp(mode, "nccl")) return CAI_OK;           // caller falls back to the library collectives
   const int world = ctx->comm->world, rank = ctx->comm->rank;
   if (world > 8 || (max_elems % 4)) return CAI_OK;
   cai_tp_ar* ar = new cai_tp_ar();

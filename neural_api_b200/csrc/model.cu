@@ -814,9 +814,15 @@ static int enqueue_step(cai_session* s) {
         const int Bg = B * m->ep_size, W = (H + 2 * K + 3) & ~3;
         const QWeight& gu = L.exp_gu[(size_t)m->expert_lo()];
         const QWeight& dn = L.exp_down[(size_t)m->expert_lo()];
-        CAI_TRY(op_moe_pack(ctx, s->h, H, s->expert_ids, s->gates, B, H, K, W, s->ep_pack));
-        CAI_TRY(comm_allgather(ctx, s->ep_pack, s->ep_all, (int64_t)B * W));
-        CAI_TRY(op_moe_unpack_ids(ctx, s->ep_all, Bg, H, K, W, s->ep_ids, s->ep_gates));
+        if (s->ar) {
+          // dispatch over peer memory: rows packed into this rank's slot, then pulled by the ranks that need them
+          CAI_TRY(op_moe_pack(ctx, s->h, H, s->expert_ids, s->gates, B, H, K, W, comm_ar_slot(s->ar, 2 * l)));
+          CAI_TRY(comm_ep_dispatch(ctx, s->ar, 2 * l, B, W, H, K, m->expert_lo(), m->expert_hi(), s->ep_all, s->ep_ids, s->ep_gates));
+        } else {
+          CAI_TRY(op_moe_pack(ctx, s->h, H, s->expert_ids, s->gates, B, H, K, W, s->ep_pack));
+          CAI_TRY(comm_allgather(ctx, s->ep_pack, s->ep_all, (int64_t)B * W));
+          CAI_TRY(op_moe_unpack_ids(ctx, s->ep_all, Bg, H, K, W, s->ep_ids, s->ep_gates));
+        }
         CAI_TRY(op_moe_group(ctx, s->ep_ids, Bg * K, E, 16, s->moe_tiles, s->tile_expert, s->tile_pairs, m->expert_lo(), m->expert_hi()));
         ctx->cur_family = FAM_LINEAR;
         CAI_TRY(gemm_tc_launch_grouped(ctx, gu.type, L.d_gu_codes, L.d_gu_scales, gu.n, gu.k, gu.sstride, s->ep_all, W, K, s->moe_gu, 2 * (int64_t)Im,
@@ -825,9 +831,16 @@ static int enqueue_step(cai_session* s) {
         ctx->cur_family = FAM_LINEAR;
         CAI_TRY(gemm_tc_launch_grouped(ctx, dn.type, L.d_down_codes, L.d_down_scales, dn.n, dn.k, dn.sstride, s->moe_hidden, Im, 1, s->pair_out, H,
                                        s->tile_expert, s->tile_pairs, s->moe_tiles, s->moe_xp, s->moe_unscale));
-        CAI_TRY(op_moe_combine_partial(ctx, s->pair_out, H, s->ep_ids, s->ep_gates, Bg, K, H, m->expert_lo(), m->expert_hi(), s->ep_part, H));
-        CAI_TRY(comm_reduce_scatter(ctx, s->ep_part, s->ep_mine, (int64_t)B * H));
-        CAI_TRY(op_add_rows(ctx, x, H, s->ep_mine, H, B, H));
+        if (s->ar) {
+          // combine over peer memory: this rank's partial sums of all tokens into its slot; each owner adds what it needs
+          CAI_TRY(op_moe_combine_partial(ctx, s->pair_out, H, s->ep_ids, s->ep_gates, Bg, K, H, m->expert_lo(), m->expert_hi(),
+                                         comm_ar_slot(s->ar, 2 * l + 1), H));
+          CAI_TRY(comm_ep_combine(ctx, s->ar, 2 * l + 1, B, H, K, E / m->ep_size, s->expert_ids, x, H));
+        } else {
+          CAI_TRY(op_moe_combine_partial(ctx, s->pair_out, H, s->ep_ids, s->ep_gates, Bg, K, H, m->expert_lo(), m->expert_hi(), s->ep_part, H));
+          CAI_TRY(comm_reduce_scatter(ctx, s->ep_part, s->ep_mine, (int64_t)B * H));
+          CAI_TRY(op_add_rows(ctx, x, H, s->ep_mine, H, B, H));
+        }
         continue;
       }
       if (s->moe_tiles) {
@@ -1092,6 +1105,17 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
     // and one more slot for the argmax exchange
     const int sites = (2 * c.layers + 1 > 4 * m->tp_size + 1) ? 2 * c.layers + 1 : 4 * m->tp_size + 1;
     if (comm_ar_create(ctx, sites, (int64_t)B * H, &s->ar) != CAI_OK) ok = false;
+  }
+  if (ok && !kv_owner && m->ep_size > 1 && c.n_experts > 0 && (H % 4) == 0) {
+    // collective: the expert-parallel dispatch / combine over peer memory, one slot per exchange of a step
+    // (CAI_EP_EXCHANGE=nccl, or peers that cannot be mapped: the library's all-gather and reduce-scatter instead)
+    const char* em = getenv("CAI_EP_EXCHANGE");
+    if (!(em && !strcmp(em, "nccl"))) {
+      const int W = (H + 2 * c.top_k + 3) & ~3;
+      int64_t elems = (int64_t)B * m->ep_size * H;
+      if ((int64_t)B * W > elems) elems = (int64_t)B * W;
+      if (comm_ar_create(ctx, 2 * c.layers, (elems + 3) & ~(int64_t)3, &s->ar) != CAI_OK) ok = false;
+    }
   }
   if (ok && cudaMallocHost((void**)&s->io_pinned, (size_t)4 * B * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
   if (ok && B >= 3 && B <= 64) {

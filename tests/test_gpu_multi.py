@@ -44,12 +44,17 @@ def test_tensor_parallel_matches_single_gpu(world, allreduce):
     assert "TP_GPU_OK" in r.stdout
 
 
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_expert_parallel_matches_single_gpu(world):
+def test_expert_parallel_matches_single_gpu(world, exchange):
     if gpu_count() < world:
         pytest.skip("needs %d GPUs" % world)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "ep_gpu_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    env = dict(os.environ)
+    env.pop("CAI_EP_EXCHANGE", None)
+    if exchange == "nccl":
+        env["CAI_EP_EXCHANGE"] = "nccl"           # the library's all-gather + reduce-scatter instead of the peer-memory kernels
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-5000:]
     assert "EP_GPU_OK" in r.stdout
