@@ -46,7 +46,7 @@ constexpr int SK_FOLD_FLOATS = 49152;                // splits x q_width up to w
 constexpr int SK_FOLD_MAX_CHUNK = 512;               // ... and the longest split worth accepting for that (one 32-row tile per warp)
 constexpr int SK_FOLD_MAX_SPLITS = 8;                // ... and the most splits: the fold walks them one after the other in every CTA
                                                      // (measured: 64 splits cost the O staging 13 us, the merge phase + its barrier 5)
-constexpr int SK_MIN_CHUNK = 128;                    // fewest cached rows of a context split
+constexpr int SK_MIN_CHUNK = 64;                     // fewest cached rows of a context split
 enum { MK_QKV = 0, MK_O = 1, MK_GU = 2, MK_DOWN = 3, MK_HEAD = 4 };
 
 struct SkMat {
