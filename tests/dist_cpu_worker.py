@@ -77,6 +77,74 @@ def expert_parallel_check(rank, world):
         assert float(np.max(np.abs(out[i].numpy() - y))) < 1e-5
 
 
+def expert_parallel_peer_exchange_check(rank, world):
+    """The dispatch / combine rule of the peer-memory exchange (ep_dispatch_kernel / ep_combine_kernel), replayed with numpy:
+    a rank reads the ids and gates of every token but the hidden row only of tokens that route to one of ITS experts, and
+    a token's owner adds, in rank order, only the partial sums of ranks that host one of the token's experts. Whatever the
+    rule says is not read is poisoned with NaN here, so a use of it would show. Must equal the unsharded oracle arithmetic."""
+    H, I, E, K, per_rank = 32, 16, 8, 2, 3
+    rng = np.random.default_rng(12)
+    router = (rng.standard_normal((E, H)) * 0.3).astype(np.float32)
+    experts = [dict(up=(rng.standard_normal((I, H)) * 0.2).astype(np.float32), gate=(rng.standard_normal((I, H)) * 0.2).astype(np.float32),
+                    down=(rng.standard_normal((H, I)) * 0.2).astype(np.float32)) for _ in range(E)]
+    h_all = rng.standard_normal((per_rank * world, H)).astype(np.float32)
+    mine = slice(rank * per_rank, (rank + 1) * per_rank)
+    rows = []
+    for h in h_all[mine]:
+        order, gates = router_gates(softmax_row(router @ h), K, True)
+        rows.append(np.concatenate([h, order.astype(np.int32).view(np.float32), gates.astype(np.float32)]))
+    slot = torch.from_numpy(np.stack(rows).astype(np.float32))          # this rank's dispatch slot
+    slots = [torch.zeros_like(slot) for _ in range(world)]
+    dist.all_gather(slots, slot)                                         # stands in for the peers' mapped slots
+    lo, hi = parallel.ep_expert_range(E, rank, world)
+    per = E // world
+    allrows = np.full((per_rank * world, H + 2 * K), np.nan, np.float32)
+    for r in range(world):
+        src = slots[r].numpy()
+        for t in range(per_rank):
+            row = r * per_rank + t
+            allrows[row, H:] = src[t, H:]                                # ids and gates: always
+            ids_t = src[t, H:H + K].copy().view(np.int32)
+            if np.any((ids_t >= lo) & (ids_t < hi)):
+                allrows[row, :H] = src[t, :H]                            # the hidden row: only when an expert of mine is routed to
+    ids = allrows[:, H:H + K].copy().view(np.int32)
+    gates = allrows[:, H + K:H + 2 * K]
+    part = np.zeros((per_rank * world, H), np.float32)
+    pair_out = {}
+    for e, pairs in parallel.ep_group_pairs(ids.reshape(-1), lo, hi, tile_rows=4):
+        for p in pairs:
+            hrow = allrows[p // K, :H]
+            assert not np.any(np.isnan(hrow))                            # every row a tile touches was pulled
+            fused = np.concatenate([experts[e]["up"] @ hrow, experts[e]["gate"] @ hrow])
+            pair_out[p] = experts[e]["down"] @ swiglu(fused, I)
+    for t in range(per_rank * world):
+        for k in range(K):                                               # slots in order, as moe_combine_partial_kernel adds them
+            if lo <= ids[t, k] < hi:
+                part[t] += gates[t, k] * pair_out[t * K + k]
+    cslot = torch.from_numpy(part.copy())                                # this rank's combine slot: partial sums of ALL tokens
+    cslots = [torch.zeros_like(cslot) for _ in range(world)]
+    dist.all_gather(cslots, cslot)
+    x = np.zeros((per_rank, H), np.float32)                              # the residual stream of my tokens (zero here)
+    my_ids = ids[mine]
+    for t in range(per_rank):
+        hosts = sorted(set(int(e) // per for e in my_ids[t]))
+        for r in range(world):
+            src = cslots[r].numpy().copy()
+            if r not in hosts:
+                src[:] = np.nan                                          # never read
+                continue
+            x[t] += src[rank * per_rank + t]
+    for i, h in enumerate(h_all[mine]):
+        order, g = router_gates(softmax_row(router @ h), K, True)
+        y = np.zeros(H, np.float32)
+        for e_id, gate in zip(order, g):
+            ex = experts[int(e_id)]
+            fused = np.concatenate([ex["up"] @ h, ex["gate"] @ h])
+            y = y + gate * (ex["down"] @ swiglu(fused, I))
+        assert not np.any(np.isnan(x[i]))
+        assert float(np.max(np.abs(x[i] - y))) < 1e-5
+
+
 def main():
     rank, world, local_rank, d = parallel.init_process_group("gloo")
     assert d is not None and world == 2
@@ -148,6 +216,7 @@ def main():
         err = float(np.max(np.abs(logits - ref)))
         assert err < 1e-5, (pos, err)
     expert_parallel_check(rank, world)
+    expert_parallel_peer_exchange_check(rank, world)
     dist.barrier()
     if rank == 0:
         print("DIST_CPU_OK")
