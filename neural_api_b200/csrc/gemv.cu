@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
 #pragma unroll
     for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
   // rows whose width and addresses allow it go four elements per lane and step (16-byte loads of fp32 rows, 8-byte
-  // loads of fp16 rows): a K-quant file's mixed-format [q|k|v] group, decoded to fp32 at load, is a large matrix
+  // loads of fp16 rows): a file's Q2_K / Q3_K / Q4_1 / Q5_x matrix, decoded to fp32 at load, is a large matrix
   int64_t i0 = 0;
   const bool vec4 = (p.k % 4) == 0 && (p.ldx % 4) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)codes % 16) == 0;
   if (vec4) {

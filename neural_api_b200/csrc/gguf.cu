@@ -570,26 +570,6 @@ int cai_model_load_gguf(cai_ctx* ctx, const char* path, int tp_rank, int tp_size
   const bool qwen2 = cfg.qkv_bias != 0;
   std::vector<uint8_t> raw;
   std::vector<float> f32;
-  // q/k/v rows live in one resident matrix, and so do up/gate rows: when a file stores the members of such a group in
-  // different formats (llama.cpp's mixed presets do), or in a load-time format, the whole group is decoded to fp32
-  std::map<std::string, int> group_type;                 // "<layer>.qkv" / "<layer>.gu" -> common type, or -1 when mixed
-  auto group_of = [](const std::string& n) -> std::string {
-    if (n.compare(0, 4, "blk.") != 0) return "";
-    const size_t dot = n.find('.', 4);
-    if (dot == std::string::npos) return "";
-    const std::string rest = n.substr(dot + 1);
-    if (rest == "attn_q.weight" || rest == "attn_k.weight" || rest == "attn_v.weight") return n.substr(4, dot - 4) + ".qkv";
-    if (rest == "ffn_gate.weight" || rest == "ffn_up.weight") return n.substr(4, dot - 4) + ".gu";
-    return "";
-  };
-  for (const GGUFTensor& t : g->tensors) {
-    const std::string key = group_of(t.name);
-    if (key.empty()) continue;
-    const int ty = gguf_type_needs_decode(t.type) ? CAI_TYPE_F32 : t.type;
-    auto it = group_type.find(key);
-    if (it == group_type.end()) group_type[key] = ty;
-    else if (it->second != ty) it->second = -1;
-  }
   for (size_t i = 0; i < g->tensors.size() && st == CAI_OK; ++i) {
     const GGUFTensor& t = g->tensors[i];
     std::string hf;
@@ -603,10 +583,9 @@ int cai_model_load_gguf(cai_ctx* ctx, const char* path, int tp_rank, int tp_size
     // The stored q/k rows are already in the interleaved rotary order the graph runs in: the reference's reader
     // de-interleaves them and its loader interleaves them again (neural/neuralgguf.pas:428-438,
     // neural/neuralpretrained.pas:14792-14812), so the net effect on the resident rows is none.
-    const std::string gkey = group_of(t.name);
-    const bool mixed_group = !gkey.empty() && group_type[gkey] == -1;
-    if ((t.ndims == 1 && t.type != CAI_TYPE_F32) || (mixed_group && t.type != CAI_TYPE_F32)) {
-      // norm gains and biases are F32 vectors on the device; members of a mixed group continue as F32
+    if (t.ndims == 1 && t.type != CAI_TYPE_F32) {
+      // norm gains and biases are F32 vectors on the device (matrices keep their format; a [q|k|v] or [up|gate] group
+      // whose members differ in format is kept as separate matrices by cai_model_upload_tensor)
       f32.resize((size_t)t.n_elems);
       st = gguf_decode_host(ctx, t.type, raw.data(), t.n_elems, f32.data());
       if (st == CAI_OK) st = cai_model_upload_tensor(m, hf.c_str(), CAI_TYPE_F32, f32.data(), rows, cols, 0);

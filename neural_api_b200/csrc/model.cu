@@ -57,6 +57,12 @@ struct LayerW {
   float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
   float* qkv_bias = nullptr;                  // [q | k | v] biases, owned here; wqkv.bias aliases it after finalize
   QWeight wqkv, wo, wgu, wdown, router;
+  // A file may store the members of a fused matrix in different formats (llama.cpp's mixed K-quant presets: q and k in
+  // Q4_K, v in Q6_K). Such a group is kept as separate matrices, each in its own format, and the step runs one product
+  // per member with the plain epilogue (RoPE + append and SwiGLU then run as their own kernels).
+  QWeight wq_part[3];                         // q, k, v when qkv_split
+  QWeight wgu_part[2];                        // up, gate when gu_split
+  bool qkv_split = false, gu_split = false;
   std::vector<QWeight> exp_gu, exp_down;
   std::vector<uint8_t> exp_have;              // bit 1 gate, 2 up, 4 down
   const void** d_gu_codes = nullptr; const __half** d_gu_scales = nullptr;
@@ -94,6 +100,23 @@ static int ensure_weight(cai_ctx* ctx, QWeight* w, int type, int64_t n, int64_t 
   }
   return qweight_alloc(ctx, w, type, n, k);
 }
+// Moves the members of a fused matrix that were uploaded so far into matrices of their own (same type, planes copied
+// on the device) and frees the fused one: the group continues in split form.
+static int split_fused(cai_ctx* ctx, QWeight* fused, QWeight* parts, const int64_t* row0, const int64_t* nrows, const bool* have, int n_parts) {
+  for (int i = 0; i < n_parts; ++i) {
+    if (!have[i]) continue;
+    const QWeight v = qweight_rows_view(*fused, row0[i], nrows[i]);
+    CAI_TRY(qweight_alloc(ctx, &parts[i], fused->type, nrows[i], fused->k));
+    CAI_CUDA(ctx, cudaMemcpyAsync(parts[i].codes, v.codes, parts[i].code_bytes(), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (v.scales) CAI_CUDA(ctx, cudaMemcpyAsync(parts[i].scales, v.scales, parts[i].scale_alloc_bytes(), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (v.rscale) CAI_CUDA(ctx, cudaMemcpyAsync(parts[i].rscale, v.rscale, (size_t)nrows[i] * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    parts[i].present = true;
+  }
+  CAI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  fused->bias = nullptr;
+  qweight_free(fused);
+  return CAI_OK;
+}
 static int ensure_vec(cai_ctx* ctx, float** p, int64_t n, bool zero) {
   if (*p) return CAI_OK;
   CAI_CUDA(ctx, cudaMalloc((void**)p, (size_t)n * 4));
@@ -124,6 +147,8 @@ static void layer_free(LayerW& L) {
   if (L.k_norm) cudaFree(L.k_norm);
   if (L.qkv_bias) cudaFree(L.qkv_bias);
   L.wqkv.bias = nullptr;
+  for (auto& w : L.wq_part) { w.bias = nullptr; qweight_free(&w); }
+  for (auto& w : L.wgu_part) qweight_free(&w);
   qweight_free(&L.wqkv); qweight_free(&L.wo); qweight_free(&L.wgu); qweight_free(&L.wdown); qweight_free(&L.router);
   for (auto& w : L.exp_gu) qweight_free(&w);
   for (auto& w : L.exp_down) qweight_free(&w);
@@ -278,11 +303,25 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
     case T_Q: case T_K: case T_V: {
       const bool isq = t.kind == T_Q;
       NEED_SHAPE(isq ? QW : KW, H);
-      CAI_TRY(ensure_weight(ctx, &L.wqkv, stype, qkv_rows, H));
       const int64_t nloc = isq ? m->qw_l : m->kw_l;
       const int64_t dst0 = isq ? 0 : (t.kind == T_K ? m->qw_l : m->qw_l + m->kw_l);
-      QWeight view = qweight_rows_view(L.wqkv, dst0, nloc);
-      CAI_TRY(put(&view, (int64_t)r * nloc, 0, t.kind == T_V ? 0 : interleave_head_dim));
+      const int part = isq ? 0 : (t.kind == T_K ? 1 : 2);
+      if (!L.qkv_split && L.wqkv.codes && L.wqkv.type != stype) {
+        // a member in another format than the ones before it: the group continues as separate matrices
+        const int64_t row0[3] = {0, m->qw_l, m->qw_l + m->kw_l}, nrows[3] = {m->qw_l, m->kw_l, m->kw_l};
+        const bool have[3] = {(L.have & HAVE_Q) != 0, (L.have & HAVE_K) != 0, (L.have & HAVE_V) != 0};
+        CAI_TRY(split_fused(ctx, &L.wqkv, L.wq_part, row0, nrows, have, 3));
+        L.qkv_split = true;
+      }
+      if (L.qkv_split) {
+        if (L.wq_part[part].codes && L.wq_part[part].type != stype) { L.wq_part[part].bias = nullptr; qweight_free(&L.wq_part[part]); }
+        CAI_TRY(ensure_weight(ctx, &L.wq_part[part], stype, nloc, H));
+        CAI_TRY(put(&L.wq_part[part], (int64_t)r * nloc, 0, t.kind == T_V ? 0 : interleave_head_dim));
+      } else {
+        CAI_TRY(ensure_weight(ctx, &L.wqkv, stype, qkv_rows, H));
+        QWeight view = qweight_rows_view(L.wqkv, dst0, nloc);
+        CAI_TRY(put(&view, (int64_t)r * nloc, 0, t.kind == T_V ? 0 : interleave_head_dim));
+      }
       L.have |= isq ? HAVE_Q : (t.kind == T_K ? HAVE_K : HAVE_V);
       return CAI_OK;
     }
@@ -306,10 +345,23 @@ int cai_model_upload_tensor(cai_model* m, const char* hf_name, int type, const v
     case T_GATE: case T_UP: {
       if (c.n_experts) return cai_fail(ctx, CAI_ERR_INVALID, "'%s': dense MLP tensor in an MoE configuration", hf_name);
       NEED_SHAPE(c.inter, H);
-      CAI_TRY(ensure_weight(ctx, &L.wgu, stype, 2 * (int64_t)m->inter_l, H));
-      // up rows first, gate rows second
-      QWeight view = qweight_rows_view(L.wgu, t.kind == T_UP ? 0 : m->inter_l, m->inter_l);
-      CAI_TRY(put(&view, (int64_t)r * m->inter_l, 0, 0));
+      const int part = (t.kind == T_UP) ? 0 : 1;
+      if (!L.gu_split && L.wgu.codes && L.wgu.type != stype) {
+        const int64_t row0[2] = {0, m->inter_l}, nrows[2] = {m->inter_l, m->inter_l};
+        const bool have[2] = {(L.have & HAVE_UP) != 0, (L.have & HAVE_GATE) != 0};
+        CAI_TRY(split_fused(ctx, &L.wgu, L.wgu_part, row0, nrows, have, 2));
+        L.gu_split = true;
+      }
+      if (L.gu_split) {
+        if (L.wgu_part[part].codes && L.wgu_part[part].type != stype) qweight_free(&L.wgu_part[part]);
+        CAI_TRY(ensure_weight(ctx, &L.wgu_part[part], stype, m->inter_l, H));
+        CAI_TRY(put(&L.wgu_part[part], (int64_t)r * m->inter_l, 0, 0));
+      } else {
+        CAI_TRY(ensure_weight(ctx, &L.wgu, stype, 2 * (int64_t)m->inter_l, H));
+        // up rows first, gate rows second
+        QWeight view = qweight_rows_view(L.wgu, part == 0 ? 0 : m->inter_l, m->inter_l);
+        CAI_TRY(put(&view, (int64_t)r * m->inter_l, 0, 0));
+      }
       L.have |= (t.kind == T_UP) ? HAVE_UP : HAVE_GATE;
       return CAI_OK;
     }
@@ -477,15 +529,15 @@ static int locate_tensor(cai_model* m, const char* hf_name, QWeight* out_view, c
     case T_FFN_NORM: *out_vec = L.ffn_norm; *out_vec_len = c.hidden; return CAI_OK;
     case T_QNORM: *out_vec = L.q_norm; *out_vec_len = c.heads * c.head_dim; return CAI_OK;
     case T_KNORM: *out_vec = L.k_norm; *out_vec_len = c.kv_heads * c.head_dim; return CAI_OK;
-    case T_Q: *out_view = qweight_rows_view(L.wqkv, 0, m->qw_l); return CAI_OK;
-    case T_K: *out_view = qweight_rows_view(L.wqkv, m->qw_l, m->kw_l); return CAI_OK;
-    case T_V: *out_view = qweight_rows_view(L.wqkv, m->qw_l + m->kw_l, m->kw_l); return CAI_OK;
+    case T_Q: *out_view = L.qkv_split ? qweight_rows_view(L.wq_part[0], 0, m->qw_l) : qweight_rows_view(L.wqkv, 0, m->qw_l); return CAI_OK;
+    case T_K: *out_view = L.qkv_split ? qweight_rows_view(L.wq_part[1], 0, m->kw_l) : qweight_rows_view(L.wqkv, m->qw_l, m->kw_l); return CAI_OK;
+    case T_V: *out_view = L.qkv_split ? qweight_rows_view(L.wq_part[2], 0, m->kw_l) : qweight_rows_view(L.wqkv, m->qw_l + m->kw_l, m->kw_l); return CAI_OK;
     case T_QB: *out_vec = L.qkv_bias; *out_vec_len = m->qw_l; return CAI_OK;
     case T_KB: *out_vec = L.qkv_bias ? L.qkv_bias + m->qw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
     case T_VB: *out_vec = L.qkv_bias ? L.qkv_bias + m->qw_l + m->kw_l : nullptr; *out_vec_len = m->kw_l; return CAI_OK;
     case T_O: *out_view = qweight_rows_view(L.wo, 0, L.wo.n); return CAI_OK;
-    case T_UP: *out_view = qweight_rows_view(L.wgu, 0, m->inter_l); return CAI_OK;
-    case T_GATE: *out_view = qweight_rows_view(L.wgu, m->inter_l, m->inter_l); return CAI_OK;
+    case T_UP: *out_view = L.gu_split ? qweight_rows_view(L.wgu_part[0], 0, m->inter_l) : qweight_rows_view(L.wgu, 0, m->inter_l); return CAI_OK;
+    case T_GATE: *out_view = L.gu_split ? qweight_rows_view(L.wgu_part[1], 0, m->inter_l) : qweight_rows_view(L.wgu, m->inter_l, m->inter_l); return CAI_OK;
     case T_DOWN: *out_view = qweight_rows_view(L.wdown, 0, L.wdown.n); return CAI_OK;
     case T_ROUTER: *out_view = qweight_rows_view(L.router, 0, L.router.n); return CAI_OK;
     case T_EXP_UP: case T_EXP_GATE: case T_EXP_DOWN: {
@@ -555,6 +607,9 @@ int cai_model_finalize(cai_model* m) {
     if (c.n_experts) need |= HAVE_ROUTER; else need |= HAVE_GATE | HAVE_UP | HAVE_DOWN;
     if ((L.have & need) != need) return cai_fail(ctx, CAI_ERR_STATE, "layer %d is missing tensors (have mask 0x%x, need 0x%x)", l, L.have, need);
     L.wqkv.bias = L.qkv_bias;     // alias; freed through qkv_bias
+    if (L.qkv_split && L.qkv_bias) {
+      L.wq_part[0].bias = L.qkv_bias; L.wq_part[1].bias = L.qkv_bias + m->qw_l; L.wq_part[2].bias = L.qkv_bias + m->qw_l + m->kw_l;
+    }
     if (c.n_experts) {
       std::vector<const void*> gc, gs, dc, ds;
       const int e0 = m->expert_lo();
@@ -585,6 +640,8 @@ int cai_model_step_weight_bytes(cai_model* m, int64_t* out_bytes) {
   int64_t b = (int64_t)m->lm_head.bytes();
   for (auto& L : m->layers) {
     b += (int64_t)(L.wqkv.bytes() + L.wo.bytes());
+    if (L.qkv_split) for (const QWeight& w : L.wq_part) b += (int64_t)w.bytes();
+    if (L.gu_split) for (const QWeight& w : L.wgu_part) b += (int64_t)w.bytes();
     if (m->cfg.n_experts) {
       b += (int64_t)L.router.bytes();
       // one token touches top_k experts
@@ -725,15 +782,24 @@ static int enqueue_step(cai_session* s) {
   const bool fuse_rope = !c.qk_norm && !tc_batch && !s->kv_int8 && !s->kv_owner && !s->evict_window;
   for (int l = 0; l < c.layers; ++l) {
     LayerW& L = m->layers[(size_t)l];
-    if (linear_can_fuse_norm(&L.wqkv, B)) {
+    const bool fuse_rope_l = fuse_rope && !L.qkv_split;
+    if (L.qkv_split) {
+      // q, k and v in formats of their own: one product each into the [q | k | v] row, plain epilogue
+      CAI_TRY(op_rmsnorm(ctx, x, H, L.attn_norm, s->h, H, B, H, c.rms_eps));
+      const int64_t off[3] = {0, m->qw_l, m->qw_l + m->kw_l};
+      for (int i = 0; i < 3; ++i) {
+        LinearArgs a; a.w = &L.wq_part[i]; a.x = s->h; a.ldx = H; a.y = s->qkv + off[i]; a.ldy = QKVW; a.batch = B;
+        CAI_TRY(linear_launch(ctx, a));
+      }
+    } else if (linear_can_fuse_norm(&L.wqkv, B)) {
       LinearArgs a; a.w = &L.wqkv; a.x = x; a.ldx = H; a.y = s->qkv; a.ldy = QKVW; a.batch = B;
       a.norm_gain = L.attn_norm; a.norm_eps = c.rms_eps;
-      if (fuse_rope) set_rope(a, l);
+      if (fuse_rope_l) set_rope(a, l);
       CAI_TRY(linear_launch(ctx, a));
     } else {
       CAI_TRY(op_rmsnorm(ctx, x, H, L.attn_norm, s->h, H, B, H, c.rms_eps));
       LinearArgs a; a.w = &L.wqkv; a.x = s->h; a.ldx = H; a.y = s->qkv; a.ldy = QKVW; a.batch = B;
-      if (fuse_rope) set_rope(a, l);
+      if (fuse_rope_l) set_rope(a, l);
       CAI_TRY(linear_launch(ctx, a));
     }
     {
@@ -751,7 +817,7 @@ static int enqueue_step(cai_session* s) {
       { cai_session* o = s->kv_owner ? s->kv_owner : s; a.window = o->window; a.evict_sinks = o->evict_sinks; a.evict_window = o->evict_window; }
       a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.eps = c.rms_eps;
       a.out = s->att; a.ldo = m->qw_l; a.partial = s->partial; a.nsplit = s->nsplit;
-      if (!fuse_rope) CAI_TRY(attn_rope_append(ctx, a));
+      if (!fuse_rope_l) CAI_TRY(attn_rope_append(ctx, a));
       CAI_TRY(attn_decode(ctx, a));
     }
     // attention output projection + residual
@@ -771,11 +837,19 @@ static int enqueue_step(cai_session* s) {
       CAI_TRY(comm_allreduce(ctx, xalt, (int64_t)B * H));
       float* t = x; x = xalt; xalt = t;
     }
-    const bool fuse_ffn_norm = !c.n_experts && linear_can_fuse_norm(&L.wgu, B);
+    const bool fuse_ffn_norm = !c.n_experts && !L.gu_split && linear_can_fuse_norm(&L.wgu, B);
     if (!fuse_ffn_norm) CAI_TRY(op_rmsnorm(ctx, x, H, L.ffn_norm, s->h, H, B, H, c.rms_eps));
     if (!c.n_experts) {
       {
-        if (tc_batch && s->gu) {
+        if (L.gu_split) {
+          // up and gate in formats of their own: one product each into the [up | gate] row, then the gated activation
+          const int64_t I2 = 2 * (int64_t)m->inter_l;
+          for (int i = 0; i < 2; ++i) {
+            LinearArgs a; a.w = &L.wgu_part[i]; a.x = s->h; a.ldx = H; a.y = s->gu + (int64_t)i * m->inter_l; a.ldy = I2; a.batch = B;
+            CAI_TRY(linear_launch(ctx, a));
+          }
+          CAI_TRY(op_swiglu(ctx, s->gu, I2, s->act, m->inter_l, B, m->inter_l));
+        } else if (tc_batch && s->gu) {
           LinearArgs a; a.w = &L.wgu; a.x = fuse_ffn_norm ? x : s->h; a.ldx = H; a.y = s->gu; a.ldy = 2 * (int64_t)m->inter_l; a.batch = B;
           if (fuse_ffn_norm) { a.norm_gain = L.ffn_norm; a.norm_eps = c.rms_eps; }
           CAI_TRY(linear_launch(ctx, a));
@@ -1046,7 +1120,9 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   A((void**)&s->qkv, (size_t)B * QKVW * 4); A((void**)&s->att, (size_t)B * m->qw_l * 4);
   A((void**)&s->act, (size_t)B * (m->inter_l ? m->inter_l : 1) * 4);
   A((void**)&s->logits, (size_t)B * m->vocab_l * 4);
-  if (B >= 3 && B <= 64 && m->inter_l) A((void**)&s->gu, (size_t)B * 2 * m->inter_l * 4);
+  bool any_split = false;
+  for (const LayerW& L : m->layers) any_split = any_split || L.qkv_split || L.gu_split;
+  if (((B >= 3 && B <= 64) || any_split) && m->inter_l) A((void**)&s->gu, (size_t)B * 2 * m->inter_l * 4);
   size_t partial_floats = attn_partial_floats(B, m->heads_l, s->nsplit, c.head_dim);
   if (B == 1) {
     // the persistent step kernel deals about one (kv head, context split) item to every SM
@@ -1140,7 +1216,7 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   // extra launches per layer for the sums over the ranks).
   const int step_mode = env_int("CAI_STEP_KERNEL", -1);
   const bool step_auto = ((int64_t)c.hidden * m->inter_l * 3 >= ((int64_t)24 << 20)) || m->tp_size > 1;
-  if (B == 1 && !kv_owner && !kv_int8 && !c.n_experts && !c.qk_norm && (m->tp_size == 1 || s->ar) && (step_mode == 1 || (step_mode < 0 && step_auto))) {
+  if (B == 1 && !any_split && !kv_owner && !kv_int8 && !c.n_experts && !c.qk_norm && (m->tp_size == 1 || s->ar) && (step_mode == 1 || (step_mode < 0 && step_auto))) {
     // the whole step as one persistent kernel when the model is inside what it covers; otherwise (status
     // CAI_ERR_UNSUPPORTED) the session keeps one launch per operator
     StepSetup u;

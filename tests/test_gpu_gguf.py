@@ -203,14 +203,23 @@ def test_kquant_and_legacy_formats_from_file_to_logits(backend, tmp_path):
             assert np.all(np.isfinite(logits))
             assert np.max(np.abs(logits[0] - ref)) < 1e-3 * max(rms, 1.0)
         # the load-time formats are resident as F32, bit-equal to the reader's decode (one of each family)
-        for hf, rows, cols in (("model.layers.0.self_attn.o_proj.weight", 256, 256), ("model.layers.1.mlp.down_proj.weight", 256, 512)):
+        for hf, rows, cols in (("model.layers.0.self_attn.o_proj.weight", 256, 256), ("model.layers.1.mlp.down_proj.weight", 256, 512),
+                               ("model.layers.0.self_attn.k_proj.weight", 128, 256), ("model.layers.1.mlp.up_proj.weight", 512, 256)):
             buf, ty, r, c = model.read_tensor(hf, rows * cols * 4)
             assert (ty, r, c) == (0, rows, cols)
             assert np.array_equal(buf[:rows * cols * 4].view(np.float32).reshape(rows, cols), oracle_tensor(p, hf))
         # Q4_K / Q5_K / Q6_K stay resident as the file's own super-blocks
         g = GF.GGUFFile(p)
+        # ... also as members of a [q|k|v] or [up|gate] group whose formats differ (layer 1: q Q6_K, k Q8_0, v Q4_0;
+        # gate Q5_K beside an up matrix decoded from Q2_K): such a group is kept as separate matrices
         for name, hf, tid in (("blk.0.ffn_down.weight", "model.layers.0.mlp.down_proj.weight", 12),
                               ("blk.2.attn_output.weight", "model.layers.2.self_attn.o_proj.weight", 13),
+                              ("blk.0.attn_q.weight", "model.layers.0.self_attn.q_proj.weight", 13),
+                              ("blk.1.attn_q.weight", "model.layers.1.self_attn.q_proj.weight", 14),
+                              ("blk.1.attn_k.weight", "model.layers.1.self_attn.k_proj.weight", 8),
+                              ("blk.1.attn_v.weight", "model.layers.1.self_attn.v_proj.weight", 2),
+                              ("blk.1.ffn_gate.weight", "model.layers.1.mlp.gate_proj.weight", 13),
+                              ("blk.2.ffn_up.weight", "model.layers.2.mlp.up_proj.weight", 13),
                               ("output.weight", "lm_head.weight", 14)):
             raw = g.raw(name)
             buf, ty, r, c = model.read_tensor(hf, raw.size)

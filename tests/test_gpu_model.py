@@ -415,3 +415,41 @@ def test_chunked_prefill_equals_token_at_a_time_prefill(backend, batch, kv_type)
     rms = float(np.sqrt(np.mean(outs[1].astype(np.float64) ** 2)))
     worst = float(np.max(np.abs(outs[0] - outs[1]))) / rms
     assert worst < (5e-3 if kv_type == TYPE_I8 else 1e-4), worst
+
+
+def test_fused_groups_with_members_in_different_formats_run_as_separate_matrices(backend):
+    """q and k arrive as Q8_0 blocks, v as fp32 rows (and up as fp32 beside a Q8_0 gate): the [q|k|v] and [up|gate]
+    groups cannot share one storage type, so the members uploaded first move into matrices of their own and the step
+    runs one product per member. Same weights, so the logits must equal the all-Q8_0 upload's."""
+    z = load_golden("tiny_llama_q8_gguf")
+    cfg = LlamaConfig.from_hf(json.loads(bytes(z["config_json"]).decode()))
+    ref_model = LlamaModel(backend, cfg_to_c(cfg))
+    _upload_gguf(ref_model, z)
+    ref_model.finalize()
+    model = LlamaModel(backend, cfg_to_c(cfg))
+    for k in z.files:
+        if not k.startswith("raw::"):
+            continue
+        name = k[5:]
+        ty, rows, cols = (int(v) for v in z["meta::" + name])
+        if ty == TYPE_Q8_0 and ("v_proj" in name or "up_proj" in name):
+            w = codecs.dequantize(ty, z[k]).reshape(rows, cols)
+            model.upload_tensor(name, TYPE_F32, w, rows, cols, 0)
+        else:
+            model.upload_tensor(name, ty, z[k], rows, cols, 0)
+    model.finalize()
+    buf, ty, rows, cols = model.read_tensor("model.layers.0.self_attn.q_proj.weight", 1 << 16)
+    assert ty == TYPE_Q8_0 and np.array_equal(buf[:z["raw::model.layers.0.self_attn.q_proj.weight"].size],
+                                              z["raw::model.layers.0.self_attn.q_proj.weight"])
+    buf, ty, rows, cols = model.read_tensor("model.layers.0.self_attn.v_proj.weight", 1 << 16)
+    assert ty == TYPE_F32
+    a, b = StreamingDecoder(ref_model, 12), StreamingDecoder(model, 12)
+    try:
+        for t in [1, 5, 2, 7, 0, 3, 6, 4]:
+            la, _ = a.step_forward([t])
+            lb, _ = b.step_forward([t])
+            rms = float(np.sqrt(np.mean(la.astype(np.float64) ** 2)))
+            assert np.max(np.abs(la - lb)) < 1e-5 * max(rms, 1.0)
+        assert a.batch == 1
+    finally:
+        a.close(); b.close(); model.close(); ref_model.close()
