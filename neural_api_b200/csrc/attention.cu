@@ -753,6 +753,342 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
 }
 
 // ---------------------------------------------------------------------------
+// The int8 KV cache on the integer tensor-core path (mma.sync m16n8k32, s8 x s8 -> s32), groups of up to 5 query heads.
+//
+// The kernel above spends ~8 lane instructions per cached code (a byte-permute and half a packed subtract to make it a
+// float, G/2 packed multiply-adds): it is bound by instruction issue at a third of the copy rate. Here the codes are
+// never unpacked: they ARE the B operand of an integer matrix product, and the fp32 side (q, or p x value scale) is the
+// A operand, split exactly into three int8 limbs per head (value = s * (l0 + l1/128 + l2/16384), s a power of two, the
+// residue below 2^-21 of the largest magnitude), so the 16 rows of the instruction hold 3 limbs x up to 5 heads.
+// Every integer product and sum is exact; the limb split is the only approximation, at fp32's own level.
+//
+//   Q.K   A = q limbs [16][d], B = K codes [d][8 rows]: a thread's B registers are its 16-byte loads of the rows, used as
+//         they arrive (which 32 channels one instruction covers is free as long as A is permuted the same way);
+//         scores leave through shared memory to lane = row, where the limbs are summed, the row scale and the head's
+//         power of two applied, and the online softmax runs as in the kernels above (fp32).
+//   P.V   A = limbs of p_j * vscale_j (scaled per 32-row tile by a power of two above the tile's largest value scale),
+//         B = V codes [32 rows][8 channels]: a thread loads 16 (8) bytes of 8 rows and transposes 4x4 byte blocks
+//         with byte-permutes (8 per 16 codes); the s32 result of a tile is added into fp32 accumulators, one per
+//         (head, limb) row, with the tile's factor; the limb rows are summed once, at the end.
+// Work split, masking of the rows past the end, partial format and merge orders are those of the kernel above.
+// ---------------------------------------------------------------------------
+constexpr int I8M_SROW = 40;                                     // words between score rows in shared memory (conflict-free stores)
+constexpr int I8M_THREADS = 64;                                  // two warps: each scores 32 of a tile's 64 rows and owns half of the channels
+constexpr int I8M_SCRATCH = 2 * 15 * I8M_SROW * 4 + 16 * 64 + 2 * 8 * 4 + 8 * 4 + 2 * 8 * 4;   // scores, limb rows, exchange, head factors, sums
+static __host__ __device__ inline int i8m_slot_bytes(int HD) { return 64 * HD + 512; }        // 64 rows of codes (the K slot: and the rows' 2 x 64 scales)
+static __host__ __device__ inline int i8m_smem_bytes(int HD) { return 16 * HD + 2 * i8m_slot_bytes(HD) + I8M_SCRATCH; }
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const int (&c)[4]) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// three int8 limbs of t (|t| <= 64): t = l0 + l1/128 + l2/16384 + residue, |residue| <= 2^-15; every step is exact
+__device__ __forceinline__ void i8m_limbs(float t, int& l0, int& l1, int& l2) {
+  const float f0 = rintf(t);
+  float r = (t - f0) * 128.0f;
+  const float f1 = rintf(r);
+  r = (r - f1) * 128.0f;
+  l0 = (int)f0; l1 = (int)f1; l2 = (int)rintf(r);
+}
+__device__ __forceinline__ void i8m_cp4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint2 i8m_lds8(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t i8m_lds4(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+// Where 16-byte piece `piece` of tile row `row` sits in a stage. K rows: a thread reads two neighbouring rows' pieces
+// {0,2,4,6} + i at once (head_dim 128) or all four pieces of two rows (head_dim 64), and the block-transposed cache
+// arrives as one piece of 32 consecutive rows per copy instruction. V rows: a thread reads part of one piece of rows r,
+// r + 4, r + 8, r + 12 at once. Both swizzles keep those accesses free of bank conflicts.
+template <int HD> __device__ __forceinline__ int i8m_k_slot(int row, int piece) { return HD == 128 ? (piece ^ (row & 7)) : (piece ^ ((row >> 1) & 3)); }
+template <int HD> __device__ __forceinline__ int i8m_v_slot(int row, int piece) { return HD == 128 ? (piece ^ (((row >> 2) & 3) << 1)) : (piece ^ (((row >> 2) & 1) << 1)); }
+
+template <int G, int HD>
+__global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(const AttnParams p) {
+  static_assert(3 * G <= 15, "three limbs of every head in the 16 rows of one instruction");
+  constexpr int KP = HD / 64;                          // 16-byte pieces of a K row per thread and 8-row tile
+  constexpr int KS = HD / 32;                          // K steps of the score product
+  constexpr int E = HD / 16;                           // V channels per thread = instructions of the value product per 32 rows
+  constexpr int PPR = HD / 16;                         // 16-byte pieces per cached row
+  constexpr int SLOT = 64 * HD + 512;                  // a tile's K (or V) rows; the K slot also holds the rows' key and value scales
+  extern __shared__ __align__(16) unsigned char smem_i8m[];
+  pdl_trigger();
+  pdl_wait();
+  const int g = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;           // the instruction's row / column group and position in it
+  if (!attn_len_ok(p, p.cache_len[b])) return;
+  int base, n;
+  attn_range(p, p.cache_len[b], base, n);
+  const int chunk = attn_chunk(n - base, p.nsplit, p.min_chunk);
+  const int used = (n - base + chunk - 1) / chunk;
+  if (split >= used) return;
+  const int j_begin = base + split * chunk;
+  int j_end = j_begin + chunk; if (j_end > n) j_end = n;
+
+  int8_t* aq = (int8_t*)smem_i8m;                                            // [16][HD] limbs of q
+  unsigned char* ring_p = smem_i8m + 16 * HD;
+  const uint32_t k_sl = (uint32_t)__cvta_generic_to_shared(ring_p), v_sl = k_sl + SLOT;   // the K slot and the V slot
+  unsigned char* scratch = ring_p + 2 * SLOT;
+  int* s_s = (int*)scratch + warp * 15 * I8M_SROW;                           // this warp's scores [15][I8M_SROW]
+  int8_t* ap = (int8_t*)(scratch + 2 * 15 * I8M_SROW * 4);                   // limbs of p x vscale [16][64 rows]
+  float* xch = (float*)(ap + 16 * 64);                                       // [2 warps][8]: maxima of the warp's 32 rows (G scores, 1 value scale)
+  float* qs_s = xch + 16;                                                    // [8] power of two of each head's limbs
+  float* l_s = qs_s + 8;                                                     // [2 warps][8] sums at the end
+  float* st = (float*)ring_p;                                                // after the loop: accumulators [16][HD]
+
+  const int bs = p.seq_index ? p.seq_index[b] : b;
+  const int64_t plane = ((int64_t)bs * p.kv_heads + g) * (int64_t)p.max_ctx;
+  const int8_t* kbase = p.k_codes + plane * HD;
+  const int8_t* vbase = p.v_codes + plane * HD;
+  const float* ksc = p.k_scales + plane;
+  const float* vsc = p.v_scales + plane;
+
+  // One slot each for a tile's K rows and V rows, refilled as soon as its readers are through: the next tile's K rows
+  // fly during this tile's softmax and value product, its V rows during the next score product. One commit group per
+  // call (rows past the end re-read the last row and are masked; nothing once the tiles are through).
+  auto fill_k = [&](int tile) {
+    if (tile < j_end) {
+#pragma unroll
+      for (int it = 0; it < PPR; ++it) {
+        int row, piece;
+        if (p.k_blocked) { row = tid; piece = it; } else { row = (it * 64 + tid) / PPR; piece = (it * 64 + tid) % PPR; }
+        int r = tile + row; if (r > j_end - 1) r = j_end - 1;
+        const int8_t* src = p.k_blocked ? kbase + (int64_t)(r >> 5) * 32 * HD + piece * 512 + (r & 31) * 16 : kbase + (int64_t)r * HD + piece * 16;
+        gv_cp_async16(k_sl + row * HD + i8m_k_slot<HD>(row, piece) * 16, src, 16u);
+      }
+      int r = tile + tid; if (r > j_end - 1) r = j_end - 1;
+      i8m_cp4(k_sl + 64 * HD + tid * 4, ksc + r);
+      i8m_cp4(k_sl + 64 * HD + 256 + tid * 4, vsc + r);
+    }
+    gv_cp_async_commit();
+  };
+  auto fill_v = [&](int tile) {
+    if (tile < j_end) {
+#pragma unroll
+      for (int it = 0; it < PPR; ++it) {
+        const int row = (it * 64 + tid) / PPR, piece = (it * 64 + tid) % PPR;
+        int r = tile + row; if (r > j_end - 1) r = j_end - 1;
+        gv_cp_async16(v_sl + row * HD + i8m_v_slot<HD>(row, piece) * 16, vbase + (int64_t)r * HD + piece * 16, 16u);
+      }
+    }
+    gv_cp_async_commit();
+  };
+  // the first rows start to move before the query is even read
+  int tile = j_begin;
+  fill_k(tile);
+
+  // q -> limbs (warp w takes heads w, w + 2, ...); rows 3G..15 of both A matrices stay zero
+  const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * HD;
+  for (int i = tid; i < (16 - 3 * G) * HD; i += I8M_THREADS) aq[3 * G * HD + i] = 0;
+  for (int i = tid; i < 16 * 64 / 4; i += I8M_THREADS) ((uint32_t*)ap)[i] = 0u;
+  for (int h = warp; h < G; h += 2) {
+    float mx = 0.f;
+    for (int d = lane; d < HD; d += 32) mx = fmaxf(mx, fabsf(qrow[h * HD + d]));
+    mx = warp_max(mx);
+    int e = (mx > 0.f && mx < 3.0e38f) ? ilogbf(mx) - 5 : 0;                // |q| / 2^e < 64
+    e = e < -100 ? -100 : (e > 100 ? 100 : e);
+    const float inv = ldexpf(1.f, -e);
+    if (lane == 0) qs_s[h] = ldexpf(1.f, e);
+    for (int d = lane; d < HD; d += 32) {
+      int l0, l1, l2;
+      i8m_limbs(qrow[h * HD + d] * inv, l0, l1, l2);
+      aq[(3 * h + 0) * HD + d] = (int8_t)l0;
+      aq[(3 * h + 1) * HD + d] = (int8_t)l1;
+      aq[(3 * h + 2) * HD + d] = (int8_t)l2;
+    }
+  }
+  __syncthreads();
+  // this thread's A registers of the score product: K step s pairs with words 2(s&1), 2(s&1)+1 of the thread's piece
+  // 2 tig + (s >> 1) (head_dim 128) or tig (head_dim 64) of the K rows
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int s = 0; s < KS; ++s) {
+    const int word = (KP == 2 ? 2 * tig + (s >> 1) : tig) * 4 + 2 * (s & 1);
+    const uint32_t* a32 = (const uint32_t*)aq;
+    qa[s][0] = a32[gid * (HD / 4) + word];
+    qa[s][1] = a32[(gid + 8) * (HD / 4) + word];
+    qa[s][2] = a32[gid * (HD / 4) + word + 1];
+    qa[s][3] = a32[(gid + 8) * (HD / 4) + word + 1];
+  }
+  float qs[G];
+#pragma unroll
+  for (int h = 0; h < G; ++h) qs[h] = qs_s[h];
+
+  float m[G], l[G];                                    // m: the same in both warps; l: the sum over this warp's rows
+  float acc[E][4];
+#pragma unroll
+  for (int h = 0; h < G; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
+#pragma unroll
+  for (int e = 0; e < E; ++e) { acc[e][0] = 0.f; acc[e][1] = 0.f; acc[e][2] = 0.f; acc[e][3] = 0.f; }
+  // rows gid and gid + 8 of the value product: limb (row % 3) of head (row / 3)
+  const int h_lo = gid / 3, h_hi = (gid + 8) / 3;
+  const float pw_lo = (gid % 3 == 0) ? 1.f : ((gid % 3 == 1) ? 0.0078125f : 6.103515625e-05f);
+  const float pw_hi = ((gid + 8) % 3 == 0) ? 1.f : (((gid + 8) % 3 == 1) ? 0.0078125f : 6.103515625e-05f);
+
+  for (; tile < j_end; tile += 64) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's copies of the tile's K rows have landed
+    __syncthreads();                                    // ... and everybody else's; the V slot's readers are through
+    fill_v(tile);
+    const int my = warp * 32 + lane;                    // this lane's row of the tile
+    const bool valid = tile + my < j_end;
+    float kscale, vscale;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(kscale) : "r"(k_sl + 64 * HD + my * 4));
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(vscale) : "r"(k_sl + 64 * HD + 256 + my * 4));
+    kscale *= p.inv_sqrt_d;
+    // scores of this warp's 32 rows: four 8-row tiles x KS steps
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int row = warp * 32 + nt * 8 + gid;
+      int4 kw[KP];
+#pragma unroll
+      for (int i = 0; i < KP; ++i) kw[i] = gv_lds16(k_sl + row * HD + i8m_k_slot<HD>(row, KP == 2 ? 2 * tig + i : tig) * 16);
+      int d[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int s = 0; s < KS; ++s) {
+        const int4 w = kw[s >> 1];
+        mma_s8(d, qa[s], (uint32_t)((s & 1) ? w.z : w.x), (uint32_t)((s & 1) ? w.w : w.y), d);
+      }
+      *(int2*)(s_s + gid * I8M_SROW + nt * 8 + 2 * tig) = make_int2(d[0], d[1]);
+      if (gid + 8 < 15) *(int2*)(s_s + (gid + 8) * I8M_SROW + nt * 8 + 2 * tig) = make_int2(d[2], d[3]);
+    }
+    __syncwarp();
+    float sc[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float s0 = (float)s_s[(3 * h) * I8M_SROW + lane], s1 = (float)s_s[(3 * h + 1) * I8M_SROW + lane], s2 = (float)s_s[(3 * h + 2) * I8M_SROW + lane];
+      const float dot = fmaf(fmaf(s2, 0.0078125f, s1), 0.0078125f, s0) * qs[h];
+      sc[h] = valid ? dot * kscale : -INFINITY;
+      const float mx = warp_max(sc[h]);
+      if (lane == 0) xch[warp * 8 + h] = mx;
+    }
+    {
+      const float vmx = warp_max(valid ? vscale : 0.f);
+      if (lane == 0) xch[warp * 8 + 7] = vmx;
+    }
+    __syncthreads();                                    // the maxima are out; the K slot's readers are through
+    fill_k(tile + 64);
+    // the power of two all of the tile's p x vscale are scaled by: above the largest value scale (p <= 1)
+    const float vmax = fmaxf(xch[7], xch[15]);
+    float ts = 1.f;
+    if (vmax > 1e-30f && vmax < 1e30f) ts = __uint_as_float((__float_as_uint(vmax) & 0x7F800000u) + 0x00800000u);
+    const float to_u = 64.0f / ts;
+    bool rescale = false;
+    float corr[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      const float mnew = fmaxf(m[h], fmaxf(xch[h], xch[8 + h]));
+      const float pj = valid ? expf(sc[h] - mnew) : 0.f;
+      const float psum = warp_sum(pj);
+      corr[h] = expf(m[h] - mnew);
+      rescale = rescale || (corr[h] != 1.f);
+      l[h] = l[h] * corr[h] + psum;
+      m[h] = mnew;
+      int l0, l1, l2;
+      i8m_limbs(pj * vscale * to_u, l0, l1, l2);
+      ap[(3 * h + 0) * 64 + my] = (int8_t)l0;
+      ap[(3 * h + 1) * 64 + my] = (int8_t)l1;
+      ap[(3 * h + 2) * 64 + my] = (int8_t)l2;
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // this thread's copies of the tile's V rows (the next K rows may still fly)
+    __syncthreads();                                    // the limbs are out, the V rows are in
+    if (rescale) {                                      // the same in every thread: m and corr come out of the exchanged maxima
+      float c_lo = 1.f, c_hi = 1.f;
+#pragma unroll
+      for (int h = 0; h < G; ++h) { if (h_lo == h) c_lo = corr[h]; if (h_hi == h) c_hi = corr[h]; }
+#pragma unroll
+      for (int e = 0; e < E; ++e) { acc[e][0] *= c_lo; acc[e][1] *= c_lo; acc[e][2] *= c_hi; acc[e][3] *= c_hi; }
+    }
+    // the value product over the tile's 64 rows (two K steps summed in s32) for this warp's half of the channels:
+    // E channels from byte warp * HD/2 + gid * E on, of rows 4 tig .. 4 tig + 3 and 16 + 4 tig .. + 3 of each 32-row half
+    int dv[E][4];
+#pragma unroll
+    for (int e = 0; e < E; ++e) { dv[e][0] = 0; dv[e][1] = 0; dv[e][2] = 0; dv[e][3] = 0; }
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t pa[4];
+      pa[0] = ((const uint32_t*)ap)[gid * 16 + ks * 8 + tig];
+      pa[1] = ((const uint32_t*)ap)[(gid + 8) * 16 + ks * 8 + tig];
+      pa[2] = ((const uint32_t*)ap)[gid * 16 + ks * 8 + 4 + tig];
+      pa[3] = ((const uint32_t*)ap)[(gid + 8) * 16 + ks * 8 + 4 + tig];
+      uint32_t vw[8][E / 4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = ks * 32 + (i >> 2) * 16 + 4 * tig + (i & 3);
+        if (E == 8) {
+          const uint2 v = i8m_lds8(v_sl + row * HD + i8m_v_slot<HD>(row, warp * 4 + (gid >> 1)) * 16 + (gid & 1) * 8);
+          vw[i][0] = v.x; vw[i][E / 4 - 1] = v.y;
+        } else {
+          vw[i][0] = i8m_lds4(v_sl + row * HD + i8m_v_slot<HD>(row, warp * 2 + (gid >> 2)) * 16 + (gid & 3) * 4);
+        }
+      }
+#pragma unroll
+      for (int w = 0; w < E / 4; ++w) {
+        uint32_t o[2][4];
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {             // 4 x 4 byte transpose: word w of four rows -> one register per channel
+          const uint32_t t0 = __byte_perm(vw[grp * 4 + 0][w], vw[grp * 4 + 1][w], 0x5140), t1 = __byte_perm(vw[grp * 4 + 0][w], vw[grp * 4 + 1][w], 0x7362);
+          const uint32_t t2 = __byte_perm(vw[grp * 4 + 2][w], vw[grp * 4 + 3][w], 0x5140), t3 = __byte_perm(vw[grp * 4 + 2][w], vw[grp * 4 + 3][w], 0x7362);
+          o[grp][0] = __byte_perm(t0, t2, 0x5410); o[grp][1] = __byte_perm(t0, t2, 0x7632);
+          o[grp][2] = __byte_perm(t1, t3, 0x5410); o[grp][3] = __byte_perm(t1, t3, 0x7632);
+        }
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4) mma_s8(dv[w * 4 + e4], pa, o[0][e4], o[1][e4], dv[w * 4 + e4]);
+      }
+    }
+    const float f_lo = ts * 0.015625f * pw_lo, f_hi = ts * 0.015625f * pw_hi;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      acc[e][0] = fmaf(f_lo, (float)dv[e][0], acc[e][0]);
+      acc[e][1] = fmaf(f_lo, (float)dv[e][1], acc[e][1]);
+      acc[e][2] = fmaf(f_hi, (float)dv[e][2], acc[e][2]);
+      acc[e][3] = fmaf(f_hi, (float)dv[e][3], acc[e][3]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  // accumulators -> [16][HD] over the ring (column n of instruction e is channel warp * HD/2 + n * E + e); the limb
+  // rows of a head are summed below
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int c0 = warp * (HD / 2) + (2 * tig) * E + e, c1 = warp * (HD / 2) + (2 * tig + 1) * E + e;
+    st[gid * HD + c0] = acc[e][0];
+    st[gid * HD + c1] = acc[e][1];
+    st[(gid + 8) * HD + c0] = acc[e][2];
+    st[(gid + 8) * HD + c1] = acc[e][3];
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int h = 0; h < G; ++h) l_s[warp * 8 + h] = l[h];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * HD; idx += I8M_THREADS) {
+    const int hh = idx / HD, d = idx % HD;
+    float mh = -INFINITY;                               // m[hh] without a dynamically indexed register array
+#pragma unroll
+    for (int h = 0; h < G; ++h) if (h == hh) mh = m[h];
+    const float lt = l_s[hh] + l_s[8 + hh];
+    const float at = (st[(3 * hh) * HD + d] + st[(3 * hh + 1) * HD + d]) + st[(3 * hh + 2) * HD + d];
+    const int h = g * G + hh;
+    if (used == 1) {
+      p.out[(int64_t)b * p.ldo + (int64_t)h * HD + d] = (lt > 0.f) ? at / lt : 0.f;
+    } else {
+      float* dst = p.partial + (((int64_t)b * p.q_heads + h) * p.nsplit + split) * (HD + 2);
+      if (d == 0) { dst[0] = mh; dst[1] = lt; }
+      dst[2 + d] = at;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // The same attention with the cached rows staged through shared memory by cp.async instead of ordinary loads.
 // The kernel above is a chain of dependent round trips per warp (K pieces, then V rows, then the next tile), so the
 // memory pipe idles between them: 3.5 TB/s at context 8192 (long-scoreboard stall of 5 warps per issue). Here every
@@ -1004,6 +1340,29 @@ static void launch_tile_int8(cai_ctx* ctx, int G, dim3 grid, size_t smem, const 
   }
 }
 
+template <int G, int HD>
+static int launch_mma_int8_one(cai_ctx* ctx, dim3 grid, const AttnParams& p) {
+  static bool configured[64] = {false};
+  const size_t smem = (size_t)i8m_smem_bytes(HD);
+  const int dev = ctx->device;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    CAI_CUDA(ctx, cudaFuncSetAttribute(attn_decode_mma_int8_kernel<G, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = true;
+  }
+  pdl_launch(ctx, attn_decode_mma_int8_kernel<G, HD>, grid, dim3(I8M_THREADS), smem, p);
+  return CAI_OK;
+}
+template <int HD>
+static int launch_mma_int8(cai_ctx* ctx, int G, dim3 grid, const AttnParams& p) {
+  switch (G) {
+    case 1: return launch_mma_int8_one<1, HD>(ctx, grid, p);
+    case 2: return launch_mma_int8_one<2, HD>(ctx, grid, p);
+    case 3: return launch_mma_int8_one<3, HD>(ctx, grid, p);
+    case 4: return launch_mma_int8_one<4, HD>(ctx, grid, p);
+    default: return launch_mma_int8_one<5, HD>(ctx, grid, p);
+  }
+}
+
 template <int HD>
 static void launch_tile(cai_ctx* ctx, int G, dim3 grid, size_t smem, const AttnParams& p) {
   switch (G) {
@@ -1117,7 +1476,12 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
       return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 KV cache: head_dim 64 or 128 and groups of up to 8 query heads");
     p.min_chunk = ATTN_TILE_MIN_CHUNK;
     const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 32 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
-    if (a.head_dim == 128) launch_tile_int8<128>(ctx, G, grid, tsmem, p);
+    // groups of up to 5 query heads run on the integer tensor-core kernel (CAI_ATTN_I8MMA=0: the CUDA-core kernel)
+    static const int use_mma = [] { const char* e = getenv("CAI_ATTN_I8MMA"); return (e && *e) ? atoi(e) : 1; }();
+    if (use_mma && G <= 5) {
+      if (a.head_dim == 128) { CAI_TRY(launch_mma_int8<128>(ctx, G, grid, p)); }
+      else { CAI_TRY(launch_mma_int8<64>(ctx, G, grid, p)); }
+    } else if (a.head_dim == 128) launch_tile_int8<128>(ctx, G, grid, tsmem, p);
     else launch_tile_int8<64>(ctx, G, grid, tsmem, p);
     CAI_LAUNCHED(ctx);
     if (a.nsplit > 1) {
