@@ -774,7 +774,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32, 4) attn_decode_tile_int8_kern
 // ---------------------------------------------------------------------------
 constexpr int I8M_SROW = 40;                                     // words between score rows in shared memory (conflict-free stores)
 constexpr int I8M_THREADS = 64;                                  // two warps: each scores 32 of a tile's 64 rows and owns half of the channels
-constexpr int I8M_SCRATCH = 2 * 15 * I8M_SROW * 4 + 16 * 64 + 2 * 8 * 4 + 8 * 4 + 2 * 8 * 4;   // scores, limb rows, exchange, head factors, sums
+constexpr int I8M_PROW = 80;                                     // bytes between limb rows (64 used: conflict-free fragment loads)
+constexpr int I8M_SCRATCH = 2 * 15 * I8M_SROW * 4 + 16 * I8M_PROW + 2 * 8 * 4 + 8 * 4 + 2 * 8 * 4;   // scores, limb rows, exchange, head factors, sums
 static __host__ __device__ inline int i8m_slot_bytes(int HD) { return 64 * HD + 512; }        // 64 rows of codes (the K slot: and the rows' 2 x 64 scales)
 static __host__ __device__ inline int i8m_smem_bytes(int HD) { return 16 * HD + 2 * i8m_slot_bytes(HD) + I8M_SCRATCH; }
 
@@ -784,12 +785,25 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 // three int8 limbs of t (|t| <= 64): t = l0 + l1/128 + l2/16384 + residue, |residue| <= 2^-15; every step is exact
+// (rounding through the 1.5 * 2^23 constant: the sum's low mantissa bits are the rounded integer in two's complement,
+// so the limb's byte is the low byte of the sum's bit pattern and no conversion instruction is needed)
 __device__ __forceinline__ void i8m_limbs(float t, int& l0, int& l1, int& l2) {
-  const float f0 = rintf(t);
-  float r = (t - f0) * 128.0f;
-  const float f1 = rintf(r);
-  r = (r - f1) * 128.0f;
-  l0 = (int)f0; l1 = (int)f1; l2 = (int)rintf(r);
+  const float magic = 12582912.0f;
+  const float x0 = t + magic;
+  float r = (t - (x0 - magic)) * 128.0f;
+  const float x1 = r + magic;
+  r = (r - (x1 - magic)) * 128.0f;
+  const float x2 = r + magic;
+  l0 = __float_as_int(x0); l1 = __float_as_int(x1); l2 = __float_as_int(x2);   // only the low byte is the limb
+}
+// the largest value of a warp in one instruction: floats compare like the integers their bits map to below
+__device__ __forceinline__ float i8m_warp_max(float v) {
+  int k = __float_as_int(v);
+  k ^= (k >> 31) & 0x7FFFFFFF;
+  int r;
+  asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(r) : "r"(k));
+  r ^= (r >> 31) & 0x7FFFFFFF;
+  return __int_as_float(r);
 }
 __device__ __forceinline__ void i8m_cp4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
@@ -839,8 +853,8 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
   const uint32_t k_sl = (uint32_t)__cvta_generic_to_shared(ring_p), v_sl = k_sl + SLOT;   // the K slot and the V slot
   unsigned char* scratch = ring_p + 2 * SLOT;
   int* s_s = (int*)scratch + warp * 15 * I8M_SROW;                           // this warp's scores [15][I8M_SROW]
-  int8_t* ap = (int8_t*)(scratch + 2 * 15 * I8M_SROW * 4);                   // limbs of p x vscale [16][64 rows]
-  float* xch = (float*)(ap + 16 * 64);                                       // [2 warps][8]: maxima of the warp's 32 rows (G scores, 1 value scale)
+  int8_t* ap = (int8_t*)(scratch + 2 * 15 * I8M_SROW * 4);                   // limbs of p x vscale [16][I8M_PROW], 64 rows used
+  float* xch = (float*)(ap + 16 * I8M_PROW);                                       // [2 warps][8]: maxima of the warp's 32 rows (G scores, 1 value scale)
   float* qs_s = xch + 16;                                                    // [8] power of two of each head's limbs
   float* l_s = qs_s + 8;                                                     // [2 warps][8] sums at the end
   float* st = (float*)ring_p;                                                // after the loop: accumulators [16][HD]
@@ -855,8 +869,26 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
   // One slot each for a tile's K rows and V rows, refilled as soon as its readers are through: the next tile's K rows
   // fly during this tile's softmax and value product, its V rows during the next score product. One commit group per
   // call (rows past the end re-read the last row and are masked; nothing once the tiles are through).
+  // The parts of the copy addresses that do not change from tile to tile (whole tiles that start on a block boundary
+  // take them; the last, partial tile and a window's odd start go row by row).
+  const bool blk = p.k_blocked != 0;
+  const int k_src0 = blk ? (tid >> 5) * 32 * HD + (tid & 31) * 16 : (tid / PPR) * HD + (tid % PPR) * 16;
+  const int k_sstep = blk ? 512 : (64 / PPR) * HD;                         // source bytes between this thread's copies
+  const int k_swz = blk ? (HD == 128 ? (tid & 7) : ((tid >> 1) & 3)) : 0;
+  const uint32_t k_dst0 = blk ? (uint32_t)(tid * HD) : (uint32_t)((tid / PPR) * HD + i8m_k_slot<HD>(tid / PPR, tid % PPR) * 16);
+  const int v_src0 = (tid / PPR) * HD + (tid % PPR) * 16;
   auto fill_k = [&](int tile) {
-    if (tile < j_end) {
+    if (tile + 64 <= j_end && (!blk || (tile & 31) == 0)) {
+      const int8_t* src = kbase + (int64_t)tile * HD + k_src0;
+#pragma unroll
+      for (int it = 0; it < PPR; ++it) {
+        // block-transposed: row tid, piece it; row-major: row tid / PPR + it * 64 / PPR (same swizzle in every step), piece tid % PPR
+        const uint32_t dst = blk ? k_sl + k_dst0 + ((it ^ k_swz) << 4) : k_sl + k_dst0 + it * (64 / PPR) * HD;
+        gv_cp_async16(dst, src + it * k_sstep, 16u);
+      }
+      i8m_cp4(k_sl + 64 * HD + tid * 4, ksc + tile + tid);
+      i8m_cp4(k_sl + 64 * HD + 256 + tid * 4, vsc + tile + tid);
+    } else if (tile < j_end) {
 #pragma unroll
       for (int it = 0; it < PPR; ++it) {
         int row, piece;
@@ -872,7 +904,14 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
     gv_cp_async_commit();
   };
   auto fill_v = [&](int tile) {
-    if (tile < j_end) {
+    if (tile + 64 <= j_end) {
+      const int8_t* src = vbase + (int64_t)tile * HD + v_src0;
+#pragma unroll
+      for (int it = 0; it < PPR; ++it) {
+        const int row = tid / PPR + it * (64 / PPR);
+        gv_cp_async16(v_sl + row * HD + i8m_v_slot<HD>(row, tid % PPR) * 16, src + it * (64 / PPR) * HD, 16u);
+      }
+    } else if (tile < j_end) {
 #pragma unroll
       for (int it = 0; it < PPR; ++it) {
         const int row = (it * 64 + tid) / PPR, piece = (it * 64 + tid) % PPR;
@@ -889,7 +928,7 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
   // q -> limbs (warp w takes heads w, w + 2, ...); rows 3G..15 of both A matrices stay zero
   const float* qrow = p.qkv + (int64_t)b * p.ld + (int64_t)g * G * HD;
   for (int i = tid; i < (16 - 3 * G) * HD; i += I8M_THREADS) aq[3 * G * HD + i] = 0;
-  for (int i = tid; i < 16 * 64 / 4; i += I8M_THREADS) ((uint32_t*)ap)[i] = 0u;
+  for (int i = tid; i < 16 * I8M_PROW / 4; i += I8M_THREADS) ((uint32_t*)ap)[i] = 0u;
   for (int h = warp; h < G; h += 2) {
     float mx = 0.f;
     for (int d = lane; d < HD; d += 32) mx = fmaxf(mx, fabsf(qrow[h * HD + d]));
@@ -923,7 +962,7 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
 #pragma unroll
   for (int h = 0; h < G; ++h) qs[h] = qs_s[h];
 
-  float m[G], l[G];                                    // m: the same in both warps; l: the sum over this warp's rows
+  float m[G], l[G];                                    // m: the same in both warps; l: the sum over this lane's rows
   float acc[E][4];
 #pragma unroll
   for (int h = 0; h < G; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
@@ -934,6 +973,13 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
   const float pw_lo = (gid % 3 == 0) ? 1.f : ((gid % 3 == 1) ? 0.0078125f : 6.103515625e-05f);
   const float pw_hi = ((gid + 8) % 3 == 0) ? 1.f : (((gid + 8) % 3 == 1) ? 0.0078125f : 6.103515625e-05f);
 
+  // where this thread reads its operands in the slots: the swizzles depend on the row only through bits that the row
+  // offsets added per step do not touch
+  uint32_t k_rd[KP];
+#pragma unroll
+  for (int i = 0; i < KP; ++i) k_rd[i] = k_sl + (warp * 32 + gid) * HD + i8m_k_slot<HD>(gid, KP == 2 ? 2 * tig + i : tig) * 16;
+  const uint32_t v_rd = (E == 8) ? v_sl + (4 * tig) * HD + i8m_v_slot<HD>(4 * tig, warp * 4 + (gid >> 1)) * 16 + (gid & 1) * 8
+                                 : v_sl + (4 * tig) * HD + i8m_v_slot<HD>(4 * tig, warp * 2 + (gid >> 2)) * 16 + (gid & 3) * 4;
   for (; tile < j_end; tile += 64) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's copies of the tile's K rows have landed
     __syncthreads();                                    // ... and everybody else's; the V slot's readers are through
@@ -947,10 +993,9 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
     // scores of this warp's 32 rows: four 8-row tiles x KS steps
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
-      const int row = warp * 32 + nt * 8 + gid;
       int4 kw[KP];
 #pragma unroll
-      for (int i = 0; i < KP; ++i) kw[i] = gv_lds16(k_sl + row * HD + i8m_k_slot<HD>(row, KP == 2 ? 2 * tig + i : tig) * 16);
+      for (int i = 0; i < KP; ++i) kw[i] = gv_lds16(k_rd[i] + nt * 8 * HD);
       int d[4] = {0, 0, 0, 0};
 #pragma unroll
       for (int s = 0; s < KS; ++s) {
@@ -967,11 +1012,11 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
       const float s0 = (float)s_s[(3 * h) * I8M_SROW + lane], s1 = (float)s_s[(3 * h + 1) * I8M_SROW + lane], s2 = (float)s_s[(3 * h + 2) * I8M_SROW + lane];
       const float dot = fmaf(fmaf(s2, 0.0078125f, s1), 0.0078125f, s0) * qs[h];
       sc[h] = valid ? dot * kscale : -INFINITY;
-      const float mx = warp_max(sc[h]);
+      const float mx = i8m_warp_max(sc[h]);
       if (lane == 0) xch[warp * 8 + h] = mx;
     }
     {
-      const float vmx = warp_max(valid ? vscale : 0.f);
+      const float vmx = i8m_warp_max(valid ? vscale : 0.f);
       if (lane == 0) xch[warp * 8 + 7] = vmx;
     }
     __syncthreads();                                    // the maxima are out; the K slot's readers are through
@@ -987,16 +1032,15 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
     for (int h = 0; h < G; ++h) {
       const float mnew = fmaxf(m[h], fmaxf(xch[h], xch[8 + h]));
       const float pj = valid ? expf(sc[h] - mnew) : 0.f;
-      const float psum = warp_sum(pj);
-      corr[h] = expf(m[h] - mnew);
+      corr[h] = (mnew == m[h]) ? 1.f : expf(m[h] - mnew);     // the same in every thread
       rescale = rescale || (corr[h] != 1.f);
-      l[h] = l[h] * corr[h] + psum;
+      l[h] = l[h] * corr[h] + pj;                             // this lane's rows only: the lanes are summed once, at the end
       m[h] = mnew;
       int l0, l1, l2;
       i8m_limbs(pj * vscale * to_u, l0, l1, l2);
-      ap[(3 * h + 0) * 64 + my] = (int8_t)l0;
-      ap[(3 * h + 1) * 64 + my] = (int8_t)l1;
-      ap[(3 * h + 2) * 64 + my] = (int8_t)l2;
+      ap[(3 * h + 0) * I8M_PROW + my] = (int8_t)l0;
+      ap[(3 * h + 1) * I8M_PROW + my] = (int8_t)l1;
+      ap[(3 * h + 2) * I8M_PROW + my] = (int8_t)l2;
     }
     asm volatile("cp.async.wait_group 1;" ::: "memory");  // this thread's copies of the tile's V rows (the next K rows may still fly)
     __syncthreads();                                    // the limbs are out, the V rows are in
@@ -1015,19 +1059,19 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
       uint32_t pa[4];
-      pa[0] = ((const uint32_t*)ap)[gid * 16 + ks * 8 + tig];
-      pa[1] = ((const uint32_t*)ap)[(gid + 8) * 16 + ks * 8 + tig];
-      pa[2] = ((const uint32_t*)ap)[gid * 16 + ks * 8 + 4 + tig];
-      pa[3] = ((const uint32_t*)ap)[(gid + 8) * 16 + ks * 8 + 4 + tig];
+      pa[0] = ((const uint32_t*)ap)[gid * (I8M_PROW / 4) + ks * 8 + tig];
+      pa[1] = ((const uint32_t*)ap)[(gid + 8) * (I8M_PROW / 4) + ks * 8 + tig];
+      pa[2] = ((const uint32_t*)ap)[gid * (I8M_PROW / 4) + ks * 8 + 4 + tig];
+      pa[3] = ((const uint32_t*)ap)[(gid + 8) * (I8M_PROW / 4) + ks * 8 + 4 + tig];
       uint32_t vw[8][E / 4];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int row = ks * 32 + (i >> 2) * 16 + 4 * tig + (i & 3);
+        const int row0 = ks * 32 + (i >> 2) * 16 + (i & 3);          // the row is row0 + 4 tig
         if (E == 8) {
-          const uint2 v = i8m_lds8(v_sl + row * HD + i8m_v_slot<HD>(row, warp * 4 + (gid >> 1)) * 16 + (gid & 1) * 8);
+          const uint2 v = i8m_lds8(v_rd + row0 * HD);
           vw[i][0] = v.x; vw[i][E / 4 - 1] = v.y;
         } else {
-          vw[i][0] = i8m_lds4(v_sl + row * HD + i8m_v_slot<HD>(row, warp * 2 + (gid >> 2)) * 16 + (gid & 3) * 4);
+          vw[i][0] = i8m_lds4(v_rd + row0 * HD);
         }
       }
 #pragma unroll
@@ -1065,9 +1109,10 @@ __global__ void __launch_bounds__(I8M_THREADS, 8) attn_decode_mma_int8_kernel(co
     st[(gid + 8) * HD + c0] = acc[e][2];
     st[(gid + 8) * HD + c1] = acc[e][3];
   }
-  if (lane == 0) {
 #pragma unroll
-    for (int h = 0; h < G; ++h) l_s[warp * 8 + h] = l[h];
+  for (int h = 0; h < G; ++h) {
+    const float lw = warp_sum(l[h]);
+    if (lane == 0) l_s[warp * 8 + h] = lw;
   }
   __syncthreads();
   for (int idx = tid; idx < G * HD; idx += I8M_THREADS) {
@@ -1476,8 +1521,12 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
       return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 KV cache: head_dim 64 or 128 and groups of up to 8 query heads");
     p.min_chunk = ATTN_TILE_MIN_CHUNK;
     const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 32 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
-    // groups of up to 5 query heads run on the integer tensor-core kernel (CAI_ATTN_I8MMA=0: the CUDA-core kernel)
-    static const int use_mma = [] { const char* e = getenv("CAI_ATTN_I8MMA"); return (e && *e) ? atoi(e) : 1; }();
+    // Groups of up to 5 query heads can run on the integer tensor-core kernel. It streams 1.6x faster but starts
+    // slower (the query's limbs, two warps per CTA), so it takes the calls whose splits are long: 512 rows or more at
+    // full context (measured: 64 sequences x 8192 rows 28.2 -> 17.9 ms per 64 layers; one sequence, 128-row splits:
+    // 3.30 -> 3.45 ms). CAI_ATTN_I8MMA=1 / 0 forces it on / off; read at every call so that a test can switch it.
+    const char* mma_env = getenv("CAI_ATTN_I8MMA");
+    const bool use_mma = (mma_env && *mma_env) ? atoi(mma_env) != 0 : (a.max_ctx / (a.nsplit > 0 ? a.nsplit : 1) >= 512);
     if (use_mma && G <= 5) {
       if (a.head_dim == 128) { CAI_TRY(launch_mma_int8<128>(ctx, G, grid, p)); }
       else { CAI_TRY(launch_mma_int8<64>(ctx, G, grid, p)); }

@@ -319,18 +319,22 @@ def test_grouped_expert_batches_match_single_sequence_sessions(backend):
         model.close()
 
 
+@pytest.mark.parametrize("i8_kernel", ["0", "1"])
 @pytest.mark.parametrize("dims", [
     dict(hidden=256, inter=512, layers=2, heads=8, kv_heads=2, head_dim=64, vocab=512, qkv_bias=True),      # groups of 4
     dict(hidden=384, inter=512, layers=2, heads=3, kv_heads=3, head_dim=128, vocab=256),                   # MHA, head_dim 128
+    dict(hidden=256, inter=512, layers=1, heads=5, kv_heads=1, head_dim=128, vocab=256),                   # groups of 5 (Qwen2.5-32B)
 ])
-def test_int8_kv_cache_matches_the_oracle_int8_cache(backend, dims):
+def test_int8_kv_cache_matches_the_oracle_int8_cache(backend, monkeypatch, dims, i8_kernel):
     """The reference's default KV cache (int8 codes, one fp32 scale per row): rows are quantized when appended and
     the scales are folded into the attention sums (neural/neural.cl:2500-2687), checked against the oracle's int8
     cache. Two implementations of this cache differ wherever a value lands within float rounding of a half-way
     point and rounds to the neighbouring code (one code = 1/127 of the row maximum); on these narrow models a
     few dozen such flips over 280 positions measured 2e-3 of the logit RMS, so the gate here is 5e-3 (the
     reference holds its own device kernel to 1e-3 on its test model, tests/TestNeuralNumerical.pas:69604-69609).
-    Also truncate / snapshot / restore over the int8 buffers, and a context long enough for several splits."""
+    Also truncate / snapshot / restore over the int8 buffers, and a context long enough for several splits.
+    i8_kernel: "0" the CUDA-core kernel, "1" the integer tensor-core kernel (codes as mma operands, q and p as int8 limbs)."""
+    monkeypatch.setenv("CAI_ATTN_I8MMA", i8_kernel)
     kw = dict(rms_eps=1e-6, rope_theta=1e4, **dims)
     model = LlamaModel(backend, make_config(**kw))
     model.init_synthetic(TYPE_Q8_0, seed=21, std=0.05)
@@ -453,3 +457,36 @@ def test_fused_groups_with_members_in_different_formats_run_as_separate_matrices
         assert a.batch == 1
     finally:
         a.close(); b.close(); model.close(); ref_model.close()
+
+
+def test_int8_cache_tensor_core_kernel_equals_the_cuda_core_kernel_on_a_long_context(backend, monkeypatch):
+    """Same cache rows, same query: the integer tensor-core kernel (q and p as three exact int8 limbs) against the
+    CUDA-core kernel over 1500 cached rows, three sequences, several context splits. The limb split leaves 2^-21 of the
+    largest magnitude, so the two agree to fp32 rounding of the attention sums (measured ~1e-6 of the logit RMS)."""
+    # one layer: its cached rows do not depend on any attention output, so both runs hold identical codes (with more
+    # layers a last-bit difference upstream flips codes at rounding boundaries and the comparison measures that instead)
+    kw = dict(hidden=256, inter=512, layers=1, heads=10, kv_heads=2, head_dim=128, vocab=512, rms_eps=1e-6, rope_theta=1e4)
+    model = LlamaModel(backend, make_config(**kw))
+    model.init_synthetic(TYPE_Q8_0, seed=33, std=0.05)
+    model.finalize()
+    rng = np.random.default_rng(8)
+    prompts = rng.integers(0, kw["vocab"], (3, 1500))
+    outs = {}
+    try:
+        for kernel in ("0", "1"):
+            monkeypatch.setenv("CAI_ATTN_I8MMA", kernel)
+            sess = StreamingDecoder(model, 1600, kv_type=TYPE_I8, batch=3)
+            try:
+                sess.prefill(prompts)
+                rows = []
+                for t in (3, 4, 5):
+                    logits, _ = sess.step_forward([t, t + 1, t + 2])
+                    rows.append(logits.copy())
+                outs[kernel] = np.stack(rows)
+            finally:
+                sess.close()
+        rms = float(np.sqrt(np.mean(outs["0"].astype(np.float64) ** 2)))
+        worst = float(np.max(np.abs(outs["0"] - outs["1"]))) / rms
+        assert worst < 2e-5, worst
+    finally:
+        model.close()

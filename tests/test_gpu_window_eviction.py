@@ -78,8 +78,12 @@ def _oracle(model, cfg):
     return OracleModel.from_hf_tensors(cfg, tensors, interleave=False)
 
 
-@pytest.mark.parametrize("kv_type,tol", [(0, 1e-3), (TYPE_I8, 5e-3)])
-def test_session_eviction_and_window_match_the_oracle(backend, kv_type, tol):
+@pytest.mark.parametrize("kv_type,tol,i8_kernel", [(0, 1e-3, None), (TYPE_I8, 5e-3, "0"), (TYPE_I8, 5e-3, "1")])
+def test_session_eviction_and_window_match_the_oracle(backend, monkeypatch, kv_type, tol, i8_kernel):
+    """i8_kernel: the int8 cache's CUDA-core kernel ("0") or its integer tensor-core kernel ("1"; the window's first row is
+    not on a 32-row boundary, so its tiles take the row-by-row copy path)."""
+    if i8_kernel is not None:
+        monkeypatch.setenv("CAI_ATTN_I8MMA", i8_kernel)
     kw = dict(hidden=256, inter=512, layers=2, heads=4, kv_heads=2, head_dim=64, vocab=512, rms_eps=1e-6, rope_theta=1e4,
               tie_embeddings=True)
     model = LlamaModel(backend, make_config(**kw))
