@@ -95,6 +95,13 @@ int cai_cuda_last_error(cai_ctx* ctx, char* buf, int buf_len);
 int cai_cuda_device_info(cai_ctx* ctx, int* sm_count, int64_t* total_bytes);
 /* Number of kernels this library has launched on the context since init. */
 int cai_cuda_launch_count(cai_ctx* ctx, int64_t* out_count);
+/* 1 when this library is the checked build (libcai_cuda_checked.so, compiled with -DCAI_CHECKED): the same kernels,
+ * every launch followed by a synchronize and a look at the device error words, CUDA graphs off, and an index from
+ * device-side state that the ordinary build clamps or skips silently (an out-of-range token id, an expert id outside
+ * the bank) reported as CAI_ERR_STATE with its value and bound. 0 for the ordinary build. Needs no context.
+ * No reference counterpart. */
+int cai_cuda_is_checked_build(void);
+
 /* Longest time a kernel of this library waits on another CTA or another GPU (grid barrier of the step kernel,
  * arrival words of the tensor-parallel exchange) before it gives up, raises the context's error word and returns;
  * the next synchronizing entry point then reports CAI_ERR_CUDA and the context stays usable. Default 2 s

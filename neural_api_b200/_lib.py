@@ -7,7 +7,10 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libcai_cuda.so")
+# CAI_CUDA_CHECKED=1 binds the checked build (same entry points; every launch synchronized and looked at, indices from
+# device-side state that the ordinary build clamps silently reported as errors): `python -m neural_api_b200.build --checked`
+CHECKED = os.environ.get("CAI_CUDA_CHECKED", "") not in ("", "0")
+LIB_PATH = os.path.join(HERE, "libcai_cuda_checked.so" if CHECKED else "libcai_cuda.so")
 
 CAI_OK = 0
 TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
@@ -51,6 +54,7 @@ SIGNATURES = {
     "cai_cuda_last_error": [_P, C.c_char_p, _I],
     "cai_cuda_device_info": [_P, C.POINTER(_I), C.POINTER(_I64)],
     "cai_cuda_launch_count": [_P, C.POINTER(_I64)],
+    "cai_cuda_is_checked_build": [],
     "cai_cuda_set_wait_limit_us": [_P, C.c_uint],
     "cai_selftest_wait_timeout": [_P, _I, C.c_uint],
     "cai_dev_alloc": [_P, _I64, _PP],
@@ -154,8 +158,8 @@ def load():
         return _lib
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
-            "libcai_cuda.so is not built (%s). Run `python -m neural_api_b200.build`; "
-            "there is no CPU fallback." % LIB_PATH)
+            "%s is not built (%s). Run `python -m neural_api_b200.build%s`; "
+            "there is no CPU fallback." % (os.path.basename(LIB_PATH), LIB_PATH, " --checked" if CHECKED else ""))
     lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)          # AttributeError if the library lacks a declared symbol

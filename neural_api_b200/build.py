@@ -1,10 +1,13 @@
 """Builds libcai_cuda.so in-tree with nvcc for sm_100a.
 
-    python -m neural_api_b200.build [--force] [--verbose]
+    python -m neural_api_b200.build [--force] [--verbose] [--checked | --all]
 
 One object per .cu under csrc/, linked into neural_api_b200/libcai_cuda.so. The
 library links the CUDA runtime statically and NCCL dynamically; it does not
 link PyTorch. Objects are rebuilt when their source or a header is newer.
+--checked builds libcai_cuda_checked.so instead (-DCAI_CHECKED: every launch is
+synchronized and looked at, silent index clamps are reported; objects under
+build_checked/); --all builds both.
 """
 import os
 import subprocess
@@ -32,16 +35,17 @@ def _headers_mtime():
     return max(os.path.getmtime(p) for p in paths)
 
 
-def _compile(src, force, verbose):
-    obj = os.path.join(BUILD, src[:-3] + ".o")
+def _compile(src, force, verbose, checked=False):
+    bdir = BUILD + ("_checked" if checked else "")
+    obj = os.path.join(bdir, src[:-3] + ".o")
     srcp = os.path.join(CSRC, src)
     if (not force and os.path.exists(obj)
             and os.path.getmtime(obj) >= max(os.path.getmtime(srcp), _headers_mtime())):
         return obj, ""
-    cmd = [NVCC] + ARCH_FLAGS + COMMON + ["-c", srcp, "-o", obj]
+    cmd = [NVCC] + ARCH_FLAGS + COMMON + (["-DCAI_CHECKED=1"] if checked else []) + ["-c", srcp, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     log = r.stdout + r.stderr
-    with open(os.path.join(BUILD, src[:-3] + ".ptxas.log"), "w") as f:
+    with open(os.path.join(bdir, src[:-3] + ".ptxas.log"), "w") as f:
         f.write(log)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s" % (src, log))
@@ -50,21 +54,24 @@ def _compile(src, force, verbose):
     return obj, log
 
 
-def build(force=False, verbose=False):
-    os.makedirs(BUILD, exist_ok=True)
+def build(force=False, verbose=False, checked=False):
+    bdir = BUILD + ("_checked" if checked else "")
+    lib = os.path.join(HERE, "libcai_cuda_checked.so") if checked else LIB
+    os.makedirs(bdir, exist_ok=True)
     srcs = _sources()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        results = list(ex.map(lambda s: _compile(s, force, verbose), srcs))
+        results = list(ex.map(lambda s: _compile(s, force, verbose, checked), srcs))
     objs = [o for o, _ in results]
     newest = max(os.path.getmtime(o) for o in objs)
-    if force or not os.path.exists(LIB) or os.path.getmtime(LIB) < newest:
-        cmd = [NVCC] + ARCH_FLAGS + ["-shared", "-o", LIB] + objs + ["-cudart", "static", "-lnccl"]
+    if force or not os.path.exists(lib) or os.path.getmtime(lib) < newest:
+        cmd = [NVCC] + ARCH_FLAGS + ["-shared", "-o", lib] + objs + ["-cudart", "static", "-lnccl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
-    print(path)
+    kinds = [False, True] if "--all" in sys.argv else [("--checked" in sys.argv)]
+    for k in kinds:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, checked=k))

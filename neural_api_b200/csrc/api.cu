@@ -4,6 +4,8 @@
 #include "cai_common.cuh"
 #include <new>
 #include <stdlib.h>
+#include <string.h>
+#include <stdio.h>
 
 int cai_fail(cai_ctx* ctx, int code, const char* fmt, ...) {
   if (ctx) {
@@ -23,9 +25,31 @@ int cai_check_device_error(cai_ctx* ctx) {
       return cai_fail(ctx, CAI_ERR_STATE, "a kernel refused a cache length outside [0, max_ctx): nothing was appended or attended");
     if (code == 3)
       return cai_fail(ctx, CAI_ERR_INVALID, "a kernel met a router row without a finite maximum (NaN logits): expert ids were clamped");
+    if (code == 4) {
+      const int site = ctx->err_flag[1], value = ctx->err_flag[2], bound = ctx->err_flag[3];
+      const char* what = site == CAI_SITE_EMBED_TOKEN ? "token id in the embedding gather"
+                         : site == CAI_SITE_STEP_TOKEN ? "token id in the step kernel's embedding gather"
+                         : site == CAI_SITE_MOE_EXPERT ? "expert id in the mixture-of-experts grouping" : "index";
+      return cai_fail(ctx, CAI_ERR_STATE, "checked build: %s: %d outside [0, %d) (the ordinary build clamps or skips it silently)", what, value, bound);
+    }
     return cai_fail(ctx, CAI_ERR_CUDA, "a kernel gave up a bounded wait (device error word raised)");
   }
   return CAI_OK;
+}
+
+// Checked build only (CAI_LAUNCHED): waits for the launch just enqueued and reports what it raised, with the launch
+// site. A stream that is being captured cannot be synchronized; this build does not capture (model.cu).
+int cai_checked_after_launch(cai_ctx* ctx, const char* file, int line) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) { cudaGetLastError(); return CAI_OK; }
+  const cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "checked build: the kernel launched at %s:%d -> %s", file, line, cudaGetErrorString(e));
+  const int c = cai_check_device_error(ctx);
+  if (c != CAI_OK) {
+    const size_t n = strlen(ctx->err);
+    snprintf(ctx->err + n, sizeof(ctx->err) - n, " [launch at %s:%d]", file, line);
+  }
+  return c;
 }
 
 int cai_prof_mark(cai_ctx* ctx, int family) {
@@ -67,12 +91,12 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
     delete ctx;
     return CAI_ERR_CUDA;
   }
-  if (cudaHostAlloc((void**)&ctx->err_flag, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+  if (cudaHostAlloc((void**)&ctx->err_flag, 4 * sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
     cudaGetLastError();
     cai_cuda_shutdown(ctx);
     return CAI_ERR_CUDA;
   }
-  *ctx->err_flag = 0;
+  for (int i = 0; i < 4; ++i) ctx->err_flag[i] = 0;
   ctx->wait_limit_us = (unsigned)env_int("CAI_WAIT_LIMIT_US", 2000000);
   {
     // CAI_PDL=1 / 0 forces programmatic dependent launch on / off; unset, every session decides for its model
@@ -84,6 +108,8 @@ int cai_cuda_init(int device_id, cai_ctx** out_ctx) {
   *out_ctx = ctx;
   return CAI_OK;
 }
+
+int cai_cuda_is_checked_build(void) { return CAI_CHECKED_BUILD; }
 
 int cai_cuda_set_wait_limit_us(cai_ctx* ctx, unsigned limit_us) {
   if (!ctx || limit_us < 1) return CAI_ERR_INVALID;
@@ -646,7 +672,7 @@ int cai_moe_gate_up_dev(cai_moe_bank* b, const float* x_dev, const int32_t* slot
   if (!x_dev || !slot_expert_dev || !hidden_out_dev || tokens < 1 || top_k < 1 || top_k > b->n_experts)
     return cai_fail(ctx, CAI_ERR_INVALID, "cai_moe_gate_up_dev: bad argument");
   LinearArgs a; a.w = &b->gu[0]; a.x = x_dev; a.ldx = b->hidden; a.y = hidden_out_dev; a.ldy = b->width; a.batch = tokens * top_k;
-  a.epilogue = EPI_SWIGLU; a.bank_codes_dev = b->d_gu_codes; a.bank_scales_dev = b->d_gu_scales;
+  a.epilogue = EPI_SWIGLU; a.bank_codes_dev = b->d_gu_codes; a.bank_scales_dev = b->d_gu_scales; a.bank_count = b->n_experts;
   a.expert_ids_dev = slot_expert_dev; a.x_row_div = top_k;
   return linear_launch(ctx, a);
 }
@@ -667,7 +693,7 @@ int cai_moe_down_dev(cai_moe_bank* b, const float* hidden_dev, const int32_t* sl
     b->pair_cap = pairs;
   }
   LinearArgs a; a.w = &b->down[0]; a.x = hidden_dev; a.ldx = b->width; a.y = b->pair_out; a.ldy = b->hidden; a.batch = (int)pairs;
-  a.bank_codes_dev = b->d_down_codes; a.bank_scales_dev = b->d_down_scales; a.expert_ids_dev = slot_expert_dev; a.x_row_div = 1;
+  a.bank_codes_dev = b->d_down_codes; a.bank_scales_dev = b->d_down_scales; a.bank_count = b->n_experts; a.expert_ids_dev = slot_expert_dev; a.x_row_div = 1;
   CAI_TRY(linear_launch(ctx, a));
   // out[t] = sum over the token's slots, in slot order, of gate * down_e(hidden)   (acc = mad(g, d, acc), neural.cl:2749)
   CAI_CUDA(ctx, cudaMemsetAsync(out_dev, 0, (size_t)tokens * b->hidden * 4, ctx->stream));

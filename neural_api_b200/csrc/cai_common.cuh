@@ -30,8 +30,9 @@ struct cai_ctx {
   size_t staging_bytes;
   void* staging_pinned;      // upload staging (pinned host)
   cai_comm_state* comm;      // NULL until cai_comm_init
-  int* err_flag;             // pinned, device-visible: raised by a kernel whose bounded wait ran out (1), that refused a
-                             // cache length outside the cache (2) or that met an unusable router row (3)
+  int* err_flag;             // pinned, device-visible, 4 words: [0] raised by a kernel whose bounded wait ran out (1), that
+                             // refused a cache length outside the cache (2), that met an unusable router row (3) or, in
+                             // the checked build, that met an index outside its range (4: [1] site, [2] value, [3] bound)
   unsigned wait_limit_us;    // how long a device-side wait on another CTA or GPU may last before it gives up
   void* tc_xp;               // tensor-core GEMM: activations split into bf16 limbs, tiled (gemm_tc_reserve)
   size_t tc_xp_bytes;
@@ -68,6 +69,32 @@ bool linear_uses_tensor_cores(const struct QWeight* w, int batch);   // gemv.cu:
     if (s__ != CAI_OK) return s__;     \
   } while (0)
 
+// The checked build (-DCAI_CHECKED, libcai_cuda_checked.so): the same kernels, but
+//   * where the ordinary build silently clamps or ignores an index that comes from device-side state (a token id, an
+//     expert id), the kernel also records site, value and bound in the error words (cai_report_index), and
+//   * every launch is followed by a stream synchronize and a look at the error words and at cudaGetLastError, so a
+//     failure is reported by the entry point that enqueued the launch, with that launch's file and line (CUDA graphs
+//     are off in this build: every step runs launch by launch).
+// It is a debugging aid: nothing in it changes a result, and the ordinary build carries none of its code.
+#ifdef CAI_CHECKED
+#define CAI_CHECKED_BUILD 1
+#else
+#define CAI_CHECKED_BUILD 0
+#endif
+enum { CAI_SITE_EMBED_TOKEN = 1, CAI_SITE_STEP_TOKEN = 2, CAI_SITE_MOE_EXPERT = 3 };
+#ifdef __CUDACC__
+__device__ __forceinline__ void cai_report_index(int* err, int site, long long value, long long bound) {
+#if CAI_CHECKED_BUILD
+  if (err && *(volatile int*)err == 0) {
+    err[1] = site; err[2] = (int)value; err[3] = (int)bound;
+    __threadfence_system();
+    *(volatile int*)err = 4;
+  }
+#endif
+}
+#endif
+int cai_checked_after_launch(cai_ctx* ctx, const char* file, int line);   // api.cu
+
 // Checks the launch of the kernel just enqueued and counts it.
 #define CAI_LAUNCHED(ctx)                                                                \
   do {                                                                                   \
@@ -77,6 +104,10 @@ bool linear_uses_tensor_cores(const struct QWeight* w, int batch);   // gemv.cu:
                       cudaGetErrorString(e__), __FILE__, __LINE__);                      \
     (ctx)->launches++;                                                                   \
     if ((ctx)->prof_on) cai_prof_mark((ctx), (ctx)->cur_family);                         \
+    if (CAI_CHECKED_BUILD) {                                                             \
+      const int c__ = cai_checked_after_launch((ctx), __FILE__, __LINE__);               \
+      if (c__ != CAI_OK) return c__;                                                     \
+    }                                                                                    \
   } while (0)
 
 static inline int cai_bind(cai_ctx* ctx) {
@@ -165,6 +196,7 @@ struct LinearArgs {
   const QWeight* const* bank = nullptr;  // unused (device arrays below are what kernels read)
   const void* const* bank_codes_dev = nullptr;
   const __half* const* bank_scales_dev = nullptr;
+  int bank_count = 0;        // matrices in the bank: an expert id outside [0, bank_count) is clamped (checked build: reported)
   const int32_t* expert_ids_dev = nullptr;
   int x_row_div = 1;             // activation row of pair p = p / x_row_div
   const float* row_scale_dev = nullptr;  // optional per-pair output scale (router gate)

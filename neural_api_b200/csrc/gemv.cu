@@ -145,7 +145,11 @@ __global__ void __launch_bounds__(256, MINB) gemv_quant_kernel(const GemvParams 
   const float* x = p.x;
   if (p.expert_ids) {
     pair = blockIdx.y;
-    const int e = p.expert_ids[pair];
+    int e = p.expert_ids[pair];
+    if (e < 0 || e >= p.bank_count) {
+      if (threadIdx.x == 0) cai_report_index(p.err_flag, CAI_SITE_MOE_EXPERT, e, p.bank_count);
+      e = e < 0 ? 0 : p.bank_count - 1;
+    }
     codes = (const char*)p.bank_codes[e];
     scales = p.bank_scales[e];
     bias = nullptr;
@@ -418,7 +422,11 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, i
   const float* x;
   if (p.expert_ids) {
     pair = blockIdx.y;
-    const int e = p.expert_ids[pair];
+    int e = p.expert_ids[pair];
+    if (e < 0 || e >= p.bank_count) {
+      if (threadIdx.x == 0) cai_report_index(p.err_flag, CAI_SITE_MOE_EXPERT, e, p.bank_count);
+      e = e < 0 ? 0 : p.bank_count - 1;
+    }
     codes = (const char*)p.bank_codes[e];
     bias = nullptr;
     x = p.x + (int64_t)(pair / p.x_row_div) * p.ldx;
@@ -528,7 +536,11 @@ __global__ void __launch_bounds__(256) gemv_kq_kernel(const GemvParams p) {
   const float* x;
   if (p.expert_ids) {
     pair = blockIdx.y;
-    const int e = p.expert_ids[pair];
+    int e = p.expert_ids[pair];
+    if (e < 0 || e >= p.bank_count) {
+      if (threadIdx.x == 0) cai_report_index(p.err_flag, CAI_SITE_MOE_EXPERT, e, p.bank_count);
+      e = e < 0 ? 0 : p.bank_count - 1;
+    }
     codes = (const uint8_t*)p.bank_codes[e];
     bias = nullptr;
     x = p.x + (int64_t)(pair / p.x_row_div) * p.ldx;
@@ -700,12 +712,14 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
   if (a.epilogue == EPI_SWIGLU && (w->n % 2)) return cai_fail(ctx, CAI_ERR_INVALID, "SwiGLU epilogue needs an even row count");
   if (a.epilogue == EPI_RESID && !a.resid) return cai_fail(ctx, CAI_ERR_INVALID, "residual epilogue without residual");
   const bool indexed = a.expert_ids_dev != nullptr;
+  if (indexed && a.bank_count < 1) return cai_fail(ctx, CAI_ERR_INVALID, "indexed linear: bank of %d matrices", a.bank_count);
   GemvParams p;
   memset(&p, 0, sizeof(p));
+  p.err_flag = ctx->err_flag;
   p.codes = w->codes; p.scales = w->scales; p.bias = w->bias;
   p.x = a.x; p.ldx = a.ldx; p.y = a.y; p.ldy = a.ldy; p.resid = a.resid;
   p.n = w->n; p.k = w->k; p.sstride = w->sstride; p.batch = a.batch; p.act = a.act; p.epi = a.epilogue;
-  p.bank_codes = a.bank_codes_dev; p.bank_scales = a.bank_scales_dev; p.expert_ids = a.expert_ids_dev;
+  p.bank_codes = a.bank_codes_dev; p.bank_scales = a.bank_scales_dev; p.expert_ids = a.expert_ids_dev; p.bank_count = a.bank_count;
   p.x_row_div = a.x_row_div < 1 ? 1 : a.x_row_div; p.row_scale = a.row_scale_dev;
   p.ksplit = 1;
   if (a.epilogue == EPI_QKV_ROPE) {

@@ -27,6 +27,7 @@ struct GemvParams {
   const void* const* bank_codes;
   const __half* const* bank_scales;
   const int32_t* expert_ids;
+  int bank_count;   // expert ids are clamped into [0, bank_count): the ids come from device memory the caller owns
   int x_row_div;
   const float* row_scale;
   const float* out_scale;   // CAI_TYPE_I8ROW: one fp32 scale per weight row, applied to the finished sum (before the bias)

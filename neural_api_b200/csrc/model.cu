@@ -933,13 +933,13 @@ static int enqueue_step(cai_session* s) {
       } else {
       {
         LinearArgs a; a.w = &L.exp_gu[0]; a.x = s->h; a.ldx = H; a.y = s->moe_hidden; a.ldy = Im; a.batch = B * K;
-        a.epilogue = EPI_SWIGLU; a.bank_codes_dev = L.d_gu_codes; a.bank_scales_dev = L.d_gu_scales;
+        a.epilogue = EPI_SWIGLU; a.bank_codes_dev = L.d_gu_codes; a.bank_scales_dev = L.d_gu_scales; a.bank_count = E;
         a.expert_ids_dev = s->expert_ids; a.x_row_div = K;
         CAI_TRY(linear_launch(ctx, a));
       }
       {
         LinearArgs a; a.w = &L.exp_down[0]; a.x = s->moe_hidden; a.ldx = Im; a.y = s->pair_out; a.ldy = H; a.batch = B * K;
-        a.bank_codes_dev = L.d_down_codes; a.bank_scales_dev = L.d_down_scales; a.expert_ids_dev = s->expert_ids; a.x_row_div = 1;
+        a.bank_codes_dev = L.d_down_codes; a.bank_scales_dev = L.d_down_scales; a.bank_count = E; a.expert_ids_dev = s->expert_ids; a.x_row_div = 1;
         CAI_TRY(linear_launch(ctx, a));
       }
       }
@@ -1097,7 +1097,7 @@ static int session_create_impl(cai_model* m, int max_ctx, int batch, int kv_type
   s->len_host.assign((size_t)batch, 0);
   m->sessions += 1;
   const char* ng = getenv("CAI_NO_GRAPH");
-  s->use_graph = !(ng && *ng && *ng != '0');
+  s->use_graph = !(ng && *ng && *ng != '0') && !CAI_CHECKED_BUILD;   // the checked build looks at every launch on its own
   // Programmatic dependent launch pays when the step is a chain of short kernels (the next kernel's CTAs are
   // resident and primed when the previous one drains); on the 32B model, whose kernels each stream > 100 MB, it
   // measured slower. Rule: on when one layer's MLP weights are below 24 M elements.

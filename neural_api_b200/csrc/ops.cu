@@ -10,11 +10,12 @@
 // ---------------------------------------------------------------------------
 __global__ void embed_kernel(int type, const void* __restrict__ codes, const __half* __restrict__ scales,
                              int64_t sstride, int64_t k, int64_t n_rows, const int32_t* __restrict__ tokens, float* __restrict__ out, int64_t ld,
-                             const float* __restrict__ rscale) {
+                             const float* __restrict__ rscale, int* err) {
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x;
   int64_t tok = tokens[b];
+  if ((tok < 0 || tok >= n_rows) && threadIdx.x == 0) cai_report_index(err, CAI_SITE_EMBED_TOKEN, tok, n_rows);
   if (tok < 0) tok = 0;
   if (tok >= n_rows) tok = n_rows - 1;
   for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
@@ -40,7 +41,7 @@ __global__ void embed_kernel(int type, const void* __restrict__ codes, const __h
 
 int op_embed(cai_ctx* ctx, const QWeight* t, const int32_t* tokens_dev, int batch, float* out, int64_t ld) {
   ctx->cur_family = FAM_OTHER;
-  pdl_launch(ctx, embed_kernel, dim3(batch), dim3(256), 0, t->type, (const void*)t->codes, (const __half*)t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld, (const float*)t->rscale);
+  pdl_launch(ctx, embed_kernel, dim3(batch), dim3(256), 0, t->type, (const void*)t->codes, (const __half*)t->scales, t->sstride, t->k, t->n, tokens_dev, out, ld, (const float*)t->rscale, ctx->err_flag);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }
@@ -339,7 +340,7 @@ int op_add_inplace(cai_ctx* ctx, float* x, const float* y, int64_t n) {
 // One CTA; pairs <= 4096, experts <= 1024.
 // ---------------------------------------------------------------------------
 __global__ void moe_group_kernel(const int32_t* __restrict__ ids, int pairs, int n_experts, int tile_rows, int max_tiles,
-                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_pairs, int expert_lo, int expert_hi) {
+                                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_pairs, int expert_lo, int expert_hi, int* err) {
   extern __shared__ int32_t sh[];
   int32_t* s_ids = sh;                       // [pairs]
   int32_t* s_cnt = sh + pairs;               // [n_experts]
@@ -348,7 +349,8 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ ids, int pairs, int
   pdl_wait();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int e = ids[i];
-    s_ids[i] = (e >= expert_lo && e < expert_hi) ? e : -1;     // -1: another rank's expert
+    if (e < 0 || e >= n_experts) cai_report_index(err, CAI_SITE_MOE_EXPERT, e, n_experts);
+    s_ids[i] = (e >= expert_lo && e < expert_hi) ? e : -1;     // -1: another rank's expert (or no expert at all)
   }
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) s_cnt[e] = 0;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
@@ -383,7 +385,7 @@ int op_moe_group(cai_ctx* ctx, const int32_t* expert_ids, int pairs, int n_exper
     return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "moe grouping: %d pairs, %d experts", pairs, n_experts);
   const size_t smem = ((size_t)pairs + 2 * (size_t)n_experts + 1) * sizeof(int32_t);
   pdl_launch(ctx, moe_group_kernel, dim3(1), dim3(512), smem, expert_ids, pairs, n_experts, tile_rows, max_tiles, tile_expert, tile_pairs,
-             expert_lo, expert_hi);
+             expert_lo, expert_hi, ctx->err_flag);
   CAI_LAUNCHED(ctx);
   return CAI_OK;
 }

@@ -750,6 +750,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) step_kernel(const SkParams P) {
     return;
   }
   int token = P.tokens[0];
+#if CAI_CHECKED_BUILD
+  if ((token < 0 || token >= P.emb_rows) && blockIdx.x == 0 && threadIdx.x == 0) cai_report_index(P.err, CAI_SITE_STEP_TOKEN, token, P.emb_rows);
+#endif
   if (token < 0) token = 0;
   if (token >= P.emb_rows) token = P.emb_rows - 1;
   const int pos = P.pos[0];
@@ -1309,6 +1312,7 @@ int step_plan_enqueue(cai_ctx* ctx, StepPlan* p, unsigned long long* ts_dev) {
   cudaError_t e = cudaLaunchKernelExC(&cfg, (const void*)p->fn, args);
   if (e != cudaSuccess) return cai_fail(ctx, CAI_ERR_CUDA, "step kernel launch -> %s", cudaGetErrorString(e));
   ctx->launches++;
+  if (CAI_CHECKED_BUILD) return cai_checked_after_launch(ctx, __FILE__, __LINE__);
   return CAI_OK;
 }
 

@@ -54,6 +54,7 @@ function cai_cuda_shutdown(ctx: PCaiCtx): cint; cdecl; external CaiLib;
 function cai_cuda_last_error(ctx: PCaiCtx; buf: PChar; buf_len: cint): cint; cdecl; external CaiLib;
 function cai_cuda_device_info(ctx: PCaiCtx; sm_count: pcint; total_bytes: pcint64): cint; cdecl; external CaiLib;
 function cai_cuda_launch_count(ctx: PCaiCtx; out_count: pcint64): cint; cdecl; external CaiLib;
+function cai_cuda_is_checked_build(): cint; cdecl; external CaiLib;
 function cai_cuda_set_wait_limit_us(ctx: PCaiCtx; limit_us: cuint): cint; cdecl; external CaiLib;
 function cai_selftest_wait_timeout(ctx: PCaiCtx; which: cint; limit_us: cuint): cint; cdecl; external CaiLib;
 function cai_dev_alloc(ctx: PCaiCtx; bytes: cint64; out out_dev: Pointer): cint; cdecl; external CaiLib;

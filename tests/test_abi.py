@@ -85,3 +85,14 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_checked_twin_exports_the_same_surface_and_says_what_it_is(lib):
+    """libcai_cuda_checked.so (-DCAI_CHECKED: every launch synchronized and looked at, silent index clamps reported) has
+    the ordinary library's entry points; cai_cuda_is_checked_build tells the two apart without a GPU."""
+    from neural_api_b200 import build
+    checked = C.CDLL(build.build(checked=True))
+    for name in declared_symbols():
+        assert hasattr(checked, name), name
+    assert checked.cai_cuda_is_checked_build() == 1
+    assert lib.cai_cuda_is_checked_build() == 0
