@@ -1457,6 +1457,8 @@ int attn_nsplit(cai_ctx* ctx, int batch, int kv_heads, int max_ctx) {
   const int cap = (max_ctx + 63) / 64;                              // at least 64 rows per split at full context
   if (ns > cap) ns = cap;
   if (ns > 128) ns = 128;
+  const int forced = env_int("CAI_ATTN_NSPLIT", 0);                  // tuning knob: the number of context splits
+  if (forced > 0) ns = forced < 128 ? forced : 128;
   if (ns < 1) ns = 1;
   return ns;
 }
