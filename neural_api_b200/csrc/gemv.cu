@@ -619,6 +619,201 @@ __global__ void __launch_bounds__(256) gemv_kq_kernel(const GemvParams p) {
   gemv_epilogue<NB, RPW>(p, acc, unit0, b0, pair, bias);
 }
 
+// ---------------------------------------------------------------------------
+// Q4_K / Q5_K on integer dot products (dp4a). The kernel above turns every 4.5-bit code into a float before it multiplies
+// (11 lane instructions per weight: bound by the integer pipe at 0.15 of the HBM rate). Here the codes stay integers:
+//   * the CTA splits the activation row once into three exact int8 limbs per 32-wide sub-block (x = s_j * (l0 + l1/128 +
+//     l2/16384), s_j a power of two, what is left below 2^-21 of the sub-block's largest magnitude), with the
+//     sub-block's fp32 sum beside them, in shared memory, laid out so that a warp's 16-byte reads are conflict-free;
+//   * a lane owns one pair of sub-blocks of a super-block (32 code bytes: low nibbles = sub-block 2c, high nibbles =
+//     2c + 1), four lanes a super-block, a warp eight super-blocks of two rows per step; a word of four codes is one
+//     mask (and one shift) and three dp4a per sub-block;
+//   * per sub-block the three integer sums are combined in fp32 and enter the row's sum as in the regrouped form
+//     above:  d * sc_j * s_j * sum(code * limbs) - dmin * m_j * sum(x).
+// Every integer sum is exact, the block scales are formed as the reference forms them (d * sc rounded once).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void kqi_limbs4(const float4& v, float inv, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
+  const float magic = 12582912.0f;                        // 1.5 * 2^23: the sum's low byte is the rounded integer
+  const float t[4] = {v.x * inv, v.y * inv, v.z * inv, v.w * inv};
+  w0 = w1 = w2 = 0u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float x0 = t[i] + magic;
+    float r = (t[i] - (x0 - magic)) * 128.0f;
+    const float x1 = r + magic;
+    r = (r - (x1 - magic)) * 128.0f;
+    const float x2 = r + magic;
+    w0 |= (__float_as_uint(x0) & 0xFFu) << (8 * i);
+    w1 |= (__float_as_uint(x1) & 0xFFu) << (8 * i);
+    w2 |= (__float_as_uint(x2) & 0xFFu) << (8 * i);
+  }
+}
+static __host__ __device__ inline size_t kqi_smem_bytes(int64_t k) { return (size_t)(3 * k + 2 * (k / 32) * 4); }
+
+template <int TYPE>
+__global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
+  constexpr int BB = ggufdev::KQ<TYPE>::BB;
+  constexpr int QOFF = (TYPE == CAI_TYPE_Q4_K) ? 16 : 48;          // where the nibbles start in a super-block
+  extern __shared__ __align__(16) unsigned char kqi_smem[];
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint8_t* codes = (const uint8_t*)p.codes;
+  const float* bias = p.bias;
+  const int b0 = p.expert_ids ? 0 : blockIdx.y;
+  int pair = 0;
+  const float* x;
+  pdl_wait();                                                      // the activations (and the expert ids) are the predecessor's output
+  if (p.expert_ids) {
+    pair = blockIdx.y;
+    int e = p.expert_ids[pair];
+    if (e < 0 || e >= p.bank_count) {
+      if (threadIdx.x == 0) cai_report_index(p.err_flag, CAI_SITE_MOE_EXPERT, e, p.bank_count);
+      e = e < 0 ? 0 : p.bank_count - 1;
+    }
+    codes = (const uint8_t*)p.bank_codes[e];
+    bias = nullptr;
+    x = p.x + (int64_t)(pair / p.x_row_div) * p.ldx;
+  } else {
+    x = p.x + (int64_t)b0 * p.ldx;
+  }
+  const int K = (int)p.k, npairs = K >> 6, nsub = K >> 5;
+  unsigned char* xl = kqi_smem;                                    // limbs: [limb 3][16-byte piece 4][pair][16 bytes]
+  float* xs = (float*)(kqi_smem + 3 * (size_t)K);                  // [nsub] power of two of the sub-block's limbs
+  float* xsum = xs + nsub;                                         // [nsub] sum of the sub-block's activations
+  // ---- the activation row -> limbs: eight lanes per sub-block, four values each
+  for (int j4 = warp; j4 * 4 < nsub; j4 += 8) {
+    const int j = j4 * 4 + (lane >> 3), i4 = (lane & 7) * 4;
+    const float4 v = *(const float4*)(x + (size_t)j * 32 + i4);
+    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    float sm = (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      sm += __shfl_xor_sync(0xffffffffu, sm, o);
+    }
+    int e = (mx > 0.f && mx < 3.0e38f) ? ilogbf(mx) - 5 : 0;       // |x| / 2^e < 64
+    e = e < -100 ? -100 : (e > 100 ? 100 : e);
+    uint32_t w0, w1, w2;
+    kqi_limbs4(v, __int_as_float((127 - e) << 23), w0, w1, w2);
+    const int kk = j * 32 + i4, pr = kk >> 6, q = (kk & 63) >> 4, byte = kk & 15;
+    *(uint32_t*)(xl + ((size_t)(0 * 4 + q) * npairs + pr) * 16 + byte) = w0;
+    *(uint32_t*)(xl + ((size_t)(1 * 4 + q) * npairs + pr) * 16 + byte) = w1;
+    *(uint32_t*)(xl + ((size_t)(2 * 4 + q) * npairs + pr) * 16 + byte) = w2;
+    if ((lane & 7) == 0) {
+      xs[j] = (mx < 3.0e38f) ? __int_as_float((127 + e) << 23) : __int_as_float(0x7FC00000);   // a row with inf / NaN gives NaN
+      xsum[j] = sm;
+    }
+  }
+  __syncthreads();
+
+  const bool sw = (p.epi == EPI_SWIGLU);
+  const int64_t half = p.n >> 1;
+  const int64_t n_units = sw ? half : (p.n + 1) / 2;
+  const int64_t n_sb = p.k >> 8;
+  const int64_t row_bytes = n_sb * BB;
+  const int c = lane & 3;                                          // the lane's pair of sub-blocks in its super-block
+  for (int64_t unit = (int64_t)blockIdx.x * 8 + warp; unit < n_units; unit += (int64_t)gridDim.x * 8) {
+    int64_t rows[2];
+    if (sw) { rows[0] = unit; rows[1] = half + unit; }
+    else { rows[0] = 2 * unit; rows[1] = (2 * unit + 1 < p.n) ? 2 * unit + 1 : 2 * unit; }
+    float acc[2][1] = {{0.f}, {0.f}};
+    for (int64_t s0 = 0; s0 < n_sb; s0 += 8) {
+      const int64_t sb = s0 + (lane >> 2);
+      if (sb < n_sb) {
+        const int pr = (int)sb * 4 + c;
+        uint4 head[2], qa[2], qb[2], ha[2], hb[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint8_t* blk = codes + rows[r] * row_bytes + sb * BB;
+          head[r] = *(const uint4*)blk;
+          qa[r] = *(const uint4*)(blk + QOFF + c * 32);
+          qb[r] = *(const uint4*)(blk + QOFF + c * 32 + 16);
+          if (TYPE == CAI_TYPE_Q5_K) { ha[r] = *(const uint4*)(blk + 16); hb[r] = *(const uint4*)(blk + 32); }
+        }
+        int al[2][3], ah[2][3];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int L = 0; L < 3; ++L) { al[r][L] = 0; ah[r][L] = 0; }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {                              // code bytes 16 t .. 16 t + 15 of the pair
+          int4 xlo[3], xhi[3];
+#pragma unroll
+          for (int L = 0; L < 3; ++L) {
+            xlo[L] = *(const int4*)(xl + ((size_t)(L * 4 + t) * npairs + pr) * 16);
+            xhi[L] = *(const int4*)(xl + ((size_t)(L * 4 + 2 + t) * npairs + pr) * 16);
+          }
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const uint4 qv = t ? qb[r] : qa[r];
+            const uint4 hv = t ? hb[r] : ha[r];
+            const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+            const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t lo = qw[i] & 0x0F0F0F0Fu, hi = (qw[i] >> 4) & 0x0F0F0F0Fu;
+              if (TYPE == CAI_TYPE_Q5_K) {                         // the fifth bit of sub-block j is bit j of the plane's byte
+                lo |= ((hw[i] >> (2 * c)) & 0x01010101u) << 4;
+                hi |= ((hw[i] >> (2 * c + 1)) & 0x01010101u) << 4;
+              }
+#pragma unroll
+              for (int L = 0; L < 3; ++L) {
+                al[r][L] = __dp4a((int)lo, ((const int*)&xlo[L])[i], al[r][L]);
+                ah[r][L] = __dp4a((int)hi, ((const int*)&xhi[L])[i], ah[r][L]);
+              }
+            }
+          }
+        }
+        const float2 s2 = *(const float2*)(xs + 2 * pr), m2 = *(const float2*)(xsum + 2 * pr);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          // scales and mins of sub-blocks 2c and 2c + 1 (DequantizeQ4KScaleMin, neural/neuralgguf.pas:448-472)
+          const float d = __half2float(__ushort_as_half((unsigned short)(head[r].x & 0xFFFF)));
+          const float dmin = __half2float(__ushort_as_half((unsigned short)(head[r].x >> 16)));
+          const int sh = (2 * c & 3) * 8;
+          const uint32_t dd = head[r].y >> sh, mm = head[r].z >> sh, md = head[r].w >> sh;
+          int sc0, mn0, sc1, mn1;
+          if (c < 2) {
+            sc0 = dd & 0x3F; mn0 = mm & 0x3F;
+            sc1 = (dd >> 8) & 0x3F; mn1 = (mm >> 8) & 0x3F;
+          } else {
+            sc0 = (md & 0x0F) | ((dd >> 2) & 0x30); mn0 = ((md >> 4) & 0x0F) | ((mm >> 2) & 0x30);
+            sc1 = ((md >> 8) & 0x0F) | ((dd >> 10) & 0x30); mn1 = ((md >> 12) & 0x0F) | ((mm >> 10) & 0x30);
+          }
+          const float dl0 = __fmul_rn(d, (float)sc0), ml0 = __fmul_rn(dmin, (float)mn0);
+          const float dl1 = __fmul_rn(d, (float)sc1), ml1 = __fmul_rn(dmin, (float)mn1);
+          const float f = 0.0078125f;
+          const float dot0 = fmaf(fmaf((float)al[r][2], f, (float)al[r][1]), f, (float)al[r][0]) * s2.x;
+          const float dot1 = fmaf(fmaf((float)ah[r][2], f, (float)ah[r][1]), f, (float)ah[r][0]) * s2.y;
+          float a = acc[r][0];
+          a = fmaf(dl0, dot0, a); a = fmaf(-ml0, m2.x, a);
+          a = fmaf(dl1, dot1, a); a = fmaf(-ml1, m2.y, a);
+          acc[r][0] = a;
+        }
+      }
+    }
+    acc[0][0] = warp_sum(acc[0][0]);
+    acc[1][0] = warp_sum(acc[1][0]);
+    gemv_epilogue<1, 2>(p, acc, sw ? unit : 2 * unit, b0, pair, bias);
+  }
+}
+
+template <int TYPE>
+static int launch_kqi(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsigned grid_y) {
+  const size_t smem = kqi_smem_bytes(p.k);
+  static size_t configured[64] = {0};
+  const int dev = ctx->device;
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && configured[dev] < smem) {
+    CAI_CUDA(ctx, cudaFuncSetAttribute(gemv_kqi_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = smem;
+  }
+  int64_t ctas = (n_units + 7) / 8;
+  const int64_t resident = 2 * (int64_t)ctx->sm_count;             // every CTA splits the activation row itself: no more CTAs than run at once
+  if (ctas * grid_y > resident) ctas = resident / grid_y > 0 ? resident / grid_y : 1;
+  pdl_launch(ctx, gemv_kqi_kernel<TYPE>, dim3((unsigned)ctas, grid_y), dim3(256), smem, p);
+  return CAI_OK;
+}
+
 template <int TYPE>
 static void launch_kq(cai_ctx* ctx, int nb, dim3 grid, int threads, const GemvParams& p) {
   if (nb == 4) pdl_launch(ctx, gemv_kq_kernel<TYPE, 4>, grid, dim3(threads), 0, p);
@@ -742,7 +937,13 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     if (a.norm_gain) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: fused RMSNorm needs quantized weights");
     if (cai_type_is_kquant(w->type)) {
       if ((a.ldx % 4) || ((uintptr_t)a.x % 16)) return cai_fail(ctx, CAI_ERR_INVALID, "linear: activations must be 16-byte aligned with ldx %% 4 == 0");
-      if (w->type == CAI_TYPE_Q4_K) launch_kq<CAI_TYPE_Q4_K>(ctx, nb, grid, threads, p);
+      // Q4_K / Q5_K: the integer-dot kernel, one batch row (or expert pair) per grid row (CAI_GEMV_KQI=0: the float kernel)
+      if ((w->type == CAI_TYPE_Q4_K || w->type == CAI_TYPE_Q5_K) && a.batch <= 8 && kqi_smem_bytes(w->k) <= 96 * 1024 &&
+          env_int("CAI_GEMV_KQI", 1) != 0) {
+        if (w->type == CAI_TYPE_Q4_K) { CAI_TRY(launch_kqi<CAI_TYPE_Q4_K>(ctx, p, groups, (unsigned)a.batch)); }
+        else { CAI_TRY(launch_kqi<CAI_TYPE_Q5_K>(ctx, p, groups, (unsigned)a.batch)); }
+      }
+      else if (w->type == CAI_TYPE_Q4_K) launch_kq<CAI_TYPE_Q4_K>(ctx, nb, grid, threads, p);
       else if (w->type == CAI_TYPE_Q5_K) launch_kq<CAI_TYPE_Q5_K>(ctx, nb, grid, threads, p);
       else launch_kq<CAI_TYPE_Q6_K>(ctx, nb, grid, threads, p);
     }
