@@ -629,7 +629,10 @@ __global__ void __launch_bounds__(256) gemv_kq_kernel(const GemvParams p) {
 //     2c + 1), four lanes a super-block, a warp eight super-blocks of two rows per step; a word of four codes is one
 //     mask (and one shift) and three dp4a per sub-block;
 //   * per sub-block the three integer sums are combined in fp32 and enter the row's sum as in the regrouped form
-//     above:  d * sc_j * s_j * sum(code * limbs) - dmin * m_j * sum(x).
+//     above:  d * sc_j * s_j * sum(code * limbs) - dmin * m_j * sum(x);
+//   * the raw super-blocks come through a per-warp cp.async ring (a stage = the step's eight super-blocks of both rows)
+//     whose fill runs two stages ahead, across the warp's row pairs, and starts before the activation row is even read
+//     (the weights do not depend on the kernel before this one).
 // Every integer sum is exact, the block scales are formed as the reference forms them (d * sc rounded once).
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void kqi_limbs4(const float4& v, float inv, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
@@ -648,12 +651,17 @@ __device__ __forceinline__ void kqi_limbs4(const float4& v, float inv, uint32_t&
     w2 |= (__float_as_uint(x2) & 0xFFu) << (8 * i);
   }
 }
-static __host__ __device__ inline size_t kqi_smem_bytes(int64_t k) { return (size_t)(3 * k + 2 * (k / 32) * 4); }
+constexpr int KQI_SBS = 8;                                  // super-blocks of a row per step of a warp (four lanes each)
+constexpr int KQI_DEPTH = 3;                                // stages of a warp's ring of raw super-blocks
+static __host__ __device__ inline size_t kqi_x_bytes(int64_t k) { return (size_t)(3 * k + 2 * (k / 32) * 4); }   // limbs, scales, sums (a multiple of 16)
+static __host__ __device__ inline size_t kqi_smem_bytes(int64_t k, int bb) { return kqi_x_bytes(k) + (size_t)8 * KQI_DEPTH * 2 * KQI_SBS * bb; }
 
 template <int TYPE>
 __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
   constexpr int BB = ggufdev::KQ<TYPE>::BB;
   constexpr int QOFF = (TYPE == CAI_TYPE_Q4_K) ? 16 : 48;          // where the nibbles start in a super-block
+  constexpr int ROWSTEP = KQI_SBS * BB;                            // bytes of one row in a stage
+  constexpr int STAGE = 2 * ROWSTEP;
   extern __shared__ __align__(16) unsigned char kqi_smem[];
   pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -661,9 +669,8 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
   const float* bias = p.bias;
   const int b0 = p.expert_ids ? 0 : blockIdx.y;
   int pair = 0;
-  const float* x;
-  pdl_wait();                                                      // the activations (and the expert ids) are the predecessor's output
   if (p.expert_ids) {
+    pdl_wait();                                                    // the expert ids are the predecessor's output
     pair = blockIdx.y;
     int e = p.expert_ids[pair];
     if (e < 0 || e >= p.bank_count) {
@@ -672,14 +679,54 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
     }
     codes = (const uint8_t*)p.bank_codes[e];
     bias = nullptr;
-    x = p.x + (int64_t)(pair / p.x_row_div) * p.ldx;
-  } else {
-    x = p.x + (int64_t)b0 * p.ldx;
   }
   const int K = (int)p.k, npairs = K >> 6, nsub = K >> 5;
   unsigned char* xl = kqi_smem;                                    // limbs: [limb 3][16-byte piece 4][pair][16 bytes]
   float* xs = (float*)(kqi_smem + 3 * (size_t)K);                  // [nsub] power of two of the sub-block's limbs
   float* xsum = xs + nsub;                                         // [nsub] sum of the sub-block's activations
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(kqi_smem + kqi_x_bytes(K)) + (uint32_t)warp * KQI_DEPTH * STAGE;
+
+  const bool sw = (p.epi == EPI_SWIGLU);
+  const int64_t half = p.n >> 1;
+  const int64_t n_units = sw ? half : (p.n + 1) / 2;
+  const int64_t n_sb = p.k >> 8;
+  const int64_t row_bytes = n_sb * BB;
+  const int n_steps = (int)((n_sb + KQI_SBS - 1) / KQI_SBS);
+  const int64_t unit_first = (int64_t)blockIdx.x * 8 + warp, unit_stride = (int64_t)gridDim.x * 8;
+  const int my_units = unit_first < n_units ? (int)((n_units - unit_first + unit_stride - 1) / unit_stride) : 0;
+  const int total_items = my_units * n_steps;
+  // One commit group per call: the raw super-blocks of item `fi` (row pair fi / n_steps of this warp, step fi % n_steps).
+  int fi = 0, fslot = 0, f_st = 0;
+  int64_t f_unit = unit_first;
+  const uint8_t *f_src0 = codes, *f_src1 = codes;                  // the cursor's two rows, at the lane's first piece
+  auto fill = [&]() {
+    if (fi < total_items) {
+      if (f_st == 0) {
+        const int64_t r0 = sw ? f_unit : 2 * f_unit, r1 = sw ? half + f_unit : ((2 * f_unit + 1 < p.n) ? 2 * f_unit + 1 : 2 * f_unit);
+        f_src0 = codes + r0 * row_bytes + lane * 16;
+        f_src1 = codes + r1 * row_bytes + lane * 16;
+      }
+      const int64_t s0 = (int64_t)f_st * KQI_SBS;
+      const int np = (int)((n_sb - s0 < KQI_SBS) ? (n_sb - s0) : KQI_SBS) * (BB / 16);
+      const uint32_t dst = ring + fslot * STAGE + lane * 16;
+#pragma unroll
+      for (int i = 0; i < (KQI_SBS * BB / 16 + 31) / 32; ++i) {
+        if (lane + 32 * i < np) {
+          gv_cp_async16(dst + i * 512, f_src0 + i * 512, 16u);
+          gv_cp_async16(dst + ROWSTEP + i * 512, f_src1 + i * 512, 16u);
+        }
+      }
+      f_src0 += ROWSTEP; f_src1 += ROWSTEP;
+      ++fi;
+      if (++f_st == n_steps) { f_st = 0; f_unit += unit_stride; }
+    }
+    gv_cp_async_commit();
+    fslot = (fslot + 1 == KQI_DEPTH) ? 0 : fslot + 1;
+  };
+#pragma unroll 1
+  for (int d = 0; d < KQI_DEPTH - 1; ++d) fill();
+  if (!p.expert_ids) pdl_wait();                                   // the activations are the predecessor's output
+  const float* x = p.expert_ids ? p.x + (int64_t)(pair / p.x_row_div) * p.ldx : p.x + (int64_t)b0 * p.ldx;
   // ---- the activation row -> limbs: eight lanes per sub-block, four values each
   for (int j4 = warp; j4 * 4 < nsub; j4 += 8) {
     const int j = j4 * 4 + (lane >> 3), i4 = (lane & 7) * 4;
@@ -706,29 +753,28 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
   }
   __syncthreads();
 
-  const bool sw = (p.epi == EPI_SWIGLU);
-  const int64_t half = p.n >> 1;
-  const int64_t n_units = sw ? half : (p.n + 1) / 2;
-  const int64_t n_sb = p.k >> 8;
-  const int64_t row_bytes = n_sb * BB;
   const int c = lane & 3;                                          // the lane's pair of sub-blocks in its super-block
-  for (int64_t unit = (int64_t)blockIdx.x * 8 + warp; unit < n_units; unit += (int64_t)gridDim.x * 8) {
-    int64_t rows[2];
-    if (sw) { rows[0] = unit; rows[1] = half + unit; }
-    else { rows[0] = 2 * unit; rows[1] = (2 * unit + 1 < p.n) ? 2 * unit + 1 : 2 * unit; }
+  int rslot = 0;
+  for (int uk = 0; uk < my_units; ++uk) {
+    const int64_t unit = unit_first + (int64_t)uk * unit_stride;
     float acc[2][1] = {{0.f}, {0.f}};
-    for (int64_t s0 = 0; s0 < n_sb; s0 += 8) {
-      const int64_t sb = s0 + (lane >> 2);
+    for (int st = 0; st < n_steps; ++st) {
+      gv_cp_async_wait_depth(KQI_DEPTH);                           // this lane's copies of the oldest stage have landed
+      __syncwarp();                                                // ... and every lane's; the stage read last time is free
+      fill();
+      const uint32_t stage = ring + rslot * STAGE;
+      rslot = (rslot + 1 == KQI_DEPTH) ? 0 : rslot + 1;
+      const int64_t sb = (int64_t)st * KQI_SBS + (lane >> 2);
       if (sb < n_sb) {
         const int pr = (int)sb * 4 + c;
-        uint4 head[2], qa[2], qb[2], ha[2], hb[2];
+        int4 head[2], qa[2], qb[2], ha[2], hb[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const uint8_t* blk = codes + rows[r] * row_bytes + sb * BB;
-          head[r] = *(const uint4*)blk;
-          qa[r] = *(const uint4*)(blk + QOFF + c * 32);
-          qb[r] = *(const uint4*)(blk + QOFF + c * 32 + 16);
-          if (TYPE == CAI_TYPE_Q5_K) { ha[r] = *(const uint4*)(blk + 16); hb[r] = *(const uint4*)(blk + 32); }
+          const uint32_t blk = stage + r * ROWSTEP + (lane >> 2) * BB;
+          head[r] = gv_lds16(blk);
+          qa[r] = gv_lds16(blk + QOFF + c * 32);
+          qb[r] = gv_lds16(blk + QOFF + c * 32 + 16);
+          if (TYPE == CAI_TYPE_Q5_K) { ha[r] = gv_lds16(blk + 16); hb[r] = gv_lds16(blk + 32); }
         }
         int al[2][3], ah[2][3];
 #pragma unroll
@@ -745,10 +791,10 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
           }
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
-            const uint4 qv = t ? qb[r] : qa[r];
-            const uint4 hv = t ? hb[r] : ha[r];
-            const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
-            const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+            const int4 qv = t ? qb[r] : qa[r];
+            const int4 hv = t ? hb[r] : ha[r];
+            const uint32_t qw[4] = {(uint32_t)qv.x, (uint32_t)qv.y, (uint32_t)qv.z, (uint32_t)qv.w};
+            const uint32_t hw[4] = {(uint32_t)hv.x, (uint32_t)hv.y, (uint32_t)hv.z, (uint32_t)hv.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint32_t lo = qw[i] & 0x0F0F0F0Fu, hi = (qw[i] >> 4) & 0x0F0F0F0Fu;
@@ -768,20 +814,17 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           // scales and mins of sub-blocks 2c and 2c + 1 (DequantizeQ4KScaleMin, neural/neuralgguf.pas:448-472)
-          const float d = __half2float(__ushort_as_half((unsigned short)(head[r].x & 0xFFFF)));
-          const float dmin = __half2float(__ushort_as_half((unsigned short)(head[r].x >> 16)));
+          const uint32_t hx = (uint32_t)head[r].x;
+          const float d = __half2float(__ushort_as_half((unsigned short)(hx & 0xFFFF)));
+          const float dmin = __half2float(__ushort_as_half((unsigned short)(hx >> 16)));
+          // both sub-blocks at once, as byte pairs: sub-blocks 0..3 are six bits of the first two byte groups, 4..7 splice
+          // the third group's nibbles under the top bits of the first two (no branch: c differs inside a warp)
           const int sh = (2 * c & 3) * 8;
-          const uint32_t dd = head[r].y >> sh, mm = head[r].z >> sh, md = head[r].w >> sh;
-          int sc0, mn0, sc1, mn1;
-          if (c < 2) {
-            sc0 = dd & 0x3F; mn0 = mm & 0x3F;
-            sc1 = (dd >> 8) & 0x3F; mn1 = (mm >> 8) & 0x3F;
-          } else {
-            sc0 = (md & 0x0F) | ((dd >> 2) & 0x30); mn0 = ((md >> 4) & 0x0F) | ((mm >> 2) & 0x30);
-            sc1 = ((md >> 8) & 0x0F) | ((dd >> 10) & 0x30); mn1 = ((md >> 12) & 0x0F) | ((mm >> 10) & 0x30);
-          }
-          const float dl0 = __fmul_rn(d, (float)sc0), ml0 = __fmul_rn(dmin, (float)mn0);
-          const float dl1 = __fmul_rn(d, (float)sc1), ml1 = __fmul_rn(dmin, (float)mn1);
+          const uint32_t dd = (uint32_t)head[r].y >> sh, mm = (uint32_t)head[r].z >> sh, md = (uint32_t)head[r].w >> sh;
+          const uint32_t sc2 = (c < 2) ? (dd & 0x3F3Fu) : ((md & 0x0F0Fu) | ((dd >> 2) & 0x3030u));
+          const uint32_t mn2 = (c < 2) ? (mm & 0x3F3Fu) : (((md >> 4) & 0x0F0Fu) | ((mm >> 2) & 0x3030u));
+          const float dl0 = __fmul_rn(d, (float)(sc2 & 0xFFu)), ml0 = __fmul_rn(dmin, (float)(mn2 & 0xFFu));
+          const float dl1 = __fmul_rn(d, (float)(sc2 >> 8)), ml1 = __fmul_rn(dmin, (float)(mn2 >> 8));
           const float f = 0.0078125f;
           const float dot0 = fmaf(fmaf((float)al[r][2], f, (float)al[r][1]), f, (float)al[r][0]) * s2.x;
           const float dot1 = fmaf(fmaf((float)ah[r][2], f, (float)ah[r][1]), f, (float)ah[r][0]) * s2.y;
@@ -796,14 +839,15 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
     acc[1][0] = warp_sum(acc[1][0]);
     gemv_epilogue<1, 2>(p, acc, sw ? unit : 2 * unit, b0, pair, bias);
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 template <int TYPE>
 static int launch_kqi(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsigned grid_y) {
-  const size_t smem = kqi_smem_bytes(p.k);
+  const size_t smem = kqi_smem_bytes(p.k, ggufdev::KQ<TYPE>::BB);
   static size_t configured[64] = {0};
   const int dev = ctx->device;
-  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && configured[dev] < smem) {
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && configured[dev] < smem) {   // (one of these per instantiation)
     CAI_CUDA(ctx, cudaFuncSetAttribute(gemv_kqi_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured[dev] = smem;
   }
@@ -938,7 +982,7 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     if (cai_type_is_kquant(w->type)) {
       if ((a.ldx % 4) || ((uintptr_t)a.x % 16)) return cai_fail(ctx, CAI_ERR_INVALID, "linear: activations must be 16-byte aligned with ldx %% 4 == 0");
       // Q4_K / Q5_K: the integer-dot kernel, one batch row (or expert pair) per grid row (CAI_GEMV_KQI=0: the float kernel)
-      if ((w->type == CAI_TYPE_Q4_K || w->type == CAI_TYPE_Q5_K) && a.batch <= 8 && kqi_smem_bytes(w->k) <= 96 * 1024 &&
+      if ((w->type == CAI_TYPE_Q4_K || w->type == CAI_TYPE_Q5_K) && a.batch <= 8 && kqi_smem_bytes(w->k, 176) <= 112 * 1024 &&
           env_int("CAI_GEMV_KQI", 1) != 0) {
         if (w->type == CAI_TYPE_Q4_K) { CAI_TRY(launch_kqi<CAI_TYPE_Q4_K>(ctx, p, groups, (unsigned)a.batch)); }
         else { CAI_TRY(launch_kqi<CAI_TYPE_Q5_K>(ctx, p, groups, (unsigned)a.batch)); }
