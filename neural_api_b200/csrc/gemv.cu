@@ -842,6 +842,231 @@ __global__ void __launch_bounds__(256, 2) gemv_kqi_kernel(const GemvParams p) {
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------
+// Q6_K on integer dot products: the same scheme for the 210-byte super-block (128 bytes of low nibbles, 64 bytes of
+// high bit pairs, sixteen int8 group scales, one fp16 d; weight = d * sc_g * (code - 32), groups of 16). A lane owns
+// the 32 low-nibble bytes of one half of one half-block and with them two 32-wide runs of weights (the low and the
+// high nibbles) whose top bits share 32 bytes of the bit-pair plane. Differences to the kernel above:
+//   * super-blocks are only 2-byte aligned, so a stage copies the 16-byte pieces that cover the step's bytes and the
+//     lane reads aligned 4-byte words, joining neighbours with a funnel shift when its bytes start on a half word
+//     (the weight buffers are allocated with 64 spare bytes, so the last piece may reach past the matrix);
+//   * sum((code - 32) * limb) = sum(code * limb) - 32 * sum(limb): the limb sums of every 16 activations are kept
+//     beside the limbs;
+//   * one scale per 16 weights: four integer sums per limb and lane instead of two, no offsets.
+// ---------------------------------------------------------------------------
+constexpr int KQI6_ROWSTEP = 1712;                          // 8 x 210 bytes + up to 15 bytes of lead-in, a multiple of 16
+static __host__ __device__ inline size_t kqi6_x_bytes(int64_t k) { return (size_t)(3 * k + 2 * (k / 32) * 4 + k); }   // limbs, scales, sums, limb sums [k/16][4]
+static __host__ __device__ inline size_t kqi6_smem_bytes(int64_t k) { return kqi6_x_bytes(k) + (size_t)8 * KQI_DEPTH * 2 * KQI6_ROWSTEP; }
+
+__global__ void __launch_bounds__(256, 2) gemv_kqi6_kernel(const GemvParams p) {
+  constexpr int BB = 210;
+  constexpr int ROWSTEP = KQI6_ROWSTEP;
+  constexpr int STAGE = 2 * ROWSTEP;
+  extern __shared__ __align__(16) unsigned char kqi_smem[];
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint8_t* codes = (const uint8_t*)p.codes;
+  const float* bias = p.bias;
+  const int b0 = p.expert_ids ? 0 : blockIdx.y;
+  int pair = 0;
+  if (p.expert_ids) {
+    pdl_wait();                                                    // the expert ids are the predecessor's output
+    pair = blockIdx.y;
+    int e = p.expert_ids[pair];
+    if (e < 0 || e >= p.bank_count) {
+      if (threadIdx.x == 0) cai_report_index(p.err_flag, CAI_SITE_MOE_EXPERT, e, p.bank_count);
+      e = e < 0 ? 0 : p.bank_count - 1;
+    }
+    codes = (const uint8_t*)p.bank_codes[e];
+    bias = nullptr;
+  }
+  const int K = (int)p.k, npairs = K >> 6, nsub = K >> 5;
+  unsigned char* xl = kqi_smem;                                    // limbs: [limb 3][16-byte piece 4][pair][16 bytes]
+  float* xs = (float*)(kqi_smem + 3 * (size_t)K);                  // [nsub] power of two of the sub-block's limbs
+  float* xsum = xs + nsub;                                         // [nsub] (unused here: Q6_K has no offsets)
+  int4* lsum = (int4*)(kqi_smem + 3 * (size_t)K + 2 * (size_t)nsub * 4);   // [K / 16] sums of the three limbs over 16 activations
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(kqi_smem + kqi6_x_bytes(K)) + (uint32_t)warp * KQI_DEPTH * STAGE;
+
+  const bool sw = (p.epi == EPI_SWIGLU);
+  const int64_t half = p.n >> 1;
+  const int64_t n_units = sw ? half : (p.n + 1) / 2;
+  const int64_t n_sb = p.k >> 8;
+  const int64_t row_bytes = n_sb * BB;
+  const int n_steps = (int)((n_sb + KQI_SBS - 1) / KQI_SBS);
+  const int64_t unit_first = (int64_t)blockIdx.x * 8 + warp, unit_stride = (int64_t)gridDim.x * 8;
+  const int my_units = unit_first < n_units ? (int)((n_units - unit_first + unit_stride - 1) / unit_stride) : 0;
+  const int total_items = my_units * n_steps;
+  // One commit group per call: the 16-byte pieces that cover the item's super-blocks of both rows. A row's bytes keep
+  // their position modulo 16 (byte `start & 15` of the stage row is the first byte of the step's first super-block).
+  int fi = 0, fslot = 0, f_st = 0;
+  int64_t f_unit = unit_first;
+  int64_t f_off0 = 0, f_off1 = 0;                                  // byte offsets of the cursor's two rows in the matrix
+  auto fill = [&]() {
+    if (fi < total_items) {
+      if (f_st == 0) {
+        const int64_t r0 = sw ? f_unit : 2 * f_unit, r1 = sw ? half + f_unit : ((2 * f_unit + 1 < p.n) ? 2 * f_unit + 1 : 2 * f_unit);
+        f_off0 = r0 * row_bytes; f_off1 = r1 * row_bytes;
+      }
+      const int64_t s0 = (int64_t)f_st * KQI_SBS;
+      const int nbytes = (int)((n_sb - s0 < KQI_SBS) ? (n_sb - s0) : KQI_SBS) * BB;
+      const uint32_t dst = ring + fslot * STAGE + lane * 16;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int64_t start = (r ? f_off1 : f_off0) + s0 * BB;
+        const int np = (int)(((start & 15) + nbytes + 15) >> 4);   // <= 107 pieces
+        const uint8_t* src = codes + (start & ~(int64_t)15) + lane * 16;
+#pragma unroll
+        for (int i = 0; i < (ROWSTEP / 16 + 31) / 32; ++i)
+          if (lane + 32 * i < np) gv_cp_async16(dst + r * ROWSTEP + i * 512, src + i * 512, 16u);
+      }
+      ++fi;
+      if (++f_st == n_steps) { f_st = 0; f_unit += unit_stride; }
+    }
+    gv_cp_async_commit();
+    fslot = (fslot + 1 == KQI_DEPTH) ? 0 : fslot + 1;
+  };
+#pragma unroll 1
+  for (int d = 0; d < KQI_DEPTH - 1; ++d) fill();
+  if (!p.expert_ids) pdl_wait();                                   // the activations are the predecessor's output
+  const float* x = p.expert_ids ? p.x + (int64_t)(pair / p.x_row_div) * p.ldx : p.x + (int64_t)b0 * p.ldx;
+  // ---- the activation row -> limbs (as above), plus the limb sums of every 16 activations
+  for (int j4 = warp; j4 * 4 < nsub; j4 += 8) {
+    const int j = j4 * 4 + (lane >> 3), i4 = (lane & 7) * 4;
+    const float4 v = *(const float4*)(x + (size_t)j * 32 + i4);
+    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    int e = (mx > 0.f && mx < 3.0e38f) ? ilogbf(mx) - 5 : 0;       // |x| / 2^e < 64
+    e = e < -100 ? -100 : (e > 100 ? 100 : e);
+    uint32_t w0, w1, w2;
+    kqi_limbs4(v, __int_as_float((127 - e) << 23), w0, w1, w2);
+    const int kk = j * 32 + i4, pr = kk >> 6, q = (kk & 63) >> 4, byte = kk & 15;
+    *(uint32_t*)(xl + ((size_t)(0 * 4 + q) * npairs + pr) * 16 + byte) = w0;
+    *(uint32_t*)(xl + ((size_t)(1 * 4 + q) * npairs + pr) * 16 + byte) = w1;
+    *(uint32_t*)(xl + ((size_t)(2 * 4 + q) * npairs + pr) * 16 + byte) = w2;
+    int l0 = __dp4a((int)w0, 0x01010101, 0), l1 = __dp4a((int)w1, 0x01010101, 0), l2 = __dp4a((int)w2, 0x01010101, 0);
+#pragma unroll
+    for (int o = 1; o < 4; o <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+      l2 += __shfl_xor_sync(0xffffffffu, l2, o);
+    }
+    if ((lane & 3) == 0) lsum[kk >> 4] = make_int4(l0, l1, l2, 0);
+    if ((lane & 7) == 0) {
+      xs[j] = (mx < 3.0e38f) ? __int_as_float((127 + e) << 23) : __int_as_float(0x7FC00000);   // a row with inf / NaN gives NaN
+      xsum[j] = 0.f;
+    }
+  }
+  __syncthreads();
+
+  const int c = lane & 3, hh = c >> 1, ps = c & 1;                 // the lane's half-block and its half of that
+  int rslot = 0;
+  for (int uk = 0; uk < my_units; ++uk) {
+    const int64_t unit = unit_first + (int64_t)uk * unit_stride;
+    const int64_t r0 = sw ? unit : 2 * unit, r1 = sw ? half + unit : ((2 * unit + 1 < p.n) ? 2 * unit + 1 : 2 * unit);
+    float acc[2][1] = {{0.f}, {0.f}};
+    for (int st = 0; st < n_steps; ++st) {
+      gv_cp_async_wait_depth(KQI_DEPTH);                           // this lane's copies of the oldest stage have landed
+      __syncwarp();                                                // ... and every lane's; the stage read last time is free
+      fill();
+      const uint32_t stage = ring + rslot * STAGE;
+      rslot = (rslot + 1 == KQI_DEPTH) ? 0 : rslot + 1;
+      const int64_t sb = (int64_t)st * KQI_SBS + (lane >> 2);
+      if (sb < n_sb) {
+        // the two 32-wide runs of this lane: activations of sub-blocks j_lo (low nibbles) and j_hi (high nibbles)
+        const int j_lo = (int)sb * 8 + 4 * hh + ps, j_hi = j_lo + 2;
+        int al[2][3][2], ah[2][3][2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int L = 0; L < 3; ++L) { al[r][L][0] = 0; al[r][L][1] = 0; ah[r][L][0] = 0; ah[r][L][1] = 0; }
+        uint32_t blk[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int64_t start = (r ? r1 : r0) * row_bytes + (int64_t)st * KQI_SBS * BB;
+          blk[r] = stage + r * ROWSTEP + (uint32_t)(start & 15) + (uint32_t)(lane >> 2) * BB;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {                              // code bytes 16 t .. 16 t + 15 of the lane's 32
+          int4 xlo[3], xhi[3];
+#pragma unroll
+          for (int L = 0; L < 3; ++L) {
+            xlo[L] = *(const int4*)(xl + ((size_t)(L * 4 + (j_lo & 1) * 2 + t) * npairs + (j_lo >> 1)) * 16);
+            xhi[L] = *(const int4*)(xl + ((size_t)(L * 4 + (j_hi & 1) * 2 + t) * npairs + (j_hi >> 1)) * 16);
+          }
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            // 16 bytes of low nibbles and of bit pairs from a 2-byte aligned place: five aligned words each
+            const uint32_t qa = blk[r] + hh * 64 + ps * 32 + t * 16, ha = blk[r] + 128 + hh * 32 + t * 16;
+            const uint32_t qsh = (qa & 2u) * 8u, hsh = (ha & 2u) * 8u;
+            uint32_t qv[5], hv[5];
+#pragma unroll
+            for (int i = 0; i < 5; ++i) {
+              asm volatile("ld.shared.u32 %0, [%1];" : "=r"(qv[i]) : "r"((qa & ~3u) + 4 * i));
+              asm volatile("ld.shared.u32 %0, [%1];" : "=r"(hv[i]) : "r"((ha & ~3u) + 4 * i));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t qw = __funnelshift_r(qv[i], qv[i + 1], qsh), hw = __funnelshift_r(hv[i], hv[i + 1], hsh);
+              const uint32_t lo = (qw & 0x0F0F0F0Fu) | (((hw >> (2 * ps)) & 0x03030303u) << 4);
+              const uint32_t hi = ((qw >> 4) & 0x0F0F0F0Fu) | (((hw >> (4 + 2 * ps)) & 0x03030303u) << 4);
+#pragma unroll
+              for (int L = 0; L < 3; ++L) {
+                al[r][L][t] = __dp4a((int)lo, ((const int*)&xlo[L])[i], al[r][L][t]);
+                ah[r][L][t] = __dp4a((int)hi, ((const int*)&xhi[L])[i], ah[r][L][t]);
+              }
+            }
+          }
+        }
+        const float s_lo = xs[j_lo], s_hi = xs[j_hi];
+        const int4 ls_lo0 = lsum[2 * j_lo], ls_lo1 = lsum[2 * j_lo + 1], ls_hi0 = lsum[2 * j_hi], ls_hi1 = lsum[2 * j_hi + 1];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          // group scales 8 hh + 2 ps + {0, 1} (low nibbles) and + 4 (high nibbles); d at byte 208
+          const uint32_t sa = blk[r] + 192 + 8 * hh + 2 * ps;
+          unsigned short s01, s45, dh;
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s01) : "r"(sa));
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s45) : "r"(sa + 4));
+          asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dh) : "r"(blk[r] + 208));
+          const float d = __half2float(__ushort_as_half(dh));
+          const float f = 0.0078125f;
+          float a = acc[r][0];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {                            // low nibbles: groups 0, 1; high nibbles: groups 2, 3
+            const int4 ls = g == 0 ? ls_lo0 : (g == 1 ? ls_lo1 : (g == 2 ? ls_hi0 : ls_hi1));
+            const int a0 = (g < 2 ? al[r][0][g & 1] : ah[r][0][g & 1]) - 32 * ls.x;
+            const int a1 = (g < 2 ? al[r][1][g & 1] : ah[r][1][g & 1]) - 32 * ls.y;
+            const int a2 = (g < 2 ? al[r][2][g & 1] : ah[r][2][g & 1]) - 32 * ls.z;
+            const int sc = (int)(int8_t)(((g < 2 ? s01 : s45) >> (8 * (g & 1))) & 0xFF);
+            const float dot = fmaf(fmaf((float)a2, f, (float)a1), f, (float)a0) * (g < 2 ? s_lo : s_hi);
+            a = fmaf(__fmul_rn(d, (float)sc), dot, a);
+          }
+          acc[r][0] = a;
+        }
+      }
+    }
+    acc[0][0] = warp_sum(acc[0][0]);
+    acc[1][0] = warp_sum(acc[1][0]);
+    gemv_epilogue<1, 2>(p, acc, sw ? unit : 2 * unit, b0, pair, bias);
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+static int launch_kqi6(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsigned grid_y) {
+  const size_t smem = kqi6_smem_bytes(p.k);
+  static size_t configured[64] = {0};
+  const int dev = ctx->device;
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && configured[dev] < smem) {
+    CAI_CUDA(ctx, cudaFuncSetAttribute(gemv_kqi6_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = smem;
+  }
+  int64_t ctas = (n_units + 7) / 8;
+  const int64_t resident = (smem > 110 * 1024 ? 1 : 2) * (int64_t)ctx->sm_count;
+  if (ctas * grid_y > resident) ctas = resident / grid_y > 0 ? resident / grid_y : 1;
+  pdl_launch(ctx, gemv_kqi6_kernel, dim3((unsigned)ctas, grid_y), dim3(256), smem, p);
+  return CAI_OK;
+}
+
 template <int TYPE>
 static int launch_kqi(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsigned grid_y) {
   const size_t smem = kqi_smem_bytes(p.k, ggufdev::KQ<TYPE>::BB);
@@ -986,6 +1211,10 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
           env_int("CAI_GEMV_KQI", 1) != 0) {
         if (w->type == CAI_TYPE_Q4_K) { CAI_TRY(launch_kqi<CAI_TYPE_Q4_K>(ctx, p, groups, (unsigned)a.batch)); }
         else { CAI_TRY(launch_kqi<CAI_TYPE_Q5_K>(ctx, p, groups, (unsigned)a.batch)); }
+      }
+      else if (w->type == CAI_TYPE_Q6_K && a.batch <= 8 && kqi6_smem_bytes(w->k) <= 160 * 1024 && env_int("CAI_GEMV_KQI", 1) != 0 &&
+               ((uintptr_t)w->codes % 16) == 0) {
+        CAI_TRY(launch_kqi6(ctx, p, groups, (unsigned)a.batch));
       }
       else if (w->type == CAI_TYPE_Q4_K) launch_kq<CAI_TYPE_Q4_K>(ctx, nb, grid, threads, p);
       else if (w->type == CAI_TYPE_Q5_K) launch_kq<CAI_TYPE_Q5_K>(ctx, nb, grid, threads, p);
