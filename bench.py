@@ -628,14 +628,17 @@ def main():
             sample.close()
         except Exception as e:                               # the baseline is reported, never required
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": "failed: %s" % e}
-        for name, label, st, wu, fill in (("qwen2.5-0.5b", "qwen2.5-0.5b Q8_0 batch 1 context 256", 128, 8, "prefill"),
-                                          ("tinyllama-1.1b", "tinyllama-1.1b Q4_0 16 sequences context 768", 32, 4, "prefill"),
-                                          ("olmoe-1b-7b", "olmoe-1b-7b Q8_0 batch 64 context 2048 (context declared, not prefilled)", 16, 4, "zeros")):
+        for name, label, st, wu, fill, kv2 in (
+                ("qwen2.5-0.5b", "qwen2.5-0.5b Q8_0 batch 1 context 256", 128, 8, "prefill", "f32"),
+                ("tinyllama-1.1b", "tinyllama-1.1b Q4_0 16 sequences context 768", 32, 4, "prefill", "f32"),
+                ("olmoe-1b-7b", "olmoe-1b-7b Q8_0 batch 64 context 2048 (context declared, not prefilled)", 16, 4, "zeros", "f32"),
+                # the same with the reference's default cache (int8 rows + one scale per row): a quarter of the attention bytes
+                ("olmoe-1b-7b", "olmoe-1b-7b Q8_0 batch 64 context 2048 int8 KV (context declared, not prefilled)", 16, 4, "zeros", "int8")):
             if name == args.workload:
                 continue
             try:
                 t, sd, b2, c2 = WORKLOAD_DEFAULTS[name]
-                r2 = run_workload(backend, None, 0, 1, name, t, sd, b2, c2, st, wu, do_e2e=True, do_profile=False, fill=fill)
+                r2 = run_workload(backend, None, 0, 1, name, t, sd, b2, c2, st, wu, do_e2e=True, do_profile=False, fill=fill, kv=kv2)
                 sb = r2["weight_bytes_rank"] + r2["kv_bytes_step"]
                 also[label] = {"tokens_per_s": r2["tokens_per_s"], "ms_per_step": r2["ms_per_step"], "e2e_tokens_per_s": r2["e2e_tokens_per_s"],
                                "step_hbm_frac": sb / (r2["ms_per_step"] * 1e-3) / 1e9 / peak, "launches_per_step": r2["launches"] / st,

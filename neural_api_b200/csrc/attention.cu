@@ -1523,12 +1523,14 @@ int attn_decode(cai_ctx* ctx, const AttnArgs& a) {
       return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "int8 KV cache: head_dim 64 or 128 and groups of up to 8 query heads");
     p.min_chunk = ATTN_TILE_MIN_CHUNK;
     const size_t tsmem = ((size_t)G * a.head_dim + (size_t)ATTN_WARPS * G * 32 + (size_t)ATTN_WARPS * G * (a.head_dim + 2)) * sizeof(float);
-    // Groups of up to 5 query heads can run on the integer tensor-core kernel. It streams 1.6x faster but starts
-    // slower (the query's limbs, two warps per CTA), so it takes the calls whose splits are long: 512 rows or more at
-    // full context (measured: 64 sequences x 8192 rows 28.2 -> 17.9 ms per 64 layers; one sequence, 128-row splits:
-    // 3.30 -> 3.45 ms). CAI_ATTN_I8MMA=1 / 0 forces it on / off; read at every call so that a test can switch it.
+    // Groups of 2 to 5 query heads run on the integer tensor-core kernel when their splits are long. Its cost per cached
+    // byte does not depend on the group (the instruction's 16 rows are there anyway) while the CUDA-core kernel's grows
+    // with it, and it starts slower (the query's limbs, two warps per CTA). Measured per 64 layers: groups of 5, 64
+    // sequences x 8192 rows 28.2 -> 17.9 ms; one sequence in 128-row splits 3.30 -> 3.45 ms; groups of 1 (OLMoE, 64
+    // sequences x 2048 rows, 16 layers) 2.13 -> 2.30 ms. So: splits of 512 rows or more at full context and at least
+    // two heads per group. CAI_ATTN_I8MMA=1 / 0 forces it on / off; read at every call so that a test can switch it.
     const char* mma_env = getenv("CAI_ATTN_I8MMA");
-    const bool use_mma = (mma_env && *mma_env) ? atoi(mma_env) != 0 : (a.max_ctx / (a.nsplit > 0 ? a.nsplit : 1) >= 512);
+    const bool use_mma = (mma_env && *mma_env) ? atoi(mma_env) != 0 : (G >= 2 && a.max_ctx / (a.nsplit > 0 ? a.nsplit : 1) >= 512);
     if (use_mma && G <= 5) {
       if (a.head_dim == 128) { CAI_TRY(launch_mma_int8<128>(ctx, G, grid, p)); }
       else { CAI_TRY(launch_mma_int8<64>(ctx, G, grid, p)); }

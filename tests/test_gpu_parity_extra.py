@@ -55,11 +55,15 @@ def test_device_quantizer_reproduces_the_oracle_quantizer_byte_for_byte(backend,
         mq.close()
 
 
-def test_grouped_expert_path_at_the_olmoe_shape_matches_the_oracle(backend):
+@pytest.mark.parametrize("kv", ["f32", "int8"])
+def test_grouped_expert_path_at_the_olmoe_shape_matches_the_oracle(backend, kv):
     """One OLMoE-shaped layer (hidden 2048, 16 heads of 128, 64 experts, top-8, expert width 1024, full-width q/k norm;
     vocabulary cut), 32 sequences: 256 (token, expert) pairs per step, 4 per expert on average, so the expert products
     run as grouped tensor-core GEMMs over 16-row tiles. Every sequence's logits against the oracle's one-sequence
-    forward, 1e-3 of the logit RMS, and the same greedy token."""
+    forward, 1e-3 of the logit RMS, and the same greedy token. kv = "int8": the same model over the reference's default
+    cache (int8 rows, the q/k norm in front of the quantizing append), against the oracle's int8 cache at the int8 gate
+    of 5e-3 (two implementations of that cache differ by a code wherever a value sits on a rounding boundary, so the
+    greedy token is not compared there)."""
     kw = dict(hidden=2048, inter=1024, layers=1, heads=16, kv_heads=16, head_dim=128, vocab=1024, rms_eps=1e-5, rope_theta=1e4,
               qk_norm=True, n_experts=64, top_k=8, norm_topk=False, moe_inter=1024)
     model = LlamaModel(backend, make_config(**kw))
@@ -80,8 +84,8 @@ def test_grouped_expert_path_at_the_olmoe_shape_matches_the_oracle(backend):
     batch, n_prompt, n_new = 32, 5, 3
     rng = np.random.default_rng(4)
     prompt = rng.integers(0, kw["vocab"], (batch, n_prompt)).astype(np.int32)
-    sess = StreamingDecoder(model, n_prompt + n_new + 2, batch=batch)
-    osess = [OracleSession(oracle, n_prompt + n_new + 2) for _ in range(batch)]
+    sess = StreamingDecoder(model, n_prompt + n_new + 2, batch=batch, kv_type=TYPE_I8 if kv == "int8" else TYPE_F32)
+    osess = [OracleSession(oracle, n_prompt + n_new + 2, kv_int8=(kv == "int8")) for _ in range(batch)]
     try:
         for i in range(n_prompt - 1):                       # token-at-a-time on both sides
             sess.step_forward(prompt[:, i], want_logits=False)
@@ -97,9 +101,10 @@ def test_grouped_expert_path_at_the_olmoe_shape_matches_the_oracle(backend):
                 rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
                 worst = max(worst, float(np.max(np.abs(logits[b] - ref))) / rms)
                 nxt[b] = argmax_first(ref)
-            assert np.array_equal(amax, nxt)
+            if kv == "f32":
+                assert np.array_equal(amax, nxt)
             tok = nxt
-        assert worst < 1e-3, worst
+        assert worst < (1e-3 if kv == "f32" else 5e-3), worst
     finally:
         sess.close()
         model.close()
