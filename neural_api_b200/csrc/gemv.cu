@@ -1067,6 +1067,194 @@ static int launch_kqi6(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsig
   return CAI_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Q4_0 at batch 1 on integer dot products: the scheme of the K-quant kernels on the planar Q4_0 layout (16 code
+// bytes per 32-weight block, byte e = elements e and e + 16; one fp16 scale per block in its own plane;
+// weight = d * (code - 8)). The float kernel spends a byte-permute and half a packed multiply-add per code and is bound
+// by the integer pipe at 0.4 of the HBM rate on the largest matrices; here a word of eight codes is one mask, one
+// shift and six dp4a against the three int8 limbs of the activations, and per block
+//   d * s_j * (sum(code * limbs) - 8 * sum(limbs))
+// enters the row's fp32 sum. A lane owns two blocks of a row per step, a warp 64 blocks of two rows; codes and scales
+// come through the per-warp cp.async ring; the optional RMSNorm of the activation row is applied while it is split.
+// ---------------------------------------------------------------------------
+constexpr int Q4I_BPS = 64;                                 // blocks of a row per step
+constexpr int Q4I_ROW = Q4I_BPS * 16 + Q4I_BPS * 2;         // a row's share of a stage: code bytes, then the blocks' scales
+constexpr int Q4I_STAGE = 2 * Q4I_ROW;
+static __host__ __device__ inline size_t q4i_xs_bytes(int64_t k) { return (size_t)(((k / 32) * 4 + 15) & ~(int64_t)15); }     // the blocks' powers of two, padded to 16 bytes
+static __host__ __device__ inline size_t q4i_x_bytes(int64_t k) { return (size_t)(3 * k) + q4i_xs_bytes(k) + (size_t)(k / 32) * 16; }   // limbs, scales, limb sums
+static __host__ __device__ inline size_t q4i_smem_bytes(int64_t k) { return q4i_x_bytes(k) + (size_t)8 * KQI_DEPTH * Q4I_STAGE; }
+
+__global__ void __launch_bounds__(256, 2) gemv_q4i_kernel(const GemvParams p) {
+  constexpr int STAGE = Q4I_STAGE, ROW = Q4I_ROW;
+  extern __shared__ __align__(16) unsigned char kqi_smem[];
+  __shared__ float red[32];
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint8_t* codes = (const uint8_t*)p.codes;
+  const unsigned short* scales = (const unsigned short*)p.scales;
+  const int b0 = blockIdx.y;
+  const int K = (int)p.k, npairs = K >> 6, nblk = K >> 5;
+  unsigned char* xl = kqi_smem;                                    // limbs: [limb 3][16-byte piece 4][pair][16 bytes]
+  float* xs = (float*)(kqi_smem + 3 * (size_t)K);                  // [nblk] power of two of the block's limbs
+  int4* lsum = (int4*)(kqi_smem + 3 * (size_t)K + q4i_xs_bytes(K));    // [nblk] sums of the three limbs over the block
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(kqi_smem + q4i_x_bytes(K)) + (uint32_t)warp * KQI_DEPTH * STAGE;
+
+  const bool sw = (p.epi == EPI_SWIGLU);
+  const int64_t half = p.n >> 1;
+  const int64_t n_units = sw ? half : (p.n + 1) / 2;
+  const int64_t code_row = p.k >> 1;                               // code bytes of a row
+  const int n_steps = (nblk + Q4I_BPS - 1) / Q4I_BPS;
+  const int64_t unit_first = (int64_t)blockIdx.x * 8 + warp, unit_stride = (int64_t)gridDim.x * 8;
+  const int my_units = unit_first < n_units ? (int)((n_units - unit_first + unit_stride - 1) / unit_stride) : 0;
+  const int total_items = my_units * n_steps;
+  // One commit group per call: step f_st of the cursor's two rows: up to 64 blocks of codes (a piece each) and their
+  // scales (16-byte pieces of the scale rows, which are padded to whole pieces).
+  int fi = 0, fslot = 0, f_st = 0;
+  int64_t f_unit = unit_first, f_r0 = 0, f_r1 = 0;
+  auto fill = [&]() {
+    if (fi < total_items) {
+      if (f_st == 0) {
+        f_r0 = sw ? f_unit : 2 * f_unit;
+        f_r1 = sw ? half + f_unit : ((2 * f_unit + 1 < p.n) ? 2 * f_unit + 1 : 2 * f_unit);
+      }
+      const int s0 = f_st * Q4I_BPS;
+      const int nb = (nblk - s0 < Q4I_BPS) ? (nblk - s0) : Q4I_BPS;
+      const uint32_t dst = ring + fslot * STAGE;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int64_t row = r ? f_r1 : f_r0;
+        const uint8_t* csrc = codes + row * code_row + (int64_t)s0 * 16;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          if (lane + 32 * i < nb) gv_cp_async16(dst + r * ROW + (lane + 32 * i) * 16, csrc + (lane + 32 * i) * 16, 16u);
+        if (lane * 8 < nb) gv_cp_async16(dst + r * ROW + Q4I_BPS * 16 + lane * 16, scales + row * p.sstride + s0 + lane * 8, 16u);
+      }
+      ++fi;
+      if (++f_st == n_steps) { f_st = 0; f_unit += unit_stride; }
+    }
+    gv_cp_async_commit();
+    fslot = (fslot + 1 == KQI_DEPTH) ? 0 : fslot + 1;
+  };
+#pragma unroll 1
+  for (int d = 0; d < KQI_DEPTH - 1; ++d) fill();
+  pdl_wait();                                                      // the activations are the predecessor's output
+  const float* x = p.x + (int64_t)b0 * p.ldx;
+  // ---- the activation row (normed if asked) -> limbs: eight lanes per block, four values each
+  float inv = 1.f;
+  if (p.norm_gain) {
+    float ss = 0.f;
+    for (int c4 = threadIdx.x; c4 < (K >> 2); c4 += blockDim.x) {
+      const float4 v = *(const float4*)(x + 4 * c4);
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = block_sum(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)K + p.norm_eps);
+  }
+  for (int j4 = warp; j4 * 4 < nblk; j4 += 8) {
+    const int j = j4 * 4 + (lane >> 3), i4 = (lane & 7) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j < nblk) {
+      v = *(const float4*)(x + (size_t)j * 32 + i4);
+      if (p.norm_gain) {
+        const float4 g4 = *(const float4*)(p.norm_gain + (size_t)j * 32 + i4);
+        v.x = g4.x * (v.x * inv); v.y = g4.y * (v.y * inv); v.z = g4.z * (v.z * inv); v.w = g4.w * (v.w * inv);
+      }
+    }
+    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    int e = (mx > 0.f && mx < 3.0e38f) ? ilogbf(mx) - 5 : 0;       // |x| / 2^e < 64
+    e = e < -100 ? -100 : (e > 100 ? 100 : e);
+    uint32_t w0, w1, w2;
+    kqi_limbs4(v, __int_as_float((127 - e) << 23), w0, w1, w2);
+    int l0 = __dp4a((int)w0, 0x01010101, 0), l1 = __dp4a((int)w1, 0x01010101, 0), l2 = __dp4a((int)w2, 0x01010101, 0);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+      l2 += __shfl_xor_sync(0xffffffffu, l2, o);
+    }
+    if (j < nblk) {
+      const int kk = j * 32 + i4, pr = kk >> 6, q = (kk & 63) >> 4, byte = kk & 15;
+      *(uint32_t*)(xl + ((size_t)(0 * 4 + q) * npairs + pr) * 16 + byte) = w0;
+      *(uint32_t*)(xl + ((size_t)(1 * 4 + q) * npairs + pr) * 16 + byte) = w1;
+      *(uint32_t*)(xl + ((size_t)(2 * 4 + q) * npairs + pr) * 16 + byte) = w2;
+      if ((lane & 7) == 0) {
+        xs[j] = (mx < 3.0e38f) ? __int_as_float((127 + e) << 23) : __int_as_float(0x7FC00000);   // a row with inf / NaN gives NaN
+        lsum[j] = make_int4(l0, l1, l2, 0);
+      }
+    }
+  }
+  __syncthreads();
+
+  int rslot = 0;
+  for (int uk = 0; uk < my_units; ++uk) {
+    const int64_t unit = unit_first + (int64_t)uk * unit_stride;
+    float acc[2][1] = {{0.f}, {0.f}};
+    for (int st = 0; st < n_steps; ++st) {
+      gv_cp_async_wait_depth(KQI_DEPTH);                           // this lane's copies of the oldest stage have landed
+      __syncwarp();                                                // ... and every lane's; the stage read last time is free
+      fill();
+      const uint32_t stage = ring + rslot * STAGE;
+      rslot = (rslot + 1 == KQI_DEPTH) ? 0 : rslot + 1;
+      const int j0 = st * Q4I_BPS + 2 * lane;                      // the lane's two blocks: j0, j0 + 1 (the block count is even)
+      if (j0 < nblk) {
+        const int pr = j0 >> 1;
+        uint32_t sc2[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc2[r]) : "r"(stage + r * ROW + Q4I_BPS * 16 + lane * 4));
+        const float2 s2 = *(const float2*)(xs + j0);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {                              // block j0 + b: low nibbles = piece 2b, high nibbles = piece 2b + 1 of the pair
+          int4 xlo[3], xhi[3];
+#pragma unroll
+          for (int L = 0; L < 3; ++L) {
+            xlo[L] = *(const int4*)(xl + ((size_t)(L * 4 + 2 * b) * npairs + pr) * 16);
+            xhi[L] = *(const int4*)(xl + ((size_t)(L * 4 + 2 * b + 1) * npairs + pr) * 16);
+          }
+          const int4 ls = lsum[j0 + b];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int4 qv = gv_lds16(stage + r * ROW + (2 * lane + b) * 16);
+            const uint32_t qw[4] = {(uint32_t)qv.x, (uint32_t)qv.y, (uint32_t)qv.z, (uint32_t)qv.w};
+            int a0 = -8 * ls.x, a1 = -8 * ls.y, a2 = -8 * ls.z;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t lo = qw[i] & 0x0F0F0F0Fu, hi = (qw[i] >> 4) & 0x0F0F0F0Fu;
+              a0 = __dp4a((int)lo, ((const int*)&xlo[0])[i], a0); a0 = __dp4a((int)hi, ((const int*)&xhi[0])[i], a0);
+              a1 = __dp4a((int)lo, ((const int*)&xlo[1])[i], a1); a1 = __dp4a((int)hi, ((const int*)&xhi[1])[i], a1);
+              a2 = __dp4a((int)lo, ((const int*)&xlo[2])[i], a2); a2 = __dp4a((int)hi, ((const int*)&xhi[2])[i], a2);
+            }
+            const float d = __half2float(__ushort_as_half((unsigned short)(b ? (sc2[r] >> 16) : (sc2[r] & 0xFFFFu))));
+            const float f = 0.0078125f;
+            const float dot = fmaf(fmaf((float)a2, f, (float)a1), f, (float)a0) * (b ? s2.y : s2.x);
+            acc[r][0] = fmaf(d, dot, acc[r][0]);
+          }
+        }
+      }
+    }
+    acc[0][0] = warp_sum(acc[0][0]);
+    acc[1][0] = warp_sum(acc[1][0]);
+    gemv_epilogue<1, 2>(p, acc, sw ? unit : 2 * unit, b0, 0, p.bias);
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+static int launch_q4i(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsigned grid_y) {
+  const size_t smem = q4i_smem_bytes(p.k);
+  static size_t configured[64] = {0};
+  const int dev = ctx->device;
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && configured[dev] < smem) {
+    CAI_CUDA(ctx, cudaFuncSetAttribute(gemv_q4i_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = smem;
+  }
+  int64_t ctas = (n_units + 7) / 8;
+  const int64_t resident = (smem > 110 * 1024 ? 1 : 2) * (int64_t)ctx->sm_count;
+  if (ctas * grid_y > resident) ctas = resident / grid_y > 0 ? resident / grid_y : 1;
+  pdl_launch(ctx, gemv_q4i_kernel, dim3((unsigned)ctas, grid_y), dim3(256), smem, p);
+  return CAI_OK;
+}
+
 template <int TYPE>
 static int launch_kqi(cai_ctx* ctx, const GemvParams& p, int64_t n_units, unsigned grid_y) {
   const size_t smem = kqi_smem_bytes(p.k, ggufdev::KQ<TYPE>::BB);
@@ -1239,6 +1427,17 @@ int linear_launch(cai_ctx* ctx, const LinearArgs& a) {
     if (st != CAI_ERR_UNSUPPORTED) return st;
   }
   if (a.path == 2) return cai_fail(ctx, CAI_ERR_UNSUPPORTED, "linear: the tensor-core path covers batches of up to 64 rows with plain or residual epilogues");
+  // Q4_0 at batch 1: integer dot products (CAI_GEMV_Q4I=0: the float kernel below). Measured against that kernel:
+  // 5120 x 27648 30.3 -> 28.7 us, 4096 x 14336 18.5 -> 16.2, 3584 x 18944 18.5 -> 16.5, 896 x 4864 equal; at batch 2
+  // (one grid row per batch row: the weights cross L2 twice) 41.2 -> 47.2 us, so two rows stay on the float kernel.
+  if (w->type == CAI_TYPE_Q4_0 && !indexed && a.batch == 1 && (w->k % 64) == 0 && q4i_smem_bytes(w->k) <= 160 * 1024 &&
+      (!a.norm_gain || ((uintptr_t)a.norm_gain % 16) == 0) && env_int("CAI_GEMV_Q4I", 1) != 0) {
+    GemvParams pq = p;
+    pq.norm_gain = a.norm_gain; pq.norm_eps = a.norm_eps;
+    CAI_TRY(launch_q4i(ctx, pq, (a.epilogue == EPI_SWIGLU) ? units : (units + 1) / 2, (unsigned)a.batch));
+    CAI_LAUNCHED(ctx);
+    return CAI_OK;
+  }
   // batch tile
   int nb = 1;
   if (!indexed) nb = a.batch >= 5 ? 8 : (a.batch >= 3 ? 4 : (a.batch == 2 ? 2 : 1));
